@@ -1,0 +1,273 @@
+/*
+ * pom_b200 — C ABI of the B200 (sm_100a) Polynomial-Mixer kernels.
+ *
+ * Every entry point
+ *   - takes plain device pointers, sizes and strides (in elements) and a CUDA stream
+ *     handle (`void*` == cudaStream_t); nothing in a signature depends on PyTorch;
+ *   - only enqueues work on that stream: no allocation, no synchronisation, no host
+ *     read of device memory, no retained pointer;
+ *   - returns 0 on success or a negative POM_ERR_* code (see pom_strerror);
+ *   - reports device-side problems (a bounded wait that expired) through the optional
+ *     `status` word in device memory, which stays 0 when all is well.
+ *
+ * The caller owns all memory: inputs, outputs, saved activations, partial-sum
+ * workspaces and the status word.
+ *
+ * Reference interface replaced (paths inside davidpicard/pom):
+ *   pom/pom.py:52-100    polynomial_aggregation_      -> pom_poly_agg_fwd / pom_poly_agg_bwd
+ *   pom/pom.py:103-122   polynomial_selection_        -> pom_select_fwd / pom_select_bwd
+ *   pom/pom.py:193-231   PoM._get_h_s + PoM.forward   -> pom_ctx_gemm + pom_reduce_partials +
+ *                                                        pom_gate_gemm + pom_gemm (output projection)
+ *   pom/pom.py:233-262   PoM.state_forward            -> the same, with pom_state_merge in between
+ *   pom/pom_rope.py:152-235, 443-526 (RoPE variants)  -> the `rope` member of the operator arguments
+ *   pom/pom_triton*.py   poly_agg_*_triton            -> pom_poly_agg_fwd / pom_poly_agg_bwd
+ */
+#ifndef POM_B200_H_
+#define POM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define POM_ABI_VERSION 1
+
+enum {
+  POM_OK = 0,
+  POM_ERR_BAD_SHAPE = -1,
+  POM_ERR_BAD_STRIDE = -2,
+  POM_ERR_BAD_ALIGN = -3,
+  POM_ERR_UNSUPPORTED = -4,
+  POM_ERR_K_TOO_LARGE = -5,
+  POM_ERR_CUDA = -6,
+  POM_ERR_TIMEOUT = -7,
+  POM_ERR_NULL = -8,
+  POM_ERR_TOO_LARGE = -9
+};
+
+enum { POM_BF16 = 0, POM_F32 = 1 };
+enum { POM_ROPE_NONE = 0, POM_ROPE_1D = 1, POM_ROPE_2D = 2 };
+enum { POM_OUT_BF16 = 0, POM_OUT_F32 = 1, POM_OUT_F32_ACCUM = 2 };
+
+int pom_abi_version(void);
+const char* pom_strerror(int code);
+/* 0 when the current device is an sm_100 part the kernels can run on. */
+int pom_device_check(void);
+/* Number of kernels this library has launched since load (all entry points). */
+long long pom_launch_count(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Rotary position description shared by the operators (reference pom/pom_rope.py:93-235).
+ * 1-D: cos0/sin0 are (max_len, P/2) tables, pos is (N) int64, pos_stride 1.
+ * 2-D: cos0/sin0 are the row tables (max_h, P/4), cos1/sin1 the column tables (max_w, P/4),
+ *      pos is (N, 2) int64 (row, col), pos_stride 2.
+ * `max0`/`max1` are the table heights, used to validate nothing on the device (positions are
+ * trusted) but checked on the host side of the Python layer.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct pom_rope {
+  int32_t kind; /* POM_ROPE_* */
+  int32_t pos_stride;
+  const float* cos0;
+  const float* sin0;
+  const float* cos1;
+  const float* sin1;
+  const int64_t* pos;
+} pom_rope;
+
+/* ------------------------------------------------------------------------------------------
+ * Tensor-core GEMM (tcgen05, bf16 inputs, fp32 accumulate):
+ *     C[b, m, n] = alpha * sum_k A[b, m, k] * Bm[n, k]
+ * A is (batches, M, K) with row stride lda (K-major) or, when a_mn_major, stored as (K, M)
+ * with row stride lda (batches must be 1).  Bm is (N, K) row stride ldb, or when b_mn_major
+ * stored as (K, N).  C is (batches*M, N) row stride ldc; out_mode selects bf16 store, fp32
+ * store, or fp32 accumulate (the only mode in which split_k > 1 is allowed; C must be
+ * zeroed or hold the value to accumulate onto).  split_k == 0 picks a split automatically
+ * in accumulate mode.  All leading dimensions and base addresses must be multiples of
+ * 8 elements / 16 bytes.
+ * Replaces: the cuBLAS calls behind nn.Linear in pom/pom.py:187,191,205,231 and their autograd.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct pom_gemm_args {
+  const void* A;
+  const void* Bm;
+  void* C;
+  int64_t M, N, K;
+  int64_t lda, ldb, ldc;
+  int32_t batches;
+  int32_t a_mn_major, b_mn_major;
+  int32_t out_mode;
+  int32_t split_k;
+  float alpha;
+} pom_gemm_args;
+int pom_gemm_bf16(const pom_gemm_args* a, int* status, void* stream);
+
+/* fp32 SIMT GEMM with the same meaning (fp32 A, Bm, C; out_mode F32 or F32_ACCUM); used by the
+ * fp32 precision mode, where tensor-core inputs would not meet the 1e-4 bound. */
+int pom_gemm_f32(const pom_gemm_args* a, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Context phase, fused (bf16): hp = X·Wpoᵀ on tensor cores; the epilogue rounds hp to bf16,
+ * optionally saves it, applies act + polynomial (+ per-token weight) and reduces over each
+ * 128-token tile.  partial is (B * ceil(N/128), P) fp32; reduce it with pom_reduce_partials.
+ * Replaces: pom/pom.py:205-206 + pom/pom.py:83-91 / 35-38 (and pom_triton.py:68-153).
+ * ------------------------------------------------------------------------------------------ */
+typedef struct pom_ctx_args {
+  const void* X;       /* (B, N, D) bf16, row stride ldx */
+  const void* Wpo;     /* (P, D) bf16, row stride ldw */
+  const float* coeff;  /* (P, K) fp32 */
+  const float* row_weight; /* (B, N) fp32 or NULL */
+  void* hp_out;        /* (B*N, ld_hp) bf16 or NULL */
+  float* partial;      /* (B * ceil(N/128), P) fp32 */
+  int64_t ldx, ldw, ld_hp;
+  int32_t B, N, D, P, K;
+} pom_ctx_args;
+int pom_ctx_gemm(const pom_ctx_args* a, int* status, void* stream);
+
+/* out[b, p] = scale * inv_denom[b] * sum_c partial[b, c, p]   (inv_denom may be NULL) */
+int pom_reduce_partials(const float* partial, float* out, const float* inv_denom, float scale, int32_t B,
+                        int32_t chunks, int32_t P, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Query phase, fused (bf16): z = X·Wseᵀ; epilogue saves bf16 z (optional) and writes
+ * SH = hardsigmoid(z + bias) ⊙ H as bf16.  H is fp32 with h_batch_stride / h_row_stride
+ * (row stride 0: one vector per sample).
+ * Replaces: pom/pom.py:207 + pom/pom.py:116-118.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct pom_gate_args {
+  const void* X;      /* (B, T, D) bf16 */
+  const void* Wse;    /* (P, D) bf16 */
+  const float* bias;  /* (P) fp32 */
+  const float* H;     /* fp32 */
+  void* z_out;        /* (B*T, ld_z) bf16 or NULL */
+  void* sh_out;       /* (B*T, ld_sh) bf16 */
+  int64_t ldx, ldw, ld_z, ld_sh;
+  int64_t h_batch_stride, h_row_stride;
+  int32_t B, T, D, P;
+} pom_gate_args;
+int pom_gate_gemm(const pom_gate_args* a, int* status, void* stream);
+
+/* Backward of the query phase (bf16): dSH = dY·Wo on tensor cores; the epilogue re-reads z and
+ * emits dz (bf16, written at g_out with row stride ld_g), and per-tile column sums of
+ * dSH ⊙ s (-> dh_partial) and of dz (-> db_partial), both (B * ceil(T/128), P) fp32.
+ * Replaces: autograd of pom/pom.py:207, 116-118, 231 (input-gradient half). */
+typedef struct pom_gate_bwd_args {
+  const void* dY;     /* (B, T, D) bf16 */
+  const void* Wo;     /* (D, P) bf16, row stride ldw */
+  const float* bias;
+  const float* H;     /* (B, P) fp32, h_batch_stride */
+  const void* z;      /* (B*T, ld_z) bf16 */
+  void* g_out;        /* (B*T, ld_g) bf16 */
+  float* dh_partial;
+  float* db_partial;
+  int64_t ld_dy, ldw, ld_z, ld_g, h_batch_stride;
+  int32_t B, T, D, P;
+} pom_gate_bwd_args;
+int pom_gate_bwd_gemm(const pom_gate_bwd_args* a, int* status, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Stand-alone aggregation operator (any dtype, optional rotary embedding):
+ *   poly[b,n,:] = R_n · polynomial(act(x[b,n,:]))
+ *   causal == 0 : out[b, :]    = sum_n w[b,n] * poly[b,n,:]             -> `partial` then reduce
+ *   causal == 1 : out[b, n, :] = (carry[b,:] + sum_{m<=n} poly[b,m,:]) / (n + 1 + token_offset)
+ * Non-causal: the kernel writes per-chunk sums into partial (B, chunks, P); call
+ * pom_reduce_partials.  Causal: `partial` (B, chunks, P) is scratch; out is (B, N, P) of dtype.
+ * chunks = pom_agg_chunks(N).
+ * Replaces: pom/pom.py:83-100 and the kernels of pom/pom_triton.py, pom_triton_causal.py,
+ * pom_triton_masked.py, pom_triton_rope.py (forward halves).
+ * ------------------------------------------------------------------------------------------ */
+int32_t pom_agg_chunks(int32_t N);
+
+typedef struct pom_agg_args {
+  const void* x;        /* (B, N, P) dtype, row stride ldx */
+  const float* coeff;   /* (P, K) fp32 */
+  const float* row_weight; /* (B, N) fp32 or NULL; non-causal only */
+  const float* carry;   /* (B, P) fp32 or NULL; causal only: sum over tokens of earlier shards */
+  float* partial;       /* (B, chunks, P) fp32 */
+  void* out;            /* causal only: (B, N, P) dtype, row stride ld_out */
+  float* total;         /* causal only, optional: (B, P) fp32 sum over this call's tokens */
+  int64_t ldx, ld_out;
+  int64_t token_offset; /* global index of token 0 (causal) */
+  int32_t B, N, P, K;
+  int32_t dtype, causal;
+  pom_rope rope;
+} pom_agg_args;
+int pom_poly_agg_fwd(const pom_agg_args* a, void* stream);
+
+/* Backward of the aggregation operator.
+ *   causal == 0 : dH (B, P) fp32 is the gradient of out; token weight = row_weight[b,n] * inv_denom[b]
+ *                 (either may be NULL = 1); `scale` multiplies everything (1/N for a plain mean).
+ *   causal == 1 : dout (B, N, P) dtype; `carry` (B, P) fp32 optional = suffix sum from later shards;
+ *                 `total` optional output (B, P): this shard's sum of dout[n]/(n+1+offset).
+ * Outputs: dx (B, N, P) dtype row stride ld_dx; dcoeff_partial (B*chunks, P, K) fp32, to be
+ * reduced with pom_reduce_partials(B=1, chunks=B*chunks, P=P*K).
+ * Replaces: backward halves of the kernels named above. */
+typedef struct pom_agg_bwd_args {
+  const void* x;
+  const float* coeff;
+  const float* row_weight;
+  const float* inv_denom;
+  const float* dH;      /* non-causal */
+  const void* dout;     /* causal */
+  const float* carry;
+  float* partial;       /* causal scratch (B, chunks, P) */
+  float* total;
+  void* dx;
+  float* dcoeff_partial;
+  int64_t ldx, ld_dx, ld_dout;
+  int64_t token_offset;
+  float scale;
+  int32_t B, N, P, K;
+  int32_t dtype, causal;
+  pom_rope rope;
+} pom_agg_bwd_args;
+int pom_poly_agg_bwd(const pom_agg_bwd_args* a, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Selection operator: SH[b,t,:] = R_t·hardsigmoid(z[b,t,:] + bias) ⊙ H[b, t or 0, :]
+ * H is fp32 (B, P) when h_per_token == 0, else (B, T, P) of dtype with row stride ld_h.
+ * Replaces: pom/pom.py:207 (+ se_bias), pom/pom_rope.py:522, pom/pom.py:116-118.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct pom_select_args {
+  const void* z;       /* (B, T, P) dtype, row stride ld_z */
+  const float* bias;   /* (P) fp32 */
+  const void* H;
+  void* sh;            /* (B, T, P) dtype, row stride ld_sh */
+  int64_t ld_z, ld_h, ld_sh;
+  int32_t B, T, P;
+  int32_t dtype, h_per_token;
+  pom_rope rope;
+} pom_select_args;
+int pom_select_fwd(const pom_select_args* a, void* stream);
+
+/* Backward: given dSH, emits dz (dtype, row stride ld_dz), dbias partial sums
+ * (B*chunks, P) and either dH partial sums (B, chunks, P) fp32 (h_per_token == 0) or the
+ * per-token dH (B, T, P) dtype row stride ld_dh. */
+typedef struct pom_select_bwd_args {
+  const void* dsh;
+  const void* z;
+  const float* bias;
+  const void* H;
+  void* dz;
+  float* dbias_partial;
+  float* dh_partial;
+  void* dh_tok;
+  int64_t ld_dsh, ld_z, ld_h, ld_dz, ld_dh;
+  int32_t B, T, P;
+  int32_t dtype, h_per_token;
+  pom_rope rope;
+} pom_select_bwd_args;
+int pom_select_bwd(const pom_select_bwd_args* a, void* stream);
+
+/* Running-mean state update of state_forward (reference pom/pom.py:255-259):
+ *   h_new[b,:] = (n_past * h_past[b,:] + h_cur[b,:]) / (n_past + 1)        (fp32, B*P elements) */
+int pom_state_merge(const float* h_past, const float* h_cur, float* h_new, float n_past, int64_t count, void* stream);
+
+/* Element conversion helpers (count elements): fp32 -> bf16, bf16 -> fp32. */
+int pom_cast_f32_to_bf16(const float* src, void* dst, int64_t count, void* stream);
+int pom_cast_bf16_to_f32(const void* src, float* dst, int64_t count, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* POM_B200_H_ */

@@ -1,0 +1,547 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a: TMA-fed tcgen05.mma with
+// fp32 accumulators in tensor memory and a pluggable epilogue.
+//
+//   C[m, n] = sum_k A[m, k] * B[n, k]
+//
+// Either operand may be K-major (rows of K contiguous in memory) or MN-major
+// (the matrix is stored transposed: rows indexed by k, M or N contiguous), so
+// the same kernel covers the projections (X·Wᵀ), the data-gradient products
+// (G·W) and the weight-gradient products (Gᵀ·X) of the PoM layer without any
+// transposed copy.
+//
+// CTA layout (192 threads, one CTA per SM):
+//   warp 0      : TMA producer   (one lane issues the tile loads)
+//   warp 1      : MMA issuer     (one lane issues tcgen05.mma / commit); owns TMEM alloc
+//   warps 2..5  : epilogue       (each reads one 32-lane quarter of the accumulator)
+// The accumulator is double-buffered in tensor memory (2 x BN fp32 columns), so
+// the epilogue of tile i overlaps the main loop of tile i+1.
+//
+// M tiles never straddle a batch: the A operand is addressed as (k, row, batch)
+// and rows past the end of a batch are zero-filled by TMA, which lets epilogues
+// reduce over the tokens of one sample without segmenting.
+#pragma once
+#include "ptx_sm100.cuh"
+#include "pom_math.cuh"
+
+namespace pomk {
+
+constexpr int kBM = 128;          // rows per tile (= TMEM lanes)
+constexpr int kBK = 64;           // K elements per pipeline stage (= one 128-byte swizzle row)
+constexpr int kGemmThreads = 192;
+constexpr int kEpiThreads = 128;
+constexpr int kEpiBarrier = 1;
+
+enum GemmStatus : int {
+  kStatusOk = 0,
+  kStatusProducerTimeout = 101,
+  kStatusMmaTimeout = 102,
+  kStatusEpilogueTimeout = 103,
+};
+
+struct GemmGeom {
+  int batches;            // independent row blocks of A / C (1 for a flat GEMM)
+  int rows_per_batch;     // rows of A / C inside one batch
+  int m_tiles_per_batch;  // ceil(rows_per_batch / 128)
+  int n_tiles;            // ceil(n_cols / BN)
+  int n_cols;             // columns of C
+  int k_blocks;           // ceil(K / 64)
+  int kb_per_split;       // k blocks handled by one split (== k_blocks when split_k == 1)
+  int split_k;            // number of K splits (each split has at least one k block)
+  int group_m;            // rasterisation: m tiles per band
+};
+
+struct TileCtx {
+  int b;           // batch
+  int mt;          // m tile inside the batch
+  int row0;        // first row inside the batch
+  int rows_valid;  // valid rows of this tile (1..128)
+  int col0;        // first column of C
+  int split;       // K split index
+};
+
+__device__ __forceinline__ TileCtx decode_tile(const GemmGeom& g, int unit, int bn) {
+  TileCtx t;
+  const int tiles_m = g.batches * g.m_tiles_per_batch;
+  const int per_split = tiles_m * g.n_tiles;
+  t.split = unit / per_split;
+  int u = unit - t.split * per_split;
+  // Bands of group_m m-tiles; inside a band consecutive units walk m first so
+  // concurrently running CTAs share B tiles through L2 and reuse A tiles.
+  const int band_sz = g.group_m * g.n_tiles;
+  const int band = u / band_sz;
+  const int in_band = u - band * band_sz;
+  const int m_lo = band * g.group_m;
+  const int band_rows = min(g.group_m, tiles_m - m_lo);
+  const int n = in_band / band_rows;
+  const int m = m_lo + (in_band - n * band_rows);
+  t.b = m / g.m_tiles_per_batch;
+  t.mt = m - t.b * g.m_tiles_per_batch;
+  t.row0 = t.mt * kBM;
+  t.rows_valid = min(kBM, g.rows_per_batch - t.row0);
+  t.col0 = n * bn;
+  return t;
+}
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int kABytes = kBM * kBK * 2;  // 16 KiB
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+};
+
+template <int BN, int STAGES, int EPI_SMEM>
+constexpr int gemm_smem_bytes() {
+  // tiles + barriers/holders (256 B) + epilogue scratch + 1 KiB alignment slack
+  return STAGES * GemmSmem<BN>::kStageBytes + 256 + EPI_SMEM + 1024;
+}
+
+// ---------------------------------------------------------------------------
+// The kernel.  `Epi` supplies:
+//   struct Params;                      trivially copyable, passed by value
+//   static constexpr int kSmemBytes;    scratch shared by the 4 epilogue warps
+//   template<int BN> static __device__ void run(const Params&, const GemmGeom&, const TileCtx&,
+//        uint32_t tmem_acc, int quarter, int lane, int epi_tid, float* scratch, int tile_iter);
+// ---------------------------------------------------------------------------
+template <int BN, int STAGES, bool A_MN, bool B_MN, class Epi>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const GemmGeom geom, const typename Epi::Params ep, int* __restrict__ status) {
+  static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "BN must be 64..256 in steps of 64");
+  constexpr int kABytes = GemmSmem<BN>::kABytes;
+  constexpr int kBBytes = GemmSmem<BN>::kBBytes;
+  constexpr int kStageBytes = GemmSmem<BN>::kStageBytes;
+  constexpr uint32_t kTmemCols = (2 * BN <= 128) ? 128u : (2 * BN <= 256) ? 256u : 512u;
+  constexpr uint32_t kIdesc = make_idesc_bf16(BN, A_MN, B_MN);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* tiles = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * kStageBytes);
+  uint64_t* full_bar = bars;                    // [STAGES]  TMA -> MMA
+  uint64_t* empty_bar = bars + STAGES;          // [STAGES]  MMA -> TMA
+  uint64_t* tfull_bar = bars + 2 * STAGES;      // [2]       MMA -> epilogue
+  uint64_t* tempty_bar = bars + 2 * STAGES + 2; // [2]       epilogue -> MMA
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  float* epi_scratch = reinterpret_cast<float*>(smem + STAGES * kStageBytes + 256);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  const int total_units = geom.batches * geom.m_tiles_per_batch * geom.n_tiles * geom.split_k;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool alive = true;
+      for (int unit = blockIdx.x; unit < total_units && alive; unit += gridDim.x) {
+        const TileCtx t = decode_tile(geom, unit, BN);
+        const int kb0 = t.split * geom.kb_per_split;
+        const int kb1 = min(geom.k_blocks, kb0 + geom.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, status, kStatusProducerTimeout)) {
+            alive = false;
+            break;
+          }
+          uint8_t* sa = tiles + stage * kStageBytes;
+          uint8_t* sb = sa + kABytes;
+          mbar_expect_tx(&full_bar[stage], kStageBytes);
+          if constexpr (!A_MN) {
+            tma_load_3d(sa, &tmA, &full_bar[stage], kb * kBK, t.row0, t.b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < kBM / 64; ++j)
+              tma_load_2d(sa + j * (kBK * 128), &tmA, &full_bar[stage], t.row0 + j * 64, kb * kBK);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d(sb, &tmB, &full_bar[stage], kb * kBK, t.col0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(sb + j * (kBK * 128), &tmB, &full_bar[stage], t.col0 + j * 64, kb * kBK);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!alive) {
+        // Give loads already in flight time to land before the CTA retires.
+        for (int i = 0; i < 64; ++i) __nanosleep(2000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int iter = 0;
+      bool alive = true;
+      for (int unit = blockIdx.x; unit < total_units && alive; unit += gridDim.x, ++iter) {
+        const TileCtx t = decode_tile(geom, unit, BN);
+        const int kb0 = t.split * geom.kb_per_split;
+        const int kb1 = min(geom.k_blocks, kb0 + geom.kb_per_split);
+        const int acc = iter & 1;
+        const uint32_t acc_phase = (iter >> 1) & 1u;
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_flag, status, kStatusMmaTimeout)) {
+          alive = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, status, kStatusMmaTimeout)) {
+            alive = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(tiles + stage * kStageBytes);
+          const uint32_t sb = sa + kABytes;
+#pragma unroll
+          for (int k16 = 0; k16 < kBK / 16; ++k16) {
+            // K-major: step 16 elements (32 B) inside the swizzled 128 B row.
+            // MN-major: step 16 k-rows = two 8-row atoms (2048 B).
+            const uint64_t da = A_MN ? make_smem_desc(sa + k16 * 2048, kBK * 128, 1024)
+                                     : make_smem_desc(sa + k16 * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc(sb + k16 * 2048, kBK * 128, 1024)
+                                     : make_smem_desc(sb + k16 * 32, 16, 1024);
+            umma_bf16(tmem_d, da, db, kIdesc, (kb > kb0 || k16 > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (alive) umma_commit(&tfull_bar[acc]);  // accumulator complete
+      }
+      if (!alive) {
+        for (int i = 0; i < 64; ++i) __nanosleep(2000);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) are readable by this warp
+    const int epi_tid = quarter * 32 + lane;
+    int iter = 0;
+    for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x, ++iter) {
+      const TileCtx t = decode_tile(geom, unit, BN);
+      const int acc = iter & 1;
+      const uint32_t acc_phase = (iter >> 1) & 1u;
+      // All 32 lanes poll so the warp stays converged for the .aligned TMEM loads.
+      bool ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, status, kStatusEpilogueTimeout);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(acc * BN) + (static_cast<uint32_t>(quarter * 32) << 16);
+      Epi::template run<BN>(ep, geom, t, tmem_acc, quarter, lane, epi_tid, epi_scratch, iter);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ===========================================================================
+// Epilogues
+// ===========================================================================
+
+// Store 32 consecutive fp32 values of one row as bf16 (64 bytes, 16-byte vector stores).
+__device__ __forceinline__ void store_row32_bf16(__nv_bfloat16* dst, const float (&v)[32], int ncols_left) {
+  if (ncols_left >= 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint4 q;
+      q.x = pack_bf16x2(v[8 * j + 0], v[8 * j + 1]);
+      q.y = pack_bf16x2(v[8 * j + 2], v[8 * j + 3]);
+      q.z = pack_bf16x2(v[8 * j + 4], v[8 * j + 5]);
+      q.w = pack_bf16x2(v[8 * j + 6], v[8 * j + 7]);
+      d4[j] = q;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < ncols_left) dst[i] = __float2bfloat16_rn(v[i]);
+  }
+}
+
+__device__ __forceinline__ void load_row32_bf16(const __nv_bfloat16* src, float (&v)[32], int ncols_left) {
+  if (ncols_left >= 32 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+    const uint4* s4 = reinterpret_cast<const uint4*>(src);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint4 q = __ldg(&s4[j]);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float2 f = __bfloat1622float2(h[e]);
+        v[8 * j + 2 * e] = f.x;
+        v[8 * j + 2 * e + 1] = f.y;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = (i < ncols_left) ? __bfloat162float(src[i]) : 0.f;
+  }
+}
+
+__device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+// --------------------------------------------------------------- plain store
+struct EpiStore {
+  struct Params {
+    void* C;             // bf16 or fp32, row-major
+    long long ldc;       // elements
+    long long batch_stride;  // elements between batches
+    int mode;            // 0: bf16 store, 1: fp32 store, 2: fp32 atomic add (split-K)
+    float alpha;
+  };
+  static constexpr int kSmemBytes = 0;
+
+  template <int BN>
+  static __device__ __forceinline__ void run(const Params& p, const GemmGeom& g, const TileCtx& t, uint32_t tmem_acc,
+                                             int quarter, int lane, int, float*, int) {
+    const int row = quarter * 32 + lane;
+    const bool row_ok = row < t.rows_valid;
+    const long long off = static_cast<long long>(t.b) * p.batch_stride + static_cast<long long>(t.row0 + row) * p.ldc;
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      const int col = t.col0 + c * 32;
+      if (col >= g.n_cols) break;  // warp-uniform
+      float v[32];
+      tmem_ld32(tmem_acc + c * 32, v);
+      tmem_ld_wait();
+      const int left = g.n_cols - col;
+      if (!row_ok) continue;
+      if (p.alpha != 1.f) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] *= p.alpha;
+      }
+      if (p.mode == 0) {
+        store_row32_bf16(reinterpret_cast<__nv_bfloat16*>(p.C) + off + col, v, left);
+      } else {
+        float* dst = reinterpret_cast<float*>(p.C) + off + col;
+        if (p.mode == 1) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (i < left) dst[i] = v[i];
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (i < left) atomicAdd(dst + i, v[i]);
+        }
+      }
+    }
+  }
+};
+
+// --------------------------------------------------------------- context phase
+// acc = X·Wpoᵀ.  Rounds to bf16 (what the backward pass will re-read), stores it
+// when asked, applies act + polynomial (+ per-token weight), and reduces over the
+// tile's tokens.  Per-tile column sums go to `partial[(b * MT + mt), :]` in a
+// fixed order, so the result is run-to-run deterministic.
+struct EpiCtx {
+  struct Params {
+    const float* coeff;        // (P, K) fp32
+    int K;
+    const float* row_weight;   // (B, rows_per_batch) fp32 or null (key-padding mask weights)
+    __nv_bfloat16* hp_out;     // (B*rows, ld_hp) or null
+    long long ld_hp;
+    float* partial;            // (B * MT, P) fp32
+    int P;
+  };
+  static constexpr int kSmemBytes = 2 * 4 * 256 * 4;  // two buffers of [4 quarters][256 cols]
+
+  template <int BN>
+  static __device__ __forceinline__ void run(const Params& p, const GemmGeom& g, const TileCtx& t, uint32_t tmem_acc,
+                                             int quarter, int lane, int epi_tid, float* scratch, int iter) {
+    const int row = quarter * 32 + lane;
+    const bool row_ok = row < t.rows_valid;
+    const long long grow = static_cast<long long>(t.b) * g.rows_per_batch + t.row0 + row;
+    float w = row_ok ? 1.f : 0.f;
+    if (row_ok && p.row_weight) w = __ldg(p.row_weight + grow);
+    float* buf = scratch + (iter & 1) * (4 * 256);
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      const int col = t.col0 + c * 32;
+      if (col >= g.n_cols) {  // warp-uniform
+        buf[quarter * 256 + c * 32 + lane] = 0.f;
+        continue;
+      }
+      float v[32];
+      tmem_ld32(tmem_acc + c * 32, v);
+      tmem_ld_wait();
+      const int left = g.n_cols - col;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = round_bf16(v[i]);
+      if (p.hp_out && row_ok) store_row32_bf16(p.hp_out + grow * p.ld_hp + col, v, left);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const int ci = min(col + i, g.n_cols - 1);
+        v[i] = (i < left) ? w * pom_poly(pom_act(v[i]), p.coeff + static_cast<long long>(ci) * p.K, p.K) : 0.f;
+      }
+      warp_colsum32(v, lane);
+      buf[quarter * 256 + c * 32 + lane] = v[0];
+    }
+    named_bar_sync(kEpiBarrier, kEpiThreads);
+    for (int c = epi_tid; c < BN; c += kEpiThreads) {
+      const int col = t.col0 + c;
+      if (col < g.n_cols) {
+        const float s = (buf[c] + buf[256 + c]) + (buf[512 + c] + buf[768 + c]);
+        p.partial[(static_cast<long long>(t.b) * g.m_tiles_per_batch + t.mt) * p.P + col] = s;
+      }
+    }
+  }
+};
+
+// --------------------------------------------------------------- query phase
+// acc = X·Wseᵀ.  z = bf16(acc) is kept for the backward pass; the gated feature
+// s ⊙ H with s = hardsigmoid(z + bias) is written as bf16, ready to be the A
+// operand of the output projection.  H is addressed per (batch, row) with strides
+// so both the broadcast (B, P) state and a per-token (B, T, P) prefix are covered.
+struct EpiGate {
+  struct Params {
+    const float* bias;       // (P) fp32
+    const float* H;          // fp32
+    long long h_batch_stride;
+    long long h_row_stride;  // 0 when H is one vector per batch
+    __nv_bfloat16* z_out;    // null in inference
+    long long ld_z;
+    __nv_bfloat16* sh_out;
+    long long ld_sh;
+  };
+  static constexpr int kSmemBytes = 0;
+
+  template <int BN>
+  static __device__ __forceinline__ void run(const Params& p, const GemmGeom& g, const TileCtx& t, uint32_t tmem_acc,
+                                             int quarter, int lane, int, float*, int) {
+    const int row = quarter * 32 + lane;
+    const bool row_ok = row < t.rows_valid;
+    const long long grow = static_cast<long long>(t.b) * g.rows_per_batch + t.row0 + row;
+    const float* hrow = p.H + static_cast<long long>(t.b) * p.h_batch_stride +
+                        static_cast<long long>(row_ok ? t.row0 + row : t.row0) * p.h_row_stride;
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      const int col = t.col0 + c * 32;
+      if (col >= g.n_cols) break;
+      float v[32];
+      tmem_ld32(tmem_acc + c * 32, v);
+      tmem_ld_wait();
+      const int left = g.n_cols - col;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = round_bf16(v[i]);
+      if (p.z_out && row_ok) store_row32_bf16(p.z_out + grow * p.ld_z + col, v, left);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const int ci = min(col + i, g.n_cols - 1);
+        v[i] = pom_hardsigmoid(v[i] + __ldg(p.bias + ci)) * __ldg(hrow + ci);
+      }
+      if (row_ok) store_row32_bf16(p.sh_out + grow * p.ld_sh + col, v, left);
+    }
+  }
+};
+
+// --------------------------------------------------------------- query phase, backward
+// acc = dY·Wo = dSH.  With z re-read from the forward pass:
+//   s  = hardsigmoid(z + bias)
+//   dH partial  = sum_rows dSH ⊙ s                      -> dh_partial[(b*MT+mt), :]
+//   dz          = dSH ⊙ H ⊙ hardsigmoid'(z + bias)      -> g_out (bf16), the se half of [dhp | dz]
+//   dbias part. = sum_rows dz                            -> db_partial[(b*MT+mt), :]
+struct EpiGateBwd {
+  struct Params {
+    const float* bias;
+    const float* H;
+    long long h_batch_stride;
+    const __nv_bfloat16* z;
+    long long ld_z;
+    __nv_bfloat16* g_out;
+    long long ld_g;
+    float* dh_partial;
+    float* db_partial;
+    int P;
+  };
+  static constexpr int kSmemBytes = 2 * 2 * 4 * 256 * 4;
+
+  template <int BN>
+  static __device__ __forceinline__ void run(const Params& p, const GemmGeom& g, const TileCtx& t, uint32_t tmem_acc,
+                                             int quarter, int lane, int epi_tid, float* scratch, int iter) {
+    const int row = quarter * 32 + lane;
+    const bool row_ok = row < t.rows_valid;
+    const long long grow = static_cast<long long>(t.b) * g.rows_per_batch + t.row0 + (row_ok ? row : 0);
+    const float* hrow = p.H + static_cast<long long>(t.b) * p.h_batch_stride;
+    float* buf_h = scratch + (iter & 1) * (2 * 4 * 256);
+    float* buf_b = buf_h + 4 * 256;
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      const int col = t.col0 + c * 32;
+      if (col >= g.n_cols) {
+        buf_h[quarter * 256 + c * 32 + lane] = 0.f;
+        buf_b[quarter * 256 + c * 32 + lane] = 0.f;
+        continue;
+      }
+      float v[32], z[32];
+      tmem_ld32(tmem_acc + c * 32, v);
+      const int left = g.n_cols - col;
+      load_row32_bf16(p.z + grow * p.ld_z + col, z, left);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const int ci = min(col + i, g.n_cols - 1);
+        const float zz = z[i] + __ldg(p.bias + ci);
+        const float dsh = (row_ok && i < left) ? v[i] : 0.f;
+        z[i] = dsh * __ldg(hrow + ci) * pom_hardsigmoid_grad(zz);  // dz
+        v[i] = dsh * pom_hardsigmoid(zz);                           // dH contribution
+      }
+      if (row_ok) store_row32_bf16(p.g_out + grow * p.ld_g + col, z, left);
+      warp_colsum32(v, lane);
+      warp_colsum32(z, lane);
+      buf_h[quarter * 256 + c * 32 + lane] = v[0];
+      buf_b[quarter * 256 + c * 32 + lane] = z[0];
+    }
+    named_bar_sync(kEpiBarrier, kEpiThreads);
+    for (int c = epi_tid; c < BN; c += kEpiThreads) {
+      const int col = t.col0 + c;
+      if (col < g.n_cols) {
+        const long long o = (static_cast<long long>(t.b) * g.m_tiles_per_batch + t.mt) * p.P + col;
+        p.dh_partial[o] = (buf_h[c] + buf_h[256 + c]) + (buf_h[512 + c] + buf_h[768 + c]);
+        p.db_partial[o] = (buf_b[c] + buf_b[256 + c]) + (buf_b[512 + c] + buf_b[768 + c]);
+      }
+    }
+  }
+};
+
+}  // namespace pomk

@@ -1,0 +1,359 @@
+// Host launchers for the tcgen05 GEMM engine and its fused PoM epilogues, plus
+// the fp32 SIMT GEMM of the high-precision mode.
+#include <cudaTypedefs.h>
+#include <mutex>
+#include "common.cuh"
+#include "gemm_sm100.cuh"
+
+using namespace pomk;
+using namespace pomh;
+
+namespace pomh {
+std::atomic<long long> g_launches{0};
+}
+
+namespace {
+
+// ---------------------------------------------------------------- tensor maps
+// cuTensorMapEncodeTiled is fetched through the runtime so the library has no
+// link-time dependency on the driver (it must load on machines without one).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// bf16 tensor of `rank` dims (innermost first), 128-byte swizzle, zero fill out of bounds.
+int make_map(CUtensorMap* m, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_elems,
+             const uint32_t* box) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return POM_ERR_CUDA;
+  if (!aligned16(base)) return POM_ERR_BAD_ALIGN;
+  cuuint64_t gdim[3];
+  cuuint64_t gstr[2];
+  cuuint32_t bx[3];
+  cuuint32_t es[3] = {1, 1, 1};
+  for (int i = 0; i < rank; ++i) {
+    if (dims[i] == 0) return POM_ERR_BAD_SHAPE;
+    gdim[i] = dims[i];
+    bx[i] = box[i];
+    if (box[i] == 0 || box[i] > 256) return POM_ERR_BAD_SHAPE;
+  }
+  for (int i = 0; i + 1 < rank; ++i) {
+    uint64_t bytes = strides_elems[i] * 2ull;
+    if (bytes % 16 != 0) return POM_ERR_BAD_STRIDE;
+    if (bytes >= (1ull << 40)) return POM_ERR_TOO_LARGE;
+    gstr[i] = bytes;
+  }
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdim,
+                  gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? POM_OK : POM_ERR_CUDA;
+}
+
+struct Operands {
+  const void* A;
+  const void* Bm;
+  int64_t M, N, K;  // per batch rows, columns, reduction
+  int64_t lda, ldb;
+  int batches;
+  bool a_mn, b_mn;
+};
+
+int build_maps(const Operands& o, int bn, CUtensorMap* tmA, CUtensorMap* tmB) {
+  int rc;
+  if (!o.a_mn) {
+    uint64_t dims[3] = {static_cast<uint64_t>(o.K), static_cast<uint64_t>(o.M), static_cast<uint64_t>(o.batches)};
+    uint64_t str[2] = {static_cast<uint64_t>(o.lda), static_cast<uint64_t>(o.lda) * static_cast<uint64_t>(o.M)};
+    uint32_t box[3] = {static_cast<uint32_t>(kBK), static_cast<uint32_t>(kBM), 1};
+    rc = make_map(tmA, o.A, 3, dims, str, box);
+  } else {
+    if (o.batches != 1) return POM_ERR_UNSUPPORTED;
+    uint64_t dims[2] = {static_cast<uint64_t>(o.M), static_cast<uint64_t>(o.K)};
+    uint64_t str[1] = {static_cast<uint64_t>(o.lda)};
+    uint32_t box[2] = {64, static_cast<uint32_t>(kBK)};
+    rc = make_map(tmA, o.A, 2, dims, str, box);
+  }
+  if (rc) return rc;
+  if (!o.b_mn) {
+    uint64_t dims[2] = {static_cast<uint64_t>(o.K), static_cast<uint64_t>(o.N)};
+    uint64_t str[1] = {static_cast<uint64_t>(o.ldb)};
+    uint32_t box[2] = {static_cast<uint32_t>(kBK), static_cast<uint32_t>(bn)};
+    rc = make_map(tmB, o.Bm, 2, dims, str, box);
+  } else {
+    uint64_t dims[2] = {static_cast<uint64_t>(o.N), static_cast<uint64_t>(o.K)};
+    uint64_t str[1] = {static_cast<uint64_t>(o.ldb)};
+    uint32_t box[2] = {64, static_cast<uint32_t>(kBK)};
+    rc = make_map(tmB, o.Bm, 2, dims, str, box);
+  }
+  return rc;
+}
+
+GemmGeom make_geom(const Operands& o, int bn, int split_k) {
+  GemmGeom g;
+  g.batches = o.batches;
+  g.rows_per_batch = static_cast<int>(o.M);
+  g.m_tiles_per_batch = static_cast<int>(ceil_div(o.M, kBM));
+  g.n_tiles = static_cast<int>(ceil_div(o.N, bn));
+  g.n_cols = static_cast<int>(o.N);
+  g.k_blocks = static_cast<int>(ceil_div(o.K, kBK));
+  if (split_k < 1) split_k = 1;
+  if (split_k > g.k_blocks) split_k = g.k_blocks;
+  g.kb_per_split = static_cast<int>(ceil_div(g.k_blocks, split_k));
+  g.split_k = static_cast<int>(ceil_div(g.k_blocks, g.kb_per_split));
+  g.group_m = 8;
+  return g;
+}
+
+int check_operands(const Operands& o) {
+  if (!o.A || !o.Bm) return POM_ERR_NULL;
+  if (o.M <= 0 || o.N <= 0 || o.K <= 0 || o.batches <= 0) return POM_ERR_BAD_SHAPE;
+  if (o.M > INT32_MAX || o.N > INT32_MAX || o.K > INT32_MAX) return POM_ERR_TOO_LARGE;
+  if (o.lda % 8 || o.ldb % 8) return POM_ERR_BAD_STRIDE;
+  if ((!o.a_mn && o.lda < o.K) || (o.a_mn && o.lda < o.M)) return POM_ERR_BAD_STRIDE;
+  if ((!o.b_mn && o.ldb < o.K) || (o.b_mn && o.ldb < o.N)) return POM_ERR_BAD_STRIDE;
+  return POM_OK;
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN, class Epi>
+int launch(const Operands& o, int split_k, const typename Epi::Params& ep, int* status, cudaStream_t st) {
+  CUtensorMap tmA, tmB;
+  int rc = build_maps(o, BN, &tmA, &tmB);
+  if (rc) return rc;
+  GemmGeom g = make_geom(o, BN, split_k);
+  constexpr int smem = gemm_smem_bytes<BN, STAGES, Epi::kSmemBytes>();
+  auto kern = gemm_tcgen05_kernel<BN, STAGES, A_MN, B_MN, Epi>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return POM_ERR_CUDA;
+    }
+    attr_set = true;
+  }
+  const long long units = 1ll * g.batches * g.m_tiles_per_batch * g.n_tiles * g.split_k;
+  if (units > INT32_MAX) return POM_ERR_TOO_LARGE;
+  const int grid = static_cast<int>(units < sm_count() ? units : sm_count());
+  kern<<<grid, kGemmThreads, smem, st>>>(tmA, tmB, g, ep, status);
+  count_launch();
+  return check_launch();
+}
+
+// Majorness dispatch for one epilogue / tile width.
+template <int BN, int STAGES, class Epi>
+int launch_major(const Operands& o, int split_k, const typename Epi::Params& ep, int* status, cudaStream_t st) {
+  if (!o.a_mn && !o.b_mn) return launch<BN, STAGES, false, false, Epi>(o, split_k, ep, status, st);
+  if (!o.a_mn && o.b_mn) return launch<BN, STAGES, false, true, Epi>(o, split_k, ep, status, st);
+  if (o.a_mn && !o.b_mn) return launch<BN, STAGES, true, false, Epi>(o, split_k, ep, status, st);
+  return launch<BN, STAGES, true, true, Epi>(o, split_k, ep, status, st);
+}
+
+// Tile width: 256 columns when that wastes little of the last tile, else 128.
+int pick_bn(int64_t n) {
+  if (n <= 128) return 128;
+  const int64_t pad256 = ceil_div(n, 256) * 256 - n;
+  const int64_t pad128 = ceil_div(n, 128) * 128 - n;
+  return (pad256 <= pad128 + n / 16) ? 256 : 128;
+}
+
+// ---------------------------------------------------------------- fp32 SIMT GEMM
+// 64x64 tile, 16-deep k step, 256 threads with 4x4 outputs each.  Strided operand
+// access covers both storage orders.  Accuracy, not speed, is the purpose.
+__global__ void __launch_bounds__(256)
+sgemm_kernel(const float* __restrict__ A, const float* __restrict__ Bm, float* __restrict__ C, int M, int N, int K,
+             long long sam, long long sak, long long sbn, long long sbk, long long ldc, float alpha, int accumulate) {
+  __shared__ float As[16][64 + 1];
+  __shared__ float Bs[16][64 + 1];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < K; k0 += 16) {
+    for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+      // choose the faster-varying index to follow the contiguous dimension
+      int mm, kk;
+      if (sak == 1) {
+        kk = i & 15;
+        mm = i >> 4;
+      } else {
+        mm = i & 63;
+        kk = i >> 6;
+      }
+      const int gm = m0 + mm, gk = k0 + kk;
+      As[kk][mm] = (gm < M && gk < K) ? A[gm * sam + gk * sak] : 0.f;
+    }
+    for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+      int nn, kk;
+      if (sbk == 1) {
+        kk = i & 15;
+        nn = i >> 4;
+      } else {
+        nn = i & 63;
+        kk = i >> 6;
+      }
+      const int gn = n0 + nn, gk = k0 + kk;
+      Bs[kk][nn] = (gn < N && gk < K) ? Bm[gn * sbn + gk * sbk] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Bs[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int gm = m0 + ty * 4 + i;
+    if (gm >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int gn = n0 + tx * 4 + j;
+      if (gn >= N) continue;
+      float* c = C + static_cast<long long>(gm) * ldc + gn;
+      const float v = alpha * acc[i][j];
+      *c = accumulate ? (*c + v) : v;
+    }
+  }
+}
+
+}  // namespace
+
+// =========================================================================== C ABI
+extern "C" {
+
+int pom_gemm_bf16(const pom_gemm_args* a, int* status, void* stream) {
+  if (!a || !a->C) return POM_ERR_NULL;
+  Operands o{a->A, a->Bm, a->M, a->N, a->K, a->lda, a->ldb, a->batches, a->a_mn_major != 0, a->b_mn_major != 0};
+  int rc = check_operands(o);
+  if (rc) return rc;
+  if (a->out_mode < 0 || a->out_mode > 2) return POM_ERR_UNSUPPORTED;
+  if (a->ldc < a->N) return POM_ERR_BAD_STRIDE;
+  if (a->out_mode == POM_OUT_BF16 && (a->ldc % 8 || !aligned16(a->C))) return POM_ERR_BAD_ALIGN;
+  int split = a->split_k;
+  if (a->out_mode != POM_OUT_F32_ACCUM) {
+    if (split > 1) return POM_ERR_UNSUPPORTED;
+    split = 1;
+  }
+  const int bn = pick_bn(a->N);
+  if (split == 0) {
+    // Aim for about four waves of work units, keeping at least 8 k-blocks per split.
+    const long long tiles = 1ll * a->batches * ceil_div(a->M, kBM) * ceil_div(a->N, bn);
+    const long long kblocks = ceil_div(a->K, kBK);
+    long long want = ceil_div(4ll * sm_count(), tiles);
+    long long cap = kblocks / 8 > 0 ? kblocks / 8 : 1;
+    split = static_cast<int>(want < cap ? want : cap);
+    if (split < 1) split = 1;
+  }
+  EpiStore::Params ep;
+  ep.C = a->C;
+  ep.ldc = a->ldc;
+  ep.batch_stride = a->M * a->ldc;
+  ep.mode = a->out_mode;
+  ep.alpha = a->alpha;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (bn == 256) return launch_major<256, 4, EpiStore>(o, split, ep, status, st);
+  return launch_major<128, 6, EpiStore>(o, split, ep, status, st);
+}
+
+int pom_gemm_f32(const pom_gemm_args* a, void* stream) {
+  if (!a || !a->A || !a->Bm || !a->C) return POM_ERR_NULL;
+  if (a->M <= 0 || a->N <= 0 || a->K <= 0 || a->batches <= 0) return POM_ERR_BAD_SHAPE;
+  if (a->out_mode != POM_OUT_F32 && a->out_mode != POM_OUT_F32_ACCUM) return POM_ERR_UNSUPPORTED;
+  if (a->a_mn_major && a->batches != 1) return POM_ERR_UNSUPPORTED;
+  const long long Mtot = a->M * a->batches;
+  if (Mtot > INT32_MAX || a->N > INT32_MAX || a->K > INT32_MAX) return POM_ERR_TOO_LARGE;
+  const long long sam = a->a_mn_major ? 1 : a->lda, sak = a->a_mn_major ? a->lda : 1;
+  const long long sbn = a->b_mn_major ? 1 : a->ldb, sbk = a->b_mn_major ? a->ldb : 1;
+  dim3 grid(static_cast<unsigned>(ceil_div(a->N, 64)), static_cast<unsigned>(ceil_div(Mtot, 64)));
+  if (grid.y > 65535) return POM_ERR_TOO_LARGE;
+  sgemm_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const float*>(a->A), static_cast<const float*>(a->Bm), static_cast<float*>(a->C),
+      static_cast<int>(Mtot), static_cast<int>(a->N), static_cast<int>(a->K), sam, sak, sbn, sbk, a->ldc, a->alpha,
+      a->out_mode == POM_OUT_F32_ACCUM);
+  count_launch();
+  return check_launch();
+}
+
+int pom_ctx_gemm(const pom_ctx_args* a, int* status, void* stream) {
+  if (!a || !a->coeff || !a->partial) return POM_ERR_NULL;
+  if (a->K < 1) return POM_ERR_BAD_SHAPE;
+  Operands o{a->X, a->Wpo, a->N, a->P, a->D, a->ldx, a->ldw, a->B, false, false};
+  int rc = check_operands(o);
+  if (rc) return rc;
+  if (a->hp_out && (a->ld_hp % 8 || a->ld_hp < a->P || !aligned16(a->hp_out))) return POM_ERR_BAD_ALIGN;
+  EpiCtx::Params ep;
+  ep.coeff = a->coeff;
+  ep.K = a->K;
+  ep.row_weight = a->row_weight;
+  ep.hp_out = static_cast<__nv_bfloat16*>(a->hp_out);
+  ep.ld_hp = a->ld_hp;
+  ep.partial = a->partial;
+  ep.P = a->P;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (pick_bn(a->P) == 256) return launch<256, 4, false, false, EpiCtx>(o, 1, ep, status, st);
+  return launch<128, 6, false, false, EpiCtx>(o, 1, ep, status, st);
+}
+
+int pom_gate_gemm(const pom_gate_args* a, int* status, void* stream) {
+  if (!a || !a->bias || !a->H || !a->sh_out) return POM_ERR_NULL;
+  Operands o{a->X, a->Wse, a->T, a->P, a->D, a->ldx, a->ldw, a->B, false, false};
+  int rc = check_operands(o);
+  if (rc) return rc;
+  if (a->ld_sh % 8 || a->ld_sh < a->P || !aligned16(a->sh_out)) return POM_ERR_BAD_ALIGN;
+  if (a->z_out && (a->ld_z % 8 || a->ld_z < a->P || !aligned16(a->z_out))) return POM_ERR_BAD_ALIGN;
+  EpiGate::Params ep;
+  ep.bias = a->bias;
+  ep.H = a->H;
+  ep.h_batch_stride = a->h_batch_stride;
+  ep.h_row_stride = a->h_row_stride;
+  ep.z_out = static_cast<__nv_bfloat16*>(a->z_out);
+  ep.ld_z = a->ld_z;
+  ep.sh_out = static_cast<__nv_bfloat16*>(a->sh_out);
+  ep.ld_sh = a->ld_sh;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (pick_bn(a->P) == 256) return launch<256, 4, false, false, EpiGate>(o, 1, ep, status, st);
+  return launch<128, 6, false, false, EpiGate>(o, 1, ep, status, st);
+}
+
+int pom_gate_bwd_gemm(const pom_gate_bwd_args* a, int* status, void* stream) {
+  if (!a || !a->bias || !a->H || !a->z || !a->g_out || !a->dh_partial || !a->db_partial) return POM_ERR_NULL;
+  // dSH[t, p] = sum_d dY[t, d] * Wo[d, p]: the B operand is Wo stored (K = D rows, N = P columns).
+  Operands o{a->dY, a->Wo, a->T, a->P, a->D, a->ld_dy, a->ldw, a->B, false, true};
+  int rc = check_operands(o);
+  if (rc) return rc;
+  if (a->ld_g % 8 || !aligned16(a->g_out) || a->ld_z % 8 || !aligned16(a->z)) return POM_ERR_BAD_ALIGN;
+  EpiGateBwd::Params ep;
+  ep.bias = a->bias;
+  ep.H = a->H;
+  ep.h_batch_stride = a->h_batch_stride;
+  ep.z = static_cast<const __nv_bfloat16*>(a->z);
+  ep.ld_z = a->ld_z;
+  ep.g_out = static_cast<__nv_bfloat16*>(a->g_out);
+  ep.ld_g = a->ld_g;
+  ep.dh_partial = a->dh_partial;
+  ep.db_partial = a->db_partial;
+  ep.P = a->P;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (pick_bn(a->P) == 256) return launch<256, 4, false, true, EpiGateBwd>(o, 1, ep, status, st);
+  return launch<128, 6, false, true, EpiGateBwd>(o, 1, ep, status, st);
+}
+
+}  // extern "C"

@@ -1,0 +1,322 @@
+"""Thin tensor-level wrappers over the C ABI (no autograd here).
+
+Each function validates devices/dtypes, allocates outputs with PyTorch's caching
+allocator, and enqueues the kernel(s) on the current CUDA stream.  Nothing in this
+module computes on the CPU or with PyTorch operators.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _abi
+from ._abi import AggArgs, AggBwdArgs, CtxArgs, GateArgs, GateBwdArgs, GemmArgs, Rope, SelectArgs, SelectBwdArgs, ptr
+
+
+def _require_cuda(*tensors) -> torch.device:
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError("pom_b200 runs on CUDA tensors only (no CPU fallback)")
+        dev = dev or t.device
+        if t.device != dev:
+            raise RuntimeError("all tensors of one call must live on the same GPU")
+    return dev
+
+
+def _row_stride(t: torch.Tensor) -> int:
+    """Leading dimension of a 2-D or 3-D tensor whose last dim is contiguous and whose
+    leading dims collapse to one row index."""
+    if t.stride(-1) != 1:
+        raise ValueError("last dimension must be contiguous")
+    if t.dim() == 2:
+        return t.stride(0)
+    if t.dim() == 3:
+        if t.shape[0] > 1 and t.stride(0) != t.stride(1) * t.shape[1]:
+            raise ValueError("batch and token dimensions must collapse to one row stride")
+        return t.stride(1)
+    raise ValueError("expected a 2-D or 3-D tensor")
+
+
+@dataclass
+class RopeSpec:
+    """Rotary tables and positions for one side (context or query) of the layer."""
+    kind: int
+    cos0: torch.Tensor
+    sin0: torch.Tensor
+    pos: torch.Tensor  # int64, (N,) or (N, 2), contiguous
+    cos1: Optional[torch.Tensor] = None
+    sin1: Optional[torch.Tensor] = None
+
+    def to_c(self) -> Rope:
+        r = Rope()
+        r.kind = self.kind
+        r.pos_stride = 2 if self.kind == _abi.ROPE_2D else 1
+        r.cos0, r.sin0 = ptr(self.cos0), ptr(self.sin0)
+        r.cos1, r.sin1 = ptr(self.cos1), ptr(self.sin1)
+        r.pos = ptr(self.pos)
+        return r
+
+
+def _rope_c(spec: Optional[RopeSpec]) -> Rope:
+    if spec is None:
+        r = Rope()
+        r.kind = _abi.ROPE_NONE
+        r.pos_stride = 1
+        return r
+    return spec.to_c()
+
+
+# ---------------------------------------------------------------------------- GEMM
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+         accumulate: bool = False, split_k: int = 0, alpha: float = 1.0) -> torch.Tensor:
+    """C[m, n] = alpha * sum_k A[m, k] * B[n, k].
+
+    ``a`` is (M, K) — or (K, M) when ``a_mn`` — and ``b`` is (N, K) — or (K, N) when ``b_mn``;
+    both row-major with a contiguous last dimension.  bf16 inputs run on the tcgen05 kernel,
+    fp32 inputs on the SIMT kernel.  ``accumulate`` adds into a fp32 ``out``.
+    """
+    dev = _require_cuda(a, b, out)
+    if a.dtype != b.dtype:
+        raise TypeError("operand dtypes differ")
+    M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
+    N, Kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
+    if K != Kb:
+        raise ValueError(f"reduction dims differ: {K} vs {Kb}")
+    is_bf16 = a.dtype == torch.bfloat16
+    if out is None:
+        if accumulate:
+            raise ValueError("accumulate needs an output tensor")
+        odt = out_dtype or (torch.bfloat16 if is_bf16 else torch.float32)
+        out = torch.empty((M, N), dtype=odt, device=dev)
+    if out.shape != (M, N):
+        raise ValueError("output shape mismatch")
+    if accumulate and out.dtype != torch.float32:
+        raise TypeError("accumulate needs a float32 output")
+    g = GemmArgs()
+    g.A, g.Bm, g.C = ptr(a), ptr(b), ptr(out)
+    g.M, g.N, g.K = M, N, K
+    g.lda, g.ldb, g.ldc = _row_stride(a), _row_stride(b), _row_stride(out)
+    g.batches = 1
+    g.a_mn_major, g.b_mn_major = int(a_mn), int(b_mn)
+    g.out_mode = _abi.OUT_F32_ACCUM if accumulate else (_abi.OUT_BF16 if out.dtype == torch.bfloat16 else _abi.OUT_F32)
+    g.split_k = split_k if accumulate else 1
+    g.alpha = alpha
+    L = _abi.lib()
+    if is_bf16:
+        _abi.check(L.pom_gemm_bf16(C.byref(g), ptr(_abi.status_word(dev)), _abi.stream_ptr()), "pom_gemm_bf16")
+    else:
+        if a.dtype != torch.float32 or out.dtype != torch.float32:
+            raise TypeError("fp32 GEMM needs float32 operands and output")
+        _abi.check(L.pom_gemm_f32(C.byref(g), _abi.stream_ptr()), "pom_gemm_f32")
+    return out
+
+
+def reduce_partials(partial: torch.Tensor, *, inv_denom: Optional[torch.Tensor] = None, scale: float = 1.0,
+                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """(B, chunks, P) fp32 -> (B, P): scale * inv_denom[b] * sum over chunks, in a fixed order."""
+    _require_cuda(partial, inv_denom, out)
+    B, chunks, P = partial.shape
+    assert partial.dtype == torch.float32 and partial.is_contiguous()
+    if out is None:
+        out = torch.empty((B, P), dtype=torch.float32, device=partial.device)
+    _abi.check(_abi.lib().pom_reduce_partials(ptr(partial), ptr(out), ptr(inv_denom), scale, B, chunks, P,
+                                              _abi.stream_ptr()), "pom_reduce_partials")
+    return out
+
+
+def m_tiles(n_rows: int) -> int:
+    return (n_rows + 127) // 128
+
+
+# ---------------------------------------------------------------------------- fused GEMM phases (bf16)
+def ctx_gemm(x: torch.Tensor, w_po: torch.Tensor, coeff: torch.Tensor, *, row_weight: Optional[torch.Tensor] = None,
+             save_hp: bool = True):
+    """Context phase: returns (partial (B, MT, P) fp32, hp (B, N, P) bf16 or None)."""
+    dev = _require_cuda(x, w_po, coeff, row_weight)
+    B, N, D = x.shape
+    P, K = coeff.shape
+    partial = torch.empty((B, m_tiles(N), P), dtype=torch.float32, device=dev)
+    hp = torch.empty((B, N, P), dtype=torch.bfloat16, device=dev) if save_hp else None
+    a = CtxArgs()
+    a.X, a.Wpo, a.coeff, a.row_weight = ptr(x), ptr(w_po), ptr(coeff), ptr(row_weight)
+    a.hp_out, a.partial = ptr(hp), ptr(partial)
+    a.ldx, a.ldw, a.ld_hp = _row_stride(x), _row_stride(w_po), P
+    a.B, a.N, a.D, a.P, a.K = B, N, D, P, K
+    _abi.check(_abi.lib().pom_ctx_gemm(C.byref(a), ptr(_abi.status_word(dev)), _abi.stream_ptr()), "pom_ctx_gemm")
+    return partial, hp
+
+
+def gate_gemm(x: torch.Tensor, w_se: torch.Tensor, bias: torch.Tensor, h: torch.Tensor, *, save_z: bool = True):
+    """Query phase: returns (SH (B, T, P) bf16, z (B, T, P) bf16 or None). ``h`` is (B, P) fp32."""
+    dev = _require_cuda(x, w_se, bias, h)
+    B, T, D = x.shape
+    P = w_se.shape[0]
+    sh = torch.empty((B, T, P), dtype=torch.bfloat16, device=dev)
+    z = torch.empty((B, T, P), dtype=torch.bfloat16, device=dev) if save_z else None
+    a = GateArgs()
+    a.X, a.Wse, a.bias, a.H = ptr(x), ptr(w_se), ptr(bias), ptr(h)
+    a.z_out, a.sh_out = ptr(z), ptr(sh)
+    a.ldx, a.ldw, a.ld_z, a.ld_sh = _row_stride(x), _row_stride(w_se), P, P
+    a.h_batch_stride, a.h_row_stride = h.stride(0), 0
+    a.B, a.T, a.D, a.P = B, T, D, P
+    _abi.check(_abi.lib().pom_gate_gemm(C.byref(a), ptr(_abi.status_word(dev)), _abi.stream_ptr()), "pom_gate_gemm")
+    return sh, z
+
+
+def gate_bwd_gemm(dy: torch.Tensor, w_o: torch.Tensor, bias: torch.Tensor, h: torch.Tensor, z: torch.Tensor,
+                  g_out: torch.Tensor):
+    """Backward of the query phase. Writes dz into ``g_out`` (a (B*T, P) view with its own row
+    stride) and returns (dh_partial, dbias_partial), both (B, MT, P) fp32."""
+    dev = _require_cuda(dy, w_o, bias, h, z, g_out)
+    B, T, D = dy.shape
+    P = w_o.shape[1]
+    dh_p = torch.empty((B, m_tiles(T), P), dtype=torch.float32, device=dev)
+    db_p = torch.empty((B, m_tiles(T), P), dtype=torch.float32, device=dev)
+    a = GateBwdArgs()
+    a.dY, a.Wo, a.bias, a.H, a.z = ptr(dy), ptr(w_o), ptr(bias), ptr(h), ptr(z)
+    a.g_out, a.dh_partial, a.db_partial = ptr(g_out), ptr(dh_p), ptr(db_p)
+    a.ld_dy, a.ldw, a.ld_z, a.ld_g = _row_stride(dy), _row_stride(w_o), _row_stride(z), _row_stride(g_out)
+    a.h_batch_stride = h.stride(0)
+    a.B, a.T, a.D, a.P = B, T, D, P
+    _abi.check(_abi.lib().pom_gate_bwd_gemm(C.byref(a), ptr(_abi.status_word(dev)), _abi.stream_ptr()),
+               "pom_gate_bwd_gemm")
+    return dh_p, db_p
+
+
+# ---------------------------------------------------------------------------- stand-alone operators
+def agg_chunks(n: int) -> int:
+    return int(_abi.lib().pom_agg_chunks(n))
+
+
+def poly_agg_fwd(x: torch.Tensor, coeff: torch.Tensor, *, row_weight: Optional[torch.Tensor] = None,
+                 causal: bool = False, rope: Optional[RopeSpec] = None, carry: Optional[torch.Tensor] = None,
+                 token_offset: int = 0, want_total: bool = False):
+    """Non-causal: returns partial sums (B, chunks, P) fp32 (finish with reduce_partials).
+    Causal: returns (out (B, N, P) of x.dtype, total (B, P) fp32 or None)."""
+    dev = _require_cuda(x, coeff, row_weight, carry)
+    B, N, P = x.shape
+    K = coeff.shape[1]
+    chunks = agg_chunks(N)
+    partial = torch.empty((B, chunks, P), dtype=torch.float32, device=dev)
+    out = torch.empty((B, N, P), dtype=x.dtype, device=dev) if causal else None
+    total = torch.empty((B, P), dtype=torch.float32, device=dev) if (causal and want_total) else None
+    a = AggArgs()
+    a.x, a.coeff, a.row_weight, a.carry = ptr(x), ptr(coeff), ptr(row_weight), ptr(carry)
+    a.partial, a.out, a.total = ptr(partial), ptr(out), ptr(total)
+    a.ldx, a.ld_out, a.token_offset = _row_stride(x), P, token_offset
+    a.B, a.N, a.P, a.K = B, N, P, K
+    a.dtype, a.causal = _abi.dtype_code(x.dtype), int(causal)
+    a.rope = _rope_c(rope)
+    _abi.check(_abi.lib().pom_poly_agg_fwd(C.byref(a), _abi.stream_ptr()), "pom_poly_agg_fwd")
+    if causal:
+        return out, total
+    return partial
+
+
+def poly_agg_bwd(x: torch.Tensor, coeff: torch.Tensor, *, dx_out: torch.Tensor, dH: Optional[torch.Tensor] = None,
+                 dout: Optional[torch.Tensor] = None, row_weight: Optional[torch.Tensor] = None,
+                 inv_denom: Optional[torch.Tensor] = None, scale: float = 1.0, causal: bool = False,
+                 rope: Optional[RopeSpec] = None, carry: Optional[torch.Tensor] = None, token_offset: int = 0,
+                 want_total: bool = False):
+    """Writes dx into ``dx_out`` (a (B, N, P) view, own row stride) and returns
+    (dcoeff (P, K) fp32, total (B, P) fp32 or None)."""
+    dev = _require_cuda(x, coeff, dx_out, dH, dout, row_weight, inv_denom, carry)
+    B, N, P = x.shape
+    K = coeff.shape[1]
+    chunks = agg_chunks(N)
+    dcp = torch.empty((1, B * chunks, P * K), dtype=torch.float32, device=dev)
+    partial = torch.empty((B, chunks, P), dtype=torch.float32, device=dev) if causal else None
+    total = torch.empty((B, P), dtype=torch.float32, device=dev) if (causal and want_total) else None
+    a = AggBwdArgs()
+    a.x, a.coeff, a.row_weight, a.inv_denom = ptr(x), ptr(coeff), ptr(row_weight), ptr(inv_denom)
+    a.dH, a.dout, a.carry, a.partial, a.total = ptr(dH), ptr(dout), ptr(carry), ptr(partial), ptr(total)
+    a.dx, a.dcoeff_partial = ptr(dx_out), ptr(dcp)
+    a.ldx, a.ld_dx = _row_stride(x), _row_stride(dx_out)
+    a.ld_dout = _row_stride(dout) if dout is not None else 0
+    a.token_offset, a.scale = token_offset, scale
+    a.B, a.N, a.P, a.K = B, N, P, K
+    a.dtype, a.causal = _abi.dtype_code(x.dtype), int(causal)
+    a.rope = _rope_c(rope)
+    _abi.check(_abi.lib().pom_poly_agg_bwd(C.byref(a), _abi.stream_ptr()), "pom_poly_agg_bwd")
+    dcoeff = reduce_partials(dcp).view(P, K)
+    return dcoeff, total
+
+
+def select_fwd(z: torch.Tensor, bias: torch.Tensor, h: torch.Tensor, *, rope: Optional[RopeSpec] = None) -> torch.Tensor:
+    """SH = R·hardsigmoid(z + bias) ⊙ H.  ``h`` is (B, P) fp32 (one vector per sample) or (B, T, P) of z.dtype."""
+    dev = _require_cuda(z, bias, h)
+    B, T, P = z.shape
+    per_tok = h.dim() == 3
+    if per_tok and h.dtype != z.dtype:
+        raise TypeError("per-token H must have the dtype of z")
+    if not per_tok and h.dtype != torch.float32:
+        raise TypeError("broadcast H must be float32")
+    sh = torch.empty((B, T, P), dtype=z.dtype, device=dev)
+    a = SelectArgs()
+    a.z, a.bias, a.H, a.sh = ptr(z), ptr(bias), ptr(h), ptr(sh)
+    a.ld_z, a.ld_h, a.ld_sh = _row_stride(z), (_row_stride(h) if per_tok else 0), P
+    a.B, a.T, a.P = B, T, P
+    a.dtype, a.h_per_token = _abi.dtype_code(z.dtype), int(per_tok)
+    a.rope = _rope_c(rope)
+    _abi.check(_abi.lib().pom_select_fwd(C.byref(a), _abi.stream_ptr()), "pom_select_fwd")
+    return sh
+
+
+def select_bwd(dsh: torch.Tensor, z: torch.Tensor, bias: torch.Tensor, h: torch.Tensor, dz_out: torch.Tensor, *,
+               rope: Optional[RopeSpec] = None):
+    """Returns (dH, dbias): dH is (B, P) fp32 un-normalised sum over tokens when ``h`` is per-sample,
+    else the per-token (B, T, P) gradient in z.dtype.  dz is written into ``dz_out``."""
+    dev = _require_cuda(dsh, z, bias, h, dz_out)
+    B, T, P = z.shape
+    per_tok = h.dim() == 3
+    chunks = agg_chunks(T)
+    db_p = torch.empty((1, B * chunks, P), dtype=torch.float32, device=dev)
+    dh_p = None if per_tok else torch.empty((B, chunks, P), dtype=torch.float32, device=dev)
+    dh_tok = torch.empty((B, T, P), dtype=z.dtype, device=dev) if per_tok else None
+    a = SelectBwdArgs()
+    a.dsh, a.z, a.bias, a.H = ptr(dsh), ptr(z), ptr(bias), ptr(h)
+    a.dz, a.dbias_partial, a.dh_partial, a.dh_tok = ptr(dz_out), ptr(db_p), ptr(dh_p), ptr(dh_tok)
+    a.ld_dsh, a.ld_z, a.ld_dz = _row_stride(dsh), _row_stride(z), _row_stride(dz_out)
+    a.ld_h, a.ld_dh = (_row_stride(h) if per_tok else 0), P
+    a.B, a.T, a.P = B, T, P
+    a.dtype, a.h_per_token = _abi.dtype_code(z.dtype), int(per_tok)
+    a.rope = _rope_c(rope)
+    _abi.check(_abi.lib().pom_select_bwd(C.byref(a), _abi.stream_ptr()), "pom_select_bwd")
+    dbias = reduce_partials(db_p).view(P)
+    dH = dh_tok if per_tok else reduce_partials(dh_p)
+    return dH, dbias
+
+
+def state_merge(h_past: torch.Tensor, h_cur: torch.Tensor, n_past: float) -> torch.Tensor:
+    _require_cuda(h_past, h_cur)
+    out = torch.empty_like(h_cur)
+    _abi.check(_abi.lib().pom_state_merge(ptr(h_past), ptr(h_cur), ptr(out), float(n_past), h_cur.numel(),
+                                          _abi.stream_ptr()), "pom_state_merge")
+    return out
+
+
+def to_bf16(src: torch.Tensor) -> torch.Tensor:
+    _require_cuda(src)
+    src = src.contiguous()
+    out = torch.empty(src.shape, dtype=torch.bfloat16, device=src.device)
+    _abi.check(_abi.lib().pom_cast_f32_to_bf16(ptr(src), ptr(out), src.numel(), _abi.stream_ptr()), "pom_cast")
+    return out
+
+
+def to_f32(src: torch.Tensor) -> torch.Tensor:
+    _require_cuda(src)
+    src = src.contiguous()
+    out = torch.empty(src.shape, dtype=torch.float32, device=src.device)
+    _abi.check(_abi.lib().pom_cast_bf16_to_f32(ptr(src), ptr(out), src.numel(), _abi.stream_ptr()), "pom_cast")
+    return out
+
+
+def launch_count() -> int:
+    return int(_abi.lib().pom_launch_count())
