@@ -63,8 +63,7 @@ long long pom_launch_count(void);
  * 1-D: cos0/sin0 are (max_len, P/2) tables, pos is (N) int64, pos_stride 1.
  * 2-D: cos0/sin0 are the row tables (max_h, P/4), cos1/sin1 the column tables (max_w, P/4),
  *      pos is (N, 2) int64 (row, col), pos_stride 2.
- * `max0`/`max1` are the table heights, used to validate nothing on the device (positions are
- * trusted) but checked on the host side of the Python layer.
+ * Positions are trusted on the device; the Python layer checks them against the table heights.
  * ------------------------------------------------------------------------------------------ */
 typedef struct pom_rope {
   int32_t kind; /* POM_ROPE_* */
@@ -124,8 +123,9 @@ typedef struct pom_ctx_args {
 } pom_ctx_args;
 int pom_ctx_gemm(const pom_ctx_args* a, int* status, void* stream);
 
-/* out[b, p] = scale * inv_denom[b] * sum_c partial[b, c, p]   (inv_denom may be NULL) */
-int pom_reduce_partials(const float* partial, float* out, const float* inv_denom, float scale, int32_t B,
+/* out[b, p] = scale * sum_c partial[b, c, p] / denom[b]   (denom may be NULL = 1; a zero denominator
+ * yields 0, the convention of pom/pom_triton_masked.py:166-167 for a sample with no valid token) */
+int pom_reduce_partials(const float* partial, float* out, const float* denom, float scale, int32_t B,
                         int32_t chunks, int32_t P, void* stream);
 
 /* ------------------------------------------------------------------------------------------
@@ -195,10 +195,12 @@ typedef struct pom_agg_args {
 int pom_poly_agg_fwd(const pom_agg_args* a, void* stream);
 
 /* Backward of the aggregation operator.
- *   causal == 0 : dH (B, P) fp32 is the gradient of out; token weight = row_weight[b,n] * inv_denom[b]
+ *   causal == 0 : dH (B, P) fp32 is the gradient of out; token weight = row_weight[b,n] / denom[b]
  *                 (either may be NULL = 1); `scale` multiplies everything (1/N for a plain mean).
  *   causal == 1 : dout (B, N, P) dtype; `carry` (B, P) fp32 optional = suffix sum from later shards;
  *                 `total` optional output (B, P): this shard's sum of dout[n]/(n+1+offset).
+ *                 phase == 1 stops after the totals (used to obtain `total` before the cross-shard
+ *                 exchange that produces `carry`); phase == 0 runs everything.
  * Outputs: dx (B, N, P) dtype row stride ld_dx; dcoeff_partial (B*chunks, P, K) fp32, to be
  * reduced with pom_reduce_partials(B=1, chunks=B*chunks, P=P*K).
  * Replaces: backward halves of the kernels named above. */
@@ -206,7 +208,7 @@ typedef struct pom_agg_bwd_args {
   const void* x;
   const float* coeff;
   const float* row_weight;
-  const float* inv_denom;
+  const float* denom;
   const float* dH;      /* non-causal */
   const void* dout;     /* causal */
   const float* carry;
@@ -218,7 +220,7 @@ typedef struct pom_agg_bwd_args {
   int64_t token_offset;
   float scale;
   int32_t B, N, P, K;
-  int32_t dtype, causal;
+  int32_t dtype, causal, phase;
   pom_rope rope;
 } pom_agg_bwd_args;
 int pom_poly_agg_bwd(const pom_agg_bwd_args* a, void* stream);
@@ -236,6 +238,7 @@ typedef struct pom_select_args {
   int64_t ld_z, ld_h, ld_sh;
   int32_t B, T, P;
   int32_t dtype, h_per_token;
+  int32_t activated;   /* nonzero: z already holds the gate s (bias and hardsigmoid are skipped) */
   pom_rope rope;
 } pom_select_args;
 int pom_select_fwd(const pom_select_args* a, void* stream);
@@ -255,6 +258,7 @@ typedef struct pom_select_bwd_args {
   int64_t ld_dsh, ld_z, ld_h, ld_dz, ld_dh;
   int32_t B, T, P;
   int32_t dtype, h_per_token;
+  int32_t activated;   /* as in pom_select_args; dz is then the gradient of s itself */
   pom_rope rope;
 } pom_select_bwd_args;
 int pom_select_bwd(const pom_select_bwd_args* a, void* stream);

@@ -92,13 +92,13 @@ class AggArgs(C.Structure):
 
 class AggBwdArgs(C.Structure):
     _fields_ = [
-        ("x", C.c_void_p), ("coeff", C.c_void_p), ("row_weight", C.c_void_p), ("inv_denom", C.c_void_p),
+        ("x", C.c_void_p), ("coeff", C.c_void_p), ("row_weight", C.c_void_p), ("denom", C.c_void_p),
         ("dH", C.c_void_p), ("dout", C.c_void_p), ("carry", C.c_void_p), ("partial", C.c_void_p),
         ("total", C.c_void_p), ("dx", C.c_void_p), ("dcoeff_partial", C.c_void_p),
         ("ldx", C.c_int64), ("ld_dx", C.c_int64), ("ld_dout", C.c_int64), ("token_offset", C.c_int64),
         ("scale", C.c_float),
         ("B", C.c_int32), ("N", C.c_int32), ("P", C.c_int32), ("K", C.c_int32),
-        ("dtype", C.c_int32), ("causal", C.c_int32),
+        ("dtype", C.c_int32), ("causal", C.c_int32), ("phase", C.c_int32),
         ("rope", Rope),
     ]
 
@@ -108,7 +108,7 @@ class SelectArgs(C.Structure):
         ("z", C.c_void_p), ("bias", C.c_void_p), ("H", C.c_void_p), ("sh", C.c_void_p),
         ("ld_z", C.c_int64), ("ld_h", C.c_int64), ("ld_sh", C.c_int64),
         ("B", C.c_int32), ("T", C.c_int32), ("P", C.c_int32),
-        ("dtype", C.c_int32), ("h_per_token", C.c_int32),
+        ("dtype", C.c_int32), ("h_per_token", C.c_int32), ("activated", C.c_int32),
         ("rope", Rope),
     ]
 
@@ -119,7 +119,7 @@ class SelectBwdArgs(C.Structure):
         ("dz", C.c_void_p), ("dbias_partial", C.c_void_p), ("dh_partial", C.c_void_p), ("dh_tok", C.c_void_p),
         ("ld_dsh", C.c_int64), ("ld_z", C.c_int64), ("ld_h", C.c_int64), ("ld_dz", C.c_int64), ("ld_dh", C.c_int64),
         ("B", C.c_int32), ("T", C.c_int32), ("P", C.c_int32),
-        ("dtype", C.c_int32), ("h_per_token", C.c_int32),
+        ("dtype", C.c_int32), ("h_per_token", C.c_int32), ("activated", C.c_int32),
         ("rope", Rope),
     ]
 

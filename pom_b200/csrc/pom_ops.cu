@@ -251,7 +251,7 @@ __global__ void chunk_scan_kernel(float* partial, const float* carry, float* tot
 }
 
 __global__ void reduce_partials_kernel(const float* __restrict__ partial, float* __restrict__ out,
-                                       const float* __restrict__ inv_denom, float scale, int chunks, int P) {
+                                       const float* __restrict__ denom, float scale, int chunks, int P) {
   const int p = blockIdx.x * blockDim.x + threadIdx.x;
   const int b = blockIdx.y;
   if (p >= P) return;
@@ -267,7 +267,10 @@ __global__ void reduce_partials_kernel(const float* __restrict__ partial, float*
   for (; c < chunks; ++c) s0 += base[static_cast<long long>(c) * P];
   float s = (s0 + s1) + (s2 + s3);
   s *= scale;
-  if (inv_denom) s *= inv_denom[b];
+  if (denom) {
+    const float d = denom[b];
+    s = d != 0.f ? s / d : 0.f;  // a sample with no valid token aggregates to zero
+  }
   out[static_cast<long long>(b) * P + p] = s;
 }
 
@@ -276,7 +279,7 @@ struct AggBwdDev {
   const void* x;
   const float* coeff;
   const float* row_weight;
-  const float* inv_denom;
+  const float* denom;
   const float* dH;
   const void* dout;
   float* partial;
@@ -346,7 +349,10 @@ __global__ void __launch_bounds__(kThreads) agg_bwd_kernel(const AggBwdDev a) {
     }
   }
   float wb = a.scale;
-  if (!CAUSAL && a.inv_denom) wb *= a.inv_denom[b];
+  if (!CAUSAL && a.denom) {
+    const float dn = a.denom[b];
+    wb = dn != 0.f ? wb / dn : 0.f;
+  }
   const int n0 = c * kChunk, n1 = min(a.N, n0 + kChunk);
 #pragma unroll 2
   for (int i = 0; i < n1 - n0; ++i) {
@@ -437,7 +443,7 @@ struct SelDev {
   float* dh_partial;
   void* dh_tok;
   long long ld_z, ld_h, ld_sh, ld_dsh, ld_dz, ld_dh;
-  int B, T, P, chunks, h_per_token;
+  int B, T, P, chunks, h_per_token, activated;
   pom_rope rope;
 };
 
@@ -453,8 +459,8 @@ __global__ void __launch_bounds__(kThreads) select_kernel(const SelDev a) {
   float b1[VEC], b2[VEC], h1[VEC], h2[VEC];
 #pragma unroll
   for (int e = 0; e < VEC; ++e) {
-    b1[e] = a.bias[m.p1 + e];
-    b2[e] = rope ? a.bias[m.p2 + e] : 0.f;
+    b1[e] = a.activated ? 0.f : a.bias[m.p1 + e];
+    b2[e] = (rope && !a.activated) ? a.bias[m.p2 + e] : 0.f;
     h1[e] = h2[e] = 0.f;
     if (!a.h_per_token) {
       const float* H = static_cast<const float*>(a.H) + static_cast<long long>(b) * a.P;
@@ -482,10 +488,10 @@ __global__ void __launch_bounds__(kThreads) select_kernel(const SelDev a) {
 #pragma unroll
     for (int e = 0; e < VEC; ++e) {
       z1[e] += b1[e];
-      const float r1 = pom_hardsigmoid(z1[e]);
+      const float r1 = a.activated ? z1[e] : pom_hardsigmoid(z1[e]);
       if (rope) {
         z2[e] += b2[e];
-        const float r2 = pom_hardsigmoid(z2[e]);
+        const float r2 = a.activated ? z2[e] : pom_hardsigmoid(z2[e]);
         s1[e] = r1 * cs[e] - r2 * sn[e];
         s2[e] = r2 * cs[e] + r1 * sn[e];
       } else {
@@ -521,10 +527,10 @@ __global__ void __launch_bounds__(kThreads) select_kernel(const SelDev a) {
           const float t2v = g2[e] * h2[e];
           ds1 = t1v * cs[e] + t2v * sn[e];
           const float ds2 = t2v * cs[e] - t1v * sn[e];
-          g2[e] = ds2 * pom_hardsigmoid_grad(z2[e]);
+          g2[e] = a.activated ? ds2 : ds2 * pom_hardsigmoid_grad(z2[e]);
           accB2[e] += g2[e];
         }
-        o[e] = ds1 * pom_hardsigmoid_grad(z1[e]);
+        o[e] = a.activated ? ds1 : ds1 * pom_hardsigmoid_grad(z1[e]);
         accB1[e] += o[e];
       }
       Vec<T, VEC>::st(dz + m.p1, o);
@@ -615,13 +621,13 @@ extern "C" {
 
 int32_t pom_agg_chunks(int32_t N) { return N <= 0 ? 0 : static_cast<int32_t>(ceil_div(N, kChunk)); }
 
-int pom_reduce_partials(const float* partial, float* out, const float* inv_denom, float scale, int32_t B,
+int pom_reduce_partials(const float* partial, float* out, const float* denom, float scale, int32_t B,
                         int32_t chunks, int32_t P, void* stream) {
   if (!partial || !out) return POM_ERR_NULL;
   if (B <= 0 || chunks <= 0 || P <= 0) return POM_ERR_BAD_SHAPE;
   if (B > 65535) return POM_ERR_TOO_LARGE;
   dim3 grid(static_cast<unsigned>(ceil_div(P, 128)), static_cast<unsigned>(B));
-  reduce_partials_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(partial, out, inv_denom, scale, chunks,
+  reduce_partials_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(partial, out, denom, scale, chunks,
                                                                              P);
   count_launch();
   return check_launch();
@@ -691,7 +697,7 @@ int pom_poly_agg_bwd(const pom_agg_bwd_args* a, void* stream) {
   d.x = a->x;
   d.coeff = a->coeff;
   d.row_weight = a->row_weight;
-  d.inv_denom = a->inv_denom;
+  d.denom = a->denom;
   d.dH = a->dH;
   d.dout = a->dout;
   d.partial = a->partial;
@@ -722,6 +728,7 @@ int pom_poly_agg_bwd(const pom_agg_bwd_args* a, void* stream) {
     dim3 sgrid(static_cast<unsigned>(ceil_div(a->P, 128)), static_cast<unsigned>(a->B));
     chunk_scan_kernel<<<sgrid, 128, 0, st>>>(a->partial, a->carry, a->total, d.chunks, a->P, 1);
     count_launch();
+    if (a->phase == 1) return check_launch();  // totals only
 #define CALL_BC(T, V)                                                     \
   if (a->K <= 4) agg_bwd_kernel<T, V, 4, true><<<grid, kThreads, 0, st>>>(d); \
   else agg_bwd_kernel<T, V, kMaxDegree, true><<<grid, kThreads, 0, st>>>(d)
@@ -762,7 +769,7 @@ static int select_common(SelDev& d, int dtype, bool bwd, std::initializer_list<l
 }
 
 int pom_select_fwd(const pom_select_args* a, void* stream) {
-  if (!a || !a->z || !a->bias || !a->H || !a->sh) return POM_ERR_NULL;
+  if (!a || !a->z || (!a->bias && !a->activated) || !a->H || !a->sh) return POM_ERR_NULL;
   if (a->ld_z < a->P || a->ld_sh < a->P || (a->h_per_token && a->ld_h < a->P)) return POM_ERR_BAD_STRIDE;
   SelDev d{};
   d.z = a->z;
@@ -776,13 +783,15 @@ int pom_select_fwd(const pom_select_args* a, void* stream) {
   d.T = a->T;
   d.P = a->P;
   d.h_per_token = a->h_per_token;
+  d.activated = a->activated;
   d.rope = a->rope;
   return select_common(d, a->dtype, false, {a->ld_z, a->ld_sh, a->h_per_token ? a->ld_h : 0},
                        {a->z, a->sh, a->h_per_token ? a->H : nullptr}, static_cast<cudaStream_t>(stream));
 }
 
 int pom_select_bwd(const pom_select_bwd_args* a, void* stream) {
-  if (!a || !a->dsh || !a->z || !a->bias || !a->H || !a->dz || !a->dbias_partial) return POM_ERR_NULL;
+  if (!a || !a->dsh || !a->z || (!a->bias && !a->activated) || !a->H || !a->dz || !a->dbias_partial)
+    return POM_ERR_NULL;
   if (a->h_per_token ? !a->dh_tok : !a->dh_partial) return POM_ERR_NULL;
   if (a->ld_z < a->P || a->ld_dsh < a->P || a->ld_dz < a->P) return POM_ERR_BAD_STRIDE;
   if (a->h_per_token && (a->ld_h < a->P || a->ld_dh < a->P)) return POM_ERR_BAD_STRIDE;
@@ -804,6 +813,7 @@ int pom_select_bwd(const pom_select_bwd_args* a, void* stream) {
   d.T = a->T;
   d.P = a->P;
   d.h_per_token = a->h_per_token;
+  d.activated = a->activated;
   d.rope = a->rope;
   return select_common(d, a->dtype, true,
                        {a->ld_z, a->ld_dsh, a->ld_dz, a->h_per_token ? a->ld_h : 0, a->h_per_token ? a->ld_dh : 0},

@@ -1,0 +1,393 @@
+"""Autograd-level PoM operators on top of the C ABI.
+
+``pom_layer`` is the whole layer (projections, polynomial aggregation, gating, output
+projection) as one ``torch.autograd.Function``; ``polynomial_aggregation_`` /
+``polynomial_selection_`` / ``pom`` keep the reference's operator names and argument
+order (reference pom/pom.py:52-135) for callers that hold pre-projected features.
+
+Execution paths inside ``pom_layer`` (all CUDA, chosen from dtype / mask / rotary kind):
+
+* fused     bf16, no rotary, mask None or (B, N): tcgen05 GEMMs whose epilogues do the
+            activation, polynomial, token reduction and gating (pom_ctx_gemm, pom_gate_gemm,
+            pom_gate_bwd_gemm);
+* operator  everything else (causal, rotary, fp32): plain GEMMs (tcgen05 for bf16, SIMT for
+            fp32) around the stand-alone aggregation / selection kernels.
+
+Token sharding over several GPUs (``SeqShard``) inserts the only collectives: an all-reduce
+of the (B, P) partial sums for non-causal masks, an all-gather of per-rank totals followed
+by a local exclusive scan for the causal mask, and the mirrored exchanges in backward.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Optional, Tuple, Union
+
+import torch
+import torch.distributed as dist
+
+from . import _abi, ops
+from .ops import RopeSpec
+
+
+# --------------------------------------------------------------------------- sharding description
+@dataclass
+class SeqShard:
+    """This rank's slice of a token-sharded sequence.
+
+    ``token_offset`` is the global index of the local token 0 and ``n_global`` the global
+    context length.  ``group`` is a torch.distributed process group (None = default group).
+    Ranks hold consecutive chunks in rank order.
+    """
+    token_offset: int
+    n_global: int
+    group: Any = None
+    reduce_weight_grads: bool = True
+
+    @property
+    def world(self) -> int:
+        return dist.get_world_size(self.group)
+
+    @property
+    def rank(self) -> int:
+        return dist.get_rank(self.group)
+
+    def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+        return t
+
+    def exclusive_carry(self, total: torch.Tensor, reverse: bool = False) -> torch.Tensor:
+        """Sum of ``total`` over the ranks before (or, reversed, after) this one, in rank order."""
+        w = self.world
+        gathered = torch.empty((w,) + tuple(total.shape), dtype=total.dtype, device=total.device)
+        dist.all_gather_into_tensor(gathered, total.contiguous(), group=self.group)
+        r = self.rank
+        part = gathered[r + 1:] if reverse else gathered[:r]
+        if part.shape[0] == 0:
+            return torch.zeros_like(total)
+        return ops.reduce_partials(part.transpose(0, 1).contiguous())
+
+
+@dataclass
+class LayerSpec:
+    """Non-tensor arguments of one layer call."""
+    degree: int
+    mask_kind: str = "none"          # "none" | "keypad" | "causal"
+    self_mixing: bool = True
+    rope_ctx: Optional[RopeSpec] = None
+    rope_qry: Optional[RopeSpec] = None
+    shard: Optional[SeqShard] = None
+    n_past: Optional[float] = None   # state_forward: number of previous calls (None = plain forward)
+    want_state: bool = False
+
+
+def _f32(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    if t is None or t.dtype == torch.float32:
+        return t
+    return ops.to_f32(t)
+
+
+def _like_param(g: torch.Tensor, p: torch.Tensor) -> torch.Tensor:
+    if p.dtype == torch.float32:
+        return g
+    return ops.to_bf16(g)
+
+
+def _check_inputs(xq, xc, w_qc, w_ag, coeff, spec: LayerSpec):
+    if xq.dim() != 3 or xc.dim() != 3:
+        raise ValueError("expected (B, T, D) / (B, N, D) inputs")
+    if not xq.is_cuda:
+        raise RuntimeError("pom_b200 has no CPU path: move the module and its inputs to a CUDA device")
+    if xq.dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError(f"unsupported dtype {xq.dtype}; use bfloat16 or float32")
+    for t in (xc, w_qc, w_ag):
+        if t.dtype != xq.dtype:
+            raise TypeError("inputs and projection weights must share one dtype")
+    if coeff.shape[1] > 16:
+        raise NotImplementedError(f"polynomial degree {coeff.shape[1]} > 16 is not implemented")
+
+
+class _PoMLayer(torch.autograd.Function):
+    """y = ((R_q · hardsigmoid(xq·Wseᵀ + b)) ⊙ agg(R_c · poly(act(xc·Wpoᵀ)))) · Woᵀ
+    (reference pom/pom.py:193-231 and pom/pom_rope.py:443-526)."""
+
+    @staticmethod
+    def forward(ctx, xq, xc, w_qc, se_bias, coeff, w_ag, mask, h_past, spec: LayerSpec):
+        _check_inputs(xq, xc, w_qc, w_ag, coeff, spec)
+        B, T, D = xq.shape
+        N = xc.shape[1]
+        P, K = coeff.shape
+        bf16 = xq.dtype == torch.bfloat16
+        xq = xq.contiguous()
+        xc = xq if spec.self_mixing else xc.contiguous()
+        w_qc = w_qc.contiguous()
+        w_ag = w_ag.contiguous()
+        w_po, w_se = w_qc[:P], w_qc[P:]
+        coeff32, bias32 = _f32(coeff.contiguous()), _f32(se_bias.contiguous())
+        need_grad = any(ctx.needs_input_grad[:6]) or (h_past is not None and ctx.needs_input_grad[7])
+        shard = spec.shard
+        n_glob = shard.n_global if shard is not None else N
+        offset = shard.token_offset if shard is not None else 0
+        causal = spec.mask_kind == "causal"
+        maskf = None
+        denom = None
+        if spec.mask_kind == "keypad":
+            maskf = mask.to(device=xq.device, dtype=torch.float32).contiguous()
+            denom = ops.reduce_partials(maskf.view(B, N, 1)).view(B)
+            if shard is not None:
+                shard.all_reduce(denom)
+        fused = bf16 and spec.rope_ctx is None and spec.rope_qry is None and not causal and P % 8 == 0 and D % 8 == 0
+
+        hp = z = Hc = None
+        # ---------------------------------------------------------------- context phase
+        if fused:
+            partial, hp = ops.ctx_gemm(xc, w_po, coeff32, row_weight=maskf, save_hp=need_grad)
+            S = ops.reduce_partials(partial)
+        else:
+            if spec.self_mixing:
+                hs = ops.gemm(xq.view(B * T, D), w_qc).view(B, T, 2 * P)
+                hp, z = hs[..., :P], hs[..., P:]
+            else:
+                hp = ops.gemm(xc.view(B * N, D), w_po).view(B, N, P)
+                z = ops.gemm(xq.view(B * T, D), w_se).view(B, T, P)
+            if not causal:
+                S = ops.reduce_partials(ops.poly_agg_fwd(hp, coeff32, row_weight=maskf, rope=spec.rope_ctx))
+        if causal:
+            carry = None
+            if shard is not None:
+                S_loc = ops.reduce_partials(ops.poly_agg_fwd(hp, coeff32, rope=spec.rope_ctx))
+                carry = shard.exclusive_carry(S_loc)
+            Hc, _ = ops.poly_agg_fwd(hp, coeff32, causal=True, rope=spec.rope_ctx, carry=carry, token_offset=offset)
+            H = None
+        else:
+            if shard is not None:
+                shard.all_reduce(S)
+            H = ops.reduce_partials(S.view(B, 1, P), denom=denom, scale=(1.0 if denom is not None else 1.0 / n_glob))
+            if spec.n_past is not None and h_past is not None:
+                H = ops.state_merge(_f32(h_past.reshape(B, P).contiguous()), H, spec.n_past)
+
+        # ---------------------------------------------------------------- query phase
+        if fused:
+            sh, z = ops.gate_gemm(xq, w_se, bias32, H, save_z=need_grad)
+        else:
+            sh = ops.select_fwd(z, bias32, Hc if causal else H, rope=spec.rope_qry)
+        y = ops.gemm(sh.view(B * T, P), w_ag).view(B, T, D)
+
+        ctx.spec = spec
+        ctx.fused = fused
+        ctx.dims = (B, T, N, D, P, K, n_glob, offset)
+        ctx.h_past_dtype = None if h_past is None else h_past.dtype
+        ctx.save_for_backward(xq, xc, w_qc, w_ag, coeff32, bias32, hp, z, H, Hc, sh, maskf, denom)
+        ctx.param_like = (w_qc, se_bias, coeff, w_ag)
+        if spec.want_state:
+            h_state = H.view(B, 1, P)
+            return y, h_state
+        return y, None
+
+    @staticmethod
+    def backward(ctx, dy, dh_state):
+        spec: LayerSpec = ctx.spec
+        xq, xc, w_qc, w_ag, coeff32, bias32, hp, z, H, Hc, sh, maskf, denom = ctx.saved_tensors
+        B, T, N, D, P, K, n_glob, offset = ctx.dims
+        p_qc, p_bias, p_coeff, p_ag = ctx.param_like
+        shard = spec.shard
+        causal = spec.mask_kind == "causal"
+        dev = xq.device
+        dt = xq.dtype
+        dy = dy.contiguous()
+        dy2 = dy.view(B * T, D)
+
+        # dWo[d, p] = sum_t dY[t, d] * SH[t, p]
+        d_wag = torch.zeros((D, P), dtype=torch.float32, device=dev)
+        ops.gemm(dy2, sh.view(B * T, P), a_mn=True, b_mn=True, out=d_wag, accumulate=True)
+
+        if spec.self_mixing:
+            G = torch.empty((B * T, 2 * P), dtype=dt, device=dev)
+            g_hp, g_z = G[:, :P], G[:, P:]
+        else:
+            g_hp = torch.empty((B * N, P), dtype=dt, device=dev)
+            g_z = torch.empty((B * T, P), dtype=dt, device=dev)
+
+        # ---------------------------------------------------------------- query phase backward
+        if ctx.fused:
+            dh_p, db_p = ops.gate_bwd_gemm(dy, w_ag, bias32, H, z, g_z)
+            dH = ops.reduce_partials(dh_p)
+            d_bias = ops.reduce_partials(db_p.view(1, -1, P)).view(P)
+        else:
+            dsh = ops.gemm(dy2, w_ag, b_mn=True).view(B, T, P)
+            dH, d_bias = ops.select_bwd(dsh, z, bias32, Hc if causal else H, g_z.view(B, T, P), rope=spec.rope_qry)
+
+        # ---------------------------------------------------------------- context phase backward
+        d_hpast = None
+        if causal:
+            carry = None
+            if shard is not None:
+                _, tot = ops.poly_agg_bwd(hp, coeff32, dx_out=g_hp.view(B, N, P), dout=dH, causal=True,
+                                          rope=spec.rope_ctx, token_offset=offset, want_total=True, totals_only=True)
+                carry = shard.exclusive_carry(tot, reverse=True)
+            d_coeff, _ = ops.poly_agg_bwd(hp, coeff32, dx_out=g_hp.view(B, N, P), dout=dH, causal=True,
+                                          rope=spec.rope_ctx, carry=carry, token_offset=offset)
+        else:
+            if dh_state is not None:
+                dH = ops.reduce_partials(torch.stack([dH, _f32(dh_state.reshape(B, P).contiguous())], dim=1))
+            if shard is not None:
+                shard.all_reduce(dH)
+            scale = 1.0 if denom is not None else 1.0 / n_glob
+            if spec.n_past is not None and ctx.h_past_dtype is not None:
+                # H = (n_past * h_past + h_cur) / (n_past + 1)
+                if ctx.needs_input_grad[7]:
+                    d_hpast = ops.reduce_partials(dH.view(B, 1, P), scale=spec.n_past / (spec.n_past + 1.0))
+                    d_hpast = d_hpast.view(B, 1, P)
+                    if ctx.h_past_dtype != torch.float32:
+                        d_hpast = ops.to_bf16(d_hpast)
+                scale = scale / (spec.n_past + 1.0)
+            d_coeff, _ = ops.poly_agg_bwd(hp, coeff32, dx_out=g_hp.view(B, N, P), dH=dH, row_weight=maskf, denom=denom,
+                                          scale=scale, rope=spec.rope_ctx)
+
+        # ---------------------------------------------------------------- projections backward
+        d_wqc = torch.zeros((2 * P, D), dtype=torch.float32, device=dev)
+        if spec.self_mixing:
+            dxq = ops.gemm(G, w_qc, b_mn=True).view(B, T, D)
+            ops.gemm(G, xq.view(B * T, D), a_mn=True, b_mn=True, out=d_wqc, accumulate=True)
+            dxc = None
+        else:
+            dxc = ops.gemm(g_hp, w_qc[:P], b_mn=True).view(B, N, D)
+            dxq = ops.gemm(g_z, w_qc[P:], b_mn=True).view(B, T, D)
+            ops.gemm(g_hp, xc.view(B * N, D), a_mn=True, b_mn=True, out=d_wqc[:P], accumulate=True)
+            ops.gemm(g_z, xq.view(B * T, D), a_mn=True, b_mn=True, out=d_wqc[P:], accumulate=True)
+
+        if shard is not None and shard.reduce_weight_grads:
+            for t in (d_wqc, d_wag, d_bias, d_coeff):
+                shard.all_reduce(t)
+        return (dxq, dxc, _like_param(d_wqc, p_qc), _like_param(d_bias, p_bias), _like_param(d_coeff.contiguous(), p_coeff),
+                _like_param(d_wag, p_ag), None, d_hpast, None)
+
+
+def pom_layer(xq, xc, w_qc, se_bias, coeff, w_ag, mask=None, h_past=None, spec: Optional[LayerSpec] = None):
+    y, h = _PoMLayer.apply(xq, xc if xc is not None else xq, w_qc, se_bias, coeff, w_ag, mask, h_past, spec)
+    return y, h
+
+
+# --------------------------------------------------------------------------- reference-named operators
+class _PolyAgg(torch.autograd.Function):
+    """polynomial_aggregation_ for mask None / "causal" / (B, N), optional rotary embedding."""
+
+    @staticmethod
+    def forward(ctx, x, coeff, mask_kind, mask, rope):
+        if not x.is_cuda:
+            raise RuntimeError("pom_b200 has no CPU path: pass CUDA tensors")
+        B, N, P = x.shape
+        if x.stride(-1) != 1 or (B > 1 and x.stride(0) != x.stride(1) * N):
+            x = x.contiguous()
+        coeff32 = _f32(coeff.contiguous())
+        maskf = denom = None
+        if mask_kind == "causal":
+            out, _ = ops.poly_agg_fwd(x, coeff32, causal=True, rope=rope)
+        else:
+            if mask_kind == "keypad":
+                maskf = mask.to(device=x.device, dtype=torch.float32).contiguous()
+                denom = ops.reduce_partials(maskf.view(B, N, 1)).view(B)
+            part = ops.poly_agg_fwd(x, coeff32, row_weight=maskf, rope=rope)
+            h = ops.reduce_partials(part, denom=denom, scale=1.0 if denom is not None else 1.0 / N)
+            out = h.view(B, 1, P)
+            if x.dtype != torch.float32:
+                out = ops.to_bf16(out)
+        ctx.save_for_backward(x, coeff32, maskf, denom)
+        ctx.meta = (mask_kind, rope, coeff.dtype)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        x, coeff32, maskf, denom = ctx.saved_tensors
+        mask_kind, rope, cdt = ctx.meta
+        B, N, P = x.shape
+        dx = torch.empty((B, N, P), dtype=x.dtype, device=x.device)
+        if mask_kind == "causal":
+            g = g.contiguous()
+            dc, _ = ops.poly_agg_bwd(x, coeff32, dx_out=dx, dout=g, causal=True, rope=rope)
+        else:
+            dH = _f32(g.reshape(B, P).contiguous())
+            dc, _ = ops.poly_agg_bwd(x, coeff32, dx_out=dx, dH=dH, row_weight=maskf, denom=denom,
+                                     scale=1.0 if denom is not None else 1.0 / N, rope=rope)
+        dc = dc.contiguous()
+        if cdt != torch.float32:
+            dc = ops.to_bf16(dc)
+        return dx, dc, None, None, None
+
+
+def _mask_kind(mask) -> str:
+    if mask is None:
+        return "none"
+    if isinstance(mask, str):
+        if mask == "causal":
+            return "causal"
+        raise ValueError('Unsupported mask: expected None, "causal", or a 2/3-D tensor.')
+    if isinstance(mask, torch.Tensor):
+        if mask.dim() == 2:
+            return "keypad"
+        if mask.dim() == 3:
+            return "full"
+    raise ValueError('Unsupported mask: expected None, "causal", or a 2/3-D tensor.')
+
+
+def polynomial_aggregation_(x: torch.Tensor, coeff: torch.Tensor, k: int, mask=None,
+                            rope: Optional[RopeSpec] = None) -> torch.Tensor:
+    """Polynomial aggregation over the sequence dimension (reference pom/pom.py:52-100).
+
+    x (B, N, P), coeff (P, K).  Returns (B, 1, P) for mask None or a (B, N) mask and
+    (B, N, P) for "causal".  A (B, M, N) mask is not implemented on this path yet.
+    """
+    if coeff.shape[1] != k:
+        raise ValueError(f"coeff has {coeff.shape[1]} columns but k={k}")
+    if k > 16:
+        raise NotImplementedError(f"polynomial degree k={k} > 16 is not implemented")
+    kind = _mask_kind(mask)
+    if kind == "full":
+        raise NotImplementedError("(B, M, N) masks are not implemented by the CUDA path yet")
+    return _PolyAgg.apply(x, coeff, kind, mask if kind == "keypad" else None, rope)
+
+
+class _GateMul(torch.autograd.Function):
+    """s ⊙ h with h broadcast over tokens (g == 1) or matched per token (g == t)."""
+
+    @staticmethod
+    def forward(ctx, s, h):
+        if not s.is_cuda:
+            raise RuntimeError("pom_b200 has no CPU path: pass CUDA tensors")
+        s = s.contiguous()
+        b, g, p = h.shape
+        per_tok = g != 1
+        hk = h.to(s.dtype).contiguous() if per_tok else _f32(h.reshape(b, p).contiguous())
+        ctx.save_for_backward(s, hk)
+        ctx.meta = (per_tok, h.dtype, h.shape)
+        return ops.select_fwd(s, None, hk, activated=True)
+
+    @staticmethod
+    def backward(ctx, g):
+        s, hk = ctx.saved_tensors
+        per_tok, hdt, hshape = ctx.meta
+        ds = torch.empty_like(s)
+        dh, _ = ops.select_bwd(g.contiguous(), s, None, hk, ds, activated=True)
+        if not per_tok:
+            dh = dh.view(hshape)
+            if hdt != torch.float32:
+                dh = ops.to_bf16(dh)
+        return ds, dh
+
+
+def polynomial_selection_(s: torch.Tensor, h: torch.Tensor, n_sel_heads: int) -> torch.Tensor:
+    """Gated selection s ⊙ h (reference pom/pom.py:103-122): s (B, T, P) already activated,
+    h (B, G, P) with G == 1 or G == T.  Multi-head scalar gating is not implemented on this path."""
+    b, g, dh = h.shape
+    t = s.shape[1]
+    assert g == 1 or t == 1 or g == t, f"incompatible shapes: g={g} t={t}"
+    if n_sel_heads > 1:
+        raise NotImplementedError("n_sel_heads > 1 is not implemented by the CUDA path yet")
+    if t == 1 and g != 1:
+        s = s.expand(b, g, dh)
+    return _GateMul.apply(s, h)
+
+
+def pom(xq, xc, coeff, k, n_sel_heads, mask=None):
+    """Aggregate the context polynomially, gate with the query (reference pom/pom.py:125-135)."""
+    h = polynomial_aggregation_(xc, coeff, k, mask)
+    return polynomial_selection_(xq, h, n_sel_heads)

@@ -118,15 +118,15 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     return out
 
 
-def reduce_partials(partial: torch.Tensor, *, inv_denom: Optional[torch.Tensor] = None, scale: float = 1.0,
+def reduce_partials(partial: torch.Tensor, *, denom: Optional[torch.Tensor] = None, scale: float = 1.0,
                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """(B, chunks, P) fp32 -> (B, P): scale * inv_denom[b] * sum over chunks, in a fixed order."""
-    _require_cuda(partial, inv_denom, out)
+    """(B, chunks, P) fp32 -> (B, P): scale * (sum over chunks, in a fixed order) / denom[b]."""
+    _require_cuda(partial, denom, out)
     B, chunks, P = partial.shape
     assert partial.dtype == torch.float32 and partial.is_contiguous()
     if out is None:
         out = torch.empty((B, P), dtype=torch.float32, device=partial.device)
-    _abi.check(_abi.lib().pom_reduce_partials(ptr(partial), ptr(out), ptr(inv_denom), scale, B, chunks, P,
+    _abi.check(_abi.lib().pom_reduce_partials(ptr(partial), ptr(out), ptr(denom), scale, B, chunks, P,
                                               _abi.stream_ptr()), "pom_reduce_partials")
     return out
 
@@ -222,12 +222,12 @@ def poly_agg_fwd(x: torch.Tensor, coeff: torch.Tensor, *, row_weight: Optional[t
 
 def poly_agg_bwd(x: torch.Tensor, coeff: torch.Tensor, *, dx_out: torch.Tensor, dH: Optional[torch.Tensor] = None,
                  dout: Optional[torch.Tensor] = None, row_weight: Optional[torch.Tensor] = None,
-                 inv_denom: Optional[torch.Tensor] = None, scale: float = 1.0, causal: bool = False,
+                 denom: Optional[torch.Tensor] = None, scale: float = 1.0, causal: bool = False,
                  rope: Optional[RopeSpec] = None, carry: Optional[torch.Tensor] = None, token_offset: int = 0,
-                 want_total: bool = False):
+                 want_total: bool = False, totals_only: bool = False):
     """Writes dx into ``dx_out`` (a (B, N, P) view, own row stride) and returns
     (dcoeff (P, K) fp32, total (B, P) fp32 or None)."""
-    dev = _require_cuda(x, coeff, dx_out, dH, dout, row_weight, inv_denom, carry)
+    dev = _require_cuda(x, coeff, dx_out, dH, dout, row_weight, denom, carry)
     B, N, P = x.shape
     K = coeff.shape[1]
     chunks = agg_chunks(N)
@@ -235,21 +235,24 @@ def poly_agg_bwd(x: torch.Tensor, coeff: torch.Tensor, *, dx_out: torch.Tensor, 
     partial = torch.empty((B, chunks, P), dtype=torch.float32, device=dev) if causal else None
     total = torch.empty((B, P), dtype=torch.float32, device=dev) if (causal and want_total) else None
     a = AggBwdArgs()
-    a.x, a.coeff, a.row_weight, a.inv_denom = ptr(x), ptr(coeff), ptr(row_weight), ptr(inv_denom)
+    a.x, a.coeff, a.row_weight, a.denom = ptr(x), ptr(coeff), ptr(row_weight), ptr(denom)
     a.dH, a.dout, a.carry, a.partial, a.total = ptr(dH), ptr(dout), ptr(carry), ptr(partial), ptr(total)
     a.dx, a.dcoeff_partial = ptr(dx_out), ptr(dcp)
     a.ldx, a.ld_dx = _row_stride(x), _row_stride(dx_out)
     a.ld_dout = _row_stride(dout) if dout is not None else 0
     a.token_offset, a.scale = token_offset, scale
     a.B, a.N, a.P, a.K = B, N, P, K
-    a.dtype, a.causal = _abi.dtype_code(x.dtype), int(causal)
+    a.dtype, a.causal, a.phase = _abi.dtype_code(x.dtype), int(causal), int(totals_only)
     a.rope = _rope_c(rope)
     _abi.check(_abi.lib().pom_poly_agg_bwd(C.byref(a), _abi.stream_ptr()), "pom_poly_agg_bwd")
+    if totals_only:
+        return None, total
     dcoeff = reduce_partials(dcp).view(P, K)
     return dcoeff, total
 
 
-def select_fwd(z: torch.Tensor, bias: torch.Tensor, h: torch.Tensor, *, rope: Optional[RopeSpec] = None) -> torch.Tensor:
+def select_fwd(z: torch.Tensor, bias: Optional[torch.Tensor], h: torch.Tensor, *, rope: Optional[RopeSpec] = None,
+               activated: bool = False) -> torch.Tensor:
     """SH = R·hardsigmoid(z + bias) ⊙ H.  ``h`` is (B, P) fp32 (one vector per sample) or (B, T, P) of z.dtype."""
     dev = _require_cuda(z, bias, h)
     B, T, P = z.shape
@@ -263,14 +266,14 @@ def select_fwd(z: torch.Tensor, bias: torch.Tensor, h: torch.Tensor, *, rope: Op
     a.z, a.bias, a.H, a.sh = ptr(z), ptr(bias), ptr(h), ptr(sh)
     a.ld_z, a.ld_h, a.ld_sh = _row_stride(z), (_row_stride(h) if per_tok else 0), P
     a.B, a.T, a.P = B, T, P
-    a.dtype, a.h_per_token = _abi.dtype_code(z.dtype), int(per_tok)
+    a.dtype, a.h_per_token, a.activated = _abi.dtype_code(z.dtype), int(per_tok), int(activated)
     a.rope = _rope_c(rope)
     _abi.check(_abi.lib().pom_select_fwd(C.byref(a), _abi.stream_ptr()), "pom_select_fwd")
     return sh
 
 
-def select_bwd(dsh: torch.Tensor, z: torch.Tensor, bias: torch.Tensor, h: torch.Tensor, dz_out: torch.Tensor, *,
-               rope: Optional[RopeSpec] = None):
+def select_bwd(dsh: torch.Tensor, z: torch.Tensor, bias: Optional[torch.Tensor], h: torch.Tensor, dz_out: torch.Tensor,
+               *, rope: Optional[RopeSpec] = None, activated: bool = False):
     """Returns (dH, dbias): dH is (B, P) fp32 un-normalised sum over tokens when ``h`` is per-sample,
     else the per-token (B, T, P) gradient in z.dtype.  dz is written into ``dz_out``."""
     dev = _require_cuda(dsh, z, bias, h, dz_out)
@@ -286,7 +289,7 @@ def select_bwd(dsh: torch.Tensor, z: torch.Tensor, bias: torch.Tensor, h: torch.
     a.ld_dsh, a.ld_z, a.ld_dz = _row_stride(dsh), _row_stride(z), _row_stride(dz_out)
     a.ld_h, a.ld_dh = (_row_stride(h) if per_tok else 0), P
     a.B, a.T, a.P = B, T, P
-    a.dtype, a.h_per_token = _abi.dtype_code(z.dtype), int(per_tok)
+    a.dtype, a.h_per_token, a.activated = _abi.dtype_code(z.dtype), int(per_tok), int(activated)
     a.rope = _rope_c(rope)
     _abi.check(_abi.lib().pom_select_bwd(C.byref(a), _abi.stream_ptr()), "pom_select_bwd")
     dbias = reduce_partials(db_p).view(P)

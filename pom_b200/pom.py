@@ -1,0 +1,105 @@
+"""``PoM`` — drop-in module for the reference's ``pom.PoM`` (reference pom/pom.py:142-280)
+running on the B200 kernels of this package.
+
+Constructor arguments, parameter names (``qc_proj.weight``, ``se_bias``, ``po_coeff``,
+``ag_proj.weight``) and their creation order are those of the reference, so a given
+``torch.manual_seed`` produces the same weights and checkpoints interchange.
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from .functional import LayerSpec, SeqShard, _mask_kind, pom_layer
+
+
+class PoM(nn.Module):
+    """Polynomial Mixer layer.
+
+    Args:
+        dim:         input/output feature dimension D.
+        degree:      polynomial degree K (1..16).
+        expand:      channel expansion; the polynomial features have P = expand * dim channels.
+        n_groups:    must be 1 (grouped projections are not implemented by the CUDA path).
+        n_sel_heads: must be 0 or 1 (multi-head scalar gating is not implemented by the CUDA path).
+        bias:        add a bias to the output projection.
+    """
+
+    def __init__(self, dim: int, degree: int, expand: int, n_groups: int = 1, n_sel_heads: int = 1, bias: bool = False):
+        super().__init__()
+        assert dim % n_groups == 0, "dim must be divisible by n_groups"
+        assert n_sel_heads <= 1 or dim * expand % n_sel_heads == 0, "dim * expand must be divisible by n_sel_heads"
+        if n_groups > 1:
+            raise NotImplementedError("n_groups > 1 (grouped projection) is not implemented by the CUDA path")
+        if n_sel_heads > 1:
+            raise NotImplementedError("n_sel_heads > 1 (multi-head gating) is not implemented by the CUDA path")
+        self.dim = dim
+        self.order = degree
+        self.order_expand = expand
+        self.n_groups = n_groups
+        self.n_sel_heads = n_sel_heads
+        self.head_dim = dim * expand // max(n_sel_heads, 1)
+        self._po_dim = expand * dim
+        self._se_dim = expand * dim
+        # creation order matters for seeded initialisation: qc_proj, se_bias, po_coeff, ag_proj
+        self.qc_proj = nn.Linear(dim, self._po_dim + self._se_dim, bias=False)
+        self.se_bias = nn.Parameter(torch.zeros(self._se_dim))
+        self.po_coeff = nn.Parameter(torch.randn(dim * expand, degree).clamp(-0.001, 0.001))
+        self.ag_proj = nn.Linear(expand * dim, dim, bias=bias)
+
+    # ------------------------------------------------------------------ helpers
+    def _spec(self, xq, xc, mask, shard: Optional[SeqShard]) -> Tuple[LayerSpec, Optional[torch.Tensor]]:
+        kind = _mask_kind(mask)
+        if kind == "full":
+            raise NotImplementedError("(B, M, N) masks are not implemented by the CUDA path yet")
+        spec = LayerSpec(degree=self.order, mask_kind=kind, self_mixing=(xc is None or xc is xq), shard=shard)
+        return spec, (mask if kind == "keypad" else None)
+
+    def _finish(self, y: torch.Tensor) -> torch.Tensor:
+        return y if self.ag_proj.bias is None else y + self.ag_proj.bias
+
+    # ------------------------------------------------------------------ API
+    def forward(self, xq: torch.Tensor, xc: Optional[torch.Tensor] = None, mask=None,
+                shard: Optional[SeqShard] = None) -> torch.Tensor:
+        """xq (B, T, D) queries; xc (B, N, D) context (None: self-mixing); mask None, "causal" or (B, N).
+
+        ``shard`` (extension) declares that xq/xc are this rank's token slice of a longer sequence.
+        """
+        spec, m = self._spec(xq, xc, mask, shard)
+        y, _ = pom_layer(xq, xc, self.qc_proj.weight, self.se_bias, self.po_coeff, self.ag_proj.weight, m, None, spec)
+        return self._finish(y)
+
+    def state_forward(self, xq: torch.Tensor, xc: Optional[torch.Tensor] = None,
+                      state: Optional[Dict[str, Any]] = None) -> Tuple[torch.Tensor, Dict[str, Any]]:
+        """Incremental forward with a running-mean state {'h': (B, 1, P) fp32, 'n': calls so far}.
+
+        As in the reference (pom/pom.py:251-262) the counter advances by one per call, so every
+        call weighs equally whatever its token count.
+        """
+        spec = LayerSpec(degree=self.order, self_mixing=(xc is None or xc is xq), want_state=True)
+        h_past = None
+        n_past = 0
+        if state is not None:
+            n_past = state["n"]
+            h_past = state["h"]
+            if not torch.is_tensor(h_past):  # after reset(): h == 0.0
+                h_past = None if n_past == 0 else torch.full((xq.shape[0], 1, self._po_dim), float(h_past),
+                                                             device=xq.device, dtype=torch.float32)
+        if h_past is not None and n_past > 0:
+            spec.n_past = float(n_past)
+        else:
+            h_past = None
+        y, h = pom_layer(xq, xc, self.qc_proj.weight, self.se_bias, self.po_coeff, self.ag_proj.weight, None, h_past, spec)
+        return self._finish(y), {"h": h, "n": n_past + 1}
+
+    @torch.no_grad()
+    def ar_forward(self, xq: torch.Tensor, state: Dict[str, Any]):
+        raise NotImplementedError("ar_forward is not implemented by the CUDA path (the reference version does not "
+                                  "aggregate either; use state_forward)")
+
+    def reset(self, state: Dict[str, Any]) -> Dict[str, Any]:
+        state["h"] = 0.0
+        state["n"] = 0
+        return state

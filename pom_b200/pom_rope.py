@@ -1,0 +1,105 @@
+"""``PoMRoPE`` — drop-in for the reference's ``pom.PoMRoPE`` (reference pom/pom_rope.py:303-526).
+
+The polynomial features of each context token are rotated by that token's position before
+aggregation, and the hardsigmoid gate of each query token is rotated by the query position
+before gating.  1-D positions pair channel p with p + P/2; 2-D (row, col) positions rotate the
+first half of the channels by the row index and the second half by the column index.
+Table buffers keep the reference names (``freqs_cos``/``freqs_sin`` or ``row_cos``/``row_sin``/
+``col_cos``/``col_sin``) so state dicts interchange.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _abi
+from .functional import LayerSpec, SeqShard, _mask_kind, pom_layer
+from .ops import RopeSpec
+from .pom import PoM
+
+
+def precompute_freqs_1d(dim: int, max_seq_len: int, base: float = 10000.0) -> Tuple[torch.Tensor, torch.Tensor]:
+    """cos/sin tables (max_seq_len, dim // 2) with theta_k = base^(-k / (dim/2))  (reference pom/pom_rope.py:93-118)."""
+    assert dim % 2 == 0, f"dim must be even for 1-D RoPE, got {dim}"
+    half = dim // 2
+    inv_freq = 1.0 / (base ** (torch.arange(0, half, dtype=torch.float32) / half))
+    ang = torch.outer(torch.arange(max_seq_len, dtype=torch.float32), inv_freq)
+    return ang.cos(), ang.sin()
+
+
+def precompute_freqs_2d(dim: int, max_h: int, max_w: int, base: float = 10000.0):
+    """Row and column cos/sin tables, each (max, dim // 4)  (reference pom/pom_rope.py:121-149)."""
+    assert dim % 4 == 0, f"dim must be divisible by 4 for 2-D RoPE, got {dim}"
+    quarter = dim // 4
+    inv_freq = 1.0 / (base ** (torch.arange(0, quarter, dtype=torch.float32) / quarter))
+    ra = torch.outer(torch.arange(max_h, dtype=torch.float32), inv_freq)
+    ca = torch.outer(torch.arange(max_w, dtype=torch.float32), inv_freq)
+    return ra.cos(), ra.sin(), ca.cos(), ca.sin()
+
+
+class PoMRoPE(PoM):
+    """Polynomial Mixer with rotary position embedding.
+
+    Extra arguments: ``max_seq_len`` (1-D table length), ``max_h`` / ``max_w`` (2-D table sizes),
+    ``rope_base``, ``rope_2d``.
+    """
+
+    def __init__(self, dim: int, degree: int, expand: int, n_groups: int = 1, n_sel_heads: int = 1, bias: bool = False,
+                 max_seq_len: int = 4096, max_h: int = 64, max_w: int = 64, rope_base: float = 10000.0,
+                 rope_2d: bool = False):
+        super().__init__(dim, degree, expand, n_groups, n_sel_heads, bias)
+        self.rope_2d = rope_2d
+        rope_dim = dim * expand
+        if rope_2d:
+            assert rope_dim % 4 == 0, f"dim * expand ({rope_dim}) must be divisible by 4 for 2-D RoPE"
+            rc, rs, cc, cs = precompute_freqs_2d(rope_dim, max_h, max_w, rope_base)
+            self.register_buffer("row_cos", rc)
+            self.register_buffer("row_sin", rs)
+            self.register_buffer("col_cos", cc)
+            self.register_buffer("col_sin", cs)
+        else:
+            assert rope_dim % 2 == 0, f"dim * expand ({rope_dim}) must be even for 1-D RoPE"
+            fc, fs = precompute_freqs_1d(rope_dim, max_seq_len, rope_base)
+            self.register_buffer("freqs_cos", fc)
+            self.register_buffer("freqs_sin", fs)
+
+    def _rope_spec(self, n_tokens: int, positions, positions_hw, device) -> RopeSpec:
+        if self.rope_2d:
+            if positions_hw is None:
+                raise ValueError("positions_hw (N, 2) must be provided when rope_2d=True")
+            pos = positions_hw.to(device=device, dtype=torch.int64).contiguous()
+            if pos.shape != (n_tokens, 2):
+                raise ValueError(f"positions_hw must have shape ({n_tokens}, 2)")
+            return RopeSpec(_abi.ROPE_2D, self.row_cos.float().contiguous(), self.row_sin.float().contiguous(), pos,
+                            self.col_cos.float().contiguous(), self.col_sin.float().contiguous())
+        if positions is None:
+            positions = torch.arange(n_tokens, device=device)
+        pos = positions.to(device=device, dtype=torch.int64).contiguous()
+        if pos.shape != (n_tokens,):
+            raise ValueError(f"positions must have shape ({n_tokens},)")
+        return RopeSpec(_abi.ROPE_1D, self.freqs_cos.float().contiguous(), self.freqs_sin.float().contiguous(), pos)
+
+    def forward(self, xq: torch.Tensor, xc: Optional[torch.Tensor] = None, mask=None,
+                positions: Optional[torch.Tensor] = None, ctx_positions: Optional[torch.Tensor] = None,
+                positions_hw: Optional[torch.Tensor] = None, ctx_positions_hw: Optional[torch.Tensor] = None,
+                shard: Optional[SeqShard] = None) -> torch.Tensor:
+        """As ``PoM.forward`` plus token positions: ``positions`` (T,) / ``ctx_positions`` (N,) int64 for
+        1-D tables (default 0..T-1; the context defaults to the query positions under self-mixing, else
+        0..N-1), ``positions_hw`` (T, 2) / ``ctx_positions_hw`` (N, 2) for 2-D tables."""
+        self_mixing = xc is None or xc is xq
+        kind = _mask_kind(mask)
+        if kind == "full":
+            raise NotImplementedError("(B, M, N) masks are not implemented by the CUDA path yet")
+        T = xq.shape[1]
+        N = T if self_mixing else xc.shape[1]
+        cpos = ctx_positions if ctx_positions is not None else (positions if self_mixing else None)
+        cpos_hw = ctx_positions_hw if ctx_positions_hw is not None else (positions_hw if self_mixing else None)
+        rope_q = self._rope_spec(T, positions, positions_hw, xq.device)
+        same = self_mixing and ctx_positions is None and ctx_positions_hw is None
+        rope_c = rope_q if same else self._rope_spec(N, cpos, cpos_hw, xq.device)
+        spec = LayerSpec(degree=self.order, mask_kind=kind, self_mixing=self_mixing, rope_ctx=rope_c, rope_qry=rope_q,
+                         shard=shard)
+        y, _ = pom_layer(xq, xc, self.qc_proj.weight, self.se_bias, self.po_coeff, self.ag_proj.weight,
+                         mask if kind == "keypad" else None, None, spec)
+        return self._finish(y)

@@ -1,0 +1,79 @@
+"""Shared helpers of the GPU parity tests: build modules from golden parameters, run the
+CUDA layer and the CPU oracle on the same tensors, compare with norm-relative errors."""
+import torch
+
+from oracle import pom_oracle as O
+
+FP32_TOL = 1e-4   # norm-relative and max-normalised bound of the fp32 mode
+BF16_TOL = 2e-2   # bound for bf16 storage with fp32 accumulation
+
+PARAM_ORDER = ["qc_proj.weight", "se_bias", "po_coeff", "ag_proj.weight"]
+
+
+def rope_cfg(cfg):
+    if "rope" not in cfg:
+        return None
+    r = cfg["rope"]
+    return O.RopeConfig(two_d=r["two_d"], max_seq_len=r.get("max_seq_len", 4096), max_h=r.get("max_h", 64),
+                        max_w=r.get("max_w", 64))
+
+
+def make_cuda_module(cfg, params, dtype, device="cuda"):
+    """pom_b200 module holding ``params`` (fp32 CPU tensors) cast to ``dtype``; rotary tables stay fp32."""
+    from pom_b200 import PoM, PoMRoPE
+
+    r = cfg.get("rope")
+    if r is None:
+        mod = PoM(cfg["dim"], cfg["degree"], cfg["expand"], 1, cfg["heads"])
+    else:
+        mod = PoMRoPE(cfg["dim"], cfg["degree"], cfg["expand"], 1, cfg["heads"], rope_2d=r["two_d"],
+                      max_seq_len=r.get("max_seq_len", 4096), max_h=r.get("max_h", 64), max_w=r.get("max_w", 64))
+    with torch.no_grad():
+        mod.qc_proj.weight.copy_(params["qc_proj.weight"])
+        mod.se_bias.copy_(params["se_bias"])
+        mod.po_coeff.copy_(params["po_coeff"])
+        mod.ag_proj.weight.copy_(params["ag_proj.weight"])
+    mod = mod.to(device)
+    for p in mod.parameters():
+        p.data = p.data.to(dtype)
+    return mod
+
+
+def oracle_run(cfg, params, xq, xc, kwargs, gy):
+    """Oracle forward + gradients in fp32 on the given (already rounded) CPU tensors."""
+    ps = {k: params[k].clone().float().requires_grad_(True) for k in PARAM_ORDER}
+    model = O.OraclePoM(ps, cfg["degree"], cfg["expand"], cfg["heads"], rope_cfg(cfg))
+    xq = xq.clone().float().requires_grad_(True)
+    ins = [xq]
+    if xc is not None:
+        xc = xc.clone().float().requires_grad_(True)
+        ins.append(xc)
+    y = model.forward(xq, xc, **kwargs)
+    grads = torch.autograd.grad(y, ins + [ps[k] for k in PARAM_ORDER], gy.float())
+    names = [f"in{i}" for i in range(len(ins))] + PARAM_ORDER
+    return y.detach(), dict(zip(names, grads))
+
+
+def cuda_run(mod, xq, xc, kwargs, gy, dtype, device="cuda"):
+    xq = xq.to(device=device, dtype=dtype).requires_grad_(True)
+    ins = [xq]
+    if xc is not None:
+        xc = xc.to(device=device, dtype=dtype).requires_grad_(True)
+        ins.append(xc)
+    kw = {k: (v.to(device) if torch.is_tensor(v) else v) for k, v in kwargs.items()}
+    y = mod(xq, xc, **kw) if xc is not None else mod(xq, **kw)
+    ps = [dict(mod.named_parameters())[k] for k in PARAM_ORDER]
+    grads = torch.autograd.grad(y, ins + ps, gy.to(device=device, dtype=dtype))
+    names = [f"in{i}" for i in range(len(ins))] + PARAM_ORDER
+    return y.detach(), dict(zip(names, grads))
+
+
+def assert_close(got, want, tol, label):
+    n2, mx = O.rel_errors(got.float().cpu(), want.float().cpu())
+    assert n2 <= tol and mx <= tol, f"{label}: rel2={n2:.3e} relmax={mx:.3e} > {tol:.1e}"
+
+
+def assert_status_clean(device="cuda"):
+    from pom_b200 import _abi
+
+    assert _abi.read_status(device) == 0, "a device-side wait timed out"

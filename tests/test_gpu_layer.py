@@ -1,0 +1,250 @@
+"""GPU parity of the whole layer (forward + every gradient) against the reference's own
+vectors (fp32 mode) and against the CPU oracle on bf16-rounded inputs (bf16 mode)."""
+import pytest
+import torch
+
+from oracle import pom_oracle as O
+from tests.helpers import (BF16_TOL, FP32_TOL, PARAM_ORDER, assert_close, assert_status_clean, cuda_run,
+                           make_cuda_module, oracle_run)
+
+pytestmark = pytest.mark.gpu
+
+LAYER_CASES = ["pom_none", "pom_causal", "pom_mask2d", "pom_cross", "pom_cross_mask2d",
+               "rope1d_none", "rope1d_causal", "rope1d_mask2d", "rope1d_positions", "rope1d_cross",
+               "rope2d_none", "rope2d_causal"]
+
+
+@pytest.mark.parametrize("name", LAYER_CASES)
+def test_fp32_layer_matches_reference_vectors(golden, name):
+    case = golden[name]
+    mod = make_cuda_module(case["cfg"], case["params"], torch.float32)
+    y, grads = cuda_run(mod, case["xq"], case["xc"], case["kwargs"], case["gy"], torch.float32)
+    assert_close(y, case["y"], FP32_TOL, f"{name} y")
+    n_in = 1 if case["xc"] is None else 2
+    for i in range(n_in):
+        assert_close(grads[f"in{i}"], case["grads"][f"d_in{i}"], FP32_TOL, f"{name} d_in{i}")
+    for k in PARAM_ORDER:
+        assert_close(grads[k], case["grads"]["d_" + k], FP32_TOL, f"{name} d_{k}")
+
+
+@pytest.mark.parametrize("name", LAYER_CASES)
+def test_bf16_layer_matches_oracle_on_rounded_inputs(golden, name):
+    case = golden[name]
+    cfg = case["cfg"]
+    params = {k: O.bf16_round(case["params"][k]) for k in PARAM_ORDER}
+    xq = O.bf16_round(case["xq"])
+    xc = None if case["xc"] is None else O.bf16_round(case["xc"])
+    gy = O.bf16_round(case["gy"])
+    want_y, want_g = oracle_run(cfg, params, xq, xc, case["kwargs"], gy)
+    mod = make_cuda_module(cfg, params, torch.bfloat16)
+    y, grads = cuda_run(mod, xq, xc, case["kwargs"], gy, torch.bfloat16)
+    assert_status_clean()
+    assert_close(y, want_y, BF16_TOL, f"{name} y")
+    for k, w in want_g.items():
+        assert_close(grads[k], w, BF16_TOL, f"{name} d_{k}")
+
+
+def _seeded_case(B, N, D, K, E, seed=0, coeff_scale=None, bias_scale=0.0):
+    params = O.init_params(D, K, E, seed=seed, coeff_scale=coeff_scale)
+    g = torch.Generator().manual_seed(seed + 1)
+    if bias_scale:
+        params["se_bias"] = torch.randn(params["se_bias"].shape, generator=g) * bias_scale
+    x = torch.randn(B, N, D, generator=g)
+    gy = torch.randn(B, N, D, generator=g)
+    return dict(dim=D, degree=K, expand=E, heads=1), params, x, gy
+
+
+def test_fp32_reference_cpu_configuration(golden):
+    """BASELINE config 1 (fp32, B=2, N=256, D=256, degree 2, expand 2, seed 0) on the GPU."""
+    from pom_b200 import PoM
+
+    case = golden["cfg1_fp32"]
+    torch.manual_seed(0)
+    mod = PoM(256, 2, 2, 1, 1)
+    torch.manual_seed(0)
+    x = torch.randn(2, 256, 256)
+    y = mod.cuda()(x.cuda())
+    assert_close(y[:, ::8, ::8], case["y_sample"], FP32_TOL, "cfg1 y sample")
+    assert abs(y.abs().mean().item() - case["y_abs_mean"]) < 1e-3 * case["y_abs_mean"]
+
+
+@pytest.mark.parametrize("coeff_scale", [None, 0.1])
+@pytest.mark.parametrize("shape", [(2, 1024, 1152, 2, 2), (3, 200, 96, 3, 2), (2, 130, 64, 4, 1)])
+def test_bf16_fused_path_against_oracle(shape, coeff_scale):
+    """DiT-style no-mask layer (BASELINE config 2 at reduced batch) and ragged shapes that leave partial
+    tiles in every dimension; default (tiny) and O(1) polynomial coefficients."""
+    B, N, D, K, E = shape
+    cfg, params, x, gy = _seeded_case(B, N, D, K, E, coeff_scale=coeff_scale, bias_scale=0.5)
+    params = {k: O.bf16_round(v) for k, v in params.items()}
+    x, gy = O.bf16_round(x), O.bf16_round(gy)
+    want_y, want_g = oracle_run(cfg, params, x, None, {}, gy)
+    mod = make_cuda_module(cfg, params, torch.bfloat16)
+    y, grads = cuda_run(mod, x, None, {}, gy, torch.bfloat16)
+    assert_status_clean()
+    assert_close(y, want_y, BF16_TOL, "y")
+    for k, w in want_g.items():
+        assert_close(grads[k], w, BF16_TOL, f"d_{k}")
+
+
+def test_bf16_masked_layer_ignores_padded_noise():
+    """BASELINE config 3 at reduced size: key-padding mask from per-sample lengths, noise in the padding."""
+    B, N, D, K, E = 4, 512, 128, 3, 2
+    cfg, params, x, gy = _seeded_case(B, N, D, K, E, seed=3, coeff_scale=0.1)
+    params = {k: O.bf16_round(v) for k, v in params.items()}
+    g = torch.Generator().manual_seed(3)
+    lengths = torch.randint(64, N + 1, (B,), generator=g)
+    mask = (torch.arange(N).view(1, N) < lengths.view(B, 1)).float()
+    x, gy = O.bf16_round(x), O.bf16_round(gy)
+    want_y, want_g = oracle_run(cfg, params, x, None, {"mask": mask}, gy)
+    mod = make_cuda_module(cfg, params, torch.bfloat16)
+    y, grads = cuda_run(mod, x, None, {"mask": mask}, gy, torch.bfloat16)
+    assert_close(y, want_y, BF16_TOL, "y")
+    for k, w in want_g.items():
+        assert_close(grads[k], w, BF16_TOL, f"d_{k}")
+    # replacing the padded context rows by other noise must not change the valid outputs at all
+    x2 = x.clone()
+    pad = mask == 0
+    x2[pad] = O.bf16_round(torch.randn(int(pad.sum()), D, generator=g))
+    y2, _ = cuda_run(mod, x2, None, {"mask": mask}, gy, torch.bfloat16)
+    valid = mask.bool().cuda()
+    assert torch.equal(y[valid], y2[valid])
+
+
+def test_all_masked_sample_aggregates_to_zero():
+    """A sample whose mask has no valid token yields zeros (not NaN)."""
+    cfg, params, x, gy = _seeded_case(2, 64, 32, 2, 2, seed=5, coeff_scale=0.1)
+    mask = torch.ones(2, 64)
+    mask[1] = 0
+    mod = make_cuda_module(cfg, params, torch.float32)
+    y = mod(x.cuda(), mask=mask.cuda())
+    assert torch.isfinite(y).all()
+    assert float(y[1].abs().max()) == 0.0
+
+
+def test_state_forward_matches_reference_vectors(golden):
+    case = golden["pom_state"]
+    mod = make_cuda_module(case["cfg"], case["params"], torch.float32)
+    state = None
+    for f, want in zip(case["frames"], case["ys"]):
+        y, state = mod.state_forward(f.cuda(), None, state)
+        assert_close(y, want, FP32_TOL, "state_forward y")
+    assert state["n"] == case["n"]
+    assert_close(state["h"], case["h"], FP32_TOL, "state h")
+
+
+def test_block_causal_video_stack_frame_loop():
+    """BASELINE config 4 at reduced size: a residual stack of PoM + GELU FFN layers run frame by frame
+    with state_forward equals the oracle's frame loop; bf16."""
+    B, F, L, D, K, E, layers = 2, 4, 64, 64, 2, 4, 3
+    g = torch.Generator().manual_seed(4)
+    x = O.bf16_round(torch.randn(B, F * L, D, generator=g))
+    stack = []
+    for l in range(layers):
+        p = {k: O.bf16_round(v) for k, v in O.init_params(D, K, E, seed=10 + l, coeff_scale=0.1).items()}
+        w1 = O.bf16_round((torch.rand(4 * D, D, generator=g) * 2 - 1) / D ** 0.5)
+        w2 = O.bf16_round((torch.rand(D, 4 * D, generator=g) * 2 - 1) / (4 * D) ** 0.5)
+        stack.append((p, w1, w2))
+    cfg = dict(dim=D, degree=K, expand=E, heads=1)
+
+    def run(layer_fn, xin, to_dev):
+        states = [None] * layers
+        outs = []
+        for f in range(F):
+            h = to_dev(xin[:, f * L:(f + 1) * L])
+            for l, (p, w1, w2) in enumerate(stack):
+                y, states[l] = layer_fn(l, h, states[l])
+                h = h + y
+                h = h + torch.nn.functional.gelu(h @ to_dev(w1).t().to(h.dtype)) @ to_dev(w2).t().to(h.dtype)
+            outs.append(h)
+        return torch.cat(outs, 1)
+
+    oracles = [O.OraclePoM(p, K, E) for p, _, _ in stack]
+    want = run(lambda l, h, s: oracles[l].state_forward(h, None, s), x, lambda t: t.float())
+    mods = [make_cuda_module(cfg, p, torch.bfloat16) for p, _, _ in stack]
+    with torch.no_grad():
+        got = run(lambda l, h, s: mods[l].state_forward(h, None, s), x, lambda t: t.cuda().bfloat16())
+    assert_close(got, want, 3 * BF16_TOL, "video stack output")  # bf16 residual stream over 3 layers x 4 frames
+
+
+def test_token_causal_long_sequence_against_linear_time_oracle():
+    """Token-causal forward at a length where the reference's N x N mask would be impractical."""
+    cfg, params, x, gy = _seeded_case(1, 8192, 64, 2, 2, seed=6, coeff_scale=0.1, bias_scale=0.3)
+    want_y, want_g = oracle_run(cfg, params, x, None, {"mask": "causal"}, gy)
+    mod = make_cuda_module(cfg, params, torch.float32)
+    y, grads = cuda_run(mod, x, None, {"mask": "causal"}, gy, torch.float32)
+    assert_close(y, want_y, FP32_TOL, "y")
+    for k, w in want_g.items():
+        assert_close(grads[k], w, 2 * FP32_TOL, f"d_{k}")
+
+
+def test_rope2d_grid_bf16_against_oracle():
+    """BASELINE config 5 at reduced size: 2-D axial rotary positions on a 32 x 32 grid, non-causal and causal."""
+    D, K, E, side = 64, 2, 2, 32
+    N = side * side
+    cfg, params, x, gy = _seeded_case(1, N, D, K, E, seed=7, coeff_scale=0.1)
+    cfg = dict(cfg, rope=dict(two_d=True, max_h=side, max_w=side))
+    params = {k: O.bf16_round(v) for k, v in params.items()}
+    x, gy = O.bf16_round(x), O.bf16_round(gy)
+    hw = torch.stack([torch.arange(N) // side, torch.arange(N) % side], 1)
+    for mask in (None, "causal"):
+        kw = {"mask": mask, "positions_hw": hw}
+        want_y, want_g = oracle_run(cfg, params, x, None, kw, gy)
+        mod = make_cuda_module(cfg, params, torch.bfloat16)
+        y, grads = cuda_run(mod, x, None, kw, gy, torch.bfloat16)
+        assert_close(y, want_y, BF16_TOL, f"y mask={mask}")
+        for k, w in want_g.items():
+            assert_close(grads[k], w, BF16_TOL, f"d_{k} mask={mask}")
+
+
+def test_results_are_bitwise_reproducible():
+    cfg, params, x, gy = _seeded_case(2, 384, 128, 2, 2, seed=8, coeff_scale=0.1)
+    mod = make_cuda_module(cfg, params, torch.bfloat16)
+    y1, g1 = cuda_run(mod, x, None, {}, gy, torch.bfloat16)
+    y2, g2 = cuda_run(mod, x, None, {}, gy, torch.bfloat16)
+    assert torch.equal(y1, y2)
+    for k in ("in0", "se_bias", "po_coeff"):
+        assert torch.equal(g1[k], g2[k]), k
+
+
+def test_full_size_dit_layer_properties():
+    """BASELINE config 2 at full size (B=32, N=1024, D=1152): size-independent properties.
+    (1) permuting the tokens of a sample permutes its outputs (no-mask mixing is a set function);
+    (2) the backward pass is linear in the upstream gradient."""
+    B, N, D, K, E = 32, 1024, 1152, 2, 2
+    cfg, params, _, _ = _seeded_case(1, 8, D, K, E, seed=0, coeff_scale=0.1)
+    mod = make_cuda_module(cfg, params, torch.bfloat16)
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(B, N, D, device="cuda", generator=gen).bfloat16()
+    perm = torch.randperm(N, device="cuda", generator=gen)
+    with torch.no_grad():
+        y = mod(x)
+        yp = mod(x[:, perm].contiguous())
+    n2, mx = O.rel_errors(yp, y[:, perm])
+    assert n2 < 5e-3 and mx < 2e-2, (n2, mx)  # only the summation order inside H changes
+    g1 = torch.randn(B, N, D, device="cuda", generator=gen).bfloat16()
+    g2 = torch.randn(B, N, D, device="cuda", generator=gen).bfloat16()
+    xr = x.clone().requires_grad_(True)
+    out = mod(xr)
+    d1, = torch.autograd.grad(out, xr, g1, retain_graph=True)
+    d2, = torch.autograd.grad(out, xr, g2, retain_graph=True)
+    d12, = torch.autograd.grad(out, xr, (g1.float() + g2.float()).bfloat16())
+    n2, mx = O.rel_errors(d12, d1.float() + d2.float())
+    assert n2 < BF16_TOL, (n2, mx)
+    assert_status_clean()
+
+
+def test_cpu_tensors_are_rejected_loudly():
+    from pom_b200 import PoM
+
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        PoM(16, 2, 2)(torch.randn(1, 4, 16))
+
+
+def test_unsupported_mask_and_degree_raise_like_the_reference():
+    from pom_b200 import PoM, polynomial_aggregation_
+
+    mod = PoM(16, 2, 2).cuda()
+    with pytest.raises(ValueError):
+        mod(torch.randn(1, 4, 16, device="cuda"), mask="diagonal")
+    with pytest.raises(NotImplementedError):
+        polynomial_aggregation_(torch.randn(1, 4, 16, device="cuda"), torch.randn(16, 17, device="cuda"), 17)
