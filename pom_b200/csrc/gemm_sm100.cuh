@@ -99,6 +99,8 @@ constexpr int gemm_smem_bytes() {
 // The kernel.  `Epi` supplies:
 //   struct Params;                      trivially copyable, passed by value
 //   static constexpr int kSmemBytes;    scratch shared by the 4 epilogue warps
+//   template<int BN> static __device__ void prologue(const Params&, const GemmGeom&, const TileCtx&,
+//        int epi_tid, float* scratch, int tile_iter);      stages per-column constants in shared memory
 //   template<int BN> static __device__ void run(const Params&, const GemmGeom&, const TileCtx&,
 //        uint32_t tmem_acc, int quarter, int lane, int epi_tid, float* scratch, int tile_iter);
 // ---------------------------------------------------------------------------
@@ -254,10 +256,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const TileCtx t = decode_tile(geom, unit, BN);
       const int acc = iter & 1;
       const uint32_t acc_phase = (iter >> 1) & 1u;
+      // Stage the per-column constants of this tile while its main loop is still running.
+      Epi::template prologue<BN>(ep, geom, t, epi_tid, epi_scratch, iter);
       // All 32 lanes poll so the warp stays converged for the .aligned TMEM loads.
-      bool ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, status, kStatusEpilogueTimeout);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      const bool ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, status, kStatusEpilogueTimeout);
+      // The four epilogue warps decide together whether to go on, so none of them can be left
+      // waiting at a named barrier that another one will never reach.
+      if (named_bar_any(kEpiBarrier, kEpiThreads, !ok)) break;
       tc_fence_after();
       const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(acc * BN) + (static_cast<uint32_t>(quarter * 32) << 16);
       Epi::template run<BN>(ep, geom, t, tmem_acc, quarter, lane, epi_tid, epi_scratch, iter);
@@ -274,274 +279,5 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     tmem_dealloc(tmem_base, kTmemCols);
   }
 }
-
-// ===========================================================================
-// Epilogues
-// ===========================================================================
-
-// Store 32 consecutive fp32 values of one row as bf16 (64 bytes, 16-byte vector stores).
-__device__ __forceinline__ void store_row32_bf16(__nv_bfloat16* dst, const float (&v)[32], int ncols_left) {
-  if (ncols_left >= 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-    uint4* d4 = reinterpret_cast<uint4*>(dst);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      uint4 q;
-      q.x = pack_bf16x2(v[8 * j + 0], v[8 * j + 1]);
-      q.y = pack_bf16x2(v[8 * j + 2], v[8 * j + 3]);
-      q.z = pack_bf16x2(v[8 * j + 4], v[8 * j + 5]);
-      q.w = pack_bf16x2(v[8 * j + 6], v[8 * j + 7]);
-      d4[j] = q;
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 32; ++i)
-      if (i < ncols_left) dst[i] = __float2bfloat16_rn(v[i]);
-  }
-}
-
-__device__ __forceinline__ void load_row32_bf16(const __nv_bfloat16* src, float (&v)[32], int ncols_left) {
-  if (ncols_left >= 32 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
-    const uint4* s4 = reinterpret_cast<const uint4*>(src);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      uint4 q = __ldg(&s4[j]);
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        float2 f = __bfloat1622float2(h[e]);
-        v[8 * j + 2 * e] = f.x;
-        v[8 * j + 2 * e + 1] = f.y;
-      }
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = (i < ncols_left) ? __bfloat162float(src[i]) : 0.f;
-  }
-}
-
-__device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
-
-// --------------------------------------------------------------- plain store
-struct EpiStore {
-  struct Params {
-    void* C;             // bf16 or fp32, row-major
-    long long ldc;       // elements
-    long long batch_stride;  // elements between batches
-    int mode;            // 0: bf16 store, 1: fp32 store, 2: fp32 atomic add (split-K)
-    float alpha;
-  };
-  static constexpr int kSmemBytes = 0;
-
-  template <int BN>
-  static __device__ __forceinline__ void run(const Params& p, const GemmGeom& g, const TileCtx& t, uint32_t tmem_acc,
-                                             int quarter, int lane, int, float*, int) {
-    const int row = quarter * 32 + lane;
-    const bool row_ok = row < t.rows_valid;
-    const long long off = static_cast<long long>(t.b) * p.batch_stride + static_cast<long long>(t.row0 + row) * p.ldc;
-#pragma unroll 1
-    for (int c = 0; c < BN / 32; ++c) {
-      const int col = t.col0 + c * 32;
-      if (col >= g.n_cols) break;  // warp-uniform
-      float v[32];
-      tmem_ld32(tmem_acc + c * 32, v);
-      tmem_ld_wait();
-      const int left = g.n_cols - col;
-      if (!row_ok) continue;
-      if (p.alpha != 1.f) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] *= p.alpha;
-      }
-      if (p.mode == 0) {
-        store_row32_bf16(reinterpret_cast<__nv_bfloat16*>(p.C) + off + col, v, left);
-      } else {
-        float* dst = reinterpret_cast<float*>(p.C) + off + col;
-        if (p.mode == 1) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (i < left) dst[i] = v[i];
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (i < left) atomicAdd(dst + i, v[i]);
-        }
-      }
-    }
-  }
-};
-
-// --------------------------------------------------------------- context phase
-// acc = X·Wpoᵀ.  Rounds to bf16 (what the backward pass will re-read), stores it
-// when asked, applies act + polynomial (+ per-token weight), and reduces over the
-// tile's tokens.  Per-tile column sums go to `partial[(b * MT + mt), :]` in a
-// fixed order, so the result is run-to-run deterministic.
-struct EpiCtx {
-  struct Params {
-    const float* coeff;        // (P, K) fp32
-    int K;
-    const float* row_weight;   // (B, rows_per_batch) fp32 or null (key-padding mask weights)
-    __nv_bfloat16* hp_out;     // (B*rows, ld_hp) or null
-    long long ld_hp;
-    float* partial;            // (B * MT, P) fp32
-    int P;
-  };
-  static constexpr int kSmemBytes = 2 * 4 * 256 * 4;  // two buffers of [4 quarters][256 cols]
-
-  template <int BN>
-  static __device__ __forceinline__ void run(const Params& p, const GemmGeom& g, const TileCtx& t, uint32_t tmem_acc,
-                                             int quarter, int lane, int epi_tid, float* scratch, int iter) {
-    const int row = quarter * 32 + lane;
-    const bool row_ok = row < t.rows_valid;
-    const long long grow = static_cast<long long>(t.b) * g.rows_per_batch + t.row0 + row;
-    float w = row_ok ? 1.f : 0.f;
-    if (row_ok && p.row_weight) w = __ldg(p.row_weight + grow);
-    float* buf = scratch + (iter & 1) * (4 * 256);
-#pragma unroll 1
-    for (int c = 0; c < BN / 32; ++c) {
-      const int col = t.col0 + c * 32;
-      if (col >= g.n_cols) {  // warp-uniform
-        buf[quarter * 256 + c * 32 + lane] = 0.f;
-        continue;
-      }
-      float v[32];
-      tmem_ld32(tmem_acc + c * 32, v);
-      tmem_ld_wait();
-      const int left = g.n_cols - col;
-#pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = round_bf16(v[i]);
-      if (p.hp_out && row_ok) store_row32_bf16(p.hp_out + grow * p.ld_hp + col, v, left);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const int ci = min(col + i, g.n_cols - 1);
-        v[i] = (i < left) ? w * pom_poly(pom_act(v[i]), p.coeff + static_cast<long long>(ci) * p.K, p.K) : 0.f;
-      }
-      warp_colsum32(v, lane);
-      buf[quarter * 256 + c * 32 + lane] = v[0];
-    }
-    named_bar_sync(kEpiBarrier, kEpiThreads);
-    for (int c = epi_tid; c < BN; c += kEpiThreads) {
-      const int col = t.col0 + c;
-      if (col < g.n_cols) {
-        const float s = (buf[c] + buf[256 + c]) + (buf[512 + c] + buf[768 + c]);
-        p.partial[(static_cast<long long>(t.b) * g.m_tiles_per_batch + t.mt) * p.P + col] = s;
-      }
-    }
-  }
-};
-
-// --------------------------------------------------------------- query phase
-// acc = X·Wseᵀ.  z = bf16(acc) is kept for the backward pass; the gated feature
-// s ⊙ H with s = hardsigmoid(z + bias) is written as bf16, ready to be the A
-// operand of the output projection.  H is addressed per (batch, row) with strides
-// so both the broadcast (B, P) state and a per-token (B, T, P) prefix are covered.
-struct EpiGate {
-  struct Params {
-    const float* bias;       // (P) fp32
-    const float* H;          // fp32
-    long long h_batch_stride;
-    long long h_row_stride;  // 0 when H is one vector per batch
-    __nv_bfloat16* z_out;    // null in inference
-    long long ld_z;
-    __nv_bfloat16* sh_out;
-    long long ld_sh;
-  };
-  static constexpr int kSmemBytes = 0;
-
-  template <int BN>
-  static __device__ __forceinline__ void run(const Params& p, const GemmGeom& g, const TileCtx& t, uint32_t tmem_acc,
-                                             int quarter, int lane, int, float*, int) {
-    const int row = quarter * 32 + lane;
-    const bool row_ok = row < t.rows_valid;
-    const long long grow = static_cast<long long>(t.b) * g.rows_per_batch + t.row0 + row;
-    const float* hrow = p.H + static_cast<long long>(t.b) * p.h_batch_stride +
-                        static_cast<long long>(row_ok ? t.row0 + row : t.row0) * p.h_row_stride;
-#pragma unroll 1
-    for (int c = 0; c < BN / 32; ++c) {
-      const int col = t.col0 + c * 32;
-      if (col >= g.n_cols) break;
-      float v[32];
-      tmem_ld32(tmem_acc + c * 32, v);
-      tmem_ld_wait();
-      const int left = g.n_cols - col;
-#pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = round_bf16(v[i]);
-      if (p.z_out && row_ok) store_row32_bf16(p.z_out + grow * p.ld_z + col, v, left);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const int ci = min(col + i, g.n_cols - 1);
-        v[i] = pom_hardsigmoid(v[i] + __ldg(p.bias + ci)) * __ldg(hrow + ci);
-      }
-      if (row_ok) store_row32_bf16(p.sh_out + grow * p.ld_sh + col, v, left);
-    }
-  }
-};
-
-// --------------------------------------------------------------- query phase, backward
-// acc = dY·Wo = dSH.  With z re-read from the forward pass:
-//   s  = hardsigmoid(z + bias)
-//   dH partial  = sum_rows dSH ⊙ s                      -> dh_partial[(b*MT+mt), :]
-//   dz          = dSH ⊙ H ⊙ hardsigmoid'(z + bias)      -> g_out (bf16), the se half of [dhp | dz]
-//   dbias part. = sum_rows dz                            -> db_partial[(b*MT+mt), :]
-struct EpiGateBwd {
-  struct Params {
-    const float* bias;
-    const float* H;
-    long long h_batch_stride;
-    const __nv_bfloat16* z;
-    long long ld_z;
-    __nv_bfloat16* g_out;
-    long long ld_g;
-    float* dh_partial;
-    float* db_partial;
-    int P;
-  };
-  static constexpr int kSmemBytes = 2 * 2 * 4 * 256 * 4;
-
-  template <int BN>
-  static __device__ __forceinline__ void run(const Params& p, const GemmGeom& g, const TileCtx& t, uint32_t tmem_acc,
-                                             int quarter, int lane, int epi_tid, float* scratch, int iter) {
-    const int row = quarter * 32 + lane;
-    const bool row_ok = row < t.rows_valid;
-    const long long grow = static_cast<long long>(t.b) * g.rows_per_batch + t.row0 + (row_ok ? row : 0);
-    const float* hrow = p.H + static_cast<long long>(t.b) * p.h_batch_stride;
-    float* buf_h = scratch + (iter & 1) * (2 * 4 * 256);
-    float* buf_b = buf_h + 4 * 256;
-#pragma unroll 1
-    for (int c = 0; c < BN / 32; ++c) {
-      const int col = t.col0 + c * 32;
-      if (col >= g.n_cols) {
-        buf_h[quarter * 256 + c * 32 + lane] = 0.f;
-        buf_b[quarter * 256 + c * 32 + lane] = 0.f;
-        continue;
-      }
-      float v[32], z[32];
-      tmem_ld32(tmem_acc + c * 32, v);
-      const int left = g.n_cols - col;
-      load_row32_bf16(p.z + grow * p.ld_z + col, z, left);
-      tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const int ci = min(col + i, g.n_cols - 1);
-        const float zz = z[i] + __ldg(p.bias + ci);
-        const float dsh = (row_ok && i < left) ? v[i] : 0.f;
-        z[i] = dsh * __ldg(hrow + ci) * pom_hardsigmoid_grad(zz);  // dz
-        v[i] = dsh * pom_hardsigmoid(zz);                           // dH contribution
-      }
-      if (row_ok) store_row32_bf16(p.g_out + grow * p.ld_g + col, z, left);
-      warp_colsum32(v, lane);
-      warp_colsum32(z, lane);
-      buf_h[quarter * 256 + c * 32 + lane] = v[0];
-      buf_b[quarter * 256 + c * 32 + lane] = z[0];
-    }
-    named_bar_sync(kEpiBarrier, kEpiThreads);
-    for (int c = epi_tid; c < BN; c += kEpiThreads) {
-      const int col = t.col0 + c;
-      if (col < g.n_cols) {
-        const long long o = (static_cast<long long>(t.b) * g.m_tiles_per_batch + t.mt) * p.P + col;
-        p.dh_partial[o] = (buf_h[c] + buf_h[256 + c]) + (buf_h[512 + c] + buf_h[768 + c]);
-        p.db_partial[o] = (buf_b[c] + buf_b[256 + c]) + (buf_b[512 + c] + buf_b[768 + c]);
-      }
-    }
-  }
-};
 
 }  // namespace pomk

@@ -3,7 +3,7 @@
 #include <cudaTypedefs.h>
 #include <mutex>
 #include "common.cuh"
-#include "gemm_sm100.cuh"
+#include "epilogues.cuh"
 
 using namespace pomk;
 using namespace pomh;
@@ -159,12 +159,42 @@ int launch_major(const Operands& o, int split_k, const typename Epi::Params& ep,
   return launch<BN, STAGES, true, true, Epi>(o, split_k, ep, status, st);
 }
 
-// Tile width: 256 columns when that wastes little of the last tile, else 128.
-int pick_bn(int64_t n) {
+// Tile width: the candidate that pads the output least; ties go to the wider tile
+// (fewer operand bytes per flop).
+int pick_bn(int64_t n, bool allow_192 = true) {
   if (n <= 128) return 128;
-  const int64_t pad256 = ceil_div(n, 256) * 256 - n;
-  const int64_t pad128 = ceil_div(n, 128) * 128 - n;
-  return (pad256 <= pad128 + n / 16) ? 256 : 128;
+  int best = 256;
+  int64_t best_pad = ceil_div(n, 256) * 256;
+  const int cands[2] = {192, 128};
+  for (int c : cands) {
+    if (c == 192 && !allow_192) continue;
+    const int64_t padded = ceil_div(n, c) * c;
+    if (padded < best_pad) {
+      best_pad = padded;
+      best = c;
+    }
+  }
+  return best;
+}
+
+// Split of the reduction dimension for accumulate-mode GEMMs: the smallest split whose work
+// units fill the last wave of SMs to at least 93 %, keeping at least 8 k-blocks per split.
+int pick_split(long long tiles, long long kblocks) {
+  const int sms = sm_count();
+  long long cap = kblocks / 8 > 0 ? kblocks / 8 : 1;
+  if (cap > 32) cap = 32;
+  int best = 1;
+  double best_eff = 0.0;
+  for (int s = 1; s <= cap; ++s) {
+    const long long units = tiles * s;
+    const double eff = static_cast<double>(units) / static_cast<double>(ceil_div(units, sms) * sms);
+    if (eff > best_eff + 1e-9) {
+      best_eff = eff;
+      best = s;
+    }
+    if (eff >= 0.93) return s;
+  }
+  return best;
 }
 
 // ---------------------------------------------------------------- fp32 SIMT GEMM
@@ -253,15 +283,7 @@ int pom_gemm_bf16(const pom_gemm_args* a, int* status, void* stream) {
     split = 1;
   }
   const int bn = pick_bn(a->N);
-  if (split == 0) {
-    // Aim for about four waves of work units, keeping at least 8 k-blocks per split.
-    const long long tiles = 1ll * a->batches * ceil_div(a->M, kBM) * ceil_div(a->N, bn);
-    const long long kblocks = ceil_div(a->K, kBK);
-    long long want = ceil_div(4ll * sm_count(), tiles);
-    long long cap = kblocks / 8 > 0 ? kblocks / 8 : 1;
-    split = static_cast<int>(want < cap ? want : cap);
-    if (split < 1) split = 1;
-  }
+  if (split == 0) split = pick_split(1ll * a->batches * ceil_div(a->M, kBM) * ceil_div(a->N, bn), ceil_div(a->K, kBK));
   EpiStore::Params ep;
   ep.C = a->C;
   ep.ldc = a->ldc;
@@ -270,6 +292,7 @@ int pom_gemm_bf16(const pom_gemm_args* a, int* status, void* stream) {
   ep.alpha = a->alpha;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (bn == 256) return launch_major<256, 4, EpiStore>(o, split, ep, status, st);
+  if (bn == 192) return launch_major<192, 5, EpiStore>(o, split, ep, status, st);
   return launch_major<128, 6, EpiStore>(o, split, ep, status, st);
 }
 
@@ -308,7 +331,7 @@ int pom_ctx_gemm(const pom_ctx_args* a, int* status, void* stream) {
   ep.partial = a->partial;
   ep.P = a->P;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (pick_bn(a->P) == 256) return launch<256, 4, false, false, EpiCtx>(o, 1, ep, status, st);
+  if (pick_bn(a->P, false) == 256) return launch<256, 4, false, false, EpiCtx>(o, 1, ep, status, st);
   return launch<128, 6, false, false, EpiCtx>(o, 1, ep, status, st);
 }
 
@@ -317,6 +340,7 @@ int pom_gate_gemm(const pom_gate_args* a, int* status, void* stream) {
   Operands o{a->X, a->Wse, a->T, a->P, a->D, a->ldx, a->ldw, a->B, false, false};
   int rc = check_operands(o);
   if (rc) return rc;
+  if (a->h_row_stride != 0) return POM_ERR_UNSUPPORTED;
   if (a->ld_sh % 8 || a->ld_sh < a->P || !aligned16(a->sh_out)) return POM_ERR_BAD_ALIGN;
   if (a->z_out && (a->ld_z % 8 || a->ld_z < a->P || !aligned16(a->z_out))) return POM_ERR_BAD_ALIGN;
   EpiGate::Params ep;
@@ -329,7 +353,7 @@ int pom_gate_gemm(const pom_gate_args* a, int* status, void* stream) {
   ep.sh_out = static_cast<__nv_bfloat16*>(a->sh_out);
   ep.ld_sh = a->ld_sh;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (pick_bn(a->P) == 256) return launch<256, 4, false, false, EpiGate>(o, 1, ep, status, st);
+  if (pick_bn(a->P, false) == 256) return launch<256, 4, false, false, EpiGate>(o, 1, ep, status, st);
   return launch<128, 6, false, false, EpiGate>(o, 1, ep, status, st);
 }
 
@@ -352,7 +376,7 @@ int pom_gate_bwd_gemm(const pom_gate_bwd_args* a, int* status, void* stream) {
   ep.db_partial = a->db_partial;
   ep.P = a->P;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (pick_bn(a->P) == 256) return launch<256, 4, false, true, EpiGateBwd>(o, 1, ep, status, st);
+  if (pick_bn(a->P, false) == 256) return launch<256, 4, false, true, EpiGateBwd>(o, 1, ep, status, st);
   return launch<128, 6, false, true, EpiGateBwd>(o, 1, ep, status, st);
 }
 

@@ -150,6 +150,20 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// Barrier among `nthreads` threads that also ORs a predicate across them.
+__device__ __forceinline__ bool named_bar_any(int id, int nthreads, bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %1, 0;\n\t"
+      "bar.red.or.pred p, %2, %3, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(out)
+      : "r"(static_cast<uint32_t>(pred)), "r"(id), "r"(nthreads)
+      : "memory");
+  return out != 0;
+}
+
 // ---------------------------------------------------------------- descriptors
 // Shared-memory matrix descriptor for a 128-byte-swizzled bf16 operand tile.
 //  K-major : rows of 64 K-elements (128 B); 8 rows form a 1024 B swizzle atom; SBO = 1024 B.
