@@ -101,6 +101,11 @@ typedef struct pom_gemm_args {
 } pom_gemm_args;
 int pom_gemm_bf16(const pom_gemm_args* a, int* status, void* stream);
 
+/* Tuning knob for every tcgen05 GEMM entry point: 0 = choose per problem (default), 1 = always the
+ * kernel that gives one CTA a 128 x BN tile, 2 = always the kernel in which a cluster of two CTAs
+ * shares a 256 x BN tile (tcgen05 cta_group::2; each CTA loads half of the B tile). */
+int pom_set_gemm_mode(int mode);
+
 /* fp32 SIMT GEMM with the same meaning (fp32 A, Bm, C; out_mode F32 or F32_ACCUM); used by the
  * fp32 precision mode, where tensor-core inputs would not meet the 1e-4 bound. */
 int pom_gemm_f32(const pom_gemm_args* a, void* stream);

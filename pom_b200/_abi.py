@@ -131,6 +131,7 @@ _SIGNATURES = {
     "pom_device_check": (C.c_int, []),
     "pom_launch_count": (C.c_longlong, []),
     "pom_gemm_bf16": (C.c_int, [C.POINTER(GemmArgs), C.c_void_p, C.c_void_p]),
+    "pom_set_gemm_mode": (C.c_int, [C.c_int]),
     "pom_gemm_f32": (C.c_int, [C.POINTER(GemmArgs), C.c_void_p]),
     "pom_ctx_gemm": (C.c_int, [C.POINTER(CtxArgs), C.c_void_p, C.c_void_p]),
     "pom_reduce_partials": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),

@@ -1,0 +1,308 @@
+// Two-SM variant of the GEMM engine: a cluster of two CTAs computes one 256 x BN
+// output tile with tcgen05.mma.cta_group::2.  Each CTA loads its own 128 rows of A
+// and only HALF of the B tile (BN/2 rows), so the bytes pulled from L2 per flop drop
+// by a third against the one-CTA kernel, whose 128 x 256 tiles are L2-bandwidth bound.
+// Every CTA issues its own plain TMA loads; nothing is broadcast between CTAs.
+//
+//   CTA rank 0 (leader): TMA producer, MMA issuer for the pair, epilogue of rows 0..127
+//   CTA rank 1 (peer)  : TMA producer,                           epilogue of rows 128..255
+//
+// Synchronisation (all waits bounded):
+//   full[s]   leader only.  The leader arms it with the byte count of BOTH CTAs; the peer's
+//             loads signal it remotely (cta_group::2 load form, barrier address mapped to rank 0).
+//   empty[s]  in both CTAs, released by two tcgen05.commit (one local, one to the peer's address).
+//   tfull[a]  in both CTAs, same mechanism, after the last k-block of a tile.
+//   tempty[a] leader only; the epilogue warps of both CTAs arrive on it (the peer remotely).
+#pragma once
+#include "gemm_sm100.cuh"
+
+namespace pomk {
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Address of the same shared-memory object in CTA `rank` of this cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(smem_addr), "r"(rank));
+  return out;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma2_load_2d(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x,
+                                             int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tma2_load_3d(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x,
+                                             int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t* smem_holder, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_holder)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma2_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the barrier at `cluster_addr` (this CTA's or the peer's) once every MMA issued so far
+// by this thread has finished.
+__device__ __forceinline__ void umma2_commit(uint32_t cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+
+__host__ __device__ constexpr uint32_t make_idesc_bf16_m256(int bn, bool a_mn_major, bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |
+         (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(bn >> 3) << 17) |
+         (static_cast<uint32_t>(256 >> 4) << 24);
+}
+
+// Work unit -> the tile of THIS CTA (rank r takes the r-th 128-row half of the 256-row pair tile).
+// A pair may hang over the end of a batch: then rows_valid is 0 and the tile contributes nothing.
+__device__ __forceinline__ TileCtx decode_pair_tile(const GemmGeom& g, int unit, int bn, int rank) {
+  const int pairs_per_batch = (g.m_tiles_per_batch + 1) >> 1;
+  const int pairs_m = g.batches * pairs_per_batch;
+  const int per_split = pairs_m * g.n_tiles;
+  TileCtx t;
+  t.split = unit / per_split;
+  const int u = unit - t.split * per_split;
+  const int gm = max(1, g.group_m >> 1);
+  const int band_sz = gm * g.n_tiles;
+  const int band = u / band_sz;
+  const int in_band = u - band * band_sz;
+  const int m_lo = band * gm;
+  const int band_rows = min(gm, pairs_m - m_lo);
+  const int n = in_band / band_rows;
+  const int mp = m_lo + (in_band - n * band_rows);
+  t.b = mp / pairs_per_batch;
+  t.mt = 2 * (mp - t.b * pairs_per_batch) + rank;
+  t.row0 = t.mt * kBM;
+  t.rows_valid = max(0, min(kBM, g.rows_per_batch - t.row0));
+  t.col0 = n * bn;
+  return t;
+}
+
+template <int BN>
+struct Gemm2Smem {
+  static constexpr int kABytes = kBM * kBK * 2;        // this CTA's 128 rows of A
+  static constexpr int kBBytes = (BN / 2) * kBK * 2;   // this CTA's half of the B tile
+  static constexpr int kStageBytes = kABytes + kBBytes;
+};
+
+template <int BN, int STAGES, int EPI_SMEM>
+constexpr int gemm2_smem_bytes() {
+  return STAGES * Gemm2Smem<BN>::kStageBytes + 256 + EPI_SMEM + 1024;
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN, class Epi>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const GemmGeom geom, const typename Epi::Params ep, int* __restrict__ status) {
+  static_assert(BN == 128 || BN == 256 || (BN == 192 && !B_MN), "unsupported pair-tile width");
+  constexpr int kABytes = Gemm2Smem<BN>::kABytes;
+  constexpr int kStageBytes = Gemm2Smem<BN>::kStageBytes;
+  constexpr int kHalfN = BN / 2;
+  constexpr uint32_t kTmemCols = (2 * BN <= 256) ? 256u : 512u;
+  constexpr uint32_t kIdesc = make_idesc_bf16_m256(BN, A_MN, B_MN);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* tiles = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * kStageBytes);
+  uint64_t* full_bar = bars;                     // [STAGES]  used in the leader
+  uint64_t* empty_bar = bars + STAGES;           // [STAGES]  both CTAs
+  uint64_t* tfull_bar = bars + 2 * STAGES;       // [2]       both CTAs
+  uint64_t* tempty_bar = bars + 2 * STAGES + 2;  // [2]       used in the leader
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  float* epi_scratch = reinterpret_cast<float*>(smem + STAGES * kStageBytes + 256);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 2 * 4 * kEpiColSplit);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc2(tmem_holder, kTmemCols);
+    tmem_relinquish2();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before any remote arrive or remote load completion
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  const int pairs_per_batch = (geom.m_tiles_per_batch + 1) >> 1;
+  const int total_units = geom.batches * pairs_per_batch * geom.n_tiles * geom.split_k;
+  const int cluster_id = blockIdx.x >> 1;
+  const int n_clusters = gridDim.x >> 1;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool alive = true;
+      for (int unit = cluster_id; unit < total_units && alive; unit += n_clusters) {
+        const TileCtx t = decode_pair_tile(geom, unit, BN, rank);
+        const int kb0 = t.split * geom.kb_per_split;
+        const int kb1 = min(geom.k_blocks, kb0 + geom.kb_per_split);
+        const int bcol0 = t.col0 + static_cast<int>(rank) * kHalfN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, status, kStatusProducerTimeout)) {
+            alive = false;
+            break;
+          }
+          uint8_t* sa = tiles + stage * kStageBytes;
+          uint8_t* sb = sa + kABytes;
+          const uint32_t full0 = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          if (leader) mbar_expect_tx(&full_bar[stage], 2 * kStageBytes);
+          if constexpr (!A_MN) {
+            tma2_load_3d(sa, &tmA, full0, kb * kBK, t.row0, t.b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < kBM / 64; ++j) tma2_load_2d(sa + j * (kBK * 128), &tmA, full0, t.row0 + j * 64, kb * kBK);
+          }
+          if constexpr (!B_MN) {
+            tma2_load_2d(sb, &tmB, full0, kb * kBK, bcol0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < kHalfN / 64; ++j)
+              tma2_load_2d(sb + j * (kBK * 128), &tmB, full0, bcol0 + j * 64, kb * kBK);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!alive) {
+        for (int i = 0; i < 64; ++i) __nanosleep(2000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader only)
+    if (leader && lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int iter = 0;
+      bool alive = true;
+      for (int unit = cluster_id; unit < total_units && alive; unit += n_clusters, ++iter) {
+        const TileCtx t = decode_pair_tile(geom, unit, BN, 0);
+        const int kb0 = t.split * geom.kb_per_split;
+        const int kb1 = min(geom.k_blocks, kb0 + geom.kb_per_split);
+        const int acc = iter & 1;
+        const uint32_t acc_phase = (iter >> 1) & 1u;
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_flag, status, kStatusMmaTimeout)) {
+          alive = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, status, kStatusMmaTimeout)) {
+            alive = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(tiles + stage * kStageBytes);
+          const uint32_t sb = sa + kABytes;
+#pragma unroll
+          for (int k16 = 0; k16 < kBK / 16; ++k16) {
+            const uint64_t da = A_MN ? make_smem_desc(sa + k16 * 2048, kBK * 128, 1024)
+                                     : make_smem_desc(sa + k16 * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc(sb + k16 * 2048, kBK * 128, 1024)
+                                     : make_smem_desc(sb + k16 * 32, 16, 1024);
+            umma2_bf16(tmem_d, da, db, kIdesc, (kb > kb0 || k16 > 0) ? 1u : 0u);
+          }
+          // release the stage in both CTAs once these MMAs have read it
+          const uint32_t e_local = smem_u32(&empty_bar[stage]);
+          umma2_commit(e_local);
+          umma2_commit(map_to_cta(e_local, 1));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (alive) {
+          const uint32_t f_local = smem_u32(&tfull_bar[acc]);
+          umma2_commit(f_local);
+          umma2_commit(map_to_cta(f_local, 1));
+        }
+      }
+      if (!alive) {
+        for (int i = 0; i < 64; ++i) __nanosleep(2000);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (both CTAs, own rows)
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int epi_tid = (warp - 2) * 32 + lane;
+    int iter = 0;
+    for (int unit = cluster_id; unit < total_units; unit += n_clusters, ++iter) {
+      const TileCtx t = decode_pair_tile(geom, unit, BN, rank);
+      const int acc = iter & 1;
+      const uint32_t acc_phase = (iter >> 1) & 1u;
+      Epi::template prologue<BN>(ep, geom, t, epi_tid, epi_scratch, iter);
+      const bool ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, status, kStatusEpilogueTimeout);
+      if (named_bar_any(kEpiBarrier, kEpiThreads, !ok)) break;
+      tc_fence_after();
+      const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(acc * BN) + (static_cast<uint32_t>(quarter * 32) << 16);
+      Epi::template run<BN>(ep, geom, t, tmem_acc, quarter, lane, half, epi_tid, epi_scratch, iter);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the leader's MMAs read the peer's shared memory: nobody leaves early
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc2(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace pomk

@@ -9,10 +9,11 @@
 // (G·W) and the weight-gradient products (Gᵀ·X) of the PoM layer without any
 // transposed copy.
 //
-// CTA layout (192 threads, one CTA per SM):
+// CTA layout (320 threads, one CTA per SM):
 //   warp 0      : TMA producer   (one lane issues the tile loads)
 //   warp 1      : MMA issuer     (one lane issues tcgen05.mma / commit); owns TMEM alloc
-//   warps 2..5  : epilogue       (each reads one 32-lane quarter of the accumulator)
+//   warps 2..9  : epilogue       (two warps per 32-lane quarter of the accumulator, interleaving
+//                                 the 32-column chunks of the tile)
 // The accumulator is double-buffered in tensor memory (2 x BN fp32 columns), so
 // the epilogue of tile i overlaps the main loop of tile i+1.
 //
@@ -27,8 +28,9 @@ namespace pomk {
 
 constexpr int kBM = 128;          // rows per tile (= TMEM lanes)
 constexpr int kBK = 64;           // K elements per pipeline stage (= one 128-byte swizzle row)
-constexpr int kGemmThreads = 192;
-constexpr int kEpiThreads = 128;
+constexpr int kEpiColSplit = 2;     // epilogue warps per 32-lane quarter; they interleave the 32-column chunks
+constexpr int kGemmThreads = 64 + 128 * kEpiColSplit;
+constexpr int kEpiThreads = 128 * kEpiColSplit;
 constexpr int kEpiBarrier = 1;
 
 enum GemmStatus : int {
@@ -137,7 +139,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
-      mbar_init(&tempty_bar[a], 4);
+      mbar_init(&tempty_bar[a], 4 * kEpiColSplit);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -250,7 +252,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   } else {
     // ------------------------------------------------------------ epilogue
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) are readable by this warp
-    const int epi_tid = quarter * 32 + lane;
+    const int half = (warp - 2) >> 2;  // which of the interleaved column chunks this warp takes
+    const int epi_tid = (warp - 2) * 32 + lane;
     int iter = 0;
     for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x, ++iter) {
       const TileCtx t = decode_tile(geom, unit, BN);
@@ -265,7 +268,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       if (named_bar_any(kEpiBarrier, kEpiThreads, !ok)) break;
       tc_fence_after();
       const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(acc * BN) + (static_cast<uint32_t>(quarter * 32) << 16);
-      Epi::template run<BN>(ep, geom, t, tmem_acc, quarter, lane, epi_tid, epi_scratch, iter);
+      Epi::template run<BN>(ep, geom, t, tmem_acc, quarter, lane, half, epi_tid, epi_scratch, iter);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);

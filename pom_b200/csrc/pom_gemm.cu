@@ -4,6 +4,7 @@
 #include <mutex>
 #include "common.cuh"
 #include "epilogues.cuh"
+#include "gemm2_sm100.cuh"
 
 using namespace pomk;
 using namespace pomh;
@@ -71,7 +72,8 @@ struct Operands {
   bool a_mn, b_mn;
 };
 
-int build_maps(const Operands& o, int bn, CUtensorMap* tmA, CUtensorMap* tmB) {
+// `b_rows`: rows of the B tile one CTA loads per stage (K-major B only; MN-major B uses 64-wide boxes).
+int build_maps(const Operands& o, int b_rows, CUtensorMap* tmA, CUtensorMap* tmB) {
   int rc;
   if (!o.a_mn) {
     uint64_t dims[3] = {static_cast<uint64_t>(o.K), static_cast<uint64_t>(o.M), static_cast<uint64_t>(o.batches)};
@@ -89,7 +91,7 @@ int build_maps(const Operands& o, int bn, CUtensorMap* tmA, CUtensorMap* tmB) {
   if (!o.b_mn) {
     uint64_t dims[2] = {static_cast<uint64_t>(o.K), static_cast<uint64_t>(o.N)};
     uint64_t str[1] = {static_cast<uint64_t>(o.ldb)};
-    uint32_t box[2] = {static_cast<uint32_t>(kBK), static_cast<uint32_t>(bn)};
+    uint32_t box[2] = {static_cast<uint32_t>(kBK), static_cast<uint32_t>(b_rows)};
     rc = make_map(tmB, o.Bm, 2, dims, str, box);
   } else {
     uint64_t dims[2] = {static_cast<uint64_t>(o.N), static_cast<uint64_t>(o.K)};
@@ -126,6 +128,21 @@ int check_operands(const Operands& o) {
   return POM_OK;
 }
 
+// 0: automatic choice, 1: always the one-CTA kernel, 2: always the two-CTA (pair) kernel.
+std::atomic<int> g_gemm_mode{0};
+
+template <class Kern>
+int set_smem_once(Kern kern, int smem, bool* done) {
+  if (*done) return POM_OK;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return POM_ERR_CUDA;
+  }
+  *done = true;
+  return POM_OK;
+}
+
+// One CTA per 128 x BN tile.
 template <int BN, int STAGES, bool A_MN, bool B_MN, class Epi>
 int launch(const Operands& o, int split_k, const typename Epi::Params& ep, int* status, cudaStream_t st) {
   CUtensorMap tmA, tmB;
@@ -135,13 +152,7 @@ int launch(const Operands& o, int split_k, const typename Epi::Params& ep, int* 
   constexpr int smem = gemm_smem_bytes<BN, STAGES, Epi::kSmemBytes>();
   auto kern = gemm_tcgen05_kernel<BN, STAGES, A_MN, B_MN, Epi>;
   static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
-      (void)cudaGetLastError();
-      return POM_ERR_CUDA;
-    }
-    attr_set = true;
-  }
+  if ((rc = set_smem_once(kern, smem, &attr_set))) return rc;
   const long long units = 1ll * g.batches * g.m_tiles_per_batch * g.n_tiles * g.split_k;
   if (units > INT32_MAX) return POM_ERR_TOO_LARGE;
   const int grid = static_cast<int>(units < sm_count() ? units : sm_count());
@@ -150,44 +161,66 @@ int launch(const Operands& o, int split_k, const typename Epi::Params& ep, int* 
   return check_launch();
 }
 
-// Majorness dispatch for one epilogue / tile width.
-template <int BN, int STAGES, class Epi>
-int launch_major(const Operands& o, int split_k, const typename Epi::Params& ep, int* status, cudaStream_t st) {
-  if (!o.a_mn && !o.b_mn) return launch<BN, STAGES, false, false, Epi>(o, split_k, ep, status, st);
-  if (!o.a_mn && o.b_mn) return launch<BN, STAGES, false, true, Epi>(o, split_k, ep, status, st);
-  if (o.a_mn && !o.b_mn) return launch<BN, STAGES, true, false, Epi>(o, split_k, ep, status, st);
-  return launch<BN, STAGES, true, true, Epi>(o, split_k, ep, status, st);
+// Two CTAs (one cluster) per 256 x BN tile; each CTA loads BN/2 rows of the B tile.
+template <int BN, int STAGES, bool A_MN, bool B_MN, class Epi>
+int launch_pair(const Operands& o, int split_k, const typename Epi::Params& ep, int* status, cudaStream_t st) {
+  CUtensorMap tmA, tmB;
+  int rc = build_maps(o, BN / 2, &tmA, &tmB);
+  if (rc) return rc;
+  GemmGeom g = make_geom(o, BN, split_k);
+  constexpr int smem = gemm2_smem_bytes<BN, STAGES, Epi::kSmemBytes>();
+  auto kern = gemm_tcgen05_2cta_kernel<BN, STAGES, A_MN, B_MN, Epi>;
+  static bool attr_set = false;
+  if ((rc = set_smem_once(kern, smem, &attr_set))) return rc;
+  const long long units = 1ll * g.batches * ((g.m_tiles_per_batch + 1) / 2) * g.n_tiles * g.split_k;
+  if (units > INT32_MAX) return POM_ERR_TOO_LARGE;
+  const int clusters = static_cast<int>(units < sm_count() / 2 ? units : sm_count() / 2);
+  kern<<<2 * clusters, kGemmThreads, smem, st>>>(tmA, tmB, g, ep, status);
+  count_launch();
+  return check_launch();
 }
 
-// Tile width: the candidate that pads the output least; ties go to the wider tile
-// (fewer operand bytes per flop).
-int pick_bn(int64_t n, bool allow_192 = true) {
-  if (n <= 128) return 128;
-  int best = 256;
-  int64_t best_pad = ceil_div(n, 256) * 256;
-  const int cands[2] = {192, 128};
-  for (int c : cands) {
-    if (c == 192 && !allow_192) continue;
-    const int64_t padded = ceil_div(n, c) * c;
-    if (padded < best_pad) {
-      best_pad = padded;
-      best = c;
+struct TilePlan {
+  bool pair;
+  int bn;
+};
+
+// Operand bytes pulled from L2 per output element are proportional to (rowsA + rowsB) / (128 * BN)
+// with rowsB = BN (one CTA) or BN/2 (pair); weigh that by the padded width and take the cheapest.
+TilePlan pick_plan(const Operands& o, bool allow_192) {
+  const int mode = g_gemm_mode.load(std::memory_order_relaxed);
+  const long long m_tiles = 1ll * o.batches * ceil_div(o.M, kBM);
+  TilePlan best{false, 128};
+  double best_cost = -1.0;
+  for (int pair = 0; pair < 2; ++pair) {
+    if (mode == 1 && pair) continue;
+    if (mode == 2 && !pair) continue;
+    if (mode == 0 && pair && m_tiles * ceil_div(o.N, 256) < sm_count()) continue;  // too little work to pair up
+    const int cands[3] = {256, 192, 128};
+    for (int bn : cands) {
+      if (bn == 192 && (!allow_192 || (pair && o.b_mn))) continue;
+      if (o.N <= 128 && bn != 128) continue;
+      const double padded = static_cast<double>(ceil_div(o.N, bn) * bn);
+      const double cost = padded * (128.0 + (pair ? bn / 2 : bn)) / bn;
+      if (best_cost < 0 || cost < best_cost - 1e-9) {
+        best_cost = cost;
+        best = TilePlan{pair != 0, bn};
+      }
     }
   }
   return best;
 }
 
 // Split of the reduction dimension for accumulate-mode GEMMs: the smallest split whose work
-// units fill the last wave of SMs to at least 93 %, keeping at least 8 k-blocks per split.
-int pick_split(long long tiles, long long kblocks) {
-  const int sms = sm_count();
+// units fill the last wave to at least 93 %, keeping at least 8 k-blocks per split.
+int pick_split(long long units, long long kblocks, int slots) {
   long long cap = kblocks / 8 > 0 ? kblocks / 8 : 1;
   if (cap > 32) cap = 32;
   int best = 1;
   double best_eff = 0.0;
   for (int s = 1; s <= cap; ++s) {
-    const long long units = tiles * s;
-    const double eff = static_cast<double>(units) / static_cast<double>(ceil_div(units, sms) * sms);
+    const long long u = units * s;
+    const double eff = static_cast<double>(u) / static_cast<double>(ceil_div(u, slots) * slots);
     if (eff > best_eff + 1e-9) {
       best_eff = eff;
       best = s;
@@ -195,6 +228,36 @@ int pick_split(long long tiles, long long kblocks) {
     if (eff >= 0.93) return s;
   }
   return best;
+}
+
+long long plan_units(const Operands& o, const TilePlan& p) {
+  const long long mt = ceil_div(o.M, kBM);
+  return 1ll * o.batches * (p.pair ? (mt + 1) / 2 : mt) * ceil_div(o.N, p.bn);
+}
+
+// Dispatch over kernel flavour and tile width for a fixed operand order and epilogue.
+template <bool A_MN, bool B_MN, class Epi>
+int run_plan(const TilePlan& p, const Operands& o, int split, const typename Epi::Params& ep, int* status,
+             cudaStream_t st) {
+  if (p.pair) {
+    if (p.bn == 256) return launch_pair<256, 6, A_MN, B_MN, Epi>(o, split, ep, status, st);
+    if constexpr (!B_MN) {
+      if (p.bn == 192) return launch_pair<192, 6, A_MN, B_MN, Epi>(o, split, ep, status, st);
+    }
+    return launch_pair<128, 8, A_MN, B_MN, Epi>(o, split, ep, status, st);
+  }
+  if (p.bn == 256) return launch<256, 4, A_MN, B_MN, Epi>(o, split, ep, status, st);
+  if (p.bn == 192) return launch<192, 5, A_MN, B_MN, Epi>(o, split, ep, status, st);
+  return launch<128, 6, A_MN, B_MN, Epi>(o, split, ep, status, st);
+}
+
+template <class Epi>
+int run_plan_any_major(const TilePlan& p, const Operands& o, int split, const typename Epi::Params& ep, int* status,
+                       cudaStream_t st) {
+  if (!o.a_mn && !o.b_mn) return run_plan<false, false, Epi>(p, o, split, ep, status, st);
+  if (!o.a_mn && o.b_mn) return run_plan<false, true, Epi>(p, o, split, ep, status, st);
+  if (o.a_mn && !o.b_mn) return run_plan<true, false, Epi>(p, o, split, ep, status, st);
+  return run_plan<true, true, Epi>(p, o, split, ep, status, st);
 }
 
 // ---------------------------------------------------------------- fp32 SIMT GEMM
@@ -282,18 +345,21 @@ int pom_gemm_bf16(const pom_gemm_args* a, int* status, void* stream) {
     if (split > 1) return POM_ERR_UNSUPPORTED;
     split = 1;
   }
-  const int bn = pick_bn(a->N);
-  if (split == 0) split = pick_split(1ll * a->batches * ceil_div(a->M, kBM) * ceil_div(a->N, bn), ceil_div(a->K, kBK));
+  const TilePlan plan = pick_plan(o, true);
+  if (split == 0) split = pick_split(plan_units(o, plan), ceil_div(a->K, kBK), plan.pair ? sm_count() / 2 : sm_count());
   EpiStore::Params ep;
   ep.C = a->C;
   ep.ldc = a->ldc;
   ep.batch_stride = a->M * a->ldc;
   ep.mode = a->out_mode;
   ep.alpha = a->alpha;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (bn == 256) return launch_major<256, 4, EpiStore>(o, split, ep, status, st);
-  if (bn == 192) return launch_major<192, 5, EpiStore>(o, split, ep, status, st);
-  return launch_major<128, 6, EpiStore>(o, split, ep, status, st);
+  return run_plan_any_major<EpiStore>(plan, o, split, ep, status, static_cast<cudaStream_t>(stream));
+}
+
+int pom_set_gemm_mode(int mode) {
+  if (mode < 0 || mode > 2) return POM_ERR_UNSUPPORTED;
+  g_gemm_mode.store(mode);
+  return POM_OK;
 }
 
 int pom_gemm_f32(const pom_gemm_args* a, void* stream) {
@@ -330,9 +396,7 @@ int pom_ctx_gemm(const pom_ctx_args* a, int* status, void* stream) {
   ep.ld_hp = a->ld_hp;
   ep.partial = a->partial;
   ep.P = a->P;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (pick_bn(a->P, false) == 256) return launch<256, 4, false, false, EpiCtx>(o, 1, ep, status, st);
-  return launch<128, 6, false, false, EpiCtx>(o, 1, ep, status, st);
+  return run_plan<false, false, EpiCtx>(pick_plan(o, false), o, 1, ep, status, static_cast<cudaStream_t>(stream));
 }
 
 int pom_gate_gemm(const pom_gate_args* a, int* status, void* stream) {
@@ -352,9 +416,7 @@ int pom_gate_gemm(const pom_gate_args* a, int* status, void* stream) {
   ep.ld_z = a->ld_z;
   ep.sh_out = static_cast<__nv_bfloat16*>(a->sh_out);
   ep.ld_sh = a->ld_sh;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (pick_bn(a->P, false) == 256) return launch<256, 4, false, false, EpiGate>(o, 1, ep, status, st);
-  return launch<128, 6, false, false, EpiGate>(o, 1, ep, status, st);
+  return run_plan<false, false, EpiGate>(pick_plan(o, false), o, 1, ep, status, static_cast<cudaStream_t>(stream));
 }
 
 int pom_gate_bwd_gemm(const pom_gate_bwd_args* a, int* status, void* stream) {
@@ -375,9 +437,7 @@ int pom_gate_bwd_gemm(const pom_gate_bwd_args* a, int* status, void* stream) {
   ep.dh_partial = a->dh_partial;
   ep.db_partial = a->db_partial;
   ep.P = a->P;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (pick_bn(a->P, false) == 256) return launch<256, 4, false, true, EpiGateBwd>(o, 1, ep, status, st);
-  return launch<128, 6, false, true, EpiGateBwd>(o, 1, ep, status, st);
+  return run_plan<false, true, EpiGateBwd>(pick_plan(o, false), o, 1, ep, status, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

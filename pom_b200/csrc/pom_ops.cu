@@ -4,57 +4,92 @@
 // reductions that finish the per-tile partial sums of the fused GEMM epilogues.
 //
 // Common traversal: grid = (column blocks, token chunks, batch); one thread owns
-// VEC adjacent channels (plus their rotary partners) and walks the tokens of its
-// chunk, so global accesses are coalesced across the block and every sum is
-// formed in a fixed order (deterministic, no float atomics).
+// VEC adjacent channels (16 bytes when alignment allows, plus their rotary
+// partners) and walks the tokens of its chunk four at a time, so every global
+// access is a coalesced 16-byte vector, several are in flight per thread, and every
+// sum is formed in a fixed order (deterministic, no float atomics).
 #include "common.cuh"
 #include "pom_math.cuh"
 #include <cuda_bf16.h>
+#include <initializer_list>
+#include <type_traits>
 
 using namespace pomk;
 using namespace pomh;
 
 namespace {
 
-constexpr int kChunk = 64;     // tokens per chunk
-constexpr int kThreads = 128;  // threads per block
+constexpr int kChunk = 64;  // tokens per chunk
+constexpr int kTB = 4;      // tokens loaded per batch of independent loads
 
 // ------------------------------------------------------------------ element access
 template <typename T, int VEC>
-struct Vec;
-template <>
-struct Vec<float, 1> {
-  static __device__ __forceinline__ void ld(const float* p, float (&v)[1]) { v[0] = __ldg(p); }
-  static __device__ __forceinline__ void st(float* p, const float (&v)[1]) { p[0] = v[0]; }
-};
-template <>
-struct Vec<float, 2> {
-  static __device__ __forceinline__ void ld(const float* p, float (&v)[2]) {
-    float2 f = __ldg(reinterpret_cast<const float2*>(p));
-    v[0] = f.x;
-    v[1] = f.y;
+struct Vec {
+  static __device__ __forceinline__ void ld(const T* __restrict__ p, float (&v)[VEC]) {
+    if constexpr (std::is_same<T, float>::value) {
+      if constexpr (VEC % 4 == 0) {
+#pragma unroll
+        for (int j = 0; j < VEC / 4; ++j) {
+          const float4 f = __ldg(reinterpret_cast<const float4*>(p) + j);
+          v[4 * j] = f.x, v[4 * j + 1] = f.y, v[4 * j + 2] = f.z, v[4 * j + 3] = f.w;
+        }
+      } else if constexpr (VEC == 2) {
+        const float2 f = __ldg(reinterpret_cast<const float2*>(p));
+        v[0] = f.x, v[1] = f.y;
+      } else {
+        v[0] = __ldg(p);
+      }
+    } else {
+      if constexpr (VEC == 8) {
+        const uint4 q = __ldg(reinterpret_cast<const uint4*>(p));
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          v[2 * e] = __uint_as_float(w[e] << 16);
+          v[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
+        }
+      } else if constexpr (VEC == 2) {
+        const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(p));
+        v[0] = __uint_as_float(w << 16);
+        v[1] = __uint_as_float(w & 0xffff0000u);
+      } else {
+        v[0] = __bfloat162float(*p);
+      }
+    }
   }
-  static __device__ __forceinline__ void st(float* p, const float (&v)[2]) {
-    *reinterpret_cast<float2*>(p) = make_float2(v[0], v[1]);
+  static __device__ __forceinline__ void st(T* __restrict__ p, const float (&v)[VEC]) {
+    if constexpr (std::is_same<T, float>::value) {
+      if constexpr (VEC % 4 == 0) {
+#pragma unroll
+        for (int j = 0; j < VEC / 4; ++j)
+          reinterpret_cast<float4*>(p)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+      } else if constexpr (VEC == 2) {
+        *reinterpret_cast<float2*>(p) = make_float2(v[0], v[1]);
+      } else {
+        p[0] = v[0];
+      }
+    } else {
+      if constexpr (VEC == 8) {
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+          w[e] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+      } else if constexpr (VEC == 2) {
+        *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v[0], v[1]);
+      } else {
+        p[0] = __float2bfloat16_rn(v[0]);
+      }
+    }
   }
 };
-template <>
-struct Vec<__nv_bfloat16, 1> {
-  static __device__ __forceinline__ void ld(const __nv_bfloat16* p, float (&v)[1]) { v[0] = __bfloat162float(*p); }
-  static __device__ __forceinline__ void st(__nv_bfloat16* p, const float (&v)[1]) { p[0] = __float2bfloat16_rn(v[0]); }
-};
-template <>
-struct Vec<__nv_bfloat16, 2> {
-  static __device__ __forceinline__ void ld(const __nv_bfloat16* p, float (&v)[2]) {
-    unsigned int raw = __ldg(reinterpret_cast<const unsigned int*>(p));
-    float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&raw));
-    v[0] = f.x;
-    v[1] = f.y;
-  }
-  static __device__ __forceinline__ void st(__nv_bfloat16* p, const float (&v)[2]) {
-    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v[0], v[1]);
-  }
-};
+
+template <int VEC>
+__device__ __forceinline__ void ld_f32(const float* __restrict__ p, float (&v)[VEC]) {
+  Vec<float, VEC>::ld(p, v);
+}
 
 // ------------------------------------------------------------------ channel map
 // One work item = VEC adjacent "first" channels.  Without rotary embedding every
@@ -97,19 +132,14 @@ __device__ __forceinline__ ColMap map_unit(int u, int P, int rope_kind) {
   return m;
 }
 
-__host__ __device__ inline int first_channels(int P, int rope_kind) { return rope_kind == POM_ROPE_NONE ? P : P / 2; }
+inline int first_channels(int P, int rope_kind) { return rope_kind == POM_ROPE_NONE ? P : P / 2; }
 
 template <int VEC>
 __device__ __forceinline__ void rope_coeffs(const pom_rope& r, const ColMap& m, long long n, float (&c)[VEC],
                                             float (&s)[VEC]) {
   const long long idx = r.pos[n * r.pos_stride + m.which];
-  const float* ct = (m.which ? r.cos1 : r.cos0) + idx * m.tab_ld + m.j;
-  const float* stb = (m.which ? r.sin1 : r.sin0) + idx * m.tab_ld + m.j;
-#pragma unroll
-  for (int e = 0; e < VEC; ++e) {
-    c[e] = __ldg(ct + e);
-    s[e] = __ldg(stb + e);
-  }
+  ld_f32<VEC>((m.which ? r.cos1 : r.cos0) + idx * m.tab_ld + m.j, c);
+  ld_f32<VEC>((m.which ? r.sin1 : r.sin0) + idx * m.tab_ld + m.j, s);
 }
 
 template <int VEC, int KR>
@@ -127,31 +157,20 @@ struct Coefs {
   }
 };
 
+// Coefficients beyond K are zero, so the unrolled evaluation needs no predicate.
 template <int KR>
-__device__ __forceinline__ float poly_reg(float a, const float (&c)[KR], int K) {
-  float p = a;
-  float acc = c[0] * p;
+__device__ __forceinline__ float poly_reg(float a, const float (&c)[KR]) {
+  float r = c[KR - 1];
 #pragma unroll
-  for (int i = 1; i < KR; ++i) {
-    if (i < K) {
-      p *= a;
-      acc = fmaf(c[i], p, acc);
-    }
-  }
-  return acc;
+  for (int i = KR - 2; i >= 0; --i) r = fmaf(r, a, c[i]);
+  return r * a;
 }
 template <int KR>
-__device__ __forceinline__ float poly_grad_reg(float a, const float (&c)[KR], int K) {
-  float p = 1.f;
-  float acc = c[0];
+__device__ __forceinline__ float poly_grad_reg(float a, const float (&c)[KR]) {
+  float r = static_cast<float>(KR) * c[KR - 1];
 #pragma unroll
-  for (int i = 1; i < KR; ++i) {
-    if (i < K) {
-      p *= a;
-      acc = fmaf(static_cast<float>(i + 1) * c[i], p, acc);
-    }
-  }
-  return acc;
+  for (int i = KR - 2; i >= 0; --i) r = fmaf(r, a, static_cast<float>(i + 1) * c[i]);
+  return r;
 }
 
 struct AggDev {
@@ -168,17 +187,17 @@ struct AggDev {
 // ------------------------------------------------------------------ forward: chunk sums / prefix apply
 // PREFIX == false: partial[b, c, :] = sum over the chunk of w * R·poly.
 // PREFIX == true : partial holds the exclusive prefix per chunk; writes out[b, n, :].
-template <typename T, int VEC, int KR, bool PREFIX>
-__global__ void __launch_bounds__(kThreads) agg_fwd_kernel(const AggDev a) {
-  const int u = (blockIdx.x * kThreads + threadIdx.x) * VEC;
+template <typename T, int VEC, int KR, bool PREFIX, bool ROPE>
+__global__ void __launch_bounds__(128) agg_fwd_kernel(const AggDev a) {
+  const int u = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
   const int c = blockIdx.y, b = blockIdx.z;
-  const bool rope = a.rope.kind != POM_ROPE_NONE;
+  constexpr bool rope = ROPE;
   const ColMap m = map_unit(u, a.P, a.rope.kind);
   if (!m.valid) return;
   Coefs<VEC, KR> cf;
   cf.load(a.coeff, m, a.K, rope);
-  const T* x = static_cast<const T*>(a.x) + static_cast<long long>(b) * a.N * a.ldx;
-  T* out = PREFIX ? static_cast<T*>(a.out) + static_cast<long long>(b) * a.N * a.ld_out : nullptr;
+  const T* __restrict__ x = static_cast<const T*>(a.x) + static_cast<long long>(b) * a.N * a.ldx;
+  T* __restrict__ out = PREFIX ? static_cast<T*>(a.out) + static_cast<long long>(b) * a.N * a.ld_out : nullptr;
   float* part = a.partial + (static_cast<long long>(b) * a.chunks + c) * a.P;
   float acc1[VEC], acc2[VEC];
 #pragma unroll
@@ -187,38 +206,44 @@ __global__ void __launch_bounds__(kThreads) agg_fwd_kernel(const AggDev a) {
     acc2[e] = (PREFIX && rope) ? part[m.p2 + e] : 0.f;
   }
   const int n0 = c * kChunk, n1 = min(a.N, n0 + kChunk);
-#pragma unroll 4
-  for (int n = n0; n < n1; ++n) {
-    float x1[VEC], x2[VEC], f1[VEC], f2[VEC];
-    Vec<T, VEC>::ld(x + n * a.ldx + m.p1, x1);
-    if (rope) Vec<T, VEC>::ld(x + n * a.ldx + m.p2, x2);
-    float w = 1.f;
-    if (!PREFIX && a.row_weight) w = __ldg(a.row_weight + static_cast<long long>(b) * a.N + n);
+  for (int nb = n0; nb < n1; nb += kTB) {
+    float x1[kTB][VEC], x2[kTB][VEC], cs[kTB][VEC], sn[kTB][VEC], w[kTB];
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) f1[e] = poly_reg<KR>(pom_act(x1[e]), cf.c1[e], a.K);
-    if (rope) {
-      float cs[VEC], sn[VEC];
-      rope_coeffs<VEC>(a.rope, m, n, cs, sn);
+    for (int q = 0; q < kTB; ++q) {
+      const int n = min(nb + q, n1 - 1);
+      Vec<T, VEC>::ld(x + n * a.ldx + m.p1, x1[q]);
+      if (rope) {
+        Vec<T, VEC>::ld(x + n * a.ldx + m.p2, x2[q]);
+        rope_coeffs<VEC>(a.rope, m, n, cs[q], sn[q]);
+      }
+      w[q] = (!PREFIX && a.row_weight) ? __ldg(a.row_weight + static_cast<long long>(b) * a.N + n) : 1.f;
+    }
+#pragma unroll
+    for (int q = 0; q < kTB; ++q) {
+      const int n = nb + q;
+      if (n >= n1) break;
 #pragma unroll
       for (int e = 0; e < VEC; ++e) {
-        f2[e] = poly_reg<KR>(pom_act(x2[e]), cf.c2[e], a.K);
-        acc1[e] += w * (f1[e] * cs[e] - f2[e] * sn[e]);
-        acc2[e] += w * (f2[e] * cs[e] + f1[e] * sn[e]);
+        const float f1 = poly_reg<KR>(pom_act(x1[q][e]), cf.c1[e]);
+        if (rope) {
+          const float f2 = poly_reg<KR>(pom_act(x2[q][e]), cf.c2[e]);
+          acc1[e] += w[q] * (f1 * cs[q][e] - f2 * sn[q][e]);
+          acc2[e] += w[q] * (f2 * cs[q][e] + f1 * sn[q][e]);
+        } else {
+          acc1[e] += w[q] * f1;
+        }
       }
-    } else {
+      if (PREFIX) {
+        const float inv = 1.f / static_cast<float>(a.token_offset + n + 1);
+        float o[VEC];
 #pragma unroll
-      for (int e = 0; e < VEC; ++e) acc1[e] += w * f1[e];
-    }
-    if (PREFIX) {
-      const float inv = 1.f / static_cast<float>(a.token_offset + n + 1);
-      float o[VEC];
+        for (int e = 0; e < VEC; ++e) o[e] = acc1[e] * inv;
+        Vec<T, VEC>::st(out + n * a.ld_out + m.p1, o);
+        if (rope) {
 #pragma unroll
-      for (int e = 0; e < VEC; ++e) o[e] = acc1[e] * inv;
-      Vec<T, VEC>::st(out + n * a.ld_out + m.p1, o);
-      if (rope) {
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) o[e] = acc2[e] * inv;
-        Vec<T, VEC>::st(out + n * a.ld_out + m.p2, o);
+          for (int e = 0; e < VEC; ++e) o[e] = acc2[e] * inv;
+          Vec<T, VEC>::st(out + n * a.ld_out + m.p2, o);
+        }
       }
     }
   }
@@ -237,41 +262,64 @@ __global__ void chunk_scan_kernel(float* partial, const float* carry, float* tot
   const int b = blockIdx.y;
   if (p >= P) return;
   float* base = partial + static_cast<long long>(b) * chunks * P + p;
-  const float seed = carry ? carry[static_cast<long long>(b) * P + p] : 0.f;
-  float run = seed;
+  float run = carry ? carry[static_cast<long long>(b) * P + p] : 0.f;
   float own = 0.f;
-  for (int i = 0; i < chunks; ++i) {
-    const int c = reverse ? chunks - 1 - i : i;
-    const float t = base[static_cast<long long>(c) * P];
-    base[static_cast<long long>(c) * P] = run;
-    run += t;
-    own += t;
+  for (int i0 = 0; i0 < chunks; i0 += 8) {
+    float t[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const int i = i0 + q;
+      const int c = reverse ? chunks - 1 - i : i;
+      t[q] = i < chunks ? base[static_cast<long long>(c) * P] : 0.f;
+    }
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const int i = i0 + q;
+      if (i < chunks) {
+        const int c = reverse ? chunks - 1 - i : i;
+        base[static_cast<long long>(c) * P] = run;
+        run += t[q];
+        own += t[q];
+      }
+    }
   }
   if (total) total[static_cast<long long>(b) * P + p] = own;
 }
 
-__global__ void reduce_partials_kernel(const float* __restrict__ partial, float* __restrict__ out,
-                                       const float* __restrict__ denom, float scale, int chunks, int P) {
-  const int p = blockIdx.x * blockDim.x + threadIdx.x;
+// out[b, p] = scale * sum_c partial[b, c, p] / denom[b].  Block = 32 columns x 8 chunk lanes; each
+// lane adds every 8th chunk, then the 8 lane sums are combined in lane order.
+__global__ void __launch_bounds__(256) reduce_partials_kernel(const float* __restrict__ partial, float* __restrict__ out,
+                                                               const float* __restrict__ denom, float scale, int chunks,
+                                                               int P) {
+  __shared__ float sm[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int p = blockIdx.x * 32 + tx;
   const int b = blockIdx.y;
-  if (p >= P) return;
-  const float* base = partial + static_cast<long long>(b) * chunks * P + p;
-  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-  int c = 0;
-  for (; c + 4 <= chunks; c += 4) {
-    s0 += base[static_cast<long long>(c) * P];
-    s1 += base[static_cast<long long>(c + 1) * P];
-    s2 += base[static_cast<long long>(c + 2) * P];
-    s3 += base[static_cast<long long>(c + 3) * P];
+  float s = 0.f;
+  if (p < P) {
+    const float* base = partial + static_cast<long long>(b) * chunks * P + p;
+    float s0 = 0.f, s1 = 0.f;
+    int c = ty;
+    for (; c + 8 < chunks; c += 16) {
+      s0 += base[static_cast<long long>(c) * P];
+      s1 += base[static_cast<long long>(c + 8) * P];
+    }
+    if (c < chunks) s0 += base[static_cast<long long>(c) * P];
+    s = s0 + s1;
   }
-  for (; c < chunks; ++c) s0 += base[static_cast<long long>(c) * P];
-  float s = (s0 + s1) + (s2 + s3);
-  s *= scale;
-  if (denom) {
-    const float d = denom[b];
-    s = d != 0.f ? s / d : 0.f;  // a sample with no valid token aggregates to zero
+  sm[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && p < P) {
+    float t = 0.f;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) t += sm[q][tx];
+    t *= scale;
+    if (denom) {
+      const float d = denom[b];
+      t = d != 0.f ? t / d : 0.f;  // a sample with no valid token aggregates to zero
+    }
+    out[static_cast<long long>(b) * P + p] = t;
   }
-  out[static_cast<long long>(b) * P + p] = s;
 }
 
 // ------------------------------------------------------------------ backward
@@ -293,22 +341,26 @@ struct AggBwdDev {
 
 // Causal backward, pass 1: partial[b, c, :] = sum over the chunk of dout[b, n, :] / (n + 1 + offset).
 template <typename T, int VEC>
-__global__ void __launch_bounds__(kThreads) causal_bwd_sum_kernel(const AggBwdDev a) {
-  const int p = (blockIdx.x * kThreads + threadIdx.x) * VEC;
+__global__ void __launch_bounds__(128) causal_bwd_sum_kernel(const AggBwdDev a) {
+  const int p = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
   const int c = blockIdx.y, b = blockIdx.z;
   if (p >= a.P) return;
-  const T* g = static_cast<const T*>(a.dout) + static_cast<long long>(b) * a.N * a.ld_dout + p;
+  const T* __restrict__ g = static_cast<const T*>(a.dout) + static_cast<long long>(b) * a.N * a.ld_dout + p;
   float acc[VEC];
 #pragma unroll
   for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
   const int n0 = c * kChunk, n1 = min(a.N, n0 + kChunk);
-#pragma unroll 4
-  for (int n = n0; n < n1; ++n) {
-    float v[VEC];
-    Vec<T, VEC>::ld(g + n * a.ld_dout, v);
-    const float inv = 1.f / static_cast<float>(a.token_offset + n + 1);
+  for (int nb = n0; nb < n1; nb += kTB) {
+    float v[kTB][VEC];
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) acc[e] = fmaf(v[e], inv, acc[e]);
+    for (int q = 0; q < kTB; ++q) Vec<T, VEC>::ld(g + static_cast<long long>(min(nb + q, n1 - 1)) * a.ld_dout, v[q]);
+#pragma unroll
+    for (int q = 0; q < kTB; ++q) {
+      if (nb + q >= n1) break;
+      const float inv = 1.f / static_cast<float>(a.token_offset + nb + q + 1);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc[e] = fmaf(v[q][e], inv, acc[e]);
+    }
   }
   float* part = a.partial + (static_cast<long long>(b) * a.chunks + c) * a.P + p;
 #pragma unroll
@@ -318,18 +370,19 @@ __global__ void __launch_bounds__(kThreads) causal_bwd_sum_kernel(const AggBwdDe
 // CAUSAL == false: the gradient reaching every token is w[b,n] * dH[b, :].
 // CAUSAL == true : walk the chunk backwards; W[n] = suffix + sum_{m >= n} dout[m]/(m+1+offset).
 // Either way: un-rotate, then dx = g * poly'(a) * act'(x) and the coefficient gradient sums.
-template <typename T, int VEC, int KR, bool CAUSAL>
-__global__ void __launch_bounds__(kThreads) agg_bwd_kernel(const AggBwdDev a) {
-  const int u = (blockIdx.x * kThreads + threadIdx.x) * VEC;
+template <typename T, int VEC, int KR, bool CAUSAL, bool ROPE>
+__global__ void __launch_bounds__(128) agg_bwd_kernel(const AggBwdDev a) {
+  const int u = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
   const int c = blockIdx.y, b = blockIdx.z;
-  const bool rope = a.rope.kind != POM_ROPE_NONE;
+  constexpr bool rope = ROPE;
   const ColMap m = map_unit(u, a.P, a.rope.kind);
   if (!m.valid) return;
   Coefs<VEC, KR> cf;
   cf.load(a.coeff, m, a.K, rope);
-  const T* x = static_cast<const T*>(a.x) + static_cast<long long>(b) * a.N * a.ldx;
-  T* dx = static_cast<T*>(a.dx) + static_cast<long long>(b) * a.N * a.ld_dx;
-  const T* dout = CAUSAL ? static_cast<const T*>(a.dout) + static_cast<long long>(b) * a.N * a.ld_dout : nullptr;
+  const T* __restrict__ x = static_cast<const T*>(a.x) + static_cast<long long>(b) * a.N * a.ldx;
+  T* __restrict__ dx = static_cast<T*>(a.dx) + static_cast<long long>(b) * a.N * a.ld_dx;
+  const T* __restrict__ dout =
+      CAUSAL ? static_cast<const T*>(a.dout) + static_cast<long long>(b) * a.N * a.ld_dout : nullptr;
   float g1[VEC], g2[VEC];
   float dc1[VEC][KR], dc2[VEC][KR];
 #pragma unroll
@@ -354,70 +407,70 @@ __global__ void __launch_bounds__(kThreads) agg_bwd_kernel(const AggBwdDev a) {
     wb = dn != 0.f ? wb / dn : 0.f;
   }
   const int n0 = c * kChunk, n1 = min(a.N, n0 + kChunk);
-#pragma unroll 2
-  for (int i = 0; i < n1 - n0; ++i) {
-    const int n = CAUSAL ? (n1 - 1 - i) : (n0 + i);
-    float x1[VEC], x2[VEC];
-    Vec<T, VEC>::ld(x + n * a.ldx + m.p1, x1);
-    if (rope) Vec<T, VEC>::ld(x + n * a.ldx + m.p2, x2);
-    float w = wb;
-    if (CAUSAL) {
-      const float inv = 1.f / static_cast<float>(a.token_offset + n + 1);
-      float v[VEC];
-      Vec<T, VEC>::ld(dout + n * a.ld_dout + m.p1, v);
+  const int cnt = n1 - n0;
+  for (int ib = 0; ib < cnt; ib += kTB) {
+    float x1[kTB][VEC], x2[kTB][VEC], cs[kTB][VEC], sn[kTB][VEC], go1[kTB][VEC], go2[kTB][VEC], w[kTB];
 #pragma unroll
-      for (int e = 0; e < VEC; ++e) g1[e] = fmaf(v[e], inv, g1[e]);
+    for (int q = 0; q < kTB; ++q) {
+      const int i = min(ib + q, cnt - 1);
+      const int n = CAUSAL ? (n1 - 1 - i) : (n0 + i);
+      Vec<T, VEC>::ld(x + n * a.ldx + m.p1, x1[q]);
       if (rope) {
-        Vec<T, VEC>::ld(dout + n * a.ld_dout + m.p2, v);
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) g2[e] = fmaf(v[e], inv, g2[e]);
+        Vec<T, VEC>::ld(x + n * a.ldx + m.p2, x2[q]);
+        rope_coeffs<VEC>(a.rope, m, n, cs[q], sn[q]);
       }
-    } else if (a.row_weight) {
-      w *= __ldg(a.row_weight + static_cast<long long>(b) * a.N + n);
-    }
-    float d1[VEC], d2[VEC];
-    if (rope) {
-      float cs[VEC], sn[VEC];
-      rope_coeffs<VEC>(a.rope, m, n, cs, sn);
-#pragma unroll
-      for (int e = 0; e < VEC; ++e) {
-        d1[e] = w * (g1[e] * cs[e] + g2[e] * sn[e]);
-        d2[e] = w * (g2[e] * cs[e] - g1[e] * sn[e]);
+      if (CAUSAL) {
+        Vec<T, VEC>::ld(dout + n * a.ld_dout + m.p1, go1[q]);
+        if (rope) Vec<T, VEC>::ld(dout + n * a.ld_dout + m.p2, go2[q]);
+        w[q] = 1.f;
+      } else {
+        w[q] = a.row_weight ? wb * __ldg(a.row_weight + static_cast<long long>(b) * a.N + n) : wb;
       }
-    } else {
-#pragma unroll
-      for (int e = 0; e < VEC; ++e) d1[e] = w * g1[e];
     }
-    float o[VEC];
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) {
-      const float av = pom_act(x1[e]);
-      o[e] = d1[e] * poly_grad_reg<KR>(av, cf.c1[e], a.K) * pom_act_grad(x1[e]);
-      float pw = av;
+    for (int q = 0; q < kTB; ++q) {
+      const int i = ib + q;
+      if (i >= cnt) break;
+      const int n = CAUSAL ? (n1 - 1 - i) : (n0 + i);
+      if (CAUSAL) {
+        const float inv = 1.f / static_cast<float>(a.token_offset + n + 1);
 #pragma unroll
-      for (int k = 0; k < KR; ++k) {
-        if (k < a.K) {
-          dc1[e][k] = fmaf(d1[e], pw, dc1[e][k]);
-          pw *= av;
+        for (int e = 0; e < VEC; ++e) {
+          g1[e] = fmaf(go1[q][e], inv, g1[e]);
+          if (rope) g2[e] = fmaf(go2[q][e], inv, g2[e]);
         }
       }
-    }
-    Vec<T, VEC>::st(dx + n * a.ld_dx + m.p1, o);
-    if (rope) {
+      float o1[VEC], o2[VEC];
 #pragma unroll
       for (int e = 0; e < VEC; ++e) {
-        const float av = pom_act(x2[e]);
-        o[e] = d2[e] * poly_grad_reg<KR>(av, cf.c2[e], a.K) * pom_act_grad(x2[e]);
+        float d1, d2 = 0.f;
+        if (rope) {
+          d1 = w[q] * (g1[e] * cs[q][e] + g2[e] * sn[q][e]);
+          d2 = w[q] * (g2[e] * cs[q][e] - g1[e] * sn[q][e]);
+        } else {
+          d1 = w[q] * g1[e];
+        }
+        const float av = pom_act(x1[q][e]);
+        o1[e] = d1 * poly_grad_reg<KR>(av, cf.c1[e]) * pom_act_grad(x1[q][e]);
         float pw = av;
 #pragma unroll
         for (int k = 0; k < KR; ++k) {
-          if (k < a.K) {
-            dc2[e][k] = fmaf(d2[e], pw, dc2[e][k]);
-            pw *= av;
+          dc1[e][k] = fmaf(d1, pw, dc1[e][k]);
+          pw *= av;
+        }
+        if (rope) {
+          const float bv = pom_act(x2[q][e]);
+          o2[e] = d2 * poly_grad_reg<KR>(bv, cf.c2[e]) * pom_act_grad(x2[q][e]);
+          float pv = bv;
+#pragma unroll
+          for (int k = 0; k < KR; ++k) {
+            dc2[e][k] = fmaf(d2, pv, dc2[e][k]);
+            pv *= bv;
           }
         }
       }
-      Vec<T, VEC>::st(dx + n * a.ld_dx + m.p2, o);
+      Vec<T, VEC>::st(dx + n * a.ld_dx + m.p1, o1);
+      if (rope) Vec<T, VEC>::st(dx + n * a.ld_dx + m.p2, o2);
     }
   }
   float* dcp = a.dcoeff_partial + (static_cast<long long>(b) * a.chunks + c) * a.P * a.K;
@@ -447,98 +500,115 @@ struct SelDev {
   pom_rope rope;
 };
 
-template <typename T, int VEC, bool BWD>
-__global__ void __launch_bounds__(kThreads) select_kernel(const SelDev a) {
-  const int u = (blockIdx.x * kThreads + threadIdx.x) * VEC;
+template <typename T, int VEC, bool BWD, bool ROPE>
+__global__ void __launch_bounds__(128) select_kernel(const SelDev a) {
+  const int u = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
   const int c = blockIdx.y, b = blockIdx.z;
-  const bool rope = a.rope.kind != POM_ROPE_NONE;
+  constexpr bool rope = ROPE;
   const ColMap m = map_unit(u, a.P, a.rope.kind);
   if (!m.valid) return;
   const long long rowb = static_cast<long long>(b) * a.T;
-  const T* z = static_cast<const T*>(a.z) + rowb * a.ld_z;
-  float b1[VEC], b2[VEC], h1[VEC], h2[VEC];
+  const T* __restrict__ z = static_cast<const T*>(a.z) + rowb * a.ld_z;
+  float b1[VEC], b2[VEC], hb1[VEC], hb2[VEC];
 #pragma unroll
   for (int e = 0; e < VEC; ++e) {
     b1[e] = a.activated ? 0.f : a.bias[m.p1 + e];
     b2[e] = (rope && !a.activated) ? a.bias[m.p2 + e] : 0.f;
-    h1[e] = h2[e] = 0.f;
+    hb1[e] = hb2[e] = 0.f;
     if (!a.h_per_token) {
       const float* H = static_cast<const float*>(a.H) + static_cast<long long>(b) * a.P;
-      h1[e] = H[m.p1 + e];
-      if (rope) h2[e] = H[m.p2 + e];
+      hb1[e] = H[m.p1 + e];
+      if (rope) hb2[e] = H[m.p2 + e];
     }
   }
   float accH1[VEC], accH2[VEC], accB1[VEC], accB2[VEC];
 #pragma unroll
   for (int e = 0; e < VEC; ++e) accH1[e] = accH2[e] = accB1[e] = accB2[e] = 0.f;
   const int t0 = c * kChunk, t1 = min(a.T, t0 + kChunk);
-#pragma unroll 2
-  for (int t = t0; t < t1; ++t) {
-    float z1[VEC], z2[VEC], s1[VEC], s2[VEC], cs[VEC], sn[VEC];
-    Vec<T, VEC>::ld(z + t * a.ld_z + m.p1, z1);
-    if (rope) {
-      Vec<T, VEC>::ld(z + t * a.ld_z + m.p2, z2);
-      rope_coeffs<VEC>(a.rope, m, t, cs, sn);
-    }
-    if (a.h_per_token) {
-      const T* H = static_cast<const T*>(a.H) + (rowb + t) * a.ld_h;
-      Vec<T, VEC>::ld(H + m.p1, h1);
-      if (rope) Vec<T, VEC>::ld(H + m.p2, h2);
-    }
+  constexpr int TB = 2;
+  for (int tb = t0; tb < t1; tb += TB) {
+    float z1[TB][VEC], z2[TB][VEC], cs[TB][VEC], sn[TB][VEC], h1[TB][VEC], h2[TB][VEC], g1[TB][VEC], g2[TB][VEC];
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) {
-      z1[e] += b1[e];
-      const float r1 = a.activated ? z1[e] : pom_hardsigmoid(z1[e]);
+    for (int q = 0; q < TB; ++q) {
+      const int t = min(tb + q, t1 - 1);
+      Vec<T, VEC>::ld(z + t * a.ld_z + m.p1, z1[q]);
       if (rope) {
-        z2[e] += b2[e];
-        const float r2 = a.activated ? z2[e] : pom_hardsigmoid(z2[e]);
-        s1[e] = r1 * cs[e] - r2 * sn[e];
-        s2[e] = r2 * cs[e] + r1 * sn[e];
+        Vec<T, VEC>::ld(z + t * a.ld_z + m.p2, z2[q]);
+        rope_coeffs<VEC>(a.rope, m, t, cs[q], sn[q]);
+      }
+      if (a.h_per_token) {
+        const T* __restrict__ H = static_cast<const T*>(a.H) + (rowb + t) * a.ld_h;
+        Vec<T, VEC>::ld(H + m.p1, h1[q]);
+        if (rope) Vec<T, VEC>::ld(H + m.p2, h2[q]);
       } else {
-        s1[e] = r1;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) h1[q][e] = hb1[e], h2[q][e] = hb2[e];
+      }
+      if (BWD) {
+        const T* __restrict__ dsh = static_cast<const T*>(a.dsh) + (rowb + t) * a.ld_dsh;
+        Vec<T, VEC>::ld(dsh + m.p1, g1[q]);
+        if (rope) Vec<T, VEC>::ld(dsh + m.p2, g2[q]);
       }
     }
-    if (!BWD) {
-      float o[VEC];
-      T* sh = static_cast<T*>(a.sh) + (rowb + t) * a.ld_sh;
 #pragma unroll
-      for (int e = 0; e < VEC; ++e) o[e] = s1[e] * h1[e];
-      Vec<T, VEC>::st(sh + m.p1, o);
-      if (rope) {
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) o[e] = s2[e] * h2[e];
-        Vec<T, VEC>::st(sh + m.p2, o);
-      }
-    } else {
-      const T* dsh = static_cast<const T*>(a.dsh) + (rowb + t) * a.ld_dsh;
-      T* dz = static_cast<T*>(a.dz) + (rowb + t) * a.ld_dz;
-      float g1[VEC], g2[VEC], dh1[VEC], dh2[VEC], o[VEC];
-      Vec<T, VEC>::ld(dsh + m.p1, g1);
-      if (rope) Vec<T, VEC>::ld(dsh + m.p2, g2);
+    for (int q = 0; q < TB; ++q) {
+      const int t = tb + q;
+      if (t >= t1) break;
+      float s1[VEC], s2[VEC];
 #pragma unroll
       for (int e = 0; e < VEC; ++e) {
-        dh1[e] = g1[e] * s1[e];
-        accH1[e] += dh1[e];
-        const float t1v = g1[e] * h1[e];  // gradient of the rotated gate
-        float ds1 = t1v;
+        z1[q][e] += b1[e];
+        const float r1 = a.activated ? z1[q][e] : pom_hardsigmoid(z1[q][e]);
         if (rope) {
-          dh2[e] = g2[e] * s2[e];
-          accH2[e] += dh2[e];
-          const float t2v = g2[e] * h2[e];
-          ds1 = t1v * cs[e] + t2v * sn[e];
-          const float ds2 = t2v * cs[e] - t1v * sn[e];
-          g2[e] = a.activated ? ds2 : ds2 * pom_hardsigmoid_grad(z2[e]);
-          accB2[e] += g2[e];
+          z2[q][e] += b2[e];
+          const float r2 = a.activated ? z2[q][e] : pom_hardsigmoid(z2[q][e]);
+          s1[e] = r1 * cs[q][e] - r2 * sn[q][e];
+          s2[e] = r2 * cs[q][e] + r1 * sn[q][e];
+        } else {
+          s1[e] = r1;
+          s2[e] = 0.f;
         }
-        o[e] = a.activated ? ds1 : ds1 * pom_hardsigmoid_grad(z1[e]);
-        accB1[e] += o[e];
       }
-      Vec<T, VEC>::st(dz + m.p1, o);
-      if (rope) Vec<T, VEC>::st(dz + m.p2, g2);
-      if (a.h_per_token) {
-        T* dh = static_cast<T*>(a.dh_tok) + (rowb + t) * a.ld_dh;
-        Vec<T, VEC>::st(dh + m.p1, dh1);
-        if (rope) Vec<T, VEC>::st(dh + m.p2, dh2);
+      if (!BWD) {
+        float o[VEC];
+        T* __restrict__ sh = static_cast<T*>(a.sh) + (rowb + t) * a.ld_sh;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) o[e] = s1[e] * h1[q][e];
+        Vec<T, VEC>::st(sh + m.p1, o);
+        if (rope) {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) o[e] = s2[e] * h2[q][e];
+          Vec<T, VEC>::st(sh + m.p2, o);
+        }
+      } else {
+        T* __restrict__ dz = static_cast<T*>(a.dz) + (rowb + t) * a.ld_dz;
+        float dh1[VEC], dh2[VEC], o1[VEC], o2[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          dh1[e] = g1[q][e] * s1[e];
+          accH1[e] += dh1[e];
+          const float t1v = g1[q][e] * h1[q][e];  // gradient of the rotated gate
+          float ds1 = t1v;
+          dh2[e] = o2[e] = 0.f;
+          if (rope) {
+            dh2[e] = g2[q][e] * s2[e];
+            accH2[e] += dh2[e];
+            const float t2v = g2[q][e] * h2[q][e];
+            ds1 = t1v * cs[q][e] + t2v * sn[q][e];
+            const float ds2 = t2v * cs[q][e] - t1v * sn[q][e];
+            o2[e] = a.activated ? ds2 : ds2 * pom_hardsigmoid_grad(z2[q][e]);
+            accB2[e] += o2[e];
+          }
+          o1[e] = a.activated ? ds1 : ds1 * pom_hardsigmoid_grad(z1[q][e]);
+          accB1[e] += o1[e];
+        }
+        Vec<T, VEC>::st(dz + m.p1, o1);
+        if (rope) Vec<T, VEC>::st(dz + m.p2, o2);
+        if (a.h_per_token) {
+          T* __restrict__ dh = static_cast<T*>(a.dh_tok) + (rowb + t) * a.ld_dh;
+          Vec<T, VEC>::st(dh + m.p1, dh1);
+          if (rope) Vec<T, VEC>::st(dh + m.p2, dh2);
+        }
       }
     }
   }
@@ -561,11 +631,17 @@ __global__ void state_merge_kernel(const float* hp, const float* hc, float* hn, 
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i < count) hn[i] = (n_past * hp[i] + hc[i]) / (n_past + 1.f);
 }
-__global__ void cast_f32_bf16_kernel(const float* s, __nv_bfloat16* d, long long count) {
-  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i < count) d[i] = __float2bfloat16_rn(s[i]);
+__global__ void cast_f32_bf16_kernel(const float* __restrict__ s, __nv_bfloat16* __restrict__ d, long long count) {
+  const long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+  if (i + 4 <= count && ((reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(d)) & 15) == 0) {
+    const float4 f = __ldg(reinterpret_cast<const float4*>(s + i));
+    __nv_bfloat162 lo = __floats2bfloat162_rn(f.x, f.y), hi = __floats2bfloat162_rn(f.z, f.w);
+    *reinterpret_cast<uint2*>(d + i) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+  } else {
+    for (long long j = i; j < count && j < i + 4; ++j) d[j] = __float2bfloat16_rn(s[j]);
+  }
 }
-__global__ void cast_bf16_f32_kernel(const __nv_bfloat16* s, float* d, long long count) {
+__global__ void cast_bf16_f32_kernel(const __nv_bfloat16* __restrict__ s, float* __restrict__ d, long long count) {
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i < count) d[i] = __bfloat162float(s[i]);
 }
@@ -586,32 +662,67 @@ int check_rope(const pom_rope& r, int P) {
   return POM_ERR_UNSUPPORTED;
 }
 
-// Two channels per thread when every access stays naturally aligned.
-int pick_vec(int P, int rope_kind, int dtype, std::initializer_list<long long> lds,
+// Channels per thread: a 16-byte vector (8 bf16 / 4 fp32) when every access stays aligned and the
+// degree fits the register-resident coefficient set, else 2, else 1.
+int pick_vec(int P, const pom_rope& rope, int dtype, int K, std::initializer_list<long long> lds,
              std::initializer_list<const void*> ptrs) {
-  const int unit = rope_kind == POM_ROPE_2D ? P / 4 : rope_kind == POM_ROPE_1D ? P / 2 : P;
-  if (unit % 2) return 1;
-  for (long long ld : lds)
-    if (ld % 2) return 1;
-  const uintptr_t mask = dtype == POM_BF16 ? 3u : 7u;
-  for (const void* p : ptrs)
-    if (p && (reinterpret_cast<uintptr_t>(p) & mask)) return 1;
-  return 2;
+  const int unit = rope.kind == POM_ROPE_2D ? P / 4 : rope.kind == POM_ROPE_1D ? P / 2 : P;
+  const int wide = dtype == POM_BF16 ? 8 : 4;
+  auto ok = [&](int v) {
+    if (unit % v) return false;
+    for (long long ld : lds)
+      if (ld % v) return false;
+    const uintptr_t mask = static_cast<uintptr_t>(v * (dtype == POM_BF16 ? 2 : 4) - 1);
+    for (const void* p : ptrs)
+      if (p && (reinterpret_cast<uintptr_t>(p) & mask)) return false;
+    if (rope.kind != POM_ROPE_NONE) {
+      const uintptr_t tmask = static_cast<uintptr_t>((v >= 4 ? 16 : v * 4) - 1);
+      for (const void* p : {static_cast<const void*>(rope.cos0), static_cast<const void*>(rope.sin0),
+                            static_cast<const void*>(rope.cos1), static_cast<const void*>(rope.sin1)})
+        if (p && (reinterpret_cast<uintptr_t>(p) & tmask)) return false;
+    }
+    return true;
+  };
+  if (K <= 4 && ok(wide)) return wide;
+  if (ok(2)) return 2;
+  return 1;
 }
 
-dim3 walk_grid(int P, int rope_kind, int vec, int chunks, int B) {
+struct WalkLaunch {
+  dim3 grid;
+  int block;
+};
+
+WalkLaunch walk_launch(int P, int rope_kind, int vec, int chunks, int B) {
   const int units = static_cast<int>(ceil_div(first_channels(P, rope_kind), vec));
-  return dim3(static_cast<unsigned>(ceil_div(units, kThreads)), static_cast<unsigned>(chunks),
-              static_cast<unsigned>(B));
+  // block size: a multiple of 32 up to 128 that wastes the fewest lanes
+  int best = 128;
+  long long best_waste = -1;
+  for (int bs = 128; bs >= 32; bs -= 32) {
+    const long long waste = ceil_div(units, bs) * bs - units;
+    if (best_waste < 0 || waste < best_waste) {
+      best_waste = waste;
+      best = bs;
+    }
+  }
+  WalkLaunch w;
+  w.block = best;
+  w.grid = dim3(static_cast<unsigned>(ceil_div(units, best)), static_cast<unsigned>(chunks), static_cast<unsigned>(B));
+  return w;
 }
 
-#define POM_DISPATCH_T_VEC(dtype, vec, CALL)                   \
-  do {                                                         \
-    if ((dtype) == POM_BF16) {                                 \
-      if ((vec) == 2) { CALL(__nv_bfloat16, 2); } else { CALL(__nv_bfloat16, 1); } \
-    } else {                                                   \
-      if ((vec) == 2) { CALL(float, 2); } else { CALL(float, 1); }                 \
-    }                                                          \
+// CALL(T, VEC, KR) for the (dtype, vec) pair picked above.
+#define POM_DISPATCH(dtype, vec, CALL)                  \
+  do {                                                  \
+    if ((dtype) == POM_BF16) {                          \
+      if ((vec) == 8) { CALL(__nv_bfloat16, 8, 4); }    \
+      else if ((vec) == 2) { CALL(__nv_bfloat16, 2, kMaxDegree); } \
+      else { CALL(__nv_bfloat16, 1, kMaxDegree); }      \
+    } else {                                            \
+      if ((vec) == 4) { CALL(float, 4, 4); }            \
+      else if ((vec) == 2) { CALL(float, 2, kMaxDegree); } \
+      else { CALL(float, 1, kMaxDegree); }              \
+    }                                                   \
   } while (0)
 
 }  // namespace
@@ -626,8 +737,8 @@ int pom_reduce_partials(const float* partial, float* out, const float* denom, fl
   if (!partial || !out) return POM_ERR_NULL;
   if (B <= 0 || chunks <= 0 || P <= 0) return POM_ERR_BAD_SHAPE;
   if (B > 65535) return POM_ERR_TOO_LARGE;
-  dim3 grid(static_cast<unsigned>(ceil_div(P, 128)), static_cast<unsigned>(B));
-  reduce_partials_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(partial, out, denom, scale, chunks,
+  dim3 grid(static_cast<unsigned>(ceil_div(P, 32)), static_cast<unsigned>(B));
+  reduce_partials_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(partial, out, denom, scale, chunks,
                                                                              P);
   count_launch();
   return check_launch();
@@ -659,13 +770,14 @@ int pom_poly_agg_fwd(const pom_agg_args* a, void* stream) {
   d.K = a->K;
   d.chunks = pom_agg_chunks(a->N);
   d.rope = a->rope;
-  const int vec = pick_vec(a->P, a->rope.kind, a->dtype, {a->ldx, a->causal ? a->ld_out : 0},
+  const int vec = pick_vec(a->P, a->rope, a->dtype, a->K, {a->ldx, a->causal ? a->ld_out : 0},
                            {a->x, a->causal ? a->out : nullptr});
-  const dim3 grid = walk_grid(a->P, a->rope.kind, vec, d.chunks, a->B);
-#define CALL_SUM(T, V)                                                      \
-  if (a->K <= 4) agg_fwd_kernel<T, V, 4, false><<<grid, kThreads, 0, st>>>(d); \
-  else agg_fwd_kernel<T, V, kMaxDegree, false><<<grid, kThreads, 0, st>>>(d)
-  POM_DISPATCH_T_VEC(a->dtype, vec, CALL_SUM);
+  const WalkLaunch wl = walk_launch(a->P, a->rope.kind, vec, d.chunks, a->B);
+  const bool has_rope = a->rope.kind != POM_ROPE_NONE;
+#define CALL_SUM(T, V, KR)                                                                    \
+  if (has_rope) agg_fwd_kernel<T, V, KR, false, true><<<wl.grid, wl.block, 0, st>>>(d);        \
+  else agg_fwd_kernel<T, V, KR, false, false><<<wl.grid, wl.block, 0, st>>>(d)
+  POM_DISPATCH(a->dtype, vec, CALL_SUM);
 #undef CALL_SUM
   count_launch();
   rc = check_launch();
@@ -673,10 +785,10 @@ int pom_poly_agg_fwd(const pom_agg_args* a, void* stream) {
   dim3 sgrid(static_cast<unsigned>(ceil_div(a->P, 128)), static_cast<unsigned>(a->B));
   chunk_scan_kernel<<<sgrid, 128, 0, st>>>(a->partial, a->carry, a->total, d.chunks, a->P, 0);
   count_launch();
-#define CALL_PFX(T, V)                                                     \
-  if (a->K <= 4) agg_fwd_kernel<T, V, 4, true><<<grid, kThreads, 0, st>>>(d); \
-  else agg_fwd_kernel<T, V, kMaxDegree, true><<<grid, kThreads, 0, st>>>(d)
-  POM_DISPATCH_T_VEC(a->dtype, vec, CALL_PFX);
+#define CALL_PFX(T, V, KR)                                                                   \
+  if (has_rope) agg_fwd_kernel<T, V, KR, true, true><<<wl.grid, wl.block, 0, st>>>(d);        \
+  else agg_fwd_kernel<T, V, KR, true, false><<<wl.grid, wl.block, 0, st>>>(d)
+  POM_DISPATCH(a->dtype, vec, CALL_PFX);
 #undef CALL_PFX
   count_launch();
   return check_launch();
@@ -714,31 +826,33 @@ int pom_poly_agg_bwd(const pom_agg_bwd_args* a, void* stream) {
   d.K = a->K;
   d.chunks = pom_agg_chunks(a->N);
   d.rope = a->rope;
-  const int vec = pick_vec(a->P, a->rope.kind, a->dtype, {a->ldx, a->ld_dx, a->causal ? a->ld_dout : 0},
+  const int vec = pick_vec(a->P, a->rope, a->dtype, a->K, {a->ldx, a->ld_dx, a->causal ? a->ld_dout : 0},
                            {a->x, a->dx, a->causal ? a->dout : nullptr});
-  const dim3 grid = walk_grid(a->P, a->rope.kind, vec, d.chunks, a->B);
+  const WalkLaunch wl = walk_launch(a->P, a->rope.kind, vec, d.chunks, a->B);
+  const bool has_rope = a->rope.kind != POM_ROPE_NONE;
   if (a->causal) {
     // Plain column walk (no channel pairing) for the scaled chunk sums.
-    const int v2 = (a->P % 2 == 0) ? vec : 1;
-    const dim3 g1 = walk_grid(a->P, POM_ROPE_NONE, v2, d.chunks, a->B);
-#define CALL_CS(T, V) causal_bwd_sum_kernel<T, V><<<g1, kThreads, 0, st>>>(d)
-    POM_DISPATCH_T_VEC(a->dtype, v2, CALL_CS);
+    pom_rope none{};
+    const int v2 = pick_vec(a->P, none, a->dtype, 1, {a->ld_dout}, {a->dout});
+    const WalkLaunch w1 = walk_launch(a->P, POM_ROPE_NONE, v2, d.chunks, a->B);
+#define CALL_CS(T, V, KR) causal_bwd_sum_kernel<T, V><<<w1.grid, w1.block, 0, st>>>(d)
+    POM_DISPATCH(a->dtype, v2, CALL_CS);
 #undef CALL_CS
     count_launch();
     dim3 sgrid(static_cast<unsigned>(ceil_div(a->P, 128)), static_cast<unsigned>(a->B));
     chunk_scan_kernel<<<sgrid, 128, 0, st>>>(a->partial, a->carry, a->total, d.chunks, a->P, 1);
     count_launch();
     if (a->phase == 1) return check_launch();  // totals only
-#define CALL_BC(T, V)                                                     \
-  if (a->K <= 4) agg_bwd_kernel<T, V, 4, true><<<grid, kThreads, 0, st>>>(d); \
-  else agg_bwd_kernel<T, V, kMaxDegree, true><<<grid, kThreads, 0, st>>>(d)
-    POM_DISPATCH_T_VEC(a->dtype, vec, CALL_BC);
+#define CALL_BC(T, V, KR)                                                                    \
+  if (has_rope) agg_bwd_kernel<T, V, KR, true, true><<<wl.grid, wl.block, 0, st>>>(d);        \
+  else agg_bwd_kernel<T, V, KR, true, false><<<wl.grid, wl.block, 0, st>>>(d)
+    POM_DISPATCH(a->dtype, vec, CALL_BC);
 #undef CALL_BC
   } else {
-#define CALL_BN(T, V)                                                      \
-  if (a->K <= 4) agg_bwd_kernel<T, V, 4, false><<<grid, kThreads, 0, st>>>(d); \
-  else agg_bwd_kernel<T, V, kMaxDegree, false><<<grid, kThreads, 0, st>>>(d)
-    POM_DISPATCH_T_VEC(a->dtype, vec, CALL_BN);
+#define CALL_BN(T, V, KR)                                                                    \
+  if (has_rope) agg_bwd_kernel<T, V, KR, false, true><<<wl.grid, wl.block, 0, st>>>(d);       \
+  else agg_bwd_kernel<T, V, KR, false, false><<<wl.grid, wl.block, 0, st>>>(d)
+    POM_DISPATCH(a->dtype, vec, CALL_BN);
 #undef CALL_BN
   }
   count_launch();
@@ -753,15 +867,20 @@ static int select_common(SelDev& d, int dtype, bool bwd, std::initializer_list<l
   if (d.B > 65535 || d.chunks > 65535) return POM_ERR_TOO_LARGE;
   int rc = check_rope(d.rope, d.P);
   if (rc) return rc;
-  const int vec = pick_vec(d.P, d.rope.kind, dtype, lds, ptrs);
-  const dim3 grid = walk_grid(d.P, d.rope.kind, vec, d.chunks, d.B);
+  const int vec = pick_vec(d.P, d.rope, dtype, 1, lds, ptrs);
+  const WalkLaunch wl = walk_launch(d.P, d.rope.kind, vec, d.chunks, d.B);
+  const bool has_rope = d.rope.kind != POM_ROPE_NONE;
   if (bwd) {
-#define CALL_SB(T, V) select_kernel<T, V, true><<<grid, kThreads, 0, st>>>(d)
-    POM_DISPATCH_T_VEC(dtype, vec, CALL_SB);
+#define CALL_SB(T, V, KR)                                                          \
+  if (has_rope) select_kernel<T, V, true, true><<<wl.grid, wl.block, 0, st>>>(d);   \
+  else select_kernel<T, V, true, false><<<wl.grid, wl.block, 0, st>>>(d)
+    POM_DISPATCH(dtype, vec, CALL_SB);
 #undef CALL_SB
   } else {
-#define CALL_SF(T, V) select_kernel<T, V, false><<<grid, kThreads, 0, st>>>(d)
-    POM_DISPATCH_T_VEC(dtype, vec, CALL_SF);
+#define CALL_SF(T, V, KR)                                                          \
+  if (has_rope) select_kernel<T, V, false, true><<<wl.grid, wl.block, 0, st>>>(d);  \
+  else select_kernel<T, V, false, false><<<wl.grid, wl.block, 0, st>>>(d)
+    POM_DISPATCH(dtype, vec, CALL_SF);
 #undef CALL_SF
   }
   count_launch();
@@ -833,8 +952,8 @@ int pom_state_merge(const float* h_past, const float* h_cur, float* h_new, float
 int pom_cast_f32_to_bf16(const float* src, void* dst, int64_t count, void* stream) {
   if (!src || !dst) return POM_ERR_NULL;
   if (count <= 0) return POM_ERR_BAD_SHAPE;
-  cast_f32_bf16_kernel<<<static_cast<unsigned>(ceil_div(count, 256)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      src, static_cast<__nv_bfloat16*>(dst), count);
+  cast_f32_bf16_kernel<<<static_cast<unsigned>(ceil_div(ceil_div(count, 4), 256)), 256, 0,
+                         static_cast<cudaStream_t>(stream)>>>(src, static_cast<__nv_bfloat16*>(dst), count);
   count_launch();
   return check_launch();
 }

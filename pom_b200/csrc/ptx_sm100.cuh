@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the Blackwell (sm_100a) primitives used by the
-// PoM GEMM engine: mbarrier, TMA tiled loads (no cluster multicast anywhere),
+// PoM GEMM engine: mbarrier, TMA tiled loads (every CTA fetches its own tiles),
 // tcgen05 tensor-memory allocation / MMA / commit / load.
 //
 // Every wait in this file is bounded: a wait that runs out of time records a
