@@ -1,46 +1,55 @@
 // Epilogues of the tcgen05 GEMM engine.
 //
-// Each of the four epilogue warps owns 32 accumulator rows (one per lane) and walks
-// the tile 32 columns at a time (tcgen05.ld 32x32b.x32).  Per-column constants
-// (polynomial coefficients, gate bias, aggregated state H) are staged in shared
-// memory once per tile by `prologue`, which runs while the tile's main loop is
-// still in flight, and are read back with broadcast 128-bit loads.
+// Each epilogue warp owns 32 accumulator rows (one per lane) and walks its share of
+// the tile 32 columns at a time (tcgen05.ld 32x32b.x32).
+//
+//  * Per-column constants (polynomial coefficients, gate bias, aggregated state H) are
+//    staged in shared memory once per tile by `prologue`, which runs while the tile's
+//    main loop is still in flight, and are read back with broadcast 128-bit loads.
+//  * bf16 outputs leave through shared memory: the warp writes its 32 x 32 block (2 KiB,
+//    64-byte swizzle) and one lane hands it to the TMA engine as a tiled bulk store.  The
+//    store is clipped by the tensor map, so rows past the end of a batch and columns past
+//    the end of the matrix need no predicate, and the load/store unit sees 4 wavefronts
+//    per 512 bytes instead of 32.  Saved activations that the backward epilogue re-reads
+//    come in the same way (tiled bulk load into the warp's staging buffer).
 #pragma once
 #include "gemm_sm100.cuh"
 
 namespace pomk {
 
-// -------------------------------------------------------------------- row I/O
-// 32 consecutive values of one row <-> 64 bytes of bf16.
-__device__ __forceinline__ void store_row32_packed(__nv_bfloat16* dst, const uint32_t (&pk)[16], int ncols_left) {
-  if (ncols_left >= 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-    uint4* d4 = reinterpret_cast<uint4*>(dst);
+// 16-byte piece j (0..3) of row `lane` inside a 32-row x 64-byte block stored with the 64-byte swizzle.
+__device__ __forceinline__ uint32_t swz64(int lane, int j) { return lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4); }
+
+// Hands the warp's 32 x 32 bf16 block (row `lane` = pk) to the TMA engine.  `pending_ok` is how many of
+// this lane-0's earlier bulk stores may still be reading shared memory: 1 when the caller alternates two
+// buffers, 0 when it reuses one.
+template <int PENDING_OK>
+__device__ __forceinline__ void store_block(uint8_t* buf, const CUtensorMap* map, const uint32_t (&pk)[16], int lane,
+                                            int x, int y, int z) {
+  if (lane == 0) bulk_wait_read<PENDING_OK>();
+  __syncwarp();
 #pragma unroll
-    for (int j = 0; j < 4; ++j) d4[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
-  } else {
-    const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(pk);
-#pragma unroll
-    for (int i = 0; i < 32; ++i)
-      if (i < ncols_left) dst[i] = h[i];
+  for (int j = 0; j < 4; ++j)
+    *reinterpret_cast<uint4*>(buf + swz64(lane, j)) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+  fence_async_smem();
+  __syncwarp();
+  if (lane == 0) {
+    tma_store_3d(map, buf, x, y, z);
+    bulk_commit();
   }
 }
 
-__device__ __forceinline__ void load_row32_bf16(const __nv_bfloat16* src, float (&v)[32], int ncols_left) {
-  if (ncols_left >= 32 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
-    const uint4* s4 = reinterpret_cast<const uint4*>(src);
+// Reads row `lane` of a 32 x 32 bf16 block that a bulk load placed in `buf`.
+__device__ __forceinline__ void read_block(const uint8_t* buf, int lane, float (&v)[32]) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const uint4 q = __ldg(&s4[j]);
-      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+  for (int j = 0; j < 4; ++j) {
+    const uint4 q = *reinterpret_cast<const uint4*>(buf + swz64(lane, j));
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        v[8 * j + 2 * e] = __uint_as_float(w[e] << 16);
-        v[8 * j + 2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
-      }
+    for (int e = 0; e < 4; ++e) {
+      v[8 * j + 2 * e] = __uint_as_float(w[e] << 16);
+      v[8 * j + 2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
     }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = (i < ncols_left) ? __bfloat162float(src[i]) : 0.f;
   }
 }
 
@@ -65,38 +74,29 @@ __device__ __forceinline__ float act_fast(float x) { return fminf(fmaxf(x, fmaxf
 // sum_{i<K} c_i a^(i+1) in Horner form; coefficients of column j live at cst[i * BN + j].
 template <int KT, int BN>
 __device__ __forceinline__ void poly4(const float* cst, int K, const float (&a)[4], float (&out)[4]) {
+  const int top = KT > 0 ? KT : K;
+  float4 c = *reinterpret_cast<const float4*>(cst + (top - 1) * BN);
+  float r[4] = {c.x, c.y, c.z, c.w};
   if constexpr (KT > 0) {
-    float4 c = *reinterpret_cast<const float4*>(cst + (KT - 1) * BN);
-    float r[4] = {c.x, c.y, c.z, c.w};
 #pragma unroll
     for (int i = KT - 2; i >= 0; --i) {
       c = *reinterpret_cast<const float4*>(cst + i * BN);
-      r[0] = fmaf(r[0], a[0], c.x);
-      r[1] = fmaf(r[1], a[1], c.y);
-      r[2] = fmaf(r[2], a[2], c.z);
-      r[3] = fmaf(r[3], a[3], c.w);
+      r[0] = fmaf(r[0], a[0], c.x), r[1] = fmaf(r[1], a[1], c.y), r[2] = fmaf(r[2], a[2], c.z), r[3] = fmaf(r[3], a[3], c.w);
     }
-#pragma unroll
-    for (int e = 0; e < 4; ++e) out[e] = r[e] * a[e];
   } else {
-    float4 c = *reinterpret_cast<const float4*>(cst + (K - 1) * BN);
-    float r[4] = {c.x, c.y, c.z, c.w};
     for (int i = K - 2; i >= 0; --i) {
       c = *reinterpret_cast<const float4*>(cst + i * BN);
-      r[0] = fmaf(r[0], a[0], c.x);
-      r[1] = fmaf(r[1], a[1], c.y);
-      r[2] = fmaf(r[2], a[2], c.z);
-      r[3] = fmaf(r[3], a[3], c.w);
+      r[0] = fmaf(r[0], a[0], c.x), r[1] = fmaf(r[1], a[1], c.y), r[2] = fmaf(r[2], a[2], c.z), r[3] = fmaf(r[3], a[3], c.w);
     }
-#pragma unroll
-    for (int e = 0; e < 4; ++e) out[e] = r[e] * a[e];
   }
+#pragma unroll
+  for (int e = 0; e < 4; ++e) out[e] = r[e] * a[e];
 }
 
 // --------------------------------------------------------------- plain store
 struct EpiStore {
   struct Params {
-    void* C;                 // bf16 or fp32, row-major
+    void* C;                 // fp32 modes only (bf16 output goes through maps.out0)
     long long ldc;           // elements
     long long batch_stride;  // elements between batches
     int mode;                // 0: bf16 store, 1: fp32 store, 2: fp32 atomic add (split-K)
@@ -105,32 +105,37 @@ struct EpiStore {
   static constexpr int kSmemBytes = 0;
 
   template <int BN>
-  static __device__ __forceinline__ void prologue(const Params&, const GemmGeom&, const TileCtx&, int, float*, int) {}
+  static __device__ __forceinline__ void prologue(const Params&, const EpiMaps&, const GemmGeom&, const TileCtx&, int,
+                                                  int, float*, EpiIO&, int) {}
 
   template <int BN>
-  static __device__ __forceinline__ void run(const Params& p, const GemmGeom& g, const TileCtx& t, uint32_t tmem_acc,
-                                             int quarter, int lane, int, float*, int) {
+  static __device__ __forceinline__ void run(const Params& p, const EpiMaps& maps, const GemmGeom& g, const TileCtx& t,
+                                             uint32_t tmem_acc, int quarter, int lane, int half, int, float*,
+                                             EpiIO& io, int) {
     const int row = quarter * 32 + lane;
     const bool row_ok = row < t.rows_valid;
     const long long off = static_cast<long long>(t.b) * p.batch_stride + static_cast<long long>(t.row0 + row) * p.ldc;
+    int flip = 0;
 #pragma unroll 1
-    for (int c = 0; c < BN / 32; ++c) {
+    for (int c = half; c < BN / 32; c += kEpiColSplit) {
       const int col = t.col0 + c * 32;
       if (col >= g.n_cols) break;  // warp-uniform
       float v[32];
       tmem_ld32(tmem_acc + c * 32, v);
       tmem_ld_wait();
-      const int left = g.n_cols - col;
-      if (!row_ok) continue;
       if (p.alpha != 1.f) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] *= p.alpha;
       }
       if (p.mode == 0) {
+        if (t.rows_valid <= 0) continue;
         uint32_t pk[16];
         pack32(v, pk);
-        store_row32_packed(reinterpret_cast<__nv_bfloat16*>(p.C) + off + col, pk, left);
+        store_block<1>(flip ? io.buf1 : io.buf0, &maps.out0, pk, lane, col, t.row0 + quarter * 32, t.b);
+        flip ^= 1;
       } else {
+        if (!row_ok) continue;
+        const int left = g.n_cols - col;
         float* dst = reinterpret_cast<float*>(p.C) + off + col;
         const bool vec = left >= 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
         if (p.mode == 1) {
@@ -163,16 +168,15 @@ struct EpiStore {
 
 // --------------------------------------------------------------- context phase
 // acc = X·Wpoᵀ.  Rounds to bf16 (what the backward pass re-reads), stores it when
-// asked, applies act + polynomial (+ per-token weight) and reduces over the tile's
-// tokens.  Per-tile column sums go to partial[(b * MT + mt), :] in a fixed order,
-// so the result is run-to-run deterministic.
+// asked (maps.out0), applies act + polynomial (+ per-token weight) and reduces over the
+// tile's tokens.  Per-tile column sums go to partial[(b * MT + mt), :] in a fixed
+// order, so the result is run-to-run deterministic.
 struct EpiCtx {
   struct Params {
     const float* coeff;       // (P, K) fp32
     int K;
     const float* row_weight;  // (B, rows_per_batch) fp32 or null (key-padding mask weights)
-    __nv_bfloat16* hp_out;    // (B*rows, ld_hp) or null
-    long long ld_hp;
+    int save_hp;              // store the rounded projection through maps.out0
     float* partial;           // (B * MT, P) fp32
     int P;
   };
@@ -181,8 +185,8 @@ struct EpiCtx {
   static constexpr int kSmemBytes = (kSumFloats + kMaxDegree * 256) * 4;
 
   template <int BN>
-  static __device__ __forceinline__ void prologue(const Params& p, const GemmGeom& g, const TileCtx& t, int epi_tid,
-                                                  float* scratch, int) {
+  static __device__ __forceinline__ void prologue(const Params& p, const EpiMaps&, const GemmGeom& g, const TileCtx& t,
+                                                  int, int epi_tid, float* scratch, EpiIO&, int) {
     // The barrier that ends the previous tile's `run` guarantees nobody still reads the old constants.
     float* cst = scratch + kSumFloats;
     const int K = p.K;
@@ -195,16 +199,18 @@ struct EpiCtx {
   }
 
   template <int KT, int BN>
-  static __device__ __forceinline__ void body(const Params& p, const GemmGeom& g, const TileCtx& t, uint32_t tmem_acc,
-                                              int quarter, int lane, float* buf, const float* cst) {
+  static __device__ __forceinline__ void body(const Params& p, const EpiMaps& maps, const GemmGeom& g,
+                                              const TileCtx& t, uint32_t tmem_acc, int quarter, int lane, int half,
+                                              float* buf, const float* cst, EpiIO& io) {
     const int row = quarter * 32 + lane;
     const bool row_ok = row < t.rows_valid;
-    const long long grow = static_cast<long long>(t.b) * g.rows_per_batch + t.row0 + row;
     const bool weighted = p.row_weight != nullptr;
     float w = 1.f;
-    if (weighted) w = row_ok ? __ldg(p.row_weight + grow) : 0.f;
+    if (weighted)
+      w = row_ok ? __ldg(p.row_weight + static_cast<long long>(t.b) * g.rows_per_batch + t.row0 + row) : 0.f;
+    int flip = 0;
 #pragma unroll 1
-    for (int c = 0; c < BN / 32; ++c) {
+    for (int c = half; c < BN / 32; c += kEpiColSplit) {
       const int col = t.col0 + c * 32;
       if (col >= g.n_cols) {  // warp-uniform
         buf[quarter * 256 + c * 32 + lane] = 0.f;
@@ -215,7 +221,10 @@ struct EpiCtx {
       tmem_ld32(tmem_acc + c * 32, v);
       tmem_ld_wait();
       round_pack32(v, pk);
-      if (p.hp_out && row_ok) store_row32_packed(p.hp_out + grow * p.ld_hp + col, pk, g.n_cols - col);
+      if (p.save_hp && t.rows_valid > 0) {
+        store_block<1>(flip ? io.buf1 : io.buf0, &maps.out0, pk, lane, col, t.row0 + quarter * 32, t.b);
+        flip ^= 1;
+      }
       // Rows past the end of the batch were zero-filled by TMA: act(0) = 0 and poly(0) = 0, so they
       // add nothing.  Columns past n_cols have zero coefficients.
 #pragma unroll
@@ -233,21 +242,22 @@ struct EpiCtx {
   }
 
   template <int BN>
-  static __device__ __forceinline__ void run(const Params& p, const GemmGeom& g, const TileCtx& t, uint32_t tmem_acc,
-                                             int quarter, int lane, int epi_tid, float* scratch, int iter) {
+  static __device__ __forceinline__ void run(const Params& p, const EpiMaps& maps, const GemmGeom& g, const TileCtx& t,
+                                             uint32_t tmem_acc, int quarter, int lane, int half, int epi_tid,
+                                             float* scratch, EpiIO& io, int iter) {
     float* buf = scratch + (iter & 1) * (4 * 256);
     const float* cst = scratch + kSumFloats;
     switch (p.K) {
-      case 1: body<1, BN>(p, g, t, tmem_acc, quarter, lane, buf, cst); break;
-      case 2: body<2, BN>(p, g, t, tmem_acc, quarter, lane, buf, cst); break;
-      case 3: body<3, BN>(p, g, t, tmem_acc, quarter, lane, buf, cst); break;
-      case 4: body<4, BN>(p, g, t, tmem_acc, quarter, lane, buf, cst); break;
-      default: body<0, BN>(p, g, t, tmem_acc, quarter, lane, buf, cst); break;
+      case 1: body<1, BN>(p, maps, g, t, tmem_acc, quarter, lane, half, buf, cst, io); break;
+      case 2: body<2, BN>(p, maps, g, t, tmem_acc, quarter, lane, half, buf, cst, io); break;
+      case 3: body<3, BN>(p, maps, g, t, tmem_acc, quarter, lane, half, buf, cst, io); break;
+      case 4: body<4, BN>(p, maps, g, t, tmem_acc, quarter, lane, half, buf, cst, io); break;
+      default: body<0, BN>(p, maps, g, t, tmem_acc, quarter, lane, half, buf, cst, io); break;
     }
     named_bar_sync(kEpiBarrier, kEpiThreads);
     for (int c = epi_tid; c < BN; c += kEpiThreads) {
       const int col = t.col0 + c;
-      if (col < g.n_cols) {
+      if (col < g.n_cols && t.rows_valid > 0) {  // a tile hanging over the end of its batch owns no slot
         const float s = (buf[c] + buf[256 + c]) + (buf[512 + c] + buf[768 + c]);
         p.partial[(static_cast<long long>(t.b) * g.m_tiles_per_batch + t.mt) * p.P + col] = s;
       }
@@ -269,47 +279,44 @@ __device__ __forceinline__ void stage_bias_h(float* cst, const float* bias, cons
 }
 
 // --------------------------------------------------------------- query phase
-// acc = X·Wseᵀ.  z = bf16(acc) is kept for the backward pass; the gated feature
-// s ⊙ H with s = hardsigmoid(z + bias) is written as bf16, ready to be the A
-// operand of the output projection.  H is one fp32 vector per sample.
+// acc = X·Wseᵀ.  z = bf16(acc) is kept for the backward pass (maps.out0); the gated
+// feature s ⊙ H with s = hardsigmoid(z + bias) is written as bf16 (maps.out1), ready to
+// be the A operand of the output projection.  H is one fp32 vector per sample.
 struct EpiGate {
   struct Params {
     const float* bias;  // (P) fp32
     const float* H;     // (B, P) fp32
     long long h_batch_stride;
-    long long h_row_stride;  // must be 0 (kept for ABI stability)
-    __nv_bfloat16* z_out;    // null in inference
-    long long ld_z;
-    __nv_bfloat16* sh_out;
-    long long ld_sh;
+    int save_z;
   };
   static constexpr int kSmemBytes = 2 * 2 * 256 * 4;  // double-buffered {bias, H}
 
   template <int BN>
-  static __device__ __forceinline__ void prologue(const Params& p, const GemmGeom& g, const TileCtx& t, int epi_tid,
-                                                  float* scratch, int iter) {
+  static __device__ __forceinline__ void prologue(const Params& p, const EpiMaps&, const GemmGeom& g, const TileCtx& t,
+                                                  int, int epi_tid, float* scratch, EpiIO&, int iter) {
     stage_bias_h<BN>(scratch + (iter & 1) * 512, p.bias, p.H + static_cast<long long>(t.b) * p.h_batch_stride, g, t,
                      epi_tid);
   }
 
   template <int BN>
-  static __device__ __forceinline__ void run(const Params& p, const GemmGeom& g, const TileCtx& t, uint32_t tmem_acc,
-                                             int quarter, int lane, int, float* scratch, int iter) {
+  static __device__ __forceinline__ void run(const Params& p, const EpiMaps& maps, const GemmGeom& g, const TileCtx& t,
+                                             uint32_t tmem_acc, int quarter, int lane, int half, int, float* scratch,
+                                             EpiIO& io, int iter) {
     const float* cst = scratch + (iter & 1) * 512;
-    const int row = quarter * 32 + lane;
-    const bool row_ok = row < t.rows_valid;
-    const long long grow = static_cast<long long>(t.b) * g.rows_per_batch + t.row0 + row;
+    const int y = t.row0 + quarter * 32;
+    int flip = 0;
 #pragma unroll 1
-    for (int c = 0; c < BN / 32; ++c) {
+    for (int c = half; c < BN / 32; c += kEpiColSplit) {
       const int col = t.col0 + c * 32;
       if (col >= g.n_cols) break;
       float v[32];
       uint32_t pk[16];
       tmem_ld32(tmem_acc + c * 32, v);
       tmem_ld_wait();
-      const int left = g.n_cols - col;
+      if (t.rows_valid <= 0) continue;
       round_pack32(v, pk);
-      if (p.z_out && row_ok) store_row32_packed(p.z_out + grow * p.ld_z + col, pk, left);
+      if (p.save_z) store_block<1>(io.buf0, &maps.out0, pk, lane, col, y, t.b);
+      else flip ^= 1;  // without the z store the SH blocks alternate between the two buffers
 #pragma unroll
       for (int i = 0; i < 32; i += 4) {
         const float4 bb = *reinterpret_cast<const float4*>(cst + c * 32 + i);
@@ -319,19 +326,17 @@ struct EpiGate {
         v[i + 2] = pom_hardsigmoid(v[i + 2] + bb.z) * hh.z;
         v[i + 3] = pom_hardsigmoid(v[i + 3] + bb.w) * hh.w;
       }
-      if (row_ok) {
-        pack32(v, pk);
-        store_row32_packed(p.sh_out + grow * p.ld_sh + col, pk, left);
-      }
+      pack32(v, pk);
+      store_block<1>(flip ? io.buf0 : io.buf1, &maps.out1, pk, lane, col, y, t.b);
     }
   }
 };
 
 // --------------------------------------------------------------- query phase, backward
-// acc = dY·Wo = dSH.  With z re-read from the forward pass:
+// acc = dY·Wo = dSH.  With z re-read from the forward pass (maps.in0):
 //   s  = hardsigmoid(z + bias)
 //   dH partial  = sum_rows dSH ⊙ s                      -> dh_partial[(b*MT+mt), :]
-//   dz          = dSH ⊙ H ⊙ hardsigmoid'(z + bias)      -> g_out (bf16), the se half of [dhp | dz]
+//   dz          = dSH ⊙ H ⊙ hardsigmoid'(z + bias)      -> maps.out0 (bf16), the se half of [dhp | dz]
 //   dbias part. = sum_rows dz                            -> db_partial[(b*MT+mt), :]
 // Rows past the end of the batch carry dSH = 0 (zero-filled A rows) and add nothing.
 struct EpiGateBwd {
@@ -339,10 +344,6 @@ struct EpiGateBwd {
     const float* bias;
     const float* H;
     long long h_batch_stride;
-    const __nv_bfloat16* z;
-    long long ld_z;
-    __nv_bfloat16* g_out;
-    long long ld_g;
     float* dh_partial;
     float* db_partial;
     int P;
@@ -350,24 +351,36 @@ struct EpiGateBwd {
   static constexpr int kSumFloats = 2 * 2 * 4 * 256;
   static constexpr int kSmemBytes = (kSumFloats + 2 * 2 * 256) * 4;
 
+  // Starts the bulk load of the z block for column chunk c of tile t into buf0 (one lane per warp).
+  static __device__ __forceinline__ void fetch_z(const EpiMaps& maps, const TileCtx& t, EpiIO& io, int quarter,
+                                                 int lane, int col) {
+    if (lane == 0) {
+      mbar_expect_tx(io.bar, 32 * 64);
+      tma_load_3d(io.buf0, &maps.in0, io.bar, col, t.row0 + quarter * 32, t.b);
+    }
+  }
+
   template <int BN>
-  static __device__ __forceinline__ void prologue(const Params& p, const GemmGeom& g, const TileCtx& t, int epi_tid,
-                                                  float* scratch, int iter) {
+  static __device__ __forceinline__ void prologue(const Params& p, const EpiMaps& maps, const GemmGeom& g,
+                                                  const TileCtx& t, int warp_in_epi, int epi_tid, float* scratch,
+                                                  EpiIO& io, int iter) {
+    const int half = warp_in_epi >> 2, quarter = (warp_in_epi + 2) & 3;
+    const int col = t.col0 + half * 32;
+    if (col < g.n_cols) fetch_z(maps, t, io, quarter, epi_tid & 31, col);
     stage_bias_h<BN>(scratch + kSumFloats + (iter & 1) * 512, p.bias,
                      p.H + static_cast<long long>(t.b) * p.h_batch_stride, g, t, epi_tid);
   }
 
   template <int BN>
-  static __device__ __forceinline__ void run(const Params& p, const GemmGeom& g, const TileCtx& t, uint32_t tmem_acc,
-                                             int quarter, int lane, int epi_tid, float* scratch, int iter) {
+  static __device__ __forceinline__ void run(const Params& p, const EpiMaps& maps, const GemmGeom& g, const TileCtx& t,
+                                             uint32_t tmem_acc, int quarter, int lane, int half, int epi_tid,
+                                             float* scratch, EpiIO& io, int iter) {
     const float* cst = scratch + kSumFloats + (iter & 1) * 512;
-    const int row = quarter * 32 + lane;
-    const bool row_ok = row < t.rows_valid;
-    const long long grow = static_cast<long long>(t.b) * g.rows_per_batch + t.row0 + (row_ok ? row : 0);
     float* buf_h = scratch + (iter & 1) * (2 * 4 * 256);
     float* buf_b = buf_h + 4 * 256;
+    bool alive = true;
 #pragma unroll 1
-    for (int c = 0; c < BN / 32; ++c) {
+    for (int c = half; c < BN / 32; c += kEpiColSplit) {
       const int col = t.col0 + c * 32;
       if (col >= g.n_cols) {
         buf_h[quarter * 256 + c * 32 + lane] = 0.f;
@@ -376,8 +389,10 @@ struct EpiGateBwd {
       }
       float v[32], z[32];
       tmem_ld32(tmem_acc + c * 32, v);
-      const int left = g.n_cols - col;
-      load_row32_bf16(p.z + grow * p.ld_z + col, z, left);
+      if (alive) alive = mbar_wait(io.bar, io.load_phase, io.abort_flag, io.status, kStatusEpilogueTimeout);
+      alive = __all_sync(0xffffffffu, alive);
+      io.load_phase ^= 1u;
+      read_block(io.buf0, lane, z);
       tmem_ld_wait();
 #pragma unroll
       for (int i = 0; i < 32; i += 4) {
@@ -393,13 +408,14 @@ struct EpiGateBwd {
           v[i + e] = dsh * pom_hardsigmoid(zz);                // dH contribution
         }
       }
-      if (row_ok) {
+      // every lane has consumed its z row: the block may be refilled for this warp's next chunk
+      __syncwarp();
+      const int ncol = t.col0 + (c + kEpiColSplit) * 32;
+      if (alive && c + kEpiColSplit < BN / 32 && ncol < g.n_cols) fetch_z(maps, t, io, quarter, lane, ncol);
+      if (t.rows_valid > 0) {
         uint32_t pk[16];
         pack32(z, pk);
-        store_row32_packed(p.g_out + grow * p.ld_g + col, pk, left);
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) z[i] = 0.f;  // v is already 0 there (dSH = 0)
+        store_block<0>(io.buf1, &maps.out0, pk, lane, col, t.row0 + quarter * 32, t.b);
       }
       warp_colsum32(v, lane);
       warp_colsum32(z, lane);
@@ -409,7 +425,7 @@ struct EpiGateBwd {
     named_bar_sync(kEpiBarrier, kEpiThreads);
     for (int c = epi_tid; c < BN; c += kEpiThreads) {
       const int col = t.col0 + c;
-      if (col < g.n_cols) {
+      if (col < g.n_cols && t.rows_valid > 0) {
         const long long o = (static_cast<long long>(t.b) * g.m_tiles_per_batch + t.mt) * p.P + col;
         p.dh_partial[o] = (buf_h[c] + buf_h[256 + c]) + (buf_h[512 + c] + buf_h[768 + c]);
         p.db_partial[o] = (buf_b[c] + buf_b[256 + c]) + (buf_b[512 + c] + buf_b[768 + c]);

@@ -117,13 +117,14 @@ struct Gemm2Smem {
 
 template <int BN, int STAGES, int EPI_SMEM>
 constexpr int gemm2_smem_bytes() {
-  return STAGES * Gemm2Smem<BN>::kStageBytes + 256 + EPI_SMEM + 1024;
+  return SmemPlan<STAGES>::bytes(Gemm2Smem<BN>::kStageBytes, EPI_SMEM);
 }
 
 template <int BN, int STAGES, bool A_MN, bool B_MN, class Epi>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                         const GemmGeom geom, const typename Epi::Params ep, int* __restrict__ status) {
+                         const __grid_constant__ EpiMaps maps, const GemmGeom geom, const typename Epi::Params ep,
+                         int* __restrict__ status) {
   static_assert(BN == 128 || BN == 256 || (BN == 192 && !B_MN), "unsupported pair-tile width");
   constexpr int kABytes = Gemm2Smem<BN>::kABytes;
   constexpr int kStageBytes = Gemm2Smem<BN>::kStageBytes;
@@ -132,16 +133,15 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   constexpr uint32_t kIdesc = make_idesc_bf16_m256(BN, A_MN, B_MN);
 
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* tiles = smem;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * kStageBytes);
-  uint64_t* full_bar = bars;                     // [STAGES]  used in the leader
-  uint64_t* empty_bar = bars + STAGES;           // [STAGES]  both CTAs
-  uint64_t* tfull_bar = bars + 2 * STAGES;       // [2]       both CTAs
-  uint64_t* tempty_bar = bars + 2 * STAGES + 2;  // [2]       used in the leader
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
-  float* epi_scratch = reinterpret_cast<float*>(smem + STAGES * kStageBytes + 256);
+  const SmemPlan<STAGES> sm(smem_raw, kStageBytes);
+  uint8_t* tiles = sm.tiles;
+  uint64_t* full_bar = sm.full_bar;      // used in the leader
+  uint64_t* empty_bar = sm.empty_bar;    // both CTAs
+  uint64_t* tfull_bar = sm.tfull_bar;    // both CTAs
+  uint64_t* tempty_bar = sm.tempty_bar;  // used in the leader
+  uint32_t* tmem_holder = sm.tmem_holder;
+  volatile int* abort_flag = sm.abort_flag;
+  float* epi_scratch = sm.epi_scratch;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -155,8 +155,9 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
-      mbar_init(&tempty_bar[a], 2 * 4 * kEpiColSplit);
+      mbar_init(&tempty_bar[a], 2 * kEpiWarps);
     }
+    for (int w = 0; w < kEpiWarps; ++w) mbar_init(&sm.wload_bar[w], 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -279,21 +280,30 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     const int quarter = warp & 3;
     const int half = (warp - 2) >> 2;
     const int epi_tid = (warp - 2) * 32 + lane;
+    EpiIO io;
+    io.buf0 = sm.staging + (warp - 2) * kEpiStageBytes;
+    io.buf1 = io.buf0 + kEpiStageBytes / 2;
+    io.bar = &sm.wload_bar[warp - 2];
+    io.load_phase = 0;
+    io.abort_flag = abort_flag;
+    io.status = status;
+    const uint32_t tempty_leader[2] = {map_to_cta(smem_u32(&tempty_bar[0]), 0), map_to_cta(smem_u32(&tempty_bar[1]), 0)};
     int iter = 0;
     for (int unit = cluster_id; unit < total_units; unit += n_clusters, ++iter) {
       const TileCtx t = decode_pair_tile(geom, unit, BN, rank);
       const int acc = iter & 1;
       const uint32_t acc_phase = (iter >> 1) & 1u;
-      Epi::template prologue<BN>(ep, geom, t, epi_tid, epi_scratch, iter);
+      Epi::template prologue<BN>(ep, maps, geom, t, warp - 2, epi_tid, epi_scratch, io, iter);
       const bool ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, status, kStatusEpilogueTimeout);
       if (named_bar_any(kEpiBarrier, kEpiThreads, !ok)) break;
       tc_fence_after();
       const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(acc * BN) + (static_cast<uint32_t>(quarter * 32) << 16);
-      Epi::template run<BN>(ep, geom, t, tmem_acc, quarter, lane, half, epi_tid, epi_scratch, iter);
+      Epi::template run<BN>(ep, maps, geom, t, tmem_acc, quarter, lane, half, epi_tid, epi_scratch, io, iter);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
+      if (lane == 0) mbar_arrive_cluster(tempty_leader[acc]);
     }
+    if (lane == 0) bulk_wait_all();
   }
 
   tc_fence_before();

@@ -91,25 +91,97 @@ struct GemmSmem {
   static constexpr int kStageBytes = kABytes + kBBytes;
 };
 
+// ---------------------------------------------------------------------------
+// Epilogue I/O through the TMA engine
+// ---------------------------------------------------------------------------
+// Tensor maps of the epilogue: up to two bf16 outputs and one bf16 input, each addressed
+// as (column, row-in-batch, batch) with a 32 x 32 box and 64-byte swizzle.
+struct alignas(64) EpiMaps {
+  CUtensorMap out0;
+  CUtensorMap out1;
+  CUtensorMap in0;
+};
+
+// Per-warp staging: two 2 KiB chunk buffers (1 KiB aligned) and one mbarrier for bulk loads.
+struct EpiIO {
+  uint8_t* buf0;
+  uint8_t* buf1;
+  uint64_t* bar;
+  uint32_t load_phase;  // parity of the next bulk load to complete on `bar`
+  volatile int* abort_flag;
+  int* status;
+};
+
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* smem_src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+
+constexpr int kEpiWarps = 4 * kEpiColSplit;
+constexpr int kEpiStageBytes = 4096;  // per epilogue warp: two 2 KiB blocks for bulk stores / loads
+
+// Carves the dynamic shared memory of both GEMM kernels:
+//   [pipeline tiles][epilogue staging 8 x 4 KiB][barriers, TMEM holder, abort flag: 256 B][epilogue scratch]
+template <int STAGES>
+struct SmemPlan {
+  uint8_t* tiles;
+  uint8_t* staging;
+  uint64_t* full_bar;    // [STAGES]  TMA -> MMA
+  uint64_t* empty_bar;   // [STAGES]  MMA -> TMA
+  uint64_t* tfull_bar;   // [2]       MMA -> epilogue
+  uint64_t* tempty_bar;  // [2]       epilogue -> MMA
+  uint64_t* wload_bar;   // [8]       per epilogue warp: bulk loads into its staging block
+  uint32_t* tmem_holder;
+  volatile int* abort_flag;
+  float* epi_scratch;
+  __device__ __forceinline__ SmemPlan(uint8_t* raw, int stage_bytes) {
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+    tiles = base;
+    staging = base + STAGES * stage_bytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(staging + kEpiWarps * kEpiStageBytes);
+    full_bar = bars;
+    empty_bar = bars + STAGES;
+    tfull_bar = bars + 2 * STAGES;
+    tempty_bar = bars + 2 * STAGES + 2;
+    wload_bar = bars + 2 * STAGES + 4;
+    tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4 + kEpiWarps);
+    abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+    epi_scratch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);
+  }
+  static constexpr int bytes(int stage_bytes, int epi_smem) {
+    return STAGES * stage_bytes + kEpiWarps * kEpiStageBytes + 256 + epi_smem + 1024;  // + alignment slack
+  }
+};
+
 template <int BN, int STAGES, int EPI_SMEM>
 constexpr int gemm_smem_bytes() {
-  // tiles + barriers/holders (256 B) + epilogue scratch + 1 KiB alignment slack
-  return STAGES * GemmSmem<BN>::kStageBytes + 256 + EPI_SMEM + 1024;
+  return SmemPlan<STAGES>::bytes(GemmSmem<BN>::kStageBytes, EPI_SMEM);
 }
 
 // ---------------------------------------------------------------------------
 // The kernel.  `Epi` supplies:
 //   struct Params;                      trivially copyable, passed by value
-//   static constexpr int kSmemBytes;    scratch shared by the 4 epilogue warps
-//   template<int BN> static __device__ void prologue(const Params&, const GemmGeom&, const TileCtx&,
-//        int epi_tid, float* scratch, int tile_iter);      stages per-column constants in shared memory
-//   template<int BN> static __device__ void run(const Params&, const GemmGeom&, const TileCtx&,
-//        uint32_t tmem_acc, int quarter, int lane, int epi_tid, float* scratch, int tile_iter);
+//   static constexpr int kSmemBytes;    scratch shared by the epilogue warps
+//   template<int BN> static __device__ void prologue(const Params&, const EpiMaps&, const GemmGeom&,
+//        const TileCtx&, int warp_in_epi, int epi_tid, float* scratch, EpiIO&, int tile_iter);
+//        runs before the accumulator is ready: stages per-column constants, starts bulk loads
+//   template<int BN> static __device__ void run(const Params&, const EpiMaps&, const GemmGeom&, const TileCtx&,
+//        uint32_t tmem_acc, int quarter, int lane, int half, int epi_tid, float* scratch, EpiIO&, int tile_iter);
 // ---------------------------------------------------------------------------
 template <int BN, int STAGES, bool A_MN, bool B_MN, class Epi>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const GemmGeom geom, const typename Epi::Params ep, int* __restrict__ status) {
+                    const __grid_constant__ EpiMaps maps, const GemmGeom geom, const typename Epi::Params ep,
+                    int* __restrict__ status) {
   static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "BN must be 64..256 in steps of 64");
   constexpr int kABytes = GemmSmem<BN>::kABytes;
   constexpr int kBBytes = GemmSmem<BN>::kBBytes;
@@ -118,16 +190,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   constexpr uint32_t kIdesc = make_idesc_bf16(BN, A_MN, B_MN);
 
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* tiles = smem;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * kStageBytes);
-  uint64_t* full_bar = bars;                    // [STAGES]  TMA -> MMA
-  uint64_t* empty_bar = bars + STAGES;          // [STAGES]  MMA -> TMA
-  uint64_t* tfull_bar = bars + 2 * STAGES;      // [2]       MMA -> epilogue
-  uint64_t* tempty_bar = bars + 2 * STAGES + 2; // [2]       epilogue -> MMA
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
-  float* epi_scratch = reinterpret_cast<float*>(smem + STAGES * kStageBytes + 256);
+  const SmemPlan<STAGES> sm(smem_raw, kStageBytes);
+  uint8_t* tiles = sm.tiles;
+  uint64_t* full_bar = sm.full_bar;
+  uint64_t* empty_bar = sm.empty_bar;
+  uint64_t* tfull_bar = sm.tfull_bar;
+  uint64_t* tempty_bar = sm.tempty_bar;
+  uint32_t* tmem_holder = sm.tmem_holder;
+  volatile int* abort_flag = sm.abort_flag;
+  float* epi_scratch = sm.epi_scratch;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -139,8 +210,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
-      mbar_init(&tempty_bar[a], 4 * kEpiColSplit);
+      mbar_init(&tempty_bar[a], kEpiWarps);
     }
+    for (int w = 0; w < kEpiWarps; ++w) mbar_init(&sm.wload_bar[w], 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -254,25 +326,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) are readable by this warp
     const int half = (warp - 2) >> 2;  // which of the interleaved column chunks this warp takes
     const int epi_tid = (warp - 2) * 32 + lane;
+    EpiIO io;
+    io.buf0 = sm.staging + (warp - 2) * kEpiStageBytes;
+    io.buf1 = io.buf0 + kEpiStageBytes / 2;
+    io.bar = &sm.wload_bar[warp - 2];
+    io.load_phase = 0;
+    io.abort_flag = abort_flag;
+    io.status = status;
     int iter = 0;
     for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x, ++iter) {
       const TileCtx t = decode_tile(geom, unit, BN);
       const int acc = iter & 1;
       const uint32_t acc_phase = (iter >> 1) & 1u;
       // Stage the per-column constants of this tile while its main loop is still running.
-      Epi::template prologue<BN>(ep, geom, t, epi_tid, epi_scratch, iter);
+      Epi::template prologue<BN>(ep, maps, geom, t, warp - 2, epi_tid, epi_scratch, io, iter);
       // All 32 lanes poll so the warp stays converged for the .aligned TMEM loads.
       const bool ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, status, kStatusEpilogueTimeout);
-      // The four epilogue warps decide together whether to go on, so none of them can be left
+      // The epilogue warps decide together whether to go on, so none of them can be left
       // waiting at a named barrier that another one will never reach.
       if (named_bar_any(kEpiBarrier, kEpiThreads, !ok)) break;
       tc_fence_after();
       const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(acc * BN) + (static_cast<uint32_t>(quarter * 32) << 16);
-      Epi::template run<BN>(ep, geom, t, tmem_acc, quarter, lane, half, epi_tid, epi_scratch, iter);
+      Epi::template run<BN>(ep, maps, geom, t, tmem_acc, quarter, lane, half, epi_tid, epi_scratch, io, iter);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
     }
+    if (lane == 0) bulk_wait_all();  // bulk stores still reading this warp's staging block
   }
 
   tc_fence_before();

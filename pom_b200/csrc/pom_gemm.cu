@@ -37,7 +37,7 @@ EncodeTiledFn encode_fn() {
 
 // bf16 tensor of `rank` dims (innermost first), 128-byte swizzle, zero fill out of bounds.
 int make_map(CUtensorMap* m, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_elems,
-             const uint32_t* box) {
+             const uint32_t* box, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return POM_ERR_CUDA;
   if (!aligned16(base)) return POM_ERR_BAD_ALIGN;
@@ -58,9 +58,18 @@ int make_map(CUtensorMap* m, const void* base, int rank, const uint64_t* dims, c
     gstr[i] = bytes;
   }
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdim,
-                  gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? POM_OK : POM_ERR_CUDA;
+}
+
+// Epilogue tensor: bf16 (batches, rows, cols) with row stride ld, moved in 32 x 32 blocks (64-byte swizzle).
+int make_io_map(CUtensorMap* m, const void* base, int64_t cols, int64_t rows, int64_t batches, int64_t ld) {
+  if (ld % 8 || ld < cols) return POM_ERR_BAD_STRIDE;
+  uint64_t dims[3] = {static_cast<uint64_t>(cols), static_cast<uint64_t>(rows), static_cast<uint64_t>(batches)};
+  uint64_t str[2] = {static_cast<uint64_t>(ld), static_cast<uint64_t>(ld) * static_cast<uint64_t>(rows)};
+  uint32_t box[3] = {32, 32, 1};
+  return make_map(m, base, 3, dims, str, box, CU_TENSOR_MAP_SWIZZLE_64B);
 }
 
 struct Operands {
@@ -144,7 +153,8 @@ int set_smem_once(Kern kern, int smem, bool* done) {
 
 // One CTA per 128 x BN tile.
 template <int BN, int STAGES, bool A_MN, bool B_MN, class Epi>
-int launch(const Operands& o, int split_k, const typename Epi::Params& ep, int* status, cudaStream_t st) {
+int launch(const Operands& o, int split_k, const EpiMaps& maps, const typename Epi::Params& ep, int* status,
+           cudaStream_t st) {
   CUtensorMap tmA, tmB;
   int rc = build_maps(o, BN, &tmA, &tmB);
   if (rc) return rc;
@@ -156,14 +166,15 @@ int launch(const Operands& o, int split_k, const typename Epi::Params& ep, int* 
   const long long units = 1ll * g.batches * g.m_tiles_per_batch * g.n_tiles * g.split_k;
   if (units > INT32_MAX) return POM_ERR_TOO_LARGE;
   const int grid = static_cast<int>(units < sm_count() ? units : sm_count());
-  kern<<<grid, kGemmThreads, smem, st>>>(tmA, tmB, g, ep, status);
+  kern<<<grid, kGemmThreads, smem, st>>>(tmA, tmB, maps, g, ep, status);
   count_launch();
   return check_launch();
 }
 
 // Two CTAs (one cluster) per 256 x BN tile; each CTA loads BN/2 rows of the B tile.
 template <int BN, int STAGES, bool A_MN, bool B_MN, class Epi>
-int launch_pair(const Operands& o, int split_k, const typename Epi::Params& ep, int* status, cudaStream_t st) {
+int launch_pair(const Operands& o, int split_k, const EpiMaps& maps, const typename Epi::Params& ep, int* status,
+                cudaStream_t st) {
   CUtensorMap tmA, tmB;
   int rc = build_maps(o, BN / 2, &tmA, &tmB);
   if (rc) return rc;
@@ -175,7 +186,7 @@ int launch_pair(const Operands& o, int split_k, const typename Epi::Params& ep, 
   const long long units = 1ll * g.batches * ((g.m_tiles_per_batch + 1) / 2) * g.n_tiles * g.split_k;
   if (units > INT32_MAX) return POM_ERR_TOO_LARGE;
   const int clusters = static_cast<int>(units < sm_count() / 2 ? units : sm_count() / 2);
-  kern<<<2 * clusters, kGemmThreads, smem, st>>>(tmA, tmB, g, ep, status);
+  kern<<<2 * clusters, kGemmThreads, smem, st>>>(tmA, tmB, maps, g, ep, status);
   count_launch();
   return check_launch();
 }
@@ -235,29 +246,42 @@ long long plan_units(const Operands& o, const TilePlan& p) {
   return 1ll * o.batches * (p.pair ? (mt + 1) / 2 : mt) * ceil_div(o.N, p.bn);
 }
 
+// Pipeline depth: as many stages as fit beside the epilogue staging area and scratch in the
+// 227 KiB of shared memory one CTA may use (at most 8).
+template <int STAGE_BYTES, class Epi>
+constexpr int stages_for() {
+  constexpr int kMaxSmem = 232448;
+  constexpr int n = (kMaxSmem - SmemPlan<1>::bytes(0, Epi::kSmemBytes)) / STAGE_BYTES;
+  return n > 8 ? 8 : n;
+}
+
 // Dispatch over kernel flavour and tile width for a fixed operand order and epilogue.
 template <bool A_MN, bool B_MN, class Epi>
-int run_plan(const TilePlan& p, const Operands& o, int split, const typename Epi::Params& ep, int* status,
-             cudaStream_t st) {
+int run_plan(const TilePlan& p, const Operands& o, int split, const EpiMaps& maps, const typename Epi::Params& ep,
+             int* status, cudaStream_t st) {
   if (p.pair) {
-    if (p.bn == 256) return launch_pair<256, 6, A_MN, B_MN, Epi>(o, split, ep, status, st);
+    if (p.bn == 256)
+      return launch_pair<256, stages_for<Gemm2Smem<256>::kStageBytes, Epi>(), A_MN, B_MN, Epi>(o, split, maps, ep, status, st);
     if constexpr (!B_MN) {
-      if (p.bn == 192) return launch_pair<192, 6, A_MN, B_MN, Epi>(o, split, ep, status, st);
+      if (p.bn == 192)
+        return launch_pair<192, stages_for<Gemm2Smem<192>::kStageBytes, Epi>(), A_MN, B_MN, Epi>(o, split, maps, ep, status, st);
     }
-    return launch_pair<128, 8, A_MN, B_MN, Epi>(o, split, ep, status, st);
+    return launch_pair<128, stages_for<Gemm2Smem<128>::kStageBytes, Epi>(), A_MN, B_MN, Epi>(o, split, maps, ep, status, st);
   }
-  if (p.bn == 256) return launch<256, 4, A_MN, B_MN, Epi>(o, split, ep, status, st);
-  if (p.bn == 192) return launch<192, 5, A_MN, B_MN, Epi>(o, split, ep, status, st);
-  return launch<128, 6, A_MN, B_MN, Epi>(o, split, ep, status, st);
+  if (p.bn == 256)
+    return launch<256, stages_for<GemmSmem<256>::kStageBytes, Epi>(), A_MN, B_MN, Epi>(o, split, maps, ep, status, st);
+  if (p.bn == 192)
+    return launch<192, stages_for<GemmSmem<192>::kStageBytes, Epi>(), A_MN, B_MN, Epi>(o, split, maps, ep, status, st);
+  return launch<128, stages_for<GemmSmem<128>::kStageBytes, Epi>(), A_MN, B_MN, Epi>(o, split, maps, ep, status, st);
 }
 
 template <class Epi>
-int run_plan_any_major(const TilePlan& p, const Operands& o, int split, const typename Epi::Params& ep, int* status,
-                       cudaStream_t st) {
-  if (!o.a_mn && !o.b_mn) return run_plan<false, false, Epi>(p, o, split, ep, status, st);
-  if (!o.a_mn && o.b_mn) return run_plan<false, true, Epi>(p, o, split, ep, status, st);
-  if (o.a_mn && !o.b_mn) return run_plan<true, false, Epi>(p, o, split, ep, status, st);
-  return run_plan<true, true, Epi>(p, o, split, ep, status, st);
+int run_plan_any_major(const TilePlan& p, const Operands& o, int split, const EpiMaps& maps,
+                       const typename Epi::Params& ep, int* status, cudaStream_t st) {
+  if (!o.a_mn && !o.b_mn) return run_plan<false, false, Epi>(p, o, split, maps, ep, status, st);
+  if (!o.a_mn && o.b_mn) return run_plan<false, true, Epi>(p, o, split, maps, ep, status, st);
+  if (o.a_mn && !o.b_mn) return run_plan<true, false, Epi>(p, o, split, maps, ep, status, st);
+  return run_plan<true, true, Epi>(p, o, split, maps, ep, status, st);
 }
 
 // ---------------------------------------------------------------- fp32 SIMT GEMM
@@ -353,7 +377,9 @@ int pom_gemm_bf16(const pom_gemm_args* a, int* status, void* stream) {
   ep.batch_stride = a->M * a->ldc;
   ep.mode = a->out_mode;
   ep.alpha = a->alpha;
-  return run_plan_any_major<EpiStore>(plan, o, split, ep, status, static_cast<cudaStream_t>(stream));
+  EpiMaps maps{};
+  if (a->out_mode == POM_OUT_BF16 && (rc = make_io_map(&maps.out0, a->C, a->N, a->M, a->batches, a->ldc))) return rc;
+  return run_plan_any_major<EpiStore>(plan, o, split, maps, ep, status, static_cast<cudaStream_t>(stream));
 }
 
 int pom_set_gemm_mode(int mode) {
@@ -392,11 +418,13 @@ int pom_ctx_gemm(const pom_ctx_args* a, int* status, void* stream) {
   ep.coeff = a->coeff;
   ep.K = a->K;
   ep.row_weight = a->row_weight;
-  ep.hp_out = static_cast<__nv_bfloat16*>(a->hp_out);
-  ep.ld_hp = a->ld_hp;
+  ep.save_hp = a->hp_out != nullptr;
   ep.partial = a->partial;
   ep.P = a->P;
-  return run_plan<false, false, EpiCtx>(pick_plan(o, false), o, 1, ep, status, static_cast<cudaStream_t>(stream));
+  EpiMaps maps{};
+  if (a->hp_out && (rc = make_io_map(&maps.out0, a->hp_out, a->P, a->N, a->B, a->ld_hp))) return rc;
+  return run_plan<false, false, EpiCtx>(pick_plan(o, false), o, 1, maps, ep, status,
+                                        static_cast<cudaStream_t>(stream));
 }
 
 int pom_gate_gemm(const pom_gate_args* a, int* status, void* stream) {
@@ -411,12 +439,12 @@ int pom_gate_gemm(const pom_gate_args* a, int* status, void* stream) {
   ep.bias = a->bias;
   ep.H = a->H;
   ep.h_batch_stride = a->h_batch_stride;
-  ep.h_row_stride = a->h_row_stride;
-  ep.z_out = static_cast<__nv_bfloat16*>(a->z_out);
-  ep.ld_z = a->ld_z;
-  ep.sh_out = static_cast<__nv_bfloat16*>(a->sh_out);
-  ep.ld_sh = a->ld_sh;
-  return run_plan<false, false, EpiGate>(pick_plan(o, false), o, 1, ep, status, static_cast<cudaStream_t>(stream));
+  ep.save_z = a->z_out != nullptr;
+  EpiMaps maps{};
+  if (a->z_out && (rc = make_io_map(&maps.out0, a->z_out, a->P, a->T, a->B, a->ld_z))) return rc;
+  if ((rc = make_io_map(&maps.out1, a->sh_out, a->P, a->T, a->B, a->ld_sh))) return rc;
+  return run_plan<false, false, EpiGate>(pick_plan(o, false), o, 1, maps, ep, status,
+                                         static_cast<cudaStream_t>(stream));
 }
 
 int pom_gate_bwd_gemm(const pom_gate_bwd_args* a, int* status, void* stream) {
@@ -430,14 +458,14 @@ int pom_gate_bwd_gemm(const pom_gate_bwd_args* a, int* status, void* stream) {
   ep.bias = a->bias;
   ep.H = a->H;
   ep.h_batch_stride = a->h_batch_stride;
-  ep.z = static_cast<const __nv_bfloat16*>(a->z);
-  ep.ld_z = a->ld_z;
-  ep.g_out = static_cast<__nv_bfloat16*>(a->g_out);
-  ep.ld_g = a->ld_g;
   ep.dh_partial = a->dh_partial;
   ep.db_partial = a->db_partial;
   ep.P = a->P;
-  return run_plan<false, true, EpiGateBwd>(pick_plan(o, false), o, 1, ep, status, static_cast<cudaStream_t>(stream));
+  EpiMaps maps{};
+  if ((rc = make_io_map(&maps.in0, a->z, a->P, a->T, a->B, a->ld_z))) return rc;
+  if ((rc = make_io_map(&maps.out0, a->g_out, a->P, a->T, a->B, a->ld_g))) return rc;
+  return run_plan<false, true, EpiGateBwd>(pick_plan(o, false), o, 1, maps, ep, status,
+                                           static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"
