@@ -199,6 +199,31 @@ typedef struct pom_agg_args {
 } pom_agg_args;
 int pom_poly_agg_fwd(const pom_agg_args* a, void* stream);
 
+/* Mean / weighted-mean aggregation for callers that must not allocate.  (No counterpart in the
+ * reference: it exists for hosts of this library, not to mirror one of its functions.)
+ *
+ * Some programs that embed these kernels hand out every byte of device memory when they start and
+ * then forbid cudaMalloc for good: serving processes with a fixed memory plan, plug-in hosts whose
+ * worker threads may not enter the allocator because an allocation can stall the whole device or
+ * fail long after start-up.  Such a caller has no place to get the (B, chunks, P) partial-sum buffer
+ * that pom_poly_agg_fwd needs.  This entry point computes
+ *     out[b, :] = scale * sum_n w[b,n] * R_n·polynomial(act(x[b,n,:])) / denom[b]
+ * (non-causal pom_poly_agg_fwd followed by pom_reduce_partials, bit for bit) with the partial sums
+ * held in a workspace that is part of the library image: 4 Mi floats (16 MiB) per GPU, resident from
+ * the moment the library is loaded on that GPU until the process ends.  a->partial, a->out, a->total,
+ * a->carry and a->causal (must be 0) are not used; `denom` may be NULL (= 1); `out` is (B, P) fp32.
+ *
+ * Limits and rules:
+ *   - B * pom_agg_chunks(N) * P must not exceed 4 194 304, else POM_ERR_TOO_LARGE and nothing runs.
+ *   - No cudaMalloc / cudaFree or allocating library call is made, on any call.  The first call on
+ *     each device looks up the workspace address (a host-side runtime query, no device work); make
+ *     that first call before starting any stream capture.
+ *   - All calls on one GPU share the one workspace.  Calls whose kernels could overlap on the GPU
+ *     (different streams without ordering between them) race on it; keep them on one stream or
+ *     order them yourself.  Nothing needs clearing between calls: each call overwrites every slot
+ *     it later reads. */
+int pom_poly_agg_mean_noalloc(const pom_agg_args* a, const float* denom, float scale, float* out, void* stream);
+
 /* Backward of the aggregation operator.
  *   causal == 0 : dH (B, P) fp32 is the gradient of out; token weight = row_weight[b,n] / denom[b]
  *                 (either may be NULL = 1); `scale` multiplies everything (1/N for a plain mean).

@@ -139,6 +139,7 @@ _SIGNATURES = {
     "pom_gate_bwd_gemm": (C.c_int, [C.POINTER(GateBwdArgs), C.c_void_p, C.c_void_p]),
     "pom_agg_chunks": (C.c_int32, [C.c_int32]),
     "pom_poly_agg_fwd": (C.c_int, [C.POINTER(AggArgs), C.c_void_p]),
+    "pom_poly_agg_mean_noalloc": (C.c_int, [C.POINTER(AggArgs), C.c_void_p, C.c_float, C.c_void_p, C.c_void_p]),
     "pom_poly_agg_bwd": (C.c_int, [C.POINTER(AggBwdArgs), C.c_void_p]),
     "pom_select_fwd": (C.c_int, [C.POINTER(SelectArgs), C.c_void_p]),
     "pom_select_bwd": (C.c_int, [C.POINTER(SelectBwdArgs), C.c_void_p]),

@@ -12,6 +12,7 @@
 #include "pom_math.cuh"
 #include <cuda_bf16.h>
 #include <initializer_list>
+#include <mutex>
 #include <type_traits>
 
 using namespace pomk;
@@ -790,6 +791,84 @@ int pom_poly_agg_fwd(const pom_agg_args* a, void* stream) {
   else agg_fwd_kernel<T, V, KR, true, false><<<wl.grid, wl.block, 0, st>>>(d)
   POM_DISPATCH(a->dtype, vec, CALL_PFX);
 #undef CALL_PFX
+  count_launch();
+  return check_launch();
+}
+
+// ------------------------------------------------------------------ aggregation without any allocation
+// Built-in workspace for pom_poly_agg_mean_noalloc: 4 Mi floats (16 MiB) that every GPU loading this
+// library keeps resident until the process exits.
+constexpr long long kNoAllocFloats = 4ll << 20;
+static __device__ __align__(256) float g_noalloc_workspace[kNoAllocFloats];
+
+// Device address of the workspace on the current device.  In host code the array's name is only a
+// handle for the runtime, not something a kernel can dereference, so the address is looked up once
+// per device and cached.
+static int noalloc_workspace(float** out) {
+  static std::mutex mu;
+  static float* cache[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    (void)cudaGetLastError();
+    return POM_ERR_CUDA;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cache[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_workspace) != cudaSuccess || !p) {
+      (void)cudaGetLastError();
+      return POM_ERR_CUDA;
+    }
+    cache[dev] = static_cast<float*>(p);
+  }
+  *out = cache[dev];
+  return POM_OK;
+}
+
+int pom_poly_agg_mean_noalloc(const pom_agg_args* a, const float* denom, float scale, float* out, void* stream) {
+  if (!a || !a->x || !a->coeff || !out) return POM_ERR_NULL;
+  if (a->causal) return POM_ERR_UNSUPPORTED;
+  if (a->B <= 0 || a->N <= 0 || a->P <= 0 || a->K < 1) return POM_ERR_BAD_SHAPE;
+  if (a->K > kMaxDegree) return POM_ERR_K_TOO_LARGE;
+  const int chunks = pom_agg_chunks(a->N);
+  if (a->B > 65535 || chunks > 65535) return POM_ERR_TOO_LARGE;
+  if (1ll * a->B * chunks * a->P > kNoAllocFloats) return POM_ERR_TOO_LARGE;  // does not fit the built-in workspace
+  if (a->dtype != POM_BF16 && a->dtype != POM_F32) return POM_ERR_UNSUPPORTED;
+  if (a->ldx < a->P) return POM_ERR_BAD_STRIDE;
+  int rc = check_rope(a->rope, a->P);
+  if (rc) return rc;
+  float* ws = nullptr;
+  if ((rc = noalloc_workspace(&ws))) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  AggDev d;
+  d.x = a->x;
+  d.coeff = a->coeff;
+  d.row_weight = a->row_weight;
+  d.partial = ws;
+  d.out = nullptr;
+  d.ldx = a->ldx;
+  d.ld_out = 0;
+  d.token_offset = 0;
+  d.B = a->B;
+  d.N = a->N;
+  d.P = a->P;
+  d.K = a->K;
+  d.chunks = chunks;
+  d.rope = a->rope;
+  const int vec = pick_vec(a->P, a->rope, a->dtype, a->K, {a->ldx}, {a->x});
+  const WalkLaunch wl = walk_launch(a->P, a->rope.kind, vec, chunks, a->B);
+  const bool has_rope = a->rope.kind != POM_ROPE_NONE;
+  // Every (sample, chunk, channel) slot that the reduction below reads is written by this launch first,
+  // so nothing left in the workspace by an earlier call can leak into the result.
+#define CALL_NA(T, V, KR)                                                                      \
+  if (has_rope) agg_fwd_kernel<T, V, KR, false, true><<<wl.grid, wl.block, 0, st>>>(d);        \
+  else agg_fwd_kernel<T, V, KR, false, false><<<wl.grid, wl.block, 0, st>>>(d)
+  POM_DISPATCH(a->dtype, vec, CALL_NA);
+#undef CALL_NA
+  count_launch();
+  if ((rc = check_launch())) return rc;
+  dim3 grid(static_cast<unsigned>(ceil_div(a->P, 32)), static_cast<unsigned>(a->B));
+  reduce_partials_kernel<<<grid, 256, 0, st>>>(ws, out, denom, scale, chunks, a->P);
   count_launch();
   return check_launch();
 }
