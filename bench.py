@@ -40,9 +40,12 @@ WORKLOADS = {
 METRIC = "pom_layer_fwd_bwd_tokens_per_s"
 UNIT = "tokens/s"
 
-# DRAM bytes (read + write) per launch of the heaviest GEMM launch of the `dit` step, from the ncu
-# capture summarised in profiles/ (None until a capture exists for the current kernel).
-NCU_TRAFFIC_BYTES = None
+# DRAM bytes (read + write) per launch, from the ncu captures summarised under profiles/
+# (dram__bytes_read.sum + dram__bytes_write.sum of one launch); None where no capture exists.
+NCU_TRAFFIC_BYTES = {
+    "gemm[32768x1152x4608 B^T]": 399.2e6,   # profiles/gemm_pair_store_dx_32768x1152x4608.md (algorithmic 388.6e6)
+    "ctx_gemm": 189.3e6,                    # profiles/ctx_gemm_dit.md (algorithmic 231.8e6, part still in L2)
+}
 
 
 def measured_peaks():
@@ -66,7 +69,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
         except OSError:
@@ -219,8 +222,8 @@ def build_case(w, rank, world, device):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=30)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="dit", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -244,7 +247,10 @@ def main():
     if _abi.lib().pom_device_check() != 0:
         raise SystemExit("the kernels are built for sm_100a and need a B200-class GPU")
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+        from datetime import timedelta
+
+        # a short timeout turns a mismatched collective into an error instead of a ten-minute stall
+        dist.init_process_group("nccl", device_id=device, timeout=timedelta(seconds=180))
     args.warmup = max(args.warmup, 3)
 
     mod, host_sets, kw, tokens_local = build_case(w, rank, world, device)
@@ -299,7 +305,7 @@ def main():
         y_host.copy_(y, non_blocking=True)
         dx_host.copy_(grads[0], non_blocking=True)
 
-    e2e_steps = max(3, min(args.steps, 10))
+    e2e_steps = max(3, min(args.steps, 20))
     for i in range(2):
         e2e_step(i)
     sync_all()
@@ -317,9 +323,9 @@ def main():
 
     # ---- roofline of the tensor-core kernel: per-launch CUDA-event timing of one instrumented step
     peaks = measured_peaks()
-    roof = None
-    if rank == 0:
-        roof = gemm_roofline(mod, dev_sets, kw, w, world, peaks)
+    # every rank runs the instrumented step (a token-sharded layer contains collectives); rank 0 reports
+    roof = gemm_roofline(mod, dev_sets, kw, w, world, peaks)
+    sync_all()
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -413,7 +419,8 @@ def gemm_roofline(mod, dev_sets, kw, w, world, peaks):
     return {"bound": "tensor", "kernel": "gemm_tcgen05_kernel: " + top["kernel"], "achieved": top["tflops"],
             "peak": peaks["burst"], "unit": "TFLOP/s", "frac": top["tflops"] / peaks["burst"],
             "peak_sustained": peaks["sustained"], "frac_of_sustained": top["tflops"] / peaks["sustained"],
-            "peak_source": peaks["source"], "traffic": NCU_TRAFFIC_BYTES,
+            "peak_source": peaks["source"], "traffic": NCU_TRAFFIC_BYTES.get(top["kernel"]),
+            "traffic_by_kernel": {k: v for k, v in NCU_TRAFFIC_BYTES.items()},
             "all_gemm_launches": {"tflops": tot_fl / tot_ms / 1e9, "ms_per_step": tot_ms, "frac": tot_fl / tot_ms / 1e9 / peaks["burst"]},
             "per_launch": rows}
 

@@ -58,12 +58,15 @@ class SeqShard:
     def exclusive_carry(self, total: torch.Tensor, reverse: bool = False) -> torch.Tensor:
         """Sum of ``total`` over the ranks before (or, reversed, after) this one, in rank order."""
         w = self.world
-        gathered = torch.empty((w,) + tuple(total.shape), dtype=total.dtype, device=total.device)
-        dist.all_gather_into_tensor(gathered, total.contiguous(), group=self.group)
+        flat = torch.empty((w * total.shape[0],) + tuple(total.shape[1:]), dtype=total.dtype, device=total.device)
+        dist.all_gather_into_tensor(flat, total.contiguous(), group=self.group)
+        gathered = flat.view((w,) + tuple(total.shape))
         r = self.rank
         part = gathered[r + 1:] if reverse else gathered[:r]
         if part.shape[0] == 0:
             return torch.zeros_like(total)
+        if not total.is_cuda:  # host-side bookkeeping only (the layer itself never runs on CPU tensors)
+            return part.sum(0)
         return ops.reduce_partials(part.transpose(0, 1).contiguous())
 
 
