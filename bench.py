@@ -227,6 +227,12 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="dit", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
+                    help="replay the step as a CUDA graph (auto: on for token-sharded multi-GPU runs, where launch "
+                         "latency would otherwise dominate)")
+    ap.add_argument("--defer-weight-grad-reduce", action="store_true",
+                    help="token-sharded runs: leave the parameter-gradient all-reduce to the caller (as a data-parallel "
+                         "optimizer step would do) instead of doing it inside the layer")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
@@ -254,6 +260,8 @@ def main():
     args.warmup = max(args.warmup, 3)
 
     mod, host_sets, kw, tokens_local = build_case(w, rank, world, device)
+    if args.defer_weight_grad_reduce and "shard" in kw:
+        kw["shard"].reduce_weight_grads = False
     params = list(mod.parameters())
     dev_sets = [(x.to(device), gy.to(device)) for x, gy in host_sets]
 
@@ -272,18 +280,40 @@ def main():
     for i in range(args.warmup):
         step(*dev_sets[i % len(dev_sets)])
     sync_all()
+    l0 = ops.launch_count()
+    step(*dev_sets[0])
+    launches_per_step = ops.launch_count() - l0
+    use_graph = args.graph == "on" or (args.graph == "auto" and w["shard"] == "token" and world > 1)
+    graphs = []
+    if use_graph:
+        # one graph per input set; kernels, memsets and NCCL collectives of a whole fwd+bwd step are captured
+        sync_all()
+        for xs_d, gy_d in dev_sets:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                keep = step(xs_d, gy_d)
+            graphs.append((g, keep))
+        for g, _ in graphs:
+            g.replay()
+        sync_all()
+
+    def run_step(i):
+        if use_graph:
+            graphs[i % len(graphs)][0].replay()
+        else:
+            step(*dev_sets[i % len(dev_sets)])
+
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    l0 = ops.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sync_all()
     e0.record()
     for i in range(args.steps):
-        step(*dev_sets[i % len(dev_sets)])
+        run_step(i)
     e1.record()
     sync_all()
-    launches = ops.launch_count() - l0
+    launches = launches_per_step * args.steps
     clocks = sampler.stop() if rank == 0 else None
     ms_total = torch.tensor([e0.elapsed_time(e1)], device=device)
     if world > 1:
@@ -343,7 +373,9 @@ def main():
                        "expand": w["expand"], "mask": w["mask"], "rope": w["rope"], "sharding": w["shard"],
                        "parallelism": f"{w['shard']}-shard x{world}",
                        "l2": "3 rotating input sets (>= 450 MB) plus ~1 GB of intermediates per step, larger than the 126 MB L2",
-                       "weight_grad_allreduce_in_timed_region": bool(w["shard"] == "token" and world > 1)},
+                       "cuda_graph": use_graph,
+                       "weight_grad_allreduce_in_timed_region": bool(w["shard"] == "token" and world > 1
+                                                                     and not args.defer_weight_grad_reduce)},
             "roofline": roof,
             "step_roofline": {"flops_per_step": flops_per_step(w) / (world if w["shard"] == "token" else 1),
                               "tflops": flops_per_step(w) / (world if w["shard"] == "token" else 1) / (ms_step * 1e-3) / 1e12,

@@ -297,6 +297,9 @@ int pom_select_bwd(const pom_select_bwd_args* a, void* stream);
  *   h_new[b,:] = (n_past * h_past[b,:] + h_cur[b,:]) / (n_past + 1)        (fp32, B*P elements) */
 int pom_state_merge(const float* h_past, const float* h_cur, float* h_new, float n_past, int64_t count, void* stream);
 
+/* Asynchronous zero fill of `bytes` bytes (cudaMemsetAsync on the stream); used for split-K accumulators. */
+int pom_fill_zero(void* dst, int64_t bytes, void* stream);
+
 /* Element conversion helpers (count elements): fp32 -> bf16, bf16 -> fp32. */
 int pom_cast_f32_to_bf16(const float* src, void* dst, int64_t count, void* stream);
 int pom_cast_bf16_to_f32(const void* src, float* dst, int64_t count, void* stream);

@@ -144,6 +144,7 @@ _SIGNATURES = {
     "pom_select_fwd": (C.c_int, [C.POINTER(SelectArgs), C.c_void_p]),
     "pom_select_bwd": (C.c_int, [C.POINTER(SelectBwdArgs), C.c_void_p]),
     "pom_state_merge": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int64, C.c_void_p]),
+    "pom_fill_zero": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p]),
     "pom_cast_f32_to_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "pom_cast_bf16_to_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
 }

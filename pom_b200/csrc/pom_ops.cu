@@ -409,10 +409,11 @@ __global__ void __launch_bounds__(128) agg_bwd_kernel(const AggBwdDev a) {
   }
   const int n0 = c * kChunk, n1 = min(a.N, n0 + kChunk);
   const int cnt = n1 - n0;
-  for (int ib = 0; ib < cnt; ib += kTB) {
-    float x1[kTB][VEC], x2[kTB][VEC], cs[kTB][VEC], sn[kTB][VEC], go1[kTB][VEC], go2[kTB][VEC], w[kTB];
+  constexpr int TBW = !ROPE ? 8 : (CAUSAL && VEC > 2) ? 2 : kTB;  // tokens in flight, as registers allow
+  for (int ib = 0; ib < cnt; ib += TBW) {
+    float x1[TBW][VEC], x2[TBW][VEC], cs[TBW][VEC], sn[TBW][VEC], go1[TBW][VEC], go2[TBW][VEC], w[TBW];
 #pragma unroll
-    for (int q = 0; q < kTB; ++q) {
+    for (int q = 0; q < TBW; ++q) {
       const int i = min(ib + q, cnt - 1);
       const int n = CAUSAL ? (n1 - 1 - i) : (n0 + i);
       Vec<T, VEC>::ld(x + n * a.ldx + m.p1, x1[q]);
@@ -429,7 +430,7 @@ __global__ void __launch_bounds__(128) agg_bwd_kernel(const AggBwdDev a) {
       }
     }
 #pragma unroll
-    for (int q = 0; q < kTB; ++q) {
+    for (int q = 0; q < TBW; ++q) {
       const int i = ib + q;
       if (i >= cnt) break;
       const int n = CAUSAL ? (n1 - 1 - i) : (n0 + i);
@@ -726,6 +727,19 @@ WalkLaunch walk_launch(int P, int rope_kind, int vec, int chunks, int B) {
     }                                                   \
   } while (0)
 
+// Same, for kernels that keep the polynomial coefficients in registers: degrees 1-2 get their own
+// instantiation (half the arithmetic of the 4-coefficient form).
+#define POM_DISPATCH_K(dtype, vec, K, CALL)                                   \
+  do {                                                                        \
+    if ((dtype) == POM_BF16 && (vec) == 8) {                                  \
+      if ((K) <= 2) { CALL(__nv_bfloat16, 8, 2); } else { CALL(__nv_bfloat16, 8, 4); } \
+    } else if ((dtype) != POM_BF16 && (vec) == 4) {                           \
+      if ((K) <= 2) { CALL(float, 4, 2); } else { CALL(float, 4, 4); }        \
+    } else {                                                                  \
+      POM_DISPATCH(dtype, vec, CALL);                                         \
+    }                                                                         \
+  } while (0)
+
 }  // namespace
 
 // =========================================================================== C ABI
@@ -778,7 +792,7 @@ int pom_poly_agg_fwd(const pom_agg_args* a, void* stream) {
 #define CALL_SUM(T, V, KR)                                                                    \
   if (has_rope) agg_fwd_kernel<T, V, KR, false, true><<<wl.grid, wl.block, 0, st>>>(d);        \
   else agg_fwd_kernel<T, V, KR, false, false><<<wl.grid, wl.block, 0, st>>>(d)
-  POM_DISPATCH(a->dtype, vec, CALL_SUM);
+  POM_DISPATCH_K(a->dtype, vec, a->K, CALL_SUM);
 #undef CALL_SUM
   count_launch();
   rc = check_launch();
@@ -789,7 +803,7 @@ int pom_poly_agg_fwd(const pom_agg_args* a, void* stream) {
 #define CALL_PFX(T, V, KR)                                                                   \
   if (has_rope) agg_fwd_kernel<T, V, KR, true, true><<<wl.grid, wl.block, 0, st>>>(d);        \
   else agg_fwd_kernel<T, V, KR, true, false><<<wl.grid, wl.block, 0, st>>>(d)
-  POM_DISPATCH(a->dtype, vec, CALL_PFX);
+  POM_DISPATCH_K(a->dtype, vec, a->K, CALL_PFX);
 #undef CALL_PFX
   count_launch();
   return check_launch();
@@ -863,7 +877,7 @@ int pom_poly_agg_mean_noalloc(const pom_agg_args* a, const float* denom, float s
 #define CALL_NA(T, V, KR)                                                                      \
   if (has_rope) agg_fwd_kernel<T, V, KR, false, true><<<wl.grid, wl.block, 0, st>>>(d);        \
   else agg_fwd_kernel<T, V, KR, false, false><<<wl.grid, wl.block, 0, st>>>(d)
-  POM_DISPATCH(a->dtype, vec, CALL_NA);
+  POM_DISPATCH_K(a->dtype, vec, a->K, CALL_NA);
 #undef CALL_NA
   count_launch();
   if ((rc = check_launch())) return rc;
@@ -925,13 +939,13 @@ int pom_poly_agg_bwd(const pom_agg_bwd_args* a, void* stream) {
 #define CALL_BC(T, V, KR)                                                                    \
   if (has_rope) agg_bwd_kernel<T, V, KR, true, true><<<wl.grid, wl.block, 0, st>>>(d);        \
   else agg_bwd_kernel<T, V, KR, true, false><<<wl.grid, wl.block, 0, st>>>(d)
-    POM_DISPATCH(a->dtype, vec, CALL_BC);
+    POM_DISPATCH_K(a->dtype, vec, a->K, CALL_BC);
 #undef CALL_BC
   } else {
 #define CALL_BN(T, V, KR)                                                                    \
   if (has_rope) agg_bwd_kernel<T, V, KR, false, true><<<wl.grid, wl.block, 0, st>>>(d);       \
   else agg_bwd_kernel<T, V, KR, false, false><<<wl.grid, wl.block, 0, st>>>(d)
-    POM_DISPATCH(a->dtype, vec, CALL_BN);
+    POM_DISPATCH_K(a->dtype, vec, a->K, CALL_BN);
 #undef CALL_BN
   }
   count_launch();
@@ -1026,6 +1040,16 @@ int pom_state_merge(const float* h_past, const float* h_cur, float* h_new, float
       h_past, h_cur, h_new, n_past, count);
   count_launch();
   return check_launch();
+}
+
+int pom_fill_zero(void* dst, int64_t bytes, void* stream) {
+  if (!dst) return POM_ERR_NULL;
+  if (bytes <= 0) return POM_ERR_BAD_SHAPE;
+  if (cudaMemsetAsync(dst, 0, static_cast<size_t>(bytes), static_cast<cudaStream_t>(stream)) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return POM_ERR_CUDA;
+  }
+  return POM_OK;
 }
 
 int pom_cast_f32_to_bf16(const float* src, void* dst, int64_t count, void* stream) {

@@ -144,7 +144,7 @@ class _PoMLayer(torch.autograd.Function):
         # ---------------------------------------------------------------- context phase
         if fused:
             partial, hp = ops.ctx_gemm(xc, w_po, coeff32, row_weight=maskf, save_hp=need_grad)
-            S = ops.reduce_partials(partial)
+            S = partial  # per-tile sums; reduced (and normalised, when no exchange is needed) below
         else:
             if spec.self_mixing:
                 hs = ops.gemm(xq.view(B * T, D), w_qc).view(B, T, 2 * P)
@@ -153,7 +153,7 @@ class _PoMLayer(torch.autograd.Function):
                 hp = ops.gemm(xc.view(B * N, D), w_po).view(B, N, P)
                 z = ops.gemm(xq.view(B * T, D), w_se).view(B, T, P)
             if not causal:
-                S = ops.reduce_partials(ops.poly_agg_fwd(hp, coeff32, row_weight=maskf, rope=spec.rope_ctx))
+                S = ops.poly_agg_fwd(hp, coeff32, row_weight=maskf, rope=spec.rope_ctx)  # per-chunk sums
         if causal:
             carry = None
             if shard is not None:
@@ -162,9 +162,10 @@ class _PoMLayer(torch.autograd.Function):
             Hc, _ = ops.poly_agg_fwd(hp, coeff32, causal=True, rope=spec.rope_ctx, carry=carry, token_offset=offset)
             H = None
         else:
+            scale = 1.0 if denom is not None else 1.0 / n_glob
             if shard is not None:
-                shard.all_reduce(S)
-            H = ops.reduce_partials(S.view(B, 1, P), denom=denom, scale=(1.0 if denom is not None else 1.0 / n_glob))
+                S = shard.all_reduce(ops.reduce_partials(S)).view(B, 1, P)
+            H = ops.reduce_partials(S, denom=denom, scale=scale)
             if spec.n_past is not None and h_past is not None:
                 H = ops.state_merge(_f32(h_past.reshape(B, P).contiguous()), H, spec.n_past)
 
@@ -200,7 +201,13 @@ class _PoMLayer(torch.autograd.Function):
         dy2 = dy.view(B * T, D)
 
         # dWo[d, p] = sum_t dY[t, d] * SH[t, p]
-        d_wag = torch.zeros((D, P), dtype=torch.float32, device=dev)
+        # one flat fp32 buffer for all parameter gradients: a single zero fill, cast and (when sharded) all-reduce
+        n_qc, n_ag = 2 * P * D, D * P
+        flat = ops.zeros_f32(n_qc + n_ag + P + P * K, dev)
+        d_wqc = flat[:n_qc].view(2 * P, D)
+        d_wag = flat[n_qc:n_qc + n_ag].view(D, P)
+        d_bias = flat[n_qc + n_ag:n_qc + n_ag + P]
+        d_coeff = flat[n_qc + n_ag + P:].view(P, K)
         ops.gemm(dy2, sh.view(B * T, P), a_mn=True, b_mn=True, out=d_wag, accumulate=True)
 
         if spec.self_mixing:
@@ -214,10 +221,11 @@ class _PoMLayer(torch.autograd.Function):
         if ctx.fused:
             dh_p, db_p = ops.gate_bwd_gemm(dy, w_ag, bias32, H, z, g_z)
             dH = ops.reduce_partials(dh_p)
-            d_bias = ops.reduce_partials(db_p.view(1, -1, P)).view(P)
+            ops.reduce_partials(db_p.view(1, -1, P), out=d_bias.view(1, P))
         else:
             dsh = ops.gemm(dy2, w_ag, b_mn=True).view(B, T, P)
-            dH, d_bias = ops.select_bwd(dsh, z, bias32, Hc if causal else H, g_z.view(B, T, P), rope=spec.rope_qry)
+            dH, _ = ops.select_bwd(dsh, z, bias32, Hc if causal else H, g_z.view(B, T, P), rope=spec.rope_qry,
+                                   dbias_out=d_bias)
 
         # ---------------------------------------------------------------- context phase backward
         d_hpast = None
@@ -227,8 +235,8 @@ class _PoMLayer(torch.autograd.Function):
                 _, tot = ops.poly_agg_bwd(hp, coeff32, dx_out=g_hp.view(B, N, P), dout=dH, causal=True,
                                           rope=spec.rope_ctx, token_offset=offset, want_total=True, totals_only=True)
                 carry = shard.exclusive_carry(tot, reverse=True)
-            d_coeff, _ = ops.poly_agg_bwd(hp, coeff32, dx_out=g_hp.view(B, N, P), dout=dH, causal=True,
-                                          rope=spec.rope_ctx, carry=carry, token_offset=offset)
+            ops.poly_agg_bwd(hp, coeff32, dx_out=g_hp.view(B, N, P), dout=dH, causal=True, rope=spec.rope_ctx,
+                             carry=carry, token_offset=offset, dcoeff_out=d_coeff)
         else:
             if dh_state is not None:
                 dH = ops.reduce_partials(torch.stack([dH, _f32(dh_state.reshape(B, P).contiguous())], dim=1))
@@ -243,11 +251,10 @@ class _PoMLayer(torch.autograd.Function):
                     if ctx.h_past_dtype != torch.float32:
                         d_hpast = ops.to_bf16(d_hpast)
                 scale = scale / (spec.n_past + 1.0)
-            d_coeff, _ = ops.poly_agg_bwd(hp, coeff32, dx_out=g_hp.view(B, N, P), dH=dH, row_weight=maskf, denom=denom,
-                                          scale=scale, rope=spec.rope_ctx)
+            ops.poly_agg_bwd(hp, coeff32, dx_out=g_hp.view(B, N, P), dH=dH, row_weight=maskf, denom=denom,
+                             scale=scale, rope=spec.rope_ctx, dcoeff_out=d_coeff)
 
         # ---------------------------------------------------------------- projections backward
-        d_wqc = torch.zeros((2 * P, D), dtype=torch.float32, device=dev)
         if spec.self_mixing:
             dxq = ops.gemm(G, w_qc, b_mn=True).view(B, T, D)
             ops.gemm(G, xq.view(B * T, D), a_mn=True, b_mn=True, out=d_wqc, accumulate=True)
@@ -259,10 +266,16 @@ class _PoMLayer(torch.autograd.Function):
             ops.gemm(g_z, xq.view(B * T, D), a_mn=True, b_mn=True, out=d_wqc[P:], accumulate=True)
 
         if shard is not None and shard.reduce_weight_grads:
-            for t in (d_wqc, d_wag, d_bias, d_coeff):
-                shard.all_reduce(t)
-        return (dxq, dxc, _like_param(d_wqc, p_qc), _like_param(d_bias, p_bias), _like_param(d_coeff.contiguous(), p_coeff),
-                _like_param(d_wag, p_ag), None, d_hpast, None)
+            shard.all_reduce(flat)
+        dts = {p_qc.dtype, p_bias.dtype, p_coeff.dtype, p_ag.dtype}
+        if dts == {torch.bfloat16}:
+            f16 = ops.to_bf16(flat)
+            g_qc, g_ag = f16[:n_qc].view(2 * P, D), f16[n_qc:n_qc + n_ag].view(D, P)
+            g_bias, g_coeff = f16[n_qc + n_ag:n_qc + n_ag + P], f16[n_qc + n_ag + P:].view(P, K)
+        else:
+            g_qc, g_ag = _like_param(d_wqc, p_qc), _like_param(d_wag, p_ag)
+            g_bias, g_coeff = _like_param(d_bias, p_bias), _like_param(d_coeff, p_coeff)
+        return (dxq, dxc, g_qc, g_bias, g_coeff, g_ag, None, d_hpast, None)
 
 
 def pom_layer(xq, xc, w_qc, se_bias, coeff, w_ag, mask=None, h_past=None, spec: Optional[LayerSpec] = None):

@@ -224,7 +224,7 @@ def poly_agg_bwd(x: torch.Tensor, coeff: torch.Tensor, *, dx_out: torch.Tensor, 
                  dout: Optional[torch.Tensor] = None, row_weight: Optional[torch.Tensor] = None,
                  denom: Optional[torch.Tensor] = None, scale: float = 1.0, causal: bool = False,
                  rope: Optional[RopeSpec] = None, carry: Optional[torch.Tensor] = None, token_offset: int = 0,
-                 want_total: bool = False, totals_only: bool = False):
+                 want_total: bool = False, totals_only: bool = False, dcoeff_out: Optional[torch.Tensor] = None):
     """Writes dx into ``dx_out`` (a (B, N, P) view, own row stride) and returns
     (dcoeff (P, K) fp32, total (B, P) fp32 or None)."""
     dev = _require_cuda(x, coeff, dx_out, dH, dout, row_weight, denom, carry)
@@ -247,7 +247,7 @@ def poly_agg_bwd(x: torch.Tensor, coeff: torch.Tensor, *, dx_out: torch.Tensor, 
     _abi.check(_abi.lib().pom_poly_agg_bwd(C.byref(a), _abi.stream_ptr()), "pom_poly_agg_bwd")
     if totals_only:
         return None, total
-    dcoeff = reduce_partials(dcp).view(P, K)
+    dcoeff = reduce_partials(dcp, out=None if dcoeff_out is None else dcoeff_out.view(1, P * K)).view(P, K)
     return dcoeff, total
 
 
@@ -273,7 +273,7 @@ def select_fwd(z: torch.Tensor, bias: Optional[torch.Tensor], h: torch.Tensor, *
 
 
 def select_bwd(dsh: torch.Tensor, z: torch.Tensor, bias: Optional[torch.Tensor], h: torch.Tensor, dz_out: torch.Tensor,
-               *, rope: Optional[RopeSpec] = None, activated: bool = False):
+               *, rope: Optional[RopeSpec] = None, activated: bool = False, dbias_out: Optional[torch.Tensor] = None):
     """Returns (dH, dbias): dH is (B, P) fp32 un-normalised sum over tokens when ``h`` is per-sample,
     else the per-token (B, T, P) gradient in z.dtype.  dz is written into ``dz_out``."""
     dev = _require_cuda(dsh, z, bias, h, dz_out)
@@ -292,7 +292,7 @@ def select_bwd(dsh: torch.Tensor, z: torch.Tensor, bias: Optional[torch.Tensor],
     a.dtype, a.h_per_token, a.activated = _abi.dtype_code(z.dtype), int(per_tok), int(activated)
     a.rope = _rope_c(rope)
     _abi.check(_abi.lib().pom_select_bwd(C.byref(a), _abi.stream_ptr()), "pom_select_bwd")
-    dbias = reduce_partials(db_p).view(P)
+    dbias = reduce_partials(db_p, out=None if dbias_out is None else dbias_out.view(1, P)).view(P)
     dH = dh_tok if per_tok else reduce_partials(dh_p)
     return dH, dbias
 
@@ -302,6 +302,13 @@ def state_merge(h_past: torch.Tensor, h_cur: torch.Tensor, n_past: float) -> tor
     out = torch.empty_like(h_cur)
     _abi.check(_abi.lib().pom_state_merge(ptr(h_past), ptr(h_cur), ptr(out), float(n_past), h_cur.numel(),
                                           _abi.stream_ptr()), "pom_state_merge")
+    return out
+
+
+def zeros_f32(n: int, device) -> torch.Tensor:
+    """Flat fp32 buffer of n zeros (allocation by PyTorch, fill by cudaMemsetAsync on the current stream)."""
+    out = torch.empty((n,), dtype=torch.float32, device=device)
+    _abi.check(_abi.lib().pom_fill_zero(ptr(out), out.numel() * 4, _abi.stream_ptr()), "pom_fill_zero")
     return out
 
 
