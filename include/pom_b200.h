@@ -293,6 +293,26 @@ typedef struct pom_select_bwd_args {
 } pom_select_bwd_args;
 int pom_select_bwd(const pom_select_bwd_args* a, void* stream);
 
+/* Multi-head scalar gating (reference pom/pom.py:119-122): one gate value per (token, head) multiplies the
+ * P / heads channels of that head.  `s` is the activated (and, with rotary embedding, rotated) gate, fp32
+ * (B, T, heads).  Forward: sh[b,t,p] = s[b,t,p / head_dim] * H[b, t or 0, p].  Backward: gradient of H (per-chunk
+ * partial sums (B, chunks, P) fp32, or per token in dtype) and gradient of s, accumulated into `ds` (B, T, heads)
+ * fp32, which the caller zeroes first.  H as in pom_select_args. */
+typedef struct pom_select_heads_args {
+  const float* s;
+  const void* H;
+  const void* dsh;     /* backward only */
+  void* sh;            /* forward only */
+  float* ds;           /* backward only */
+  float* dh_partial;   /* backward, h_per_token == 0 */
+  void* dh_tok;        /* backward, h_per_token != 0 */
+  int64_t ld_h, ld_sh, ld_dsh, ld_dh;
+  int32_t B, T, P, heads;
+  int32_t dtype, h_per_token;
+} pom_select_heads_args;
+int pom_select_heads_fwd(const pom_select_heads_args* a, void* stream);
+int pom_select_heads_bwd(const pom_select_heads_args* a, void* stream);
+
 /* Running-mean state update of state_forward (reference pom/pom.py:255-259):
  *   h_new[b,:] = (n_past * h_past[b,:] + h_cur[b,:]) / (n_past + 1)        (fp32, B*P elements) */
 int pom_state_merge(const float* h_past, const float* h_cur, float* h_new, float n_past, int64_t count, void* stream);

@@ -124,6 +124,16 @@ class SelectBwdArgs(C.Structure):
     ]
 
 
+class SelectHeadsArgs(C.Structure):
+    _fields_ = [
+        ("s", C.c_void_p), ("H", C.c_void_p), ("dsh", C.c_void_p), ("sh", C.c_void_p), ("ds", C.c_void_p),
+        ("dh_partial", C.c_void_p), ("dh_tok", C.c_void_p),
+        ("ld_h", C.c_int64), ("ld_sh", C.c_int64), ("ld_dsh", C.c_int64), ("ld_dh", C.c_int64),
+        ("B", C.c_int32), ("T", C.c_int32), ("P", C.c_int32), ("heads", C.c_int32),
+        ("dtype", C.c_int32), ("h_per_token", C.c_int32),
+    ]
+
+
 # Every exported symbol with its signature; test_abi_exports checks the list against the header.
 _SIGNATURES = {
     "pom_abi_version": (C.c_int, []),
@@ -143,6 +153,8 @@ _SIGNATURES = {
     "pom_poly_agg_bwd": (C.c_int, [C.POINTER(AggBwdArgs), C.c_void_p]),
     "pom_select_fwd": (C.c_int, [C.POINTER(SelectArgs), C.c_void_p]),
     "pom_select_bwd": (C.c_int, [C.POINTER(SelectBwdArgs), C.c_void_p]),
+    "pom_select_heads_fwd": (C.c_int, [C.POINTER(SelectHeadsArgs), C.c_void_p]),
+    "pom_select_heads_bwd": (C.c_int, [C.POINTER(SelectHeadsArgs), C.c_void_p]),
     "pom_state_merge": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int64, C.c_void_p]),
     "pom_fill_zero": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p]),
     "pom_cast_f32_to_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),

@@ -628,6 +628,79 @@ __global__ void __launch_bounds__(128) select_kernel(const SelDev a) {
   }
 }
 
+// ------------------------------------------------------------------ multi-head scalar gating
+// One gate value per (token, head) multiplies every channel of that head
+// (reference pom/pom.py:119-122).  The gate s (B, T, heads) is fp32 and already activated / rotated.
+struct SelHeadsDev {
+  const float* s;
+  const void* H;
+  const void* dsh;
+  void* sh;
+  float* ds;
+  float* dh_partial;
+  void* dh_tok;
+  long long ld_h, ld_sh, ld_dsh, ld_dh;
+  int B, T, P, heads, head_dim, chunks, h_per_token;
+};
+
+template <typename T, int VEC, bool BWD>
+__global__ void __launch_bounds__(128) select_heads_kernel(const SelHeadsDev a) {
+  const int p = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+  const int c = blockIdx.y, b = blockIdx.z;
+  if (p >= a.P) return;
+  const int head = p / a.head_dim;  // VEC divides head_dim, so the thread's channels share one head
+  const long long rowb = static_cast<long long>(b) * a.T;
+  float hb[VEC], accH[VEC];
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) {
+    hb[e] = a.h_per_token ? 0.f : static_cast<const float*>(a.H)[static_cast<long long>(b) * a.P + p + e];
+    accH[e] = 0.f;
+  }
+  const int t0 = c * kChunk, t1 = min(a.T, t0 + kChunk);
+  constexpr int TB = 4;
+  for (int tb = t0; tb < t1; tb += TB) {
+    float h[TB][VEC], g[TB][VEC], sv[TB];
+#pragma unroll
+    for (int q = 0; q < TB; ++q) {
+      const int t = min(tb + q, t1 - 1);
+      sv[q] = __ldg(a.s + (rowb + t) * a.heads + head);
+      if (a.h_per_token) {
+        Vec<T, VEC>::ld(static_cast<const T*>(a.H) + (rowb + t) * a.ld_h + p, h[q]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) h[q][e] = hb[e];
+      }
+      if (BWD) Vec<T, VEC>::ld(static_cast<const T*>(a.dsh) + (rowb + t) * a.ld_dsh + p, g[q]);
+    }
+#pragma unroll
+    for (int q = 0; q < TB; ++q) {
+      const int t = tb + q;
+      if (t >= t1) break;
+      float o[VEC];
+      if (!BWD) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) o[e] = sv[q] * h[q][e];
+        Vec<T, VEC>::st(static_cast<T*>(a.sh) + (rowb + t) * a.ld_sh + p, o);
+      } else {
+        float dsum = 0.f;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          o[e] = g[q][e] * sv[q];      // gradient of H
+          accH[e] += o[e];
+          dsum = fmaf(g[q][e], h[q][e], dsum);  // gradient of the gate, summed over the head's channels
+        }
+        atomicAdd(a.ds + (rowb + t) * a.heads + head, dsum);
+        if (a.h_per_token) Vec<T, VEC>::st(static_cast<T*>(a.dh_tok) + (rowb + t) * a.ld_dh + p, o);
+      }
+    }
+  }
+  if (BWD && !a.h_per_token) {
+    float* dst = a.dh_partial + (static_cast<long long>(b) * a.chunks + c) * a.P + p;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) dst[e] = accH[e];
+  }
+}
+
 // ------------------------------------------------------------------ small element-wise
 __global__ void state_merge_kernel(const float* hp, const float* hc, float* hn, float n_past, long long count) {
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -1032,6 +1105,54 @@ int pom_select_bwd(const pom_select_bwd_args* a, void* stream) {
                        {a->z, a->dsh, a->dz, a->h_per_token ? a->H : nullptr, a->h_per_token ? a->dh_tok : nullptr},
                        static_cast<cudaStream_t>(stream));
 }
+
+static int select_heads_common(const pom_select_heads_args* a, bool bwd, void* stream) {
+  if (!a || !a->s || !a->H) return POM_ERR_NULL;
+  if (bwd ? (!a->dsh || !a->ds || (a->h_per_token ? !a->dh_tok : !a->dh_partial)) : !a->sh) return POM_ERR_NULL;
+  if (a->B <= 0 || a->T <= 0 || a->P <= 0 || a->heads <= 0 || a->P % a->heads) return POM_ERR_BAD_SHAPE;
+  if (a->dtype != POM_BF16 && a->dtype != POM_F32) return POM_ERR_UNSUPPORTED;
+  SelHeadsDev d{};
+  d.s = a->s;
+  d.H = a->H;
+  d.dsh = a->dsh;
+  d.sh = a->sh;
+  d.ds = a->ds;
+  d.dh_partial = a->dh_partial;
+  d.dh_tok = a->dh_tok;
+  d.ld_h = a->ld_h;
+  d.ld_sh = a->ld_sh;
+  d.ld_dsh = a->ld_dsh;
+  d.ld_dh = a->ld_dh;
+  d.B = a->B;
+  d.T = a->T;
+  d.P = a->P;
+  d.heads = a->heads;
+  d.head_dim = a->P / a->heads;
+  d.chunks = pom_agg_chunks(a->T);
+  d.h_per_token = a->h_per_token;
+  if (d.B > 65535 || d.chunks > 65535) return POM_ERR_TOO_LARGE;
+  pom_rope none{};
+  // the channel vector must not straddle two heads: treat head_dim as the unit the vector has to divide
+  int vec = pick_vec(d.head_dim, none, a->dtype, 1,
+                     {a->h_per_token ? a->ld_h : 0, bwd ? a->ld_dsh : a->ld_sh, (bwd && a->h_per_token) ? a->ld_dh : 0},
+                     {a->h_per_token ? a->H : nullptr, bwd ? a->dsh : a->sh, (bwd && a->h_per_token) ? a->dh_tok : nullptr});
+  const WalkLaunch wl = walk_launch(a->P, POM_ROPE_NONE, vec, d.chunks, a->B);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (bwd) {
+#define CALL_HB(T, V, KR) select_heads_kernel<T, V, true><<<wl.grid, wl.block, 0, st>>>(d)
+    POM_DISPATCH(a->dtype, vec, CALL_HB);
+#undef CALL_HB
+  } else {
+#define CALL_HF(T, V, KR) select_heads_kernel<T, V, false><<<wl.grid, wl.block, 0, st>>>(d)
+    POM_DISPATCH(a->dtype, vec, CALL_HF);
+#undef CALL_HF
+  }
+  count_launch();
+  return check_launch();
+}
+
+int pom_select_heads_fwd(const pom_select_heads_args* a, void* stream) { return select_heads_common(a, false, stream); }
+int pom_select_heads_bwd(const pom_select_heads_args* a, void* stream) { return select_heads_common(a, true, stream); }
 
 int pom_state_merge(const float* h_past, const float* h_cur, float* h_new, float n_past, int64_t count, void* stream) {
   if (!h_past || !h_cur || !h_new) return POM_ERR_NULL;

@@ -81,6 +81,7 @@ class LayerSpec:
     shard: Optional[SeqShard] = None
     n_past: Optional[float] = None   # state_forward: number of previous calls (None = plain forward)
     want_state: bool = False
+    n_sel_heads: int = 1
 
 
 def _f32(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
@@ -111,7 +112,8 @@ def _check_inputs(xq, xc, w_qc, w_ag, coeff, spec: LayerSpec):
 
 class _PoMLayer(torch.autograd.Function):
     """y = ((R_q · hardsigmoid(xq·Wseᵀ + b)) ⊙ agg(R_c · poly(act(xc·Wpoᵀ)))) · Woᵀ
-    (reference pom/pom.py:193-231 and pom/pom_rope.py:443-526)."""
+    (reference pom/pom.py:193-231 and pom/pom_rope.py:443-526).  With ``spec.n_sel_heads > 1`` the gate has one
+    value per head (Wse is (heads, D)) and multiplies all channels of its head (pom/pom.py:119-122)."""
 
     @staticmethod
     def forward(ctx, xq, xc, w_qc, se_bias, coeff, w_ag, mask, h_past, spec: LayerSpec):
@@ -119,7 +121,11 @@ class _PoMLayer(torch.autograd.Function):
         B, T, D = xq.shape
         N = xc.shape[1]
         P, K = coeff.shape
+        heads = spec.n_sel_heads if spec.n_sel_heads > 1 else 0
+        S = heads if heads else P  # width of the gate projection
         bf16 = xq.dtype == torch.bfloat16
+        if heads and bf16 and (heads % 8 or P % 8 or D % 8):
+            raise NotImplementedError("bf16 multi-head gating needs n_sel_heads, dim and dim*expand to be multiples of 8")
         xq = xq.contiguous()
         xc = xq if spec.self_mixing else xc.contiguous()
         w_qc = w_qc.contiguous()
@@ -138,22 +144,23 @@ class _PoMLayer(torch.autograd.Function):
             denom = ops.reduce_partials(maskf.view(B, N, 1)).view(B)
             if shard is not None:
                 shard.all_reduce(denom)
-        fused = bf16 and spec.rope_ctx is None and spec.rope_qry is None and not causal and P % 8 == 0 and D % 8 == 0
+        fused = (bf16 and not heads and spec.rope_ctx is None and spec.rope_qry is None and not causal
+                 and P % 8 == 0 and D % 8 == 0)
 
-        hp = z = Hc = None
+        hp = z = Hc = s32 = None
         # ---------------------------------------------------------------- context phase
         if fused:
             partial, hp = ops.ctx_gemm(xc, w_po, coeff32, row_weight=maskf, save_hp=need_grad)
-            S = partial  # per-tile sums; reduced (and normalised, when no exchange is needed) below
+            S_part = partial  # per-tile sums; reduced (and normalised, when no exchange is needed) below
         else:
             if spec.self_mixing:
-                hs = ops.gemm(xq.view(B * T, D), w_qc).view(B, T, 2 * P)
+                hs = ops.gemm(xq.view(B * T, D), w_qc).view(B, T, P + S)
                 hp, z = hs[..., :P], hs[..., P:]
             else:
                 hp = ops.gemm(xc.view(B * N, D), w_po).view(B, N, P)
-                z = ops.gemm(xq.view(B * T, D), w_se).view(B, T, P)
+                z = ops.gemm(xq.view(B * T, D), w_se).view(B, T, S)
             if not causal:
-                S = ops.poly_agg_fwd(hp, coeff32, row_weight=maskf, rope=spec.rope_ctx)  # per-chunk sums
+                S_part = ops.poly_agg_fwd(hp, coeff32, row_weight=maskf, rope=spec.rope_ctx)  # per-chunk sums
         if causal:
             carry = None
             if shard is not None:
@@ -164,34 +171,37 @@ class _PoMLayer(torch.autograd.Function):
         else:
             scale = 1.0 if denom is not None else 1.0 / n_glob
             if shard is not None:
-                S = shard.all_reduce(ops.reduce_partials(S)).view(B, 1, P)
-            H = ops.reduce_partials(S, denom=denom, scale=scale)
+                S_part = shard.all_reduce(ops.reduce_partials(S_part)).view(B, 1, P)
+            H = ops.reduce_partials(S_part, denom=denom, scale=scale)
             if spec.n_past is not None and h_past is not None:
                 H = ops.state_merge(_f32(h_past.reshape(B, P).contiguous()), H, spec.n_past)
 
         # ---------------------------------------------------------------- query phase
         if fused:
             sh, z = ops.gate_gemm(xq, w_se, bias32, H, save_z=need_grad)
+        elif heads:
+            ones = _ones(B, heads, xq.device)
+            s32 = _f32(ops.select_fwd(z, bias32, ones, rope=spec.rope_qry))   # gate in head space (B, T, heads)
+            sh = ops.select_heads_fwd(s32, Hc if causal else H, xq.dtype)
         else:
             sh = ops.select_fwd(z, bias32, Hc if causal else H, rope=spec.rope_qry)
         y = ops.gemm(sh.view(B * T, P), w_ag).view(B, T, D)
 
         ctx.spec = spec
         ctx.fused = fused
-        ctx.dims = (B, T, N, D, P, K, n_glob, offset)
+        ctx.dims = (B, T, N, D, P, K, S, heads, n_glob, offset)
         ctx.h_past_dtype = None if h_past is None else h_past.dtype
-        ctx.save_for_backward(xq, xc, w_qc, w_ag, coeff32, bias32, hp, z, H, Hc, sh, maskf, denom)
+        ctx.save_for_backward(xq, xc, w_qc, w_ag, coeff32, bias32, hp, z, H, Hc, sh, maskf, denom, s32)
         ctx.param_like = (w_qc, se_bias, coeff, w_ag)
         if spec.want_state:
-            h_state = H.view(B, 1, P)
-            return y, h_state
+            return y, H.view(B, 1, P)
         return y, None
 
     @staticmethod
     def backward(ctx, dy, dh_state):
         spec: LayerSpec = ctx.spec
-        xq, xc, w_qc, w_ag, coeff32, bias32, hp, z, H, Hc, sh, maskf, denom = ctx.saved_tensors
-        B, T, N, D, P, K, n_glob, offset = ctx.dims
+        xq, xc, w_qc, w_ag, coeff32, bias32, hp, z, H, Hc, sh, maskf, denom, s32 = ctx.saved_tensors
+        B, T, N, D, P, K, S, heads, n_glob, offset = ctx.dims
         p_qc, p_bias, p_coeff, p_ag = ctx.param_like
         shard = spec.shard
         causal = spec.mask_kind == "causal"
@@ -200,22 +210,22 @@ class _PoMLayer(torch.autograd.Function):
         dy = dy.contiguous()
         dy2 = dy.view(B * T, D)
 
-        # dWo[d, p] = sum_t dY[t, d] * SH[t, p]
         # one flat fp32 buffer for all parameter gradients: a single zero fill, cast and (when sharded) all-reduce
-        n_qc, n_ag = 2 * P * D, D * P
-        flat = ops.zeros_f32(n_qc + n_ag + P + P * K, dev)
-        d_wqc = flat[:n_qc].view(2 * P, D)
+        n_qc, n_ag = (P + S) * D, D * P
+        flat = ops.zeros_f32(n_qc + n_ag + S + P * K, dev)
+        d_wqc = flat[:n_qc].view(P + S, D)
         d_wag = flat[n_qc:n_qc + n_ag].view(D, P)
-        d_bias = flat[n_qc + n_ag:n_qc + n_ag + P]
-        d_coeff = flat[n_qc + n_ag + P:].view(P, K)
+        d_bias = flat[n_qc + n_ag:n_qc + n_ag + S]
+        d_coeff = flat[n_qc + n_ag + S:].view(P, K)
+        # dWo[d, p] = sum_t dY[t, d] * SH[t, p]
         ops.gemm(dy2, sh.view(B * T, P), a_mn=True, b_mn=True, out=d_wag, accumulate=True)
 
         if spec.self_mixing:
-            G = torch.empty((B * T, 2 * P), dtype=dt, device=dev)
+            G = torch.empty((B * T, P + S), dtype=dt, device=dev)
             g_hp, g_z = G[:, :P], G[:, P:]
         else:
             g_hp = torch.empty((B * N, P), dtype=dt, device=dev)
-            g_z = torch.empty((B * T, P), dtype=dt, device=dev)
+            g_z = torch.empty((B * T, S), dtype=dt, device=dev)
 
         # ---------------------------------------------------------------- query phase backward
         if ctx.fused:
@@ -224,8 +234,15 @@ class _PoMLayer(torch.autograd.Function):
             ops.reduce_partials(db_p.view(1, -1, P), out=d_bias.view(1, P))
         else:
             dsh = ops.gemm(dy2, w_ag, b_mn=True).view(B, T, P)
-            dH, _ = ops.select_bwd(dsh, z, bias32, Hc if causal else H, g_z.view(B, T, P), rope=spec.rope_qry,
-                                   dbias_out=d_bias)
+            if heads:
+                ds32 = ops.zeros_f32(B * T * heads, dev).view(B, T, heads)
+                dH = ops.select_heads_bwd(dsh, s32, Hc if causal else H, ds32)
+                ds = ds32 if dt == torch.float32 else ops.to_bf16(ds32)
+                ops.select_bwd(ds, z, bias32, _ones(B, heads, dev), g_z.view(B, T, heads), rope=spec.rope_qry,
+                               dbias_out=d_bias)
+            else:
+                dH, _ = ops.select_bwd(dsh, z, bias32, Hc if causal else H, g_z.view(B, T, P), rope=spec.rope_qry,
+                                       dbias_out=d_bias)
 
         # ---------------------------------------------------------------- context phase backward
         d_hpast = None
@@ -270,12 +287,23 @@ class _PoMLayer(torch.autograd.Function):
         dts = {p_qc.dtype, p_bias.dtype, p_coeff.dtype, p_ag.dtype}
         if dts == {torch.bfloat16}:
             f16 = ops.to_bf16(flat)
-            g_qc, g_ag = f16[:n_qc].view(2 * P, D), f16[n_qc:n_qc + n_ag].view(D, P)
-            g_bias, g_coeff = f16[n_qc + n_ag:n_qc + n_ag + P], f16[n_qc + n_ag + P:].view(P, K)
+            g_qc, g_ag = f16[:n_qc].view(P + S, D), f16[n_qc:n_qc + n_ag].view(D, P)
+            g_bias, g_coeff = f16[n_qc + n_ag:n_qc + n_ag + S], f16[n_qc + n_ag + S:].view(P, K)
         else:
             g_qc, g_ag = _like_param(d_wqc, p_qc), _like_param(d_wag, p_ag)
             g_bias, g_coeff = _like_param(d_bias, p_bias), _like_param(d_coeff, p_coeff)
         return (dxq, dxc, g_qc, g_bias, g_coeff, g_ag, None, d_hpast, None)
+
+
+_ones_cache = {}
+
+
+def _ones(b: int, n: int, device) -> torch.Tensor:
+    """(b, n) fp32 ones on ``device`` (identity 'state' used to run the gate kernels in head space)."""
+    key = (b, n, str(device))
+    if key not in _ones_cache:
+        _ones_cache[key] = torch.ones((b, n), dtype=torch.float32, device=device)
+    return _ones_cache[key]
 
 
 def pom_layer(xq, xc, w_qc, se_bias, coeff, w_ag, mask=None, h_past=None, spec: Optional[LayerSpec] = None):

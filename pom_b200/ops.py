@@ -13,7 +13,8 @@ from typing import Optional
 import torch
 
 from . import _abi
-from ._abi import AggArgs, AggBwdArgs, CtxArgs, GateArgs, GateBwdArgs, GemmArgs, Rope, SelectArgs, SelectBwdArgs, ptr
+from ._abi import (AggArgs, AggBwdArgs, CtxArgs, GateArgs, GateBwdArgs, GemmArgs, Rope, SelectArgs, SelectBwdArgs,
+                   SelectHeadsArgs, ptr)
 
 
 def _require_cuda(*tensors) -> torch.device:
@@ -295,6 +296,49 @@ def select_bwd(dsh: torch.Tensor, z: torch.Tensor, bias: Optional[torch.Tensor],
     dbias = reduce_partials(db_p, out=None if dbias_out is None else dbias_out.view(1, P)).view(P)
     dH = dh_tok if per_tok else reduce_partials(dh_p)
     return dH, dbias
+
+
+def _heads_args(s: torch.Tensor, h: torch.Tensor, dtype: torch.dtype) -> SelectHeadsArgs:
+    B, T, heads = s.shape
+    per_tok = h.dim() == 3
+    P = h.shape[-1]
+    if s.dtype != torch.float32 or not s.is_contiguous():
+        raise TypeError("the per-head gate must be a contiguous float32 tensor")
+    if per_tok and h.dtype != dtype:
+        raise TypeError("per-token H must have the activation dtype")
+    if not per_tok and h.dtype != torch.float32:
+        raise TypeError("broadcast H must be float32")
+    a = SelectHeadsArgs()
+    a.s, a.H = ptr(s), ptr(h)
+    a.ld_h = _row_stride(h) if per_tok else 0
+    a.B, a.T, a.P, a.heads = B, T, P, heads
+    a.dtype, a.h_per_token = _abi.dtype_code(dtype), int(per_tok)
+    return a
+
+
+def select_heads_fwd(s: torch.Tensor, h: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """SH[b,t,p] = s[b,t,head(p)] * H: s (B, T, heads) fp32; H (B, P) fp32 or (B, T, P) of ``dtype``."""
+    dev = _require_cuda(s, h)
+    a = _heads_args(s, h, dtype)
+    sh = torch.empty((a.B, a.T, a.P), dtype=dtype, device=dev)
+    a.sh, a.ld_sh = ptr(sh), a.P
+    _abi.check(_abi.lib().pom_select_heads_fwd(C.byref(a), _abi.stream_ptr()), "pom_select_heads_fwd")
+    return sh
+
+
+def select_heads_bwd(dsh: torch.Tensor, s: torch.Tensor, h: torch.Tensor, ds_out: torch.Tensor) -> torch.Tensor:
+    """Adds the gate gradient into ``ds_out`` (B, T, heads) fp32 (zeroed by the caller) and returns dH:
+    (B, P) fp32 summed over tokens when H is per sample, else per token in dsh.dtype."""
+    dev = _require_cuda(dsh, s, h, ds_out)
+    a = _heads_args(s, h, dsh.dtype)
+    per_tok = bool(a.h_per_token)
+    chunks = agg_chunks(a.T)
+    dh_p = None if per_tok else torch.empty((a.B, chunks, a.P), dtype=torch.float32, device=dev)
+    dh_tok = torch.empty((a.B, a.T, a.P), dtype=dsh.dtype, device=dev) if per_tok else None
+    a.dsh, a.ld_dsh, a.ds = ptr(dsh), _row_stride(dsh), ptr(ds_out)
+    a.dh_partial, a.dh_tok, a.ld_dh = ptr(dh_p), ptr(dh_tok), a.P
+    _abi.check(_abi.lib().pom_select_heads_bwd(C.byref(a), _abi.stream_ptr()), "pom_select_heads_bwd")
+    return dh_tok if per_tok else reduce_partials(dh_p)
 
 
 def state_merge(h_past: torch.Tensor, h_cur: torch.Tensor, n_past: float) -> torch.Tensor:

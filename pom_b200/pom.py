@@ -23,7 +23,8 @@ class PoM(nn.Module):
         degree:      polynomial degree K (1..16).
         expand:      channel expansion; the polynomial features have P = expand * dim channels.
         n_groups:    must be 1 (grouped projections are not implemented by the CUDA path).
-        n_sel_heads: must be 0 or 1 (multi-head scalar gating is not implemented by the CUDA path).
+        n_sel_heads: 0 or 1: one gate value per channel; > 1: one gate value per head, shared by the
+                     dim*expand / n_sel_heads channels of that head (bf16 needs a multiple of 8 heads).
         bias:        add a bias to the output projection.
     """
 
@@ -33,8 +34,6 @@ class PoM(nn.Module):
         assert n_sel_heads <= 1 or dim * expand % n_sel_heads == 0, "dim * expand must be divisible by n_sel_heads"
         if n_groups > 1:
             raise NotImplementedError("n_groups > 1 (grouped projection) is not implemented by the CUDA path")
-        if n_sel_heads > 1:
-            raise NotImplementedError("n_sel_heads > 1 (multi-head gating) is not implemented by the CUDA path")
         self.dim = dim
         self.order = degree
         self.order_expand = expand
@@ -42,7 +41,7 @@ class PoM(nn.Module):
         self.n_sel_heads = n_sel_heads
         self.head_dim = dim * expand // max(n_sel_heads, 1)
         self._po_dim = expand * dim
-        self._se_dim = expand * dim
+        self._se_dim = n_sel_heads if n_sel_heads > 1 else expand * dim
         # creation order matters for seeded initialisation: qc_proj, se_bias, po_coeff, ag_proj
         self.qc_proj = nn.Linear(dim, self._po_dim + self._se_dim, bias=False)
         self.se_bias = nn.Parameter(torch.zeros(self._se_dim))
@@ -54,7 +53,8 @@ class PoM(nn.Module):
         kind = _mask_kind(mask)
         if kind == "full":
             raise NotImplementedError("(B, M, N) masks are not implemented by the CUDA path yet")
-        spec = LayerSpec(degree=self.order, mask_kind=kind, self_mixing=(xc is None or xc is xq), shard=shard)
+        spec = LayerSpec(degree=self.order, mask_kind=kind, self_mixing=(xc is None or xc is xq), shard=shard,
+                         n_sel_heads=self.n_sel_heads)
         return spec, (mask if kind == "keypad" else None)
 
     def _finish(self, y: torch.Tensor) -> torch.Tensor:
@@ -78,7 +78,8 @@ class PoM(nn.Module):
         As in the reference (pom/pom.py:251-262) the counter advances by one per call, so every
         call weighs equally whatever its token count.
         """
-        spec = LayerSpec(degree=self.order, self_mixing=(xc is None or xc is xq), want_state=True)
+        spec = LayerSpec(degree=self.order, self_mixing=(xc is None or xc is xq), want_state=True,
+                         n_sel_heads=self.n_sel_heads)
         h_past = None
         n_past = 0
         if state is not None:

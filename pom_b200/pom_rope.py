@@ -51,6 +51,14 @@ class PoMRoPE(PoM):
         super().__init__(dim, degree, expand, n_groups, n_sel_heads, bias)
         self.rope_2d = rope_2d
         rope_dim = dim * expand
+        if n_sel_heads > 1:  # same constraints as the reference (pom/pom_rope.py:343-359)
+            hd = rope_dim // n_sel_heads
+            if rope_2d:
+                assert n_sel_heads % 4 == 0, f"n_sel_heads ({n_sel_heads}) must be divisible by 4 for 2-D RoPE"
+                assert hd >= 4, f"head_dim ({hd}) must be >= 4 for 2-D RoPE with n_sel_heads > 1"
+            else:
+                assert n_sel_heads % 2 == 0, f"n_sel_heads ({n_sel_heads}) must be even for 1-D RoPE"
+                assert hd >= 2, f"head_dim ({hd}) must be >= 2 for 1-D RoPE with n_sel_heads > 1"
         if rope_2d:
             assert rope_dim % 4 == 0, f"dim * expand ({rope_dim}) must be divisible by 4 for 2-D RoPE"
             rc, rs, cc, cs = precompute_freqs_2d(rope_dim, max_h, max_w, rope_base)
@@ -64,21 +72,34 @@ class PoMRoPE(PoM):
             self.register_buffer("freqs_cos", fc)
             self.register_buffer("freqs_sin", fs)
 
-    def _rope_spec(self, n_tokens: int, positions, positions_hw, device) -> RopeSpec:
+    def _tables(self, for_gate: bool):
+        """fp32 tables; for the per-head gate the columns are sub-sampled so that gate pair k rotates at the
+        leading frequency of head k (reference pom/pom_rope.py:417-437)."""
+        names = ("row_cos", "row_sin", "col_cos", "col_sin") if self.rope_2d else ("freqs_cos", "freqs_sin")
+        tabs = [getattr(self, n).float() for n in names]
+        if for_gate and self.n_sel_heads > 1:
+            if self.rope_2d:
+                stride, keep = self.head_dim, self.n_sel_heads // 4
+            else:
+                stride, keep = self.head_dim // 2, self.n_sel_heads // 2
+            tabs = [t[:, ::stride][:, :keep] for t in tabs]
+        return [t.contiguous() for t in tabs]
+
+    def _rope_spec(self, n_tokens: int, positions, positions_hw, device, for_gate: bool = False) -> RopeSpec:
+        tabs = self._tables(for_gate)
         if self.rope_2d:
             if positions_hw is None:
                 raise ValueError("positions_hw (N, 2) must be provided when rope_2d=True")
             pos = positions_hw.to(device=device, dtype=torch.int64).contiguous()
             if pos.shape != (n_tokens, 2):
                 raise ValueError(f"positions_hw must have shape ({n_tokens}, 2)")
-            return RopeSpec(_abi.ROPE_2D, self.row_cos.float().contiguous(), self.row_sin.float().contiguous(), pos,
-                            self.col_cos.float().contiguous(), self.col_sin.float().contiguous())
+            return RopeSpec(_abi.ROPE_2D, tabs[0], tabs[1], pos, tabs[2], tabs[3])
         if positions is None:
             positions = torch.arange(n_tokens, device=device)
         pos = positions.to(device=device, dtype=torch.int64).contiguous()
         if pos.shape != (n_tokens,):
             raise ValueError(f"positions must have shape ({n_tokens},)")
-        return RopeSpec(_abi.ROPE_1D, self.freqs_cos.float().contiguous(), self.freqs_sin.float().contiguous(), pos)
+        return RopeSpec(_abi.ROPE_1D, tabs[0], tabs[1], pos)
 
     def forward(self, xq: torch.Tensor, xc: Optional[torch.Tensor] = None, mask=None,
                 positions: Optional[torch.Tensor] = None, ctx_positions: Optional[torch.Tensor] = None,
@@ -95,11 +116,11 @@ class PoMRoPE(PoM):
         N = T if self_mixing else xc.shape[1]
         cpos = ctx_positions if ctx_positions is not None else (positions if self_mixing else None)
         cpos_hw = ctx_positions_hw if ctx_positions_hw is not None else (positions_hw if self_mixing else None)
-        rope_q = self._rope_spec(T, positions, positions_hw, xq.device)
-        same = self_mixing and ctx_positions is None and ctx_positions_hw is None
+        rope_q = self._rope_spec(T, positions, positions_hw, xq.device, for_gate=True)
+        same = self_mixing and ctx_positions is None and ctx_positions_hw is None and self.n_sel_heads <= 1
         rope_c = rope_q if same else self._rope_spec(N, cpos, cpos_hw, xq.device)
         spec = LayerSpec(degree=self.order, mask_kind=kind, self_mixing=self_mixing, rope_ctx=rope_c, rope_qry=rope_q,
-                         shard=shard)
+                         shard=shard, n_sel_heads=self.n_sel_heads)
         y, _ = pom_layer(xq, xc, self.qc_proj.weight, self.se_bias, self.po_coeff, self.ag_proj.weight,
                          mask if kind == "keypad" else None, None, spec)
         return self._finish(y)

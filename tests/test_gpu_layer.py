@@ -14,7 +14,10 @@ LAYER_CASES = ["pom_none", "pom_causal", "pom_mask2d", "pom_cross", "pom_cross_m
                "rope2d_none", "rope2d_causal"]
 
 
-@pytest.mark.parametrize("name", LAYER_CASES)
+HEAD_CASES = ["pom_heads4_none", "pom_heads4_causal", "rope2d_heads4_none", "rope1d_heads4_causal"]
+
+
+@pytest.mark.parametrize("name", LAYER_CASES + HEAD_CASES)
 def test_fp32_layer_matches_reference_vectors(golden, name):
     case = golden[name]
     mod = make_cuda_module(case["cfg"], case["params"], torch.float32)
@@ -80,6 +83,34 @@ def test_bf16_fused_path_against_oracle(shape, coeff_scale):
     want_y, want_g = oracle_run(cfg, params, x, None, {}, gy)
     mod = make_cuda_module(cfg, params, torch.bfloat16)
     y, grads = cuda_run(mod, x, None, {}, gy, torch.bfloat16)
+    assert_status_clean()
+    assert_close(y, want_y, BF16_TOL, "y")
+    for k, w in want_g.items():
+        assert_close(grads[k], w, BF16_TOL, f"d_{k}")
+
+
+@pytest.mark.parametrize("mask", [None, "causal"])
+@pytest.mark.parametrize("rope", [None, "1d", "2d"])
+def test_bf16_multi_head_gating_against_oracle(mask, rope):
+    """n_sel_heads = 16, the setting of the reference's own benchmark scripts (bench_attn_vs_pom.py:94-97)."""
+    B, side, D, K, E, heads = 2, 16, 64, 2, 2, 16
+    N = side * side
+    params = O.init_params(D, K, E, n_sel_heads=heads, seed=9, coeff_scale=0.1)
+    g = torch.Generator().manual_seed(10)
+    params["se_bias"] = torch.randn(heads, generator=g) * 0.5
+    params = {k: O.bf16_round(v) for k, v in params.items()}
+    x = O.bf16_round(torch.randn(B, N, D, generator=g))
+    gy = O.bf16_round(torch.randn(B, N, D, generator=g))
+    cfg = dict(dim=D, degree=K, expand=E, heads=heads)
+    kw = {"mask": mask}
+    if rope == "1d":
+        cfg["rope"] = dict(two_d=False, max_seq_len=N)
+    elif rope == "2d":
+        cfg["rope"] = dict(two_d=True, max_h=side, max_w=side)
+        kw["positions_hw"] = torch.stack([torch.arange(N) // side, torch.arange(N) % side], 1)
+    want_y, want_g = oracle_run(cfg, params, x, None, kw, gy)
+    mod = make_cuda_module(cfg, params, torch.bfloat16)
+    y, grads = cuda_run(mod, x, None, kw, gy, torch.bfloat16)
     assert_status_clean()
     assert_close(y, want_y, BF16_TOL, "y")
     for k, w in want_g.items():
