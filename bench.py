@@ -227,9 +227,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="dit", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
-                    help="replay the step as a CUDA graph (auto: on for token-sharded multi-GPU runs, where launch "
-                         "latency would otherwise dominate)")
+    ap.add_argument("--graph", default="off", choices=["on", "off"],
+                    help="replay the whole fwd+bwd step as a CUDA graph instead of launching it from Python")
     ap.add_argument("--defer-weight-grad-reduce", action="store_true",
                     help="token-sharded runs: leave the parameter-gradient all-reduce to the caller (as a data-parallel "
                          "optimizer step would do) instead of doing it inside the layer")
@@ -243,6 +242,8 @@ def main():
         run_reference(args, w, rank)
         return
 
+    if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+        os.environ["NCCL_DEBUG"] = "WARN"  # keep stdout to the one JSON line
     import torch.distributed as dist
     from pom_b200 import _abi, ops
 
@@ -255,8 +256,20 @@ def main():
     if world > 1:
         from datetime import timedelta
 
-        # a short timeout turns a mismatched collective into an error instead of a ten-minute stall
-        dist.init_process_group("nccl", device_id=device, timeout=timedelta(seconds=180))
+        # a short timeout turns a mismatched collective into an error instead of a ten-minute stall.
+        # NCCL may print a version banner on stdout while the communicator comes up: point fd 1 at stderr
+        # for that moment so that stdout carries nothing but the JSON line.
+        sys.stdout.flush()
+        saved_fd = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=device, timeout=timedelta(seconds=180))
+            warm = torch.zeros(1, device=device)
+            dist.all_reduce(warm)
+            torch.cuda.synchronize()
+        finally:
+            os.dup2(saved_fd, 1)
+            os.close(saved_fd)
     args.warmup = max(args.warmup, 3)
 
     mod, host_sets, kw, tokens_local = build_case(w, rank, world, device)
@@ -283,7 +296,7 @@ def main():
     l0 = ops.launch_count()
     step(*dev_sets[0])
     launches_per_step = ops.launch_count() - l0
-    use_graph = args.graph == "on" or (args.graph == "auto" and w["shard"] == "token" and world > 1)
+    use_graph = args.graph == "on"
     graphs = []
     if use_graph:
         # one graph per input set; kernels, memsets and NCCL collectives of a whole fwd+bwd step are captured
