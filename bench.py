@@ -16,6 +16,9 @@ Workloads
                  (strong scaling; all-reduce of the (B, P) partial sums, weight-gradient all-reduce
                  inside the timed region).
   seq64k_causal  same, token-causal (all-gather of rank totals + local exclusive scan).
+  video          forward only: B=8, 16 frames x 256 tokens, D=1024, degree 2, expand 4, 12 layers of
+                 x += PoM.state_forward(x); x += W2 gelu(W1 x), state carried across frames; one step = all 16
+                 frames through all layers, replayed as one CUDA graph (metric: tokens/s through the stack).
 """
 import argparse
 import json
@@ -36,6 +39,8 @@ WORKLOADS = {
     "masked": dict(B=64, N=2048, D=1024, degree=3, expand=2, mask="keypad", rope=None, shard="batch"),
     "seq64k": dict(B=1, N=65536, D=1152, degree=2, expand=2, mask="none", rope="2d", shard="token"),
     "seq64k_causal": dict(B=1, N=65536, D=1152, degree=2, expand=2, mask="causal", rope="2d", shard="token"),
+    "video": dict(B=8, N=4096, D=1024, degree=2, expand=4, mask="block-causal", rope=None, shard="batch",
+                  frame=256, layers=12),
 }
 METRIC = "pom_layer_fwd_bwd_tokens_per_s"
 UNIT = "tokens/s"
@@ -108,6 +113,8 @@ def flops_per_step(w, valid_frac=1.0):
     """Algorithmic tensor work of one fwd+bwd step: 18 * M * D * P (projections 4+2 forward, 12 backward)."""
     M, D = w["B"] * w["N"], w["D"]
     P = w["expand"] * D
+    if "layers" in w:  # forward only: projections 6 M D P plus the 4 D feed-forward 16 M D^2, per layer
+        return w["layers"] * M * (6.0 * D * P + 16.0 * D * D)
     return 18.0 * M * D * P
 
 
@@ -120,6 +127,8 @@ def cpu_reference_tokens_per_s(w, steps, warmup, sample_tokens=4096):
 
     torch.set_num_threads(os.cpu_count() or 1)
     D, K, E = w["D"], w["degree"], w["expand"]
+    if "layers" in w:
+        return cpu_reference_video(w, steps, warmup, O)
     if w["B"] > 1:
         N = w["N"]
         B = max(1, sample_tokens // N)
@@ -158,6 +167,42 @@ def cpu_reference_tokens_per_s(w, steps, warmup, sample_tokens=4096):
     return (B * N) / sec, sec, f"B={B}, N={N} of the workload (fp32, {torch.get_num_threads()} threads), median of {steps}"
 
 
+def cpu_reference_video(w, steps, warmup, O):
+    """Frame loop of the oracle (state_forward + GELU feed-forward) for ONE sample and TWO layers; the
+    tokens/s of the full 12-layer stack is the measured figure divided by layers / 2."""
+    D, K, E, L = w["D"], w["degree"], w["expand"], w["frame"]
+    sample_layers = 2
+    g = torch.Generator().manual_seed(0)
+    layers = []
+    for i in range(sample_layers):
+        p = O.init_params(D, K, E, seed=i)
+        w1 = (torch.rand(4 * D, D, generator=g) * 2 - 1) / D ** 0.5
+        w2 = (torch.rand(D, 4 * D, generator=g) * 2 - 1) / (4 * D) ** 0.5
+        layers.append((O.OraclePoM(p, K, E), w1, w2))
+    x = torch.randn(1, w["N"], D, generator=g)
+
+    def step():
+        states = [None] * sample_layers
+        with torch.no_grad():
+            for f in range(w["N"] // L):
+                h = x[:, f * L:(f + 1) * L]
+                for i, (m, w1, w2) in enumerate(layers):
+                    y, states[i] = m.state_forward(h, None, states[i])
+                    h = h + y
+                    h = h + torch.nn.functional.gelu(h @ w1.t()) @ w2.t()
+
+    for _ in range(warmup):
+        step()
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        step()
+        times.append(time.perf_counter() - t0)
+    sec = statistics.median(times) * (w["layers"] / sample_layers)
+    return w["N"] / sec, sec, (f"B=1, {sample_layers} of {w['layers']} layers timed and scaled by {w['layers'] // sample_layers} "
+                               f"(fp32, {torch.get_num_threads()} threads), median of {steps}")
+
+
 def run_reference(args, w, rank):
     if rank != 0:
         return
@@ -182,6 +227,16 @@ def build_case(w, rank, world, device):
 
     D, K, E = w["D"], w["degree"], w["expand"]
     torch.manual_seed(0)
+    if "layers" in w:
+        from pom_b200.stack import PoMStack
+
+        mod = PoMStack(D, K, E, w["layers"]).to(device)
+        for p in mod.parameters():
+            p.data = p.data.to(torch.bfloat16)
+        gen = torch.Generator().manual_seed(1000 + rank)
+        host_sets = [(torch.randn(w["B"], w["N"], D, generator=gen).to(torch.bfloat16).pin_memory(), None)
+                     for _ in range(3)]
+        return mod, host_sets, {}, w["B"] * w["N"]
     if w["rope"] == "2d":
         side = int(w["N"] ** 0.5)
         mod = PoMRoPE(D, K, E, 1, 1, rope_2d=True, max_h=side, max_w=side)
@@ -232,8 +287,11 @@ def main():
     ap.add_argument("--defer-weight-grad-reduce", action="store_true",
                     help="token-sharded runs: leave the parameter-gradient all-reduce to the caller (as a data-parallel "
                          "optimizer step would do) instead of doing it inside the layer")
+    ap.add_argument("--tokens", type=int, default=0, help="override the workload's tokens per sample (N)")
     args = ap.parse_args()
-    w = WORKLOADS[args.workload]
+    w = dict(WORKLOADS[args.workload])
+    if args.tokens:
+        w["N"] = args.tokens
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -276,13 +334,28 @@ def main():
     if args.defer_weight_grad_reduce and "shard" in kw:
         kw["shard"].reduce_weight_grads = False
     params = list(mod.parameters())
-    dev_sets = [(x.to(device), gy.to(device)) for x, gy in host_sets]
+    video = "layers" in w
+    if video:
+        L = w["frame"]
+        split = lambda x: [x[:, f * L:(f + 1) * L].contiguous() for f in range(w["N"] // L)]
+        dev_sets = [(split(x.to(device)), None) for x, _ in host_sets]
+        if args.graph == "off" and "--graph" not in sys.argv:
+            args.graph = "on"  # the frame loop is launch-bound from Python; the graph is the product path here
 
-    def step(x, gy):
-        xr = x.requires_grad_(True)
-        y = mod(xr, **kw)
-        grads = torch.autograd.grad(y, [xr] + params, gy)
-        return y, grads
+        def step(frames, _):
+            states, outs = None, []
+            for f in frames:
+                y, states = mod.frame_forward(f, states)
+                outs.append(y)
+            return outs[-1], outs
+    else:
+        dev_sets = [(x.to(device), gy.to(device)) for x, gy in host_sets]
+
+        def step(x, gy):
+            xr = x.requires_grad_(True)
+            y = mod(xr, **kw)
+            grads = torch.autograd.grad(y, [xr] + params, gy)
+            return y, grads
 
     def sync_all():
         if world > 1:
@@ -343,6 +416,10 @@ def main():
     def e2e_step(i):
         hx, hg = host_sets[i % len(host_sets)]
         x = hx.to(device, non_blocking=True)
+        if video:
+            _, outs = step(split(x), None)
+            y_host.copy_(torch.cat(outs, dim=1), non_blocking=True)
+            return
         gy = hg.to(device, non_blocking=True)
         y, grads = step(x, gy)
         y_host.copy_(y, non_blocking=True)
@@ -361,13 +438,13 @@ def main():
     if world > 1:
         dist.all_reduce(ms_e2e, op=dist.ReduceOp.MAX)
     e2e_val = tokens_all / (ms_e2e.item() / e2e_steps * 1e-3)
-    h2d = 2 * xs.numel() * xs.element_size()
-    d2h = 2 * xs.numel() * xs.element_size()
+    h2d = (1 if video else 2) * xs.numel() * xs.element_size()
+    d2h = (1 if video else 2) * xs.numel() * xs.element_size()
 
     # ---- roofline of the tensor-core kernel: per-launch CUDA-event timing of one instrumented step
     peaks = measured_peaks()
     # every rank runs the instrumented step (a token-sharded layer contains collectives); rank 0 reports
-    roof = gemm_roofline(mod, dev_sets, kw, w, world, peaks)
+    roof = gemm_roofline(step, dev_sets, peaks, reps=2 if video else 5)
     sync_all()
 
     cpu = None
@@ -378,7 +455,7 @@ def main():
     if rank == 0:
         status = _abi.read_status(device)
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "metric": "pom_stack_fwd_tokens_per_s" if video else METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong" if w["shard"] == "token" else "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
@@ -406,7 +483,7 @@ def main():
         dist.destroy_process_group()
 
 
-def gemm_roofline(mod, dev_sets, kw, w, world, peaks):
+def gemm_roofline(step, dev_sets, peaks, reps=5):
     """Times every tcgen05 GEMM launch of one step with CUDA events (on the launching stream) by wrapping the
     binding's GEMM entry points, and reports the launch that dominates the step."""
     from pom_b200 import ops
@@ -437,14 +514,9 @@ def gemm_roofline(mod, dev_sets, kw, w, world, peaks):
     wrap("ctx_gemm", lambda x, wpo, c, **_: (2.0 * x.shape[0] * x.shape[1] * x.shape[2] * wpo.shape[0], "ctx_gemm"))
     wrap("gate_gemm", lambda x, wse, b, h, **_: (2.0 * x.shape[0] * x.shape[1] * x.shape[2] * wse.shape[0], "gate_gemm"))
     wrap("gate_bwd_gemm", lambda dy, wo, *a, **_: (2.0 * dy.shape[0] * dy.shape[1] * dy.shape[2] * wo.shape[1], "gate_bwd_gemm"))
-    params = list(mod.parameters())
     try:
-        reps = 5
         for i in range(reps):
-            x, gy = dev_sets[i % len(dev_sets)]
-            xr = x.requires_grad_(True)
-            y = mod(xr, **kw)
-            torch.autograd.grad(y, [xr] + params, gy)
+            step(*dev_sets[i % len(dev_sets)])
         torch.cuda.synchronize()
     finally:
         for n, fn in originals.items():

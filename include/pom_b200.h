@@ -98,6 +98,10 @@ typedef struct pom_gemm_args {
   int32_t out_mode;
   int32_t split_k;
   float alpha;
+  /* bf16 output only (the feed-forward block of the README's layer stack, README.md:28-35): */
+  int32_t act;          /* 0 none, 1 exact GELU applied to alpha * sum */
+  const void* residual; /* bf16 (batches*M, N) row stride ldr, added after the activation; NULL = none */
+  int64_t ldr;
 } pom_gemm_args;
 int pom_gemm_bf16(const pom_gemm_args* a, int* status, void* stream);
 

@@ -47,6 +47,7 @@ class GemmArgs(C.Structure):
         ("lda", C.c_int64), ("ldb", C.c_int64), ("ldc", C.c_int64),
         ("batches", C.c_int32), ("a_mn_major", C.c_int32), ("b_mn_major", C.c_int32),
         ("out_mode", C.c_int32), ("split_k", C.c_int32), ("alpha", C.c_float),
+        ("act", C.c_int32), ("residual", C.c_void_p), ("ldr", C.c_int64),
     ]
 
 

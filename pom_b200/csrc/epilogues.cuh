@@ -101,6 +101,9 @@ struct EpiStore {
     long long batch_stride;  // elements between batches
     int mode;                // 0: bf16 store, 1: fp32 store, 2: fp32 atomic add (split-K)
     float alpha;
+    int act;                 // bf16 store only: 0 none, 1 exact GELU 0.5 x (1 + erf(x / sqrt 2))
+    const __nv_bfloat16* residual;  // bf16 store only: added after the activation (row stride ldr), or null
+    long long ldr;
   };
   static constexpr int kSmemBytes = 0;
 
@@ -129,6 +132,30 @@ struct EpiStore {
       }
       if (p.mode == 0) {
         if (t.rows_valid <= 0) continue;
+        if (p.act == 1) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0.5f * v[i] * (1.f + erff(v[i] * 0.70710678118654752f));
+        }
+        if (p.residual && row_ok) {
+          const __nv_bfloat16* r = p.residual + (static_cast<long long>(t.b) * g.rows_per_batch + t.row0 + row) * p.ldr + col;
+          const int left = g.n_cols - col;
+          if (left >= 32 && (reinterpret_cast<uintptr_t>(r) & 15) == 0) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint4 q = __ldg(reinterpret_cast<const uint4*>(r) + j);
+              const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                v[8 * j + 2 * e] += __uint_as_float(w[e] << 16);
+                v[8 * j + 2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (i < left) v[i] += __bfloat162float(r[i]);
+          }
+        }
         uint32_t pk[16];
         pack32(v, pk);
         store_block<1>(flip ? io.buf1 : io.buf0, &maps.out0, pk, lane, col, t.row0 + quarter * 32, t.b);

@@ -377,6 +377,11 @@ int pom_gemm_bf16(const pom_gemm_args* a, int* status, void* stream) {
   ep.batch_stride = a->M * a->ldc;
   ep.mode = a->out_mode;
   ep.alpha = a->alpha;
+  ep.act = a->act;
+  ep.residual = static_cast<const __nv_bfloat16*>(a->residual);
+  ep.ldr = a->ldr;
+  if ((a->act || a->residual) && a->out_mode != POM_OUT_BF16) return POM_ERR_UNSUPPORTED;
+  if (a->act < 0 || a->act > 1 || (a->residual && a->ldr < a->N)) return POM_ERR_UNSUPPORTED;
   EpiMaps maps{};
   if (a->out_mode == POM_OUT_BF16 && (rc = make_io_map(&maps.out0, a->C, a->N, a->M, a->batches, a->ldc))) return rc;
   return run_plan_any_major<EpiStore>(plan, o, split, maps, ep, status, static_cast<cudaStream_t>(stream));

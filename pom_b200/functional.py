@@ -116,7 +116,7 @@ class _PoMLayer(torch.autograd.Function):
     value per head (Wse is (heads, D)) and multiplies all channels of its head (pom/pom.py:119-122)."""
 
     @staticmethod
-    def forward(ctx, xq, xc, w_qc, se_bias, coeff, w_ag, mask, h_past, spec: LayerSpec):
+    def forward(ctx, xq, xc, w_qc, se_bias, coeff, w_ag, mask, h_past, spec: LayerSpec, residual=None):
         _check_inputs(xq, xc, w_qc, w_ag, coeff, spec)
         B, T, D = xq.shape
         N = xc.shape[1]
@@ -185,8 +185,12 @@ class _PoMLayer(torch.autograd.Function):
             sh = ops.select_heads_fwd(s32, Hc if causal else H, xq.dtype)
         else:
             sh = ops.select_fwd(z, bias32, Hc if causal else H, rope=spec.rope_qry)
-        y = ops.gemm(sh.view(B * T, P), w_ag).view(B, T, D)
+        if residual is not None and not bf16:
+            raise NotImplementedError("the fused residual add of the output projection is a bf16 feature")
+        y = ops.gemm(sh.view(B * T, P), w_ag,
+                     residual=None if residual is None else residual.contiguous().view(B * T, D)).view(B, T, D)
 
+        ctx.has_residual = residual is not None
         ctx.spec = spec
         ctx.fused = fused
         ctx.dims = (B, T, N, D, P, K, S, heads, n_glob, offset)
@@ -292,7 +296,7 @@ class _PoMLayer(torch.autograd.Function):
         else:
             g_qc, g_ag = _like_param(d_wqc, p_qc), _like_param(d_wag, p_ag)
             g_bias, g_coeff = _like_param(d_bias, p_bias), _like_param(d_coeff, p_coeff)
-        return (dxq, dxc, g_qc, g_bias, g_coeff, g_ag, None, d_hpast, None)
+        return (dxq, dxc, g_qc, g_bias, g_coeff, g_ag, None, d_hpast, None, dy if ctx.has_residual else None)
 
 
 _ones_cache = {}
@@ -306,8 +310,10 @@ def _ones(b: int, n: int, device) -> torch.Tensor:
     return _ones_cache[key]
 
 
-def pom_layer(xq, xc, w_qc, se_bias, coeff, w_ag, mask=None, h_past=None, spec: Optional[LayerSpec] = None):
-    y, h = _PoMLayer.apply(xq, xc if xc is not None else xq, w_qc, se_bias, coeff, w_ag, mask, h_past, spec)
+def pom_layer(xq, xc, w_qc, se_bias, coeff, w_ag, mask=None, h_past=None, spec: Optional[LayerSpec] = None,
+              residual=None):
+    """Whole layer; ``residual`` (B, T, D), bf16 only, is added to the output inside the output projection."""
+    y, h = _PoMLayer.apply(xq, xc if xc is not None else xq, w_qc, se_bias, coeff, w_ag, mask, h_past, spec, residual)
     return y, h
 
 

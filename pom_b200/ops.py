@@ -76,12 +76,14 @@ def _rope_c(spec: Optional[RopeSpec]) -> Rope:
 # ---------------------------------------------------------------------------- GEMM
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
          out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
-         accumulate: bool = False, split_k: int = 0, alpha: float = 1.0) -> torch.Tensor:
+         accumulate: bool = False, split_k: int = 0, alpha: float = 1.0, act: Optional[str] = None,
+         residual: Optional[torch.Tensor] = None) -> torch.Tensor:
     """C[m, n] = alpha * sum_k A[m, k] * B[n, k].
 
     ``a`` is (M, K) — or (K, M) when ``a_mn`` — and ``b`` is (N, K) — or (K, N) when ``b_mn``;
     both row-major with a contiguous last dimension.  bf16 inputs run on the tcgen05 kernel,
-    fp32 inputs on the SIMT kernel.  ``accumulate`` adds into a fp32 ``out``.
+    fp32 inputs on the SIMT kernel.  ``accumulate`` adds into a fp32 ``out``.  For bf16 outputs the epilogue can
+    apply ``act="gelu"`` and add a bf16 ``residual`` of the output's shape.
     """
     dev = _require_cuda(a, b, out)
     if a.dtype != b.dtype:
@@ -109,6 +111,15 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     g.out_mode = _abi.OUT_F32_ACCUM if accumulate else (_abi.OUT_BF16 if out.dtype == torch.bfloat16 else _abi.OUT_F32)
     g.split_k = split_k if accumulate else 1
     g.alpha = alpha
+    if act not in (None, "gelu"):
+        raise ValueError("act must be None or 'gelu'")
+    g.act = 1 if act == "gelu" else 0
+    if residual is not None:
+        if residual.shape != (M, N) or residual.dtype != torch.bfloat16:
+            raise ValueError("residual must be a bfloat16 tensor of the output's shape")
+        g.residual, g.ldr = ptr(residual), _row_stride(residual)
+    if (g.act or residual is not None) and not (is_bf16 and out.dtype == torch.bfloat16):
+        raise TypeError("activation / residual epilogue needs bfloat16 operands and output")
     L = _abi.lib()
     if is_bf16:
         _abi.check(L.pom_gemm_bf16(C.byref(g), ptr(_abi.status_word(dev)), _abi.stream_ptr()), "pom_gemm_bf16")

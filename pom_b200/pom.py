@@ -72,11 +72,13 @@ class PoM(nn.Module):
         return self._finish(y)
 
     def state_forward(self, xq: torch.Tensor, xc: Optional[torch.Tensor] = None,
-                      state: Optional[Dict[str, Any]] = None) -> Tuple[torch.Tensor, Dict[str, Any]]:
+                      state: Optional[Dict[str, Any]] = None,
+                      residual: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, Dict[str, Any]]:
         """Incremental forward with a running-mean state {'h': (B, 1, P) fp32, 'n': calls so far}.
 
         As in the reference (pom/pom.py:251-262) the counter advances by one per call, so every
-        call weighs equally whatever its token count.
+        call weighs equally whatever its token count.  ``residual`` (extension, bf16): a (B, T, D) tensor added
+        to the output inside the output projection's epilogue.
         """
         spec = LayerSpec(degree=self.order, self_mixing=(xc is None or xc is xq), want_state=True,
                          n_sel_heads=self.n_sel_heads)
@@ -92,7 +94,8 @@ class PoM(nn.Module):
             spec.n_past = float(n_past)
         else:
             h_past = None
-        y, h = pom_layer(xq, xc, self.qc_proj.weight, self.se_bias, self.po_coeff, self.ag_proj.weight, None, h_past, spec)
+        y, h = pom_layer(xq, xc, self.qc_proj.weight, self.se_bias, self.po_coeff, self.ag_proj.weight, None, h_past,
+                         spec, residual)
         return self._finish(y), {"h": h, "n": n_past + 1}
 
     @torch.no_grad()

@@ -68,3 +68,21 @@ def test_fp32_gemm(M, N, K, a_mn, b_mn):
     B = torch.randn(N, K, device="cuda")
     out = ops.gemm(A.t().contiguous() if a_mn else A, B.t().contiguous() if b_mn else B, a_mn=a_mn, b_mn=b_mn)
     assert _rel(out, A.double() @ B.double().t()) < 1e-6
+
+
+def test_bf16_gemm_gelu_and_residual_epilogue():
+    """The feed-forward epilogue options: exact GELU, then a bf16 residual add."""
+    from pom_b200 import ops
+
+    torch.manual_seed(3)
+    M, N, K = 520, 392, 264
+    A = torch.randn(M, K, device="cuda").bfloat16()
+    B = (torch.randn(N, K, device="cuda") * 0.1).bfloat16()
+    R = torch.randn(M, N, device="cuda").bfloat16()
+    acc = A.float() @ B.float().t()
+    got = ops.gemm(A, B, act="gelu")
+    assert _rel(got, torch.nn.functional.gelu(acc)) < 4e-3
+    got = ops.gemm(A, B, residual=R)
+    assert _rel(got, acc + R.float()) < 4e-3
+    got = ops.gemm(A, B, act="gelu", residual=R)
+    assert _rel(got, torch.nn.functional.gelu(acc) + R.float()) < 4e-3

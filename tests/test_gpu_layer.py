@@ -197,6 +197,37 @@ def test_block_causal_video_stack_frame_loop():
     assert_close(got, want, 3 * BF16_TOL, "video stack output")  # bf16 residual stream over 3 layers x 4 frames
 
 
+def test_pom_stack_matches_oracle_frame_loop():
+    """PoMStack (fused residual / GELU epilogues, state carried across frames) against the oracle's frame loop."""
+    from pom_b200.stack import PoMStack
+
+    B, F, L, D, K, E, layers = 2, 4, 64, 64, 2, 4, 3
+    torch.manual_seed(11)
+    stack = PoMStack(D, K, E, layers)
+    with torch.no_grad():
+        for m in stack.mixers:
+            m.po_coeff.copy_(torch.randn_like(m.po_coeff) * 0.1)
+        for p in stack.parameters():
+            p.copy_(O.bf16_round(p))
+    x = O.bf16_round(torch.randn(B, F * L, D))
+    oracles = [O.OraclePoM({k: v.detach().clone() for k, v in m.state_dict().items()}, K, E) for m in stack.mixers]
+    states, outs = [None] * layers, []
+    with torch.no_grad():
+        for f in range(F):
+            h = x[:, f * L:(f + 1) * L]
+            for i in range(layers):
+                y, states[i] = oracles[i].state_forward(h, None, states[i])
+                h = h + y
+                h = h + torch.nn.functional.gelu(h @ stack.ffn_in[i].weight.t()) @ stack.ffn_out[i].weight.t()
+            outs.append(h)
+    want = torch.cat(outs, 1)
+    stack = stack.cuda()
+    for p in stack.parameters():
+        p.data = p.data.bfloat16()
+    got = stack(x.cuda().bfloat16(), L)
+    assert_close(got, want, 3 * BF16_TOL, "stack output")  # bf16 residual stream over 3 layers x 4 frames
+
+
 def test_token_causal_long_sequence_against_linear_time_oracle():
     """Token-causal forward at a length where the reference's N x N mask would be impractical."""
     cfg, params, x, gy = _seeded_case(1, 8192, 64, 2, 2, seed=6, coeff_scale=0.1, bias_scale=0.3)
