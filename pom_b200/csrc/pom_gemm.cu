@@ -198,7 +198,7 @@ struct TilePlan {
 
 // Operand bytes pulled from L2 per output element are proportional to (rowsA + rowsB) / (128 * BN)
 // with rowsB = BN (one CTA) or BN/2 (pair); weigh that by the padded width and take the cheapest.
-TilePlan pick_plan(const Operands& o, bool allow_192) {
+TilePlan pick_plan(const Operands& o, bool allow_192, bool splittable = false) {
   const int mode = g_gemm_mode.load(std::memory_order_relaxed);
   const long long m_tiles = 1ll * o.batches * ceil_div(o.M, kBM);
   TilePlan best{false, 128};
@@ -212,7 +212,11 @@ TilePlan pick_plan(const Operands& o, bool allow_192) {
       if (bn == 192 && (!allow_192 || (pair && o.b_mn))) continue;
       if (o.N <= 128 && bn != 128) continue;
       const double padded = static_cast<double>(ceil_div(o.N, bn) * bn);
-      const double cost = padded * (128.0 + (pair ? bn / 2 : bn)) / bn;
+      double cost = padded * (128.0 + (pair ? bn / 2 : bn)) / bn;
+      // fewer work units than SMs (or SM pairs): the idle ones are paid for too (split-K GEMMs fill them)
+      const long long units = (pair ? (m_tiles + 1) / 2 : m_tiles) * ceil_div(o.N, bn);
+      const int slots = pair ? sm_count() / 2 : sm_count();
+      if (!splittable && units < slots) cost *= static_cast<double>(slots) / static_cast<double>(units);
       if (best_cost < 0 || cost < best_cost - 1e-9) {
         best_cost = cost;
         best = TilePlan{pair != 0, bn};
@@ -369,7 +373,7 @@ int pom_gemm_bf16(const pom_gemm_args* a, int* status, void* stream) {
     if (split > 1) return POM_ERR_UNSUPPORTED;
     split = 1;
   }
-  const TilePlan plan = pick_plan(o, true);
+  const TilePlan plan = pick_plan(o, true, a->out_mode == POM_OUT_F32_ACCUM && a->split_k == 0);
   if (split == 0) split = pick_split(plan_units(o, plan), ceil_div(a->K, kBK), plan.pair ? sm_count() / 2 : sm_count());
   EpiStore::Params ep;
   ep.C = a->C;
