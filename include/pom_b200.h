@@ -179,6 +179,8 @@ int pom_gate_bwd_gemm(const pom_gate_bwd_args* a, int* status, void* stream);
  *   poly[b,n,:] = R_n · polynomial(act(x[b,n,:]))
  *   causal == 0 : out[b, :]    = sum_n w[b,n] * poly[b,n,:]             -> `partial` then reduce
  *   causal == 1 : out[b, n, :] = (carry[b,:] + sum_{m<=n} poly[b,m,:]) / (n + 1 + token_offset)
+ *   causal == 2 : out[b, n, :] = poly[b,n,:]     (per-token features, no reduction; `partial` unused; the
+ *                 input of the (B, M, N)-mask product, reference pom/pom.py:41-45, 98-99)
  * Non-causal: the kernel writes per-chunk sums into partial (B, chunks, P); call
  * pom_reduce_partials.  Causal: `partial` (B, chunks, P) is scratch; out is (B, N, P) of dtype.
  * chunks = pom_agg_chunks(N).
@@ -233,6 +235,7 @@ int pom_poly_agg_mean_noalloc(const pom_agg_args* a, const float* denom, float s
  *                 (either may be NULL = 1); `scale` multiplies everything (1/N for a plain mean).
  *   causal == 1 : dout (B, N, P) dtype; `carry` (B, P) fp32 optional = suffix sum from later shards;
  *                 `total` optional output (B, P): this shard's sum of dout[n]/(n+1+offset).
+ *   causal == 2 : dout (B, N, P) dtype is the gradient of each token's own features (no suffix sum).
  *                 phase == 1 stops after the totals (used to obtain `total` before the cross-shard
  *                 exchange that produces `carry`); phase == 0 runs everything.
  * Outputs: dx (B, N, P) dtype row stride ld_dx; dcoeff_partial (B*chunks, P, K) fp32, to be
@@ -273,6 +276,8 @@ typedef struct pom_select_args {
   int32_t B, T, P;
   int32_t dtype, h_per_token;
   int32_t activated;   /* nonzero: z already holds the gate s (bias and hardsigmoid are skipped) */
+  const float* row_denom; /* optional, per-token H only: H[b,t,:] is divided by row_denom[b*T+t] (a zero divisor
+                             makes the row 0); the row sums of a (B, M, N) mask (reference pom/pom.py:41-45) */
   pom_rope rope;
 } pom_select_args;
 int pom_select_fwd(const pom_select_args* a, void* stream);
@@ -293,6 +298,7 @@ typedef struct pom_select_bwd_args {
   int32_t B, T, P;
   int32_t dtype, h_per_token;
   int32_t activated;   /* as in pom_select_args; dz is then the gradient of s itself */
+  const float* row_denom; /* as in pom_select_args; dh_tok is then the gradient of the un-divided H */
   pom_rope rope;
 } pom_select_bwd_args;
 int pom_select_bwd(const pom_select_bwd_args* a, void* stream);

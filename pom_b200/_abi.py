@@ -110,6 +110,7 @@ class SelectArgs(C.Structure):
         ("ld_z", C.c_int64), ("ld_h", C.c_int64), ("ld_sh", C.c_int64),
         ("B", C.c_int32), ("T", C.c_int32), ("P", C.c_int32),
         ("dtype", C.c_int32), ("h_per_token", C.c_int32), ("activated", C.c_int32),
+        ("row_denom", C.c_void_p),
         ("rope", Rope),
     ]
 
@@ -121,6 +122,7 @@ class SelectBwdArgs(C.Structure):
         ("ld_dsh", C.c_int64), ("ld_z", C.c_int64), ("ld_h", C.c_int64), ("ld_dz", C.c_int64), ("ld_dh", C.c_int64),
         ("B", C.c_int32), ("T", C.c_int32), ("P", C.c_int32),
         ("dtype", C.c_int32), ("h_per_token", C.c_int32), ("activated", C.c_int32),
+        ("row_denom", C.c_void_p),
         ("rope", Rope),
     ]
 

@@ -182,6 +182,7 @@ struct AggDev {
   void* out;
   long long ldx, ld_out, token_offset;
   int B, N, P, K, chunks;
+  int per_token;  // PREFIX kernel only: write each token's own (rotated) features, no running sum
   pom_rope rope;
 };
 
@@ -203,8 +204,8 @@ __global__ void __launch_bounds__(128) agg_fwd_kernel(const AggDev a) {
   float acc1[VEC], acc2[VEC];
 #pragma unroll
   for (int e = 0; e < VEC; ++e) {
-    acc1[e] = PREFIX ? part[m.p1 + e] : 0.f;
-    acc2[e] = (PREFIX && rope) ? part[m.p2 + e] : 0.f;
+    acc1[e] = (PREFIX && !a.per_token) ? part[m.p1 + e] : 0.f;
+    acc2[e] = (PREFIX && rope && !a.per_token) ? part[m.p2 + e] : 0.f;
   }
   const int n0 = c * kChunk, n1 = min(a.N, n0 + kChunk);
   for (int nb = n0; nb < n1; nb += kTB) {
@@ -223,6 +224,10 @@ __global__ void __launch_bounds__(128) agg_fwd_kernel(const AggDev a) {
     for (int q = 0; q < kTB; ++q) {
       const int n = nb + q;
       if (n >= n1) break;
+      if (PREFIX && a.per_token) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) acc1[e] = acc2[e] = 0.f;
+      }
 #pragma unroll
       for (int e = 0; e < VEC; ++e) {
         const float f1 = poly_reg<KR>(pom_act(x1[q][e]), cf.c1[e]);
@@ -235,7 +240,7 @@ __global__ void __launch_bounds__(128) agg_fwd_kernel(const AggDev a) {
         }
       }
       if (PREFIX) {
-        const float inv = 1.f / static_cast<float>(a.token_offset + n + 1);
+        const float inv = a.per_token ? 1.f : 1.f / static_cast<float>(a.token_offset + n + 1);
         float o[VEC];
 #pragma unroll
         for (int e = 0; e < VEC; ++e) o[e] = acc1[e] * inv;
@@ -337,6 +342,7 @@ struct AggBwdDev {
   long long ldx, ld_dx, ld_dout, token_offset;
   float scale;
   int B, N, P, K, chunks;
+  int per_token;  // CAUSAL kernel only: dout[n] is the gradient of token n's own features (no suffix sum)
   pom_rope rope;
 };
 
@@ -390,8 +396,8 @@ __global__ void __launch_bounds__(128) agg_bwd_kernel(const AggBwdDev a) {
   for (int e = 0; e < VEC; ++e) {
     if (CAUSAL) {
       const float* part = a.partial + (static_cast<long long>(b) * a.chunks + c) * a.P;
-      g1[e] = part[m.p1 + e];
-      g2[e] = rope ? part[m.p2 + e] : 0.f;
+      g1[e] = a.per_token ? 0.f : part[m.p1 + e];
+      g2[e] = (rope && !a.per_token) ? part[m.p2 + e] : 0.f;
     } else {
       g1[e] = a.dH[static_cast<long long>(b) * a.P + m.p1 + e];
       g2[e] = rope ? a.dH[static_cast<long long>(b) * a.P + m.p2 + e] : 0.f;
@@ -435,11 +441,11 @@ __global__ void __launch_bounds__(128) agg_bwd_kernel(const AggBwdDev a) {
       if (i >= cnt) break;
       const int n = CAUSAL ? (n1 - 1 - i) : (n0 + i);
       if (CAUSAL) {
-        const float inv = 1.f / static_cast<float>(a.token_offset + n + 1);
+        const float inv = a.per_token ? 1.f : 1.f / static_cast<float>(a.token_offset + n + 1);
 #pragma unroll
         for (int e = 0; e < VEC; ++e) {
-          g1[e] = fmaf(go1[q][e], inv, g1[e]);
-          if (rope) g2[e] = fmaf(go2[q][e], inv, g2[e]);
+          g1[e] = fmaf(go1[q][e], inv, a.per_token ? 0.f : g1[e]);
+          if (rope) g2[e] = fmaf(go2[q][e], inv, a.per_token ? 0.f : g2[e]);
         }
       }
       float o1[VEC], o2[VEC];
@@ -499,6 +505,7 @@ struct SelDev {
   void* dh_tok;
   long long ld_z, ld_h, ld_sh, ld_dsh, ld_dz, ld_dh;
   int B, T, P, chunks, h_per_token, activated;
+  const float* row_denom;  // per-token H only: H[b,t,:] is divided by row_denom[b*T + t] (0 -> the row counts as 0)
   pom_rope rope;
 };
 
@@ -530,6 +537,9 @@ __global__ void __launch_bounds__(128) select_kernel(const SelDev a) {
   constexpr int TB = 2;
   for (int tb = t0; tb < t1; tb += TB) {
     float z1[TB][VEC], z2[TB][VEC], cs[TB][VEC], sn[TB][VEC], h1[TB][VEC], h2[TB][VEC], g1[TB][VEC], g2[TB][VEC];
+    float rs[TB];
+#pragma unroll
+    for (int q = 0; q < TB; ++q) rs[q] = 1.f;
 #pragma unroll
     for (int q = 0; q < TB; ++q) {
       const int t = min(tb + q, t1 - 1);
@@ -542,6 +552,12 @@ __global__ void __launch_bounds__(128) select_kernel(const SelDev a) {
         const T* __restrict__ H = static_cast<const T*>(a.H) + (rowb + t) * a.ld_h;
         Vec<T, VEC>::ld(H + m.p1, h1[q]);
         if (rope) Vec<T, VEC>::ld(H + m.p2, h2[q]);
+        if (a.row_denom) {
+          const float dn = __ldg(a.row_denom + rowb + t);
+          rs[q] = dn != 0.f ? 1.f / dn : 0.f;
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) h1[q][e] *= rs[q], h2[q][e] = rope ? h2[q][e] * rs[q] : 0.f;
+        }
       } else {
 #pragma unroll
         for (int e = 0; e < VEC; ++e) h1[q][e] = hb1[e], h2[q][e] = hb2[e];
@@ -608,6 +624,8 @@ __global__ void __launch_bounds__(128) select_kernel(const SelDev a) {
         if (rope) Vec<T, VEC>::st(dz + m.p2, o2);
         if (a.h_per_token) {
           T* __restrict__ dh = static_cast<T*>(a.dh_tok) + (rowb + t) * a.ld_dh;
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) dh1[e] *= rs[q], dh2[e] *= rs[q];  // gradient of the un-normalised H
           Vec<T, VEC>::st(dh + m.p1, dh1);
           if (rope) Vec<T, VEC>::st(dh + m.p2, dh2);
         }
@@ -833,7 +851,8 @@ int pom_reduce_partials(const float* partial, float* out, const float* denom, fl
 }
 
 int pom_poly_agg_fwd(const pom_agg_args* a, void* stream) {
-  if (!a || !a->x || !a->coeff || !a->partial) return POM_ERR_NULL;
+  if (!a || !a->x || !a->coeff || (!a->partial && a->causal != 2)) return POM_ERR_NULL;
+  if (a->causal < 0 || a->causal > 2) return POM_ERR_UNSUPPORTED;
   if (a->B <= 0 || a->N <= 0 || a->P <= 0 || a->K < 1) return POM_ERR_BAD_SHAPE;
   if (a->K > kMaxDegree) return POM_ERR_K_TOO_LARGE;
   if (a->B > 65535 || pom_agg_chunks(a->N) > 65535) return POM_ERR_TOO_LARGE;
@@ -857,22 +876,25 @@ int pom_poly_agg_fwd(const pom_agg_args* a, void* stream) {
   d.P = a->P;
   d.K = a->K;
   d.chunks = pom_agg_chunks(a->N);
+  d.per_token = a->causal == 2;
   d.rope = a->rope;
   const int vec = pick_vec(a->P, a->rope, a->dtype, a->K, {a->ldx, a->causal ? a->ld_out : 0},
                            {a->x, a->causal ? a->out : nullptr});
   const WalkLaunch wl = walk_launch(a->P, a->rope.kind, vec, d.chunks, a->B);
   const bool has_rope = a->rope.kind != POM_ROPE_NONE;
+  if (a->causal != 2) {  // per-token features (causal == 2) need neither the sums nor the scan
 #define CALL_SUM(T, V, KR)                                                                    \
   if (has_rope) agg_fwd_kernel<T, V, KR, false, true><<<wl.grid, wl.block, 0, st>>>(d);        \
   else agg_fwd_kernel<T, V, KR, false, false><<<wl.grid, wl.block, 0, st>>>(d)
-  POM_DISPATCH_K(a->dtype, vec, a->K, CALL_SUM);
+    POM_DISPATCH_K(a->dtype, vec, a->K, CALL_SUM);
 #undef CALL_SUM
-  count_launch();
-  rc = check_launch();
-  if (rc || !a->causal) return rc;
-  dim3 sgrid(static_cast<unsigned>(ceil_div(a->P, 128)), static_cast<unsigned>(a->B));
-  chunk_scan_kernel<<<sgrid, 128, 0, st>>>(a->partial, a->carry, a->total, d.chunks, a->P, 0);
-  count_launch();
+    count_launch();
+    rc = check_launch();
+    if (rc || !a->causal) return rc;
+    dim3 sgrid(static_cast<unsigned>(ceil_div(a->P, 128)), static_cast<unsigned>(a->B));
+    chunk_scan_kernel<<<sgrid, 128, 0, st>>>(a->partial, a->carry, a->total, d.chunks, a->P, 0);
+    count_launch();
+  }
 #define CALL_PFX(T, V, KR)                                                                   \
   if (has_rope) agg_fwd_kernel<T, V, KR, true, true><<<wl.grid, wl.block, 0, st>>>(d);        \
   else agg_fwd_kernel<T, V, KR, true, false><<<wl.grid, wl.block, 0, st>>>(d)
@@ -941,6 +963,7 @@ int pom_poly_agg_mean_noalloc(const pom_agg_args* a, const float* denom, float s
   d.P = a->P;
   d.K = a->K;
   d.chunks = chunks;
+  d.per_token = 0;
   d.rope = a->rope;
   const int vec = pick_vec(a->P, a->rope, a->dtype, a->K, {a->ldx}, {a->x});
   const WalkLaunch wl = walk_launch(a->P, a->rope.kind, vec, chunks, a->B);
@@ -967,7 +990,8 @@ int pom_poly_agg_bwd(const pom_agg_bwd_args* a, void* stream) {
   if (a->B > 65535 || pom_agg_chunks(a->N) > 65535) return POM_ERR_TOO_LARGE;
   if (a->dtype != POM_BF16 && a->dtype != POM_F32) return POM_ERR_UNSUPPORTED;
   if (a->ldx < a->P || a->ld_dx < a->P) return POM_ERR_BAD_STRIDE;
-  if (a->causal ? (!a->dout || !a->partial || a->ld_dout < a->P) : !a->dH) return POM_ERR_NULL;
+  if (a->causal < 0 || a->causal > 2) return POM_ERR_UNSUPPORTED;
+  if (a->causal ? (!a->dout || (!a->partial && a->causal == 1) || a->ld_dout < a->P) : !a->dH) return POM_ERR_NULL;
   int rc = check_rope(a->rope, a->P);
   if (rc) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -991,24 +1015,27 @@ int pom_poly_agg_bwd(const pom_agg_bwd_args* a, void* stream) {
   d.P = a->P;
   d.K = a->K;
   d.chunks = pom_agg_chunks(a->N);
+  d.per_token = a->causal == 2;
   d.rope = a->rope;
   const int vec = pick_vec(a->P, a->rope, a->dtype, a->K, {a->ldx, a->ld_dx, a->causal ? a->ld_dout : 0},
                            {a->x, a->dx, a->causal ? a->dout : nullptr});
   const WalkLaunch wl = walk_launch(a->P, a->rope.kind, vec, d.chunks, a->B);
   const bool has_rope = a->rope.kind != POM_ROPE_NONE;
   if (a->causal) {
-    // Plain column walk (no channel pairing) for the scaled chunk sums.
-    pom_rope none{};
-    const int v2 = pick_vec(a->P, none, a->dtype, 1, {a->ld_dout}, {a->dout});
-    const WalkLaunch w1 = walk_launch(a->P, POM_ROPE_NONE, v2, d.chunks, a->B);
+    if (a->causal == 1) {
+      // Plain column walk (no channel pairing) for the scaled chunk sums.
+      pom_rope none{};
+      const int v2 = pick_vec(a->P, none, a->dtype, 1, {a->ld_dout}, {a->dout});
+      const WalkLaunch w1 = walk_launch(a->P, POM_ROPE_NONE, v2, d.chunks, a->B);
 #define CALL_CS(T, V, KR) causal_bwd_sum_kernel<T, V><<<w1.grid, w1.block, 0, st>>>(d)
-    POM_DISPATCH(a->dtype, v2, CALL_CS);
+      POM_DISPATCH(a->dtype, v2, CALL_CS);
 #undef CALL_CS
-    count_launch();
-    dim3 sgrid(static_cast<unsigned>(ceil_div(a->P, 128)), static_cast<unsigned>(a->B));
-    chunk_scan_kernel<<<sgrid, 128, 0, st>>>(a->partial, a->carry, a->total, d.chunks, a->P, 1);
-    count_launch();
-    if (a->phase == 1) return check_launch();  // totals only
+      count_launch();
+      dim3 sgrid(static_cast<unsigned>(ceil_div(a->P, 128)), static_cast<unsigned>(a->B));
+      chunk_scan_kernel<<<sgrid, 128, 0, st>>>(a->partial, a->carry, a->total, d.chunks, a->P, 1);
+      count_launch();
+      if (a->phase == 1) return check_launch();  // totals only
+    }
 #define CALL_BC(T, V, KR)                                                                    \
   if (has_rope) agg_bwd_kernel<T, V, KR, true, true><<<wl.grid, wl.block, 0, st>>>(d);        \
   else agg_bwd_kernel<T, V, KR, true, false><<<wl.grid, wl.block, 0, st>>>(d)
@@ -1069,6 +1096,7 @@ int pom_select_fwd(const pom_select_args* a, void* stream) {
   d.P = a->P;
   d.h_per_token = a->h_per_token;
   d.activated = a->activated;
+  d.row_denom = a->h_per_token ? a->row_denom : nullptr;
   d.rope = a->rope;
   return select_common(d, a->dtype, false, {a->ld_z, a->ld_sh, a->h_per_token ? a->ld_h : 0},
                        {a->z, a->sh, a->h_per_token ? a->H : nullptr}, static_cast<cudaStream_t>(stream));
@@ -1099,6 +1127,7 @@ int pom_select_bwd(const pom_select_bwd_args* a, void* stream) {
   d.P = a->P;
   d.h_per_token = a->h_per_token;
   d.activated = a->activated;
+  d.row_denom = a->h_per_token ? a->row_denom : nullptr;
   d.rope = a->rope;
   return select_common(d, a->dtype, true,
                        {a->ld_z, a->ld_dsh, a->ld_dz, a->h_per_token ? a->ld_h : 0, a->h_per_token ? a->ld_dh : 0},

@@ -137,14 +137,23 @@ class _PoMLayer(torch.autograd.Function):
         n_glob = shard.n_global if shard is not None else N
         offset = shard.token_offset if shard is not None else 0
         causal = spec.mask_kind == "causal"
+        full = spec.mask_kind == "full"
         maskf = None
         denom = None
+        maskd = rowden = None
+        if full:
+            if shard is not None or heads or spec.n_past is not None:
+                raise NotImplementedError("(B, M, N) masks are not combined with token sharding, multi-head gating or state")
+            if mask.dim() != 3 or mask.shape[0] != B or mask.shape[2] != N or mask.shape[1] != T:
+                raise ValueError(f"expected a (B, T, N) = ({B}, {T}, {N}) mask, got {tuple(mask.shape)}")
+            maskd = mask.to(device=xq.device, dtype=xq.dtype).contiguous()
+            rowden = _row_sums(mask.to(device=xq.device, dtype=torch.float32).contiguous().view(B * T, N))
         if spec.mask_kind == "keypad":
             maskf = mask.to(device=xq.device, dtype=torch.float32).contiguous()
             denom = ops.reduce_partials(maskf.view(B, N, 1)).view(B)
             if shard is not None:
                 shard.all_reduce(denom)
-        fused = (bf16 and not heads and spec.rope_ctx is None and spec.rope_qry is None and not causal
+        fused = (bf16 and not heads and spec.rope_ctx is None and spec.rope_qry is None and not causal and not full
                  and P % 8 == 0 and D % 8 == 0)
 
         hp = z = Hc = s32 = None
@@ -159,7 +168,7 @@ class _PoMLayer(torch.autograd.Function):
             else:
                 hp = ops.gemm(xc.view(B * N, D), w_po).view(B, N, P)
                 z = ops.gemm(xq.view(B * T, D), w_se).view(B, T, S)
-            if not causal:
+            if not causal and not full:
                 S_part = ops.poly_agg_fwd(hp, coeff32, row_weight=maskf, rope=spec.rope_ctx)  # per-chunk sums
         if causal:
             carry = None
@@ -167,6 +176,13 @@ class _PoMLayer(torch.autograd.Function):
                 S_loc = ops.reduce_partials(ops.poly_agg_fwd(hp, coeff32, rope=spec.rope_ctx))
                 carry = shard.exclusive_carry(S_loc)
             Hc, _ = ops.poly_agg_fwd(hp, coeff32, causal=True, rope=spec.rope_ctx, carry=carry, token_offset=offset)
+            H = None
+        elif full:
+            # H[b, m, :] = sum_n mask[b, m, n] * features[b, n, :] (divided by the row sum inside the selection)
+            feat = ops.poly_agg_fwd(hp, coeff32, rope=spec.rope_ctx, per_token=True)
+            Hc = torch.empty((B, T, P), dtype=xq.dtype, device=xq.device)
+            for b in range(B):
+                ops.gemm(maskd[b], feat[b], b_mn=True, out=Hc[b])
             H = None
         else:
             scale = 1.0 if denom is not None else 1.0 / n_glob
@@ -184,7 +200,7 @@ class _PoMLayer(torch.autograd.Function):
             s32 = _f32(ops.select_fwd(z, bias32, ones, rope=spec.rope_qry))   # gate in head space (B, T, heads)
             sh = ops.select_heads_fwd(s32, Hc if causal else H, xq.dtype)
         else:
-            sh = ops.select_fwd(z, bias32, Hc if causal else H, rope=spec.rope_qry)
+            sh = ops.select_fwd(z, bias32, Hc if (causal or full) else H, rope=spec.rope_qry, row_denom=rowden)
         if residual is not None and not bf16:
             raise NotImplementedError("the fused residual add of the output projection is a bf16 feature")
         y = ops.gemm(sh.view(B * T, P), w_ag,
@@ -195,7 +211,7 @@ class _PoMLayer(torch.autograd.Function):
         ctx.fused = fused
         ctx.dims = (B, T, N, D, P, K, S, heads, n_glob, offset)
         ctx.h_past_dtype = None if h_past is None else h_past.dtype
-        ctx.save_for_backward(xq, xc, w_qc, w_ag, coeff32, bias32, hp, z, H, Hc, sh, maskf, denom, s32)
+        ctx.save_for_backward(xq, xc, w_qc, w_ag, coeff32, bias32, hp, z, H, Hc, sh, maskf, denom, s32, maskd, rowden)
         ctx.param_like = (w_qc, se_bias, coeff, w_ag)
         if spec.want_state:
             return y, H.view(B, 1, P)
@@ -204,11 +220,12 @@ class _PoMLayer(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy, dh_state):
         spec: LayerSpec = ctx.spec
-        xq, xc, w_qc, w_ag, coeff32, bias32, hp, z, H, Hc, sh, maskf, denom, s32 = ctx.saved_tensors
+        xq, xc, w_qc, w_ag, coeff32, bias32, hp, z, H, Hc, sh, maskf, denom, s32, maskd, rowden = ctx.saved_tensors
         B, T, N, D, P, K, S, heads, n_glob, offset = ctx.dims
         p_qc, p_bias, p_coeff, p_ag = ctx.param_like
         shard = spec.shard
         causal = spec.mask_kind == "causal"
+        full = spec.mask_kind == "full"
         dev = xq.device
         dt = xq.dtype
         dy = dy.contiguous()
@@ -245,8 +262,8 @@ class _PoMLayer(torch.autograd.Function):
                 ops.select_bwd(ds, z, bias32, _ones(B, heads, dev), g_z.view(B, T, heads), rope=spec.rope_qry,
                                dbias_out=d_bias)
             else:
-                dH, _ = ops.select_bwd(dsh, z, bias32, Hc if causal else H, g_z.view(B, T, P), rope=spec.rope_qry,
-                                       dbias_out=d_bias)
+                dH, _ = ops.select_bwd(dsh, z, bias32, Hc if (causal or full) else H, g_z.view(B, T, P),
+                                       rope=spec.rope_qry, dbias_out=d_bias, row_denom=rowden)
 
         # ---------------------------------------------------------------- context phase backward
         d_hpast = None
@@ -258,6 +275,13 @@ class _PoMLayer(torch.autograd.Function):
                 carry = shard.exclusive_carry(tot, reverse=True)
             ops.poly_agg_bwd(hp, coeff32, dx_out=g_hp.view(B, N, P), dout=dH, causal=True, rope=spec.rope_ctx,
                              carry=carry, token_offset=offset, dcoeff_out=d_coeff)
+        elif full:
+            # d features[b] = mask[b]^T (N x T) · dH[b] (T x P)
+            dfeat = torch.empty((B, N, P), dtype=dt, device=dev)
+            for b in range(B):
+                ops.gemm(maskd[b], dH[b], a_mn=True, b_mn=True, out=dfeat[b])
+            ops.poly_agg_bwd(hp, coeff32, dx_out=g_hp.view(B, N, P), dout=dfeat, per_token=True, rope=spec.rope_ctx,
+                             dcoeff_out=d_coeff)
         else:
             if dh_state is not None:
                 dH = ops.reduce_partials(torch.stack([dH, _f32(dh_state.reshape(B, P).contiguous())], dim=1))
@@ -297,6 +321,16 @@ class _PoMLayer(torch.autograd.Function):
             g_qc, g_ag = _like_param(d_wqc, p_qc), _like_param(d_wag, p_ag)
             g_bias, g_coeff = _like_param(d_bias, p_bias), _like_param(d_coeff, p_coeff)
         return (dxq, dxc, g_qc, g_bias, g_coeff, g_ag, None, d_hpast, None, dy if ctx.has_residual else None)
+
+
+def _row_sums(m: torch.Tensor) -> torch.Tensor:
+    """Row sums of a (rows, N) fp32 matrix through the partial-sum reduction kernel (grid-limited slices)."""
+    rows, n = m.shape
+    out = torch.empty((rows,), dtype=torch.float32, device=m.device)
+    for lo in range(0, rows, 32768):
+        hi = min(rows, lo + 32768)
+        ops.reduce_partials(m[lo:hi].view(hi - lo, n, 1), out=out[lo:hi].view(hi - lo, 1))
+    return out
 
 
 _ones_cache = {}

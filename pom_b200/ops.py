@@ -209,14 +209,16 @@ def agg_chunks(n: int) -> int:
 
 def poly_agg_fwd(x: torch.Tensor, coeff: torch.Tensor, *, row_weight: Optional[torch.Tensor] = None,
                  causal: bool = False, rope: Optional[RopeSpec] = None, carry: Optional[torch.Tensor] = None,
-                 token_offset: int = 0, want_total: bool = False):
+                 token_offset: int = 0, want_total: bool = False, per_token: bool = False):
     """Non-causal: returns partial sums (B, chunks, P) fp32 (finish with reduce_partials).
-    Causal: returns (out (B, N, P) of x.dtype, total (B, P) fp32 or None)."""
+    Causal: returns (out (B, N, P) of x.dtype, total (B, P) fp32 or None).
+    ``per_token``: returns each token's own rotated polynomial features (B, N, P), no reduction."""
     dev = _require_cuda(x, coeff, row_weight, carry)
     B, N, P = x.shape
     K = coeff.shape[1]
     chunks = agg_chunks(N)
-    partial = torch.empty((B, chunks, P), dtype=torch.float32, device=dev)
+    causal = causal or per_token
+    partial = None if per_token else torch.empty((B, chunks, P), dtype=torch.float32, device=dev)
     out = torch.empty((B, N, P), dtype=x.dtype, device=dev) if causal else None
     total = torch.empty((B, P), dtype=torch.float32, device=dev) if (causal and want_total) else None
     a = AggArgs()
@@ -224,9 +226,11 @@ def poly_agg_fwd(x: torch.Tensor, coeff: torch.Tensor, *, row_weight: Optional[t
     a.partial, a.out, a.total = ptr(partial), ptr(out), ptr(total)
     a.ldx, a.ld_out, a.token_offset = _row_stride(x), P, token_offset
     a.B, a.N, a.P, a.K = B, N, P, K
-    a.dtype, a.causal = _abi.dtype_code(x.dtype), int(causal)
+    a.dtype, a.causal = _abi.dtype_code(x.dtype), (2 if per_token else int(causal))
     a.rope = _rope_c(rope)
     _abi.check(_abi.lib().pom_poly_agg_fwd(C.byref(a), _abi.stream_ptr()), "pom_poly_agg_fwd")
+    if per_token:
+        return out
     if causal:
         return out, total
     return partial
@@ -236,7 +240,8 @@ def poly_agg_bwd(x: torch.Tensor, coeff: torch.Tensor, *, dx_out: torch.Tensor, 
                  dout: Optional[torch.Tensor] = None, row_weight: Optional[torch.Tensor] = None,
                  denom: Optional[torch.Tensor] = None, scale: float = 1.0, causal: bool = False,
                  rope: Optional[RopeSpec] = None, carry: Optional[torch.Tensor] = None, token_offset: int = 0,
-                 want_total: bool = False, totals_only: bool = False, dcoeff_out: Optional[torch.Tensor] = None):
+                 want_total: bool = False, totals_only: bool = False, dcoeff_out: Optional[torch.Tensor] = None,
+                 per_token: bool = False):
     """Writes dx into ``dx_out`` (a (B, N, P) view, own row stride) and returns
     (dcoeff (P, K) fp32, total (B, P) fp32 or None)."""
     dev = _require_cuda(x, coeff, dx_out, dH, dout, row_weight, denom, carry)
@@ -244,7 +249,8 @@ def poly_agg_bwd(x: torch.Tensor, coeff: torch.Tensor, *, dx_out: torch.Tensor, 
     K = coeff.shape[1]
     chunks = agg_chunks(N)
     dcp = torch.empty((1, B * chunks, P * K), dtype=torch.float32, device=dev)
-    partial = torch.empty((B, chunks, P), dtype=torch.float32, device=dev) if causal else None
+    causal = causal or per_token
+    partial = torch.empty((B, chunks, P), dtype=torch.float32, device=dev) if (causal and not per_token) else None
     total = torch.empty((B, P), dtype=torch.float32, device=dev) if (causal and want_total) else None
     a = AggBwdArgs()
     a.x, a.coeff, a.row_weight, a.denom = ptr(x), ptr(coeff), ptr(row_weight), ptr(denom)
@@ -254,7 +260,7 @@ def poly_agg_bwd(x: torch.Tensor, coeff: torch.Tensor, *, dx_out: torch.Tensor, 
     a.ld_dout = _row_stride(dout) if dout is not None else 0
     a.token_offset, a.scale = token_offset, scale
     a.B, a.N, a.P, a.K = B, N, P, K
-    a.dtype, a.causal, a.phase = _abi.dtype_code(x.dtype), int(causal), int(totals_only)
+    a.dtype, a.causal, a.phase = _abi.dtype_code(x.dtype), (2 if per_token else int(causal)), int(totals_only)
     a.rope = _rope_c(rope)
     _abi.check(_abi.lib().pom_poly_agg_bwd(C.byref(a), _abi.stream_ptr()), "pom_poly_agg_bwd")
     if totals_only:
@@ -264,7 +270,7 @@ def poly_agg_bwd(x: torch.Tensor, coeff: torch.Tensor, *, dx_out: torch.Tensor, 
 
 
 def select_fwd(z: torch.Tensor, bias: Optional[torch.Tensor], h: torch.Tensor, *, rope: Optional[RopeSpec] = None,
-               activated: bool = False) -> torch.Tensor:
+               activated: bool = False, row_denom: Optional[torch.Tensor] = None) -> torch.Tensor:
     """SH = R·hardsigmoid(z + bias) ⊙ H.  ``h`` is (B, P) fp32 (one vector per sample) or (B, T, P) of z.dtype."""
     dev = _require_cuda(z, bias, h)
     B, T, P = z.shape
@@ -279,13 +285,15 @@ def select_fwd(z: torch.Tensor, bias: Optional[torch.Tensor], h: torch.Tensor, *
     a.ld_z, a.ld_h, a.ld_sh = _row_stride(z), (_row_stride(h) if per_tok else 0), P
     a.B, a.T, a.P = B, T, P
     a.dtype, a.h_per_token, a.activated = _abi.dtype_code(z.dtype), int(per_tok), int(activated)
+    a.row_denom = ptr(row_denom)
     a.rope = _rope_c(rope)
     _abi.check(_abi.lib().pom_select_fwd(C.byref(a), _abi.stream_ptr()), "pom_select_fwd")
     return sh
 
 
 def select_bwd(dsh: torch.Tensor, z: torch.Tensor, bias: Optional[torch.Tensor], h: torch.Tensor, dz_out: torch.Tensor,
-               *, rope: Optional[RopeSpec] = None, activated: bool = False, dbias_out: Optional[torch.Tensor] = None):
+               *, rope: Optional[RopeSpec] = None, activated: bool = False, dbias_out: Optional[torch.Tensor] = None,
+               row_denom: Optional[torch.Tensor] = None):
     """Returns (dH, dbias): dH is (B, P) fp32 un-normalised sum over tokens when ``h`` is per-sample,
     else the per-token (B, T, P) gradient in z.dtype.  dz is written into ``dz_out``."""
     dev = _require_cuda(dsh, z, bias, h, dz_out)
@@ -302,6 +310,7 @@ def select_bwd(dsh: torch.Tensor, z: torch.Tensor, bias: Optional[torch.Tensor],
     a.ld_h, a.ld_dh = (_row_stride(h) if per_tok else 0), P
     a.B, a.T, a.P = B, T, P
     a.dtype, a.h_per_token, a.activated = _abi.dtype_code(z.dtype), int(per_tok), int(activated)
+    a.row_denom = ptr(row_denom)
     a.rope = _rope_c(rope)
     _abi.check(_abi.lib().pom_select_bwd(C.byref(a), _abi.stream_ptr()), "pom_select_bwd")
     dbias = reduce_partials(db_p, out=None if dbias_out is None else dbias_out.view(1, P)).view(P)

@@ -51,11 +51,9 @@ class PoM(nn.Module):
     # ------------------------------------------------------------------ helpers
     def _spec(self, xq, xc, mask, shard: Optional[SeqShard]) -> Tuple[LayerSpec, Optional[torch.Tensor]]:
         kind = _mask_kind(mask)
-        if kind == "full":
-            raise NotImplementedError("(B, M, N) masks are not implemented by the CUDA path yet")
         spec = LayerSpec(degree=self.order, mask_kind=kind, self_mixing=(xc is None or xc is xq), shard=shard,
                          n_sel_heads=self.n_sel_heads)
-        return spec, (mask if kind == "keypad" else None)
+        return spec, (mask if kind in ("keypad", "full") else None)
 
     def _finish(self, y: torch.Tensor) -> torch.Tensor:
         return y if self.ag_proj.bias is None else y + self.ag_proj.bias
@@ -63,7 +61,7 @@ class PoM(nn.Module):
     # ------------------------------------------------------------------ API
     def forward(self, xq: torch.Tensor, xc: Optional[torch.Tensor] = None, mask=None,
                 shard: Optional[SeqShard] = None) -> torch.Tensor:
-        """xq (B, T, D) queries; xc (B, N, D) context (None: self-mixing); mask None, "causal" or (B, N).
+        """xq (B, T, D) queries; xc (B, N, D) context (None: self-mixing); mask None, "causal", (B, N) or (B, T, N).
 
         ``shard`` (extension) declares that xq/xc are this rank's token slice of a longer sequence.
         """

@@ -110,8 +110,6 @@ class PoMRoPE(PoM):
         0..N-1), ``positions_hw`` (T, 2) / ``ctx_positions_hw`` (N, 2) for 2-D tables."""
         self_mixing = xc is None or xc is xq
         kind = _mask_kind(mask)
-        if kind == "full":
-            raise NotImplementedError("(B, M, N) masks are not implemented by the CUDA path yet")
         T = xq.shape[1]
         N = T if self_mixing else xc.shape[1]
         cpos = ctx_positions if ctx_positions is not None else (positions if self_mixing else None)
@@ -122,5 +120,5 @@ class PoMRoPE(PoM):
         spec = LayerSpec(degree=self.order, mask_kind=kind, self_mixing=self_mixing, rope_ctx=rope_c, rope_qry=rope_q,
                          shard=shard, n_sel_heads=self.n_sel_heads)
         y, _ = pom_layer(xq, xc, self.qc_proj.weight, self.se_bias, self.po_coeff, self.ag_proj.weight,
-                         mask if kind == "keypad" else None, None, spec)
+                         mask if kind in ("keypad", "full") else None, None, spec)
         return self._finish(y)

@@ -9,7 +9,7 @@ from tests.helpers import (BF16_TOL, FP32_TOL, PARAM_ORDER, assert_close, assert
 
 pytestmark = pytest.mark.gpu
 
-LAYER_CASES = ["pom_none", "pom_causal", "pom_mask2d", "pom_cross", "pom_cross_mask2d",
+LAYER_CASES = ["pom_none", "pom_causal", "pom_mask2d", "pom_mask3d", "pom_cross", "pom_cross_mask2d",
                "rope1d_none", "rope1d_causal", "rope1d_mask2d", "rope1d_positions", "rope1d_cross",
                "rope2d_none", "rope2d_causal"]
 
@@ -115,6 +115,35 @@ def test_bf16_multi_head_gating_against_oracle(mask, rope):
     assert_close(y, want_y, BF16_TOL, "y")
     for k, w in want_g.items():
         assert_close(grads[k], w, BF16_TOL, f"d_{k}")
+
+
+@pytest.mark.parametrize("rope", [None, "2d"])
+def test_block_causal_mask_equals_frame_loop(rope):
+    """A (B, N, N) block-lower-triangular mask reproduces state_forward's frame loop when all frames have
+    the same length (single layer); bf16, against the oracle with the same mask."""
+    B, F, L, D, K, E = 2, 4, 64, 64, 2, 2
+    N = F * L
+    cfg, params, x, gy = _seeded_case(B, N, D, K, E, seed=12, coeff_scale=0.1, bias_scale=0.3)
+    params = {k: O.bf16_round(v) for k, v in params.items()}
+    x, gy = O.bf16_round(x), O.bf16_round(gy)
+    mask = O.block_causal_mask(N, L, B)
+    kw = {"mask": mask}
+    if rope:
+        cfg = dict(cfg, rope=dict(two_d=True, max_h=16, max_w=16))
+        kw["positions_hw"] = torch.stack([torch.arange(N) // 16, torch.arange(N) % 16], 1)
+    want_y, want_g = oracle_run(cfg, params, x, None, kw, gy)
+    mod = make_cuda_module(cfg, params, torch.bfloat16)
+    y, grads = cuda_run(mod, x, None, kw, gy, torch.bfloat16)
+    assert_close(y, want_y, BF16_TOL, "y")
+    for k, w in want_g.items():
+        assert_close(grads[k], w, BF16_TOL, f"d_{k}")
+    if not rope:
+        state, outs = None, []
+        with torch.no_grad():
+            for f in range(F):
+                yf, state = mod.state_forward(x[:, f * L:(f + 1) * L].cuda().bfloat16().contiguous(), None, state)
+                outs.append(yf)
+        assert_close(torch.cat(outs, 1), y, BF16_TOL, "frame loop vs block-causal mask")
 
 
 def test_bf16_masked_layer_ignores_padded_noise():
