@@ -334,6 +334,64 @@ int pom_fill_zero(void* dst, int64_t bytes, void* stream);
 int pom_cast_f32_to_bf16(const float* src, void* dst, int64_t count, void* stream);
 int pom_cast_bf16_to_f32(const void* src, float* dst, int64_t count, void* stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * Token-sharding exchanges over NVLink peer memory (no counterpart in the reference, which is single-GPU;
+ * they carry the cross-rank sums that a token-sharded PoM.forward needs: the (B, P) aggregate of
+ * pom/pom.py:90-96 split over ranks, its gradient, the causal prefix/suffix carries, and the sum of
+ * the parameter gradients).
+ *
+ * Every rank owns one exchange buffer of pom_peer_layout()[2] bytes, zero-filled before first use, which all
+ * ranks of the node map: the owner exports it (pom_peer_export: CUDA IPC handle of the enclosing allocation +
+ * byte offset of the buffer inside it), the handle travels by any host channel, the others open it
+ * (pom_peer_open, returns the allocation's base in this process; add the offset).  Layout:
+ *   [0, POM_PEER_HEADER_BYTES)  epoch counters and flags
+ *   [layout[0], layout[1])      message slots: 2 epochs x world writers x slot_floats fp32
+ *   [layout[1], layout[2])      parameter-gradient region, flat_floats fp32, reduced in place
+ * The library allocates nothing; the caller owns the buffers and must keep them alive, and mapped by the
+ * peers, until all ranks have finished their last exchange.  All ranks must issue the same sequence of
+ * exchange calls.  Waits on other ranks are bounded (2 s): on expiry POM_ERR_TIMEOUT is stored in *status
+ * (device int, zero before the first call; once non-zero, later exchanges do not wait) and the results are
+ * undefined.  The calls only enqueue work on `stream` and can be captured into CUDA graphs (the epochs
+ * are device-side counters).  Kernels of different ranks wait on each other, so every rank must run on its
+ * own GPU. */
+#define POM_PEER_MAX_RANKS 16
+#define POM_PEER_FLAT_CTAS 128
+#define POM_PEER_HEADER_BYTES 65536
+#define POM_PEER_HANDLE_BYTES 64
+
+typedef struct pom_peer_comm {
+  void* base[POM_PEER_MAX_RANKS];   /* base[r]: rank r's exchange buffer as addressable from this process */
+  int32_t rank, world;
+  unsigned long long slot_floats;   /* capacity of one message (multiple of 4) */
+  unsigned long long flat_floats;   /* capacity of the gradient region (multiple of 4, may be 0) */
+} pom_peer_comm;
+
+/* out[0] = byte offset of the slots, out[1] = of the gradient region, out[2] = total bytes. */
+int pom_peer_layout(int world, unsigned long long slot_floats, unsigned long long flat_floats,
+                    unsigned long long out[3]);
+int pom_peer_export(const void* dev_ptr, void* handle_out /* POM_PEER_HANDLE_BYTES */, unsigned long long* offset_out);
+int pom_peer_open(const void* handle, void** base_out);
+int pom_peer_close(void* base);
+
+enum { POM_PEER_SUM_ALL = 0, POM_PEER_SUM_BEFORE = 1, POM_PEER_SUM_AFTER = 2 };
+
+/* out[b, p] = scale * sum_{r in range} sum_c partial_r[b, c, p] / denom[b]   (denom optional; 0 -> 0)
+ * range = all ranks, the ranks before this one, or the ranks after it (rank order, so every rank of an
+ * all-reduce gets bitwise the same result).  B * P <= slot_floats.  out may alias partial when chunks == 1. */
+typedef struct pom_peer_xchg_args {
+  const float* partial;
+  float* out;
+  const float* denom;
+  float scale;
+  int32_t B, chunks, P;
+  int32_t mode;
+} pom_peer_xchg_args;
+int pom_peer_exchange(const pom_peer_comm* c, const pom_peer_xchg_args* a, int* status, void* stream);
+
+/* In-place sum over ranks of the first n_floats (multiple of 4) of every rank's gradient region: rank r adds
+ * slice r of all ranks in rank order and stores the result to all ranks. */
+int pom_peer_allreduce_flat(const pom_peer_comm* c, unsigned long long n_floats, int* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -137,6 +137,27 @@ class SelectHeadsArgs(C.Structure):
     ]
 
 
+PEER_MAX_RANKS = 16
+PEER_HANDLE_BYTES = 64
+PEER_SUM_ALL, PEER_SUM_BEFORE, PEER_SUM_AFTER = 0, 1, 2
+
+
+class PeerComm(C.Structure):
+    _fields_ = [
+        ("base", C.c_void_p * PEER_MAX_RANKS),
+        ("rank", C.c_int32), ("world", C.c_int32),
+        ("slot_floats", C.c_ulonglong), ("flat_floats", C.c_ulonglong),
+    ]
+
+
+class PeerXchgArgs(C.Structure):
+    _fields_ = [
+        ("partial", C.c_void_p), ("out", C.c_void_p), ("denom", C.c_void_p),
+        ("scale", C.c_float),
+        ("B", C.c_int32), ("chunks", C.c_int32), ("P", C.c_int32), ("mode", C.c_int32),
+    ]
+
+
 # Every exported symbol with its signature; test_abi_exports checks the list against the header.
 _SIGNATURES = {
     "pom_abi_version": (C.c_int, []),
@@ -162,6 +183,12 @@ _SIGNATURES = {
     "pom_fill_zero": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p]),
     "pom_cast_f32_to_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "pom_cast_bf16_to_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
+    "pom_peer_layout": (C.c_int, [C.c_int, C.c_ulonglong, C.c_ulonglong, C.POINTER(C.c_ulonglong)]),
+    "pom_peer_export": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_ulonglong)]),
+    "pom_peer_open": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    "pom_peer_close": (C.c_int, [C.c_void_p]),
+    "pom_peer_exchange": (C.c_int, [C.POINTER(PeerComm), C.POINTER(PeerXchgArgs), C.c_void_p, C.c_void_p]),
+    "pom_peer_allreduce_flat": (C.c_int, [C.POINTER(PeerComm), C.c_ulonglong, C.c_void_p, C.c_void_p]),
 }
 
 _lib = None

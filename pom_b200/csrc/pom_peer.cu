@@ -1,0 +1,340 @@
+// Token-sharding exchanges over NVLink peer memory: every rank owns one exchange buffer that all ranks of the
+// node map (CUDA IPC), and the kernels below move the layer's small cross-rank sums by plain peer stores and
+// loads — no library collective, so a whole sharded layer step can be captured into a CUDA graph.
+//
+//   peer_exchange_kernel        sum a (B, chunks, P) partial over chunks, push the (B, P) message into every
+//                               rank's slot, wait (bounded) for the other ranks' messages, add the slots of a
+//                               rank range in rank order and normalise: all-reduce / exclusive prefix / suffix.
+//   peer_allreduce_flat_kernel  in-place two-shot all-reduce of the parameter-gradient region: rank r reduces
+//                               slice r from all ranks (peer loads) and writes the result to all ranks.
+//
+// Synchronisation is by epoch flags in the buffer header, written with st.release.sys after a system fence and
+// polled with ld.acquire.sys under a 2 s limit; the epoch counters live in device memory so a replayed graph
+// advances them.  A wait that expires records POM_ERR_TIMEOUT in the status word and the kernel carries on (its
+// result is then meaningless, which the host sees from the status word); later kernels skip their waits.
+// No TMA and no multicast instruction touches peer memory here.
+#include <cstring>
+#include <mutex>
+
+#include "common.cuh"
+
+using namespace pomh;
+
+namespace {
+
+constexpr int kMaxRanks = POM_PEER_MAX_RANKS;
+constexpr int kFlatCtas = POM_PEER_FLAT_CTAS;
+constexpr int kFlatThreads = 512;
+constexpr int kXchgThreads = 1024;
+constexpr unsigned long long kWaitNs = 2000000000ull;
+
+// Header at the start of every rank's exchange buffer (POM_PEER_HEADER_BYTES reserved).
+struct PeerHeader {
+  unsigned ctr_small;                          // epochs of peer_exchange_kernel launched by the owner
+  unsigned pad0[63];
+  unsigned flag_small[2][kMaxRanks];           // [epoch parity][writer rank]
+  unsigned pad1[32];
+  unsigned ctr_flat[kFlatCtas];                // epochs of peer_allreduce_flat_kernel, per CTA
+  unsigned flag_start[kMaxRanks][kFlatCtas];   // [writer rank][cta]
+  unsigned flag_done[kMaxRanks][kFlatCtas];
+};
+static_assert(sizeof(PeerHeader) <= POM_PEER_HEADER_BYTES, "header region too small");
+
+struct PeerDev {
+  char* base[kMaxRanks];
+  int rank, world;
+  unsigned long long slot_floats, slots_off, flat_off;
+};
+
+__device__ __forceinline__ PeerHeader* header(const PeerDev& c, int r) {
+  return reinterpret_cast<PeerHeader*>(c.base[r]);
+}
+__device__ __forceinline__ float* slot(const PeerDev& c, int owner, unsigned parity, int writer) {
+  return reinterpret_cast<float*>(c.base[owner] + c.slots_off) +
+         (static_cast<unsigned long long>(parity) * c.world + writer) * c.slot_floats;
+}
+
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float4 ld_sys_f4(const float4* p) {
+  float4 v;
+  asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_sys_f4(float4* p, float4 v) {
+  asm volatile("st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ float ld_sys_f(const float* p) {
+  float v;
+  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Poll until *flag has reached `epoch` (wrap-safe) or the limit passes; false on expiry.
+__device__ __forceinline__ bool wait_flag(const unsigned* flag, unsigned epoch, bool skip) {
+  if (static_cast<int>(ld_acquire_sys(flag) - epoch) >= 0) return true;
+  if (skip) return false;
+  const unsigned long long t0 = now_ns();
+  for (;;) {
+    for (int i = 0; i < 64; ++i)
+      if (static_cast<int>(ld_acquire_sys(flag) - epoch) >= 0) return true;
+    if (now_ns() - t0 > kWaitNs) return false;
+    __nanosleep(100);
+  }
+}
+
+struct XchgDev {
+  const float* partial;
+  float* out;
+  const float* denom;
+  float scale;
+  int B, chunks, P;
+  int lo, hi;  // ranks [lo, hi) enter the sum
+};
+
+__global__ void __launch_bounds__(kXchgThreads) peer_exchange_kernel(PeerDev c, XchgDev a, int* status) {
+  __shared__ unsigned s_epoch;
+  __shared__ int s_fail;
+  const int tid = threadIdx.x;
+  PeerHeader* mine = header(c, c.rank);
+  if (tid == 0) {
+    s_epoch = mine->ctr_small + 1;
+    mine->ctr_small = s_epoch;
+    s_fail = 0;
+  }
+  __syncthreads();
+  const unsigned epoch = s_epoch, parity = epoch & 1u;
+  const bool poisoned = *reinterpret_cast<volatile int*>(status) != 0;
+  const int n = a.B * a.P;
+
+  // local chunk sums, pushed into this rank's slot on every rank (own included)
+  for (int e = tid; e < n; e += kXchgThreads) {
+    const int b = e / a.P, p = e - b * a.P;
+    const float* src = a.partial + static_cast<long long>(b) * a.chunks * a.P + p;
+    float s0 = 0.f, s1 = 0.f;
+    int k = 0;
+    for (; k + 1 < a.chunks; k += 2) {
+      s0 += src[static_cast<long long>(k) * a.P];
+      s1 += src[static_cast<long long>(k + 1) * a.P];
+    }
+    if (k < a.chunks) s0 += src[static_cast<long long>(k) * a.P];
+    const float s = s0 + s1;
+    for (int q = 0; q < c.world; ++q) slot(c, q, parity, c.rank)[e] = s;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid < c.world) st_release_sys(&header(c, tid)->flag_small[parity][c.rank], epoch);
+  if (tid < c.world && !wait_flag(&mine->flag_small[parity][tid], epoch, poisoned)) s_fail = 1;
+  __syncthreads();
+  if (s_fail && tid == 0 && !poisoned) atomicCAS(status, 0, POM_ERR_TIMEOUT);
+
+  for (int e = tid; e < n; e += kXchgThreads) {
+    float t = 0.f;
+    for (int q = a.lo; q < a.hi; ++q) t += ld_sys_f(slot(c, c.rank, parity, q) + e);
+    t *= a.scale;
+    if (a.denom) {
+      const float d = a.denom[e / a.P];
+      t = d != 0.f ? t / d : 0.f;
+    }
+    a.out[e] = t;
+  }
+}
+
+__global__ void __launch_bounds__(kFlatThreads) peer_allreduce_flat_kernel(PeerDev c, unsigned long long n4, int* status) {
+  __shared__ unsigned s_epoch;
+  __shared__ int s_fail;
+  const int tid = threadIdx.x, cta = blockIdx.x;
+  PeerHeader* mine = header(c, c.rank);
+  if (tid == 0) {
+    s_epoch = mine->ctr_flat[cta] + 1;
+    mine->ctr_flat[cta] = s_epoch;
+    s_fail = 0;
+  }
+  __syncthreads();
+  const unsigned epoch = s_epoch;
+  const bool poisoned = *reinterpret_cast<volatile int*>(status) != 0;
+
+  // every rank's gradients are complete once its kernel has started (stream order)
+  if (tid < c.world) st_release_sys(&header(c, tid)->flag_start[c.rank][cta], epoch);
+  if (tid < c.world && !wait_flag(&mine->flag_start[tid][cta], epoch, poisoned)) s_fail = 1;
+  __syncthreads();
+
+  const unsigned long long per = (n4 + c.world - 1) / c.world;
+  const unsigned long long lo = per * c.rank;
+  const unsigned long long hi = lo + per < n4 ? lo + per : n4;
+  float4* buf[kMaxRanks];
+#pragma unroll
+  for (int q = 0; q < kMaxRanks; ++q)
+    buf[q] = q < c.world ? reinterpret_cast<float4*>(c.base[q] + c.flat_off) : nullptr;
+  if (!s_fail) {
+    for (unsigned long long i = lo + static_cast<unsigned long long>(cta) * kFlatThreads + tid; i < hi;
+         i += static_cast<unsigned long long>(kFlatCtas) * kFlatThreads) {
+      float4 v[kMaxRanks];
+#pragma unroll
+      for (int q = 0; q < kMaxRanks; ++q)
+        if (q < c.world) v[q] = ld_sys_f4(buf[q] + i);
+      float4 acc = v[0];
+#pragma unroll
+      for (int q = 1; q < kMaxRanks; ++q)
+        if (q < c.world) {
+          acc.x += v[q].x;
+          acc.y += v[q].y;
+          acc.z += v[q].z;
+          acc.w += v[q].w;
+        }
+#pragma unroll
+      for (int q = 0; q < kMaxRanks; ++q)
+        if (q < c.world) st_sys_f4(buf[q] + i, acc);
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid < c.world) st_release_sys(&header(c, tid)->flag_done[c.rank][cta], epoch);
+  if (tid < c.world && !wait_flag(&mine->flag_done[tid][cta], epoch, poisoned || s_fail)) s_fail = 1;
+  __syncthreads();
+  if (s_fail && tid == 0 && !poisoned) atomicCAS(status, 0, POM_ERR_TIMEOUT);
+}
+
+int to_dev(const pom_peer_comm* c, PeerDev* d) {
+  if (!c) return POM_ERR_NULL;
+  if (c->world < 1 || c->world > kMaxRanks || c->rank < 0 || c->rank >= c->world) return POM_ERR_BAD_SHAPE;
+  unsigned long long lay[3];
+  int rc = pom_peer_layout(c->world, c->slot_floats, c->flat_floats, lay);
+  if (rc) return rc;
+  for (int q = 0; q < kMaxRanks; ++q) {
+    d->base[q] = q < c->world ? static_cast<char*>(c->base[q]) : nullptr;
+    if (q < c->world && (!c->base[q] || !aligned16(c->base[q]))) return POM_ERR_NULL;
+  }
+  d->rank = c->rank;
+  d->world = c->world;
+  d->slot_floats = c->slot_floats;
+  d->slots_off = lay[0];
+  d->flat_off = lay[1];
+  return POM_OK;
+}
+
+typedef CUresult (*GetRangeFn)(CUdeviceptr*, size_t*, CUdeviceptr);
+
+GetRangeFn range_fn() {
+  static GetRangeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<GetRangeFn>(p);
+  });
+  return fn;
+}
+
+}  // namespace
+
+extern "C" {
+
+int pom_peer_layout(int world, unsigned long long slot_floats, unsigned long long flat_floats,
+                    unsigned long long out[3]) {
+  if (!out) return POM_ERR_NULL;
+  if (world < 1 || world > kMaxRanks) return POM_ERR_BAD_SHAPE;
+  if (slot_floats == 0 || (slot_floats & 3ull) || (flat_floats & 3ull)) return POM_ERR_BAD_ALIGN;
+  out[0] = POM_PEER_HEADER_BYTES;
+  out[1] = out[0] + 2ull * world * slot_floats * sizeof(float);
+  out[2] = out[1] + flat_floats * sizeof(float);
+  return POM_OK;
+}
+
+int pom_peer_export(const void* dev_ptr, void* handle_out, unsigned long long* offset_out) {
+  if (!dev_ptr || !handle_out || !offset_out) return POM_ERR_NULL;
+  static_assert(sizeof(cudaIpcMemHandle_t) == POM_PEER_HANDLE_BYTES, "IPC handle size");
+  GetRangeFn fn = range_fn();
+  if (!fn) return POM_ERR_CUDA;
+  CUdeviceptr base = 0;
+  size_t size = 0;
+  if (fn(&base, &size, reinterpret_cast<CUdeviceptr>(dev_ptr)) != CUDA_SUCCESS) return POM_ERR_CUDA;
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base)) != cudaSuccess) {
+    cudaGetLastError();
+    return POM_ERR_CUDA;
+  }
+  std::memcpy(handle_out, &h, sizeof(h));
+  *offset_out = reinterpret_cast<CUdeviceptr>(dev_ptr) - base;
+  return POM_OK;
+}
+
+int pom_peer_open(const void* handle, void** base_out) {
+  if (!handle || !base_out) return POM_ERR_NULL;
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle, sizeof(h));
+  void* p = nullptr;
+  if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+    cudaGetLastError();
+    return POM_ERR_CUDA;
+  }
+  *base_out = p;
+  return POM_OK;
+}
+
+int pom_peer_close(void* base) {
+  if (!base) return POM_ERR_NULL;
+  if (cudaIpcCloseMemHandle(base) != cudaSuccess) {
+    cudaGetLastError();
+    return POM_ERR_CUDA;
+  }
+  return POM_OK;
+}
+
+int pom_peer_exchange(const pom_peer_comm* c, const pom_peer_xchg_args* a, int* status, void* stream) {
+  if (!a || !a->partial || !a->out || !status) return POM_ERR_NULL;
+  PeerDev d;
+  int rc = to_dev(c, &d);
+  if (rc) return rc;
+  if (a->B <= 0 || a->chunks <= 0 || a->P <= 0) return POM_ERR_BAD_SHAPE;
+  if (static_cast<unsigned long long>(a->B) * a->P > c->slot_floats) return POM_ERR_TOO_LARGE;
+  XchgDev x;
+  x.partial = a->partial;
+  x.out = a->out;
+  x.denom = a->denom;
+  x.scale = a->scale;
+  x.B = a->B;
+  x.chunks = a->chunks;
+  x.P = a->P;
+  switch (a->mode) {
+    case POM_PEER_SUM_ALL: x.lo = 0; x.hi = c->world; break;
+    case POM_PEER_SUM_BEFORE: x.lo = 0; x.hi = c->rank; break;
+    case POM_PEER_SUM_AFTER: x.lo = c->rank + 1; x.hi = c->world; break;
+    default: return POM_ERR_UNSUPPORTED;
+  }
+  peer_exchange_kernel<<<1, kXchgThreads, 0, static_cast<cudaStream_t>(stream)>>>(d, x, status);
+  count_launch();
+  return check_launch();
+}
+
+int pom_peer_allreduce_flat(const pom_peer_comm* c, unsigned long long n_floats, int* status, void* stream) {
+  if (!status) return POM_ERR_NULL;
+  PeerDev d;
+  int rc = to_dev(c, &d);
+  if (rc) return rc;
+  if (n_floats == 0 || (n_floats & 3ull)) return POM_ERR_BAD_ALIGN;
+  if (n_floats > c->flat_floats) return POM_ERR_TOO_LARGE;
+  peer_allreduce_flat_kernel<<<kFlatCtas, kFlatThreads, 0, static_cast<cudaStream_t>(stream)>>>(d, n_floats / 4,
+                                                                                                 status);
+  count_launch();
+  return check_launch();
+}
+
+}  // extern "C"

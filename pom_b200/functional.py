@@ -36,12 +36,15 @@ class SeqShard:
 
     ``token_offset`` is the global index of the local token 0 and ``n_global`` the global
     context length.  ``group`` is a torch.distributed process group (None = default group).
-    Ranks hold consecutive chunks in rank order.
+    Ranks hold consecutive chunks in rank order.  ``peer`` (a :class:`pom_b200.peer.PeerExchange` built on
+    the same group) moves the exchanges over NVLink peer memory instead of through torch.distributed, which
+    makes a sharded step capturable into a CUDA graph.
     """
     token_offset: int
     n_global: int
     group: Any = None
     reduce_weight_grads: bool = True
+    peer: Any = None
 
     @property
     def world(self) -> int:
@@ -51,12 +54,41 @@ class SeqShard:
     def rank(self) -> int:
         return dist.get_rank(self.group)
 
+    def _use_peer(self, t: torch.Tensor, count: int) -> bool:
+        return (self.peer is not None and t.is_cuda and t.dtype == torch.float32 and t.is_contiguous()
+                and count <= self.peer.slot_floats)
+
     def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        """In-place sum over ranks (same bits on every rank on the peer path: fixed rank order)."""
+        if self._use_peer(t, t.numel()):
+            self.peer.exchange(t.view(1, 1, -1), out=t.view(1, -1))
+            return t
         dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
         return t
 
+    def sum_partials(self, partial: torch.Tensor, denom: Optional[torch.Tensor] = None, scale: float = 1.0):
+        """(B, chunks, P) local partial sums -> (B, P) = scale · Σ_ranks Σ_chunks / denom."""
+        B, chunks, P = partial.shape
+        if self._use_peer(partial, B * P):
+            if chunks > 128:  # one CTA walks the chunks serially: keep that short
+                partial = ops.reduce_partials(partial).view(B, 1, P)
+            return self.peer.exchange(partial, denom=denom, scale=scale)
+        total = self.all_reduce(ops.reduce_partials(partial)).view(B, 1, P)
+        return ops.reduce_partials(total, denom=denom, scale=scale)
+
+    def reduce_grads(self, flat: torch.Tensor) -> torch.Tensor:
+        """Sum of the flat parameter-gradient buffer over ranks, in place."""
+        if self.peer is not None and self.peer.owns(flat):
+            self.peer.allreduce_flat(flat.numel())
+            return flat
+        dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group)
+        return flat
+
     def exclusive_carry(self, total: torch.Tensor, reverse: bool = False) -> torch.Tensor:
         """Sum of ``total`` over the ranks before (or, reversed, after) this one, in rank order."""
+        if self._use_peer(total, total.numel()):
+            mode = _abi.PEER_SUM_AFTER if reverse else _abi.PEER_SUM_BEFORE
+            return self.peer.exchange(total.view(total.shape[0], 1, -1), mode=mode).view(total.shape)
         w = self.world
         flat = torch.empty((w * total.shape[0],) + tuple(total.shape[1:]), dtype=total.dtype, device=total.device)
         dist.all_gather_into_tensor(flat, total.contiguous(), group=self.group)
@@ -187,8 +219,9 @@ class _PoMLayer(torch.autograd.Function):
         else:
             scale = 1.0 if denom is not None else 1.0 / n_glob
             if shard is not None:
-                S_part = shard.all_reduce(ops.reduce_partials(S_part)).view(B, 1, P)
-            H = ops.reduce_partials(S_part, denom=denom, scale=scale)
+                H = shard.sum_partials(S_part, denom=denom, scale=scale)
+            else:
+                H = ops.reduce_partials(S_part, denom=denom, scale=scale)
             if spec.n_past is not None and h_past is not None:
                 H = ops.state_merge(_f32(h_past.reshape(B, P).contiguous()), H, spec.n_past)
 
@@ -233,11 +266,20 @@ class _PoMLayer(torch.autograd.Function):
 
         # one flat fp32 buffer for all parameter gradients: a single zero fill, cast and (when sharded) all-reduce
         n_qc, n_ag = (P + S) * D, D * P
-        flat = ops.zeros_f32(n_qc + n_ag + S + P * K, dev)
+        n_flat = n_qc + n_ag + S + P * K
+        flat = None
+        peer_flat = shard is not None and shard.reduce_weight_grads and shard.peer is not None
+        if peer_flat:  # accumulate straight into the peer-mapped gradient region
+            flat = shard.peer.flat_buffer((n_flat + 3) // 4 * 4)
+        if flat is not None:
+            ops.fill_zero(flat)
+        else:
+            peer_flat = False
+            flat = ops.zeros_f32(n_flat, dev)
         d_wqc = flat[:n_qc].view(P + S, D)
         d_wag = flat[n_qc:n_qc + n_ag].view(D, P)
         d_bias = flat[n_qc + n_ag:n_qc + n_ag + S]
-        d_coeff = flat[n_qc + n_ag + S:].view(P, K)
+        d_coeff = flat[n_qc + n_ag + S:n_flat].view(P, K)
         # dWo[d, p] = sum_t dY[t, d] * SH[t, p]
         ops.gemm(dy2, sh.view(B * T, P), a_mn=True, b_mn=True, out=d_wag, accumulate=True)
 
@@ -311,13 +353,17 @@ class _PoMLayer(torch.autograd.Function):
             ops.gemm(g_z, xq.view(B * T, D), a_mn=True, b_mn=True, out=d_wqc[P:], accumulate=True)
 
         if shard is not None and shard.reduce_weight_grads:
-            shard.all_reduce(flat)
+            shard.reduce_grads(flat)
         dts = {p_qc.dtype, p_bias.dtype, p_coeff.dtype, p_ag.dtype}
         if dts == {torch.bfloat16}:
             f16 = ops.to_bf16(flat)
             g_qc, g_ag = f16[:n_qc].view(P + S, D), f16[n_qc:n_qc + n_ag].view(D, P)
             g_bias, g_coeff = f16[n_qc + n_ag:n_qc + n_ag + S], f16[n_qc + n_ag + S:].view(P, K)
         else:
+            if peer_flat:  # the shared region is reused by the next call: hand out copies
+                own = flat[:n_flat].clone()
+                d_wqc, d_wag = own[:n_qc].view(P + S, D), own[n_qc:n_qc + n_ag].view(D, P)
+                d_bias, d_coeff = own[n_qc + n_ag:n_qc + n_ag + S], own[n_qc + n_ag + S:].view(P, K)
             g_qc, g_ag = _like_param(d_wqc, p_qc), _like_param(d_wag, p_ag)
             g_bias, g_coeff = _like_param(d_bias, p_bias), _like_param(d_coeff, p_coeff)
         return (dxq, dxc, g_qc, g_bias, g_coeff, g_ag, None, d_hpast, None, dy if ctx.has_residual else None)

@@ -376,6 +376,13 @@ def zeros_f32(n: int, device) -> torch.Tensor:
     return out
 
 
+def fill_zero(t: torch.Tensor) -> torch.Tensor:
+    """Zero an existing contiguous tensor in place on the current stream."""
+    _require_cuda(t)
+    _abi.check(_abi.lib().pom_fill_zero(ptr(t), t.numel() * t.element_size(), _abi.stream_ptr()), "pom_fill_zero")
+    return t
+
+
 def to_bf16(src: torch.Tensor) -> torch.Tensor:
     _require_cuda(src)
     src = src.contiguous()

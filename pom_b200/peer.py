@@ -1,0 +1,111 @@
+"""``PeerExchange`` — the cross-rank sums of a token-sharded layer over NVLink peer memory.
+
+Each rank allocates one exchange buffer, exports it as a CUDA IPC handle, and maps the buffers of the
+other ranks of the node; the kernels behind ``pom_peer_exchange`` / ``pom_peer_allreduce_flat`` then push
+and pull the messages with plain peer stores and loads.  Unlike library collectives these launches can be
+captured into a CUDA graph together with the rest of the layer step.
+
+The reference is single-GPU (pom/pom.py:216-231 runs the whole sequence on one device); this is the
+transport for the ``SeqShard`` extension of :mod:`pom_b200.functional`.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from . import _abi
+from ._abi import PeerComm, PeerXchgArgs, ptr
+
+
+class PeerExchange:
+    """Exchange buffers of all ranks of ``group`` (one node, one GPU per rank).
+
+    ``slot_floats``: largest message (B·P fp32 values) a single exchange may carry.
+    ``flat_floats``: size of the parameter-gradient region that ``allreduce_flat`` sums in place.
+    Collective: every rank of the group must construct it at the same point of the program.
+    """
+
+    def __init__(self, group=None, slot_floats: int = 1 << 16, flat_floats: int = 0, device=None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world > _abi.PEER_MAX_RANKS:
+            raise ValueError(f"at most {_abi.PEER_MAX_RANKS} ranks")
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        slot_floats = (int(slot_floats) + 3) // 4 * 4
+        flat_floats = (int(flat_floats) + 3) // 4 * 4
+        lay = (C.c_ulonglong * 3)()
+        lib = _abi.lib()
+        _abi.check(lib.pom_peer_layout(self.world, slot_floats, flat_floats, lay), "pom_peer_layout")
+        self._slots_off, self._flat_off, total = int(lay[0]), int(lay[1]), int(lay[2])
+        self.slot_floats, self.flat_floats = slot_floats, flat_floats
+        # an allocation of its own (>= 20 MiB requests bypass the allocator's shared segments)
+        self.mem = torch.zeros(max(total, 32 << 20), dtype=torch.uint8, device=self.device)
+        torch.cuda.synchronize(self.device)
+
+        handle = (C.c_ubyte * _abi.PEER_HANDLE_BYTES)()
+        offset = C.c_ulonglong(0)
+        _abi.check(lib.pom_peer_export(ptr(self.mem), handle, C.byref(offset)), "pom_peer_export")
+        mine = (bytes(handle), int(offset.value))
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, mine, group=group)
+
+        self._opened = []
+        self.comm = PeerComm()
+        self.comm.rank, self.comm.world = self.rank, self.world
+        self.comm.slot_floats, self.comm.flat_floats = slot_floats, flat_floats
+        for r, (h, off) in enumerate(everyone):
+            if r == self.rank:
+                self.comm.base[r] = self.mem.data_ptr()
+                continue
+            buf = (C.c_ubyte * _abi.PEER_HANDLE_BYTES).from_buffer_copy(h)
+            base = C.c_void_p()
+            _abi.check(lib.pom_peer_open(buf, C.byref(base)), "pom_peer_open")
+            self._opened.append(base.value)
+            self.comm.base[r] = base.value + off
+        # nobody pushes before every buffer is zeroed and mapped
+        dist.barrier(group=group)
+        self.flat = self.mem[self._flat_off:self._flat_off + 4 * flat_floats].view(torch.float32)
+
+    # ------------------------------------------------------------------ exchanges
+    def exchange(self, partial: torch.Tensor, *, mode: int = _abi.PEER_SUM_ALL, denom: Optional[torch.Tensor] = None,
+                 scale: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """(B, chunks, P) fp32 local partial sums -> (B, P) sum over chunks and over the ranks ``mode`` selects."""
+        B, chunks, P = partial.shape
+        if partial.dtype != torch.float32 or not partial.is_contiguous():
+            raise TypeError("expected a contiguous fp32 (B, chunks, P) tensor")
+        if B * P > self.slot_floats:
+            raise ValueError(f"message of {B * P} values exceeds slot_floats={self.slot_floats}")
+        if out is None:
+            out = torch.empty((B, P), dtype=torch.float32, device=partial.device)
+        a = PeerXchgArgs()
+        a.partial, a.out, a.denom = ptr(partial), ptr(out), ptr(denom)
+        a.scale, a.B, a.chunks, a.P, a.mode = float(scale), B, chunks, P, mode
+        _abi.check(_abi.lib().pom_peer_exchange(C.byref(self.comm), C.byref(a), ptr(_abi.status_word(partial.device)),
+                                                _abi.stream_ptr()), "pom_peer_exchange")
+        return out
+
+    def flat_buffer(self, n: int) -> Optional[torch.Tensor]:
+        """The first ``n`` floats of the gradient region (None when it is too small)."""
+        return self.flat[:n] if n <= self.flat_floats else None
+
+    def owns(self, t: torch.Tensor) -> bool:
+        return t.data_ptr() == self.flat.data_ptr()
+
+    def allreduce_flat(self, n: int) -> None:
+        """In-place sum over ranks of the first ``n`` floats (rounded up to 4) of the gradient region."""
+        n4 = (n + 3) // 4 * 4
+        _abi.check(_abi.lib().pom_peer_allreduce_flat(C.byref(self.comm), n4, ptr(_abi.status_word(self.device)),
+                                                      _abi.stream_ptr()), "pom_peer_allreduce_flat")
+
+    def close(self) -> None:
+        """Unmap the peers' buffers (after a barrier: nobody may still be reading ours)."""
+        if self._opened:
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.group)
+            for base in self._opened:
+                _abi.lib().pom_peer_close(C.c_void_p(base))
+            self._opened = []

@@ -41,7 +41,8 @@ def test_struct_sizes_match_the_c_compiler():
     structs = {"pom_rope": _abi.Rope, "pom_gemm_args": _abi.GemmArgs, "pom_ctx_args": _abi.CtxArgs,
                "pom_gate_args": _abi.GateArgs, "pom_gate_bwd_args": _abi.GateBwdArgs, "pom_agg_args": _abi.AggArgs,
                "pom_agg_bwd_args": _abi.AggBwdArgs, "pom_select_args": _abi.SelectArgs,
-               "pom_select_bwd_args": _abi.SelectBwdArgs, "pom_select_heads_args": _abi.SelectHeadsArgs}
+               "pom_select_bwd_args": _abi.SelectBwdArgs, "pom_select_heads_args": _abi.SelectHeadsArgs,
+               "pom_peer_comm": _abi.PeerComm, "pom_peer_xchg_args": _abi.PeerXchgArgs}
     src = '#include <stdio.h>\n#include "pom_b200.h"\nint main(void){' + "".join(
         f'printf("{n} %zu\\n", sizeof({n}));' for n in structs) + "return 0;}\n"
     with tempfile.TemporaryDirectory() as d:

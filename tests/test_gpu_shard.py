@@ -1,4 +1,5 @@
-"""Token-sharded layer on two GPUs (NCCL): forward output, input gradient and the all-reduced parameter
+"""Token-sharded layer on two GPUs (NCCL or the peer-memory exchange kernels, eager and replayed from a CUDA
+graph): forward output, input gradient and the all-reduced parameter
 gradients of each rank's slice must match the single-GPU layer on the full sequence.  Needs two devices."""
 import os
 import socket
@@ -15,7 +16,68 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, case, ret):
+COMBOS = ((None, False), ("causal", False), (None, True), ("causal", True), ("keypad", False))
+
+
+def _one_combo(rank, world, mask, rope2d, transport, peer):
+    from oracle import pom_oracle as O
+    from pom_b200 import PoM, PoMRoPE, SeqShard
+
+    keypad = mask == "keypad"
+    D, K, E, side = 64, 2, 2, 16
+    N = side * side
+    torch.manual_seed(0)
+    mod = (PoMRoPE(D, K, E, 1, 1, rope_2d=True, max_h=side, max_w=side) if rope2d else PoM(D, K, E, 1, 1))
+    with torch.no_grad():
+        mod.po_coeff.copy_(torch.randn_like(mod.po_coeff) * 0.1)
+    mod = mod.cuda()
+    for p in mod.parameters():
+        p.data = p.data.bfloat16()
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(1, N, D, generator=g).bfloat16().cuda()
+    gy = torch.randn(1, N, D, generator=g).bfloat16().cuda()
+    hw = torch.stack([torch.arange(N) // side, torch.arange(N) % side], 1).cuda()
+    if keypad:
+        mask = (torch.rand(1, N, generator=g) < 0.7).float().cuda()
+    params = list(mod.parameters())
+
+    def run(xs, gys, **kw):
+        xr = xs.clone().requires_grad_(True)
+        y = mod(xr, **kw)
+        grads = torch.autograd.grad(y, [xr] + params, gys)
+        return y.detach(), grads
+
+    kw_full = {"mask": mask}
+    if rope2d:
+        kw_full["positions_hw"] = hw
+    y_full, g_full = run(x, gy, **kw_full)
+
+    n_loc = N // world
+    lo = rank * n_loc
+    kw = {"mask": mask[:, lo:lo + n_loc].contiguous() if keypad else mask,
+          "shard": SeqShard(token_offset=lo, n_global=N, peer=peer)}
+    if rope2d:
+        kw["positions_hw"] = hw[lo:lo + n_loc].contiguous()
+    xs, gys = x[:, lo:lo + n_loc].contiguous(), gy[:, lo:lo + n_loc].contiguous()
+    y_loc, g_loc = run(xs, gys, **kw)
+    if transport == "peer_graph":  # the whole sharded step replayed from a CUDA graph (epochs advance on the device)
+        side_stream = torch.cuda.Stream()
+        with torch.cuda.stream(side_stream):
+            run(xs, gys, **kw)
+        torch.cuda.current_stream().wait_stream(side_stream)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            y_loc, g_loc = run(xs, gys, **kw)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+    errs = [O.rel_errors(y_loc, y_full[:, lo:lo + n_loc])[0], O.rel_errors(g_loc[0], g_full[0][:, lo:lo + n_loc])[0]]
+    errs += [O.rel_errors(a, b)[0] for a, b in zip(g_loc[1:], g_full[1:])]
+    return max(errs)
+
+
+def _worker(rank, world, port, transport, ret):
     import torch.distributed as dist
 
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -23,50 +85,24 @@ def _worker(rank, world, port, case, ret):
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
-        from oracle import pom_oracle as O
-        from pom_b200 import PoM, PoMRoPE, SeqShard
+        from pom_b200 import _abi
 
-        mask, rope2d = case
-        D, K, E, side = 64, 2, 2, 16
-        N = side * side
-        torch.manual_seed(0)
-        mod = (PoMRoPE(D, K, E, 1, 1, rope_2d=True, max_h=side, max_w=side) if rope2d else PoM(D, K, E, 1, 1))
-        with torch.no_grad():
-            mod.po_coeff.copy_(torch.randn_like(mod.po_coeff) * 0.1)
-        mod = mod.cuda()
-        for p in mod.parameters():
-            p.data = p.data.bfloat16()
-        g = torch.Generator().manual_seed(1)
-        x = torch.randn(1, N, D, generator=g).bfloat16().cuda()
-        gy = torch.randn(1, N, D, generator=g).bfloat16().cuda()
-        hw = torch.stack([torch.arange(N) // side, torch.arange(N) % side], 1).cuda()
-        params = list(mod.parameters())
-
-        def run(xs, gys, **kw):
-            xr = xs.clone().requires_grad_(True)
-            y = mod(xr, **kw)
-            grads = torch.autograd.grad(y, [xr] + params, gys)
-            return y.detach(), grads
-
-        kw_full = {"mask": mask}
-        if rope2d:
-            kw_full["positions_hw"] = hw
-        y_full, g_full = run(x, gy, **kw_full)
-
-        n_loc = N // world
-        lo = rank * n_loc
-        kw = {"mask": mask, "shard": SeqShard(token_offset=lo, n_global=N)}
-        if rope2d:
-            kw["positions_hw"] = hw[lo:lo + n_loc].contiguous()
-        y_loc, g_loc = run(x[:, lo:lo + n_loc].contiguous(), gy[:, lo:lo + n_loc].contiguous(), **kw)
-        errs = [O.rel_errors(y_loc, y_full[:, lo:lo + n_loc])[0], O.rel_errors(g_loc[0], g_full[0][:, lo:lo + n_loc])[0]]
-        errs += [O.rel_errors(a, b)[0] for a, b in zip(g_loc[1:], g_full[1:])]
-        ret[rank] = max(errs)
+        peer = None
+        if transport != "nccl":
+            from pom_b200.peer import PeerExchange
+            peer = PeerExchange(slot_floats=4096, flat_floats=1 << 16)
+        worst = {}
+        for mask, rope2d in COMBOS:
+            worst[f"{mask}/{rope2d}"] = _one_combo(rank, world, mask, rope2d, transport, peer)
+        assert _abi.read_status(torch.device("cuda", rank)) == 0, "an exchange wait expired"
+        ret[rank] = worst
+        if peer is not None:
+            peer.close()
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("case", [(None, False), ("causal", False), (None, True), ("causal", True)])
+@pytest.mark.parametrize("case", ["nccl", "peer", "peer_graph"])
 def test_two_gpu_token_sharding_matches_single_gpu(case):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -81,6 +117,11 @@ def test_two_gpu_token_sharding_matches_single_gpu(case):
             p.start()
         for p in procs:
             p.join(300)
-            assert p.exitcode == 0
+        codes = [p.exitcode for p in procs]
+        for p in procs:
+            if p.exitcode is None:
+                p.kill()
+        assert codes == [0, 0], codes
         # both sides are bf16 results of the same kernels; only summation order and rounding of partials differ
-        assert max(ret.values()) < 1.5e-2, dict(ret)
+        for rank_worst in ret.values():
+            assert max(rank_worst.values()) < 1.5e-2, dict(ret)
