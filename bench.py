@@ -221,7 +221,7 @@ def run_reference(args, w, rank):
 
 
 # ------------------------------------------------------------------------------------------- B200 arm
-def build_case(w, rank, world, device):
+def build_case(w, rank, world, device, exchange="nccl"):
     """Module, rotating input sets and call kwargs for this rank."""
     from pom_b200 import PoM, PoMRoPE, SeqShard
 
@@ -254,7 +254,22 @@ def build_case(w, rank, world, device):
             idx = torch.arange(off, off + n_loc)
             kw["positions_hw"] = torch.stack([idx // side, idx % side], 1).to(device)
         if world > 1:
-            kw["shard"] = SeqShard(token_offset=off, n_global=N)
+            peer = None
+            if exchange == "peer":
+                from pom_b200.peer import PeerExchange
+
+                # collective: either every rank maps its peers or (agreed through a reduction) none uses them
+                try:
+                    peer = PeerExchange(slot_floats=max(4096, B * D * E),
+                                        flat_floats=sum(p.numel() for p in mod.parameters()) + 4)
+                    ok = torch.ones(1, device=device)
+                except Exception as e:  # e.g. CUDA IPC not permitted between these processes
+                    print(f"[bench] peer exchange unavailable on rank {rank}: {e}; using NCCL", file=sys.stderr)
+                    ok = torch.zeros(1, device=device)
+                torch.distributed.all_reduce(ok, op=torch.distributed.ReduceOp.MIN)
+                if float(ok.item()) == 0.0:
+                    peer = None
+            kw["shard"] = SeqShard(token_offset=off, n_global=N, peer=peer)
         tokens_local = B * n_loc
     else:
         n_loc = N
@@ -287,6 +302,9 @@ def main():
     ap.add_argument("--defer-weight-grad-reduce", action="store_true",
                     help="token-sharded runs: leave the parameter-gradient all-reduce to the caller (as a data-parallel "
                          "optimizer step would do) instead of doing it inside the layer")
+    ap.add_argument("--exchange", default="peer", choices=["nccl", "peer"],
+                    help="token-sharded runs: carry the cross-rank sums by NCCL calls between kernels, or by the "
+                         "library's own peer-memory kernels (graph-capturable; turns --graph on unless given)")
     ap.add_argument("--tokens", type=int, default=0, help="override the workload's tokens per sample (N)")
     args = ap.parse_args()
     w = dict(WORKLOADS[args.workload])
@@ -330,7 +348,10 @@ def main():
             os.close(saved_fd)
     args.warmup = max(args.warmup, 3)
 
-    mod, host_sets, kw, tokens_local = build_case(w, rank, world, device)
+    mod, host_sets, kw, tokens_local = build_case(w, rank, world, device, args.exchange)
+    peer_on = "shard" in kw and kw["shard"].peer is not None
+    if peer_on and "--graph" not in sys.argv:
+        args.graph = "on"
     if args.defer_weight_grad_reduce and "shard" in kw:
         kw["shard"].reduce_weight_grads = False
     params = list(mod.parameters())
@@ -464,6 +485,7 @@ def main():
                        "parallelism": f"{w['shard']}-shard x{world}",
                        "l2": "3 rotating input sets (>= 450 MB) plus ~1 GB of intermediates per step, larger than the 126 MB L2",
                        "cuda_graph": use_graph,
+                       "exchange": ("peer-memory kernels" if peer_on else "nccl") if w["shard"] == "token" and world > 1 else None,
                        "weight_grad_allreduce_in_timed_region": bool(w["shard"] == "token" and world > 1
                                                                      and not args.defer_weight_grad_reduce)},
             "roofline": roof,

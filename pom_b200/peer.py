@@ -46,28 +46,42 @@ class PeerExchange:
         self.mem = torch.zeros(max(total, 32 << 20), dtype=torch.uint8, device=self.device)
         torch.cuda.synchronize(self.device)
 
+        # Every step below is agreed on by all ranks, so a failure on one of them raises everywhere instead of
+        # leaving the others waiting in a collective.
         handle = (C.c_ubyte * _abi.PEER_HANDLE_BYTES)()
         offset = C.c_ulonglong(0)
-        _abi.check(lib.pom_peer_export(ptr(self.mem), handle, C.byref(offset)), "pom_peer_export")
-        mine = (bytes(handle), int(offset.value))
+        rc = lib.pom_peer_export(ptr(self.mem), handle, C.byref(offset))
+        mine = (bytes(handle), int(offset.value)) if rc == 0 else None
         everyone = [None] * self.world
         dist.all_gather_object(everyone, mine, group=group)
+        if any(e is None for e in everyone):
+            raise RuntimeError("CUDA IPC export of the exchange buffer failed on rank(s) "
+                               f"{[r for r, e in enumerate(everyone) if e is None]}")
 
         self._opened = []
         self.comm = PeerComm()
         self.comm.rank, self.comm.world = self.rank, self.world
         self.comm.slot_floats, self.comm.flat_floats = slot_floats, flat_floats
+        mapped = True
         for r, (h, off) in enumerate(everyone):
             if r == self.rank:
                 self.comm.base[r] = self.mem.data_ptr()
                 continue
             buf = (C.c_ubyte * _abi.PEER_HANDLE_BYTES).from_buffer_copy(h)
             base = C.c_void_p()
-            _abi.check(lib.pom_peer_open(buf, C.byref(base)), "pom_peer_open")
+            if lib.pom_peer_open(buf, C.byref(base)) != 0:
+                mapped = False
+                break
             self._opened.append(base.value)
             self.comm.base[r] = base.value + off
-        # nobody pushes before every buffer is zeroed and mapped
-        dist.barrier(group=group)
+        verdicts = [None] * self.world
+        dist.all_gather_object(verdicts, mapped, group=group)  # also: nobody pushes before every buffer is mapped
+        if not all(verdicts):
+            for base in self._opened:
+                lib.pom_peer_close(C.c_void_p(base))
+            self._opened = []
+            raise RuntimeError(f"mapping a peer's exchange buffer failed on rank(s) "
+                               f"{[r for r, v in enumerate(verdicts) if not v]}")
         self.flat = self.mem[self._flat_off:self._flat_off + 4 * flat_floats].view(torch.float32)
 
     # ------------------------------------------------------------------ exchanges
