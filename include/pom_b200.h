@@ -327,6 +327,14 @@ int pom_select_heads_bwd(const pom_select_heads_args* a, void* stream);
  *   h_new[b,:] = (n_past * h_past[b,:] + h_cur[b,:]) / (n_past + 1)        (fp32, B*P elements) */
 int pom_state_merge(const float* h_past, const float* h_cur, float* h_new, float n_past, int64_t count, void* stream);
 
+/* Block-causal aggregate over equal frames: the single-pass form of calling state_forward once per frame
+ * (reference pom/pom.py:251-259, where every call weighs equally) and of a block-lower-triangular (B, N, N) mask
+ * (pom/pom.py:41-45, 98-99).  in/out (B, F, P) fp32, in = per-frame means.
+ *   adjoint == 0:  out[b,f,:] = (1/(f+1)) * sum_{g<=f} in[b,g,:]
+ *   adjoint != 0:  out[b,g,:] = sum_{f>=g} in[b,f,:] / (f+1)          (gradient of the above)
+ * in and out may be the same buffer. */
+int pom_frame_prefix_mean(const float* in, float* out, int32_t B, int32_t F, int32_t P, int32_t adjoint, void* stream);
+
 /* Asynchronous zero fill of `bytes` bytes (cudaMemsetAsync on the stream); used for split-K accumulators. */
 int pom_fill_zero(void* dst, int64_t bytes, void* stream);
 

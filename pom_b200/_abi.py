@@ -180,6 +180,7 @@ _SIGNATURES = {
     "pom_select_heads_fwd": (C.c_int, [C.POINTER(SelectHeadsArgs), C.c_void_p]),
     "pom_select_heads_bwd": (C.c_int, [C.POINTER(SelectHeadsArgs), C.c_void_p]),
     "pom_state_merge": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int64, C.c_void_p]),
+    "pom_frame_prefix_mean": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "pom_fill_zero": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p]),
     "pom_cast_f32_to_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "pom_cast_bf16_to_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),

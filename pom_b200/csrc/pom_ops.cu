@@ -724,6 +724,25 @@ __global__ void state_merge_kernel(const float* hp, const float* hc, float* hn, 
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i < count) hn[i] = (n_past * hp[i] + hc[i]) / (n_past + 1.f);
 }
+// Running mean over frames: forward out[b,f,:] = (1/(f+1)) sum_{g<=f} in[b,g,:];
+// adjoint out[b,g,:] = sum_{f>=g} in[b,f,:]/(f+1).  One thread per (b, p).
+__global__ void frame_prefix_kernel(const float* __restrict__ in, float* __restrict__ out, int F, int P, int adjoint) {
+  const int p = blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= P) return;
+  const long long base = static_cast<long long>(blockIdx.y) * F * P + p;
+  float acc = 0.f;
+  if (!adjoint) {
+    for (int f = 0; f < F; ++f) {
+      acc += in[base + static_cast<long long>(f) * P];
+      out[base + static_cast<long long>(f) * P] = acc / static_cast<float>(f + 1);
+    }
+  } else {
+    for (int f = F - 1; f >= 0; --f) {
+      acc += in[base + static_cast<long long>(f) * P] / static_cast<float>(f + 1);
+      out[base + static_cast<long long>(f) * P] = acc;
+    }
+  }
+}
 __global__ void cast_f32_bf16_kernel(const float* __restrict__ s, __nv_bfloat16* __restrict__ d, long long count) {
   const long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
   if (i + 4 <= count && ((reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(d)) & 15) == 0) {
@@ -1188,6 +1207,16 @@ int pom_state_merge(const float* h_past, const float* h_cur, float* h_new, float
   if (count <= 0) return POM_ERR_BAD_SHAPE;
   state_merge_kernel<<<static_cast<unsigned>(ceil_div(count, 256)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       h_past, h_cur, h_new, n_past, count);
+  count_launch();
+  return check_launch();
+}
+
+int pom_frame_prefix_mean(const float* in, float* out, int32_t B, int32_t F, int32_t P, int32_t adjoint, void* stream) {
+  if (!in || !out) return POM_ERR_NULL;
+  if (B <= 0 || F <= 0 || P <= 0) return POM_ERR_BAD_SHAPE;
+  if (B > 65535) return POM_ERR_TOO_LARGE;
+  dim3 grid(static_cast<unsigned>(ceil_div(P, 128)), static_cast<unsigned>(B));
+  frame_prefix_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(in, out, F, P, adjoint);
   count_launch();
   return check_launch();
 }

@@ -102,6 +102,15 @@ class SeqShard:
         return ops.reduce_partials(part.transpose(0, 1).contiguous())
 
 
+@dataclass(frozen=True)
+class BlockCausal:
+    """``mask=BlockCausal(frame_len)``: token m sees every token of its own and of earlier frames, all frames
+    ``frame_len`` tokens long.  Same result as the (B, N, N) block-lower-triangular 0/1 mask (reference
+    pom/pom.py:41-45, 98-99) and as one ``state_forward`` call per frame (pom/pom.py:251-259), computed in one
+    pass: per-frame means, then a running mean over frames."""
+    frame_len: int
+
+
 @dataclass
 class LayerSpec:
     """Non-tensor arguments of one layer call."""
@@ -114,6 +123,7 @@ class LayerSpec:
     n_past: Optional[float] = None   # state_forward: number of previous calls (None = plain forward)
     want_state: bool = False
     n_sel_heads: int = 1
+    frames: int = 1                  # > 1: the batch rows are (sample, frame) pairs of a block-causal sequence
 
 
 def _f32(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
@@ -222,6 +232,8 @@ class _PoMLayer(torch.autograd.Function):
                 H = shard.sum_partials(S_part, denom=denom, scale=scale)
             else:
                 H = ops.reduce_partials(S_part, denom=denom, scale=scale)
+            if spec.frames > 1:
+                H = ops.frame_prefix_mean(H, spec.frames)
             if spec.n_past is not None and h_past is not None:
                 H = ops.state_merge(_f32(h_past.reshape(B, P).contiguous()), H, spec.n_past)
 
@@ -329,6 +341,8 @@ class _PoMLayer(torch.autograd.Function):
                 dH = ops.reduce_partials(torch.stack([dH, _f32(dh_state.reshape(B, P).contiguous())], dim=1))
             if shard is not None:
                 shard.all_reduce(dH)
+            if spec.frames > 1:
+                dH = ops.frame_prefix_mean(dH.contiguous(), spec.frames, adjoint=True)
             scale = 1.0 if denom is not None else 1.0 / n_glob
             if spec.n_past is not None and ctx.h_past_dtype is not None:
                 # H = (n_past * h_past + h_cur) / (n_past + 1)
@@ -393,6 +407,18 @@ def _ones(b: int, n: int, device) -> torch.Tensor:
 def pom_layer(xq, xc, w_qc, se_bias, coeff, w_ag, mask=None, h_past=None, spec: Optional[LayerSpec] = None,
               residual=None):
     """Whole layer; ``residual`` (B, T, D), bf16 only, is added to the output inside the output projection."""
+    if spec is not None and spec.frames > 1:
+        F = spec.frames
+        B, T, D = xq.shape
+        if (spec.rope_ctx is not None or spec.rope_qry is not None or spec.shard is not None or mask is not None
+                or spec.want_state or spec.n_past is not None or spec.mask_kind != "none"):
+            raise NotImplementedError("BlockCausal is not combined with rotary embedding, other masks, token sharding or state")
+        if T % F or (xc is not None and xc.shape[1] != T):
+            raise ValueError("BlockCausal needs equal query and context lengths, a multiple of frame_len")
+        fold = lambda t: None if t is None else t.contiguous().view(B * F, T // F, t.shape[-1])
+        y, h = _PoMLayer.apply(fold(xq), fold(xc) if xc is not None else fold(xq), w_qc, se_bias, coeff, w_ag, None,
+                               None, spec, fold(residual))
+        return y.view(B, T, -1), h
     y, h = _PoMLayer.apply(xq, xc if xc is not None else xq, w_qc, se_bias, coeff, w_ag, mask, h_past, spec, residual)
     return y, h
 
@@ -451,6 +477,8 @@ def _mask_kind(mask) -> str:
         if mask == "causal":
             return "causal"
         raise ValueError('Unsupported mask: expected None, "causal", or a 2/3-D tensor.')
+    if isinstance(mask, BlockCausal):
+        return "block"
     if isinstance(mask, torch.Tensor):
         if mask.dim() == 2:
             return "keypad"

@@ -369,6 +369,18 @@ def state_merge(h_past: torch.Tensor, h_cur: torch.Tensor, n_past: float) -> tor
     return out
 
 
+def frame_prefix_mean(h: torch.Tensor, frames: int, adjoint: bool = False) -> torch.Tensor:
+    """(B·F, P) fp32 per-frame means -> running mean over the frames of each sample (or its adjoint)."""
+    _require_cuda(h)
+    rows, P = h.shape
+    if h.dtype != torch.float32 or not h.is_contiguous() or rows % frames:
+        raise ValueError("expected a contiguous fp32 (B*F, P) tensor")
+    out = torch.empty_like(h)
+    _abi.check(_abi.lib().pom_frame_prefix_mean(ptr(h), ptr(out), rows // frames, frames, P, int(adjoint),
+                                                _abi.stream_ptr()), "pom_frame_prefix_mean")
+    return out
+
+
 def zeros_f32(n: int, device) -> torch.Tensor:
     """Flat fp32 buffer of n zeros (allocation by PyTorch, fill by cudaMemsetAsync on the current stream)."""
     out = torch.empty((n,), dtype=torch.float32, device=device)

@@ -51,8 +51,13 @@ class PoM(nn.Module):
     # ------------------------------------------------------------------ helpers
     def _spec(self, xq, xc, mask, shard: Optional[SeqShard]) -> Tuple[LayerSpec, Optional[torch.Tensor]]:
         kind = _mask_kind(mask)
+        frames = 1
+        if kind == "block":
+            if mask.frame_len <= 0 or xq.shape[1] % mask.frame_len:
+                raise ValueError(f"sequence length {xq.shape[1]} is not a multiple of frame_len {mask.frame_len}")
+            kind, frames = "none", xq.shape[1] // mask.frame_len
         spec = LayerSpec(degree=self.order, mask_kind=kind, self_mixing=(xc is None or xc is xq), shard=shard,
-                         n_sel_heads=self.n_sel_heads)
+                         n_sel_heads=self.n_sel_heads, frames=frames)
         return spec, (mask if kind in ("keypad", "full") else None)
 
     def _finish(self, y: torch.Tensor) -> torch.Tensor:
@@ -60,13 +65,15 @@ class PoM(nn.Module):
 
     # ------------------------------------------------------------------ API
     def forward(self, xq: torch.Tensor, xc: Optional[torch.Tensor] = None, mask=None,
-                shard: Optional[SeqShard] = None) -> torch.Tensor:
-        """xq (B, T, D) queries; xc (B, N, D) context (None: self-mixing); mask None, "causal", (B, N) or (B, T, N).
+                shard: Optional[SeqShard] = None, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """xq (B, T, D) queries; xc (B, N, D) context (None: self-mixing); mask None, "causal", (B, N), (B, T, N) or ``BlockCausal(frame_len)`` (extension).
 
-        ``shard`` (extension) declares that xq/xc are this rank's token slice of a longer sequence.
+        ``shard`` (extension) declares that xq/xc are this rank's token slice of a longer sequence;
+        ``residual`` (extension, bf16) is added to the output inside the output projection's epilogue.
         """
         spec, m = self._spec(xq, xc, mask, shard)
-        y, _ = pom_layer(xq, xc, self.qc_proj.weight, self.se_bias, self.po_coeff, self.ag_proj.weight, m, None, spec)
+        y, _ = pom_layer(xq, xc, self.qc_proj.weight, self.se_bias, self.po_coeff, self.ag_proj.weight, m, None, spec,
+                         residual)
         return self._finish(y)
 
     def state_forward(self, xq: torch.Tensor, xc: Optional[torch.Tensor] = None,

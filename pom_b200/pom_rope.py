@@ -110,6 +110,8 @@ class PoMRoPE(PoM):
         0..N-1), ``positions_hw`` (T, 2) / ``ctx_positions_hw`` (N, 2) for 2-D tables."""
         self_mixing = xc is None or xc is xq
         kind = _mask_kind(mask)
+        if kind == "block":
+            raise NotImplementedError("BlockCausal is not combined with rotary embedding")
         T = xq.shape[1]
         N = T if self_mixing else xc.shape[1]
         cpos = ctx_positions if ctx_positions is not None else (positions if self_mixing else None)

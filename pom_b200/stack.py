@@ -16,6 +16,7 @@ import torch
 import torch.nn as nn
 
 from . import ops
+from .functional import BlockCausal
 from .pom import PoM
 
 
@@ -44,6 +45,22 @@ class PoMStack(nn.Module):
             u = ops.gemm(h2, self.ffn_in[i].weight, act="gelu")
             h = ops.gemm(u, self.ffn_out[i].weight, residual=h2).view(B, L, D)
         return h, states
+
+    @torch.no_grad()
+    def forward_single_pass(self, x: torch.Tensor, frame_len: int) -> torch.Tensor:
+        """Same result as :meth:`forward`, all frames at once: each mixer runs with ``BlockCausal(frame_len)``, so
+        every GEMM sees the whole (B·N)-row batch instead of one frame's rows."""
+        if x.dtype != torch.bfloat16 or not x.is_cuda:
+            raise TypeError("PoMStack runs on CUDA bfloat16 tensors")
+        B, N, D = x.shape
+        mask = BlockCausal(frame_len)
+        h = x.contiguous()
+        for i, mixer in enumerate(self.mixers):
+            y = mixer(h, None, mask, residual=h)
+            h2 = y.view(B * N, D)
+            u = ops.gemm(h2, self.ffn_in[i].weight, act="gelu")
+            h = ops.gemm(u, self.ffn_out[i].weight, residual=h2).view(B, N, D)
+        return h
 
     @torch.no_grad()
     def forward(self, x: torch.Tensor, frame_len: int) -> torch.Tensor:

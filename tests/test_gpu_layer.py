@@ -117,6 +117,38 @@ def test_bf16_multi_head_gating_against_oracle(mask, rope):
         assert_close(grads[k], w, BF16_TOL, f"d_{k}")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("cross", [False, True])
+def test_block_causal_fast_path_matches_block_triangular_mask(dtype, cross):
+    """``BlockCausal(L)`` (per-frame means + running mean over frames) against the oracle run with the explicit
+    (B, N, N) block-lower-triangular mask: outputs and every gradient."""
+    from pom_b200 import BlockCausal
+
+    B, F, L, D, K, E = 2, 5, 48, 64, 3, 2
+    N = F * L
+    cfg, params, x, gy = _seeded_case(B, N, D, K, E, seed=13, coeff_scale=0.1, bias_scale=0.3)
+    xc = torch.randn(B, N, D, generator=torch.Generator().manual_seed(14)) if cross else None
+    if dtype == torch.bfloat16:
+        params = {k: O.bf16_round(v) for k, v in params.items()}
+        x, gy = O.bf16_round(x), O.bf16_round(gy)
+        xc = O.bf16_round(xc) if cross else None
+    tol = FP32_TOL if dtype == torch.float32 else BF16_TOL
+    want_y, want_g = oracle_run(cfg, params, x, xc, {"mask": O.block_causal_mask(N, L, B)}, gy)
+    mod = make_cuda_module(cfg, params, dtype)
+    y, grads = cuda_run(mod, x, xc, {"mask": BlockCausal(L)}, gy, dtype)
+    assert_close(y, want_y, tol, "y")
+    for k, w in want_g.items():
+        assert_close(grads[k], w, 2 * tol if dtype == torch.float32 else tol, f"d_{k}")
+
+
+def test_block_causal_rejects_ragged_lengths():
+    from pom_b200 import BlockCausal, PoM
+
+    mod = PoM(64, 2, 2, 1, 1).cuda()
+    with pytest.raises(ValueError):
+        mod(torch.randn(1, 100, 64, device="cuda"), mask=BlockCausal(48))
+
+
 @pytest.mark.parametrize("rope", [None, "2d"])
 def test_block_causal_mask_equals_frame_loop(rope):
     """A (B, N, N) block-lower-triangular mask reproduces state_forward's frame loop when all frames have
@@ -255,6 +287,9 @@ def test_pom_stack_matches_oracle_frame_loop():
         p.data = p.data.bfloat16()
     got = stack(x.cuda().bfloat16(), L)
     assert_close(got, want, 3 * BF16_TOL, "stack output")  # bf16 residual stream over 3 layers x 4 frames
+    one_pass = stack.forward_single_pass(x.cuda().bfloat16(), L)
+    assert_close(one_pass, want, 3 * BF16_TOL, "single-pass block-causal stack output")
+    assert_close(one_pass, got, 3 * BF16_TOL, "single pass vs frame loop")
 
 
 def test_token_causal_long_sequence_against_linear_time_oracle():
