@@ -2,8 +2,9 @@
 running on the B200 kernels of this package.
 
 Constructor arguments, parameter names (``qc_proj.weight``, ``se_bias``, ``po_coeff``,
-``ag_proj.weight``) and their creation order are those of the reference, so a given
-``torch.manual_seed`` produces the same weights and checkpoints interchange.
+``ag_proj.weight``; with ``n_groups > 1``: ``po_proj.weight``, ``se_proj.weight``, ``se_proj.bias``) and their
+creation order are those of the reference, so a given ``torch.manual_seed`` produces the same weights and
+checkpoints interchange.
 """
 from __future__ import annotations
 
@@ -12,7 +13,8 @@ from typing import Any, Dict, Optional, Tuple
 import torch
 import torch.nn as nn
 
-from .functional import LayerSpec, SeqShard, _mask_kind, pom_layer
+from . import ops
+from .functional import LayerSpec, SeqShard, _f32, _mask_kind, _ones, pom_layer
 
 
 class PoM(nn.Module):
@@ -22,7 +24,10 @@ class PoM(nn.Module):
         dim:         input/output feature dimension D.
         degree:      polynomial degree K (1..16).
         expand:      channel expansion; the polynomial features have P = expand * dim channels.
-        n_groups:    must be 1 (grouped projections are not implemented by the CUDA path).
+        n_groups:    > 1: the polynomial projection is a grouped 1x1 convolution (input slice i feeds output
+                     slice i) and the gate projection a separate biased Linear, as in the reference.  The layer
+                     runs the grouped projection as one dense tensor-core GEMM on the block-diagonal weight
+                     assembled per call (a copy; no arithmetic).
         n_sel_heads: 0 or 1: one gate value per channel; > 1: one gate value per head, shared by the
                      dim*expand / n_sel_heads channels of that head (bf16 needs a multiple of 8 heads).
         bias:        add a bias to the output projection.
@@ -32,8 +37,6 @@ class PoM(nn.Module):
         super().__init__()
         assert dim % n_groups == 0, "dim must be divisible by n_groups"
         assert n_sel_heads <= 1 or dim * expand % n_sel_heads == 0, "dim * expand must be divisible by n_sel_heads"
-        if n_groups > 1:
-            raise NotImplementedError("n_groups > 1 (grouped projection) is not implemented by the CUDA path")
         self.dim = dim
         self.order = degree
         self.order_expand = expand
@@ -42,9 +45,15 @@ class PoM(nn.Module):
         self.head_dim = dim * expand // max(n_sel_heads, 1)
         self._po_dim = expand * dim
         self._se_dim = n_sel_heads if n_sel_heads > 1 else expand * dim
-        # creation order matters for seeded initialisation: qc_proj, se_bias, po_coeff, ag_proj
-        self.qc_proj = nn.Linear(dim, self._po_dim + self._se_dim, bias=False)
-        self.se_bias = nn.Parameter(torch.zeros(self._se_dim))
+        # creation order matters for seeded initialisation: (qc_proj, se_bias | po_proj, se_proj), po_coeff, ag_proj
+        if n_groups > 1:
+            if bias:
+                raise NotImplementedError("a bias on the grouped polynomial projection is not implemented by the CUDA path")
+            self.po_proj = nn.Conv1d(dim, expand * dim, kernel_size=1, bias=False, groups=n_groups)
+            self.se_proj = nn.Linear(dim, self._se_dim, bias=True)
+        else:
+            self.qc_proj = nn.Linear(dim, self._po_dim + self._se_dim, bias=False)
+            self.se_bias = nn.Parameter(torch.zeros(self._se_dim))
         self.po_coeff = nn.Parameter(torch.randn(dim * expand, degree).clamp(-0.001, 0.001))
         self.ag_proj = nn.Linear(expand * dim, dim, bias=bias)
 
@@ -60,6 +69,17 @@ class PoM(nn.Module):
                          n_sel_heads=self.n_sel_heads, frames=frames)
         return spec, (mask if kind in ("keypad", "full") else None)
 
+    def _weights(self) -> Tuple[torch.Tensor, torch.Tensor]:
+        """(P + S, D) projection weight and (S,) gate bias.  Grouped: the (P, D/g, 1) convolution weight is laid
+        out as its block-diagonal (P, D) matrix (reference pom/pom.py:180-183, 203-205); gradients flow back
+        through the copy to the blocks."""
+        if self.n_groups == 1:
+            return self.qc_proj.weight, self.se_bias
+        g = self.n_groups
+        w = self.po_proj.weight.squeeze(-1)
+        dense = torch.block_diag(*w.view(g, self._po_dim // g, self.dim // g).unbind(0))
+        return torch.cat([dense, self.se_proj.weight], dim=0), self.se_proj.bias
+
     def _finish(self, y: torch.Tensor) -> torch.Tensor:
         return y if self.ag_proj.bias is None else y + self.ag_proj.bias
 
@@ -72,8 +92,8 @@ class PoM(nn.Module):
         ``residual`` (extension, bf16) is added to the output inside the output projection's epilogue.
         """
         spec, m = self._spec(xq, xc, mask, shard)
-        y, _ = pom_layer(xq, xc, self.qc_proj.weight, self.se_bias, self.po_coeff, self.ag_proj.weight, m, None, spec,
-                         residual)
+        w_qc, se_bias = self._weights()
+        y, _ = pom_layer(xq, xc, w_qc, se_bias, self.po_coeff, self.ag_proj.weight, m, None, spec, residual)
         return self._finish(y)
 
     def state_forward(self, xq: torch.Tensor, xc: Optional[torch.Tensor] = None,
@@ -99,14 +119,31 @@ class PoM(nn.Module):
             spec.n_past = float(n_past)
         else:
             h_past = None
-        y, h = pom_layer(xq, xc, self.qc_proj.weight, self.se_bias, self.po_coeff, self.ag_proj.weight, None, h_past,
-                         spec, residual)
+        w_qc, se_bias = self._weights()
+        y, h = pom_layer(xq, xc, w_qc, se_bias, self.po_coeff, self.ag_proj.weight, None, h_past, spec, residual)
         return self._finish(y), {"h": h, "n": n_past + 1}
 
     @torch.no_grad()
-    def ar_forward(self, xq: torch.Tensor, state: Dict[str, Any]):
-        raise NotImplementedError("ar_forward is not implemented by the CUDA path (the reference version does not "
-                                  "aggregate either; use state_forward)")
+    def ar_forward(self, xq: torch.Tensor, state: Dict[str, Any]) -> Tuple[torch.Tensor, Dict[str, Any]]:
+        """Autoregressive forward exactly as the reference defines it (pom/pom.py:264-275): no activation,
+        polynomial or aggregation — the gate of each token multiplies that token's raw projection — and the
+        returned state holds that projection as 'h' and the advanced token count.  For a running aggregate over
+        chunks use :meth:`state_forward`."""
+        if not xq.is_cuda:
+            raise RuntimeError("pom_b200 has no CPU path: move the module and its inputs to a CUDA device")
+        B, T, D = xq.shape
+        P, S = self._po_dim, self._se_dim
+        w_qc, se_bias = self._weights()
+        hs = ops.gemm(xq.contiguous().view(B * T, D), w_qc.contiguous()).view(B, T, P + S)
+        hp, z = hs[..., :P], hs[..., P:]
+        bias32 = _f32(se_bias.contiguous())
+        if self.n_sel_heads > 1:
+            s32 = _f32(ops.select_fwd(z, bias32, _ones(B, S, xq.device)))
+            sh = ops.select_heads_fwd(s32, hp, xq.dtype)
+        else:
+            sh = ops.select_fwd(z, bias32, hp)
+        y = ops.gemm(sh.view(B * T, P), self.ag_proj.weight).view(B, T, D)
+        return self._finish(y), {"max_len": state["max_len"], "h": hp, "n": state["n"] + T}
 
     def reset(self, state: Dict[str, Any]) -> Dict[str, Any]:
         state["h"] = 0.0

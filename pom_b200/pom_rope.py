@@ -121,6 +121,7 @@ class PoMRoPE(PoM):
         rope_c = rope_q if same else self._rope_spec(N, cpos, cpos_hw, xq.device)
         spec = LayerSpec(degree=self.order, mask_kind=kind, self_mixing=self_mixing, rope_ctx=rope_c, rope_qry=rope_q,
                          shard=shard, n_sel_heads=self.n_sel_heads)
-        y, _ = pom_layer(xq, xc, self.qc_proj.weight, self.se_bias, self.po_coeff, self.ag_proj.weight,
+        w_qc, se_bias = self._weights()
+        y, _ = pom_layer(xq, xc, w_qc, se_bias, self.po_coeff, self.ag_proj.weight,
                          mask if kind in ("keypad", "full") else None, None, spec)
         return self._finish(y)

@@ -92,6 +92,35 @@ def main(ref_root: str) -> None:
     record("pom_heads4_none", mh, lambda: dict(mask=None), x, cfg=cfg_h)
     record("pom_heads4_causal", mh, lambda: dict(mask="causal"), x, cfg=cfg_h)
 
+    # grouped polynomial projection (n_groups = 2): po_proj is a grouped 1x1 convolution, se_proj a biased Linear
+    def make_grouped(cls, heads=1, seed=3, **kw):
+        torch.manual_seed(seed)
+        mg = cls(D, K, E, 2, heads, **kw)
+        with torch.no_grad():
+            torch.manual_seed(seed + 100)
+            mg.po_coeff.copy_(torch.randn_like(mg.po_coeff) * 0.1)
+            mg.se_proj.bias.copy_(torch.randn_like(mg.se_proj.bias) * 0.5)
+        return mg
+
+    cfg_g = dict(dim=D, degree=K, expand=E, heads=1, groups=2)
+    mg = make_grouped(PoM)
+    record("pom_groups2_none", mg, lambda: dict(mask=None), x, cfg=cfg_g)
+    record("pom_groups2_causal", mg, lambda: dict(mask="causal"), x, cfg=cfg_g)
+    record("pom_groups2_cross_mask2d", mg, lambda: dict(mask=m2c), xq_cross, xc=x, cfg=cfg_g)
+    mgh = make_grouped(PoM, heads=4)
+    record("pom_groups2_heads4_none", mgh, lambda: dict(mask=None), x, cfg=dict(cfg_g, heads=4))
+
+    # ar_forward as the reference defines it (no aggregation: the gate multiplies the raw projection)
+    with torch.no_grad():
+        y_ar, st_ar = m.ar_forward(x, {"max_len": 64, "h": 0.0, "n": 5})
+        yh_ar, sth_ar = mh.ar_forward(x, {"max_len": 64, "h": 0.0, "n": 0})
+    cases["pom_ar"] = {"cfg": cfg, "params": {k: v.detach().clone() for k, v in m.state_dict().items()},
+                       "xq": x.clone(), "y": y_ar.clone(), "h": st_ar["h"].clone(), "n": int(st_ar["n"]),
+                       "max_len": st_ar["max_len"]}
+    cases["pom_ar_heads4"] = {"cfg": cfg_h, "params": {k: v.detach().clone() for k, v in mh.state_dict().items()},
+                              "xq": x.clone(), "y": yh_ar.clone(), "h": sth_ar["h"].clone(), "n": int(sth_ar["n"]),
+                              "max_len": sth_ar["max_len"]}
+
     # state_forward over three frames of unequal length
     frames = [x[:, :8], x[:, 8:14], x[:, 14:]]
     state, ys = None, []

@@ -8,6 +8,12 @@ FP32_TOL = 1e-4   # norm-relative and max-normalised bound of the fp32 mode
 BF16_TOL = 2e-2   # bound for bf16 storage with fp32 accumulation
 
 PARAM_ORDER = ["qc_proj.weight", "se_bias", "po_coeff", "ag_proj.weight"]
+GROUPED_PARAM_ORDER = ["po_proj.weight", "se_proj.weight", "se_proj.bias", "po_coeff", "ag_proj.weight"]
+
+
+def param_order(params):
+    """Trainable-parameter names of a case: the fused layout, or the grouped one when po_proj is present."""
+    return GROUPED_PARAM_ORDER if "po_proj.weight" in params else PARAM_ORDER
 
 
 def rope_cfg(cfg):
@@ -23,16 +29,16 @@ def make_cuda_module(cfg, params, dtype, device="cuda"):
     from pom_b200 import PoM, PoMRoPE
 
     r = cfg.get("rope")
+    groups = cfg.get("groups", 1)
     if r is None:
-        mod = PoM(cfg["dim"], cfg["degree"], cfg["expand"], 1, cfg["heads"])
+        mod = PoM(cfg["dim"], cfg["degree"], cfg["expand"], groups, cfg["heads"])
     else:
-        mod = PoMRoPE(cfg["dim"], cfg["degree"], cfg["expand"], 1, cfg["heads"], rope_2d=r["two_d"],
+        mod = PoMRoPE(cfg["dim"], cfg["degree"], cfg["expand"], groups, cfg["heads"], rope_2d=r["two_d"],
                       max_seq_len=r.get("max_seq_len", 4096), max_h=r.get("max_h", 64), max_w=r.get("max_w", 64))
     with torch.no_grad():
-        mod.qc_proj.weight.copy_(params["qc_proj.weight"])
-        mod.se_bias.copy_(params["se_bias"])
-        mod.po_coeff.copy_(params["po_coeff"])
-        mod.ag_proj.weight.copy_(params["ag_proj.weight"])
+        named = dict(mod.named_parameters())
+        for k in param_order(params):
+            named[k].copy_(params[k])
     mod = mod.to(device)
     for p in mod.parameters():
         p.data = p.data.to(dtype)
@@ -41,7 +47,8 @@ def make_cuda_module(cfg, params, dtype, device="cuda"):
 
 def oracle_run(cfg, params, xq, xc, kwargs, gy):
     """Oracle forward + gradients in fp32 on the given (already rounded) CPU tensors."""
-    ps = {k: params[k].clone().float().requires_grad_(True) for k in PARAM_ORDER}
+    order = param_order(params)
+    ps = {k: params[k].clone().float().requires_grad_(True) for k in order}
     model = O.OraclePoM(ps, cfg["degree"], cfg["expand"], cfg["heads"], rope_cfg(cfg))
     xq = xq.clone().float().requires_grad_(True)
     ins = [xq]
@@ -49,8 +56,8 @@ def oracle_run(cfg, params, xq, xc, kwargs, gy):
         xc = xc.clone().float().requires_grad_(True)
         ins.append(xc)
     y = model.forward(xq, xc, **kwargs)
-    grads = torch.autograd.grad(y, ins + [ps[k] for k in PARAM_ORDER], gy.float())
-    names = [f"in{i}" for i in range(len(ins))] + PARAM_ORDER
+    grads = torch.autograd.grad(y, ins + [ps[k] for k in order], gy.float())
+    names = [f"in{i}" for i in range(len(ins))] + order
     return y.detach(), dict(zip(names, grads))
 
 
@@ -62,9 +69,11 @@ def cuda_run(mod, xq, xc, kwargs, gy, dtype, device="cuda"):
         ins.append(xc)
     kw = {k: (v.to(device) if torch.is_tensor(v) else v) for k, v in kwargs.items()}
     y = mod(xq, xc, **kw) if xc is not None else mod(xq, **kw)
-    ps = [dict(mod.named_parameters())[k] for k in PARAM_ORDER]
+    named = dict(mod.named_parameters())
+    order = param_order(named)
+    ps = [named[k] for k in order]
     grads = torch.autograd.grad(y, ins + ps, gy.to(device=device, dtype=dtype))
-    names = [f"in{i}" for i in range(len(ins))] + PARAM_ORDER
+    names = [f"in{i}" for i in range(len(ins))] + order
     return y.detach(), dict(zip(names, grads))
 
 

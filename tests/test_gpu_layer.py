@@ -4,7 +4,7 @@ import pytest
 import torch
 
 from oracle import pom_oracle as O
-from tests.helpers import (BF16_TOL, FP32_TOL, PARAM_ORDER, assert_close, assert_status_clean, cuda_run,
+from tests.helpers import (BF16_TOL, FP32_TOL, PARAM_ORDER, param_order, assert_close, assert_status_clean, cuda_run,
                            make_cuda_module, oracle_run)
 
 pytestmark = pytest.mark.gpu
@@ -15,9 +15,10 @@ LAYER_CASES = ["pom_none", "pom_causal", "pom_mask2d", "pom_mask3d", "pom_cross"
 
 
 HEAD_CASES = ["pom_heads4_none", "pom_heads4_causal", "rope2d_heads4_none", "rope1d_heads4_causal"]
+GROUP_CASES = ["pom_groups2_none", "pom_groups2_causal", "pom_groups2_cross_mask2d", "pom_groups2_heads4_none"]
 
 
-@pytest.mark.parametrize("name", LAYER_CASES + HEAD_CASES)
+@pytest.mark.parametrize("name", LAYER_CASES + HEAD_CASES + GROUP_CASES)
 def test_fp32_layer_matches_reference_vectors(golden, name):
     case = golden[name]
     mod = make_cuda_module(case["cfg"], case["params"], torch.float32)
@@ -26,15 +27,38 @@ def test_fp32_layer_matches_reference_vectors(golden, name):
     n_in = 1 if case["xc"] is None else 2
     for i in range(n_in):
         assert_close(grads[f"in{i}"], case["grads"][f"d_in{i}"], FP32_TOL, f"{name} d_in{i}")
-    for k in PARAM_ORDER:
+    for k in param_order(case["params"]):
         assert_close(grads[k], case["grads"]["d_" + k], FP32_TOL, f"{name} d_{k}")
 
 
-@pytest.mark.parametrize("name", LAYER_CASES)
+@pytest.mark.parametrize("name", ["pom_ar", "pom_ar_heads4"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_ar_forward_matches_reference_vectors(golden, name, dtype):
+    """ar_forward as the reference defines it (gate x raw projection per token, state = that projection)."""
+    if dtype == torch.bfloat16 and name == "pom_ar_heads4":
+        pytest.skip("bf16 multi-head gating needs a multiple of 8 heads (16-byte rows of the gate projection)")
+    case = golden[name]
+    params, x = case["params"], case["xq"]
+    want_y, want_h = case["y"], case["h"]
+    tol = FP32_TOL
+    if dtype == torch.bfloat16:
+        params = {k: O.bf16_round(v) for k, v in params.items()}
+        x = O.bf16_round(x)
+        model = O.OraclePoM(params, case["cfg"]["degree"], case["cfg"]["expand"], case["cfg"]["heads"])
+        want_y, st = model.ar_forward(x, {"max_len": case["max_len"], "n": 0})
+        want_h, tol = st["h"], BF16_TOL
+    mod = make_cuda_module(case["cfg"], params, dtype)
+    y, st = mod.ar_forward(x.cuda().to(dtype), {"max_len": case["max_len"], "h": 0.0, "n": case["n"] - x.shape[1]})
+    assert st["n"] == case["n"] and st["max_len"] == case["max_len"]
+    assert_close(y, want_y, tol, f"{name} y")
+    assert_close(st["h"], want_h, tol, f"{name} state h")
+
+
+@pytest.mark.parametrize("name", LAYER_CASES + ["pom_groups2_none", "pom_groups2_causal"])
 def test_bf16_layer_matches_oracle_on_rounded_inputs(golden, name):
     case = golden[name]
     cfg = case["cfg"]
-    params = {k: O.bf16_round(case["params"][k]) for k in PARAM_ORDER}
+    params = {k: O.bf16_round(case["params"][k]) for k in param_order(case["params"])}
     xq = O.bf16_round(case["xq"])
     xc = None if case["xc"] is None else O.bf16_round(case["xc"])
     gy = O.bf16_round(case["gy"])

@@ -12,7 +12,8 @@ def _oracle_from_case(case, requires_grad=True):
     cfg = case["cfg"]
     params = {}
     for k, v in case["params"].items():
-        if k in ("qc_proj.weight", "se_bias", "po_coeff", "ag_proj.weight"):
+        if k in ("qc_proj.weight", "se_bias", "po_coeff", "ag_proj.weight", "po_proj.weight", "se_proj.weight",
+                 "se_proj.bias"):
             params[k] = v.clone().requires_grad_(requires_grad)
     rope = None
     if "rope" in cfg:
@@ -27,6 +28,7 @@ MODULE_CASES = [
     "pom_heads4_none", "pom_heads4_causal",
     "rope1d_none", "rope1d_causal", "rope1d_mask2d", "rope1d_positions", "rope1d_cross",
     "rope2d_none", "rope2d_causal", "rope2d_heads4_none", "rope1d_heads4_causal",
+    "pom_groups2_none", "pom_groups2_causal", "pom_groups2_cross_mask2d", "pom_groups2_heads4_none",
 ]
 
 
@@ -41,6 +43,8 @@ def test_layer_matches_reference_vectors(golden, name):
     assert n2 < TOL and mx < TOL, (name, n2, mx)
     ins = [xq] + ([xc] if xc is not None else [])
     order = ["se_bias", "po_coeff", "qc_proj.weight", "ag_proj.weight"]
+    if "po_proj.weight" in params:
+        order = ["po_proj.weight", "se_proj.weight", "se_proj.bias", "po_coeff", "ag_proj.weight"]
     grads = torch.autograd.grad(y, ins + [params[k] for k in order], case["gy"])
     want = [case["grads"][f"d_in{i}"] for i in range(len(ins))] + [case["grads"]["d_" + k] for k in order]
     for g, w, label in zip(grads, want, [f"in{i}" for i in range(len(ins))] + order):
@@ -59,6 +63,17 @@ def test_state_forward_matches_reference_vectors(golden):
     assert state["n"] == case["n"] == 3  # the counter advances once per call, not per token
     n2, mx = O.rel_errors(state["h"], case["h"])
     assert n2 < TOL and mx < TOL
+
+
+@pytest.mark.parametrize("name", ["pom_ar", "pom_ar_heads4"])
+def test_ar_forward_matches_reference_vectors(golden, name):
+    case = golden[name]
+    model, _ = _oracle_from_case(case, requires_grad=False)
+    y, st = model.ar_forward(case["xq"], {"max_len": case["max_len"], "h": 0.0, "n": case["n"] - case["xq"].shape[1]})
+    assert st["n"] == case["n"] and st["max_len"] == case["max_len"]
+    for got, want in ((y, case["y"]), (st["h"], case["h"])):
+        n2, mx = O.rel_errors(got, want)
+        assert n2 < TOL and mx < TOL, (name, n2, mx)
 
 
 @pytest.mark.parametrize("k", [1, 2, 4, 8, 16])
