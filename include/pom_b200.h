@@ -261,6 +261,12 @@ typedef struct pom_agg_bwd_args {
   pom_rope rope;
 } pom_agg_bwd_args;
 int pom_poly_agg_bwd(const pom_agg_bwd_args* a, void* stream);
+/* Number of (P, K) slots of dcoeff_partial that pom_poly_agg_bwd writes for these arguments (the caller sums
+ * exactly that many); never more than B * pom_agg_chunks(N), which is the capacity to allocate. */
+int32_t pom_poly_agg_bwd_slots(const pom_agg_bwd_args* a);
+/* Synchronous read of this device's operator status word: 0, or the code of the first bounded wait inside an
+ * operator kernel (a shared-memory staging barrier) that expired; results of that launch are then incomplete. */
+int pom_ops_status(int32_t* value_out);
 
 /* ------------------------------------------------------------------------------------------
  * Selection operator: SH[b,t,:] = R_t·hardsigmoid(z[b,t,:] + bias) ⊙ H[b, t or 0, :]

@@ -175,6 +175,8 @@ _SIGNATURES = {
     "pom_poly_agg_fwd": (C.c_int, [C.POINTER(AggArgs), C.c_void_p]),
     "pom_poly_agg_mean_noalloc": (C.c_int, [C.POINTER(AggArgs), C.c_void_p, C.c_float, C.c_void_p, C.c_void_p]),
     "pom_poly_agg_bwd": (C.c_int, [C.POINTER(AggBwdArgs), C.c_void_p]),
+    "pom_poly_agg_bwd_slots": (C.c_int32, [C.POINTER(AggBwdArgs)]),
+    "pom_ops_status": (C.c_int, [C.POINTER(C.c_int32)]),
     "pom_select_fwd": (C.c_int, [C.POINTER(SelectArgs), C.c_void_p]),
     "pom_select_bwd": (C.c_int, [C.POINTER(SelectBwdArgs), C.c_void_p]),
     "pom_select_heads_fwd": (C.c_int, [C.POINTER(SelectHeadsArgs), C.c_void_p]),
@@ -251,5 +253,12 @@ def status_word(device) -> torch.Tensor:
 
 
 def read_status(device) -> int:
-    """Synchronising read of the status word (tests and debugging only)."""
-    return int(status_word(device).item())
+    """Synchronising read of the status words (tests and debugging only): the GEMM / exchange word, else the
+    operator kernels' word."""
+    word = int(status_word(device).item())
+    if word:
+        return word
+    v = C.c_int32(0)
+    with torch.cuda.device(device):
+        check(lib().pom_ops_status(C.byref(v)), "pom_ops_status")
+    return int(v.value)

@@ -10,6 +10,7 @@
 // sum is formed in a fixed order (deterministic, no float atomics).
 #include "common.cuh"
 #include "pom_math.cuh"
+#include "ptx_sm100.cuh"
 #include <cuda_bf16.h>
 #include <initializer_list>
 #include <mutex>
@@ -490,6 +491,204 @@ __global__ void __launch_bounds__(128) agg_bwd_kernel(const AggBwdDev a) {
         dcp[static_cast<long long>(m.p1 + e) * a.K + k] = dc1[e][k];
         if (rope) dcp[static_cast<long long>(m.p2 + e) * a.K + k] = dc2[e][k];
       }
+}
+
+// ------------------------------------------------------------------ streamed backward
+// The bf16, non-causal, no-rotary backward (the one on the fused layer path) as a staged stream: a CTA owns
+// 256 channels of one sample and a run of 64-token tiles; warp 0 brings each tile's rows into a 3-deep shared
+// memory ring with 512-byte bulk copies that complete on an mbarrier, so the bytes in flight sit in shared
+// memory (96 KiB per CTA, two CTAs per SM) instead of in registers; all 8 warps then read 16 bytes per thread,
+// compute, and store dx straight from registers.  The coefficient sums stay in registers over the whole run
+// and are combined across the 8 row groups in a fixed order at the end: one partial per (sample, run).
+constexpr int kStTok = 64;
+constexpr int kStCols = 256;
+constexpr int kStStages = 3;
+constexpr int kStVec = 8;       // channels per thread (16-byte accesses): 256 threads per CTA
+constexpr int kStTileBytes = kStTok * kStCols * 2;
+constexpr int kStSmemBytes = kStStages * kStTileBytes + 128;
+constexpr int kStatusStreamTimeout = 201;
+
+__device__ int g_ops_status;  // first bounded wait of an operator kernel that expired (0 = none)
+
+__device__ __forceinline__ void bulk_load_row(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+struct StreamPlan {
+  int col_blocks, tiles, tiles_per_cta, splits;
+};
+
+// Enough CTAs for two per SM on every SM, each with a contiguous run of tiles.
+inline StreamPlan stream_plan(int B, int N, int P) {
+  StreamPlan s;
+  s.col_blocks = static_cast<int>(ceil_div(P, kStCols));
+  s.tiles = static_cast<int>(ceil_div(N, kStTok));
+  const long long pairs = static_cast<long long>(s.col_blocks) * B;
+  long long want = ceil_div(4LL * sm_count(), pairs);
+  if (want < 1) want = 1;
+  if (want > s.tiles) want = s.tiles;
+  s.tiles_per_cta = static_cast<int>(ceil_div(s.tiles, want));
+  s.splits = static_cast<int>(ceil_div(s.tiles, s.tiles_per_cta));
+  return s;
+}
+
+template <int KR, int VEC>
+__global__ void __launch_bounds__(kStCols / VEC * 8, 2) agg_bwd_stream_kernel(const AggBwdDev a, int tiles_per_cta, int splits,
+                                                                       int* status) {
+  extern __shared__ __align__(128) uint8_t st_smem[];
+  __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(st_smem);
+  uint64_t* full = reinterpret_cast<uint64_t*>(st_smem + kStStages * kStTileBytes);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(full + kStStages);
+  constexpr int kLanes = kStCols / VEC;   // threads across one row
+  constexpr int kGroups = 8;              // row groups
+  const int tid = threadIdx.x, tx = tid % kLanes, ty = tid / kLanes;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int p0 = blockIdx.x * kStCols, split = blockIdx.y, b = blockIdx.z;
+  const int width = min(kStCols, a.P - p0);  // channels of this block (multiple of 8)
+  const int tiles_total = (a.N + kStTok - 1) / kStTok;
+  const int t_begin = split * tiles_per_cta;
+  const int my_tiles = min(tiles_total, t_begin + tiles_per_cta) - t_begin;
+  if (tid == 0) {
+    for (int s = 0; s < kStStages; ++s) mbar_init(&full[s], 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(a.x) + static_cast<long long>(b) * a.N * a.ldx + p0;
+  __nv_bfloat16* dxb = static_cast<__nv_bfloat16*>(a.dx) + static_cast<long long>(b) * a.N * a.ld_dx + p0;
+  auto issue = [&](int i) {  // warp 0, all lanes
+    const int stage = i % kStStages;
+    const int n0 = (t_begin + i) * kStTok;
+    const int rows = min(kStTok, a.N - n0);
+    if (lane == 0) mbar_expect_tx(&full[stage], static_cast<uint32_t>(rows * width * 2));
+    __syncwarp();
+    for (int r = lane; r < rows; r += 32)
+      bulk_load_row(ring + (stage * kStTok + r) * kStCols, xb + static_cast<long long>(n0 + r) * a.ldx,
+                    static_cast<uint32_t>(width * 2), &full[stage]);
+  };
+  if (warp == 0)
+    for (int i = 0; i < kStStages - 1 && i < my_tiles; ++i) issue(i);
+
+  const int c = tx * VEC;
+  const bool live = c < width;
+  float cf[VEC][KR], g[VEC], dc[VEC][KR];
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) {
+    g[e] = live ? a.dH[static_cast<long long>(b) * a.P + p0 + c + e] : 0.f;
+#pragma unroll
+    for (int k = 0; k < KR; ++k) {
+      cf[e][k] = (live && k < a.K) ? __ldg(a.coeff + static_cast<long long>(p0 + c + e) * a.K + k) : 0.f;
+      dc[e][k] = 0.f;
+    }
+  }
+  float wb = a.scale;
+  if (a.denom) {
+    const float dn = a.denom[b];
+    wb = dn != 0.f ? wb / dn : 0.f;
+  }
+
+  for (int i = 0; i < my_tiles; ++i) {
+    const int stage = i % kStStages;
+    const bool ok = mbar_wait(&full[stage], static_cast<uint32_t>(i / kStStages) & 1u, abort_flag, status,
+                              kStatusStreamTimeout);
+    // also the point where every thread has finished reading the stage that is refilled next
+    if (__syncthreads_or(!ok)) return;
+    if (warp == 0 && i + kStStages - 1 < my_tiles) issue(i + kStStages - 1);
+    const int n0 = (t_begin + i) * kStTok;
+    const int rows = min(kStTok, a.N - n0);
+    if (live) {
+#pragma unroll 2
+      for (int r = ty; r < rows; r += kGroups) {
+        const int n = n0 + r;
+        float x[VEC], o[VEC];
+        {
+          const __nv_bfloat16* src = ring + (stage * kStTok + r) * kStCols + c;
+          uint32_t w4[VEC / 2];
+          if constexpr (VEC == 8) {
+            const uint4 q = *reinterpret_cast<const uint4*>(src);
+            w4[0] = q.x, w4[1] = q.y, w4[2] = q.z, w4[3] = q.w;
+          } else {
+            const uint2 q = *reinterpret_cast<const uint2*>(src);
+            w4[0] = q.x, w4[1] = q.y;
+          }
+#pragma unroll
+          for (int e = 0; e < VEC / 2; ++e) {
+            x[2 * e] = __uint_as_float(w4[e] << 16);
+            x[2 * e + 1] = __uint_as_float(w4[e] & 0xffff0000u);
+          }
+        }
+        const float w = a.row_weight ? wb * __ldg(a.row_weight + static_cast<long long>(b) * a.N + n) : wb;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          const float d = w * g[e];
+          const float av = pom_act(x[e]);
+          o[e] = d * poly_grad_reg<KR>(av, cf[e]) * pom_act_grad(x[e]);
+          float pw = av;
+#pragma unroll
+          for (int k = 0; k < KR; ++k) {
+            dc[e][k] = fmaf(d, pw, dc[e][k]);
+            pw *= av;
+          }
+        }
+        {
+          uint32_t pk[VEC / 2];
+#pragma unroll
+          for (int e = 0; e < VEC / 2; ++e) pk[e] = pack_bf16x2(o[2 * e], o[2 * e + 1]);
+          __nv_bfloat16* dst = dxb + static_cast<long long>(n) * a.ld_dx + c;
+          if constexpr (VEC == 8) *reinterpret_cast<uint4*>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          else *reinterpret_cast<uint2*>(dst) = make_uint2(pk[0], pk[1]);
+        }
+      }
+    }
+  }
+  // every bulk copy issued above has been waited for: the ring is free to hold the coefficient sums
+  __syncthreads();
+  float* red = reinterpret_cast<float*>(st_smem);  // [row group 1..7][value][thread of the row]
+  if (ty > 0) {
+#pragma unroll
+    for (int e = 0; e < VEC; ++e)
+#pragma unroll
+      for (int k = 0; k < KR; ++k) red[((ty - 1) * VEC * KR + e * KR + k) * kLanes + tx] = dc[e][k];
+  }
+  __syncthreads();
+  if (ty == 0 && live) {
+    float* dcp = a.dcoeff_partial + (static_cast<long long>(b) * splits + split) * a.P * a.K;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e)
+#pragma unroll
+      for (int k = 0; k < KR; ++k) {
+        float s = dc[e][k];
+        for (int q = 0; q < kGroups - 1; ++q) s += red[(q * VEC * KR + e * KR + k) * kLanes + tx];
+        if (k < a.K) dcp[static_cast<long long>(p0 + c + e) * a.K + k] = s;
+      }
+  }
+}
+
+bool stream_bwd_eligible(const pom_agg_bwd_args* a) {
+  return a->dtype == POM_BF16 && a->causal == 0 && a->rope.kind == POM_ROPE_NONE && a->K <= 4 && a->P % 8 == 0 &&
+         a->ldx % 8 == 0 && a->ld_dx % 8 == 0 && aligned16(a->x) && aligned16(a->dx);
+}
+
+int* ops_status_ptr() {
+  // one address per device (the symbol is per device)
+  static std::mutex mu;
+  static int* cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cached[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_ops_status) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    cached[dev] = static_cast<int*>(p);
+  }
+  return cached[dev];
 }
 
 // ------------------------------------------------------------------ selection
@@ -1002,6 +1201,23 @@ int pom_poly_agg_mean_noalloc(const pom_agg_args* a, const float* denom, float s
   return check_launch();
 }
 
+int32_t pom_poly_agg_bwd_slots(const pom_agg_bwd_args* a) {
+  if (!a || a->B <= 0 || a->N <= 0 || a->P <= 0) return 0;
+  if (stream_bwd_eligible(a)) return a->B * stream_plan(a->B, a->N, a->P).splits;
+  return a->B * pom_agg_chunks(a->N);
+}
+
+int pom_ops_status(int32_t* value_out) {
+  if (!value_out) return POM_ERR_NULL;
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_ops_status, sizeof(int)) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return POM_ERR_CUDA;
+  }
+  *value_out = v;
+  return POM_OK;
+}
+
 int pom_poly_agg_bwd(const pom_agg_bwd_args* a, void* stream) {
   if (!a || !a->x || !a->coeff || !a->dx || !a->dcoeff_partial) return POM_ERR_NULL;
   if (a->B <= 0 || a->N <= 0 || a->P <= 0 || a->K < 1) return POM_ERR_BAD_SHAPE;
@@ -1036,6 +1252,26 @@ int pom_poly_agg_bwd(const pom_agg_bwd_args* a, void* stream) {
   d.chunks = pom_agg_chunks(a->N);
   d.per_token = a->causal == 2;
   d.rope = a->rope;
+  if (stream_bwd_eligible(a)) {
+    int* status = ops_status_ptr();
+    if (!status) return POM_ERR_CUDA;
+    const StreamPlan sp = stream_plan(a->B, a->N, a->P);
+    const dim3 sgrid(static_cast<unsigned>(sp.col_blocks), static_cast<unsigned>(sp.splits),
+                     static_cast<unsigned>(a->B));
+    if (sp.splits > 65535) return POM_ERR_TOO_LARGE;
+    static std::once_flag attr_once;
+    std::call_once(attr_once, [] {
+      cudaFuncSetAttribute(agg_bwd_stream_kernel<2, kStVec>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStSmemBytes);
+      cudaFuncSetAttribute(agg_bwd_stream_kernel<4, kStVec>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStSmemBytes);
+    });
+    constexpr int threads = kStCols / kStVec * 8;
+    if (a->K <= 2)
+      agg_bwd_stream_kernel<2, kStVec><<<sgrid, threads, kStSmemBytes, st>>>(d, sp.tiles_per_cta, sp.splits, status);
+    else
+      agg_bwd_stream_kernel<4, kStVec><<<sgrid, threads, kStSmemBytes, st>>>(d, sp.tiles_per_cta, sp.splits, status);
+    count_launch();
+    return check_launch();
+  }
   const int vec = pick_vec(a->P, a->rope, a->dtype, a->K, {a->ldx, a->ld_dx, a->causal ? a->ld_dout : 0},
                            {a->x, a->dx, a->causal ? a->dout : nullptr});
   const WalkLaunch wl = walk_launch(a->P, a->rope.kind, vec, d.chunks, a->B);

@@ -138,6 +138,15 @@ def reduce_partials(partial: torch.Tensor, *, denom: Optional[torch.Tensor] = No
     assert partial.dtype == torch.float32 and partial.is_contiguous()
     if out is None:
         out = torch.empty((B, P), dtype=torch.float32, device=partial.device)
+    # Few samples and many chunks (one long sequence): the kernel's grid is (P/32, B), so first fold groups of
+    # chunks into (B*G, P) with G times as many CTAs, then finish over the G group sums.
+    if chunks >= 128 and B * ((P + 31) // 32) < 256:
+        G = next((g for g in (32, 16, 8, 4) if chunks % g == 0), 0)
+        if G:
+            part = torch.empty((B * G, P), dtype=torch.float32, device=partial.device)
+            _abi.check(_abi.lib().pom_reduce_partials(ptr(partial), ptr(part), None, 1.0, B * G, chunks // G, P,
+                                                      _abi.stream_ptr()), "pom_reduce_partials")
+            partial, chunks = part, G
     _abi.check(_abi.lib().pom_reduce_partials(ptr(partial), ptr(out), ptr(denom), scale, B, chunks, P,
                                               _abi.stream_ptr()), "pom_reduce_partials")
     return out
@@ -265,7 +274,8 @@ def poly_agg_bwd(x: torch.Tensor, coeff: torch.Tensor, *, dx_out: torch.Tensor, 
     _abi.check(_abi.lib().pom_poly_agg_bwd(C.byref(a), _abi.stream_ptr()), "pom_poly_agg_bwd")
     if totals_only:
         return None, total
-    dcoeff = reduce_partials(dcp, out=None if dcoeff_out is None else dcoeff_out.view(1, P * K)).view(P, K)
+    slots = int(_abi.lib().pom_poly_agg_bwd_slots(C.byref(a)))
+    dcoeff = reduce_partials(dcp[:, :slots], out=None if dcoeff_out is None else dcoeff_out.view(1, P * K)).view(P, K)
     return dcoeff, total
 
 
