@@ -516,10 +516,12 @@ def main():
 def gemm_roofline(step, dev_sets, peaks, reps=5):
     """Times every tcgen05 GEMM launch of one step with CUDA events (on the launching stream) by wrapping the
     binding's GEMM entry points, and reports the launch that dominates the step."""
-    from pom_b200 import ops
+    from pom_b200 import functional, ops
 
     records = []
     originals = {}
+    whole = functional.WHOLE_LAYER_CALLS
+    functional.WHOLE_LAYER_CALLS = False  # same kernels, launched phase by phase so each can be bracketed by events
 
     def wrap(name, flops_of):
         fn = getattr(ops, name)
@@ -549,6 +551,7 @@ def gemm_roofline(step, dev_sets, peaks, reps=5):
             step(*dev_sets[i % len(dev_sets)])
         torch.cuda.synchronize()
     finally:
+        functional.WHOLE_LAYER_CALLS = whole
         for n, fn in originals.items():
             setattr(ops, n, fn)
     agg = {}

@@ -349,6 +349,54 @@ int pom_cast_f32_to_bf16(const float* src, void* dst, int64_t count, void* strea
 int pom_cast_bf16_to_f32(const void* src, float* dst, int64_t count, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Whole layer in two calls (bf16, one GPU, no rotary embedding, mask none or (B, N)): everything
+ * PoM.forward / PoM.state_forward (reference pom/pom.py:216-262) and their autograd do, sequenced on `stream`
+ * from the phase entry points above.  All tensors contiguous; the caller owns every buffer.
+ *
+ *   forward : [denom = sum_n mask] -> pom_ctx_gemm -> H = mean (or masked mean) [-> running mean over frames]
+ *             [-> merge with h_past] -> pom_gate_gemm -> y = SH·Woᵀ (+ residual)
+ *   backward: grads := 0; dWo; pom_gate_bwd_gemm; dH, dbias [+ dh_state] [-> adjoint of the frame mean]
+ *             [-> d_hpast]; streamed aggregation backward; dX and dWqc (one GEMM each under self-mixing)
+ *
+ * `frames` > 1 folds a block-causal sequence: batch rows are (sample, frame) pairs, B % frames == 0 (see
+ * pom_frame_prefix_mean).  h_past / n_past: the running-mean state of state_forward.  Hosts that need an exchange
+ * between the phases (token sharding) call the phase entry points themselves. */
+typedef struct pom_layer_args {
+  int32_t B, T, N, D, P, K;   /* T query tokens, N context tokens per batch row; P = expand * D; K = degree */
+  int32_t self_mixing;        /* context == queries (T == N, xc ignored) */
+  int32_t frames;             /* >= 1 */
+  int32_t save;               /* forward: keep hp and z for backward */
+  float n_past;               /* weight of h_past (calls so far) */
+  const void* xq;             /* (B, T, D) bf16 */
+  const void* xc;             /* (B, N, D) bf16 or NULL */
+  const void* w_qc;           /* (2P, D) bf16: rows [0, P) polynomial projection, [P, 2P) gate projection */
+  const void* w_ag;           /* (D, P) bf16 */
+  const float* se_bias;       /* (P) */
+  const float* coeff;         /* (P, K) */
+  const float* mask;          /* (B, N) fp32 weights or NULL */
+  const float* h_past;        /* (B, P) fp32 or NULL */
+  const void* residual;       /* (B, T, D) bf16 or NULL: added to y */
+  void* y;                    /* (B, T, D) bf16, forward output */
+  void* hp;                   /* (B, N, P) bf16, saved projection (forward out when save, backward in) */
+  void* z;                    /* (B, T, P) bf16, saved gate pre-activation */
+  void* sh;                   /* (B, T, P) bf16, gated state (operand of the output projection) */
+  float* H;                   /* (B, P) fp32 aggregate (forward out, backward in) */
+  float* denom;               /* (B) fp32 mask sums (forward out, backward in); required with mask */
+  const void* dy;             /* backward: (B, T, D) bf16 */
+  const float* dh_state;      /* backward: (B, P) fp32 gradient of the returned state, or NULL */
+  void* G;                    /* backward scratch, bf16: (B*T, 2P) under self-mixing, else (B*N + B*T) * P */
+  void* dxq;                  /* (B, T, D) bf16 */
+  void* dxc;                  /* (B, N, D) bf16 (cross-mixing only) */
+  float* grads;               /* fp32, zeroed by the call: [dWqc (2P*D) | dWo (D*P) | dbias (P) | dcoeff (P*K)] */
+  float* d_hpast;             /* (B, P) fp32 or NULL */
+  void* workspace;            /* pom_layer_workspace_bytes() bytes, 256-byte aligned, shared by both calls */
+  uint64_t workspace_bytes;
+} pom_layer_args;
+uint64_t pom_layer_workspace_bytes(const pom_layer_args* a);
+int pom_layer_fwd(const pom_layer_args* a, int* status, void* stream);
+int pom_layer_bwd(const pom_layer_args* a, int* status, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Token-sharding exchanges over NVLink peer memory (no counterpart in the reference, which is single-GPU;
  * they carry the cross-rank sums that a token-sharded PoM.forward needs: the (B, P) aggregate of
  * pom/pom.py:90-96 split over ranks, its gradient, the causal prefix/suffix carries, and the sum of

@@ -137,6 +137,21 @@ class SelectHeadsArgs(C.Structure):
     ]
 
 
+class LayerArgs(C.Structure):
+    _fields_ = [
+        ("B", C.c_int32), ("T", C.c_int32), ("N", C.c_int32), ("D", C.c_int32), ("P", C.c_int32), ("K", C.c_int32),
+        ("self_mixing", C.c_int32), ("frames", C.c_int32), ("save", C.c_int32), ("n_past", C.c_float),
+        ("xq", C.c_void_p), ("xc", C.c_void_p), ("w_qc", C.c_void_p), ("w_ag", C.c_void_p),
+        ("se_bias", C.c_void_p), ("coeff", C.c_void_p), ("mask", C.c_void_p), ("h_past", C.c_void_p),
+        ("residual", C.c_void_p),
+        ("y", C.c_void_p), ("hp", C.c_void_p), ("z", C.c_void_p), ("sh", C.c_void_p),
+        ("H", C.c_void_p), ("denom", C.c_void_p),
+        ("dy", C.c_void_p), ("dh_state", C.c_void_p), ("G", C.c_void_p), ("dxq", C.c_void_p), ("dxc", C.c_void_p),
+        ("grads", C.c_void_p), ("d_hpast", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_uint64),
+    ]
+
+
 PEER_MAX_RANKS = 16
 PEER_HANDLE_BYTES = 64
 PEER_SUM_ALL, PEER_SUM_BEFORE, PEER_SUM_AFTER = 0, 1, 2
@@ -186,6 +201,9 @@ _SIGNATURES = {
     "pom_fill_zero": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p]),
     "pom_cast_f32_to_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "pom_cast_bf16_to_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
+    "pom_layer_workspace_bytes": (C.c_uint64, [C.POINTER(LayerArgs)]),
+    "pom_layer_fwd": (C.c_int, [C.POINTER(LayerArgs), C.c_void_p, C.c_void_p]),
+    "pom_layer_bwd": (C.c_int, [C.POINTER(LayerArgs), C.c_void_p, C.c_void_p]),
     "pom_peer_layout": (C.c_int, [C.c_int, C.c_ulonglong, C.c_ulonglong, C.POINTER(C.c_ulonglong)]),
     "pom_peer_export": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_ulonglong)]),
     "pom_peer_open": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),

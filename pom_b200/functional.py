@@ -29,6 +29,10 @@ from . import _abi, ops
 from .ops import RopeSpec
 
 
+# True: a fused-path layer without token sharding is two library calls (pom_layer_fwd / pom_layer_bwd).  False:
+# the same kernels are launched phase by phase from Python (what per-launch timing instrumentation hooks into).
+WHOLE_LAYER_CALLS = True
+
 # --------------------------------------------------------------------------- sharding description
 @dataclass
 class SeqShard:
@@ -199,6 +203,27 @@ class _PoMLayer(torch.autograd.Function):
                  and P % 8 == 0 and D % 8 == 0)
 
         hp = z = Hc = s32 = None
+        ctx.composite = fused and shard is None and WHOLE_LAYER_CALLS
+        if ctx.composite:
+            # the whole fused layer is one library call (no exchange to put between its phases)
+            if spec.frames > 1 and (spec.n_past is not None or maskf is not None):
+                raise NotImplementedError("BlockCausal is not combined with masks or state")
+            h_past32 = None
+            if spec.n_past is not None and h_past is not None:
+                h_past32 = _f32(h_past.reshape(B, P).contiguous())
+            y, hp, z, sh, H, denom = ops.layer_fwd(
+                xq, None if spec.self_mixing else xc, w_qc, w_ag, bias32, coeff32, mask=maskf, h_past=h_past32,
+                n_past=spec.n_past, residual=None if residual is None else residual.contiguous(), frames=spec.frames,
+                save=need_grad)
+            ctx.has_residual = residual is not None
+            ctx.spec = spec
+            ctx.fused = True
+            ctx.dims = (B, T, N, D, P, K, S, heads, n_glob, offset)
+            ctx.h_past_dtype = None if h_past is None else h_past.dtype
+            ctx.save_for_backward(xq, xc, w_qc, w_ag, coeff32, bias32, hp, z, H, h_past32, sh, maskf, denom, None, None,
+                                  None)
+            ctx.param_like = (w_qc, se_bias, coeff, w_ag)
+            return (y, H.view(B, 1, P)) if spec.want_state else (y, None)
         # ---------------------------------------------------------------- context phase
         if fused:
             partial, hp = ops.ctx_gemm(xc, w_po, coeff32, row_weight=maskf, save_hp=need_grad)
@@ -275,6 +300,26 @@ class _PoMLayer(torch.autograd.Function):
         dt = xq.dtype
         dy = dy.contiguous()
         dy2 = dy.view(B * T, D)
+        if ctx.composite:
+            h_past32 = Hc  # slot reused by the composite forward
+            dh32 = None if dh_state is None else _f32(dh_state.reshape(B, P).contiguous())
+            dxq, dxc, flat, d_hpast = ops.layer_bwd(
+                dy, xq, None if spec.self_mixing else xc, w_qc, w_ag, bias32, coeff32, hp, z, sh, H, mask=maskf,
+                denom=denom, h_past=h_past32, n_past=spec.n_past, dh_state=dh32, frames=spec.frames,
+                want_d_hpast=bool(ctx.needs_input_grad[7]))
+            if d_hpast is not None:
+                d_hpast = d_hpast.view(B, 1, P)
+                if ctx.h_past_dtype != torch.float32:
+                    d_hpast = ops.to_bf16(d_hpast)
+            n_qc, n_ag = 2 * P * D, D * P
+            f16 = ops.to_bf16(flat)
+            g_qc, g_ag = f16[:n_qc].view(2 * P, D), f16[n_qc:n_qc + n_ag].view(D, P)
+            g_bias, g_coeff = f16[n_qc + n_ag:n_qc + n_ag + P], f16[n_qc + n_ag + P:].view(P, K)
+            if p_bias.dtype == torch.float32:
+                g_bias = flat[n_qc + n_ag:n_qc + n_ag + P]
+            if p_coeff.dtype == torch.float32:
+                g_coeff = flat[n_qc + n_ag + P:].view(P, K)
+            return (dxq, dxc, g_qc, g_bias, g_coeff, g_ag, None, d_hpast, None, dy if ctx.has_residual else None)
 
         # one flat fp32 buffer for all parameter gradients: a single zero fill, cast and (when sharded) all-reduce
         n_qc, n_ag = (P + S) * D, D * P
