@@ -436,6 +436,8 @@ def main():
     ms_step = ms_total.item() / args.steps
     tokens_all = tokens_local * world
     value = tokens_all / (ms_step * 1e-3)
+    # key-padding workload: `value` counts padded tokens; the fraction of valid context tokens is reported beside it
+    valid_frac = float(kw["mask"].float().mean().item()) if torch.is_tensor(kw.get("mask")) else None
 
     # ---- end to end through the module API with host buffers (pinned), copies inside the timed region
     xs, gs = host_sets[0]
@@ -523,6 +525,8 @@ def main():
                        "parallelism": f"{w['shard']}-shard x{world}",
                        "l2": "3 rotating input sets (>= 450 MB) plus ~1 GB of intermediates per step, larger than the 126 MB L2",
                        "e2e_pipeline": "double-buffered: H2D of step i+1 and D2H of step i-1 on their own streams beside the kernels of step i",
+                       "valid_token_fraction": valid_frac,
+                       "valid_tokens_per_s": None if valid_frac is None else value * valid_frac,
                        "cuda_graph": use_graph,
                        "exchange": ("peer-memory kernels" if peer_on else "nccl") if w["shard"] == "token" and world > 1 else None,
                        "weight_grad_allreduce_in_timed_region": bool(w["shard"] == "token" and world > 1

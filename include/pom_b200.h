@@ -129,8 +129,13 @@ typedef struct pom_ctx_args {
   float* partial;      /* (B * ceil(N/128), P) fp32 */
   int64_t ldx, ldw, ld_hp;
   int32_t B, N, D, P, K;
+  const float* tile_weight; /* optional with row_weight: (B * ceil(N/128)) fp32 from pom_tile_weights; a 128-token
+                               tile whose weights sum to 0 is skipped: no loads, no MMAs, partial = 0 and its rows of
+                               hp_out are NOT written (pom_poly_agg_bwd never uses rows of weight 0) */
 } pom_ctx_args;
 int pom_ctx_gemm(const pom_ctx_args* a, int* status, void* stream);
+/* out[b * ceil(N/128) + t] = sum of w[b, 128 t .. 128 t + 127] (w (B, N) fp32, key-padding weights >= 0). */
+int pom_tile_weights(const float* w, float* out, int32_t B, int32_t N, void* stream);
 
 /* out[b, p] = scale * sum_c partial[b, c, p] / denom[b]   (denom may be NULL = 1; a zero denominator
  * yields 0, the convention of pom/pom_triton_masked.py:166-167 for a sample with no valid token) */

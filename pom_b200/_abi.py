@@ -57,6 +57,7 @@ class CtxArgs(C.Structure):
         ("hp_out", C.c_void_p), ("partial", C.c_void_p),
         ("ldx", C.c_int64), ("ldw", C.c_int64), ("ld_hp", C.c_int64),
         ("B", C.c_int32), ("N", C.c_int32), ("D", C.c_int32), ("P", C.c_int32), ("K", C.c_int32),
+        ("tile_weight", C.c_void_p),
     ]
 
 
@@ -197,6 +198,7 @@ _SIGNATURES = {
     "pom_select_heads_fwd": (C.c_int, [C.POINTER(SelectHeadsArgs), C.c_void_p]),
     "pom_select_heads_bwd": (C.c_int, [C.POINTER(SelectHeadsArgs), C.c_void_p]),
     "pom_state_merge": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int64, C.c_void_p]),
+    "pom_tile_weights": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
     "pom_frame_prefix_mean": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "pom_fill_zero": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p]),
     "pom_cast_f32_to_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),

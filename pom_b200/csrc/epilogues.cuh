@@ -239,7 +239,7 @@ struct EpiCtx {
 #pragma unroll 1
     for (int c = half; c < BN / 32; c += kEpiColSplit) {
       const int col = t.col0 + c * 32;
-      if (col >= g.n_cols) {  // warp-uniform
+      if (col >= g.n_cols || !t.live) {  // warp-uniform; a skipped tile has no accumulator and adds nothing
         buf[quarter * 256 + c * 32 + lane] = 0.f;
         continue;
       }

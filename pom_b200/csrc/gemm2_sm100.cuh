@@ -105,6 +105,13 @@ __device__ __forceinline__ TileCtx decode_pair_tile(const GemmGeom& g, int unit,
   t.row0 = t.mt * kBM;
   t.rows_valid = max(0, min(kBM, g.rows_per_batch - t.row0));
   t.col0 = n * bn;
+  // the two halves of a pair share one main loop: it is skipped only when both are empty
+  t.live = true;
+  if (g.tile_weight) {
+    const int m0 = t.b * g.m_tiles_per_batch + 2 * (mp - t.b * pairs_per_batch);
+    const bool second = 2 * (mp - t.b * pairs_per_batch) + 1 < g.m_tiles_per_batch;
+    t.live = __ldg(g.tile_weight + m0) != 0.f || (second && __ldg(g.tile_weight + m0 + 1) != 0.f);
+  }
   return t;
 }
 
@@ -187,7 +194,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       for (int unit = cluster_id; unit < total_units && alive; unit += n_clusters) {
         const TileCtx t = decode_pair_tile(geom, unit, BN, rank);
         const int kb0 = t.split * geom.kb_per_split;
-        const int kb1 = min(geom.k_blocks, kb0 + geom.kb_per_split);
+        const int kb1 = t.live ? min(geom.k_blocks, kb0 + geom.kb_per_split) : kb0;
         const int bcol0 = t.col0 + static_cast<int>(rank) * kHalfN;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, status, kStatusProducerTimeout)) {
@@ -231,7 +238,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       for (int unit = cluster_id; unit < total_units && alive; unit += n_clusters, ++iter) {
         const TileCtx t = decode_pair_tile(geom, unit, BN, 0);
         const int kb0 = t.split * geom.kb_per_split;
-        const int kb1 = min(geom.k_blocks, kb0 + geom.kb_per_split);
+        const int kb1 = t.live ? min(geom.k_blocks, kb0 + geom.kb_per_split) : kb0;
         const int acc = iter & 1;
         const uint32_t acc_phase = (iter >> 1) & 1u;
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_flag, status, kStatusMmaTimeout)) {

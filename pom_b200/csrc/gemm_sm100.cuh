@@ -50,6 +50,9 @@ struct GemmGeom {
   int kb_per_split;       // k blocks handled by one split (== k_blocks when split_k == 1)
   int split_k;            // number of K splits (each split has at least one k block)
   int group_m;            // rasterisation: m tiles per band
+  // Optional (batches * m_tiles_per_batch) fp32: a tile whose entry is 0 is not computed (no loads, no MMAs; its
+  // epilogue sees t.live == false).  Used by the context phase to skip 128-token tiles that a mask empties.
+  const float* tile_weight;
 };
 
 struct TileCtx {
@@ -59,6 +62,7 @@ struct TileCtx {
   int rows_valid;  // valid rows of this tile (1..128)
   int col0;        // first column of C
   int split;       // K split index
+  bool live;       // false: the main loop is skipped for this tile (see GemmGeom::tile_weight)
 };
 
 __device__ __forceinline__ TileCtx decode_tile(const GemmGeom& g, int unit, int bn) {
@@ -81,6 +85,7 @@ __device__ __forceinline__ TileCtx decode_tile(const GemmGeom& g, int unit, int 
   t.row0 = t.mt * kBM;
   t.rows_valid = min(kBM, g.rows_per_batch - t.row0);
   t.col0 = n * bn;
+  t.live = !g.tile_weight || __ldg(g.tile_weight + m) != 0.f;
   return t;
 }
 
@@ -238,7 +243,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       for (int unit = blockIdx.x; unit < total_units && alive; unit += gridDim.x) {
         const TileCtx t = decode_tile(geom, unit, BN);
         const int kb0 = t.split * geom.kb_per_split;
-        const int kb1 = min(geom.k_blocks, kb0 + geom.kb_per_split);
+        const int kb1 = t.live ? min(geom.k_blocks, kb0 + geom.kb_per_split) : kb0;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, status, kStatusProducerTimeout)) {
             alive = false;
@@ -282,7 +287,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       for (int unit = blockIdx.x; unit < total_units && alive; unit += gridDim.x, ++iter) {
         const TileCtx t = decode_tile(geom, unit, BN);
         const int kb0 = t.split * geom.kb_per_split;
-        const int kb1 = min(geom.k_blocks, kb0 + geom.kb_per_split);
+        const int kb1 = t.live ? min(geom.k_blocks, kb0 + geom.kb_per_split) : kb0;
         const int acc = iter & 1;
         const uint32_t acc_phase = (iter >> 1) & 1u;
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_flag, status, kStatusMmaTimeout)) {

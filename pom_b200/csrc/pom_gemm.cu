@@ -79,6 +79,7 @@ struct Operands {
   int64_t lda, ldb;
   int batches;
   bool a_mn, b_mn;
+  const float* tile_weight = nullptr;  // optional per (batch, 128-row tile) weights: 0 skips the tile
 };
 
 // `b_rows`: rows of the B tile one CTA loads per stage (K-major B only; MN-major B uses 64-wide boxes).
@@ -124,6 +125,7 @@ GemmGeom make_geom(const Operands& o, int bn, int split_k) {
   g.kb_per_split = static_cast<int>(ceil_div(g.k_blocks, split_k));
   g.split_k = static_cast<int>(ceil_div(g.k_blocks, g.kb_per_split));
   g.group_m = 8;
+  g.tile_weight = o.tile_weight;
   return g;
 }
 
@@ -420,6 +422,7 @@ int pom_ctx_gemm(const pom_ctx_args* a, int* status, void* stream) {
   if (!a || !a->coeff || !a->partial) return POM_ERR_NULL;
   if (a->K < 1) return POM_ERR_BAD_SHAPE;
   Operands o{a->X, a->Wpo, a->N, a->P, a->D, a->ldx, a->ldw, a->B, false, false};
+  o.tile_weight = a->row_weight ? a->tile_weight : nullptr;
   int rc = check_operands(o);
   if (rc) return rc;
   if (a->hp_out && (a->ld_hp % 8 || a->ld_hp < a->P || !aligned16(a->hp_out))) return POM_ERR_BAD_ALIGN;

@@ -17,6 +17,7 @@ struct Workspace {
   // forward
   uint64_t ctx_partial;   // (B, MT_N, P) fp32
   uint64_t h_tmp;         // (B, P) fp32: aggregate before the frame / state merge
+  uint64_t tile_w;        // (B, MT_N) fp32: mask weight of every 128-token tile
   // backward
   uint64_t dh_partial;    // (B, MT_T, P)
   uint64_t db_partial;    // (B, MT_T, P)
@@ -34,6 +35,8 @@ Workspace carve(const pom_layer_args* a) {
   off = align_up(off + static_cast<uint64_t>(m_tiles(a->N)) * bp);
   w.h_tmp = off;
   off = align_up(off + bp);
+  w.tile_w = off;
+  off = align_up(off + static_cast<uint64_t>(a->B) * m_tiles(a->N) * sizeof(float));
   const uint64_t fwd_end = off;
   // the backward regions reuse the buffer from its start
   off = 0;
@@ -120,14 +123,17 @@ int pom_layer_fwd(const pom_layer_args* a, int* status, void* stream) {
   const __nv_bfloat16* w_se = bf(a->w_qc) + static_cast<int64_t>(a->P) * a->D;
   const int64_t BP = static_cast<int64_t>(a->B) * a->P;
 
-  if (a->mask)  // denominators: valid context tokens per sample
+  if (a->mask) {  // denominators (valid context tokens per sample) and the weight of every 128-token tile
     POM_TRY(pom_reduce_partials(a->mask, a->denom, nullptr, 1.f, a->B, a->N, 1, stream));
+    POM_TRY(pom_tile_weights(a->mask, at<float>(a, w.tile_w), a->B, a->N, stream));
+  }
 
   pom_ctx_args c{};
   c.X = xc;
   c.Wpo = w_po;
   c.coeff = a->coeff;
   c.row_weight = a->mask;
+  c.tile_weight = a->mask ? at<float>(a, w.tile_w) : nullptr;  // tiles that the mask empties are skipped
   c.hp_out = a->save ? a->hp : nullptr;
   c.partial = at<float>(a, w.ctx_partial);
   c.ldx = a->D;

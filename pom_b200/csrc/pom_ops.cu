@@ -450,6 +450,10 @@ __global__ void __launch_bounds__(128) agg_bwd_kernel(const AggBwdDev a) {
         }
       }
       float o1[VEC], o2[VEC];
+      if (!CAUSAL && w[q] == 0.f) {  // a token of weight zero: its saved projection may never have been written
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) x1[q][e] = 0.f, x2[q][e] = 0.f;
+      }
 #pragma unroll
       for (int e = 0; e < VEC; ++e) {
         float d1, d2 = 0.f;
@@ -622,6 +626,10 @@ __global__ void __launch_bounds__(kStCols / VEC * 8, 2) agg_bwd_stream_kernel(co
           }
         }
         const float w = a.row_weight ? wb * __ldg(a.row_weight + static_cast<long long>(b) * a.N + n) : wb;
+        if (w == 0.f) {  // a token of weight zero: its saved projection may never have been written
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) x[e] = 0.f;
+        }
 #pragma unroll
         for (int e = 0; e < VEC; ++e) {
           const float d = w * g[e];
@@ -923,6 +931,19 @@ __global__ void state_merge_kernel(const float* hp, const float* hc, float* hn, 
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i < count) hn[i] = (n_past * hp[i] + hc[i]) / (n_past + 1.f);
 }
+// out[b, t] = sum of the 128 mask weights of tile t of sample b (one warp per tile).
+__global__ void tile_weights_kernel(const float* __restrict__ w, float* __restrict__ out, int N, int tiles) {
+  const int t = blockIdx.x, b = blockIdx.y, lane = threadIdx.x;
+  float s = 0.f;
+  for (int r = lane; r < 128; r += 32) {
+    const int n = t * 128 + r;
+    if (n < N) s += w[static_cast<long long>(b) * N + n];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (lane == 0) out[static_cast<long long>(b) * tiles + t] = s;
+}
+
 // Running mean over frames: forward out[b,f,:] = (1/(f+1)) sum_{g<=f} in[b,g,:];
 // adjoint out[b,g,:] = sum_{f>=g} in[b,f,:]/(f+1).  One thread per (b, p).
 __global__ void frame_prefix_kernel(const float* __restrict__ in, float* __restrict__ out, int F, int P, int adjoint) {
@@ -1443,6 +1464,17 @@ int pom_state_merge(const float* h_past, const float* h_cur, float* h_new, float
   if (count <= 0) return POM_ERR_BAD_SHAPE;
   state_merge_kernel<<<static_cast<unsigned>(ceil_div(count, 256)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       h_past, h_cur, h_new, n_past, count);
+  count_launch();
+  return check_launch();
+}
+
+int pom_tile_weights(const float* w, float* out, int32_t B, int32_t N, void* stream) {
+  if (!w || !out) return POM_ERR_NULL;
+  if (B <= 0 || N <= 0) return POM_ERR_BAD_SHAPE;
+  if (B > 65535) return POM_ERR_TOO_LARGE;
+  const int tiles = (N + 127) / 128;
+  tile_weights_kernel<<<dim3(static_cast<unsigned>(tiles), static_cast<unsigned>(B)), 32, 0,
+                        static_cast<cudaStream_t>(stream)>>>(w, out, N, tiles);
   count_launch();
   return check_launch();
 }

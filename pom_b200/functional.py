@@ -226,7 +226,8 @@ class _PoMLayer(torch.autograd.Function):
             return (y, H.view(B, 1, P)) if spec.want_state else (y, None)
         # ---------------------------------------------------------------- context phase
         if fused:
-            partial, hp = ops.ctx_gemm(xc, w_po, coeff32, row_weight=maskf, save_hp=need_grad)
+            partial, hp = ops.ctx_gemm(xc, w_po, coeff32, row_weight=maskf, save_hp=need_grad,
+                                       tile_weight=None if maskf is None else ops.tile_weights(maskf))
             S_part = partial  # per-tile sums; reduced (and normalised, when no exchange is needed) below
         else:
             if spec.self_mixing:

@@ -157,9 +157,19 @@ def m_tiles(n_rows: int) -> int:
 
 
 # ---------------------------------------------------------------------------- fused GEMM phases (bf16)
+def tile_weights(mask: torch.Tensor) -> torch.Tensor:
+    """(B, N) fp32 key-padding weights -> (B, ceil(N/128)) sums per 128-token tile."""
+    _require_cuda(mask)
+    B, N = mask.shape
+    out = torch.empty((B, m_tiles(N)), dtype=torch.float32, device=mask.device)
+    _abi.check(_abi.lib().pom_tile_weights(ptr(mask), ptr(out), B, N, _abi.stream_ptr()), "pom_tile_weights")
+    return out
+
+
 def ctx_gemm(x: torch.Tensor, w_po: torch.Tensor, coeff: torch.Tensor, *, row_weight: Optional[torch.Tensor] = None,
-             save_hp: bool = True):
-    """Context phase: returns (partial (B, MT, P) fp32, hp (B, N, P) bf16 or None)."""
+             save_hp: bool = True, tile_weight: Optional[torch.Tensor] = None):
+    """Context phase: returns (partial (B, MT, P) fp32, hp (B, N, P) bf16 or None).  With ``tile_weight``
+    (from :func:`tile_weights`) tiles that the mask empties are skipped and their rows of hp stay unwritten."""
     dev = _require_cuda(x, w_po, coeff, row_weight)
     B, N, D = x.shape
     P, K = coeff.shape
@@ -168,6 +178,7 @@ def ctx_gemm(x: torch.Tensor, w_po: torch.Tensor, coeff: torch.Tensor, *, row_we
     a = CtxArgs()
     a.X, a.Wpo, a.coeff, a.row_weight = ptr(x), ptr(w_po), ptr(coeff), ptr(row_weight)
     a.hp_out, a.partial = ptr(hp), ptr(partial)
+    a.tile_weight = ptr(tile_weight)
     a.ldx, a.ldw, a.ld_hp = _row_stride(x), _row_stride(w_po), P
     a.B, a.N, a.D, a.P, a.K = B, N, D, P, K
     _abi.check(_abi.lib().pom_ctx_gemm(C.byref(a), ptr(_abi.status_word(dev)), _abi.stream_ptr()), "pom_ctx_gemm")

@@ -202,6 +202,28 @@ def test_block_causal_mask_equals_frame_loop(rope):
         assert_close(torch.cat(outs, 1), y, BF16_TOL, "frame loop vs block-causal mask")
 
 
+def test_prefix_length_mask_with_empty_tiles_matches_oracle():
+    """Key-padding by valid lengths: 128-token tiles that the mask empties are skipped by the context GEMM (their
+    saved projection is never written), which must not change outputs or gradients.  The allocator is primed with
+    NaNs so that any use of an unwritten row would show."""
+    B, N, D, K, E = 3, 512, 64, 2, 2
+    cfg, params, x, gy = _seeded_case(B, N, D, K, E, seed=21, coeff_scale=0.1, bias_scale=0.3)
+    params = {k: O.bf16_round(v) for k, v in params.items()}
+    x, gy = O.bf16_round(x), O.bf16_round(gy)
+    lengths = torch.tensor([100, 256, 512])
+    mask = (torch.arange(N).view(1, N) < lengths.view(B, 1)).float()
+    want_y, want_g = oracle_run(cfg, params, x, None, {"mask": mask}, gy)
+    mod = make_cuda_module(cfg, params, torch.bfloat16)
+    junk = torch.full((32 << 20,), float("nan"), device="cuda", dtype=torch.bfloat16)
+    del junk
+    y, grads = cuda_run(mod, x, None, {"mask": mask}, gy, torch.bfloat16)
+    assert_status_clean()
+    assert_close(y, want_y, BF16_TOL, "y")
+    for k, w in want_g.items():
+        assert torch.isfinite(grads[k].float()).all(), k
+        assert_close(grads[k], w, BF16_TOL, f"d_{k}")
+
+
 def test_bf16_masked_layer_ignores_padded_noise():
     """BASELINE config 3 at reduced size: key-padding mask from per-sample lengths, noise in the padding."""
     B, N, D, K, E = 4, 512, 128, 3, 2
