@@ -309,6 +309,9 @@ def main():
     ap.add_argument("--exchange", default="peer", choices=["nccl", "peer"],
                     help="token-sharded runs: carry the cross-rank sums by NCCL calls between kernels, or by the "
                          "library's own peer-memory kernels (graph-capturable; turns --graph on unless given)")
+    ap.add_argument("--no-overlap-grad-reduce", action="store_true",
+                    help="peer exchange: run the parameter-gradient all-reduce on the main stream after the last GEMM "
+                         "instead of on a side stream beside the data-gradient GEMM")
     ap.add_argument("--tokens", type=int, default=0, help="override the workload's tokens per sample (N)")
     args = ap.parse_args()
     w = dict(WORKLOADS[args.workload])
@@ -358,6 +361,8 @@ def main():
         args.graph = "on"
     if args.defer_weight_grad_reduce and "shard" in kw:
         kw["shard"].reduce_weight_grads = False
+    if args.no_overlap_grad_reduce and "shard" in kw:
+        kw["shard"].overlap_grad_reduce = False
     params = list(mod.parameters())
     video = "layers" in w
     if video:

@@ -49,6 +49,13 @@ class SeqShard:
     group: Any = None
     reduce_weight_grads: bool = True
     peer: Any = None
+    overlap_grad_reduce: bool = True   # peer transport: all-reduce the parameter gradients on a side stream
+    _side: Any = None
+
+    def side_stream(self):
+        if self._side is None:
+            self._side = torch.cuda.Stream()
+        return self._side
 
     @property
     def world(self) -> int:
@@ -402,21 +409,36 @@ class _PoMLayer(torch.autograd.Function):
                              scale=scale, rope=spec.rope_ctx, dcoeff_out=d_coeff)
 
         # ---------------------------------------------------------------- projections backward
+        dts = {p_qc.dtype, p_bias.dtype, p_coeff.dtype, p_ag.dtype}
+        overlap = peer_flat and shard.overlap_grad_reduce and dts == {torch.bfloat16}
+        f16 = None
+        # weight-gradient products first, so that (peer transport) their all-reduce over NVLink and the cast run on
+        # a side stream beside the data-gradient products: its 128 small CTAs fit next to the GEMM's one CTA per SM
+        if spec.self_mixing:
+            ops.gemm(G, xq.view(B * T, D), a_mn=True, b_mn=True, out=d_wqc, accumulate=True)
+        else:
+            ops.gemm(g_hp, xc.view(B * N, D), a_mn=True, b_mn=True, out=d_wqc[:P], accumulate=True)
+            ops.gemm(g_z, xq.view(B * T, D), a_mn=True, b_mn=True, out=d_wqc[P:], accumulate=True)
+        if overlap:
+            main, side = torch.cuda.current_stream(), shard.side_stream()
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                shard.reduce_grads(flat)
+                f16 = ops.to_bf16(flat)
         if spec.self_mixing:
             dxq = ops.gemm(G, w_qc, b_mn=True).view(B, T, D)
-            ops.gemm(G, xq.view(B * T, D), a_mn=True, b_mn=True, out=d_wqc, accumulate=True)
             dxc = None
         else:
             dxc = ops.gemm(g_hp, w_qc[:P], b_mn=True).view(B, N, D)
             dxq = ops.gemm(g_z, w_qc[P:], b_mn=True).view(B, T, D)
-            ops.gemm(g_hp, xc.view(B * N, D), a_mn=True, b_mn=True, out=d_wqc[:P], accumulate=True)
-            ops.gemm(g_z, xq.view(B * T, D), a_mn=True, b_mn=True, out=d_wqc[P:], accumulate=True)
-
-        if shard is not None and shard.reduce_weight_grads:
+        if overlap:
+            main.wait_stream(side)
+            f16.record_stream(main)
+        elif shard is not None and shard.reduce_weight_grads:
             shard.reduce_grads(flat)
-        dts = {p_qc.dtype, p_bias.dtype, p_coeff.dtype, p_ag.dtype}
         if dts == {torch.bfloat16}:
-            f16 = ops.to_bf16(flat)
+            if f16 is None:
+                f16 = ops.to_bf16(flat)
             g_qc, g_ag = f16[:n_qc].view(P + S, D), f16[n_qc:n_qc + n_ag].view(D, P)
             g_bias, g_coeff = f16[n_qc + n_ag:n_qc + n_ag + S], f16[n_qc + n_ag + S:].view(P, K)
         else:

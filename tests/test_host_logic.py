@@ -1,0 +1,64 @@
+"""Host-side arithmetic of the C ABI that needs no GPU: buffer layouts, workspace sizes, argument checks."""
+import ctypes as C
+
+import pytest
+
+from pom_b200 import _abi, _build
+
+
+@pytest.fixture(scope="module")
+def lib():
+    _build.build()
+    return _abi.lib()
+
+
+def test_peer_layout_offsets(lib):
+    lay = (C.c_ulonglong * 3)()
+    assert lib.pom_peer_layout(8, 4096, 1024, lay) == 0
+    assert lay[0] == 65536                                   # header
+    assert lay[1] == lay[0] + 2 * 8 * 4096 * 4               # two epochs x eight writers x slot
+    assert lay[2] == lay[1] + 1024 * 4
+    assert lib.pom_peer_layout(17, 4096, 0, lay) < 0         # more ranks than the header has flags for
+    assert lib.pom_peer_layout(2, 4095, 0, lay) < 0          # slots are multiples of 4 floats (16-byte accesses)
+
+
+def test_layer_workspace_covers_both_passes(lib):
+    a = _abi.LayerArgs()
+    a.B, a.T, a.N, a.D, a.P, a.K = 32, 1024, 1024, 1152, 2304, 2
+    a.self_mixing, a.frames = 1, 1
+    n = int(lib.pom_layer_workspace_bytes(C.byref(a)))
+    bp = 32 * 2304 * 4
+    fwd = 8 * bp + bp                       # per-tile sums of 8 m-tiles + one (B, P) vector
+    bwd = 2 * 8 * bp + 16 * bp * 2 + 2 * bp  # two partial sets, coefficient partials (16 chunks x K), two vectors
+    assert n >= max(fwd, bwd) and n < 2 * max(fwd, bwd)
+    a.N = 0
+    assert int(lib.pom_layer_workspace_bytes(C.byref(a))) == 0
+
+
+def test_layer_entry_points_validate_before_touching_the_gpu(lib):
+    a = _abi.LayerArgs()
+    assert lib.pom_layer_fwd(C.byref(a), None, None) == -8      # null pointers
+    a.B, a.T, a.N, a.D, a.P, a.K = 2, 16, 16, 60, 120, 2         # D not a multiple of 8
+    a.self_mixing, a.frames = 1, 1
+    dummy = C.c_void_p(256)
+    for f in ("xq", "w_qc", "w_ag", "se_bias", "coeff", "H", "workspace"):
+        setattr(a, f, dummy)
+    a.workspace_bytes = 1 << 30
+    assert lib.pom_layer_fwd(C.byref(a), None, None) == -3      # alignment
+    a.D, a.P, a.K = 64, 128, 17
+    assert lib.pom_layer_fwd(C.byref(a), None, None) == -5      # degree above 16
+    a.K, a.frames = 2, 3                                         # B not a multiple of frames
+    assert lib.pom_layer_fwd(C.byref(a), None, None) == -1
+    a.frames, a.workspace_bytes = 1, 16
+    assert lib.pom_layer_fwd(C.byref(a), None, None) == -9      # workspace too small
+
+
+def test_backward_partial_slot_count_never_exceeds_the_chunk_capacity(lib):
+    a = _abi.AggBwdArgs()
+    for B, N, P in ((32, 1024, 2304), (1, 65536, 2304), (64, 2048, 2048), (3, 70, 96)):
+        a.B, a.N, a.P, a.K = B, N, P, 2
+        a.dtype, a.causal = 0, 0
+        a.ldx = a.ld_dx = P
+        a.x = a.dx = C.c_void_p(512)
+        slots = lib.pom_poly_agg_bwd_slots(C.byref(a))
+        assert 0 < slots <= B * lib.pom_agg_chunks(N)
