@@ -500,16 +500,17 @@ __global__ void __launch_bounds__(128) agg_bwd_kernel(const AggBwdDev a) {
 // ------------------------------------------------------------------ streamed backward
 // The bf16, non-causal, no-rotary backward (the one on the fused layer path) as a staged stream: a CTA owns
 // 256 channels of one sample and a run of 64-token tiles; warp 0 brings each tile's rows into a 3-deep shared
-// memory ring with 512-byte bulk copies that complete on an mbarrier, so the bytes in flight sit in shared
-// memory (96 KiB per CTA, two CTAs per SM) instead of in registers; all 8 warps then read 16 bytes per thread,
-// compute, and store dx straight from registers.  The coefficient sums stay in registers over the whole run
+// memory ring with 512-byte bulk copies that complete on a "full" mbarrier, so the bytes in flight sit in shared
+// memory (96 KiB per CTA, two CTAs per SM) instead of in registers; all 8 warps read 16 bytes per thread,
+// compute, store dx straight from registers and release the stage on an "empty" mbarrier (one arrival per
+// warp) — no CTA-wide barrier inside the loop.  The coefficient sums stay in registers over the whole run
 // and are combined across the 8 row groups in a fixed order at the end: one partial per (sample, run).
 constexpr int kStTok = 64;
 constexpr int kStCols = 256;
 constexpr int kStStages = 3;
 constexpr int kStVec = 8;       // channels per thread (16-byte accesses): 256 threads per CTA
 constexpr int kStTileBytes = kStTok * kStCols * 2;
-constexpr int kStSmemBytes = kStStages * kStTileBytes + 128;
+constexpr int kStSmemBytes = kStStages * kStTileBytes + 128;  // ring + full/empty barriers + abort flag
 constexpr int kStatusStreamTimeout = 201;
 
 __device__ int g_ops_status;  // first bounded wait of an operator kernel that expired (0 = none)
@@ -539,15 +540,19 @@ inline StreamPlan stream_plan(int B, int N, int P) {
   return s;
 }
 
-template <int KR, int VEC>
-__global__ void __launch_bounds__(kStCols / VEC * 8, 2) agg_bwd_stream_kernel(const AggBwdDev a, int tiles_per_cta, int splits,
+// PROD: a ninth warp does nothing but issue the copies (fastest, but 288 threads leave 112 registers per thread,
+// which the degree-3/4 variant would spill); otherwise warp 0 issues them between its own tiles.
+template <int KR, int VEC, bool PROD>
+__global__ void __launch_bounds__(kStCols / VEC * 8 + (PROD ? 32 : 0), 2) agg_bwd_stream_kernel(const AggBwdDev a, int tiles_per_cta, int splits,
                                                                        int* status) {
   extern __shared__ __align__(128) uint8_t st_smem[];
   __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(st_smem);
   uint64_t* full = reinterpret_cast<uint64_t*>(st_smem + kStStages * kStTileBytes);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(full + kStStages);
+  uint64_t* empty = full + kStStages;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + kStStages);
   constexpr int kLanes = kStCols / VEC;   // threads across one row
   constexpr int kGroups = 8;              // row groups
+  constexpr int kConsumers = kLanes * kGroups;
   const int tid = threadIdx.x, tx = tid % kLanes, ty = tid / kLanes;
   const int warp = tid >> 5, lane = tid & 31;
   const int p0 = blockIdx.x * kStCols, split = blockIdx.y, b = blockIdx.z;
@@ -556,7 +561,10 @@ __global__ void __launch_bounds__(kStCols / VEC * 8, 2) agg_bwd_stream_kernel(co
   const int t_begin = split * tiles_per_cta;
   const int my_tiles = min(tiles_total, t_begin + tiles_per_cta) - t_begin;
   if (tid == 0) {
-    for (int s = 0; s < kStStages; ++s) mbar_init(&full[s], 1);
+    for (int s = 0; s < kStStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], kConsumers / 32);
+    }
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -564,7 +572,7 @@ __global__ void __launch_bounds__(kStCols / VEC * 8, 2) agg_bwd_stream_kernel(co
 
   const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(a.x) + static_cast<long long>(b) * a.N * a.ldx + p0;
   __nv_bfloat16* dxb = static_cast<__nv_bfloat16*>(a.dx) + static_cast<long long>(b) * a.N * a.ld_dx + p0;
-  auto issue = [&](int i) {  // warp 0, all lanes
+  auto issue = [&](int i) {  // producer warp, all lanes
     const int stage = i % kStStages;
     const int n0 = (t_begin + i) * kStTok;
     const int rows = min(kStTok, a.N - n0);
@@ -574,11 +582,22 @@ __global__ void __launch_bounds__(kStCols / VEC * 8, 2) agg_bwd_stream_kernel(co
       bulk_load_row(ring + (stage * kStTok + r) * kStCols, xb + static_cast<long long>(n0 + r) * a.ldx,
                     static_cast<uint32_t>(width * 2), &full[stage]);
   };
-  if (warp == 0)
+  const bool consumer = !PROD || warp < kConsumers / 32;
+  if (PROD && !consumer) {
+    // producer warp: refill a stage as soon as every consumer warp has released it
+    for (int i = 0; i < my_tiles; ++i) {
+      if (i >= kStStages &&
+          !mbar_wait(&empty[i % kStStages], static_cast<uint32_t>(i / kStStages - 1) & 1u, abort_flag, status,
+                     kStatusStreamTimeout))
+        break;
+      issue(i);
+    }
+  }
+  if (!PROD && warp == 0)
     for (int i = 0; i < kStStages - 1 && i < my_tiles; ++i) issue(i);
 
   const int c = tx * VEC;
-  const bool live = c < width;
+  const bool live = consumer && c < width;
   float cf[VEC][KR], g[VEC], dc[VEC][KR];
 #pragma unroll
   for (int e = 0; e < VEC; ++e) {
@@ -595,13 +614,20 @@ __global__ void __launch_bounds__(kStCols / VEC * 8, 2) agg_bwd_stream_kernel(co
     wb = dn != 0.f ? wb / dn : 0.f;
   }
 
-  for (int i = 0; i < my_tiles; ++i) {
+  for (int i = 0; i < my_tiles && consumer; ++i) {
     const int stage = i % kStStages;
-    const bool ok = mbar_wait(&full[stage], static_cast<uint32_t>(i / kStStages) & 1u, abort_flag, status,
-                              kStatusStreamTimeout);
-    // also the point where every thread has finished reading the stage that is refilled next
-    if (__syncthreads_or(!ok)) return;
-    if (warp == 0 && i + kStStages - 1 < my_tiles) issue(i + kStStages - 1);
+    if (!PROD && warp == 0) {
+      // refill the stage of tile i-1 with tile i+S-1 once every warp has released it (no CTA-wide barrier)
+      const int j = i + kStStages - 1;
+      if (j < my_tiles) {
+        if (j >= kStStages && !mbar_wait(&empty[j % kStStages], static_cast<uint32_t>(j / kStStages - 1) & 1u,
+                                         abort_flag, status, kStatusStreamTimeout))
+          break;
+        issue(j);
+      }
+    }
+    if (!mbar_wait(&full[stage], static_cast<uint32_t>(i / kStStages) & 1u, abort_flag, status, kStatusStreamTimeout))
+      break;
     const int n0 = (t_begin + i) * kStTok;
     const int rows = min(kStTok, a.N - n0);
     if (live) {
@@ -652,11 +678,14 @@ __global__ void __launch_bounds__(kStCols / VEC * 8, 2) agg_bwd_stream_kernel(co
         }
       }
     }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[stage]);  // this warp is done reading the stage
   }
   // every bulk copy issued above has been waited for: the ring is free to hold the coefficient sums
   __syncthreads();
+  if (*abort_flag) return;  // a wait expired (status word set): leave the outputs incomplete rather than wrong
   float* red = reinterpret_cast<float*>(st_smem);  // [row group 1..7][value][thread of the row]
-  if (ty > 0) {
+  if (ty > 0 && consumer) {
 #pragma unroll
     for (int e = 0; e < VEC; ++e)
 #pragma unroll
@@ -1282,14 +1311,18 @@ int pom_poly_agg_bwd(const pom_agg_bwd_args* a, void* stream) {
     if (sp.splits > 65535) return POM_ERR_TOO_LARGE;
     static std::once_flag attr_once;
     std::call_once(attr_once, [] {
-      cudaFuncSetAttribute(agg_bwd_stream_kernel<2, kStVec>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStSmemBytes);
-      cudaFuncSetAttribute(agg_bwd_stream_kernel<4, kStVec>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStSmemBytes);
+      cudaFuncSetAttribute(agg_bwd_stream_kernel<2, kStVec, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           kStSmemBytes);
+      cudaFuncSetAttribute(agg_bwd_stream_kernel<4, kStVec, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           kStSmemBytes);
     });
     constexpr int threads = kStCols / kStVec * 8;
     if (a->K <= 2)
-      agg_bwd_stream_kernel<2, kStVec><<<sgrid, threads, kStSmemBytes, st>>>(d, sp.tiles_per_cta, sp.splits, status);
+      agg_bwd_stream_kernel<2, kStVec, true><<<sgrid, threads + 32, kStSmemBytes, st>>>(d, sp.tiles_per_cta, sp.splits,
+                                                                                        status);
     else
-      agg_bwd_stream_kernel<4, kStVec><<<sgrid, threads, kStSmemBytes, st>>>(d, sp.tiles_per_cta, sp.splits, status);
+      agg_bwd_stream_kernel<4, kStVec, false><<<sgrid, threads, kStSmemBytes, st>>>(d, sp.tiles_per_cta, sp.splits,
+                                                                                    status);
     count_launch();
     return check_launch();
   }
