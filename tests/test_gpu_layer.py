@@ -82,7 +82,7 @@ def _seeded_case(B, N, D, K, E, seed=0, coeff_scale=None, bias_scale=0.0):
 
 
 def test_fp32_reference_cpu_configuration(golden):
-    """BASELINE config 1 (fp32, B=2, N=256, D=256, degree 2, expand 2, seed 0) on the GPU."""
+    """benchmark configuration 1 (fp32, B=2, N=256, D=256, degree 2, expand 2, seed 0) on the GPU."""
     from pom_b200 import PoM
 
     case = golden["cfg1_fp32"]
@@ -98,7 +98,7 @@ def test_fp32_reference_cpu_configuration(golden):
 @pytest.mark.parametrize("coeff_scale", [None, 0.1])
 @pytest.mark.parametrize("shape", [(2, 1024, 1152, 2, 2), (3, 200, 96, 3, 2), (2, 130, 64, 4, 1)])
 def test_bf16_fused_path_against_oracle(shape, coeff_scale):
-    """DiT-style no-mask layer (BASELINE config 2 at reduced batch) and ragged shapes that leave partial
+    """DiT-style no-mask layer (benchmark configuration 2 at reduced batch) and ragged shapes that leave partial
     tiles in every dimension; default (tiny) and O(1) polynomial coefficients."""
     B, N, D, K, E = shape
     cfg, params, x, gy = _seeded_case(B, N, D, K, E, coeff_scale=coeff_scale, bias_scale=0.5)
@@ -225,7 +225,7 @@ def test_prefix_length_mask_with_empty_tiles_matches_oracle():
 
 
 def test_bf16_masked_layer_ignores_padded_noise():
-    """BASELINE config 3 at reduced size: key-padding mask from per-sample lengths, noise in the padding."""
+    """benchmark configuration 3 at reduced size: key-padding mask from per-sample lengths, noise in the padding."""
     B, N, D, K, E = 4, 512, 128, 3, 2
     cfg, params, x, gy = _seeded_case(B, N, D, K, E, seed=3, coeff_scale=0.1)
     params = {k: O.bf16_round(v) for k, v in params.items()}
@@ -271,7 +271,7 @@ def test_state_forward_matches_reference_vectors(golden):
 
 
 def test_block_causal_video_stack_frame_loop():
-    """BASELINE config 4 at reduced size: a residual stack of PoM + GELU FFN layers run frame by frame
+    """benchmark configuration 4 at reduced size: a residual stack of PoM + GELU FFN layers run frame by frame
     with state_forward equals the oracle's frame loop; bf16."""
     B, F, L, D, K, E, layers = 2, 4, 64, 64, 2, 4, 3
     g = torch.Generator().manual_seed(4)
@@ -350,7 +350,7 @@ def test_token_causal_long_sequence_against_linear_time_oracle():
 
 
 def test_rope2d_grid_bf16_against_oracle():
-    """BASELINE config 5 at reduced size: 2-D axial rotary positions on a 32 x 32 grid, non-causal and causal."""
+    """benchmark configuration 5 at reduced size: 2-D axial rotary positions on a 32 x 32 grid, non-causal and causal."""
     D, K, E, side = 64, 2, 2, 32
     N = side * side
     cfg, params, x, gy = _seeded_case(1, N, D, K, E, seed=7, coeff_scale=0.1)
@@ -379,7 +379,7 @@ def test_results_are_bitwise_reproducible():
 
 
 def test_full_size_dit_layer_properties():
-    """BASELINE config 2 at full size (B=32, N=1024, D=1152): size-independent properties.
+    """benchmark configuration 2 at full size (B=32, N=1024, D=1152): size-independent properties.
     (1) permuting the tokens of a sample permutes its outputs (no-mask mixing is a set function);
     (2) the backward pass is linear in the upstream gradient."""
     B, N, D, K, E = 32, 1024, 1152, 2, 2

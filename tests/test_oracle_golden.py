@@ -90,7 +90,7 @@ def test_operator_matches_reference_vectors(golden, k, kind):
 
 
 def test_reference_cpu_configuration_replayed_from_seeds(golden):
-    """BASELINE config 1: fp32, B=2, N=256, D=256, degree 2, expand 2, seed 0 weights and inputs."""
+    """benchmark configuration 1: fp32, B=2, N=256, D=256, degree 2, expand 2, seed 0 weights and inputs."""
     from pom_b200.pom import PoM
 
     case = golden["cfg1_fp32"]
