@@ -11,6 +11,8 @@ Workloads
   dit            B=32, N=1024 (32x32 patches), D=1152, degree 2, expand 2, bf16, no mask.  With
                  --gpus N every rank runs its own batch of 32 samples (weak scaling, no collective
                  on the data path: samples are independent).
+  dit_heads16    dit with n_sel_heads=16 (one gate value per head, as the reference's own benchmarks instantiate the
+                 layer): the query side collapses to (heads x D) matrices per sample, see csrc/pom_heads.cu.
   masked         B=64, N=2048, D=1024, degree 3, expand 2, key-padding mask (lengths U[256, 2048]).
   seq64k         B=1, N=65536 (256x256 grid, 2-D rotary), D=1152, token-sharded over the ranks
                  (strong scaling; all-reduce of the (B, P) partial sums, weight-gradient all-reduce
@@ -38,6 +40,7 @@ sys.path.insert(0, ROOT)
 
 WORKLOADS = {
     "dit": dict(B=32, N=1024, D=1152, degree=2, expand=2, mask="none", rope=None, shard="batch"),
+    "dit_heads16": dict(B=32, N=1024, D=1152, degree=2, expand=2, mask="none", rope=None, shard="batch", heads=16),
     "masked": dict(B=64, N=2048, D=1024, degree=3, expand=2, mask="keypad", rope=None, shard="batch"),
     "seq64k": dict(B=1, N=65536, D=1152, degree=2, expand=2, mask="none", rope="2d", shard="token"),
     "seq64k_causal": dict(B=1, N=65536, D=1152, degree=2, expand=2, mask="causal", rope="2d", shard="token"),
@@ -138,7 +141,8 @@ def cpu_reference_tokens_per_s(w, steps, warmup, sample_tokens=4096):
         B = max(1, sample_tokens // N)
     else:
         B, N = 1, sample_tokens
-    params = {k: v.requires_grad_(True) for k, v in O.init_params(D, K, E, seed=0).items()}
+    heads = w.get("heads", 1)
+    params = {k: v.requires_grad_(True) for k, v in O.init_params(D, K, E, heads, seed=0).items()}
     rope = None
     kw = {}
     if w["rope"] == "2d":
@@ -146,7 +150,7 @@ def cpu_reference_tokens_per_s(w, steps, warmup, sample_tokens=4096):
         N = side * side
         rope = O.RopeConfig(two_d=True, max_h=side, max_w=side)
         kw["positions_hw"] = torch.stack([torch.arange(N) // side, torch.arange(N) % side], 1)
-    model = O.OraclePoM(params, K, E, 1, rope)
+    model = O.OraclePoM(params, K, E, heads, rope)
     g = torch.Generator().manual_seed(0)
     x = torch.randn(B, N, D, generator=g).requires_grad_(True)
     gy = torch.randn(B, N, D, generator=g)
@@ -245,7 +249,7 @@ def build_case(w, rank, world, device, exchange="nccl"):
         side = int(w["N"] ** 0.5)
         mod = PoMRoPE(D, K, E, 1, 1, rope_2d=True, max_h=side, max_w=side)
     else:
-        mod = PoM(D, K, E, 1, 1)
+        mod = PoM(D, K, E, 1, w.get("heads", 1))
     mod = mod.to(device)
     for p in mod.parameters():
         p.data = p.data.to(torch.bfloat16)

@@ -334,6 +334,38 @@ typedef struct pom_select_heads_args {
 int pom_select_heads_fwd(const pom_select_heads_args* a, void* stream);
 int pom_select_heads_bwd(const pom_select_heads_args* a, void* stream);
 
+/* Multi-head gating (n_sel_heads > 1, reference pom/pom.py:119-122) with a per-sample aggregate H: the gate has
+ * one value per head, so  y[b,t,:] = sum_h s[b,t,h] * Mb[b,h,:]  with  Mb[b,h,d] = sum_{p in head h} H[b,p] Wo[d,p].
+ * These four calls replace pom_select_heads_* plus the output projection and its two backward GEMMs
+ * (pom/pom.py:231 and autograd) by products whose inner dimension is the head count:
+ *   pom_heads_mix      Mb from H and Wo
+ *   pom_heads_out_fwd  y = s·Mb (+ residual)
+ *   pom_heads_out_bwd  ds[b,t,h] = sum_d dy·Mb ;  dMb[b,h,d] = sum_t s·dy   (dMb_partial: scratch)
+ *   pom_heads_mix_bwd  dH[b,p] = sum_d dMb[b,head(p),d] Wo[d,p] ;  dWo[d,p] += sum_b dMb[b,head(p),d] H[b,p]
+ * dtype (POM_BF16 / POM_F32) is that of Wo, y, residual and dy; everything else is fp32.  heads <= 64, P % heads == 0,
+ * D % 4 == 0 and heads * D fp32 must fit in shared memory (pom_heads_supported). */
+typedef struct pom_heads_args {
+  const float* H;        /* (B, P) */
+  const void* Wo;        /* (D, P), row stride ldw */
+  const float* s;        /* (B, T, heads) gate values */
+  float* Mb;             /* (B, heads, D) */
+  void* y;               /* (B, T, D) */
+  const void* residual;  /* (B, T, D) or NULL */
+  const void* dy;        /* (B, T, D) */
+  float* ds;             /* (B, T, heads) */
+  float* dMb_partial;    /* (B, ceil(T/128), heads, D) scratch */
+  float* dMb;            /* (B, heads, D) */
+  float* dH;             /* (B, P) */
+  float* dWo;            /* (D, P) contiguous, accumulated into */
+  int64_t ldw;
+  int32_t B, T, D, P, heads, dtype;
+} pom_heads_args;
+int pom_heads_supported(int32_t heads, int32_t D, int32_t P);
+int pom_heads_mix(const pom_heads_args* a, void* stream);
+int pom_heads_out_fwd(const pom_heads_args* a, void* stream);
+int pom_heads_out_bwd(const pom_heads_args* a, void* stream);
+int pom_heads_mix_bwd(const pom_heads_args* a, void* stream);
+
 /* Running-mean state update of state_forward (reference pom/pom.py:255-259):
  *   h_new[b,:] = (n_past * h_past[b,:] + h_cur[b,:]) / (n_past + 1)        (fp32, B*P elements) */
 int pom_state_merge(const float* h_past, const float* h_cur, float* h_new, float n_past, int64_t count, void* stream);

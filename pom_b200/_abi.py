@@ -138,6 +138,17 @@ class SelectHeadsArgs(C.Structure):
     ]
 
 
+class HeadsArgs(C.Structure):
+    _fields_ = [
+        ("H", C.c_void_p), ("Wo", C.c_void_p), ("s", C.c_void_p), ("Mb", C.c_void_p), ("y", C.c_void_p),
+        ("residual", C.c_void_p), ("dy", C.c_void_p), ("ds", C.c_void_p), ("dMb_partial", C.c_void_p),
+        ("dMb", C.c_void_p), ("dH", C.c_void_p), ("dWo", C.c_void_p),
+        ("ldw", C.c_int64),
+        ("B", C.c_int32), ("T", C.c_int32), ("D", C.c_int32), ("P", C.c_int32), ("heads", C.c_int32),
+        ("dtype", C.c_int32),
+    ]
+
+
 class LayerArgs(C.Structure):
     _fields_ = [
         ("B", C.c_int32), ("T", C.c_int32), ("N", C.c_int32), ("D", C.c_int32), ("P", C.c_int32), ("K", C.c_int32),
@@ -203,6 +214,11 @@ _SIGNATURES = {
     "pom_fill_zero": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p]),
     "pom_cast_f32_to_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "pom_cast_bf16_to_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
+    "pom_heads_supported": (C.c_int, [C.c_int32, C.c_int32, C.c_int32]),
+    "pom_heads_mix": (C.c_int, [C.POINTER(HeadsArgs), C.c_void_p]),
+    "pom_heads_out_fwd": (C.c_int, [C.POINTER(HeadsArgs), C.c_void_p]),
+    "pom_heads_out_bwd": (C.c_int, [C.POINTER(HeadsArgs), C.c_void_p]),
+    "pom_heads_mix_bwd": (C.c_int, [C.POINTER(HeadsArgs), C.c_void_p]),
     "pom_layer_workspace_bytes": (C.c_uint64, [C.POINTER(LayerArgs)]),
     "pom_layer_fwd": (C.c_int, [C.POINTER(LayerArgs), C.c_void_p, C.c_void_p]),
     "pom_layer_bwd": (C.c_int, [C.POINTER(LayerArgs), C.c_void_p, C.c_void_p]),

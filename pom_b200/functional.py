@@ -210,6 +210,8 @@ class _PoMLayer(torch.autograd.Function):
                  and P % 8 == 0 and D % 8 == 0)
 
         hp = z = Hc = s32 = None
+        collapsed = False
+        ctx.collapsed = False
         ctx.composite = fused and shard is None and WHOLE_LAYER_CALLS
         if ctx.composite:
             # the whole fused layer is one library call (no exchange to put between its phases)
@@ -276,17 +278,27 @@ class _PoMLayer(torch.autograd.Function):
         elif heads:
             ones = _ones(B, heads, xq.device)
             s32 = _f32(ops.select_fwd(z, bias32, ones, rope=spec.rope_qry))   # gate in head space (B, T, heads)
-            sh = ops.select_heads_fwd(s32, Hc if causal else H, xq.dtype)
+            # one aggregate per sample: the P-wide gated state and its output GEMM collapse to a (heads x D)
+            # matrix per sample (pom_heads_*); per-token aggregates (causal) keep the explicit form
+            collapsed = not causal and ops.heads_supported(heads, D, P)
+            if collapsed:
+                sh = ops.heads_mix(H, w_ag, heads)  # Mb (B, heads, D), kept in the slot of the gated state
+            else:
+                sh = ops.select_heads_fwd(s32, Hc if causal else H, xq.dtype)
         else:
             sh = ops.select_fwd(z, bias32, Hc if (causal or full) else H, rope=spec.rope_qry, row_denom=rowden)
         if residual is not None and not bf16:
             raise NotImplementedError("the fused residual add of the output projection is a bf16 feature")
-        y = ops.gemm(sh.view(B * T, P), w_ag,
-                     residual=None if residual is None else residual.contiguous().view(B * T, D)).view(B, T, D)
+        if collapsed:
+            y = ops.heads_out_fwd(s32, sh, xq.dtype, None if residual is None else residual.contiguous())
+        else:
+            y = ops.gemm(sh.view(B * T, P), w_ag,
+                         residual=None if residual is None else residual.contiguous().view(B * T, D)).view(B, T, D)
 
         ctx.has_residual = residual is not None
         ctx.spec = spec
         ctx.fused = fused
+        ctx.collapsed = collapsed
         ctx.dims = (B, T, N, D, P, K, S, heads, n_glob, offset)
         ctx.h_past_dtype = None if h_past is None else h_past.dtype
         ctx.save_for_backward(xq, xc, w_qc, w_ag, coeff32, bias32, hp, z, H, Hc, sh, maskf, denom, s32, maskd, rowden)
@@ -345,8 +357,9 @@ class _PoMLayer(torch.autograd.Function):
         d_wag = flat[n_qc:n_qc + n_ag].view(D, P)
         d_bias = flat[n_qc + n_ag:n_qc + n_ag + S]
         d_coeff = flat[n_qc + n_ag + S:n_flat].view(P, K)
-        # dWo[d, p] = sum_t dY[t, d] * SH[t, p]
-        ops.gemm(dy2, sh.view(B * T, P), a_mn=True, b_mn=True, out=d_wag, accumulate=True)
+        # dWo[d, p] = sum_t dY[t, d] * SH[t, p]   (collapsed multi-head path: formed from dMb further down)
+        if not ctx.collapsed:
+            ops.gemm(dy2, sh.view(B * T, P), a_mn=True, b_mn=True, out=d_wag, accumulate=True)
 
         if spec.self_mixing:
             G = torch.empty((B * T, P + S), dtype=dt, device=dev)
@@ -360,6 +373,12 @@ class _PoMLayer(torch.autograd.Function):
             dh_p, db_p = ops.gate_bwd_gemm(dy, w_ag, bias32, H, z, g_z)
             dH = ops.reduce_partials(dh_p)
             ops.reduce_partials(db_p.view(1, -1, P), out=d_bias.view(1, P))
+        elif ctx.collapsed:
+            ds32, dMb = ops.heads_out_bwd(dy, s32, sh)          # sh holds Mb here
+            dH = ops.heads_mix_bwd(dMb, H, w_ag, d_wag)         # also dWo
+            ds = ds32 if dt == torch.float32 else ops.to_bf16(ds32)
+            ops.select_bwd(ds, z, bias32, _ones(B, heads, dev), g_z.view(B, T, heads), rope=spec.rope_qry,
+                           dbias_out=d_bias)
         else:
             dsh = ops.gemm(dy2, w_ag, b_mn=True).view(B, T, P)
             if heads:

@@ -437,6 +437,68 @@ def select_heads_bwd(dsh: torch.Tensor, s: torch.Tensor, h: torch.Tensor, ds_out
     return dh_tok if per_tok else reduce_partials(dh_p)
 
 
+# ---------------------------------------------------------------------------- multi-head gate, collapsed output side
+def heads_supported(heads: int, D: int, P: int) -> bool:
+    return bool(_abi.lib().pom_heads_supported(heads, D, P))
+
+
+def _heads_common(B, T, D, P, heads, dtype):
+    a = _abi.HeadsArgs()
+    a.B, a.T, a.D, a.P, a.heads, a.dtype = B, T, D, P, heads, _abi.dtype_code(dtype)
+    return a
+
+
+def heads_mix(H: torch.Tensor, w_ag: torch.Tensor, heads: int) -> torch.Tensor:
+    """Mb[b, h, d] = sum over the channels p of head h of H[b, p] * Wo[d, p]  ->  (B, heads, D) fp32."""
+    dev = _require_cuda(H, w_ag)
+    B, P = H.shape
+    D = w_ag.shape[0]
+    Mb = torch.empty((B, heads, D), dtype=torch.float32, device=dev)
+    a = _heads_common(B, 1, D, P, heads, w_ag.dtype)
+    a.H, a.Wo, a.Mb, a.ldw = ptr(H), ptr(w_ag), ptr(Mb), _row_stride(w_ag)
+    _abi.check(_abi.lib().pom_heads_mix(C.byref(a), _abi.stream_ptr()), "pom_heads_mix")
+    return Mb
+
+
+def heads_out_fwd(s: torch.Tensor, Mb: torch.Tensor, dtype: torch.dtype, residual: Optional[torch.Tensor] = None):
+    """y[b, t, :] = sum_h s[b, t, h] * Mb[b, h, :] (+ residual): s (B, T, heads) fp32 -> (B, T, D) of ``dtype``."""
+    dev = _require_cuda(s, Mb, residual)
+    B, T, heads = s.shape
+    D = Mb.shape[2]
+    y = torch.empty((B, T, D), dtype=dtype, device=dev)
+    a = _heads_common(B, T, D, heads, heads, dtype)  # P is not used by this call; any multiple of heads
+    a.s, a.Mb, a.y, a.residual = ptr(s), ptr(Mb), ptr(y), ptr(residual)
+    _abi.check(_abi.lib().pom_heads_out_fwd(C.byref(a), _abi.stream_ptr()), "pom_heads_out_fwd")
+    return y
+
+
+def heads_out_bwd(dy: torch.Tensor, s: torch.Tensor, Mb: torch.Tensor):
+    """Returns (ds (B, T, heads) fp32, dMb (B, heads, D) fp32)."""
+    dev = _require_cuda(dy, s, Mb)
+    B, T, heads = s.shape
+    D = Mb.shape[2]
+    ds = torch.empty((B, T, heads), dtype=torch.float32, device=dev)
+    dMb = torch.empty((B, heads, D), dtype=torch.float32, device=dev)
+    part = torch.empty((B, (T + 127) // 128, heads, D), dtype=torch.float32, device=dev)
+    a = _heads_common(B, T, D, heads, heads, dy.dtype)
+    a.dy, a.s, a.Mb, a.ds, a.dMb_partial, a.dMb = ptr(dy), ptr(s), ptr(Mb), ptr(ds), ptr(part), ptr(dMb)
+    _abi.check(_abi.lib().pom_heads_out_bwd(C.byref(a), _abi.stream_ptr()), "pom_heads_out_bwd")
+    return ds, dMb
+
+
+def heads_mix_bwd(dMb: torch.Tensor, H: torch.Tensor, w_ag: torch.Tensor, dwo_accum: torch.Tensor) -> torch.Tensor:
+    """Returns dH (B, P) fp32 and adds the output-projection gradient into ``dwo_accum`` ((D, P) fp32, contiguous)."""
+    dev = _require_cuda(dMb, H, w_ag, dwo_accum)
+    B, heads, D = dMb.shape
+    P = H.shape[1]
+    assert dwo_accum.is_contiguous() and dwo_accum.dtype == torch.float32 and dwo_accum.shape == (D, P)
+    dH = torch.empty((B, P), dtype=torch.float32, device=dev)
+    a = _heads_common(B, 1, D, P, heads, w_ag.dtype)
+    a.dMb, a.H, a.Wo, a.dH, a.dWo, a.ldw = ptr(dMb), ptr(H), ptr(w_ag), ptr(dH), ptr(dwo_accum), _row_stride(w_ag)
+    _abi.check(_abi.lib().pom_heads_mix_bwd(C.byref(a), _abi.stream_ptr()), "pom_heads_mix_bwd")
+    return dH
+
+
 def state_merge(h_past: torch.Tensor, h_cur: torch.Tensor, n_past: float) -> torch.Tensor:
     _require_cuda(h_past, h_cur)
     out = torch.empty_like(h_cur)

@@ -42,7 +42,7 @@ def test_struct_sizes_match_the_c_compiler():
                "pom_gate_args": _abi.GateArgs, "pom_gate_bwd_args": _abi.GateBwdArgs, "pom_agg_args": _abi.AggArgs,
                "pom_agg_bwd_args": _abi.AggBwdArgs, "pom_select_args": _abi.SelectArgs,
                "pom_select_bwd_args": _abi.SelectBwdArgs, "pom_select_heads_args": _abi.SelectHeadsArgs,
-               "pom_layer_args": _abi.LayerArgs, "pom_peer_comm": _abi.PeerComm, "pom_peer_xchg_args": _abi.PeerXchgArgs}
+               "pom_layer_args": _abi.LayerArgs, "pom_heads_args": _abi.HeadsArgs, "pom_peer_comm": _abi.PeerComm, "pom_peer_xchg_args": _abi.PeerXchgArgs}
     src = '#include <stdio.h>\n#include "pom_b200.h"\nint main(void){' + "".join(
         f'printf("{n} %zu\\n", sizeof({n}));' for n in structs) + "return 0;}\n"
     with tempfile.TemporaryDirectory() as d:
