@@ -85,6 +85,10 @@ typedef struct pom_rope {
  * zeroed or hold the value to accumulate onto).  split_k == 0 picks a split automatically
  * in accumulate mode.  All leading dimensions and base addresses must be multiples of
  * 8 elements / 16 bytes.
+ * Strided batches: with b_batched the B operand has one matrix per batch as well (C[b] = A[b]·Bm[b]ᵀ); the
+ * *_batch_stride fields give the element offset between consecutive batches of each tensor (0 = the matrices
+ * follow one another; multiples of 8), so heads / frames / samples that sit side by side inside a wider matrix
+ * run as one launch.  A transposed A may now have batches too.
  * Replaces: the cuBLAS calls behind nn.Linear in pom/pom.py:187,191,205,231 and their autograd.
  * ------------------------------------------------------------------------------------------ */
 typedef struct pom_gemm_args {
@@ -102,6 +106,8 @@ typedef struct pom_gemm_args {
   int32_t act;          /* 0 none, 1 exact GELU applied to alpha * sum */
   const void* residual; /* bf16 (batches*M, N) row stride ldr, added after the activation; NULL = none */
   int64_t ldr;
+  int64_t a_batch_stride, b_batch_stride, c_batch_stride; /* elements; 0 = densely packed batches */
+  int32_t b_batched;    /* 0: one B matrix for all batches; 1: one per batch */
 } pom_gemm_args;
 int pom_gemm_bf16(const pom_gemm_args* a, int* status, void* stream);
 

@@ -48,6 +48,8 @@ class GemmArgs(C.Structure):
         ("batches", C.c_int32), ("a_mn_major", C.c_int32), ("b_mn_major", C.c_int32),
         ("out_mode", C.c_int32), ("split_k", C.c_int32), ("alpha", C.c_float),
         ("act", C.c_int32), ("residual", C.c_void_p), ("ldr", C.c_int64),
+        ("a_batch_stride", C.c_int64), ("b_batch_stride", C.c_int64), ("c_batch_stride", C.c_int64),
+        ("b_batched", C.c_int32),
     ]
 
 

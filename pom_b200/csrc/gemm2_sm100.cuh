@@ -204,19 +204,21 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           uint8_t* sa = tiles + stage * kStageBytes;
           uint8_t* sb = sa + kABytes;
           const uint32_t full0 = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          const int bz = geom.b_batched ? t.b : 0;
           if (leader) mbar_expect_tx(&full_bar[stage], 2 * kStageBytes);
           if constexpr (!A_MN) {
             tma2_load_3d(sa, &tmA, full0, kb * kBK, t.row0, t.b);
           } else {
 #pragma unroll
-            for (int j = 0; j < kBM / 64; ++j) tma2_load_2d(sa + j * (kBK * 128), &tmA, full0, t.row0 + j * 64, kb * kBK);
+            for (int j = 0; j < kBM / 64; ++j)
+              tma2_load_3d(sa + j * (kBK * 128), &tmA, full0, t.row0 + j * 64, kb * kBK, t.b);
           }
           if constexpr (!B_MN) {
-            tma2_load_2d(sb, &tmB, full0, kb * kBK, bcol0);
+            tma2_load_3d(sb, &tmB, full0, kb * kBK, bcol0, bz);
           } else {
 #pragma unroll
             for (int j = 0; j < kHalfN / 64; ++j)
-              tma2_load_2d(sb + j * (kBK * 128), &tmB, full0, bcol0 + j * 64, kb * kBK);
+              tma2_load_3d(sb + j * (kBK * 128), &tmB, full0, bcol0 + j * 64, kb * kBK, bz);
           }
           if (++stage == STAGES) {
             stage = 0;

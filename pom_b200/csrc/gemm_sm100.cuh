@@ -53,6 +53,7 @@ struct GemmGeom {
   // Optional (batches * m_tiles_per_batch) fp32: a tile whose entry is 0 is not computed (no loads, no MMAs; its
   // epilogue sees t.live == false).  Used by the context phase to skip 128-token tiles that a mask empties.
   const float* tile_weight;
+  int b_batched;          // 1: the B operand has one matrix per batch (third tensor-map coordinate = batch)
 };
 
 struct TileCtx {
@@ -251,20 +252,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
           uint8_t* sa = tiles + stage * kStageBytes;
           uint8_t* sb = sa + kABytes;
+          const int bz = geom.b_batched ? t.b : 0;
           mbar_expect_tx(&full_bar[stage], kStageBytes);
           if constexpr (!A_MN) {
             tma_load_3d(sa, &tmA, &full_bar[stage], kb * kBK, t.row0, t.b);
           } else {
 #pragma unroll
             for (int j = 0; j < kBM / 64; ++j)
-              tma_load_2d(sa + j * (kBK * 128), &tmA, &full_bar[stage], t.row0 + j * 64, kb * kBK);
+              tma_load_3d(sa + j * (kBK * 128), &tmA, &full_bar[stage], t.row0 + j * 64, kb * kBK, t.b);
           }
           if constexpr (!B_MN) {
-            tma_load_2d(sb, &tmB, &full_bar[stage], kb * kBK, t.col0);
+            tma_load_3d(sb, &tmB, &full_bar[stage], kb * kBK, t.col0, bz);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(sb + j * (kBK * 128), &tmB, &full_bar[stage], t.col0 + j * 64, kb * kBK);
+              tma_load_3d(sb + j * (kBK * 128), &tmB, &full_bar[stage], t.col0 + j * 64, kb * kBK, bz);
           }
           if (++stage == STAGES) {
             stage = 0;

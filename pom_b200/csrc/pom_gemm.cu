@@ -64,10 +64,14 @@ int make_map(CUtensorMap* m, const void* base, int rank, const uint64_t* dims, c
 }
 
 // Epilogue tensor: bf16 (batches, rows, cols) with row stride ld, moved in 32 x 32 blocks (64-byte swizzle).
-int make_io_map(CUtensorMap* m, const void* base, int64_t cols, int64_t rows, int64_t batches, int64_t ld) {
+// batch_stride (elements) 0 = rows * ld.
+int make_io_map(CUtensorMap* m, const void* base, int64_t cols, int64_t rows, int64_t batches, int64_t ld,
+                int64_t batch_stride = 0) {
   if (ld % 8 || ld < cols) return POM_ERR_BAD_STRIDE;
   uint64_t dims[3] = {static_cast<uint64_t>(cols), static_cast<uint64_t>(rows), static_cast<uint64_t>(batches)};
-  uint64_t str[2] = {static_cast<uint64_t>(ld), static_cast<uint64_t>(ld) * static_cast<uint64_t>(rows)};
+  uint64_t str[2] = {static_cast<uint64_t>(ld),
+                     batch_stride ? static_cast<uint64_t>(batch_stride)
+                                  : static_cast<uint64_t>(ld) * static_cast<uint64_t>(rows)};
   uint32_t box[3] = {32, 32, 1};
   return make_map(m, base, 3, dims, str, box, CU_TENSOR_MAP_SWIZZLE_64B);
 }
@@ -80,34 +84,43 @@ struct Operands {
   int batches;
   bool a_mn, b_mn;
   const float* tile_weight = nullptr;  // optional per (batch, 128-row tile) weights: 0 skips the tile
+  // strided batches: element offsets between consecutive batches (0 = the matrices follow one another);
+  // b_batched: the B operand has one matrix per batch too
+  int64_t a_batch_stride = 0, b_batch_stride = 0;
+  bool b_batched = false;
 };
 
 // `b_rows`: rows of the B tile one CTA loads per stage (K-major B only; MN-major B uses 64-wide boxes).
 int build_maps(const Operands& o, int b_rows, CUtensorMap* tmA, CUtensorMap* tmB) {
   int rc;
+  const uint64_t nb_a = static_cast<uint64_t>(o.batches);
+  const uint64_t nb_b = o.b_batched ? static_cast<uint64_t>(o.batches) : 1;
   if (!o.a_mn) {
-    uint64_t dims[3] = {static_cast<uint64_t>(o.K), static_cast<uint64_t>(o.M), static_cast<uint64_t>(o.batches)};
-    uint64_t str[2] = {static_cast<uint64_t>(o.lda), static_cast<uint64_t>(o.lda) * static_cast<uint64_t>(o.M)};
+    uint64_t dims[3] = {static_cast<uint64_t>(o.K), static_cast<uint64_t>(o.M), nb_a};
+    uint64_t str[2] = {static_cast<uint64_t>(o.lda),
+                       static_cast<uint64_t>(o.a_batch_stride ? o.a_batch_stride : o.lda * o.M)};
     uint32_t box[3] = {static_cast<uint32_t>(kBK), static_cast<uint32_t>(kBM), 1};
     rc = make_map(tmA, o.A, 3, dims, str, box);
   } else {
-    if (o.batches != 1) return POM_ERR_UNSUPPORTED;
-    uint64_t dims[2] = {static_cast<uint64_t>(o.M), static_cast<uint64_t>(o.K)};
-    uint64_t str[1] = {static_cast<uint64_t>(o.lda)};
-    uint32_t box[2] = {64, static_cast<uint32_t>(kBK)};
-    rc = make_map(tmA, o.A, 2, dims, str, box);
+    uint64_t dims[3] = {static_cast<uint64_t>(o.M), static_cast<uint64_t>(o.K), nb_a};
+    uint64_t str[2] = {static_cast<uint64_t>(o.lda),
+                       static_cast<uint64_t>(o.a_batch_stride ? o.a_batch_stride : o.lda * o.K)};
+    uint32_t box[3] = {64, static_cast<uint32_t>(kBK), 1};
+    rc = make_map(tmA, o.A, 3, dims, str, box);
   }
   if (rc) return rc;
   if (!o.b_mn) {
-    uint64_t dims[2] = {static_cast<uint64_t>(o.K), static_cast<uint64_t>(o.N)};
-    uint64_t str[1] = {static_cast<uint64_t>(o.ldb)};
-    uint32_t box[2] = {static_cast<uint32_t>(kBK), static_cast<uint32_t>(b_rows)};
-    rc = make_map(tmB, o.Bm, 2, dims, str, box);
+    uint64_t dims[3] = {static_cast<uint64_t>(o.K), static_cast<uint64_t>(o.N), nb_b};
+    uint64_t str[2] = {static_cast<uint64_t>(o.ldb),
+                       static_cast<uint64_t>(o.b_batch_stride ? o.b_batch_stride : o.ldb * o.N)};
+    uint32_t box[3] = {static_cast<uint32_t>(kBK), static_cast<uint32_t>(b_rows), 1};
+    rc = make_map(tmB, o.Bm, 3, dims, str, box);
   } else {
-    uint64_t dims[2] = {static_cast<uint64_t>(o.N), static_cast<uint64_t>(o.K)};
-    uint64_t str[1] = {static_cast<uint64_t>(o.ldb)};
-    uint32_t box[2] = {64, static_cast<uint32_t>(kBK)};
-    rc = make_map(tmB, o.Bm, 2, dims, str, box);
+    uint64_t dims[3] = {static_cast<uint64_t>(o.N), static_cast<uint64_t>(o.K), nb_b};
+    uint64_t str[2] = {static_cast<uint64_t>(o.ldb),
+                       static_cast<uint64_t>(o.b_batch_stride ? o.b_batch_stride : o.ldb * o.K)};
+    uint32_t box[3] = {64, static_cast<uint32_t>(kBK), 1};
+    rc = make_map(tmB, o.Bm, 3, dims, str, box);
   }
   return rc;
 }
@@ -126,6 +139,7 @@ GemmGeom make_geom(const Operands& o, int bn, int split_k) {
   g.split_k = static_cast<int>(ceil_div(g.k_blocks, g.kb_per_split));
   g.group_m = 8;
   g.tile_weight = o.tile_weight;
+  g.b_batched = o.b_batched ? 1 : 0;
   return g;
 }
 
@@ -365,6 +379,12 @@ extern "C" {
 int pom_gemm_bf16(const pom_gemm_args* a, int* status, void* stream) {
   if (!a || !a->C) return POM_ERR_NULL;
   Operands o{a->A, a->Bm, a->M, a->N, a->K, a->lda, a->ldb, a->batches, a->a_mn_major != 0, a->b_mn_major != 0};
+  o.a_batch_stride = a->a_batch_stride;
+  o.b_batch_stride = a->b_batch_stride;
+  o.b_batched = a->b_batched != 0;
+  if (a->a_batch_stride % 8 || a->b_batch_stride % 8 || a->a_batch_stride < 0 || a->b_batch_stride < 0 ||
+      a->c_batch_stride < 0)
+    return POM_ERR_BAD_STRIDE;
   int rc = check_operands(o);
   if (rc) return rc;
   if (a->out_mode < 0 || a->out_mode > 2) return POM_ERR_UNSUPPORTED;
@@ -380,7 +400,9 @@ int pom_gemm_bf16(const pom_gemm_args* a, int* status, void* stream) {
   EpiStore::Params ep;
   ep.C = a->C;
   ep.ldc = a->ldc;
-  ep.batch_stride = a->M * a->ldc;
+  ep.batch_stride = a->c_batch_stride ? a->c_batch_stride : a->M * a->ldc;
+  if (a->out_mode == POM_OUT_BF16 && a->c_batch_stride % 8) return POM_ERR_BAD_STRIDE;
+  if (a->residual && a->c_batch_stride) return POM_ERR_UNSUPPORTED;
   ep.mode = a->out_mode;
   ep.alpha = a->alpha;
   ep.act = a->act;
@@ -389,7 +411,9 @@ int pom_gemm_bf16(const pom_gemm_args* a, int* status, void* stream) {
   if ((a->act || a->residual) && a->out_mode != POM_OUT_BF16) return POM_ERR_UNSUPPORTED;
   if (a->act < 0 || a->act > 1 || (a->residual && a->ldr < a->N)) return POM_ERR_UNSUPPORTED;
   EpiMaps maps{};
-  if (a->out_mode == POM_OUT_BF16 && (rc = make_io_map(&maps.out0, a->C, a->N, a->M, a->batches, a->ldc))) return rc;
+  if (a->out_mode == POM_OUT_BF16 &&
+      (rc = make_io_map(&maps.out0, a->C, a->N, a->M, a->batches, a->ldc, a->c_batch_stride)))
+    return rc;
   return run_plan_any_major<EpiStore>(plan, o, split, maps, ep, status, static_cast<cudaStream_t>(stream));
 }
 

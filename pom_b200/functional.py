@@ -258,8 +258,11 @@ class _PoMLayer(torch.autograd.Function):
             # H[b, m, :] = sum_n mask[b, m, n] * features[b, n, :] (divided by the row sum inside the selection)
             feat = ops.poly_agg_fwd(hp, coeff32, rope=spec.rope_ctx, per_token=True)
             Hc = torch.empty((B, T, P), dtype=xq.dtype, device=xq.device)
-            for b in range(B):
-                ops.gemm(maskd[b], feat[b], b_mn=True, out=Hc[b])
+            if bf16:
+                ops.gemm_batched(maskd, feat, b_mn=True, out=Hc)  # all samples in one strided-batched launch
+            else:
+                for b in range(B):
+                    ops.gemm(maskd[b], feat[b], b_mn=True, out=Hc[b])
             H = None
         else:
             scale = 1.0 if denom is not None else 1.0 / n_glob
@@ -404,8 +407,11 @@ class _PoMLayer(torch.autograd.Function):
         elif full:
             # d features[b] = mask[b]^T (N x T) · dH[b] (T x P)
             dfeat = torch.empty((B, N, P), dtype=dt, device=dev)
-            for b in range(B):
-                ops.gemm(maskd[b], dH[b], a_mn=True, b_mn=True, out=dfeat[b])
+            if dt == torch.bfloat16:
+                ops.gemm_batched(maskd, dH, a_mn=True, b_mn=True, out=dfeat)
+            else:
+                for b in range(B):
+                    ops.gemm(maskd[b], dH[b], a_mn=True, b_mn=True, out=dfeat[b])
             ops.poly_agg_bwd(hp, coeff32, dx_out=g_hp.view(B, N, P), dout=dfeat, per_token=True, rope=spec.rope_ctx,
                              dcoeff_out=d_coeff)
         else:

@@ -130,6 +130,53 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     return out
 
 
+def gemm_batched(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+                 out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+                 accumulate: bool = False, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[i] = A[i]·B[i]ᵀ on the tcgen05 kernel, one launch for all batches.
+
+    ``a`` is (batch, M, K) — or (batch, K, M) with ``a_mn`` —, ``b`` is (batch, N, K) — or (batch, K, N) with ``b_mn`` —
+    or 2-D (shared by all batches); bf16, last dimension contiguous, any row and batch strides that are multiples of
+    8 elements, so heads or samples that sit side by side inside a wider matrix can be passed as strided views.
+    ``out`` (batch, M, N) may be such a view too (bf16, fp32, or fp32 accumulate)."""
+    dev = _require_cuda(a, b, out, residual)
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        raise TypeError("gemm_batched needs bfloat16 operands")
+    nb = a.shape[0]
+    M, K = (a.shape[2], a.shape[1]) if a_mn else (a.shape[1], a.shape[2])
+    bb = b.dim() == 3
+    bs = b.shape[1:] if bb else b.shape
+    N, Kb = (bs[1], bs[0]) if b_mn else (bs[0], bs[1])
+    if K != Kb or (bb and b.shape[0] != nb):
+        raise ValueError("operand shapes do not match")
+    if a.stride(2) != 1 or b.stride(-1) != 1:
+        raise ValueError("last dimensions must be contiguous")
+    if out is None:
+        if accumulate:
+            raise ValueError("accumulate needs an output tensor")
+        out = torch.empty((nb, M, N), dtype=out_dtype or torch.bfloat16, device=dev)
+    if out.shape != (nb, M, N) or out.stride(2) != 1:
+        raise ValueError("output shape mismatch")
+    g = GemmArgs()
+    g.A, g.Bm, g.C = ptr(a), ptr(b), ptr(out)
+    g.M, g.N, g.K = M, N, K
+    g.lda, g.ldb, g.ldc = a.stride(1), b.stride(-2), out.stride(1)
+    g.batches = nb
+    g.a_batch_stride, g.c_batch_stride = a.stride(0), out.stride(0)
+    g.b_batched, g.b_batch_stride = int(bb), (b.stride(0) if bb else 0)
+    g.a_mn_major, g.b_mn_major = int(a_mn), int(b_mn)
+    g.out_mode = _abi.OUT_F32_ACCUM if accumulate else (_abi.OUT_BF16 if out.dtype == torch.bfloat16 else _abi.OUT_F32)
+    g.split_k, g.alpha = 1, 1.0
+    if residual is not None:
+        if residual.shape != out.shape or residual.dtype != torch.bfloat16 or not residual.is_contiguous() \
+                or not out.is_contiguous():
+            raise ValueError("residual must be a contiguous bfloat16 tensor of the (contiguous) output's shape")
+        g.residual, g.ldr = ptr(residual), residual.stride(1)
+        g.c_batch_stride = 0
+    _abi.check(_abi.lib().pom_gemm_bf16(C.byref(g), ptr(_abi.status_word(dev)), _abi.stream_ptr()), "pom_gemm_bf16")
+    return out
+
+
 def reduce_partials(partial: torch.Tensor, *, denom: Optional[torch.Tensor] = None, scale: float = 1.0,
                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """(B, chunks, P) fp32 -> (B, P): scale * (sum over chunks, in a fixed order) / denom[b]."""
@@ -453,6 +500,12 @@ def heads_mix(H: torch.Tensor, w_ag: torch.Tensor, heads: int) -> torch.Tensor:
     dev = _require_cuda(H, w_ag)
     B, P = H.shape
     D = w_ag.shape[0]
+    if w_ag.dtype == torch.bfloat16:  # one strided-batched tensor-core launch over the heads; Mb in bf16
+        hd = P // heads
+        Mb = torch.empty((B, heads, D), dtype=torch.bfloat16, device=dev)
+        gemm_batched(to_bf16(H).view(B, heads, hd).transpose(0, 1), w_ag.view(D, heads, hd).transpose(0, 1),
+                     out=Mb.transpose(0, 1))
+        return Mb
     Mb = torch.empty((B, heads, D), dtype=torch.float32, device=dev)
     a = _heads_common(B, 1, D, P, heads, w_ag.dtype)
     a.H, a.Wo, a.Mb, a.ldw = ptr(H), ptr(w_ag), ptr(Mb), _row_stride(w_ag)
@@ -465,6 +518,8 @@ def heads_out_fwd(s: torch.Tensor, Mb: torch.Tensor, dtype: torch.dtype, residua
     dev = _require_cuda(s, Mb, residual)
     B, T, heads = s.shape
     D = Mb.shape[2]
+    if dtype == torch.bfloat16:  # per sample: (T x heads) · (heads x D), the inner dimension zero-padded by TMA
+        return gemm_batched(to_bf16(s), Mb, b_mn=True, residual=residual)
     y = torch.empty((B, T, D), dtype=dtype, device=dev)
     a = _heads_common(B, T, D, heads, heads, dtype)  # P is not used by this call; any multiple of heads
     a.s, a.Mb, a.y, a.residual = ptr(s), ptr(Mb), ptr(y), ptr(residual)
@@ -477,6 +532,10 @@ def heads_out_bwd(dy: torch.Tensor, s: torch.Tensor, Mb: torch.Tensor):
     dev = _require_cuda(dy, s, Mb)
     B, T, heads = s.shape
     D = Mb.shape[2]
+    if dy.dtype == torch.bfloat16:
+        ds = gemm_batched(dy, Mb, out_dtype=torch.float32)                              # (B, T, heads)
+        dMb = gemm_batched(to_bf16(s), dy, a_mn=True, b_mn=True, out_dtype=torch.float32)  # (B, heads, D)
+        return ds, dMb
     ds = torch.empty((B, T, heads), dtype=torch.float32, device=dev)
     dMb = torch.empty((B, heads, D), dtype=torch.float32, device=dev)
     part = torch.empty((B, (T + 127) // 128, heads, D), dtype=torch.float32, device=dev)
@@ -493,6 +552,14 @@ def heads_mix_bwd(dMb: torch.Tensor, H: torch.Tensor, w_ag: torch.Tensor, dwo_ac
     P = H.shape[1]
     assert dwo_accum.is_contiguous() and dwo_accum.dtype == torch.float32 and dwo_accum.shape == (D, P)
     dH = torch.empty((B, P), dtype=torch.float32, device=dev)
+    if w_ag.dtype == torch.bfloat16:
+        hd = P // heads
+        g16 = to_bf16(dMb).transpose(0, 1)                       # (heads, B, D) view
+        w3 = w_ag.view(D, heads, hd).transpose(0, 1)             # (heads, D, hd) view
+        gemm_batched(g16, w3, b_mn=True, out=dH.view(B, heads, hd).transpose(0, 1))
+        gemm_batched(g16, to_bf16(H).view(B, heads, hd).transpose(0, 1), a_mn=True, b_mn=True,
+                     out=dwo_accum.view(D, heads, hd).transpose(0, 1), accumulate=True)
+        return dH
     a = _heads_common(B, 1, D, P, heads, w_ag.dtype)
     a.dMb, a.H, a.Wo, a.dH, a.dWo, a.ldw = ptr(dMb), ptr(H), ptr(w_ag), ptr(dH), ptr(dwo_accum), _row_stride(w_ag)
     _abi.check(_abi.lib().pom_heads_mix_bwd(C.byref(a), _abi.stream_ptr()), "pom_heads_mix_bwd")

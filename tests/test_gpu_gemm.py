@@ -86,3 +86,49 @@ def test_bf16_gemm_gelu_and_residual_epilogue():
     assert _rel(got, acc + R.float()) < 4e-3
     got = ops.gemm(A, B, act="gelu", residual=R)
     assert _rel(got, torch.nn.functional.gelu(acc) + R.float()) < 4e-3
+
+
+@pytest.mark.parametrize("a_mn", [False, True])
+@pytest.mark.parametrize("b_mn", [False, True])
+@pytest.mark.parametrize("nb,M,N,K", [(3, 200, 136, 96), (4, 16, 264, 304), (2, 304, 16, 16), (5, 128, 128, 32)])
+def test_bf16_gemm_strided_batches(nb, M, N, K, a_mn, b_mn):
+    """One launch for all batches, each with its own A and B (any operand order), against per-batch fp32 products;
+    includes inner and outer dimensions far below a tile (zero-filled by TMA)."""
+    from pom_b200 import _abi, ops
+
+    torch.manual_seed(2)
+    A = torch.randn(nb, M, K, device="cuda").bfloat16()
+    B = torch.randn(nb, N, K, device="cuda").bfloat16()
+    ref = torch.matmul(A.float(), B.float().transpose(1, 2))
+    a = A.transpose(1, 2).contiguous() if a_mn else A
+    b = B.transpose(1, 2).contiguous() if b_mn else B
+    out = ops.gemm_batched(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+    assert _abi.read_status("cuda") == 0
+    assert _rel(out, ref) < 1e-5
+    out16 = ops.gemm_batched(a, b, a_mn=a_mn, b_mn=b_mn)
+    assert _rel(out16, ref) < 4e-3
+    shared = ops.gemm_batched(a, b[0], a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)  # one B for all batches
+    assert _rel(shared, torch.matmul(A.float(), B[0].float().t())) < 1e-5
+
+
+def test_bf16_gemm_batches_as_column_blocks_of_wider_matrices():
+    """Heads that sit side by side inside (rows, heads * hd) matrices, passed as strided views: per-head products
+    written into / accumulated onto column blocks of a wider output."""
+    from pom_b200 import ops
+
+    torch.manual_seed(3)
+    rows, heads, hd, D = 24, 4, 40, 72
+    H = torch.randn(rows, heads * hd, device="cuda").bfloat16()
+    W = torch.randn(D, heads * hd, device="cuda").bfloat16()
+    Mb = torch.empty(rows, heads, D, device="cuda", dtype=torch.bfloat16)
+    ops.gemm_batched(H.view(rows, heads, hd).transpose(0, 1), W.view(D, heads, hd).transpose(0, 1),
+                     out=Mb.transpose(0, 1))
+    ref = torch.einsum("bhj,dhj->bhd", H.float().view(rows, heads, hd), W.float().view(D, heads, hd))
+    assert _rel(Mb, ref) < 4e-3
+    # accumulate onto column blocks: acc[d, h*hd + j] += sum_b G[b, h, d] * H[b, h*hd + j]
+    G = torch.randn(rows, heads, D, device="cuda").bfloat16()
+    acc = torch.ones(D, heads * hd, device="cuda")
+    ops.gemm_batched(G.transpose(0, 1), H.view(rows, heads, hd).transpose(0, 1), a_mn=True, b_mn=True,
+                     out=acc.view(D, heads, hd).transpose(0, 1), accumulate=True)
+    ref2 = 1.0 + torch.einsum("bhd,bhj->dhj", G.float(), H.float().view(rows, heads, hd)).reshape(D, heads * hd)
+    assert _rel(acc, ref2) < 1e-5
