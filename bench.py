@@ -122,6 +122,10 @@ def flops_per_step(w, valid_frac=1.0):
     P = w["expand"] * D
     if "layers" in w:  # forward only: projections 6 M D P plus the 4 D feed-forward 16 M D^2, per layer
         return w["layers"] * M * (6.0 * D * P + 16.0 * D * D)
+    if w.get("heads", 1) > 1:
+        # one gate value per head and one aggregate per sample: the query side is (heads x D)-sized, what remains
+        # is the (P + heads)-wide input projection forward (2) and its two backward products (2 + 2)
+        return 6.0 * M * D * (P + w["heads"])
     return 18.0 * M * D * P
 
 
