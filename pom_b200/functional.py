@@ -625,14 +625,46 @@ class _GateMul(torch.autograd.Function):
         return ds, dh
 
 
+class _GateMulHeads(torch.autograd.Function):
+    """s (B, T, heads) broadcast over the channels of each head, times h (per sample or per token)."""
+
+    @staticmethod
+    def forward(ctx, s, h):
+        if not s.is_cuda:
+            raise RuntimeError("pom_b200 has no CPU path: pass CUDA tensors")
+        b, g, p = h.shape
+        per_tok = g != 1
+        s32 = _f32(s.contiguous())
+        hk = h.contiguous() if per_tok else _f32(h.reshape(b, p).contiguous())
+        ctx.save_for_backward(s32, hk)
+        ctx.meta = (per_tok, s.dtype, h.dtype, h.shape)
+        return ops.select_heads_fwd(s32, hk, h.dtype)
+
+    @staticmethod
+    def backward(ctx, g):
+        s32, hk = ctx.saved_tensors
+        per_tok, sdt, hdt, hshape = ctx.meta
+        ds32 = ops.zeros_f32(s32.numel(), s32.device).view(s32.shape)
+        dh = ops.select_heads_bwd(g.contiguous(), s32, hk, ds32)
+        if not per_tok:
+            dh = dh.view(hshape)
+            if hdt != torch.float32:
+                dh = ops.to_bf16(dh)
+        return (ds32 if sdt == torch.float32 else ops.to_bf16(ds32)), dh
+
+
 def polynomial_selection_(s: torch.Tensor, h: torch.Tensor, n_sel_heads: int) -> torch.Tensor:
-    """Gated selection s ⊙ h (reference pom/pom.py:103-122): s (B, T, P) already activated,
-    h (B, G, P) with G == 1 or G == T.  Multi-head scalar gating is not implemented on this path."""
+    """Gated selection s ⊙ h (reference pom/pom.py:103-122): s already activated, (B, T, P) — or
+    (B, T, n_sel_heads) with one gate value per head —, h (B, G, P) with G == 1 or G == T."""
     b, g, dh = h.shape
     t = s.shape[1]
     assert g == 1 or t == 1 or g == t, f"incompatible shapes: g={g} t={t}"
     if n_sel_heads > 1:
-        raise NotImplementedError("n_sel_heads > 1 is not implemented by the CUDA path yet")
+        if s.shape[2] != n_sel_heads or dh % n_sel_heads:
+            raise ValueError(f"expected a (B, T, {n_sel_heads}) gate and dim divisible by n_sel_heads")
+        if t == 1 and g != 1:
+            s = s.expand(b, g, n_sel_heads)
+        return _GateMulHeads.apply(s, h)
     if t == 1 and g != 1:
         s = s.expand(b, g, dh)
     return _GateMul.apply(s, h)

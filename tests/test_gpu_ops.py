@@ -159,3 +159,25 @@ def test_selection_operator(per_token):
     _close(got, want, tol, "forward")
     _close(gds, wds, tol, "grad_s")
     _close(gdh, wdh, tol, "grad_h")
+
+
+@pytest.mark.parametrize("per_token", [False, True])
+def test_selection_operator_with_one_gate_value_per_head(per_token):
+    """polynomial_selection_ with n_sel_heads > 1 (reference pom/pom.py:119-122): s is (B, T, heads)."""
+    from pom_b200 import polynomial_selection_
+
+    torch.manual_seed(3)
+    heads = 4
+    s = torch.rand(2, 20, heads)
+    h = torch.randn(2, 20 if per_token else 1, 48)
+    sr, hr = s.clone().requires_grad_(True), h.clone().requires_grad_(True)
+    want = O.selection(sr, hr, heads)
+    g = torch.randn_like(want)
+    wds, wdh = torch.autograd.grad(want, [sr, hr], g)
+    sg, hg = s.cuda().requires_grad_(True), h.cuda().requires_grad_(True)
+    got = polynomial_selection_(sg, hg, heads)
+    gds, gdh = torch.autograd.grad(got, [sg, hg], g.cuda())
+    tol = TOLS[torch.float32]
+    _close(got, want, tol, "forward")
+    _close(gds, wds, tol, "grad_s")
+    _close(gdh, wdh, tol, "grad_h")
