@@ -1,8 +1,8 @@
 #!/usr/bin/env python
 """Benchmark of the PoM layer hot path (forward + backward) on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload dit|masked|seq64k|seq64k_causal]
-    python bench.py --impl reference ...        # CPU restatement of the reference path, same metric
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload dit|dit4k|masked|seq64k|seq64k_causal|...]
+    python bench.py --impl reference ...        # CPU restatement of the reference path, same metric and config
 
 One "step" is one forward + backward pass of one PoM layer over one batch of seeded synthetic
 input, with gradients for the input and all four parameters.  Rank 0 prints one JSON line.
@@ -11,6 +11,7 @@ Workloads
   dit            B=32, N=1024 (32x32 patches), D=1152, degree 2, expand 2, bf16, no mask.  With
                  --gpus N every rank runs its own batch of 32 samples (weak scaling, no collective
                  on the data path: samples are independent).
+  dit4k          the same token count as 8 samples of 4096 tokens (the headline sequence length).
   dit_heads16    dit with n_sel_heads=16 (one gate value per head, as the reference's own benchmarks instantiate the
                  layer): the query side collapses to (heads x D) matrices per sample, see csrc/pom_heads.cu.
   masked         B=64, N=2048, D=1024, degree 3, expand 2, key-padding mask (lengths U[256, 2048]).
@@ -23,6 +24,10 @@ Workloads
                  frames through all layers, replayed as one CUDA graph (metric: tokens/s through the stack).
   video_block    the same stack and result, all 16 frames in one pass: every mixer runs with
                  BlockCausal(256) (per-frame means + running mean over frames), so each GEMM sees 32768 rows.
+
+The default run (workload dit) adds two records to its line: `headline_n4096` (the dit4k shape timed the same
+way) and `token_shard` (seq64k and seq64k_causal: the 65536-token sequence sharded by token over the N ranks,
+beside the same problem on one GPU timed in the same process; skip with --no-token-shard).
 """
 import argparse
 import json
@@ -40,6 +45,7 @@ sys.path.insert(0, ROOT)
 
 WORKLOADS = {
     "dit": dict(B=32, N=1024, D=1152, degree=2, expand=2, mask="none", rope=None, shard="batch"),
+    "dit4k": dict(B=8, N=4096, D=1152, degree=2, expand=2, mask="none", rope=None, shard="batch"),
     "dit_heads16": dict(B=32, N=1024, D=1152, degree=2, expand=2, mask="none", rope=None, shard="batch", heads=16),
     "masked": dict(B=64, N=2048, D=1024, degree=3, expand=2, mask="keypad", rope=None, shard="batch"),
     "seq64k": dict(B=1, N=65536, D=1152, degree=2, expand=2, mask="none", rope="2d", shard="token"),
@@ -51,12 +57,12 @@ WORKLOADS = {
 }
 METRIC = "pom_layer_fwd_bwd_tokens_per_s"
 UNIT = "tokens/s"
+N_INPUT_SETS = 3
 
-# DRAM bytes (read + write) per launch, from the ncu captures summarised under profiles/
-# (dram__bytes_read.sum + dram__bytes_write.sum of one launch); None where no capture exists.
+# DRAM bytes (read + write) of one launch from an ncu capture of the kernel as shipped (dram__bytes_read.sum +
+# dram__bytes_write.sum); launches without a capture report null beside their algorithmic bytes.
 NCU_TRAFFIC_BYTES = {
-    "gemm[32768x1152x4608 B^T]": 399.2e6,   # profiles/gemm_pair_store_dx_32768x1152x4608.md (algorithmic 388.6e6)
-    "ctx_gemm": 189.3e6,                    # profiles/ctx_gemm_dit.md (algorithmic 231.8e6, part still in L2)
+    "gemm[32768x1152x4608 B^T]": 399.2e6,
 }
 
 
@@ -69,8 +75,16 @@ def measured_peaks():
     return dict(hbm=6650.0, burst=1590.0, sustained=1400.0, source="fallback")
 
 
+def workload_config(name, w, world):
+    """The `config` object of the JSON line: the same for the B200 arm and the CPU reference arm."""
+    return {"workload": name, "B_per_rank": w["B"], "N": w["N"], "D": w["D"], "degree": w["degree"],
+            "expand": w["expand"], "mask": w["mask"], "rope": w["rope"], "sharding": w["shard"],
+            "parallelism": f"{w['shard']}-shard x{world}",
+            "l2": f"{N_INPUT_SETS} rotating input sets; inputs plus per-step intermediates (~1 GB) exceed the 126 MB L2"}
+
+
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed regions run."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
@@ -99,7 +113,7 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        sm, mx, pw, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for r in self.rows:
             if len(r) < 7:
@@ -107,16 +121,43 @@ class ClockSampler:
             try:
                 sm.append(float(r[0]))
                 mx.append(float(r[1]))
+                pw.append(float(r[2]))
             except ValueError:
                 continue
             for n, v in zip(names, r[3:7]):
                 if v.lower().startswith("active"):
                     reasons.add(n)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+        # "under load": samples drawing clearly more than the idle power of the board
+        busy = [s for s, p in zip(sm, pw) if p > 350.0]
+        return {"sm_mhz": statistics.median(busy or sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm), "samples_under_load": len(busy),
+                "power_w_max": max(pw) if pw else None}
 
 
-def flops_per_step(w, valid_frac=1.0):
+def bind_to_gpu_numa_node(local_rank):
+    """Pins this process to the CPUs of the NUMA node its GPU hangs off, before any pinned host buffer is
+    allocated: first touch then places the staging pages on that node and the copy threads run beside them.
+    Returns a short description (None when the topology cannot be read; nothing is changed then)."""
+    try:
+        p = torch.cuda.get_device_properties(local_rank)
+        bus = f"{p.pci_domain_id:04x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0"
+        node = int(open(f"/sys/bus/pci/devices/{bus}/numa_node").read().strip())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return f"numa node {node}, {len(allowed)} cpus"
+    except Exception:
+        return None
+
+
+def flops_per_step(w):
     """Algorithmic tensor work of one fwd+bwd step: 18 * M * D * P (projections 4+2 forward, 12 backward)."""
     M, D = w["B"] * w["N"], w["D"]
     P = w["expand"] * D
@@ -130,21 +171,21 @@ def flops_per_step(w, valid_frac=1.0):
 
 
 # ------------------------------------------------------------------------------------------- reference arm
-def cpu_reference_tokens_per_s(w, steps, warmup, sample_tokens=4096):
-    """Times the CPU restatement of the reference path (oracle/pom_oracle.py, fp32, all host threads) on a
-    bounded sample of the workload: the same layer and distributions with the batch (or, for one long
-    sequence, the token count) cut down so that a step takes about a second."""
+def cpu_reference_tokens_per_s(w, steps, warmup, max_tokens=65536):
+    """Times the CPU restatement of the reference path (oracle/pom_oracle.py, fp32, all host threads) on the
+    workload's own shape when it has at most `max_tokens` tokens per step, else on a sample of it with the batch cut
+    down to that many tokens.  Inputs rotate over N_INPUT_SETS sets like the B200 arm's."""
     from oracle import pom_oracle as O
 
     torch.set_num_threads(os.cpu_count() or 1)
     D, K, E = w["D"], w["degree"], w["expand"]
     if "layers" in w:
         return cpu_reference_video(w, steps, warmup, O)
-    if w["B"] > 1:
-        N = w["N"]
-        B = max(1, sample_tokens // N)
-    else:
-        B, N = 1, sample_tokens
+    B, N = w["B"], w["N"]
+    full = B * N <= max_tokens
+    if not full:
+        B = max(1, max_tokens // N)
+        N = min(N, max_tokens)
     heads = w.get("heads", 1)
     params = {k: v.requires_grad_(True) for k, v in O.init_params(D, K, E, heads, seed=0).items()}
     rope = None
@@ -156,27 +197,29 @@ def cpu_reference_tokens_per_s(w, steps, warmup, sample_tokens=4096):
         kw["positions_hw"] = torch.stack([torch.arange(N) // side, torch.arange(N) % side], 1)
     model = O.OraclePoM(params, K, E, heads, rope)
     g = torch.Generator().manual_seed(0)
-    x = torch.randn(B, N, D, generator=g).requires_grad_(True)
-    gy = torch.randn(B, N, D, generator=g)
+    sets = [(torch.randn(B, N, D, generator=g).requires_grad_(True), torch.randn(B, N, D, generator=g))
+            for _ in range(N_INPUT_SETS)]
     if w["mask"] == "keypad":
         L = torch.randint(256, N + 1, (B,), generator=g)
         kw["mask"] = (torch.arange(N).view(1, N) < L.view(B, 1)).float()
     elif w["mask"] == "causal":
         kw["mask"] = "causal"
 
-    def step():
+    def step(i):
+        x, gy = sets[i % N_INPUT_SETS]
         y = model.forward(x, **kw)
         torch.autograd.grad(y, [x] + model.parameters(), gy)
 
-    for _ in range(warmup):
-        step()
+    for i in range(warmup):
+        step(i)
     times = []
-    for _ in range(steps):
+    for i in range(steps):
         t0 = time.perf_counter()
-        step()
+        step(i)
         times.append(time.perf_counter() - t0)
     sec = statistics.median(times)
-    return (B * N) / sec, sec, f"B={B}, N={N} of the workload (fp32, {torch.get_num_threads()} threads), median of {steps}"
+    what = "the full workload shape" if full else "a sample of the workload"
+    return (B * N) / sec, sec, f"{what}: B={B}, N={N} (fp32, {torch.get_num_threads()} threads), median of {steps} steps"
 
 
 def cpu_reference_video(w, steps, warmup, O):
@@ -215,16 +258,26 @@ def cpu_reference_video(w, steps, warmup, O):
                                f"(fp32, {torch.get_num_threads()} threads), median of {steps}")
 
 
-def run_reference(args, w, rank):
+def run_reference(args, w, rank, world):
+    """CPU arm: rank 0 alone runs the oracle port with all host threads, on the B200 arm's config."""
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 5))
-    val, sec, sample = cpu_reference_tokens_per_s(w, steps, min(args.warmup, 1))
+    steps, warmup = max(1, args.steps), max(0, args.warmup)
+    # keep the whole run within a few minutes whatever --steps says: probe one step, then cap
+    t0 = time.perf_counter()
+    cpu_reference_tokens_per_s(w, 1, 0)
+    probe = time.perf_counter() - t0
+    budget = 150.0
+    if (steps + warmup) * probe > budget:
+        warmup = min(warmup, 1)
+        steps = max(1, min(steps, int(budget / probe) - warmup))
+    val, sec, sample = cpu_reference_tokens_per_s(w, steps, warmup)
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
-        "warmup": min(args.warmup, 1), "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+        "warmup": warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "scaling": "strong" if w["shard"] == "token" else "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, **{k: w[k] for k in ("B", "N", "D", "degree", "expand", "mask")}},
+        "config": workload_config(args.workload, w, world),
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -233,8 +286,8 @@ def run_reference(args, w, rank):
 
 
 # ------------------------------------------------------------------------------------------- B200 arm
-def build_case(w, rank, world, device, exchange="nccl"):
-    """Module, rotating input sets and call kwargs for this rank."""
+def build_case(w, rank, world, device, exchange="nccl", peer=None):
+    """Module, rotating pinned input sets and call kwargs for this rank."""
     from pom_b200 import PoM, PoMRoPE, SeqShard
 
     D, K, E = w["D"], w["degree"], w["expand"]
@@ -247,7 +300,7 @@ def build_case(w, rank, world, device, exchange="nccl"):
             p.data = p.data.to(torch.bfloat16)
         gen = torch.Generator().manual_seed(1000 + rank)
         host_sets = [(torch.randn(w["B"], w["N"], D, generator=gen).to(torch.bfloat16).pin_memory(), None)
-                     for _ in range(3)]
+                     for _ in range(N_INPUT_SETS)]
         return mod, host_sets, {}, w["B"] * w["N"]
     if w["rope"] == "2d":
         side = int(w["N"] ** 0.5)
@@ -266,22 +319,7 @@ def build_case(w, rank, world, device, exchange="nccl"):
             idx = torch.arange(off, off + n_loc)
             kw["positions_hw"] = torch.stack([idx // side, idx % side], 1).to(device)
         if world > 1:
-            peer = None
-            if exchange == "peer":
-                from pom_b200.peer import PeerExchange
-
-                # collective: either every rank maps its peers or (agreed through a reduction) none uses them
-                try:
-                    peer = PeerExchange(slot_floats=max(4096, B * D * E),
-                                        flat_floats=sum(p.numel() for p in mod.parameters()) + 4)
-                    ok = torch.ones(1, device=device)
-                except Exception as e:  # e.g. CUDA IPC not permitted between these processes
-                    print(f"[bench] peer exchange unavailable on rank {rank}: {e}; using NCCL", file=sys.stderr)
-                    ok = torch.zeros(1, device=device)
-                torch.distributed.all_reduce(ok, op=torch.distributed.ReduceOp.MIN)
-                if float(ok.item()) == 0.0:
-                    peer = None
-            kw["shard"] = SeqShard(token_offset=off, n_global=N, peer=peer)
+            kw["shard"] = SeqShard(token_offset=off, n_global=N, peer=peer if exchange == "peer" else None)
         tokens_local = B * n_loc
     else:
         n_loc = N
@@ -289,9 +327,8 @@ def build_case(w, rank, world, device, exchange="nccl"):
     if w["mask"] == "causal":
         kw["mask"] = "causal"
     gen = torch.Generator().manual_seed(1000 + rank)
-    n_sets = 3
     host_sets = []
-    for _ in range(n_sets):
+    for _ in range(N_INPUT_SETS):
         x = torch.randn(B, n_loc, D, generator=gen).to(torch.bfloat16).pin_memory()
         gy = torch.randn(B, n_loc, D, generator=gen).to(torch.bfloat16).pin_memory()
         host_sets.append((x, gy))
@@ -301,14 +338,123 @@ def build_case(w, rank, world, device, exchange="nccl"):
     return mod, host_sets, kw, tokens_local
 
 
+def make_peer(w, world, device, rank):
+    """Peer-memory exchange buffers for the token-sharded workloads (collective); None when the ranks cannot map
+    each other's memory, in which case every rank falls back to NCCL together."""
+    import torch.distributed as dist
+    from pom_b200.peer import PeerExchange
+
+    P = w["D"] * w["expand"]
+    n_params = 2 * P * w["D"] + w["D"] * P + P + P * w["degree"]
+    peer = None
+    try:
+        peer = PeerExchange(slot_floats=max(4096, w["B"] * P), flat_floats=n_params + 4)
+        ok = torch.ones(1, device=device)
+    except Exception as e:  # e.g. CUDA IPC not permitted between these processes
+        print(f"[bench] peer exchange unavailable on rank {rank}: {e}; using NCCL", file=sys.stderr)
+        ok = torch.zeros(1, device=device)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    return peer if float(ok.item()) != 0.0 else None
+
+
+class Case:
+    """One workload on this rank: module, device-resident input sets and a step function, optionally replayed
+    from CUDA graphs (one per input set)."""
+
+    def __init__(self, name, w, rank, world, device, exchange="nccl", peer=None, graph=False):
+        from pom_b200 import ops
+
+        self.name, self.w, self.world, self.device = name, w, world, device
+        self.mod, self.host_sets, self.kw, self.tokens_local = build_case(w, rank, world, device, exchange, peer)
+        self.params = list(self.mod.parameters())
+        self.video = "layers" in w
+        self.peer_on = "shard" in self.kw and self.kw["shard"].peer is not None
+        if self.video:
+            L = w["frame"]
+            self.single = bool(w.get("single_pass"))
+            self.split = lambda x: [x] if self.single else [x[:, f * L:(f + 1) * L].contiguous()
+                                                           for f in range(w["N"] // L)]
+            self.dev_sets = [(self.split(x.to(device)), None) for x, _ in self.host_sets]
+        else:
+            self.dev_sets = [(x.to(device), gy.to(device)) for x, gy in self.host_sets]
+        self.graphs = []
+        self.use_graph = graph
+        self.ops = ops
+        self.launches_per_step = 0
+
+    def step(self, x, gy):
+        if self.video:
+            if self.single:
+                y = self.mod.forward_single_pass(x[0], self.w["frame"])
+                return y, [y]
+            states, outs = None, []
+            for f in x:
+                y, states = self.mod.frame_forward(f, states)
+                outs.append(y)
+            return outs[-1], outs
+        xr = x.requires_grad_(True)
+        y = self.mod(xr, **self.kw)
+        grads = torch.autograd.grad(y, [xr] + self.params, gy)
+        return y, grads
+
+    def prepare(self, warmup, sync_all):
+        for i in range(warmup):
+            self.step(*self.dev_sets[i % len(self.dev_sets)])
+        sync_all()
+        l0 = self.ops.launch_count()
+        self.step(*self.dev_sets[0])
+        self.launches_per_step = self.ops.launch_count() - l0
+        if self.use_graph:
+            sync_all()
+            for xs_d, gy_d in self.dev_sets:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    keep = self.step(xs_d, gy_d)
+                self.graphs.append((g, keep))
+            for g, _ in self.graphs:
+                g.replay()
+        sync_all()
+
+    def run(self, i):
+        if self.use_graph:
+            self.graphs[i % len(self.graphs)][0].replay()
+        else:
+            self.step(*self.dev_sets[i % len(self.dev_sets)])
+
+    def timed(self, steps, reps, sync_all, reduce_max):
+        """`reps` repetitions of exactly `steps` steps, each bracketed by barrier + synchronize and timed with CUDA
+        events on the launching stream; every repetition is the max over ranks.  Returns ms per step per repetition."""
+        out = []
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(reps):
+            sync_all()
+            e0.record()
+            for i in range(steps):
+                self.run(i)
+            e1.record()
+            sync_all()
+            out.append(reduce_max(e0.elapsed_time(e1)) / steps)
+        return out
+
+    def release(self):
+        self.graphs = []
+        self.dev_sets = []
+        self.host_sets = []
+        self.mod = None
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--reps", type=int, default=10,
+                    help="repetitions of the timed region of --steps steps; ms_per_step is their median")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="dit", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-token-shard", action="store_true",
+                    help="default workload: skip the token-sharded 64 k-token records")
     ap.add_argument("--graph", default="off", choices=["on", "off"],
                     help="replay the whole fwd+bwd step as a CUDA graph instead of launching it from Python")
     ap.add_argument("--defer-weight-grad-reduce", action="store_true",
@@ -330,16 +476,18 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
     if args.impl == "reference":
-        run_reference(args, w, rank)
+        run_reference(args, w, rank, world)
         return
 
     if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
         os.environ["NCCL_DEBUG"] = "WARN"  # keep stdout to the one JSON line
     import torch.distributed as dist
-    from pom_b200 import _abi, ops
+    from pom_b200 import _abi
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the B200 arm has no CPU path (use --impl reference for the CPU arm)")
+    all_cpus = os.sched_getaffinity(0)
+    numa = bind_to_gpu_numa_node(local_rank)
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if _abi.lib().pom_device_check() != 0:
@@ -362,105 +510,117 @@ def main():
             os.dup2(saved_fd, 1)
             os.close(saved_fd)
     args.warmup = max(args.warmup, 3)
-
-    mod, host_sets, kw, tokens_local = build_case(w, rank, world, device, args.exchange)
-    peer_on = "shard" in kw and kw["shard"].peer is not None
-    if peer_on and "--graph" not in sys.argv:
-        args.graph = "on"
-    if args.defer_weight_grad_reduce and "shard" in kw:
-        kw["shard"].reduce_weight_grads = False
-    if args.no_overlap_grad_reduce and "shard" in kw:
-        kw["shard"].overlap_grad_reduce = False
-    params = list(mod.parameters())
-    video = "layers" in w
-    if video:
-        L = w["frame"]
-        single = bool(w.get("single_pass"))
-        split = lambda x: [x] if single else [x[:, f * L:(f + 1) * L].contiguous() for f in range(w["N"] // L)]
-        dev_sets = [(split(x.to(device)), None) for x, _ in host_sets]
-        if args.graph == "off" and "--graph" not in sys.argv:
-            args.graph = "on"  # the frame loop is launch-bound from Python; the graph is the product path here
-
-        def step(frames, _):
-            if single:
-                y = mod.forward_single_pass(frames[0], L)
-                return y, [y]
-            states, outs = None, []
-            for f in frames:
-                y, states = mod.frame_forward(f, states)
-                outs.append(y)
-            return outs[-1], outs
-    else:
-        dev_sets = [(x.to(device), gy.to(device)) for x, gy in host_sets]
-
-        def step(x, gy):
-            xr = x.requires_grad_(True)
-            y = mod(xr, **kw)
-            grads = torch.autograd.grad(y, [xr] + params, gy)
-            return y, grads
+    args.reps = max(args.reps, 1)
 
     def sync_all():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- device-resident timing
-    for i in range(args.warmup):
-        step(*dev_sets[i % len(dev_sets)])
-    sync_all()
-    l0 = ops.launch_count()
-    step(*dev_sets[0])
-    launches_per_step = ops.launch_count() - l0
-    use_graph = args.graph == "on"
-    graphs = []
-    if use_graph:
-        # one graph per input set; kernels, memsets and NCCL collectives of a whole fwd+bwd step are captured
-        sync_all()
-        for xs_d, gy_d in dev_sets:
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                keep = step(xs_d, gy_d)
-            graphs.append((g, keep))
-        for g, _ in graphs:
-            g.replay()
-        sync_all()
-
-    def run_step(i):
-        if use_graph:
-            graphs[i % len(graphs)][0].replay()
-        else:
-            step(*dev_sets[i % len(dev_sets)])
+    def reduce_max(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
-        sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sync_all()
-    e0.record()
-    for i in range(args.steps):
-        run_step(i)
-    e1.record()
-    sync_all()
-    launches = launches_per_step * args.steps
-    clocks = sampler.stop() if rank == 0 else None
-    ms_total = torch.tensor([e0.elapsed_time(e1)], device=device)
-    if world > 1:
-        dist.all_reduce(ms_total, op=dist.ReduceOp.MAX)
-    ms_step = ms_total.item() / args.steps
-    tokens_all = tokens_local * world
+        sampler.start()  # runs from before the warm-up until after the end-to-end leg
+
+    peaks = measured_peaks()
+    token = w["shard"] == "token"
+    peer = make_peer(w, world, device, rank) if (token and world > 1 and args.exchange == "peer") else None
+    graph_flag_given = "--graph" in sys.argv
+    graph = args.graph == "on" or ((peer is not None or "layers" in w) and not graph_flag_given)
+    case = Case(args.workload, w, rank, world, device, args.exchange, peer, graph)
+    if args.defer_weight_grad_reduce and "shard" in case.kw:
+        case.kw["shard"].reduce_weight_grads = False
+    if args.no_overlap_grad_reduce and "shard" in case.kw:
+        case.kw["shard"].overlap_grad_reduce = False
+    video = case.video
+
+    # ---- device-resident timing
+    case.prepare(args.warmup, sync_all)
+    per_rep = case.timed(args.steps, args.reps, sync_all, reduce_max)
+    ms_step = statistics.median(per_rep)
+    launches = case.launches_per_step * args.steps
+    tokens_all = case.tokens_local * world
     value = tokens_all / (ms_step * 1e-3)
     # key-padding workload: `value` counts padded tokens; the fraction of valid context tokens is reported beside it
-    valid_frac = float(kw["mask"].float().mean().item()) if torch.is_tensor(kw.get("mask")) else None
+    valid_frac = float(case.kw["mask"].float().mean().item()) if torch.is_tensor(case.kw.get("mask")) else None
 
     # ---- end to end through the module API with host buffers (pinned), copies inside the timed region
-    xs, gs = host_sets[0]
+    e2e = measure_e2e(case, args, device, world, sync_all, reduce_max)
+
+    # ---- roofline of the tensor-core kernel: per-launch CUDA-event timing of one instrumented step
+    # every rank runs the instrumented step (a token-sharded layer contains collectives); rank 0 reports
+    roof = gemm_roofline(case.step, case.dev_sets, peaks, reps=2 if video else 5)
+    sync_all()
+    clocks = sampler.stop() if rank == 0 else None
+
+    headline = None
+    shard_rec = None
+    if args.workload == "dit":
+        case.release()
+        torch.cuda.empty_cache()
+        headline = measure_headline(args, rank, world, device, sync_all, reduce_max, peaks)
+        if not args.no_token_shard:
+            shard_rec = measure_token_shard(args, rank, world, device, sync_all, reduce_max, peaks)
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        os.sched_setaffinity(0, all_cpus)  # the CPU leg may use every core the process was given
+        v, sec, sample = cpu_reference_tokens_per_s(w, 3, 1)
+        cpu = {"value": v, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": sample}
+
+    if rank == 0:
+        status = _abi.read_status(device)
+        fl = flops_per_step(w) / (world if token else 1)
+        config = workload_config(args.workload, w, world)
+        config.update({
+            "e2e_pipeline": "double-buffered: H2D of step i+1 and D2H of step i-1 on their own streams beside the kernels of step i",
+            "valid_token_fraction": valid_frac,
+            "valid_tokens_per_s": None if valid_frac is None else value * valid_frac,
+            "cuda_graph": case.use_graph,
+            "exchange": ("peer-memory kernels" if case.peer_on else "nccl") if token and world > 1 else None,
+            "weight_grad_allreduce_in_timed_region": bool(token and world > 1 and not args.defer_weight_grad_reduce),
+            "host_affinity": numa,
+        })
+        line = {
+            "metric": "pom_stack_fwd_tokens_per_s" if video else METRIC, "value": value, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "ms_per_step_min": min(per_rep), "ms_per_step_max": max(per_rep), "reps": args.reps,
+            "higher_is_better": True, "scaling": "strong" if token else "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": config,
+            "roofline": roof,
+            "step_roofline": {"flops_per_step": fl, "tflops": fl / (ms_step * 1e-3) / 1e12,
+                              "frac_of_burst_peak": fl / (ms_step * 1e-3) / 1e12 / peaks["burst"],
+                              "peak_source": peaks["source"]},
+            "headline_n4096": headline,
+            "token_shard": shard_rec,
+            "cpu_baseline": cpu,
+            "e2e": e2e,
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "device_status": status,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def measure_e2e(case, args, device, world, sync_all, reduce_max):
+    """The same metric through the module API with pinned host buffers: every step's inputs cross PCIe host to
+    device and its outputs (y, dx) device to host inside the timed region.  Double-buffered: the host->device copy
+    of step i+1 and the device->host copy of step i-1 run on their own streams while the kernels of step i run."""
+    video = case.video
+    xs, _ = case.host_sets[0]
     y_host = torch.empty_like(xs).pin_memory()
     dx_host = torch.empty_like(xs).pin_memory()
-
-    # Double-buffered: the host->device copy of step i+1 and the device->host copy of step i-1 run on their own
-    # streams while the kernels of step i run; every step's copies are inside the timed region.
     copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
-    main = torch.cuda.current_stream()
+    main_stream = torch.cuda.current_stream()
     n_buf = 2
     xb = [torch.empty(xs.shape, dtype=xs.dtype, device=device) for _ in range(n_buf)]
     gb = None if video else [torch.empty(xs.shape, dtype=xs.dtype, device=device) for _ in range(n_buf)]
@@ -469,7 +629,7 @@ def main():
 
     def stage_in(i):
         j = i % n_buf
-        hx, hg = host_sets[i % len(host_sets)]
+        hx, hg = case.host_sets[i % len(case.host_sets)]
         with torch.cuda.stream(copy_in):
             if ev_done[j] is not None:
                 copy_in.wait_event(ev_done[j])  # the step that last read this buffer
@@ -484,81 +644,115 @@ def main():
             j = i % n_buf
             if i + 1 < n:
                 stage_in(i + 1)
-            main.wait_event(ev_in[j])
+            main_stream.wait_event(ev_in[j])
             if video:
-                _, outs = step(split(xb[j]), None)
+                _, outs = case.step(case.split(xb[j]), None)
                 results = ((torch.cat(outs, dim=1), y_host),)
             else:
-                y, grads = step(xb[j].detach(), gb[j])
+                y, grads = case.step(xb[j].detach(), gb[j])
                 results = ((y, y_host), (grads[0], dx_host))
             done = torch.cuda.Event()
-            done.record(main)
+            done.record(main_stream)
             ev_done[j] = done
             with torch.cuda.stream(copy_out):
                 copy_out.wait_event(done)
                 for t, h in results:
                     h.copy_(t, non_blocking=True)
                     t.record_stream(copy_out)
-        main.wait_stream(copy_out)
+        main_stream.wait_stream(copy_out)
 
     e2e_steps = max(3, min(args.steps, 20))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     run_e2e(2)
     sync_all()
     e0.record()
     run_e2e(e2e_steps)
     e1.record()
     sync_all()
-    ms_e2e = torch.tensor([e0.elapsed_time(e1)], device=device)
-    if world > 1:
-        dist.all_reduce(ms_e2e, op=dist.ReduceOp.MAX)
-    e2e_val = tokens_all / (ms_e2e.item() / e2e_steps * 1e-3)
+    ms = reduce_max(e0.elapsed_time(e1)) / e2e_steps
     h2d = (1 if video else 2) * xs.numel() * xs.element_size()
     d2h = (1 if video else 2) * xs.numel() * xs.element_size()
+    return {"value": case.tokens_local * world / (ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
+            "d2h_bytes_per_step": d2h, "ms_per_step": ms, "steps": e2e_steps,
+            "copy_gbs_per_rank_each_way": h2d / (ms * 1e-3) / 1e9}
 
-    # ---- roofline of the tensor-core kernel: per-launch CUDA-event timing of one instrumented step
-    peaks = measured_peaks()
-    # every rank runs the instrumented step (a token-sharded layer contains collectives); rank 0 reports
-    roof = gemm_roofline(step, dev_sets, peaks, reps=2 if video else 5)
-    sync_all()
 
-    cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        v, sec, sample = cpu_reference_tokens_per_s(w, 3, 1)
-        cpu = {"value": v, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": sample}
+def measure_headline(args, rank, world, device, sync_all, reduce_max, peaks):
+    """The layer at the headline sequence length: D=1152, degree 2, expand 2, N=4096, B=8 per rank (the same
+    32768 tokens per step as the dit workload), timed exactly like `value`."""
+    w = dict(WORKLOADS["dit4k"])
+    case = Case("dit4k", w, rank, world, device)
+    case.prepare(args.warmup, sync_all)
+    per_rep = case.timed(args.steps, max(3, args.reps // 2), sync_all, reduce_max)
+    ms = statistics.median(per_rep)
+    fl = flops_per_step(w)
+    rec = {"config": workload_config("dit4k", w, world), "ms_per_step": ms, "ms_per_step_min": min(per_rep),
+           "ms_per_step_max": max(per_rep), "tokens_per_s": case.tokens_local * world / (ms * 1e-3),
+           "tflops_per_gpu": fl / (ms * 1e-3) / 1e12, "frac_of_burst_peak": fl / (ms * 1e-3) / 1e12 / peaks["burst"],
+           "peak_source": peaks["source"]}
+    case.release()
+    torch.cuda.empty_cache()
+    return rec
 
-    if rank == 0:
-        status = _abi.read_status(device)
-        line = {
-            "metric": "pom_stack_fwd_tokens_per_s" if video else METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_step, "higher_is_better": True,
-            "scaling": "strong" if w["shard"] == "token" else "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": args.workload, "B_per_rank": w["B"], "N": w["N"], "D": w["D"], "degree": w["degree"],
-                       "expand": w["expand"], "mask": w["mask"], "rope": w["rope"], "sharding": w["shard"],
-                       "parallelism": f"{w['shard']}-shard x{world}",
-                       "l2": "3 rotating input sets (>= 450 MB) plus ~1 GB of intermediates per step, larger than the 126 MB L2",
-                       "e2e_pipeline": "double-buffered: H2D of step i+1 and D2H of step i-1 on their own streams beside the kernels of step i",
-                       "valid_token_fraction": valid_frac,
-                       "valid_tokens_per_s": None if valid_frac is None else value * valid_frac,
-                       "cuda_graph": use_graph,
-                       "exchange": ("peer-memory kernels" if peer_on else "nccl") if w["shard"] == "token" and world > 1 else None,
-                       "weight_grad_allreduce_in_timed_region": bool(w["shard"] == "token" and world > 1
-                                                                     and not args.defer_weight_grad_reduce)},
-            "roofline": roof,
-            "step_roofline": {"flops_per_step": flops_per_step(w) / (world if w["shard"] == "token" else 1),
-                              "tflops": flops_per_step(w) / (world if w["shard"] == "token" else 1) / (ms_step * 1e-3) / 1e12,
-                              "frac_of_burst_peak": flops_per_step(w) / (world if w["shard"] == "token" else 1) / (ms_step * 1e-3) / 1e12 / peaks["burst"],
-                              "peak_source": peaks["source"]},
-            "cpu_baseline": cpu,
-            "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": ms_e2e.item() / e2e_steps},
-            "gpu_launches": launches,
-            "clocks": clocks,
-            "device_status": status,
-        }
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+
+def measure_token_shard(args, rank, world, device, sync_all, reduce_max, peaks):
+    """Strong scaling of one 65536-token sequence (2-D rotary, non-causal and token-causal) sharded by token over
+    the `world` ranks: ms/step of the sharded step (parameter-gradient all-reduce inside the timed region), the
+    same problem on one GPU timed on rank 0 in this process, and their ratio."""
+    import torch.distributed as dist
+    from pom_b200 import _abi
+
+    out = {}
+    steps = max(5, min(args.steps, 50))
+    reps = max(3, args.reps // 2)
+    solo_sync = torch.cuda.synchronize
+    peer = None
+    if world > 1 and args.exchange == "peer":
+        peer = make_peer(WORKLOADS["seq64k"], world, device, rank)
+    for name in ("seq64k", "seq64k_causal"):
+        w = dict(WORKLOADS[name])
+        fl = flops_per_step(w)
+        rec = {"config": workload_config(name, w, world), "n_gpus": world, "steps": steps, "reps": reps,
+               "flops_per_step": fl}
+        # one GPU, whole sequence, on rank 0 (the other ranks wait at the barrier below)
+        ms1 = 0.0
+        if rank == 0:
+            solo = Case(name, w, 0, 1, device)
+            solo.prepare(args.warmup, solo_sync)
+            r1 = solo.timed(steps, reps, solo_sync, lambda ms: ms)
+            ms1 = statistics.median(r1)
+            rec["launches_per_step_1gpu"] = solo.launches_per_step
+            solo.release()
+            torch.cuda.empty_cache()
+        if world > 1:
+            t = torch.tensor([ms1], device=device)
+            dist.broadcast(t, 0)
+            ms1 = t.item()
+        rec["ms_per_step_1gpu"] = ms1
+        rec["frac_of_burst_peak_1gpu"] = fl / (ms1 * 1e-3) / 1e12 / peaks["burst"]
+        if world > 1:
+            sh = Case(name, w, rank, world, device, args.exchange, peer, graph=peer is not None)
+            sh.prepare(args.warmup, sync_all)
+            rs = sh.timed(steps, reps, sync_all, reduce_max)
+            msn = statistics.median(rs)
+            rec.update({"ms_per_step_sharded": msn, "ms_per_step_sharded_min": min(rs),
+                        "ms_per_step_sharded_max": max(rs), "speedup_vs_1gpu": ms1 / msn,
+                        "tokens_per_s": w["B"] * w["N"] / (msn * 1e-3),
+                        "frac_of_burst_peak_per_gpu": fl / world / (msn * 1e-3) / 1e12 / peaks["burst"],
+                        "transport": "peer-memory kernels inside one CUDA graph per rank" if sh.peer_on else "nccl, eager",
+                        "weight_grad_allreduce_in_timed_region": True,
+                        "launches_per_step_per_rank": sh.launches_per_step})
+            sh.release()
+            torch.cuda.empty_cache()
+            st = torch.tensor([float(_abi.read_status(device))], device=device)
+            dist.all_reduce(st, op=dist.ReduceOp.MAX)
+            rec["peer_status_max_over_ranks"] = int(st.item())
+        else:
+            rec["tokens_per_s"] = w["B"] * w["N"] / (ms1 * 1e-3)
+        out[name] = rec
+    if peer is not None:
+        peer.close()
+    return out
 
 
 def gemm_roofline(step, dev_sets, peaks, reps=5):
@@ -585,15 +779,25 @@ def gemm_roofline(step, dev_sets, peaks, reps=5):
 
         setattr(ops, name, timed)
 
-    def gemm_flops(a, b, a_mn=False, b_mn=False, **_):
+    def gemm_flops(a, b, a_mn=False, b_mn=False, out=None, accumulate=False, **_):
         M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
         N = b.shape[1] if b_mn else b.shape[0]
-        return 2.0 * M * N * K, f"gemm[{M}x{N}x{K}{' A^T' if a_mn else ''}{' B^T' if b_mn else ''}]"
+        nbytes = 2.0 * (M * K + N * K) + M * N * (4.0 if accumulate or (out is not None and out.dtype == torch.float32) else 2.0)
+        return 2.0 * M * N * K, f"gemm[{M}x{N}x{K}{' A^T' if a_mn else ''}{' B^T' if b_mn else ''}]", nbytes
+
+    def phase(label, n_out):
+        # operands A (M x D) and B (P x D) read once; n_out bf16 (M x P) tensors written (and z re-read in backward)
+        def f(x, wgt, *a, **k):
+            M, D = x.shape[0] * x.shape[1], x.shape[2]
+            P = wgt.shape[0] if label != "gate_bwd_gemm" else wgt.shape[1]
+            tag = label + ("+rope" if k.get("rope") is not None else "")
+            return 2.0 * M * D * P, tag, 2.0 * (M * D + P * D) + 2.0 * n_out * M * P
+        return f
 
     wrap("gemm", gemm_flops)
-    wrap("ctx_gemm", lambda x, wpo, c, **_: (2.0 * x.shape[0] * x.shape[1] * x.shape[2] * wpo.shape[0], "ctx_gemm"))
-    wrap("gate_gemm", lambda x, wse, b, h, **_: (2.0 * x.shape[0] * x.shape[1] * x.shape[2] * wse.shape[0], "gate_gemm"))
-    wrap("gate_bwd_gemm", lambda dy, wo, *a, **_: (2.0 * dy.shape[0] * dy.shape[1] * dy.shape[2] * wo.shape[1], "gate_bwd_gemm"))
+    wrap("ctx_gemm", phase("ctx_gemm", 1))
+    wrap("gate_gemm", phase("gate_gemm", 2))
+    wrap("gate_bwd_gemm", phase("gate_bwd_gemm", 2))
     try:
         for i in range(reps):
             step(*dev_sets[i % len(dev_sets)])
@@ -603,13 +807,14 @@ def gemm_roofline(step, dev_sets, peaks, reps=5):
         for n, fn in originals.items():
             setattr(ops, n, fn)
     agg = {}
-    for name, (fl, label), s, e in records:
-        a = agg.setdefault(label, [0.0, 0.0, 0])
+    for name, (fl, label, nbytes), s, e in records:
+        a = agg.setdefault(label, [0.0, 0.0, 0, nbytes])
         a[0] += fl
         a[1] += s.elapsed_time(e)
         a[2] += 1
     rows = [{"kernel": k, "launches_per_step": v[2] / reps, "flops_per_launch": v[0] / v[2], "ms_per_launch": v[1] / v[2],
-             "tflops": v[0] / v[1] / 1e9} for k, v in agg.items() if v[0] > 0]
+             "tflops": v[0] / v[1] / 1e9, "algorithmic_bytes": v[3], "ncu_dram_bytes": NCU_TRAFFIC_BYTES.get(k)}
+            for k, v in agg.items() if v[0] > 0]
     rows.sort(key=lambda r: -r["ms_per_launch"] * r["launches_per_step"])
     tot_fl = sum(v[0] for v in agg.values()) / reps
     tot_ms = sum(v[1] for v in agg.values()) / reps
@@ -617,8 +822,8 @@ def gemm_roofline(step, dev_sets, peaks, reps=5):
     return {"bound": "tensor", "kernel": "gemm_tcgen05_kernel: " + top["kernel"], "achieved": top["tflops"],
             "peak": peaks["burst"], "unit": "TFLOP/s", "frac": top["tflops"] / peaks["burst"],
             "peak_sustained": peaks["sustained"], "frac_of_sustained": top["tflops"] / peaks["sustained"],
-            "peak_source": peaks["source"], "traffic": NCU_TRAFFIC_BYTES.get(top["kernel"]),
-            "traffic_by_kernel": {k: v for k, v in NCU_TRAFFIC_BYTES.items()},
+            "peak_source": peaks["source"], "traffic": top["ncu_dram_bytes"],
+            "algorithmic_bytes": top["algorithmic_bytes"],
             "all_gemm_launches": {"tflops": tot_fl / tot_ms / 1e9, "ms_per_step": tot_ms, "frac": tot_fl / tot_ms / 1e9 / peaks["burst"]},
             "per_launch": rows}
 

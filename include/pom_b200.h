@@ -32,7 +32,7 @@
 extern "C" {
 #endif
 
-#define POM_ABI_VERSION 1
+#define POM_ABI_VERSION 2
 
 enum {
   POM_OK = 0,
@@ -63,7 +63,16 @@ long long pom_launch_count(void);
  * 1-D: cos0/sin0 are (max_len, P/2) tables, pos is (N) int64, pos_stride 1.
  * 2-D: cos0/sin0 are the row tables (max_h, P/4), cos1/sin1 the column tables (max_w, P/4),
  *      pos is (N, 2) int64 (row, col), pos_stride 2.
- * Positions are trusted on the device; the Python layer checks them against the table heights.
+ * len0 / len1 are the heights of the tables (rows).  The host validates positions against them
+ * (pom_rope_pos_info gives min / max); on the device a position outside [0, len) is clamped into the
+ * table, so a bad position gives a wrong rotation but never a read outside the tables (len 0 = unknown:
+ * no clamp).
+ * step0 / step1 describe the positions that section 0 (1-D, or the row half of 2-D) and section 1 (the
+ * column half) use, per aligned group of 32 tokens:  0 = the tokens of a group share one position,
+ * 1 = they hold consecutive positions (base, base + 1, ...), -1 = anything else.  The stand-alone
+ * operators ignore it; the fused tensor-core phases (pom_ctx_gemm, pom_gate_gemm, pom_gate_bwd_gemm)
+ * need 0 or 1 (they build every token's angle from its group's base angle and a lane offset) and return
+ * POM_ERR_UNSUPPORTED otherwise.  pom_rope_pos_info computes both from the positions.
  * ------------------------------------------------------------------------------------------ */
 typedef struct pom_rope {
   int32_t kind; /* POM_ROPE_* */
@@ -73,7 +82,16 @@ typedef struct pom_rope {
   const float* cos1;
   const float* sin1;
   const int64_t* pos;
+  int32_t len0, len1;
+  int32_t step0, step1;
 } pom_rope;
+
+/* Scans positions (n, pos_stride) int64 on the device and writes, for column c of the positions (c = 0, 1;
+ * only c = 0 when pos_stride == 1), info[4c + 0] = min, info[4c + 1] = max, info[4c + 2] = 1 when every aligned
+ * 32-token group is constant, info[4c + 3] = 1 when every aligned 32-token group is consecutive.  info is 8 int64
+ * in device memory; the call only enqueues work.  (Host helper of the rotary epilogues: no reference counterpart,
+ * the reference indexes its tables with the positions directly, pom/pom_rope.py:171-172.) */
+int pom_rope_pos_info(const int64_t* pos, int64_t n, int32_t pos_stride, int64_t* info, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Tensor-core GEMM (tcgen05, bf16 inputs, fp32 accumulate):
@@ -124,6 +142,9 @@ int pom_gemm_f32(const pom_gemm_args* a, void* stream);
  * Context phase, fused (bf16): hp = X·Wpoᵀ on tensor cores; the epilogue rounds hp to bf16,
  * optionally saves it, applies act + polynomial (+ per-token weight) and reduces over each
  * 128-token tile.  partial is (B * ceil(N/128), P) fp32; reduce it with pom_reduce_partials.
+ * With rope.kind != POM_ROPE_NONE the polynomial features of every token are rotated by its position before
+ * the reduction (reference pom/pom_rope.py:513-515, pom_triton_rope.py:93-217): needs K <= 4, P % 16 == 0
+ * (1-D) or P % 32 == 0 (2-D) and rope.step0/1 in {0, 1}; otherwise POM_ERR_UNSUPPORTED (use pom_poly_agg_fwd).
  * Replaces: pom/pom.py:205-206 + pom/pom.py:83-91 / 35-38 (and pom_triton.py:68-153).
  * ------------------------------------------------------------------------------------------ */
 typedef struct pom_ctx_args {
@@ -138,6 +159,7 @@ typedef struct pom_ctx_args {
   const float* tile_weight; /* optional with row_weight: (B * ceil(N/128)) fp32 from pom_tile_weights; a 128-token
                                tile whose weights sum to 0 is skipped: no loads, no MMAs, partial = 0 and its rows of
                                hp_out are NOT written (pom_poly_agg_bwd never uses rows of weight 0) */
+  pom_rope rope;       /* positions of the N context tokens (shared by all samples) */
 } pom_ctx_args;
 int pom_ctx_gemm(const pom_ctx_args* a, int* status, void* stream);
 /* out[b * ceil(N/128) + t] = sum of w[b, 128 t .. 128 t + 127] (w (B, N) fp32, key-padding weights >= 0). */
@@ -151,7 +173,8 @@ int pom_reduce_partials(const float* partial, float* out, const float* denom, fl
 /* ------------------------------------------------------------------------------------------
  * Query phase, fused (bf16): z = X·Wseᵀ; epilogue saves bf16 z (optional) and writes
  * SH = hardsigmoid(z + bias) ⊙ H as bf16.  H is fp32 with h_batch_stride / h_row_stride
- * (row stride 0: one vector per sample).
+ * (row stride 0: one vector per sample).  With rope.kind != POM_ROPE_NONE the gate is rotated by the query
+ * token's position after the hardsigmoid (reference pom/pom_rope.py:522); same conditions as pom_ctx_gemm.
  * Replaces: pom/pom.py:207 + pom/pom.py:116-118.
  * ------------------------------------------------------------------------------------------ */
 typedef struct pom_gate_args {
@@ -164,13 +187,17 @@ typedef struct pom_gate_args {
   int64_t ldx, ldw, ld_z, ld_sh;
   int64_t h_batch_stride, h_row_stride;
   int32_t B, T, D, P;
+  pom_rope rope;      /* positions of the T query tokens */
 } pom_gate_args;
 int pom_gate_gemm(const pom_gate_args* a, int* status, void* stream);
 
 /* Backward of the query phase (bf16): dSH = dY·Wo on tensor cores; the epilogue re-reads z and
  * emits dz (bf16, written at g_out with row stride ld_g), and per-tile column sums of
  * dSH ⊙ s (-> dh_partial) and of dz (-> db_partial), both (B * ceil(T/128), P) fp32.
- * Replaces: autograd of pom/pom.py:207, 116-118, 231 (input-gradient half). */
+ * With rope.kind != POM_ROPE_NONE (rotated gate): dH sums dSH ⊙ R·s and dz is the transposed rotation of
+ * dSH ⊙ H times hardsigmoid'; this form reads the output weight transposed, WoT (P, D) row stride ldwt (make it
+ * with pom_transpose_bf16), so that the channel pairs of a tile are two row boxes of one K-major operand.
+ * Replaces: autograd of pom/pom.py:207, 116-118, 231 (input-gradient half) and of pom/pom_rope.py:522. */
 typedef struct pom_gate_bwd_args {
   const void* dY;     /* (B, T, D) bf16 */
   const void* Wo;     /* (D, P) bf16, row stride ldw */
@@ -182,6 +209,9 @@ typedef struct pom_gate_bwd_args {
   float* db_partial;
   int64_t ld_dy, ldw, ld_z, ld_g, h_batch_stride;
   int32_t B, T, D, P;
+  const void* WoT;    /* rotary form only: (P, D) bf16, row stride ldwt */
+  int64_t ldwt;
+  pom_rope rope;      /* positions of the T query tokens */
 } pom_gate_bwd_args;
 int pom_gate_bwd_gemm(const pom_gate_bwd_args* a, int* status, void* stream);
 
@@ -386,6 +416,10 @@ int pom_frame_prefix_mean(const float* in, float* out, int32_t B, int32_t F, int
 
 /* Asynchronous zero fill of `bytes` bytes (cudaMemsetAsync on the stream); used for split-K accumulators. */
 int pom_fill_zero(void* dst, int64_t bytes, void* stream);
+
+/* dst (cols, rows) bf16 row stride ld_dst  <-  transpose of src (rows, cols) bf16 row stride ld_src. */
+int pom_transpose_bf16(const void* src, void* dst, int64_t rows, int64_t cols, int64_t ld_src, int64_t ld_dst,
+                       void* stream);
 
 /* Element conversion helpers (count elements): fp32 -> bf16, bf16 -> fp32. */
 int pom_cast_f32_to_bf16(const float* src, void* dst, int64_t count, void* stream);

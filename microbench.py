@@ -1,19 +1,22 @@
 """Micro-benchmarks of single kernels of libpom_b200 (CUDA-event timing, optional cuBLAS comparison).
 
-    python -m pom_b200.microbench gemm --m 32768 --n 2304 --k 1152 [--a-mn] [--b-mn] [--accumulate] [--mode 0|1|2]
-    python -m pom_b200.microbench ctx|gate|gate_bwd --b 32 --tokens 1024 --d 1152 --expand 2 --degree 2
-    python -m pom_b200.microbench agg_bwd|agg_fwd|select --b 32 --tokens 1024 --p 2304 --degree 2 [--causal] [--rope 0|1|2]
+    python microbench.py gemm --m 32768 --n 2304 --k 1152 [--a-mn] [--b-mn] [--accumulate] [--mode 0|1|2]
+    python microbench.py ctx|gate|gate_bwd --b 32 --tokens 1024 --d 1152 --expand 2 --degree 2 [--rope 0|1|2]
+    python microbench.py agg_bwd|agg_fwd|select --b 32 --tokens 1024 --p 2304 --degree 2 [--causal] [--rope 0|1|2]
 
-Each run prints one line with the average launch time and the achieved TFLOP/s or GB/s.  The same
-commands are the ones profiled with ncu for the summaries under profiles/.
+Each run prints one line with the average launch time and the achieved TFLOP/s or GB/s; the commands that
+were profiled with ncu are of this form.
 """
 from __future__ import annotations
 
 import argparse
+import os
+import sys
 
 import torch
 
-from . import _abi, ops
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from pom_b200 import _abi, ops  # noqa: E402
 
 
 def _time(fn, iters: int, warmup: int = 3) -> float:
@@ -32,16 +35,18 @@ def _time(fn, iters: int, warmup: int = 3) -> float:
 def _rope_spec(kind: int, n: int, p: int, dev):
     if kind == 0:
         return None
-    from .pom_rope import precompute_freqs_1d, precompute_freqs_2d
+    from pom_b200.pom_rope import precompute_freqs_1d, precompute_freqs_2d
 
     if kind == 1:
         c, s = precompute_freqs_1d(p, n)
-        return ops.RopeSpec(_abi.ROPE_1D, c.to(dev), s.to(dev), torch.arange(n, device=dev))
+        pos = torch.arange(n, device=dev)
+        return ops.RopeSpec(_abi.ROPE_1D, c.to(dev), s.to(dev), pos, steps=(ops.rope_pos_info(pos)[0][2], -1))
     side = int(n ** 0.5)
     rc, rs, cc, cs = precompute_freqs_2d(p, side, side)
     idx = torch.arange(n, device=dev)
     hw = torch.stack([idx // side, idx % side], 1).contiguous()
-    return ops.RopeSpec(_abi.ROPE_2D, rc.to(dev), rs.to(dev), hw, cc.to(dev), cs.to(dev))
+    steps = tuple(s for _, _, s in ops.rope_pos_info(hw))
+    return ops.RopeSpec(_abi.ROPE_2D, rc.to(dev), rs.to(dev), hw, cc.to(dev), cs.to(dev), steps=steps)
 
 
 def main(argv=None) -> None:
@@ -86,23 +91,24 @@ def main(argv=None) -> None:
         P = a.expand * a.d
         x = rnd(a.b, a.tokens, a.d)
         fl = 2.0 * a.b * a.tokens * a.d * P
+        rope = _rope_spec(a.rope, a.tokens, P, dev)
         if a.what == "ctx":
             w = rnd(P, a.d) * 0.03
             coeff = torch.randn(P, a.degree, device=dev, generator=g) * 0.1
-            ms = _time(lambda: ops.ctx_gemm(x, w, coeff), a.iters)
+            ms = _time(lambda: ops.ctx_gemm(x, w, coeff, rope=rope), a.iters)
         elif a.what == "gate":
             w = rnd(P, a.d) * 0.03
             bias = torch.zeros(P, device=dev)
             h = torch.randn(a.b, P, device=dev, generator=g)
-            ms = _time(lambda: ops.gate_gemm(x, w, bias, h), a.iters)
+            ms = _time(lambda: ops.gate_gemm(x, w, bias, h, rope=rope), a.iters)
         else:
             wo = rnd(a.d, P) * 0.03
             bias = torch.zeros(P, device=dev)
             h = torch.randn(a.b, P, device=dev, generator=g)
             z = rnd(a.b, a.tokens, P)
             G = torch.empty(a.b * a.tokens, 2 * P, device=dev, dtype=torch.bfloat16)
-            ms = _time(lambda: ops.gate_bwd_gemm(x, wo, bias, h, z, G[:, P:]), a.iters)
-        print(f"{a.what} b={a.b} tokens={a.tokens} d={a.d} p={P} degree={a.degree} mode={a.mode}: {ms:.4f} ms {fl / ms / 1e9:.0f} TFLOP/s")
+            ms = _time(lambda: ops.gate_bwd_gemm(x, wo, bias, h, z, G[:, P:], rope=rope), a.iters)
+        print(f"{a.what} b={a.b} tokens={a.tokens} d={a.d} p={P} degree={a.degree} rope={a.rope} mode={a.mode}: {ms:.4f} ms {fl / ms / 1e9:.0f} TFLOP/s")
     else:
         P = a.p
         x = rnd(a.b, a.tokens, P) * 0.5

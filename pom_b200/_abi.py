@@ -13,6 +13,7 @@ import torch
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libpom_b200.so")
 
+ABI_VERSION = 2
 POM_BF16, POM_F32 = 0, 1
 ROPE_NONE, ROPE_1D, ROPE_2D = 0, 1, 2
 OUT_BF16, OUT_F32, OUT_F32_ACCUM = 0, 1, 2
@@ -37,6 +38,8 @@ class Rope(C.Structure):
         ("cos1", C.c_void_p),
         ("sin1", C.c_void_p),
         ("pos", C.c_void_p),
+        ("len0", C.c_int32), ("len1", C.c_int32),
+        ("step0", C.c_int32), ("step1", C.c_int32),
     ]
 
 
@@ -60,6 +63,7 @@ class CtxArgs(C.Structure):
         ("ldx", C.c_int64), ("ldw", C.c_int64), ("ld_hp", C.c_int64),
         ("B", C.c_int32), ("N", C.c_int32), ("D", C.c_int32), ("P", C.c_int32), ("K", C.c_int32),
         ("tile_weight", C.c_void_p),
+        ("rope", Rope),
     ]
 
 
@@ -70,6 +74,7 @@ class GateArgs(C.Structure):
         ("ldx", C.c_int64), ("ldw", C.c_int64), ("ld_z", C.c_int64), ("ld_sh", C.c_int64),
         ("h_batch_stride", C.c_int64), ("h_row_stride", C.c_int64),
         ("B", C.c_int32), ("T", C.c_int32), ("D", C.c_int32), ("P", C.c_int32),
+        ("rope", Rope),
     ]
 
 
@@ -80,6 +85,8 @@ class GateBwdArgs(C.Structure):
         ("ld_dy", C.c_int64), ("ldw", C.c_int64), ("ld_z", C.c_int64), ("ld_g", C.c_int64),
         ("h_batch_stride", C.c_int64),
         ("B", C.c_int32), ("T", C.c_int32), ("D", C.c_int32), ("P", C.c_int32),
+        ("WoT", C.c_void_p), ("ldwt", C.c_int64),
+        ("rope", Rope),
     ]
 
 
@@ -214,6 +221,8 @@ _SIGNATURES = {
     "pom_tile_weights": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
     "pom_frame_prefix_mean": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "pom_fill_zero": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p]),
+    "pom_rope_pos_info": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]),
+    "pom_transpose_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
     "pom_cast_f32_to_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "pom_cast_bf16_to_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "pom_heads_supported": (C.c_int, [C.c_int32, C.c_int32, C.c_int32]),
@@ -248,7 +257,7 @@ def lib() -> C.CDLL:
             fn = getattr(handle, name)
             fn.restype = res
             fn.argtypes = args
-        if handle.pom_abi_version() != 1:
+        if handle.pom_abi_version() != ABI_VERSION:
             raise ImportError("libpom_b200.so ABI version mismatch; rebuild it")
         _lib = handle
     return _lib

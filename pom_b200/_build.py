@@ -13,8 +13,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libpom_b200.so")
-SOURCES = ["pom_gemm.cu", "pom_ops.cu", "pom_peer.cu", "pom_layer.cu", "pom_heads.cu"]
-HEADERS = ["ptx_sm100.cuh", "pom_math.cuh", "gemm_sm100.cuh", "gemm2_sm100.cuh", "epilogues.cuh", "common.cuh", os.path.join("..", "..", "include", "pom_b200.h")]
+SOURCES = ["pom_gemm.cu", "pom_gemm_rope.cu", "pom_ops.cu", "pom_peer.cu", "pom_layer.cu", "pom_heads.cu"]
+HEADERS = ["ptx_sm100.cuh", "pom_math.cuh", "gemm_sm100.cuh", "gemm2_sm100.cuh", "epilogues.cuh", "epilogues_rope.cuh", "gemm_launch.cuh", "common.cuh", os.path.join("..", "..", "include", "pom_b200.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -64,11 +64,14 @@ def build(force: bool = False, verbose: bool = False) -> str:
             sys.stderr.write(out)
         if p.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src}")
-    link = [nvcc, "-shared", "-o", LIB_PATH, *objs, "-Xcompiler", "-fPIC", "-gencode", "arch=compute_100a,code=sm_100a"]
+    # link beside the target and rename: a reader of the tree never sees a half-written library
+    tmp = LIB_PATH + ".tmp"
+    link = [nvcc, "-shared", "-o", tmp, *objs, "-Xcompiler", "-fPIC", "-gencode", "arch=compute_100a,code=sm_100a"]
     r = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if r.returncode != 0:
         sys.stderr.write(r.stdout)
         raise RuntimeError("link of libpom_b200.so failed")
+    os.replace(tmp, LIB_PATH)
     return LIB_PATH
 
 

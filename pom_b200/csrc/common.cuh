@@ -33,4 +33,10 @@ inline int sm_count() {
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
+// Rotary forms of the fused tensor-core phases (pom_gemm_rope.cu), reached through pom_ctx_gemm,
+// pom_gate_gemm and pom_gate_bwd_gemm when their `rope` member names a rotary kind.
+int ctx_gemm_rope(const pom_ctx_args* a, int* status, cudaStream_t st);
+int gate_gemm_rope(const pom_gate_args* a, int* status, cudaStream_t st);
+int gate_bwd_gemm_rope(const pom_gate_bwd_args* a, int* status, cudaStream_t st);
+
 }  // namespace pomh

@@ -106,6 +106,9 @@ struct EpiStore {
     long long ldr;
   };
   static constexpr int kSmemBytes = 0;
+  static constexpr int kStageBytes = kEpiStageBytes;
+  template <int BN>
+  static constexpr int smem_bytes() { return kSmemBytes; }
 
   template <int BN>
   static __device__ __forceinline__ void prologue(const Params&, const EpiMaps&, const GemmGeom&, const TileCtx&, int,
@@ -210,6 +213,9 @@ struct EpiCtx {
   // two column-sum buffers [4 quarters][256] + coefficients [16][256]
   static constexpr int kSumFloats = 2 * 4 * 256;
   static constexpr int kSmemBytes = (kSumFloats + kMaxDegree * 256) * 4;
+  static constexpr int kStageBytes = kEpiStageBytes;
+  template <int BN>
+  static constexpr int smem_bytes() { return kSmemBytes; }
 
   template <int BN>
   static __device__ __forceinline__ void prologue(const Params& p, const EpiMaps&, const GemmGeom& g, const TileCtx& t,
@@ -317,6 +323,9 @@ struct EpiGate {
     int save_z;
   };
   static constexpr int kSmemBytes = 2 * 2 * 256 * 4;  // double-buffered {bias, H}
+  static constexpr int kStageBytes = kEpiStageBytes;
+  template <int BN>
+  static constexpr int smem_bytes() { return kSmemBytes; }
 
   template <int BN>
   static __device__ __forceinline__ void prologue(const Params& p, const EpiMaps&, const GemmGeom& g, const TileCtx& t,
@@ -377,6 +386,9 @@ struct EpiGateBwd {
   };
   static constexpr int kSumFloats = 2 * 2 * 4 * 256;
   static constexpr int kSmemBytes = (kSumFloats + 2 * 2 * 256) * 4;
+  static constexpr int kStageBytes = kEpiStageBytes;
+  template <int BN>
+  static constexpr int smem_bytes() { return kSmemBytes; }
 
   // Starts the bulk load of the z block for column chunk c of tile t into buf0 (one lane per warp).
   static __device__ __forceinline__ void fetch_z(const EpiMaps& maps, const TileCtx& t, EpiIO& io, int quarter,

@@ -104,7 +104,7 @@ __device__ __forceinline__ TileCtx decode_pair_tile(const GemmGeom& g, int unit,
   t.mt = 2 * (mp - t.b * pairs_per_batch) + rank;
   t.row0 = t.mt * kBM;
   t.rows_valid = max(0, min(kBM, g.rows_per_batch - t.row0));
-  t.col0 = n * bn;
+  set_tile_cols(g, t, n, bn);
   // the two halves of a pair share one main loop: it is skipped only when both are empty
   t.live = true;
   if (g.tile_weight) {
@@ -122,9 +122,9 @@ struct Gemm2Smem {
   static constexpr int kStageBytes = kABytes + kBBytes;
 };
 
-template <int BN, int STAGES, int EPI_SMEM>
+template <int BN, int STAGES, class Epi>
 constexpr int gemm2_smem_bytes() {
-  return SmemPlan<STAGES>::bytes(Gemm2Smem<BN>::kStageBytes, EPI_SMEM);
+  return SmemPlan<STAGES>::bytes(Gemm2Smem<BN>::kStageBytes, Epi::template smem_bytes<BN>(), Epi::kStageBytes);
 }
 
 template <int BN, int STAGES, bool A_MN, bool B_MN, class Epi>
@@ -140,7 +140,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   constexpr uint32_t kIdesc = make_idesc_bf16_m256(BN, A_MN, B_MN);
 
   extern __shared__ uint8_t smem_raw[];
-  const SmemPlan<STAGES> sm(smem_raw, kStageBytes);
+  const SmemPlan<STAGES> sm(smem_raw, kStageBytes, Epi::kStageBytes);
   uint8_t* tiles = sm.tiles;
   uint64_t* full_bar = sm.full_bar;      // used in the leader
   uint64_t* empty_bar = sm.empty_bar;    // both CTAs
@@ -165,6 +165,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       mbar_init(&tempty_bar[a], 2 * kEpiWarps);
     }
     for (int w = 0; w < kEpiWarps; ++w) mbar_init(&sm.wload_bar[w], 1);
+    mbar_init(sm.eshared_bar, 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -195,7 +196,8 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         const TileCtx t = decode_pair_tile(geom, unit, BN, rank);
         const int kb0 = t.split * geom.kb_per_split;
         const int kb1 = t.live ? min(geom.k_blocks, kb0 + geom.kb_per_split) : kb0;
-        const int bcol0 = t.col0 + static_cast<int>(rank) * kHalfN;
+        // paired columns: the leader's half of the B tile holds the first channels, the peer's their partners
+        const int bcol0 = geom.pair_q ? (rank == 0 ? t.col0 : t.col1) : t.col0 + static_cast<int>(rank) * kHalfN;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, status, kStatusProducerTimeout)) {
             alive = false;
@@ -290,10 +292,12 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     const int half = (warp - 2) >> 2;
     const int epi_tid = (warp - 2) * 32 + lane;
     EpiIO io;
-    io.buf0 = sm.staging + (warp - 2) * kEpiStageBytes;
-    io.buf1 = io.buf0 + kEpiStageBytes / 2;
+    io.buf0 = sm.staging + (warp - 2) * Epi::kStageBytes;
+    io.buf1 = io.buf0 + Epi::kStageBytes / 2;
     io.bar = &sm.wload_bar[warp - 2];
     io.load_phase = 0;
+    io.shared_bar = sm.eshared_bar;
+    io.shared_phase = 0;
     io.abort_flag = abort_flag;
     io.status = status;
     const uint32_t tempty_leader[2] = {map_to_cta(smem_u32(&tempty_bar[0]), 0), map_to_cta(smem_u32(&tempty_bar[1]), 0)};

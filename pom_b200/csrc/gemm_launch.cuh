@@ -1,0 +1,338 @@
+// Host side of the tcgen05 GEMM engine: tensor-map construction, tile-plan selection and the
+// launchers that every fused-epilogue entry point shares.
+#pragma once
+#include <cudaTypedefs.h>
+#include <mutex>
+#include "common.cuh"
+#include "gemm2_sm100.cuh"
+
+namespace pomh {
+using namespace pomk;
+
+// ---------------------------------------------------------------- tensor maps
+// cuTensorMapEncodeTiled is fetched through the runtime so the library has no
+// link-time dependency on the driver (it must load on machines without one).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// Tensor of `rank` <= 4 dims (innermost first), zero fill out of bounds.  elem_bytes 2 = bf16, 4 = fp32.
+inline int make_map(CUtensorMap* m, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_elems,
+             const uint32_t* box, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B, int elem_bytes = 2) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return POM_ERR_CUDA;
+  if (!aligned16(base)) return POM_ERR_BAD_ALIGN;
+  if (rank < 2 || rank > 4) return POM_ERR_BAD_SHAPE;
+  cuuint64_t gdim[4];
+  cuuint64_t gstr[3];
+  cuuint32_t bx[4];
+  cuuint32_t es[4] = {1, 1, 1, 1};
+  for (int i = 0; i < rank; ++i) {
+    if (dims[i] == 0) return POM_ERR_BAD_SHAPE;
+    gdim[i] = dims[i];
+    bx[i] = box[i];
+    if (box[i] == 0 || box[i] > 256) return POM_ERR_BAD_SHAPE;
+  }
+  for (int i = 0; i + 1 < rank; ++i) {
+    uint64_t bytes = strides_elems[i] * static_cast<uint64_t>(elem_bytes);
+    if (bytes % 16 != 0) return POM_ERR_BAD_STRIDE;
+    if (bytes >= (1ull << 40)) return POM_ERR_TOO_LARGE;
+    gstr[i] = bytes;
+  }
+  CUresult r = fn(m, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                  static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdim, gstr, bx, es,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? POM_OK : POM_ERR_CUDA;
+}
+
+// Epilogue tensor: bf16 (batches, rows, cols) with row stride ld, moved in 32 x 32 blocks (64-byte swizzle).
+// batch_stride (elements) 0 = rows * ld.
+inline int make_io_map(CUtensorMap* m, const void* base, int64_t cols, int64_t rows, int64_t batches, int64_t ld,
+                int64_t batch_stride = 0) {
+  if (ld % 8 || ld < cols) return POM_ERR_BAD_STRIDE;
+  uint64_t dims[3] = {static_cast<uint64_t>(cols), static_cast<uint64_t>(rows), static_cast<uint64_t>(batches)};
+  uint64_t str[2] = {static_cast<uint64_t>(ld),
+                     batch_stride ? static_cast<uint64_t>(batch_stride)
+                                  : static_cast<uint64_t>(ld) * static_cast<uint64_t>(rows)};
+  uint32_t box[3] = {32, 32, 1};
+  return make_map(m, base, 3, dims, str, box, CU_TENSOR_MAP_SWIZZLE_64B);
+}
+
+// Epilogue tensor of a GEMM with rotary column pairing: the P columns are `nq` runs of `q` channels
+// (1-D rotary: [first | partner]; 2-D: [row first | row partner | col first | col partner]) addressed as
+// (channel in run, run, row in batch, batch) and moved in 32-row x 16-channel blocks (32-byte swizzle), so a
+// block that hangs over the end of its run is clipped there.
+inline int make_io_map_paired(CUtensorMap* m, const void* base, int64_t q, int64_t nq, int64_t rows, int64_t batches,
+                       int64_t ld, int64_t batch_stride = 0) {
+  if (ld % 8 || ld < q * nq || q % 8) return POM_ERR_BAD_STRIDE;
+  uint64_t dims[4] = {static_cast<uint64_t>(q), static_cast<uint64_t>(nq), static_cast<uint64_t>(rows),
+                      static_cast<uint64_t>(batches)};
+  uint64_t str[3] = {static_cast<uint64_t>(q), static_cast<uint64_t>(ld),
+                     batch_stride ? static_cast<uint64_t>(batch_stride)
+                                  : static_cast<uint64_t>(ld) * static_cast<uint64_t>(rows)};
+  uint32_t box[4] = {16, 1, 32, 1};
+  return make_map(m, base, 4, dims, str, box, CU_TENSOR_MAP_SWIZZLE_32B);
+}
+
+// The first 32 rows of a (len, q) fp32 rotary table, moved in 32-row x 16-column blocks (64-byte swizzle).
+inline int make_lane_table_map(CUtensorMap* m, const float* table, int64_t q, int64_t len) {
+  if (q % 4) return POM_ERR_BAD_STRIDE;
+  uint64_t dims[2] = {static_cast<uint64_t>(q), static_cast<uint64_t>(len < 32 ? len : 32)};
+  uint64_t str[1] = {static_cast<uint64_t>(q)};
+  uint32_t box[2] = {16, 32};
+  return make_map(m, table, 2, dims, str, box, CU_TENSOR_MAP_SWIZZLE_64B, 4);
+}
+
+struct Operands {
+  const void* A;
+  const void* Bm;
+  int64_t M, N, K;  // per batch rows, columns, reduction
+  int64_t lda, ldb;
+  int batches;
+  bool a_mn, b_mn;
+  const float* tile_weight = nullptr;  // optional per (batch, 128-row tile) weights: 0 skips the tile
+  // strided batches: element offsets between consecutive batches (0 = the matrices follow one another);
+  // b_batched: the B operand has one matrix per batch too
+  int64_t a_batch_stride = 0, b_batch_stride = 0;
+  bool b_batched = false;
+  // rotary column pairing (K-major B only): the N columns are `pair_sections` sections of 2 * pair_q channels,
+  // first channels followed by their partners; every tile holds first channels in its left half and their
+  // partners in its right half
+  int pair_q = 0;
+  int pair_sections = 1;
+};
+
+// `b_rows`: rows of the B tile one CTA loads per stage (K-major B only; MN-major B uses 64-wide boxes).
+inline int build_maps(const Operands& o, int b_rows, CUtensorMap* tmA, CUtensorMap* tmB) {
+  int rc;
+  const uint64_t nb_a = static_cast<uint64_t>(o.batches);
+  const uint64_t nb_b = o.b_batched ? static_cast<uint64_t>(o.batches) : 1;
+  if (!o.a_mn) {
+    uint64_t dims[3] = {static_cast<uint64_t>(o.K), static_cast<uint64_t>(o.M), nb_a};
+    uint64_t str[2] = {static_cast<uint64_t>(o.lda),
+                       static_cast<uint64_t>(o.a_batch_stride ? o.a_batch_stride : o.lda * o.M)};
+    uint32_t box[3] = {static_cast<uint32_t>(kBK), static_cast<uint32_t>(kBM), 1};
+    rc = make_map(tmA, o.A, 3, dims, str, box);
+  } else {
+    uint64_t dims[3] = {static_cast<uint64_t>(o.M), static_cast<uint64_t>(o.K), nb_a};
+    uint64_t str[2] = {static_cast<uint64_t>(o.lda),
+                       static_cast<uint64_t>(o.a_batch_stride ? o.a_batch_stride : o.lda * o.K)};
+    uint32_t box[3] = {64, static_cast<uint32_t>(kBK), 1};
+    rc = make_map(tmA, o.A, 3, dims, str, box);
+  }
+  if (rc) return rc;
+  if (!o.b_mn) {
+    uint64_t dims[3] = {static_cast<uint64_t>(o.K), static_cast<uint64_t>(o.N), nb_b};
+    uint64_t str[2] = {static_cast<uint64_t>(o.ldb),
+                       static_cast<uint64_t>(o.b_batch_stride ? o.b_batch_stride : o.ldb * o.N)};
+    uint32_t box[3] = {static_cast<uint32_t>(kBK), static_cast<uint32_t>(b_rows), 1};
+    rc = make_map(tmB, o.Bm, 3, dims, str, box);
+  } else {
+    uint64_t dims[3] = {static_cast<uint64_t>(o.N), static_cast<uint64_t>(o.K), nb_b};
+    uint64_t str[2] = {static_cast<uint64_t>(o.ldb),
+                       static_cast<uint64_t>(o.b_batch_stride ? o.b_batch_stride : o.ldb * o.K)};
+    uint32_t box[3] = {64, static_cast<uint32_t>(kBK), 1};
+    rc = make_map(tmB, o.Bm, 3, dims, str, box);
+  }
+  return rc;
+}
+
+inline GemmGeom make_geom(const Operands& o, int bn, int split_k) {
+  GemmGeom g;
+  g.batches = o.batches;
+  g.rows_per_batch = static_cast<int>(o.M);
+  g.m_tiles_per_batch = static_cast<int>(ceil_div(o.M, kBM));
+  g.pair_q = o.pair_q;
+  g.tiles_per_section = o.pair_q ? static_cast<int>(ceil_div(o.pair_q, bn / 2)) : 0;
+  g.n_tiles = o.pair_q ? o.pair_sections * g.tiles_per_section : static_cast<int>(ceil_div(o.N, bn));
+  g.n_cols = static_cast<int>(o.N);
+  g.k_blocks = static_cast<int>(ceil_div(o.K, kBK));
+  if (split_k < 1) split_k = 1;
+  if (split_k > g.k_blocks) split_k = g.k_blocks;
+  g.kb_per_split = static_cast<int>(ceil_div(g.k_blocks, split_k));
+  g.split_k = static_cast<int>(ceil_div(g.k_blocks, g.kb_per_split));
+  g.group_m = 8;
+  g.tile_weight = o.tile_weight;
+  g.b_batched = o.b_batched ? 1 : 0;
+  return g;
+}
+
+inline int check_operands(const Operands& o) {
+  if (!o.A || !o.Bm) return POM_ERR_NULL;
+  if (o.M <= 0 || o.N <= 0 || o.K <= 0 || o.batches <= 0) return POM_ERR_BAD_SHAPE;
+  if (o.M > INT32_MAX || o.N > INT32_MAX || o.K > INT32_MAX) return POM_ERR_TOO_LARGE;
+  if (o.lda % 8 || o.ldb % 8) return POM_ERR_BAD_STRIDE;
+  if ((!o.a_mn && o.lda < o.K) || (o.a_mn && o.lda < o.M)) return POM_ERR_BAD_STRIDE;
+  if ((!o.b_mn && o.ldb < o.K) || (o.b_mn && o.ldb < o.N)) return POM_ERR_BAD_STRIDE;
+  return POM_OK;
+}
+
+// 0: automatic choice, 1: always the one-CTA kernel, 2: always the two-CTA (pair) kernel.
+extern std::atomic<int> g_gemm_mode;
+
+template <class Kern>
+int set_smem_once(Kern kern, int smem, bool* done) {
+  if (*done) return POM_OK;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return POM_ERR_CUDA;
+  }
+  *done = true;
+  return POM_OK;
+}
+
+// One CTA per 128 x BN tile.
+template <int BN, int STAGES, bool A_MN, bool B_MN, class Epi>
+int launch(const Operands& o, int split_k, const EpiMaps& maps, const typename Epi::Params& ep, int* status,
+           cudaStream_t st) {
+  CUtensorMap tmA, tmB;
+  int rc = build_maps(o, o.pair_q ? BN / 2 : BN, &tmA, &tmB);
+  if (rc) return rc;
+  GemmGeom g = make_geom(o, BN, split_k);
+  constexpr int smem = gemm_smem_bytes<BN, STAGES, Epi>();
+  auto kern = gemm_tcgen05_kernel<BN, STAGES, A_MN, B_MN, Epi>;
+  static bool attr_set = false;
+  if ((rc = set_smem_once(kern, smem, &attr_set))) return rc;
+  const long long units = 1ll * g.batches * g.m_tiles_per_batch * g.n_tiles * g.split_k;
+  if (units > INT32_MAX) return POM_ERR_TOO_LARGE;
+  const int grid = static_cast<int>(units < sm_count() ? units : sm_count());
+  kern<<<grid, kGemmThreads, smem, st>>>(tmA, tmB, maps, g, ep, status);
+  count_launch();
+  return check_launch();
+}
+
+// Two CTAs (one cluster) per 256 x BN tile; each CTA loads BN/2 rows of the B tile.
+template <int BN, int STAGES, bool A_MN, bool B_MN, class Epi>
+int launch_pair(const Operands& o, int split_k, const EpiMaps& maps, const typename Epi::Params& ep, int* status,
+                cudaStream_t st) {
+  CUtensorMap tmA, tmB;
+  int rc = build_maps(o, BN / 2, &tmA, &tmB);
+  if (rc) return rc;
+  GemmGeom g = make_geom(o, BN, split_k);
+  constexpr int smem = gemm2_smem_bytes<BN, STAGES, Epi>();
+  auto kern = gemm_tcgen05_2cta_kernel<BN, STAGES, A_MN, B_MN, Epi>;
+  static bool attr_set = false;
+  if ((rc = set_smem_once(kern, smem, &attr_set))) return rc;
+  const long long units = 1ll * g.batches * ((g.m_tiles_per_batch + 1) / 2) * g.n_tiles * g.split_k;
+  if (units > INT32_MAX) return POM_ERR_TOO_LARGE;
+  const int clusters = static_cast<int>(units < sm_count() / 2 ? units : sm_count() / 2);
+  kern<<<2 * clusters, kGemmThreads, smem, st>>>(tmA, tmB, maps, g, ep, status);
+  count_launch();
+  return check_launch();
+}
+
+struct TilePlan {
+  bool pair;
+  int bn;
+};
+
+// Operand bytes pulled from L2 per output element are proportional to (rowsA + rowsB) / (128 * BN)
+// with rowsB = BN (one CTA) or BN/2 (pair); weigh that by the padded width and take the cheapest.
+inline TilePlan pick_plan(const Operands& o, bool allow_192, bool splittable = false) {
+  const int mode = g_gemm_mode.load(std::memory_order_relaxed);
+  const long long m_tiles = 1ll * o.batches * ceil_div(o.M, kBM);
+  TilePlan best{false, 128};
+  double best_cost = -1.0;
+  for (int pair = 0; pair < 2; ++pair) {
+    if (mode == 1 && pair) continue;
+    if (mode == 2 && !pair) continue;
+    if (mode == 0 && pair && m_tiles * ceil_div(o.N, 256) < sm_count()) continue;  // too little work to pair up
+    const int cands[3] = {256, 192, 128};
+    for (int bn : cands) {
+      if (bn == 192 && (!allow_192 || (pair && o.b_mn))) continue;
+      if (o.N <= 128 && bn != 128) continue;
+      const double padded = o.pair_q ? static_cast<double>(o.pair_sections * ceil_div(o.pair_q, bn / 2) * bn)
+                                     : static_cast<double>(ceil_div(o.N, bn) * bn);
+      double cost = padded * (128.0 + (pair ? bn / 2 : bn)) / bn;
+      // fewer work units than SMs (or SM pairs): the idle ones are paid for too (split-K GEMMs fill them)
+      const long long units = (pair ? (m_tiles + 1) / 2 : m_tiles) * static_cast<long long>(padded / bn);
+      const int slots = pair ? sm_count() / 2 : sm_count();
+      if (!splittable && units < slots) cost *= static_cast<double>(slots) / static_cast<double>(units);
+      if (best_cost < 0 || cost < best_cost - 1e-9) {
+        best_cost = cost;
+        best = TilePlan{pair != 0, bn};
+      }
+    }
+  }
+  return best;
+}
+
+// Split of the reduction dimension for accumulate-mode GEMMs: the smallest split whose work
+// units fill the last wave to at least 93 %, keeping at least 8 k-blocks per split.
+inline int pick_split(long long units, long long kblocks, int slots) {
+  long long cap = kblocks / 8 > 0 ? kblocks / 8 : 1;
+  if (cap > 32) cap = 32;
+  int best = 1;
+  double best_eff = 0.0;
+  for (int s = 1; s <= cap; ++s) {
+    const long long u = units * s;
+    const double eff = static_cast<double>(u) / static_cast<double>(ceil_div(u, slots) * slots);
+    if (eff > best_eff + 1e-9) {
+      best_eff = eff;
+      best = s;
+    }
+    if (eff >= 0.93) return s;
+  }
+  return best;
+}
+
+inline long long plan_units(const Operands& o, const TilePlan& p) {
+  const long long mt = ceil_div(o.M, kBM);
+  const long long nt = o.pair_q ? o.pair_sections * ceil_div(o.pair_q, p.bn / 2) : ceil_div(o.N, p.bn);
+  return 1ll * o.batches * (p.pair ? (mt + 1) / 2 : mt) * nt;
+}
+
+// Pipeline depth: as many stages as fit beside the epilogue staging area and scratch in the
+// 227 KiB of shared memory one CTA may use (at most 8).
+template <int STAGE_BYTES, class Epi, int BN>
+constexpr int stages_for() {
+  constexpr int kMaxSmem = 232448;
+  constexpr int n = (kMaxSmem - SmemPlan<1>::bytes(0, Epi::template smem_bytes<BN>(), Epi::kStageBytes)) / STAGE_BYTES;
+  return n > 8 ? 8 : n;
+}
+
+// Dispatch over kernel flavour and tile width for a fixed operand order and epilogue.
+template <bool A_MN, bool B_MN, class Epi>
+int run_plan(const TilePlan& p, const Operands& o, int split, const EpiMaps& maps, const typename Epi::Params& ep,
+             int* status, cudaStream_t st) {
+  if (p.pair) {
+    if (p.bn == 256)
+      return launch_pair<256, stages_for<Gemm2Smem<256>::kStageBytes, Epi, 256>(), A_MN, B_MN, Epi>(o, split, maps, ep, status, st);
+    if constexpr (!B_MN) {
+      if (p.bn == 192)
+        return launch_pair<192, stages_for<Gemm2Smem<192>::kStageBytes, Epi, 192>(), A_MN, B_MN, Epi>(o, split, maps, ep, status, st);
+    }
+    return launch_pair<128, stages_for<Gemm2Smem<128>::kStageBytes, Epi, 128>(), A_MN, B_MN, Epi>(o, split, maps, ep, status, st);
+  }
+  if (p.bn == 256)
+    return launch<256, stages_for<GemmSmem<256>::kStageBytes, Epi, 256>(), A_MN, B_MN, Epi>(o, split, maps, ep, status, st);
+  if (p.bn == 192)
+    return launch<192, stages_for<GemmSmem<192>::kStageBytes, Epi, 192>(), A_MN, B_MN, Epi>(o, split, maps, ep, status, st);
+  return launch<128, stages_for<GemmSmem<128>::kStageBytes, Epi, 128>(), A_MN, B_MN, Epi>(o, split, maps, ep, status, st);
+}
+
+template <class Epi>
+int run_plan_any_major(const TilePlan& p, const Operands& o, int split, const EpiMaps& maps,
+                       const typename Epi::Params& ep, int* status, cudaStream_t st) {
+  if (!o.a_mn && !o.b_mn) return run_plan<false, false, Epi>(p, o, split, maps, ep, status, st);
+  if (!o.a_mn && o.b_mn) return run_plan<false, true, Epi>(p, o, split, maps, ep, status, st);
+  if (o.a_mn && !o.b_mn) return run_plan<true, false, Epi>(p, o, split, maps, ep, status, st);
+  return run_plan<true, true, Epi>(p, o, split, maps, ep, status, st);
+}
+
+
+}  // namespace pomh

@@ -54,6 +54,11 @@ struct GemmGeom {
   // epilogue sees t.live == false).  Used by the context phase to skip 128-token tiles that a mask empties.
   const float* tile_weight;
   int b_batched;          // 1: the B operand has one matrix per batch (third tensor-map coordinate = batch)
+  // Rotary column pairing (0 = off): the N columns are sections of 2 * pair_q channels, pair_q first channels
+  // followed by their pair_q rotation partners.  A tile then holds BN/2 first channels in its left half and
+  // their partners in its right half (two B boxes), and never straddles a section.
+  int pair_q;
+  int tiles_per_section;  // ceil(pair_q / (BN / 2))
 };
 
 struct TileCtx {
@@ -61,10 +66,27 @@ struct TileCtx {
   int mt;          // m tile inside the batch
   int row0;        // first row inside the batch
   int rows_valid;  // valid rows of this tile (1..128)
-  int col0;        // first column of C
+  int col0;        // first column of C (paired: global column of the tile's first first-channel)
+  int col1;        // paired: global column of the partner of col0 (= col0 + pair_q)
+  int u0;          // paired: index of col0 inside its section's run of first channels
+  int sec;         // paired: section
   int split;       // K split index
   bool live;       // false: the main loop is skipped for this tile (see GemmGeom::tile_weight)
 };
+
+__device__ __forceinline__ void set_tile_cols(const GemmGeom& g, TileCtx& t, int n, int bn) {
+  if (g.pair_q) {
+    t.sec = n / g.tiles_per_section;
+    t.u0 = (n - t.sec * g.tiles_per_section) * (bn >> 1);
+    t.col0 = t.sec * 2 * g.pair_q + t.u0;
+    t.col1 = t.col0 + g.pair_q;
+  } else {
+    t.col0 = n * bn;
+    t.col1 = t.col0;
+    t.u0 = t.col0;
+    t.sec = 0;
+  }
+}
 
 __device__ __forceinline__ TileCtx decode_tile(const GemmGeom& g, int unit, int bn) {
   TileCtx t;
@@ -85,7 +107,7 @@ __device__ __forceinline__ TileCtx decode_tile(const GemmGeom& g, int unit, int 
   t.mt = m - t.b * g.m_tiles_per_batch;
   t.row0 = t.mt * kBM;
   t.rows_valid = min(kBM, g.rows_per_batch - t.row0);
-  t.col0 = n * bn;
+  set_tile_cols(g, t, n, bn);
   t.live = !g.tile_weight || __ldg(g.tile_weight + m) != 0.f;
   return t;
 }
@@ -106,6 +128,8 @@ struct alignas(64) EpiMaps {
   CUtensorMap out0;
   CUtensorMap out1;
   CUtensorMap in0;
+  // rotary epilogues: rows 0..31 of the {cos, sin} table of section 0 and of section 1 (fp32, 32 x 16 boxes)
+  CUtensorMap lane[4];
 };
 
 // Per-warp staging: two 2 KiB chunk buffers (1 KiB aligned) and one mbarrier for bulk loads.
@@ -114,6 +138,8 @@ struct EpiIO {
   uint8_t* buf1;
   uint64_t* bar;
   uint32_t load_phase;  // parity of the next bulk load to complete on `bar`
+  uint64_t* shared_bar;  // one barrier for loads that all epilogue warps consume (rotary lane tables)
+  uint32_t shared_phase;
   volatile int* abort_flag;
   int* status;
 };
@@ -125,6 +151,20 @@ __device__ __forceinline__ void bulk_wait_read() {
 }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, const void* smem_src, int x, int y, int z, int w) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z), "r"(w)
+               : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z,
+                                            int w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z),
+      "r"(w)
+      : "memory");
+}
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* smem_src, int x, int y, int z) {
   asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
                    reinterpret_cast<uint64_t>(map)),
@@ -133,7 +173,7 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void*
 }
 
 constexpr int kEpiWarps = 4 * kEpiColSplit;
-constexpr int kEpiStageBytes = 4096;  // per epilogue warp: two 2 KiB blocks for bulk stores / loads
+constexpr int kEpiStageBytes = 4096;  // default per epilogue warp: two 2 KiB blocks for bulk stores / loads
 
 // Carves the dynamic shared memory of both GEMM kernels:
 //   [pipeline tiles][epilogue staging 8 x 4 KiB][barriers, TMEM holder, abort flag: 256 B][epilogue scratch]
@@ -146,31 +186,38 @@ struct SmemPlan {
   uint64_t* tfull_bar;   // [2]       MMA -> epilogue
   uint64_t* tempty_bar;  // [2]       epilogue -> MMA
   uint64_t* wload_bar;   // [8]       per epilogue warp: bulk loads into its staging block
+  uint64_t* eshared_bar; // [1]       bulk loads that all epilogue warps consume
   uint32_t* tmem_holder;
   volatile int* abort_flag;
   float* epi_scratch;
-  __device__ __forceinline__ SmemPlan(uint8_t* raw, int stage_bytes) {
+  __device__ __forceinline__ SmemPlan(uint8_t* raw, int stage_bytes, int epi_stage_bytes = kEpiStageBytes) {
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
     tiles = base;
     staging = base + STAGES * stage_bytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(staging + kEpiWarps * kEpiStageBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(staging + kEpiWarps * epi_stage_bytes);
     full_bar = bars;
     empty_bar = bars + STAGES;
     tfull_bar = bars + 2 * STAGES;
     tempty_bar = bars + 2 * STAGES + 2;
     wload_bar = bars + 2 * STAGES + 4;
-    tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4 + kEpiWarps);
+    eshared_bar = bars + 2 * STAGES + 4 + kEpiWarps;
+    tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 5 + kEpiWarps);
     abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
     epi_scratch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);
   }
-  static constexpr int bytes(int stage_bytes, int epi_smem) {
-    return STAGES * stage_bytes + kEpiWarps * kEpiStageBytes + 256 + epi_smem + 1024;  // + alignment slack
+  static constexpr int bytes(int stage_bytes, int epi_smem, int epi_stage_bytes = kEpiStageBytes) {
+    return STAGES * stage_bytes + kEpiWarps * epi_stage_bytes + 256 + epi_smem + 1024;  // + alignment slack
   }
 };
 
-template <int BN, int STAGES, int EPI_SMEM>
+template <class Epi>
+constexpr int epi_stage_bytes() {
+  return Epi::kStageBytes;
+}
+
+template <int BN, int STAGES, class Epi>
 constexpr int gemm_smem_bytes() {
-  return SmemPlan<STAGES>::bytes(GemmSmem<BN>::kStageBytes, EPI_SMEM);
+  return SmemPlan<STAGES>::bytes(GemmSmem<BN>::kStageBytes, Epi::template smem_bytes<BN>(), Epi::kStageBytes);
 }
 
 // ---------------------------------------------------------------------------
@@ -196,7 +243,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   constexpr uint32_t kIdesc = make_idesc_bf16(BN, A_MN, B_MN);
 
   extern __shared__ uint8_t smem_raw[];
-  const SmemPlan<STAGES> sm(smem_raw, kStageBytes);
+  const SmemPlan<STAGES> sm(smem_raw, kStageBytes, Epi::kStageBytes);
   uint8_t* tiles = sm.tiles;
   uint64_t* full_bar = sm.full_bar;
   uint64_t* empty_bar = sm.empty_bar;
@@ -219,6 +266,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       mbar_init(&tempty_bar[a], kEpiWarps);
     }
     for (int w = 0; w < kEpiWarps; ++w) mbar_init(&sm.wload_bar[w], 1);
+    mbar_init(sm.eshared_bar, 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -262,7 +310,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               tma_load_3d(sa + j * (kBK * 128), &tmA, &full_bar[stage], t.row0 + j * 64, kb * kBK, t.b);
           }
           if constexpr (!B_MN) {
-            tma_load_3d(sb, &tmB, &full_bar[stage], kb * kBK, t.col0, bz);
+            if (geom.pair_q) {  // first channels, then their rotation partners (two boxes of BN/2 rows)
+              tma_load_3d(sb, &tmB, &full_bar[stage], kb * kBK, t.col0, bz);
+              tma_load_3d(sb + (BN / 2) * kBK * 2, &tmB, &full_bar[stage], kb * kBK, t.col1, bz);
+            } else {
+              tma_load_3d(sb, &tmB, &full_bar[stage], kb * kBK, t.col0, bz);
+            }
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
@@ -334,10 +387,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int half = (warp - 2) >> 2;  // which of the interleaved column chunks this warp takes
     const int epi_tid = (warp - 2) * 32 + lane;
     EpiIO io;
-    io.buf0 = sm.staging + (warp - 2) * kEpiStageBytes;
-    io.buf1 = io.buf0 + kEpiStageBytes / 2;
+    io.buf0 = sm.staging + (warp - 2) * Epi::kStageBytes;
+    io.buf1 = io.buf0 + Epi::kStageBytes / 2;
     io.bar = &sm.wload_bar[warp - 2];
     io.load_phase = 0;
+    io.shared_bar = sm.eshared_bar;
+    io.shared_phase = 0;
     io.abort_flag = abort_flag;
     io.status = status;
     int iter = 0;

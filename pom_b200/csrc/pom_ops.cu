@@ -139,7 +139,9 @@ inline int first_channels(int P, int rope_kind) { return rope_kind == POM_ROPE_N
 template <int VEC>
 __device__ __forceinline__ void rope_coeffs(const pom_rope& r, const ColMap& m, long long n, float (&c)[VEC],
                                             float (&s)[VEC]) {
-  const long long idx = r.pos[n * r.pos_stride + m.which];
+  long long idx = r.pos[n * r.pos_stride + m.which];
+  const long long len = m.which ? r.len1 : r.len0;  // the host validates positions; a bad one never reads outside
+  if (len > 0) idx = idx < 0 ? 0 : (idx >= len ? len - 1 : idx);
   ld_f32<VEC>((m.which ? r.cos1 : r.cos0) + idx * m.tab_ld + m.j, c);
   ld_f32<VEC>((m.which ? r.sin1 : r.sin0) + idx * m.tab_ld + m.j, s);
 }
@@ -705,6 +707,243 @@ __global__ void __launch_bounds__(kStCols / VEC * 8 + (PROD ? 32 : 0), 2) agg_bw
   }
 }
 
+// The same stream with rotary embedding: a CTA owns up to 128 first channels of one section and their 128
+// rotation partners (two 256-byte bulk copies per token row: [first | partner]), a thread 4 first channels and
+// their 4 partners.  The gradient reaching token n is the transposed rotation of dH by that token's angle
+// (reference pom/pom_rope.py:171-180, 208-235; backward of pom_triton_rope.py:227-475); cos/sin rows are read
+// from the (L2-resident) tables, 16 bytes per thread and coalesced across the 32 threads of a row.
+constexpr int kStHalf = kStCols / 2;
+
+template <int KR, bool PROD>
+__global__ void __launch_bounds__(256 + (PROD ? 32 : 0), 2)
+agg_bwd_stream_rope_kernel(const AggBwdDev a, int tiles_per_cta, int splits, int q, int blocks_per_section,
+                           int* status) {
+  extern __shared__ __align__(128) uint8_t st_smem[];
+  __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(st_smem);
+  uint64_t* full = reinterpret_cast<uint64_t*>(st_smem + kStStages * kStTileBytes);
+  uint64_t* empty = full + kStStages;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + kStStages);
+  constexpr int VEC = 4;
+  constexpr int kLanes = kStHalf / VEC;  // 32 threads across one row
+  constexpr int kGroups = 8;
+  constexpr int kConsumers = kLanes * kGroups;
+  const int tid = threadIdx.x, tx = tid % kLanes, ty = tid / kLanes;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int sec = blockIdx.x / blocks_per_section;
+  const int u0 = (blockIdx.x - sec * blocks_per_section) * kStHalf;  // first channel index inside the section
+  const int split = blockIdx.y, b = blockIdx.z;
+  const int width = min(kStHalf, q - u0);  // pairs of this block (multiple of 8)
+  const int p1_0 = sec * 2 * q + u0, p2_0 = p1_0 + q;
+  const int tiles_total = (a.N + kStTok - 1) / kStTok;
+  const int t_begin = split * tiles_per_cta;
+  const int my_tiles = min(tiles_total, t_begin + tiles_per_cta) - t_begin;
+  if (tid == 0) {
+    for (int s = 0; s < kStStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], kConsumers / 32);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(a.x) + static_cast<long long>(b) * a.N * a.ldx;
+  __nv_bfloat16* dxb = static_cast<__nv_bfloat16*>(a.dx) + static_cast<long long>(b) * a.N * a.ld_dx;
+  auto issue = [&](int i) {  // producer warp, all lanes
+    const int stage = i % kStStages;
+    const int n0 = (t_begin + i) * kStTok;
+    const int rows = min(kStTok, a.N - n0);
+    if (lane == 0) mbar_expect_tx(&full[stage], static_cast<uint32_t>(rows * width * 4));
+    __syncwarp();
+    for (int r = lane; r < rows; r += 32) {
+      __nv_bfloat16* dst = ring + (stage * kStTok + r) * kStCols;
+      const __nv_bfloat16* src = xb + static_cast<long long>(n0 + r) * a.ldx;
+      bulk_load_row(dst, src + p1_0, static_cast<uint32_t>(width * 2), &full[stage]);
+      bulk_load_row(dst + kStHalf, src + p2_0, static_cast<uint32_t>(width * 2), &full[stage]);
+    }
+  };
+  const bool consumer = !PROD || warp < kConsumers / 32;
+  if (PROD && !consumer) {
+    for (int i = 0; i < my_tiles; ++i) {
+      if (i >= kStStages &&
+          !mbar_wait(&empty[i % kStStages], static_cast<uint32_t>(i / kStStages - 1) & 1u, abort_flag, status,
+                     kStatusStreamTimeout))
+        break;
+      issue(i);
+    }
+  }
+  if (!PROD && warp == 0)
+    for (int i = 0; i < kStStages - 1 && i < my_tiles; ++i) issue(i);
+
+  const int c = tx * VEC;
+  const bool live = consumer && c < width;
+  float cf1[VEC][KR], cf2[VEC][KR], g1[VEC], g2[VEC], dc1[VEC][KR], dc2[VEC][KR];
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) {
+    g1[e] = live ? a.dH[static_cast<long long>(b) * a.P + p1_0 + c + e] : 0.f;
+    g2[e] = live ? a.dH[static_cast<long long>(b) * a.P + p2_0 + c + e] : 0.f;
+#pragma unroll
+    for (int k = 0; k < KR; ++k) {
+      cf1[e][k] = (live && k < a.K) ? __ldg(a.coeff + static_cast<long long>(p1_0 + c + e) * a.K + k) : 0.f;
+      cf2[e][k] = (live && k < a.K) ? __ldg(a.coeff + static_cast<long long>(p2_0 + c + e) * a.K + k) : 0.f;
+      dc1[e][k] = 0.f;
+      dc2[e][k] = 0.f;
+    }
+  }
+  float wb = a.scale;
+  if (a.denom) {
+    const float dn = a.denom[b];
+    wb = dn != 0.f ? wb / dn : 0.f;
+  }
+  const int which = a.rope.pos_stride == 2 ? sec : 0;
+  const float* __restrict__ cos_t = (sec ? a.rope.cos1 : a.rope.cos0) + u0 + c;
+  const float* __restrict__ sin_t = (sec ? a.rope.sin1 : a.rope.sin0) + u0 + c;
+  const long long tab_len = sec ? a.rope.len1 : a.rope.len0;
+
+  for (int i = 0; i < my_tiles && consumer; ++i) {
+    const int stage = i % kStStages;
+    if (!PROD && warp == 0) {
+      const int j = i + kStStages - 1;
+      if (j < my_tiles) {
+        if (j >= kStStages && !mbar_wait(&empty[j % kStStages], static_cast<uint32_t>(j / kStStages - 1) & 1u,
+                                         abort_flag, status, kStatusStreamTimeout))
+          break;
+        issue(j);
+      }
+    }
+    const int n0 = (t_begin + i) * kStTok;
+    const int rows = min(kStTok, a.N - n0);
+    // this thread's rows of the tile are n0 + ty + 8 k, handled four at a time: the table rows of a batch are
+    // requested before its tokens are touched (for the first batch, while the tile is still landing)
+    constexpr int kBatch = 2;
+    bool ok = true;
+#pragma unroll 1
+    for (int k0 = 0; k0 < kStTok / kGroups && ok; k0 += kBatch) {
+      float4 cs[kBatch], sn[kBatch];
+      if (live) {
+#pragma unroll
+        for (int k = 0; k < kBatch; ++k) {
+          const int n = min(n0 + ty + kGroups * (k0 + k), a.N - 1);
+          long long idx = __ldg(a.rope.pos + static_cast<long long>(n) * a.rope.pos_stride + which);
+          if (tab_len > 0) idx = idx < 0 ? 0 : (idx >= tab_len ? tab_len - 1 : idx);
+          cs[k] = __ldg(reinterpret_cast<const float4*>(cos_t + idx * q));
+          sn[k] = __ldg(reinterpret_cast<const float4*>(sin_t + idx * q));
+        }
+      }
+      if (k0 == 0)
+        ok = mbar_wait(&full[stage], static_cast<uint32_t>(i / kStStages) & 1u, abort_flag, status, kStatusStreamTimeout);
+      if (!ok || !live) continue;
+#pragma unroll
+      for (int k = 0; k < kBatch; ++k) {
+        const int r = ty + kGroups * (k0 + k);
+        if (r >= rows) break;
+        const int n = n0 + r;
+        float x1[VEC], x2[VEC], o1[VEC], o2[VEC];
+        {
+          const __nv_bfloat16* src = ring + (stage * kStTok + r) * kStCols + c;
+          const uint2 qa = *reinterpret_cast<const uint2*>(src);
+          const uint2 qb = *reinterpret_cast<const uint2*>(src + kStHalf);
+          x1[0] = __uint_as_float(qa.x << 16), x1[1] = __uint_as_float(qa.x & 0xffff0000u);
+          x1[2] = __uint_as_float(qa.y << 16), x1[3] = __uint_as_float(qa.y & 0xffff0000u);
+          x2[0] = __uint_as_float(qb.x << 16), x2[1] = __uint_as_float(qb.x & 0xffff0000u);
+          x2[2] = __uint_as_float(qb.y << 16), x2[3] = __uint_as_float(qb.y & 0xffff0000u);
+        }
+        const float w = a.row_weight ? wb * __ldg(a.row_weight + static_cast<long long>(b) * a.N + n) : wb;
+        if (w == 0.f) {  // a token of weight zero: its saved projection may never have been written
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) x1[e] = 0.f, x2[e] = 0.f;
+        }
+        const float cc[4] = {cs[k].x, cs[k].y, cs[k].z, cs[k].w};
+        const float ss[4] = {sn[k].x, sn[k].y, sn[k].z, sn[k].w};
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          const float d1 = w * (g1[e] * cc[e] + g2[e] * ss[e]);
+          const float d2 = w * (g2[e] * cc[e] - g1[e] * ss[e]);
+          const float av = pom_act(x1[e]), bv = pom_act(x2[e]);
+          o1[e] = d1 * poly_grad_reg<KR>(av, cf1[e]) * pom_act_grad(x1[e]);
+          o2[e] = d2 * poly_grad_reg<KR>(bv, cf2[e]) * pom_act_grad(x2[e]);
+          float pa = av, pb = bv;
+#pragma unroll
+          for (int kk = 0; kk < KR; ++kk) {
+            dc1[e][kk] = fmaf(d1, pa, dc1[e][kk]);
+            dc2[e][kk] = fmaf(d2, pb, dc2[e][kk]);
+            pa *= av;
+            pb *= bv;
+          }
+        }
+        __nv_bfloat16* dst = dxb + static_cast<long long>(n) * a.ld_dx;
+        *reinterpret_cast<uint2*>(dst + p1_0 + c) = make_uint2(pack_bf16x2(o1[0], o1[1]), pack_bf16x2(o1[2], o1[3]));
+        *reinterpret_cast<uint2*>(dst + p2_0 + c) = make_uint2(pack_bf16x2(o2[0], o2[1]), pack_bf16x2(o2[2], o2[3]));
+      }
+    }
+    if (!ok) break;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[stage]);
+  }
+  __syncthreads();
+  if (*abort_flag) return;
+  float* red = reinterpret_cast<float*>(st_smem);  // [row group 1..7][value][thread of the row]
+  if (ty > 0 && consumer) {
+#pragma unroll
+    for (int e = 0; e < VEC; ++e)
+#pragma unroll
+      for (int k = 0; k < KR; ++k) {
+        red[((ty - 1) * 2 * VEC * KR + e * KR + k) * kLanes + tx] = dc1[e][k];
+        red[((ty - 1) * 2 * VEC * KR + VEC * KR + e * KR + k) * kLanes + tx] = dc2[e][k];
+      }
+  }
+  __syncthreads();
+  if (ty == 0 && live) {
+    float* dcp = a.dcoeff_partial + (static_cast<long long>(b) * splits + split) * a.P * a.K;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e)
+#pragma unroll
+      for (int k = 0; k < KR; ++k) {
+        float s1 = dc1[e][k], s2 = dc2[e][k];
+        for (int qg = 0; qg < kGroups - 1; ++qg) {
+          s1 += red[(qg * 2 * VEC * KR + e * KR + k) * kLanes + tx];
+          s2 += red[(qg * 2 * VEC * KR + VEC * KR + e * KR + k) * kLanes + tx];
+        }
+        if (k < a.K) {
+          dcp[static_cast<long long>(p1_0 + c + e) * a.K + k] = s1;
+          dcp[static_cast<long long>(p2_0 + c + e) * a.K + k] = s2;
+        }
+      }
+  }
+}
+
+// Sections and first channels per section of the paired stream (0 sections: not a rotary call).
+struct StreamPairs {
+  int sections, q;
+};
+inline StreamPairs stream_pairs(const pom_agg_bwd_args* a) {
+  if (a->rope.kind == POM_ROPE_1D) return StreamPairs{1, a->P / 2};
+  if (a->rope.kind == POM_ROPE_2D) return StreamPairs{2, a->P / 4};
+  return StreamPairs{0, 0};
+}
+inline StreamPlan stream_plan_rope(int B, int N, const StreamPairs& sp) {
+  StreamPlan s = stream_plan(B, N, 1);
+  s.col_blocks = sp.sections * static_cast<int>(ceil_div(sp.q, kStHalf));
+  const long long pairs = static_cast<long long>(s.col_blocks) * B;
+  long long want = ceil_div(4LL * sm_count(), pairs);
+  if (want < 1) want = 1;
+  if (want > s.tiles) want = s.tiles;
+  s.tiles_per_cta = static_cast<int>(ceil_div(s.tiles, want));
+  s.splits = static_cast<int>(ceil_div(s.tiles, s.tiles_per_cta));
+  return s;
+}
+
+bool stream_bwd_rope_eligible(const pom_agg_bwd_args* a) {
+  if (a->dtype != POM_BF16 || a->causal != 0 || a->K > 4) return false;
+  const StreamPairs sp = stream_pairs(a);
+  if (sp.sections == 0 || sp.q % 8 || sp.q * 2 * sp.sections != a->P) return false;
+  if (a->ldx % 8 || a->ld_dx % 8 || !aligned16(a->x) || !aligned16(a->dx)) return false;
+  for (const void* t : {static_cast<const void*>(a->rope.cos0), static_cast<const void*>(a->rope.sin0),
+                        static_cast<const void*>(a->rope.cos1), static_cast<const void*>(a->rope.sin1)})
+    if (t && !aligned16(t)) return false;
+  return true;
+}
+
 bool stream_bwd_eligible(const pom_agg_bwd_args* a) {
   return a->dtype == POM_BF16 && a->causal == 0 && a->rope.kind == POM_ROPE_NONE && a->K <= 4 && a->P % 8 == 0 &&
          a->ldx % 8 == 0 && a->ld_dx % 8 == 0 && aligned16(a->x) && aligned16(a->dx);
@@ -1254,6 +1493,7 @@ int pom_poly_agg_mean_noalloc(const pom_agg_args* a, const float* denom, float s
 int32_t pom_poly_agg_bwd_slots(const pom_agg_bwd_args* a) {
   if (!a || a->B <= 0 || a->N <= 0 || a->P <= 0) return 0;
   if (stream_bwd_eligible(a)) return a->B * stream_plan(a->B, a->N, a->P).splits;
+  if (stream_bwd_rope_eligible(a)) return a->B * stream_plan_rope(a->B, a->N, stream_pairs(a)).splits;
   return a->B * pom_agg_chunks(a->N);
 }
 
@@ -1323,6 +1563,32 @@ int pom_poly_agg_bwd(const pom_agg_bwd_args* a, void* stream) {
     else
       agg_bwd_stream_kernel<4, kStVec, false><<<sgrid, threads, kStSmemBytes, st>>>(d, sp.tiles_per_cta, sp.splits,
                                                                                     status);
+    count_launch();
+    return check_launch();
+  }
+  if (stream_bwd_rope_eligible(a)) {
+    int* status = ops_status_ptr();
+    if (!status) return POM_ERR_CUDA;
+    const StreamPairs pr = stream_pairs(a);
+    const StreamPlan sp = stream_plan_rope(a->B, a->N, pr);
+    if (sp.splits > 65535) return POM_ERR_TOO_LARGE;
+    const dim3 sgrid(static_cast<unsigned>(sp.col_blocks), static_cast<unsigned>(sp.splits),
+                     static_cast<unsigned>(a->B));
+    static std::once_flag attr_once_rope;
+    std::call_once(attr_once_rope, [] {
+      cudaFuncSetAttribute(agg_bwd_stream_rope_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           kStSmemBytes);
+      cudaFuncSetAttribute(agg_bwd_stream_rope_kernel<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           kStSmemBytes);
+    });
+    const int bps = sp.col_blocks / pr.sections;
+    // (a copy-only ninth warp would cap the kernel at 96 registers per thread, which the paired state spills)
+    if (a->K <= 2)
+      agg_bwd_stream_rope_kernel<2, false><<<sgrid, 256, kStSmemBytes, st>>>(d, sp.tiles_per_cta, sp.splits, pr.q, bps,
+                                                                           status);
+    else
+      agg_bwd_stream_rope_kernel<4, false><<<sgrid, 256, kStSmemBytes, st>>>(d, sp.tiles_per_cta, sp.splits, pr.q, bps,
+                                                                           status);
     count_launch();
     return check_launch();
   }

@@ -152,6 +152,16 @@ def _like_param(g: torch.Tensor, p: torch.Tensor) -> torch.Tensor:
 def _check_inputs(xq, xc, w_qc, w_ag, coeff, spec: LayerSpec):
     if xq.dim() != 3 or xc.dim() != 3:
         raise ValueError("expected (B, T, D) / (B, N, D) inputs")
+    if xq.shape[0] != xc.shape[0]:
+        raise ValueError(f"queries and context differ in batch size: {xq.shape[0]} vs {xc.shape[0]}")
+    if xq.shape[2] != xc.shape[2]:
+        raise ValueError(f"queries and context differ in feature size: {xq.shape[2]} vs {xc.shape[2]}")
+    if spec.mask_kind == "causal" and xq.shape[1] != xc.shape[1]:
+        # token m gates with the prefix aggregate of token m (reference pom/pom.py:115 asserts g == t)
+        raise ValueError(f'mask="causal" needs as many query tokens as context tokens, got {xq.shape[1]} and '
+                         f"{xc.shape[1]}")
+    if coeff.shape[1] > 16:
+        raise NotImplementedError(f"polynomial degree {coeff.shape[1]} > 16 is not implemented")
     if not xq.is_cuda:
         raise RuntimeError("pom_b200 has no CPU path: move the module and its inputs to a CUDA device")
     if xq.dtype not in (torch.bfloat16, torch.float32):
@@ -159,8 +169,6 @@ def _check_inputs(xq, xc, w_qc, w_ag, coeff, spec: LayerSpec):
     for t in (xc, w_qc, w_ag):
         if t.dtype != xq.dtype:
             raise TypeError("inputs and projection weights must share one dtype")
-    if coeff.shape[1] > 16:
-        raise NotImplementedError(f"polynomial degree {coeff.shape[1]} > 16 is not implemented")
 
 
 class _PoMLayer(torch.autograd.Function):
@@ -202,17 +210,23 @@ class _PoMLayer(torch.autograd.Function):
             maskd = mask.to(device=xq.device, dtype=xq.dtype).contiguous()
             rowden = _row_sums(mask.to(device=xq.device, dtype=torch.float32).contiguous().view(B * T, N))
         if spec.mask_kind == "keypad":
+            if tuple(mask.shape) != (B, N):
+                raise ValueError(f"expected a (B, N) = ({B}, {N}) mask, got {tuple(mask.shape)}")
             maskf = mask.to(device=xq.device, dtype=torch.float32).contiguous()
             denom = ops.reduce_partials(maskf.view(B, N, 1)).view(B)
             if shard is not None:
                 shard.all_reduce(denom)
-        fused = (bf16 and not heads and spec.rope_ctx is None and spec.rope_qry is None and not causal and not full
+        # rotary embedding rides in the GEMM epilogues when the positions of every aligned 32-token group are
+        # constant or consecutive (RopeSpec.steps) and the degree is at most 4; otherwise on the operator path
+        rotary = spec.rope_ctx is not None or spec.rope_qry is not None
+        rope_ok = K <= 4 and all(r is None or r.fusable(P) for r in (spec.rope_ctx, spec.rope_qry))
+        fused = (bf16 and not heads and (not rotary or rope_ok) and not causal and not full
                  and P % 8 == 0 and D % 8 == 0)
 
         hp = z = Hc = s32 = None
         collapsed = False
         ctx.collapsed = False
-        ctx.composite = fused and shard is None and WHOLE_LAYER_CALLS
+        ctx.composite = fused and shard is None and WHOLE_LAYER_CALLS and not rotary
         if ctx.composite:
             # the whole fused layer is one library call (no exchange to put between its phases)
             if spec.frames > 1 and (spec.n_past is not None or maskf is not None):
@@ -236,7 +250,8 @@ class _PoMLayer(torch.autograd.Function):
         # ---------------------------------------------------------------- context phase
         if fused:
             partial, hp = ops.ctx_gemm(xc, w_po, coeff32, row_weight=maskf, save_hp=need_grad,
-                                       tile_weight=None if maskf is None else ops.tile_weights(maskf))
+                                       tile_weight=None if maskf is None else ops.tile_weights(maskf),
+                                       rope=spec.rope_ctx)
             S_part = partial  # per-tile sums; reduced (and normalised, when no exchange is needed) below
         else:
             if spec.self_mixing:
@@ -277,7 +292,7 @@ class _PoMLayer(torch.autograd.Function):
 
         # ---------------------------------------------------------------- query phase
         if fused:
-            sh, z = ops.gate_gemm(xq, w_se, bias32, H, save_z=need_grad)
+            sh, z = ops.gate_gemm(xq, w_se, bias32, H, save_z=need_grad, rope=spec.rope_qry)
         elif heads:
             ones = _ones(B, heads, xq.device)
             s32 = _f32(ops.select_fwd(z, bias32, ones, rope=spec.rope_qry))   # gate in head space (B, T, heads)
@@ -373,7 +388,7 @@ class _PoMLayer(torch.autograd.Function):
 
         # ---------------------------------------------------------------- query phase backward
         if ctx.fused:
-            dh_p, db_p = ops.gate_bwd_gemm(dy, w_ag, bias32, H, z, g_z)
+            dh_p, db_p = ops.gate_bwd_gemm(dy, w_ag, bias32, H, z, g_z, rope=spec.rope_qry)
             dH = ops.reduce_partials(dh_p)
             ops.reduce_partials(db_p.view(1, -1, P), out=d_bias.view(1, P))
         elif ctx.collapsed:
@@ -563,6 +578,56 @@ class _PolyAgg(torch.autograd.Function):
         return dx, dc, None, None, None
 
 
+class _PolyAggFull(torch.autograd.Function):
+    """polynomial_aggregation_ with a (B, M, N) mask: out[b, m] = sum_n mask[b, m, n] poly[b, n] / sum_n mask[b, m, n]
+    (reference pom/pom.py:41-45, 98-99).  Per-token features, one tensor-core product mask[b]·features[b] per sample,
+    division by the row sums inside the selection kernel (whose gate is the constant 1 here)."""
+
+    @staticmethod
+    def forward(ctx, x, coeff, mask, rope):
+        if not x.is_cuda:
+            raise RuntimeError("pom_b200 has no CPU path: pass CUDA tensors")
+        B, N, P = x.shape
+        if mask.dim() != 3 or mask.shape[0] != B or mask.shape[2] != N:
+            raise ValueError(f"expected a (B, M, N) mask with B = {B}, N = {N}, got {tuple(mask.shape)}")
+        M = mask.shape[1]
+        if x.stride(-1) != 1 or (B > 1 and x.stride(0) != x.stride(1) * N):
+            x = x.contiguous()
+        coeff32 = _f32(coeff.contiguous())
+        maskd = mask.to(device=x.device, dtype=x.dtype).contiguous()
+        rowden = _row_sums(mask.to(device=x.device, dtype=torch.float32).contiguous().view(B * M, N))
+        feat = ops.poly_agg_fwd(x, coeff32, rope=rope, per_token=True)
+        Hc = torch.empty((B, M, P), dtype=x.dtype, device=x.device)
+        if x.dtype == torch.bfloat16:
+            ops.gemm_batched(maskd, feat, b_mn=True, out=Hc)
+        else:
+            for b in range(B):
+                ops.gemm(maskd[b], feat[b], b_mn=True, out=Hc[b])
+        one = _ones(1, 1, x.device).to(x.dtype).expand(B, M, P).contiguous()
+        ctx.save_for_backward(x, coeff32, maskd, rowden, Hc, one)
+        ctx.meta = (rope, coeff.dtype)
+        return ops.select_fwd(one, None, Hc, activated=True, row_denom=rowden)
+
+    @staticmethod
+    def backward(ctx, g):
+        x, coeff32, maskd, rowden, Hc, one = ctx.saved_tensors
+        rope, cdt = ctx.meta
+        B, N, P = x.shape
+        dH, _ = ops.select_bwd(g.contiguous(), one, None, Hc, torch.empty_like(one), activated=True, row_denom=rowden)
+        dfeat = torch.empty((B, N, P), dtype=x.dtype, device=x.device)
+        if x.dtype == torch.bfloat16:
+            ops.gemm_batched(maskd, dH, a_mn=True, b_mn=True, out=dfeat)
+        else:
+            for b in range(B):
+                ops.gemm(maskd[b], dH[b], a_mn=True, b_mn=True, out=dfeat[b])
+        dx = torch.empty((B, N, P), dtype=x.dtype, device=x.device)
+        dc, _ = ops.poly_agg_bwd(x, coeff32, dx_out=dx, dout=dfeat, per_token=True, rope=rope)
+        dc = dc.contiguous()
+        if cdt != torch.float32:
+            dc = ops.to_bf16(dc)
+        return dx, dc, None, None
+
+
 def _mask_kind(mask) -> str:
     if mask is None:
         return "none"
@@ -584,16 +649,19 @@ def polynomial_aggregation_(x: torch.Tensor, coeff: torch.Tensor, k: int, mask=N
                             rope: Optional[RopeSpec] = None) -> torch.Tensor:
     """Polynomial aggregation over the sequence dimension (reference pom/pom.py:52-100).
 
-    x (B, N, P), coeff (P, K).  Returns (B, 1, P) for mask None or a (B, N) mask and
-    (B, N, P) for "causal".  A (B, M, N) mask is not implemented on this path yet.
+    x (B, N, P), coeff (P, K).  Returns (B, 1, P) for mask None or a (B, N) mask, (B, N, P) for "causal" and
+    (B, M, P) for a (B, M, N) mask (bf16: N a multiple of 8; a mask row of zeros gives 0 where the reference
+    divides by zero).
     """
     if coeff.shape[1] != k:
         raise ValueError(f"coeff has {coeff.shape[1]} columns but k={k}")
     if k > 16:
         raise NotImplementedError(f"polynomial degree k={k} > 16 is not implemented")
     kind = _mask_kind(mask)
+    if kind == "block":
+        raise ValueError("BlockCausal is a layer-level mask (PoM.forward); pass a (B, M, N) tensor to the operator")
     if kind == "full":
-        raise NotImplementedError("(B, M, N) masks are not implemented by the CUDA path yet")
+        return _PolyAggFull.apply(x, coeff, mask, rope)
     return _PolyAgg.apply(x, coeff, kind, mask if kind == "keypad" else None, rope)
 
 

@@ -7,8 +7,9 @@ module computes on the CPU or with PyTorch operators.
 from __future__ import annotations
 
 import ctypes as C
+import weakref
 from dataclasses import dataclass
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 
@@ -53,6 +54,10 @@ class RopeSpec:
     pos: torch.Tensor  # int64, (N,) or (N, 2), contiguous
     cos1: Optional[torch.Tensor] = None
     sin1: Optional[torch.Tensor] = None
+    # per position column, how the positions of every aligned group of 32 tokens look: 0 = one shared position,
+    # 1 = consecutive positions, -1 = anything else / unknown (see rope_pos_info); the fused tensor-core phases
+    # need 0 or 1, the stand-alone operators take any positions
+    steps: Tuple[int, int] = (-1, -1)
 
     def to_c(self) -> Rope:
         r = Rope()
@@ -61,7 +66,57 @@ class RopeSpec:
         r.cos0, r.sin0 = ptr(self.cos0), ptr(self.sin0)
         r.cos1, r.sin1 = ptr(self.cos1), ptr(self.sin1)
         r.pos = ptr(self.pos)
+        r.len0 = self.cos0.shape[0]
+        r.len1 = self.cos1.shape[0] if self.cos1 is not None else 0
+        r.step0, r.step1 = self.steps
         return r
+
+    def fusable(self, p: int) -> bool:
+        """Whether the rotary GEMM epilogues can take this description for p channels."""
+        if self.kind == _abi.ROPE_1D:
+            return p % 16 == 0 and self.cos0.shape[1] == p // 2 and self.steps[0] in (0, 1)
+        return (p % 32 == 0 and self.cos0.shape[1] == p // 4 and self.cos1.shape[1] == p // 4
+                and self.steps[0] in (0, 1) and self.steps[1] in (0, 1))
+
+
+_pos_info_cache = {}
+
+
+def rope_pos_info(pos: torch.Tensor):
+    """Per column of ``pos`` ((N,) or (N, 2) int64, CUDA, contiguous): (min, max, step) with step as in
+    :class:`RopeSpec`.  One small kernel plus a synchronising read the first time a given tensor (object and
+    version) is seen; later calls are answered from a cache, so a training loop that reuses its position tensor
+    never synchronises (and may be captured into a CUDA graph after its first step)."""
+    _require_cuda(pos)
+    if pos.dtype != torch.int64 or not pos.is_contiguous():
+        raise TypeError("positions must be a contiguous int64 tensor")
+    key = id(pos)
+    ent = _pos_info_cache.get(key)
+    if ent is not None and ent[0]() is pos and ent[1] == pos._version:
+        return ent[2]
+    for k in [k for k, e in _pos_info_cache.items() if e[0]() is None]:
+        del _pos_info_cache[k]
+    stride = 1 if pos.dim() == 1 else pos.shape[1]
+    info = torch.empty((8,), dtype=torch.int64, device=pos.device)
+    _abi.check(_abi.lib().pom_rope_pos_info(ptr(pos), pos.shape[0], stride, ptr(info), _abi.stream_ptr()),
+               "pom_rope_pos_info")
+    vals = info.cpu().tolist()
+    out = tuple((vals[4 * c], vals[4 * c + 1], 0 if vals[4 * c + 2] else (1 if vals[4 * c + 3] else -1))
+                for c in range(stride))
+    _pos_info_cache[key] = (weakref.ref(pos), pos._version, out)
+    return out
+
+
+def transpose_bf16(src: torch.Tensor) -> torch.Tensor:
+    """(rows, cols) bf16 -> its (cols, rows) transpose as a new contiguous tensor."""
+    _require_cuda(src)
+    if src.dim() != 2 or src.dtype != torch.bfloat16 or src.stride(1) != 1:
+        raise ValueError("expected a 2-D bfloat16 tensor with a contiguous last dimension")
+    rows, cols = src.shape
+    dst = torch.empty((cols, rows), dtype=torch.bfloat16, device=src.device)
+    _abi.check(_abi.lib().pom_transpose_bf16(ptr(src), ptr(dst), rows, cols, src.stride(0), rows, _abi.stream_ptr()),
+               "pom_transpose_bf16")
+    return dst
 
 
 def _rope_c(spec: Optional[RopeSpec]) -> Rope:
@@ -214,9 +269,10 @@ def tile_weights(mask: torch.Tensor) -> torch.Tensor:
 
 
 def ctx_gemm(x: torch.Tensor, w_po: torch.Tensor, coeff: torch.Tensor, *, row_weight: Optional[torch.Tensor] = None,
-             save_hp: bool = True, tile_weight: Optional[torch.Tensor] = None):
+             save_hp: bool = True, tile_weight: Optional[torch.Tensor] = None, rope: Optional[RopeSpec] = None):
     """Context phase: returns (partial (B, MT, P) fp32, hp (B, N, P) bf16 or None).  With ``tile_weight``
-    (from :func:`tile_weights`) tiles that the mask empties are skipped and their rows of hp stay unwritten."""
+    (from :func:`tile_weights`) tiles that the mask empties are skipped and their rows of hp stay unwritten.
+    ``rope`` (fusable, degree <= 4): the polynomial features are rotated by the token positions before the sum."""
     dev = _require_cuda(x, w_po, coeff, row_weight)
     B, N, D = x.shape
     P, K = coeff.shape
@@ -228,12 +284,15 @@ def ctx_gemm(x: torch.Tensor, w_po: torch.Tensor, coeff: torch.Tensor, *, row_we
     a.tile_weight = ptr(tile_weight)
     a.ldx, a.ldw, a.ld_hp = _row_stride(x), _row_stride(w_po), P
     a.B, a.N, a.D, a.P, a.K = B, N, D, P, K
+    a.rope = _rope_c(rope)
     _abi.check(_abi.lib().pom_ctx_gemm(C.byref(a), ptr(_abi.status_word(dev)), _abi.stream_ptr()), "pom_ctx_gemm")
     return partial, hp
 
 
-def gate_gemm(x: torch.Tensor, w_se: torch.Tensor, bias: torch.Tensor, h: torch.Tensor, *, save_z: bool = True):
-    """Query phase: returns (SH (B, T, P) bf16, z (B, T, P) bf16 or None). ``h`` is (B, P) fp32."""
+def gate_gemm(x: torch.Tensor, w_se: torch.Tensor, bias: torch.Tensor, h: torch.Tensor, *, save_z: bool = True,
+              rope: Optional[RopeSpec] = None):
+    """Query phase: returns (SH (B, T, P) bf16, z (B, T, P) bf16 or None). ``h`` is (B, P) fp32.  ``rope``: the
+    gate is rotated by the query positions after the hardsigmoid."""
     dev = _require_cuda(x, w_se, bias, h)
     B, T, D = x.shape
     P = w_se.shape[0]
@@ -245,14 +304,16 @@ def gate_gemm(x: torch.Tensor, w_se: torch.Tensor, bias: torch.Tensor, h: torch.
     a.ldx, a.ldw, a.ld_z, a.ld_sh = _row_stride(x), _row_stride(w_se), P, P
     a.h_batch_stride, a.h_row_stride = h.stride(0), 0
     a.B, a.T, a.D, a.P = B, T, D, P
+    a.rope = _rope_c(rope)
     _abi.check(_abi.lib().pom_gate_gemm(C.byref(a), ptr(_abi.status_word(dev)), _abi.stream_ptr()), "pom_gate_gemm")
     return sh, z
 
 
 def gate_bwd_gemm(dy: torch.Tensor, w_o: torch.Tensor, bias: torch.Tensor, h: torch.Tensor, z: torch.Tensor,
-                  g_out: torch.Tensor):
+                  g_out: torch.Tensor, *, rope: Optional[RopeSpec] = None):
     """Backward of the query phase. Writes dz into ``g_out`` (a (B*T, P) view with its own row
-    stride) and returns (dh_partial, dbias_partial), both (B, MT, P) fp32."""
+    stride) and returns (dh_partial, dbias_partial), both (B, MT, P) fp32.  ``rope``: backward of the rotated
+    gate; this form reads the output weight transposed (a (P, D) copy made here, 2 P D bytes each way)."""
     dev = _require_cuda(dy, w_o, bias, h, z, g_out)
     B, T, D = dy.shape
     P = w_o.shape[1]
@@ -264,6 +325,10 @@ def gate_bwd_gemm(dy: torch.Tensor, w_o: torch.Tensor, bias: torch.Tensor, h: to
     a.ld_dy, a.ldw, a.ld_z, a.ld_g = _row_stride(dy), _row_stride(w_o), _row_stride(z), _row_stride(g_out)
     a.h_batch_stride = h.stride(0)
     a.B, a.T, a.D, a.P = B, T, D, P
+    a.rope = _rope_c(rope)
+    if rope is not None:
+        w_t = transpose_bf16(w_o)
+        a.WoT, a.ldwt = ptr(w_t), D
     _abi.check(_abi.lib().pom_gate_bwd_gemm(C.byref(a), ptr(_abi.status_word(dev)), _abi.stream_ptr()),
                "pom_gate_bwd_gemm")
     return dh_p, db_p
@@ -392,16 +457,27 @@ def poly_agg_bwd(x: torch.Tensor, coeff: torch.Tensor, *, dx_out: torch.Tensor, 
     return dcoeff, total
 
 
+def _check_h(h: torch.Tensor, per_tok: bool, B: int, T: int, P: int, dtype: torch.dtype) -> None:
+    """The selection kernels index a per-token H with the query token: its shape must be that of z."""
+    if per_tok:
+        if h.dtype != dtype:
+            raise TypeError("per-token H must have the dtype of z")
+        if tuple(h.shape) != (B, T, P):
+            raise ValueError(f"per-token H must have shape {(B, T, P)}, got {tuple(h.shape)}")
+    else:
+        if h.dtype != torch.float32:
+            raise TypeError("broadcast H must be float32")
+        if tuple(h.shape) != (B, P):
+            raise ValueError(f"broadcast H must have shape {(B, P)}, got {tuple(h.shape)}")
+
+
 def select_fwd(z: torch.Tensor, bias: Optional[torch.Tensor], h: torch.Tensor, *, rope: Optional[RopeSpec] = None,
                activated: bool = False, row_denom: Optional[torch.Tensor] = None) -> torch.Tensor:
     """SH = R·hardsigmoid(z + bias) ⊙ H.  ``h`` is (B, P) fp32 (one vector per sample) or (B, T, P) of z.dtype."""
     dev = _require_cuda(z, bias, h)
     B, T, P = z.shape
     per_tok = h.dim() == 3
-    if per_tok and h.dtype != z.dtype:
-        raise TypeError("per-token H must have the dtype of z")
-    if not per_tok and h.dtype != torch.float32:
-        raise TypeError("broadcast H must be float32")
+    _check_h(h, per_tok, B, T, P, z.dtype)
     sh = torch.empty((B, T, P), dtype=z.dtype, device=dev)
     a = SelectArgs()
     a.z, a.bias, a.H, a.sh = ptr(z), ptr(bias), ptr(h), ptr(sh)
@@ -422,6 +498,9 @@ def select_bwd(dsh: torch.Tensor, z: torch.Tensor, bias: Optional[torch.Tensor],
     dev = _require_cuda(dsh, z, bias, h, dz_out)
     B, T, P = z.shape
     per_tok = h.dim() == 3
+    _check_h(h, per_tok, B, T, P, z.dtype)
+    if tuple(dsh.shape) != (B, T, P):
+        raise ValueError(f"dsh must have the shape of z {(B, T, P)}, got {tuple(dsh.shape)}")
     chunks = agg_chunks(T)
     db_p = torch.empty((1, B * chunks, P), dtype=torch.float32, device=dev)
     dh_p = None if per_tok else torch.empty((B, chunks, P), dtype=torch.float32, device=dev)
@@ -447,10 +526,7 @@ def _heads_args(s: torch.Tensor, h: torch.Tensor, dtype: torch.dtype) -> SelectH
     P = h.shape[-1]
     if s.dtype != torch.float32 or not s.is_contiguous():
         raise TypeError("the per-head gate must be a contiguous float32 tensor")
-    if per_tok and h.dtype != dtype:
-        raise TypeError("per-token H must have the activation dtype")
-    if not per_tok and h.dtype != torch.float32:
-        raise TypeError("broadcast H must be float32")
+    _check_h(h, per_tok, B, T, P, dtype)
     a = SelectHeadsArgs()
     a.s, a.H = ptr(s), ptr(h)
     a.ld_h = _row_stride(h) if per_tok else 0

@@ -13,7 +13,7 @@ from typing import Optional, Tuple
 
 import torch
 
-from . import _abi
+from . import _abi, ops
 from .functional import LayerSpec, SeqShard, _mask_kind, pom_layer
 from .ops import RopeSpec
 from .pom import PoM
@@ -85,6 +85,25 @@ class PoMRoPE(PoM):
             tabs = [t[:, ::stride][:, :keep] for t in tabs]
         return [t.contiguous() for t in tabs]
 
+    def _default_positions(self, n_tokens: int, device) -> torch.Tensor:
+        """0..n-1 on ``device``, one tensor per (length, device) so that its position scan is cached."""
+        cache = self.__dict__.setdefault("_arange_cache", {})
+        key = (n_tokens, str(device))
+        if key not in cache:
+            cache[key] = torch.arange(n_tokens, device=device, dtype=torch.int64)
+        return cache[key]
+
+    @staticmethod
+    def _checked_steps(pos: torch.Tensor, heights) -> Tuple[int, ...]:
+        """Validates the positions against the table heights (the reference's table lookup raises an index
+        error for a position outside its tables, pom/pom_rope.py:171-172) and returns their group structure."""
+        info = ops.rope_pos_info(pos)
+        for (lo, hi, _), height, name in zip(info, heights, ("row / sequence", "column")):
+            if lo < 0 or hi >= height:
+                raise IndexError(f"{name} positions span [{lo}, {hi}] but the rotary table has {height} rows "
+                                 "(raise max_seq_len / max_h / max_w)")
+        return tuple(step for _, _, step in info)
+
     def _rope_spec(self, n_tokens: int, positions, positions_hw, device, for_gate: bool = False) -> RopeSpec:
         tabs = self._tables(for_gate)
         if self.rope_2d:
@@ -93,13 +112,15 @@ class PoMRoPE(PoM):
             pos = positions_hw.to(device=device, dtype=torch.int64).contiguous()
             if pos.shape != (n_tokens, 2):
                 raise ValueError(f"positions_hw must have shape ({n_tokens}, 2)")
-            return RopeSpec(_abi.ROPE_2D, tabs[0], tabs[1], pos, tabs[2], tabs[3])
+            steps = self._checked_steps(pos, (tabs[0].shape[0], tabs[2].shape[0]))
+            return RopeSpec(_abi.ROPE_2D, tabs[0], tabs[1], pos, tabs[2], tabs[3], steps=steps)
         if positions is None:
-            positions = torch.arange(n_tokens, device=device)
+            positions = self._default_positions(n_tokens, device)
         pos = positions.to(device=device, dtype=torch.int64).contiguous()
         if pos.shape != (n_tokens,):
             raise ValueError(f"positions must have shape ({n_tokens},)")
-        return RopeSpec(_abi.ROPE_1D, tabs[0], tabs[1], pos)
+        steps = self._checked_steps(pos, (tabs[0].shape[0],))
+        return RopeSpec(_abi.ROPE_1D, tabs[0], tabs[1], pos, steps=(steps[0], -1))
 
     def forward(self, xq: torch.Tensor, xc: Optional[torch.Tensor] = None, mask=None,
                 positions: Optional[torch.Tensor] = None, ctx_positions: Optional[torch.Tensor] = None,

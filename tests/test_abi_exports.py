@@ -27,7 +27,7 @@ def test_library_loads_and_exports_every_declared_symbol():
     for name in _declared_functions():
         assert hasattr(lib, name), f"{name} declared in include/pom_b200.h but not exported"
         assert name in _abi._SIGNATURES, f"{name} has no ctypes signature"
-    assert lib.pom_abi_version() == 1
+    assert lib.pom_abi_version() == _abi.ABI_VERSION
     assert _abi.strerror(0) == "ok" and "degree" in _abi.strerror(-5)
 
 

@@ -181,3 +181,16 @@ def test_selection_operator_with_one_gate_value_per_head(per_token):
     _close(got, want, tol, "forward")
     _close(gds, wds, tol, "grad_s")
     _close(gdh, wdh, tol, "grad_h")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_poly_agg_with_a_three_dimensional_mask(dtype):
+    """(B, M, N) mask through the operator entry (reference pom/pom.py:41-45, 98-99): M query rows, each its own
+    weighted mean over the N context tokens; M != N, half of the entries masked out, the diagonal kept."""
+    B, M, N, D, K = 2, 24, 40, 64, 3
+    x, coeff = _inputs(B, N, D, K, dtype)
+    torch.manual_seed(99)
+    mask = (torch.rand(B, M, N) < 0.5).float()
+    mask[:, torch.arange(M), torch.arange(M)] = 1.0
+    tol = TOLS[dtype] if dtype == torch.float32 else ROPE_BF16  # bf16: features and sums are rounded twice
+    _run_pair(x, coeff, K, mask, dtype, tol=tol)

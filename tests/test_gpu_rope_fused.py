@@ -1,0 +1,148 @@
+"""Rotary position embedding inside the tensor-core epilogues (bf16): the context, gate and gate-backward phases
+with paired channel tiles, against the CPU oracle at the layer level and against the stand-alone operators at
+the phase level; both GEMM kernels (one CTA per tile, two-CTA pair), ragged token counts, key-padding masks, and
+the fall-back for positions the epilogues cannot take."""
+import pytest
+import torch
+
+from oracle import pom_oracle as O
+from tests.helpers import BF16_TOL, assert_close, assert_status_clean, cuda_run, make_cuda_module, oracle_run
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(B, N, D, K, E, seed, two_d, side=None, max_len=None, bias_scale=0.5):
+    params = O.init_params(D, K, E, seed=seed, coeff_scale=0.1)
+    g = torch.Generator().manual_seed(seed + 1)
+    params["se_bias"] = torch.randn(params["se_bias"].shape, generator=g) * bias_scale
+    params = {k: O.bf16_round(v) for k, v in params.items()}
+    x = O.bf16_round(torch.randn(B, N, D, generator=g))
+    gy = O.bf16_round(torch.randn(B, N, D, generator=g))
+    cfg = dict(dim=D, degree=K, expand=E, heads=1)
+    kw = {}
+    if two_d:
+        cfg["rope"] = dict(two_d=True, max_h=side, max_w=side)
+        kw["positions_hw"] = torch.stack([torch.arange(N) // side, torch.arange(N) % side], 1)
+    else:
+        cfg["rope"] = dict(two_d=False, max_seq_len=max_len or N)
+    return cfg, params, x, gy, kw
+
+
+class _Spy:
+    """Counts calls of the stand-alone rotary operators, to tell which path a layer call took."""
+
+    def __init__(self, monkeypatch):
+        from pom_b200 import ops
+
+        self.calls = 0
+        for name in ("select_fwd", "select_bwd"):
+            fn = getattr(ops, name)
+
+            def wrapped(*a, _fn=fn, **k):
+                self.calls += 1
+                return _fn(*a, **k)
+
+            monkeypatch.setattr(ops, name, wrapped)
+
+
+def _check_layer(cfg, params, x, gy, kw, label, tol=BF16_TOL):
+    want_y, want_g = oracle_run(cfg, params, x, None, kw, gy)
+    mod = make_cuda_module(cfg, params, torch.bfloat16)
+    y, grads = cuda_run(mod, x, None, kw, gy, torch.bfloat16)
+    assert_status_clean()
+    assert_close(y, want_y, tol, f"{label} y")
+    for k, w in want_g.items():
+        assert_close(grads[k], w, tol, f"{label} d_{k}")
+
+
+@pytest.mark.parametrize("gemm_mode", [1, 2], ids=["one_cta", "cta_pair"])
+@pytest.mark.parametrize("shape", [
+    # B, N, D, K, E, two_d, side
+    (2, 1024, 64, 2, 2, True, 32),      # 2-D, 32 x 32 grid: rows constant per group, columns consecutive
+    (2, 320, 128, 3, 2, False, None),   # 1-D, degree 3, a partial last 128-token tile
+    (3, 200, 96, 2, 2, False, None),    # 1-D, P = 192: 96 first channels, ragged tokens
+    (1, 2048, 128, 4, 1, True, 64),     # 2-D, degree 4, expand 1 (quarter = 32 channels)
+], ids=["2d_grid32", "1d_k3", "1d_ragged", "2d_k4"])
+def test_fused_rotary_layer_against_oracle(shape, gemm_mode, monkeypatch):
+    from pom_b200 import _abi
+
+    B, N, D, K, E, two_d, side = shape
+    cfg, params, x, gy, kw = _case(B, N, D, K, E, seed=21, two_d=two_d, side=side)
+    spy = _Spy(monkeypatch)
+    assert _abi.lib().pom_set_gemm_mode(gemm_mode) == 0
+    try:
+        _check_layer(cfg, params, x, gy, kw, f"{shape} mode {gemm_mode}")
+    finally:
+        _abi.lib().pom_set_gemm_mode(0)
+    assert spy.calls == 0, "the layer left the fused rotary path"
+
+
+@pytest.mark.parametrize("two_d", [False, True], ids=["1d", "2d"])
+def test_fused_rotary_at_the_long_sequence_width(two_d):
+    """The channel width of the 64 k-token benchmark configuration (D = 1152, P = 2304: rotation partners
+    1152 or 576 channels apart) on a 64 x 64 grid of tokens."""
+    side = 64
+    cfg, params, x, gy, kw = _case(1, side * side, 1152, 2, 2, seed=22, two_d=two_d, side=side)
+    _check_layer(cfg, params, x, gy, kw, f"D=1152 two_d={two_d}")
+
+
+def test_fused_rotary_with_key_padding_mask(monkeypatch):
+    B, N, D, K, E = 3, 384, 128, 2, 2
+    cfg, params, x, gy, kw = _case(B, N, D, K, E, seed=23, two_d=False)
+    lengths = torch.tensor([384, 130, 17])
+    kw["mask"] = (torch.arange(N).view(1, N) < lengths.view(B, 1)).float()
+    spy = _Spy(monkeypatch)
+    _check_layer(cfg, params, x, gy, kw, "1-D rotary + key padding")
+    assert spy.calls == 0
+
+
+def test_shifted_and_strided_positions(monkeypatch):
+    """Consecutive positions that do not start at 0 stay on the fused path; positions with a stride of 2 are not
+    consecutive inside a 32-token group and take the stand-alone operators: same result either way."""
+    B, N, D, K, E = 2, 256, 128, 2, 2
+    cfg, params, x, gy, kw = _case(B, N, D, K, E, seed=24, two_d=False, max_len=1024)
+    spy = _Spy(monkeypatch)
+    _check_layer(cfg, params, x, gy, dict(kw, positions=torch.arange(N) + 300), "shifted")
+    assert spy.calls == 0
+    _check_layer(cfg, params, x, gy, dict(kw, positions=torch.arange(N) * 2), "strided")
+    assert spy.calls > 0
+
+
+def test_fused_context_phase_matches_the_operator():
+    """pom_ctx_gemm with a rotary description against pom_gemm_bf16 + pom_poly_agg_fwd (itself pinned to the
+    reference's operator tests): per-sample sums and the saved projection."""
+    from pom_b200 import _abi, ops
+    from pom_b200.pom_rope import precompute_freqs_2d
+
+    B, side, D, P, K = 2, 32, 64, 128, 2
+    N = side * side
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(B, N, D, generator=g).cuda().bfloat16()
+    w = (torch.randn(P, D, generator=g) / D ** 0.5).cuda().bfloat16()
+    coeff = (torch.randn(P, K, generator=g) * 0.1).cuda()
+    tabs = [t.cuda().contiguous() for t in precompute_freqs_2d(P, side, side)]
+    hw = torch.stack([torch.arange(N) // side, torch.arange(N) % side], 1).cuda()
+    steps = tuple(s for _, _, s in ops.rope_pos_info(hw))
+    assert steps == (0, 1)
+    rope = ops.RopeSpec(_abi.ROPE_2D, tabs[0], tabs[1], hw, tabs[2], tabs[3], steps=steps)
+    partial, hp = ops.ctx_gemm(x, w, coeff, rope=rope)
+    got = ops.reduce_partials(partial)
+    hp_ref = ops.gemm(x.view(B * N, D), w).view(B, N, P)
+    want = ops.reduce_partials(ops.poly_agg_fwd(hp_ref, coeff, rope=rope))
+    torch.cuda.synchronize()
+    assert_status_clean()
+    assert torch.equal(hp, hp_ref), "saved projection differs from the plain GEMM"
+    assert_close(got, want, 2e-4, "rotated sums")
+
+
+def test_positions_outside_the_tables_raise():
+    from pom_b200 import PoMRoPE
+
+    mod = PoMRoPE(64, 2, 2, 1, 1, max_seq_len=128).cuda()
+    for p in mod.parameters():
+        p.data = p.data.bfloat16()
+    x = torch.randn(1, 256, 64, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(IndexError):
+        mod(x)  # default positions 0..255 against a 128-row table
+    with pytest.raises(IndexError):
+        mod(x[:, :64], positions=torch.arange(64, device="cuda") - 1)

@@ -62,3 +62,52 @@ def test_backward_partial_slot_count_never_exceeds_the_chunk_capacity(lib):
         a.x = a.dx = C.c_void_p(512)
         slots = lib.pom_poly_agg_bwd_slots(C.byref(a))
         assert 0 < slots <= B * lib.pom_agg_chunks(N)
+
+
+def _module_for(cfg):
+    from pom_b200 import PoM, PoMRoPE
+
+    r = cfg.get("rope")
+    args = (cfg["dim"], cfg["degree"], cfg["expand"], cfg.get("groups", 1), cfg["heads"])
+    if r is None:
+        return PoM(*args)
+    return PoMRoPE(*args, rope_2d=r["two_d"], max_seq_len=r.get("max_seq_len", 4096), max_h=r.get("max_h", 64),
+                   max_w=r.get("max_w", 64))
+
+
+@pytest.mark.parametrize("name", ["pom_none", "pom_heads4_none", "pom_groups2_none", "pom_groups2_heads4_none",
+                                  "rope1d_none", "rope2d_none", "rope2d_heads4_none"])
+def test_reference_state_dicts_load_strictly_and_round_trip(golden, name):
+    """Checkpoints interchange with the reference: same parameter and buffer names and shapes, and the rotary
+    tables the module builds equal the reference's buffers."""
+    import torch
+
+    case = golden[name]
+    mod = _module_for(case["cfg"])
+    own = mod.state_dict()
+    assert sorted(own.keys()) == sorted(case["params"].keys())
+    for k, v in case["params"].items():
+        assert own[k].shape == v.shape, k
+        if "cos" in k or "sin" in k:  # tables are deterministic functions of the constructor arguments
+            assert torch.allclose(own[k], v, atol=1e-6, rtol=0), k
+    mod.load_state_dict(case["params"], strict=True)
+    back = mod.state_dict()
+    for k, v in case["params"].items():
+        assert torch.equal(back[k], v), k
+
+
+def test_shape_errors_are_raised_before_any_device_work():
+    """mask="causal" pairs query token m with the prefix aggregate of context token m: different lengths are an
+    error (the reference asserts the same in its selection step), as are mismatched batch or feature sizes."""
+    import torch
+
+    from pom_b200 import PoM
+
+    mod = PoM(16, 2, 2)
+    xq, xc = torch.randn(2, 6, 16), torch.randn(2, 9, 16)
+    with pytest.raises(ValueError, match="causal"):
+        mod(xq, xc, mask="causal")
+    with pytest.raises(ValueError, match="batch"):
+        mod(xq, torch.randn(3, 6, 16))
+    with pytest.raises(ValueError, match="feature"):
+        mod(xq, torch.randn(2, 6, 8))
