@@ -129,9 +129,11 @@ typedef struct pom_gemm_args {
 } pom_gemm_args;
 int pom_gemm_bf16(const pom_gemm_args* a, int* status, void* stream);
 
-/* Tuning knob for every tcgen05 GEMM entry point: 0 = choose per problem (default), 1 = always the
- * kernel that gives one CTA a 128 x BN tile, 2 = always the kernel in which a cluster of two CTAs
- * shares a 256 x BN tile (tcgen05 cta_group::2; each CTA loads half of the B tile). */
+/* Diagnostic override for every tcgen05 GEMM entry point (tests and micro-benchmarks use it to reach each kernel
+ * variant; production code leaves it at 0 = choose per problem).  Units digit: 1 = always the kernel that gives one
+ * CTA a 128 x BN tile, 2 = always the kernel in which a cluster of two CTAs shares a 256 x BN tile (tcgen05
+ * cta_group::2; each CTA loads half of the B tile).  Tens digit: 1 / 2 / 3 = 128 / 192 / 256 columns per tile where
+ * the operands allow that width.  Process-wide, not thread-safe against concurrent launches. */
 int pom_set_gemm_mode(int mode);
 
 /* fp32 SIMT GEMM with the same meaning (fp32 A, Bm, C; out_mode F32 or F32_ACCUM); used by the
@@ -160,6 +162,15 @@ typedef struct pom_ctx_args {
                                tile whose weights sum to 0 is skipped: no loads, no MMAs, partial = 0 and its rows of
                                hp_out are NOT written (pom_poly_agg_bwd never uses rows of weight 0) */
   pom_rope rope;       /* positions of the N context tokens (shared by all samples) */
+  /* Token-causal form (causal != 0; reference pom/pom.py:92-95, pom_triton_causal.py:68-160): instead of per-tile
+   * sums the epilogue writes, per aligned group of 32 tokens, the inclusive running sums of the (rotated)
+   * polynomial features as bf16 `pre_out` (B*N, ld_pre) and the group totals `group_sums` (B, ceil(N/32), P) fp32;
+   * `partial` and `row_weight` are not used.  pom_group_scan then turns the totals into carries for
+   * pom_gate_gemm.  Works with and without rotary embedding (K <= 4, P % 16 == 0; 2-D rotary P % 32 == 0). */
+  int32_t causal;
+  void* pre_out;
+  int64_t ld_pre;
+  float* group_sums;
 } pom_ctx_args;
 int pom_ctx_gemm(const pom_ctx_args* a, int* status, void* stream);
 /* out[b * ceil(N/128) + t] = sum of w[b, 128 t .. 128 t + 127] (w (B, N) fp32, key-padding weights >= 0). */
@@ -188,6 +199,14 @@ typedef struct pom_gate_args {
   int64_t h_batch_stride, h_row_stride;
   int32_t B, T, D, P;
   pom_rope rope;      /* positions of the T query tokens */
+  /* Token-causal form (causal != 0): H is not used; the epilogue re-reads `pre` (B*T, ld_pre) bf16 written by
+   * the causal pom_ctx_gemm, adds the group carries `carry` (B, ceil(T/32), P) fp32 from pom_group_scan and
+   * divides by (token_offset + t + 1): the prefix mean of pom/pom.py:92-95 for query token t. */
+  int32_t causal;
+  const void* pre;
+  int64_t ld_pre;
+  const float* carry;
+  int64_t token_offset;
 } pom_gate_args;
 int pom_gate_gemm(const pom_gate_args* a, int* status, void* stream);
 
@@ -209,10 +228,32 @@ typedef struct pom_gate_bwd_args {
   float* db_partial;
   int64_t ld_dy, ldw, ld_z, ld_g, h_batch_stride;
   int32_t B, T, D, P;
-  const void* WoT;    /* rotary form only: (P, D) bf16, row stride ldwt */
+  const void* WoT;    /* rotary and causal forms: (P, D) bf16, row stride ldwt */
   int64_t ldwt;
   pom_rope rope;      /* positions of the T query tokens */
+  /* Token-causal form (causal != 0; needs WoT): `pre` / `carry` as in pom_gate_args rebuild the prefix means for
+   * dz; the gradient of the prefix means, dSH ⊙ R·s / (token_offset + t + 1), is summed UP the rows of every
+   * 32-token group and written as bf16 `suf_out` (B*T, ld_suf) plus group totals `group_sums`
+   * (B, ceil(T/32), P) fp32 (reverse pom_group_scan, then pom_poly_agg_bwd with causal == 3).  dh_partial and H are
+   * not used.  Backward halves of pom_triton_causal.py:176-344 / pom_triton_rope.py:618-873. */
+  int32_t causal;
+  const void* pre;
+  int64_t ld_pre;
+  const float* carry;
+  void* suf_out;
+  int64_t ld_suf;
+  float* group_sums;
+  int64_t token_offset;
 } pom_gate_bwd_args;
+
+/* In-place exclusive scan over the 32-token groups of (B, groups, P) fp32 group totals:
+ *   reverse == 0:  sums[b, g, :] <- carry_in[b, :] + sum_{g' < g} sums[b, g', :]
+ *   reverse != 0:  sums[b, g, :] <- carry_in[b, :] + sum_{g' > g} sums[b, g', :]
+ * carry_in (B, P) may be NULL (token sharding: the totals of the ranks before / after this one); total_out (B, P),
+ * optional, receives the sum over this call's groups (without carry_in).  scratch: B * ceil(groups / 32) * P floats.
+ * Replaces the serial token loops of pom_triton_causal.py:107-160 / 233-325 at group granularity. */
+int pom_group_scan(float* sums, const float* carry_in, float* total_out, float* scratch, int32_t B, int32_t groups,
+                   int32_t P, int32_t reverse, void* stream);
 int pom_gate_bwd_gemm(const pom_gate_bwd_args* a, int* status, void* stream);
 
 /* ------------------------------------------------------------------------------------------
@@ -277,6 +318,9 @@ int pom_poly_agg_mean_noalloc(const pom_agg_args* a, const float* denom, float s
  *   causal == 1 : dout (B, N, P) dtype; `carry` (B, P) fp32 optional = suffix sum from later shards;
  *                 `total` optional output (B, P): this shard's sum of dout[n]/(n+1+offset).
  *   causal == 2 : dout (B, N, P) dtype is the gradient of each token's own features (no suffix sum).
+ *   causal == 3 : fused token-causal path (bf16, K <= 4): the gradient of token n's features is
+ *                 suf[b, n, :] + carry_b[b, n / 32, :] with `suf` = dout (bf16 running sums written by the causal
+ *                 pom_gate_bwd_gemm) and carry_b = `partial` after the reverse pom_group_scan.
  *                 phase == 1 stops after the totals (used to obtain `total` before the cross-shard
  *                 exchange that produces `carry`); phase == 0 runs everything.
  * Outputs: dx (B, N, P) dtype row stride ld_dx; dcoeff_partial (B*chunks, P, K) fp32, to be
@@ -488,9 +532,11 @@ int pom_layer_bwd(const pom_layer_args* a, int* status, void* stream);
  *   [layout[1], layout[2])      parameter-gradient region, flat_floats fp32, reduced in place
  * The library allocates nothing; the caller owns the buffers and must keep them alive, and mapped by the
  * peers, until all ranks have finished their last exchange.  All ranks must issue the same sequence of
- * exchange calls.  Waits on other ranks are bounded (2 s): on expiry POM_ERR_TIMEOUT is stored in *status
- * (device int, zero before the first call; once non-zero, later exchanges do not wait) and the results are
- * undefined.  The calls only enqueue work on `stream` and can be captured into CUDA graphs (the epochs
+ * exchange calls.  Waits on other ranks are bounded (pom_peer_comm::wait_ns, 2 s when 0): on expiry
+ * POM_ERR_TIMEOUT is stored in *status (device int, zero before the first call; once non-zero, later exchanges do
+ * not wait) and the results are undefined.  Recovery: the epoch counters of the rank that gave up have moved on,
+ * so the group must drop its buffers, zero-fill new ones, exchange handles again and clear the status word before
+ * the next exchange; a comm is not usable again after a timeout.  The calls only enqueue work on `stream` and can be captured into CUDA graphs (the epochs
  * are device-side counters).  Kernels of different ranks wait on each other, so every rank must run on its
  * own GPU. */
 #define POM_PEER_MAX_RANKS 16
@@ -503,6 +549,7 @@ typedef struct pom_peer_comm {
   int32_t rank, world;
   unsigned long long slot_floats;   /* capacity of one message (multiple of 4) */
   unsigned long long flat_floats;   /* capacity of the gradient region (multiple of 4, may be 0) */
+  unsigned long long wait_ns;       /* limit of every wait on another rank, in nanoseconds; 0 = 2 s */
 } pom_peer_comm;
 
 /* out[0] = byte offset of the slots, out[1] = of the gradient region, out[2] = total bytes. */

@@ -64,6 +64,7 @@ class CtxArgs(C.Structure):
         ("B", C.c_int32), ("N", C.c_int32), ("D", C.c_int32), ("P", C.c_int32), ("K", C.c_int32),
         ("tile_weight", C.c_void_p),
         ("rope", Rope),
+        ("causal", C.c_int32), ("pre_out", C.c_void_p), ("ld_pre", C.c_int64), ("group_sums", C.c_void_p),
     ]
 
 
@@ -75,6 +76,8 @@ class GateArgs(C.Structure):
         ("h_batch_stride", C.c_int64), ("h_row_stride", C.c_int64),
         ("B", C.c_int32), ("T", C.c_int32), ("D", C.c_int32), ("P", C.c_int32),
         ("rope", Rope),
+        ("causal", C.c_int32), ("pre", C.c_void_p), ("ld_pre", C.c_int64), ("carry", C.c_void_p),
+        ("token_offset", C.c_int64),
     ]
 
 
@@ -87,6 +90,8 @@ class GateBwdArgs(C.Structure):
         ("B", C.c_int32), ("T", C.c_int32), ("D", C.c_int32), ("P", C.c_int32),
         ("WoT", C.c_void_p), ("ldwt", C.c_int64),
         ("rope", Rope),
+        ("causal", C.c_int32), ("pre", C.c_void_p), ("ld_pre", C.c_int64), ("carry", C.c_void_p),
+        ("suf_out", C.c_void_p), ("ld_suf", C.c_int64), ("group_sums", C.c_void_p), ("token_offset", C.c_int64),
     ]
 
 
@@ -183,6 +188,7 @@ class PeerComm(C.Structure):
         ("base", C.c_void_p * PEER_MAX_RANKS),
         ("rank", C.c_int32), ("world", C.c_int32),
         ("slot_floats", C.c_ulonglong), ("flat_floats", C.c_ulonglong),
+        ("wait_ns", C.c_ulonglong),
     ]
 
 
@@ -221,6 +227,8 @@ _SIGNATURES = {
     "pom_tile_weights": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
     "pom_frame_prefix_mean": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "pom_fill_zero": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p]),
+    "pom_group_scan": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                C.c_void_p]),
     "pom_rope_pos_info": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]),
     "pom_transpose_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
     "pom_cast_f32_to_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),

@@ -13,8 +13,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libpom_b200.so")
-SOURCES = ["pom_gemm.cu", "pom_gemm_rope.cu", "pom_ops.cu", "pom_peer.cu", "pom_layer.cu", "pom_heads.cu"]
-HEADERS = ["ptx_sm100.cuh", "pom_math.cuh", "gemm_sm100.cuh", "gemm2_sm100.cuh", "epilogues.cuh", "epilogues_rope.cuh", "gemm_launch.cuh", "common.cuh", os.path.join("..", "..", "include", "pom_b200.h")]
+SOURCES = ["pom_gemm.cu", "pom_gemm_rope.cu", "pom_gemm_causal.cu", "pom_ops.cu", "pom_peer.cu", "pom_layer.cu", "pom_heads.cu"]
+HEADERS = ["ptx_sm100.cuh", "pom_math.cuh", "gemm_sm100.cuh", "gemm2_sm100.cuh", "epilogues.cuh", "epilogues_rope.cuh", "epilogues_causal.cuh", "gemm_launch.cuh", "common.cuh", os.path.join("..", "..", "include", "pom_b200.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

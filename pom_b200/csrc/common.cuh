@@ -38,5 +38,9 @@ inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 int ctx_gemm_rope(const pom_ctx_args* a, int* status, cudaStream_t st);
 int gate_gemm_rope(const pom_gate_args* a, int* status, cudaStream_t st);
 int gate_bwd_gemm_rope(const pom_gate_bwd_args* a, int* status, cudaStream_t st);
+// Token-causal forms (pom_gemm_causal.cu), reached when the `causal` member of the arguments is set.
+int ctx_gemm_causal(const pom_ctx_args* a, int* status, cudaStream_t st);
+int gate_gemm_causal(const pom_gate_args* a, int* status, cudaStream_t st);
+int gate_bwd_gemm_causal(const pom_gate_bwd_args* a, int* status, cudaStream_t st);
 
 }  // namespace pomh

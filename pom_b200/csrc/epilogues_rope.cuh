@@ -27,6 +27,7 @@ struct RopeEpi {
   int pos_stride;
   int len[2];
   int step[2];           // 0: the tokens of an aligned 32-token group share one position; 1: consecutive
+  int rotate;            // 0: no rotation at all (cos = 1, sin = 0; tables and positions are not read)
   // selections by ternary keep the kernel parameters out of local memory (no dynamically indexed arrays)
   __device__ __forceinline__ int step_of(int sec) const { return sec ? step[1] : step[0]; }
   __device__ __forceinline__ int len_of(int sec) const { return sec ? len[1] : len[0]; }
@@ -77,7 +78,7 @@ __device__ __forceinline__ void rope_stage(const RopeEpi& r, const EpiMaps& maps
     const int quarter = idx / kHalf, j = idx - quarter * kHalf;
     const int n = t.row0 + 32 * quarter, u = t.u0 + j;
     float c = 1.f, s = 0.f;
-    if (n < g.rows_per_batch && u < g.pair_q) {
+    if (r.rotate && n < g.rows_per_batch && u < g.pair_q) {
       long long p = __ldg(r.pos + static_cast<long long>(n) * r.pos_stride + which);
       p = p < 0 ? 0 : (p >= len ? len - 1 : p);  // the host validates positions; never read outside the table
       c = __ldg(cosp + p * g.pair_q + u);

@@ -240,28 +240,42 @@ struct TilePlan {
   int bn;
 };
 
-// Operand bytes pulled from L2 per output element are proportional to (rowsA + rowsB) / (128 * BN)
-// with rowsB = BN (one CTA) or BN/2 (pair); weigh that by the padded width and take the cheapest.
+// Tile plan by estimated time: (waves of work units over the SMs, or SM pairs) x (columns per tile) x a factor
+// per kernel flavour and width.  The factors are measured time per (wave x column) relative to the pair kernel at
+// 256 columns (32768..8192 x 1152 x 2304 and x 4608 products on B200): narrower tiles re-read the A operand more
+// often and pay more per column, but they divide a small problem into more units, which wins when the wide plan
+// would leave most SMs idle in its last wave (8192-row problems: 160 pair tiles = 2.2 waves of 74 clusters).
+inline double plan_factor(bool pair, int bn) {
+  if (pair) return bn == 256 ? 1.00 : bn == 192 ? 1.21 : 1.71;
+  return bn == 256 ? 1.02 : bn == 192 ? 1.17 : 1.53;
+}
+
 inline TilePlan pick_plan(const Operands& o, bool allow_192, bool splittable = false) {
-  const int mode = g_gemm_mode.load(std::memory_order_relaxed);
+  // diagnostic override (pom_set_gemm_mode): units digit 1 / 2 forces the one-CTA / pair kernel, tens digit
+  // 1 / 2 / 3 forces 128 / 192 / 256 columns per tile where that width exists for the operands
+  const int knob = g_gemm_mode.load(std::memory_order_relaxed);
+  const int mode = knob % 10;
+  const int force_bn = knob / 10 == 1 ? 128 : knob / 10 == 2 ? 192 : knob / 10 == 3 ? 256 : 0;
   const long long m_tiles = 1ll * o.batches * ceil_div(o.M, kBM);
   TilePlan best{false, 128};
   double best_cost = -1.0;
-  for (int pair = 0; pair < 2; ++pair) {
+  for (int pair = 1; pair >= 0; --pair) {
     if (mode == 1 && pair) continue;
     if (mode == 2 && !pair) continue;
-    if (mode == 0 && pair && m_tiles * ceil_div(o.N, 256) < sm_count()) continue;  // too little work to pair up
     const int cands[3] = {256, 192, 128};
     for (int bn : cands) {
-      if (bn == 192 && (!allow_192 || (pair && o.b_mn))) continue;
+      const bool has_192 = allow_192 && !(pair && o.b_mn);
+      if (bn == 192 && !has_192) continue;
       if (o.N <= 128 && bn != 128) continue;
-      const double padded = o.pair_q ? static_cast<double>(o.pair_sections * ceil_div(o.pair_q, bn / 2) * bn)
-                                     : static_cast<double>(ceil_div(o.N, bn) * bn);
-      double cost = padded * (128.0 + (pair ? bn / 2 : bn)) / bn;
-      // fewer work units than SMs (or SM pairs): the idle ones are paid for too (split-K GEMMs fill them)
-      const long long units = (pair ? (m_tiles + 1) / 2 : m_tiles) * static_cast<long long>(padded / bn);
+      if (force_bn && bn != force_bn && !(force_bn == 192 && !has_192)) continue;
+      const long long n_tiles = o.pair_q ? o.pair_sections * ceil_div(o.pair_q, bn / 2) : ceil_div(o.N, bn);
+      const long long units = (pair ? (m_tiles + 1) / 2 : m_tiles) * n_tiles;
       const int slots = pair ? sm_count() / 2 : sm_count();
-      if (!splittable && units < slots) cost *= static_cast<double>(slots) / static_cast<double>(units);
+      // split-K products fill the last wave with K slices (pick_split): their cost is the work itself (an odd row
+      // of tiles that leaves half a pair empty is not charged either: the split spreads it)
+      const double waves = splittable ? (pair ? 0.5 : 1.0) * static_cast<double>(m_tiles * n_tiles) / slots
+                                      : static_cast<double>(ceil_div(units, slots));
+      const double cost = waves * bn * plan_factor(pair != 0, bn);
       if (best_cost < 0 || cost < best_cost - 1e-9) {
         best_cost = cost;
         best = TilePlan{pair != 0, bn};

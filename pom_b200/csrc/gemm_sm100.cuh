@@ -128,6 +128,7 @@ struct alignas(64) EpiMaps {
   CUtensorMap out0;
   CUtensorMap out1;
   CUtensorMap in0;
+  CUtensorMap in1;
   // rotary epilogues: rows 0..31 of the {cos, sin} table of section 0 and of section 1 (fp32, 32 x 16 boxes)
   CUtensorMap lane[4];
 };

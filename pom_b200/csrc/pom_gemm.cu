@@ -131,7 +131,7 @@ int pom_gemm_bf16(const pom_gemm_args* a, int* status, void* stream) {
 }
 
 int pom_set_gemm_mode(int mode) {
-  if (mode < 0 || mode > 2) return POM_ERR_UNSUPPORTED;
+  if (mode < 0 || mode % 10 > 2 || mode / 10 > 3) return POM_ERR_UNSUPPORTED;
   g_gemm_mode.store(mode);
   return POM_OK;
 }
@@ -156,8 +156,9 @@ int pom_gemm_f32(const pom_gemm_args* a, void* stream) {
 }
 
 int pom_ctx_gemm(const pom_ctx_args* a, int* status, void* stream) {
-  if (!a || !a->coeff || !a->partial) return POM_ERR_NULL;
+  if (!a || !a->coeff || (!a->partial && !a->causal)) return POM_ERR_NULL;
   if (a->K < 1) return POM_ERR_BAD_SHAPE;
+  if (a->causal) return ctx_gemm_causal(a, status, static_cast<cudaStream_t>(stream));
   if (a->rope.kind != POM_ROPE_NONE) return ctx_gemm_rope(a, status, static_cast<cudaStream_t>(stream));
   Operands o{a->X, a->Wpo, a->N, a->P, a->D, a->ldx, a->ldw, a->B, false, false};
   o.tile_weight = a->row_weight ? a->tile_weight : nullptr;
@@ -178,7 +179,8 @@ int pom_ctx_gemm(const pom_ctx_args* a, int* status, void* stream) {
 }
 
 int pom_gate_gemm(const pom_gate_args* a, int* status, void* stream) {
-  if (!a || !a->bias || !a->H || !a->sh_out) return POM_ERR_NULL;
+  if (!a || !a->bias || (!a->H && !a->causal) || !a->sh_out) return POM_ERR_NULL;
+  if (a->causal) return gate_gemm_causal(a, status, static_cast<cudaStream_t>(stream));
   if (a->rope.kind != POM_ROPE_NONE) return gate_gemm_rope(a, status, static_cast<cudaStream_t>(stream));
   Operands o{a->X, a->Wse, a->T, a->P, a->D, a->ldx, a->ldw, a->B, false, false};
   int rc = check_operands(o);
@@ -199,7 +201,9 @@ int pom_gate_gemm(const pom_gate_args* a, int* status, void* stream) {
 }
 
 int pom_gate_bwd_gemm(const pom_gate_bwd_args* a, int* status, void* stream) {
-  if (!a || !a->bias || !a->H || !a->z || !a->g_out || !a->dh_partial || !a->db_partial) return POM_ERR_NULL;
+  if (!a || !a->bias || !a->z || !a->g_out || !a->db_partial) return POM_ERR_NULL;
+  if (a->causal) return gate_bwd_gemm_causal(a, status, static_cast<cudaStream_t>(stream));
+  if (!a->H || !a->dh_partial) return POM_ERR_NULL;
   if (a->rope.kind != POM_ROPE_NONE) return gate_bwd_gemm_rope(a, status, static_cast<cudaStream_t>(stream));
   // dSH[t, p] = sum_d dY[t, d] * Wo[d, p]: the B operand is Wo stored (K = D rows, N = P columns).
   Operands o{a->dY, a->Wo, a->T, a->P, a->D, a->ld_dy, a->ldw, a->B, false, true};

@@ -39,6 +39,7 @@ int make_rope(const pom_rope& r, const PairShape& ps, RopeEpi* e, EpiMaps* maps)
   e->sin[1] = ps.sections == 2 ? r.sin1 : r.sin0;
   e->pos = reinterpret_cast<const long long*>(r.pos);
   e->pos_stride = r.pos_stride;
+  e->rotate = 1;
   e->len[0] = r.len0, e->len[1] = ps.sections == 2 ? r.len1 : r.len0;
   e->step[0] = r.step0, e->step[1] = ps.sections == 2 ? r.step1 : r.step0;
   for (int s = 0; s < ps.sections; ++s) {

@@ -9,6 +9,7 @@
 // access is a coalesced 16-byte vector, several are in flight per thread, and every
 // sum is formed in a fixed order (deterministic, no float atomics).
 #include "common.cuh"
+#include "gemm_launch.cuh"
 #include "pom_math.cuh"
 #include "ptx_sm100.cuh"
 #include <cuda_bf16.h>
@@ -545,8 +546,9 @@ inline StreamPlan stream_plan(int B, int N, int P) {
 // PROD: a ninth warp does nothing but issue the copies (fastest, but 288 threads leave 112 registers per thread,
 // which the degree-3/4 variant would spill); otherwise warp 0 issues them between its own tiles.
 template <int KR, int VEC, bool PROD>
-__global__ void __launch_bounds__(kStCols / VEC * 8 + (PROD ? 32 : 0), 2) agg_bwd_stream_kernel(const AggBwdDev a, int tiles_per_cta, int splits,
-                                                                       int* status) {
+__global__ void __launch_bounds__(kStCols / VEC * 8 + (PROD ? 32 : 0), 2)
+agg_bwd_stream_kernel(const __grid_constant__ CUtensorMap tmx, const AggBwdDev a, int tiles_per_cta, int splits,
+                      int* status) {
   extern __shared__ __align__(128) uint8_t st_smem[];
   __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(st_smem);
   uint64_t* full = reinterpret_cast<uint64_t*>(st_smem + kStStages * kStTileBytes);
@@ -572,17 +574,16 @@ __global__ void __launch_bounds__(kStCols / VEC * 8 + (PROD ? 32 : 0), 2) agg_bw
   }
   __syncthreads();
 
-  const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(a.x) + static_cast<long long>(b) * a.N * a.ldx + p0;
   __nv_bfloat16* dxb = static_cast<__nv_bfloat16*>(a.dx) + static_cast<long long>(b) * a.N * a.ld_dx + p0;
-  auto issue = [&](int i) {  // producer warp, all lanes
+  // One tiled bulk load brings the whole 64-token x 256-channel tile (rows and channels past the end are
+  // zero-filled): per-row bulk copies were bound by the copy engine's per-request cost, not by bandwidth.
+  auto issue = [&](int i) {  // producer warp
     const int stage = i % kStStages;
-    const int n0 = (t_begin + i) * kStTok;
-    const int rows = min(kStTok, a.N - n0);
-    if (lane == 0) mbar_expect_tx(&full[stage], static_cast<uint32_t>(rows * width * 2));
+    if (lane == 0) {
+      mbar_expect_tx(&full[stage], static_cast<uint32_t>(kStTileBytes));
+      tma_load_3d(ring + stage * kStTok * kStCols, &tmx, &full[stage], p0, (t_begin + i) * kStTok, b);
+    }
     __syncwarp();
-    for (int r = lane; r < rows; r += 32)
-      bulk_load_row(ring + (stage * kStTok + r) * kStCols, xb + static_cast<long long>(n0 + r) * a.ldx,
-                    static_cast<uint32_t>(width * 2), &full[stage]);
   };
   const bool consumer = !PROD || warp < kConsumers / 32;
   if (PROD && !consumer) {
@@ -710,13 +711,22 @@ __global__ void __launch_bounds__(kStCols / VEC * 8 + (PROD ? 32 : 0), 2) agg_bw
 // The same stream with rotary embedding: a CTA owns up to 128 first channels of one section and their 128
 // rotation partners (two 256-byte bulk copies per token row: [first | partner]), a thread 4 first channels and
 // their 4 partners.  The gradient reaching token n is the transposed rotation of dH by that token's angle
-// (reference pom/pom_rope.py:171-180, 208-235; backward of pom_triton_rope.py:227-475); cos/sin rows are read
-// from the (L2-resident) tables, 16 bytes per thread and coalesced across the 32 threads of a row.
+// (reference pom/pom_rope.py:171-180, 208-235; backward of pom_triton_rope.py:227-475).
+//
+// No table row is read per token.  The positions of every aligned group of 32 tokens are constant or consecutive
+// (pom_rope::step0/1), so angle(token) = angle(group base) + lane * step * freq: a thread visits rows ty, ty + 8,
+// ... of each 64-token tile, i.e. four lane offsets that never change, whose cos/sin it keeps in registers for the
+// whole run; per tile it fetches the table rows of the two group bases (two 16-byte loads each) while the tile is
+// still landing, and combines both with the angle-addition formulas.
 constexpr int kStHalf = kStCols / 2;
 
-template <int KR, bool PROD>
-__global__ void __launch_bounds__(256 + (PROD ? 32 : 0), 2)
-agg_bwd_stream_rope_kernel(const AggBwdDev a, int tiles_per_cta, int splits, int q, int blocks_per_section,
+// CAUSAL (the fused token-causal layer): tiles are one 32-token group; beside hp the ring carries `suf`, the
+// running sums (up the group's rows) of the gradient of the prefix means written by the causal gate-backward
+// epilogue, and the gradient of token n's features is suf[n] + carry[group] instead of w[n]·dH.
+template <int KR, bool CAUSAL>
+__global__ void __launch_bounds__(256, 2)
+agg_bwd_stream_pair_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tms,
+                           const AggBwdDev a, int tiles_per_cta, int splits, int q, int blocks_per_section,
                            int* status) {
   extern __shared__ __align__(128) uint8_t st_smem[];
   __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(st_smem);
@@ -725,8 +735,11 @@ agg_bwd_stream_rope_kernel(const AggBwdDev a, int tiles_per_cta, int splits, int
   volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + kStStages);
   constexpr int VEC = 4;
   constexpr int kLanes = kStHalf / VEC;  // 32 threads across one row
-  constexpr int kGroups = 8;
+  constexpr int kGroups = 8;             // row groups of the CTA (not to be confused with 32-token groups)
   constexpr int kConsumers = kLanes * kGroups;
+  constexpr int TT = CAUSAL ? 32 : 64;   // tokens per tile
+  constexpr int kBox = TT * kStHalf;     // elements of one [TT x 128] box of the tile
+  static_assert(kStTileBytes == (CAUSAL ? 4 : 2) * kBox * 2, "ring stage must hold the tile's boxes");
   const int tid = threadIdx.x, tx = tid % kLanes, ty = tid / kLanes;
   const int warp = tid >> 5, lane = tid & 31;
   const int sec = blockIdx.x / blocks_per_section;
@@ -734,7 +747,7 @@ agg_bwd_stream_rope_kernel(const AggBwdDev a, int tiles_per_cta, int splits, int
   const int split = blockIdx.y, b = blockIdx.z;
   const int width = min(kStHalf, q - u0);  // pairs of this block (multiple of 8)
   const int p1_0 = sec * 2 * q + u0, p2_0 = p1_0 + q;
-  const int tiles_total = (a.N + kStTok - 1) / kStTok;
+  const int tiles_total = (a.N + TT - 1) / TT;
   const int t_begin = split * tiles_per_cta;
   const int my_tiles = min(tiles_total, t_begin + tiles_per_cta) - t_begin;
   if (tid == 0) {
@@ -747,41 +760,33 @@ agg_bwd_stream_rope_kernel(const AggBwdDev a, int tiles_per_cta, int splits, int
   }
   __syncthreads();
 
-  const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(a.x) + static_cast<long long>(b) * a.N * a.ldx;
   __nv_bfloat16* dxb = static_cast<__nv_bfloat16*>(a.dx) + static_cast<long long>(b) * a.N * a.ld_dx;
-  auto issue = [&](int i) {  // producer warp, all lanes
+  // tiled bulk loads per tile: [TT tokens x 128 first channels], [TT x 128 partners] (and the same two boxes of suf)
+  auto issue = [&](int i) {  // warp 0
     const int stage = i % kStStages;
-    const int n0 = (t_begin + i) * kStTok;
-    const int rows = min(kStTok, a.N - n0);
-    if (lane == 0) mbar_expect_tx(&full[stage], static_cast<uint32_t>(rows * width * 4));
+    if (lane == 0) {
+      __nv_bfloat16* dst = ring + stage * (kStTileBytes / 2);
+      const int n0 = (t_begin + i) * TT;
+      mbar_expect_tx(&full[stage], static_cast<uint32_t>(kStTileBytes));
+      tma_load_3d(dst, &tmx, &full[stage], p1_0, n0, b);
+      tma_load_3d(dst + kBox, &tmx, &full[stage], p2_0, n0, b);
+      if (CAUSAL) {
+        tma_load_3d(dst + 2 * kBox, &tms, &full[stage], p1_0, n0, b);
+        tma_load_3d(dst + 3 * kBox, &tms, &full[stage], p2_0, n0, b);
+      }
+    }
     __syncwarp();
-    for (int r = lane; r < rows; r += 32) {
-      __nv_bfloat16* dst = ring + (stage * kStTok + r) * kStCols;
-      const __nv_bfloat16* src = xb + static_cast<long long>(n0 + r) * a.ldx;
-      bulk_load_row(dst, src + p1_0, static_cast<uint32_t>(width * 2), &full[stage]);
-      bulk_load_row(dst + kStHalf, src + p2_0, static_cast<uint32_t>(width * 2), &full[stage]);
-    }
   };
-  const bool consumer = !PROD || warp < kConsumers / 32;
-  if (PROD && !consumer) {
-    for (int i = 0; i < my_tiles; ++i) {
-      if (i >= kStStages &&
-          !mbar_wait(&empty[i % kStStages], static_cast<uint32_t>(i / kStStages - 1) & 1u, abort_flag, status,
-                     kStatusStreamTimeout))
-        break;
-      issue(i);
-    }
-  }
-  if (!PROD && warp == 0)
+  if (warp == 0)
     for (int i = 0; i < kStStages - 1 && i < my_tiles; ++i) issue(i);
 
   const int c = tx * VEC;
-  const bool live = consumer && c < width;
+  const bool live = c < width;
   float cf1[VEC][KR], cf2[VEC][KR], g1[VEC], g2[VEC], dc1[VEC][KR], dc2[VEC][KR];
 #pragma unroll
   for (int e = 0; e < VEC; ++e) {
-    g1[e] = live ? a.dH[static_cast<long long>(b) * a.P + p1_0 + c + e] : 0.f;
-    g2[e] = live ? a.dH[static_cast<long long>(b) * a.P + p2_0 + c + e] : 0.f;
+    g1[e] = (live && !CAUSAL) ? a.dH[static_cast<long long>(b) * a.P + p1_0 + c + e] : 0.f;
+    g2[e] = (live && !CAUSAL) ? a.dH[static_cast<long long>(b) * a.P + p2_0 + c + e] : 0.f;
 #pragma unroll
     for (int k = 0; k < KR; ++k) {
       cf1[e][k] = (live && k < a.K) ? __ldg(a.coeff + static_cast<long long>(p1_0 + c + e) * a.K + k) : 0.f;
@@ -791,18 +796,35 @@ agg_bwd_stream_rope_kernel(const AggBwdDev a, int tiles_per_cta, int splits, int
     }
   }
   float wb = a.scale;
-  if (a.denom) {
+  if (!CAUSAL && a.denom) {
     const float dn = a.denom[b];
     wb = dn != 0.f ? wb / dn : 0.f;
   }
+  const bool rotate = a.rope.kind != POM_ROPE_NONE;
   const int which = a.rope.pos_stride == 2 ? sec : 0;
   const float* __restrict__ cos_t = (sec ? a.rope.cos1 : a.rope.cos0) + u0 + c;
   const float* __restrict__ sin_t = (sec ? a.rope.sin1 : a.rope.sin0) + u0 + c;
   const long long tab_len = sec ? a.rope.len1 : a.rope.len0;
+  const bool stepped = rotate && (sec ? a.rope.step1 : a.rope.step0) != 0;
+  // cos/sin of (lane offset * freq) for this thread's four lane offsets ty, ty + 8, ty + 16, ty + 24
+  float4 cl[4], sl[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    cl[j] = make_float4(1.f, 1.f, 1.f, 1.f);
+    sl[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (stepped && live) {
+      long long row = ty + 8 * j;
+      row = row >= tab_len ? tab_len - 1 : row;  // offsets past the table belong to tokens that do not exist
+      cl[j] = __ldg(reinterpret_cast<const float4*>(cos_t + row * q));
+      sl[j] = __ldg(reinterpret_cast<const float4*>(sin_t + row * q));
+    }
+  }
+  const int token_groups = (a.N + 31) / 32;
 
-  for (int i = 0; i < my_tiles && consumer; ++i) {
+  for (int i = 0; i < my_tiles; ++i) {
     const int stage = i % kStStages;
-    if (!PROD && warp == 0) {
+    if (warp == 0) {
+      // refill the stage of tile i-1 with tile i+S-1 once every warp has released it (no CTA-wide barrier)
       const int j = i + kStStages - 1;
       if (j < my_tiles) {
         if (j >= kStStages && !mbar_wait(&empty[j % kStStages], static_cast<uint32_t>(j / kStStages - 1) & 1u,
@@ -811,54 +833,76 @@ agg_bwd_stream_rope_kernel(const AggBwdDev a, int tiles_per_cta, int splits, int
         issue(j);
       }
     }
-    const int n0 = (t_begin + i) * kStTok;
-    const int rows = min(kStTok, a.N - n0);
-    // this thread's rows of the tile are n0 + ty + 8 k, handled four at a time: the table rows of a batch are
-    // requested before its tokens are touched (for the first batch, while the tile is still landing)
-    constexpr int kBatch = 2;
-    bool ok = true;
-#pragma unroll 1
-    for (int k0 = 0; k0 < kStTok / kGroups && ok; k0 += kBatch) {
-      float4 cs[kBatch], sn[kBatch];
-      if (live) {
+    const int n0 = (t_begin + i) * TT;
+    const int rows = min(TT, a.N - n0);
+    // table rows of the base positions of the tile's 32-token groups (and, causal, the group's carry), requested
+    // while the tile is landing
+    float4 c0[TT / 32], s0[TT / 32], kb1, kb2;
+    kb1 = kb2 = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int k = 0; k < kBatch; ++k) {
-          const int n = min(n0 + ty + kGroups * (k0 + k), a.N - 1);
-          long long idx = __ldg(a.rope.pos + static_cast<long long>(n) * a.rope.pos_stride + which);
-          if (tab_len > 0) idx = idx < 0 ? 0 : (idx >= tab_len ? tab_len - 1 : idx);
-          cs[k] = __ldg(reinterpret_cast<const float4*>(cos_t + idx * q));
-          sn[k] = __ldg(reinterpret_cast<const float4*>(sin_t + idx * q));
-        }
+    for (int g = 0; g < TT / 32; ++g) {
+      c0[g] = make_float4(1.f, 1.f, 1.f, 1.f);
+      s0[g] = make_float4(0.f, 0.f, 0.f, 0.f);
+      const int n = n0 + 32 * g;
+      if (rotate && live && n < a.N) {
+        long long idx = __ldg(a.rope.pos + static_cast<long long>(n) * a.rope.pos_stride + which);
+        idx = idx < 0 ? 0 : (idx >= tab_len ? tab_len - 1 : idx);
+        c0[g] = __ldg(reinterpret_cast<const float4*>(cos_t + idx * q));
+        s0[g] = __ldg(reinterpret_cast<const float4*>(sin_t + idx * q));
       }
-      if (k0 == 0)
-        ok = mbar_wait(&full[stage], static_cast<uint32_t>(i / kStStages) & 1u, abort_flag, status, kStatusStreamTimeout);
-      if (!ok || !live) continue;
+    }
+    if (CAUSAL && live) {
+      const float* kb = a.partial + (static_cast<long long>(b) * token_groups + (t_begin + i)) * a.P;
+      kb1 = __ldg(reinterpret_cast<const float4*>(kb + p1_0 + c));
+      kb2 = __ldg(reinterpret_cast<const float4*>(kb + p2_0 + c));
+    }
+    if (!mbar_wait(&full[stage], static_cast<uint32_t>(i / kStStages) & 1u, abort_flag, status, kStatusStreamTimeout))
+      break;
+    if (live) {
+      const __nv_bfloat16* tile = ring + stage * (kStTileBytes / 2);
 #pragma unroll
-      for (int k = 0; k < kBatch; ++k) {
-        const int r = ty + kGroups * (k0 + k);
+      for (int k = 0; k < TT / kGroups; ++k) {
+        const int r = ty + kGroups * k;
         if (r >= rows) break;
         const int n = n0 + r;
-        float x1[VEC], x2[VEC], o1[VEC], o2[VEC];
+        const int g = k >> 2, j = k & 3;
+        float x1[VEC], x2[VEC], o1[VEC], o2[VEC], gg1[VEC], gg2[VEC];
         {
-          const __nv_bfloat16* src = ring + (stage * kStTok + r) * kStCols + c;
+          const __nv_bfloat16* src = tile + r * kStHalf + c;
           const uint2 qa = *reinterpret_cast<const uint2*>(src);
-          const uint2 qb = *reinterpret_cast<const uint2*>(src + kStHalf);
+          const uint2 qb = *reinterpret_cast<const uint2*>(src + kBox);
           x1[0] = __uint_as_float(qa.x << 16), x1[1] = __uint_as_float(qa.x & 0xffff0000u);
           x1[2] = __uint_as_float(qa.y << 16), x1[3] = __uint_as_float(qa.y & 0xffff0000u);
           x2[0] = __uint_as_float(qb.x << 16), x2[1] = __uint_as_float(qb.x & 0xffff0000u);
           x2[2] = __uint_as_float(qb.y << 16), x2[3] = __uint_as_float(qb.y & 0xffff0000u);
-        }
-        const float w = a.row_weight ? wb * __ldg(a.row_weight + static_cast<long long>(b) * a.N + n) : wb;
-        if (w == 0.f) {  // a token of weight zero: its saved projection may never have been written
+          if (CAUSAL) {
+            const uint2 sa = *reinterpret_cast<const uint2*>(src + 2 * kBox);
+            const uint2 sb = *reinterpret_cast<const uint2*>(src + 3 * kBox);
+            gg1[0] = __uint_as_float(sa.x << 16) + kb1.x, gg1[1] = __uint_as_float(sa.x & 0xffff0000u) + kb1.y;
+            gg1[2] = __uint_as_float(sa.y << 16) + kb1.z, gg1[3] = __uint_as_float(sa.y & 0xffff0000u) + kb1.w;
+            gg2[0] = __uint_as_float(sb.x << 16) + kb2.x, gg2[1] = __uint_as_float(sb.x & 0xffff0000u) + kb2.y;
+            gg2[2] = __uint_as_float(sb.y << 16) + kb2.z, gg2[3] = __uint_as_float(sb.y & 0xffff0000u) + kb2.w;
+          } else {
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) x1[e] = 0.f, x2[e] = 0.f;
+            for (int e = 0; e < VEC; ++e) gg1[e] = g1[e], gg2[e] = g2[e];
+          }
         }
-        const float cc[4] = {cs[k].x, cs[k].y, cs[k].z, cs[k].w};
-        const float ss[4] = {sn[k].x, sn[k].y, sn[k].z, sn[k].w};
+        float w = 1.f;
+        if (!CAUSAL) {
+          w = a.row_weight ? wb * __ldg(a.row_weight + static_cast<long long>(b) * a.N + n) : wb;
+          if (w == 0.f) {  // a token of weight zero: its saved projection may never have been written
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) x1[e] = 0.f, x2[e] = 0.f;
+          }
+        }
+        const float C0[4] = {c0[g].x, c0[g].y, c0[g].z, c0[g].w}, S0[4] = {s0[g].x, s0[g].y, s0[g].z, s0[g].w};
+        const float CL[4] = {cl[j].x, cl[j].y, cl[j].z, cl[j].w}, SL[4] = {sl[j].x, sl[j].y, sl[j].z, sl[j].w};
 #pragma unroll
         for (int e = 0; e < VEC; ++e) {
-          const float d1 = w * (g1[e] * cc[e] + g2[e] * ss[e]);
-          const float d2 = w * (g2[e] * cc[e] - g1[e] * ss[e]);
+          const float cc = C0[e] * CL[e] - S0[e] * SL[e];
+          const float ss = S0[e] * CL[e] + C0[e] * SL[e];
+          const float d1 = w * (gg1[e] * cc + gg2[e] * ss);
+          const float d2 = w * (gg2[e] * cc - gg1[e] * ss);
           const float av = pom_act(x1[e]), bv = pom_act(x2[e]);
           o1[e] = d1 * poly_grad_reg<KR>(av, cf1[e]) * pom_act_grad(x1[e]);
           o2[e] = d2 * poly_grad_reg<KR>(bv, cf2[e]) * pom_act_grad(x2[e]);
@@ -876,14 +920,14 @@ agg_bwd_stream_rope_kernel(const AggBwdDev a, int tiles_per_cta, int splits, int
         *reinterpret_cast<uint2*>(dst + p2_0 + c) = make_uint2(pack_bf16x2(o2[0], o2[1]), pack_bf16x2(o2[2], o2[3]));
       }
     }
-    if (!ok) break;
     __syncwarp();
-    if (lane == 0) mbar_arrive(&empty[stage]);
+    if (lane == 0) mbar_arrive(&empty[stage]);  // this warp is done reading the stage
   }
+  // every bulk copy issued above has been waited for: the ring is free to hold the coefficient sums
   __syncthreads();
-  if (*abort_flag) return;
+  if (*abort_flag) return;  // a wait expired (status word set): leave the outputs incomplete rather than wrong
   float* red = reinterpret_cast<float*>(st_smem);  // [row group 1..7][value][thread of the row]
-  if (ty > 0 && consumer) {
+  if (ty > 0) {
 #pragma unroll
     for (int e = 0; e < VEC; ++e)
 #pragma unroll
@@ -919,10 +963,12 @@ struct StreamPairs {
 inline StreamPairs stream_pairs(const pom_agg_bwd_args* a) {
   if (a->rope.kind == POM_ROPE_1D) return StreamPairs{1, a->P / 2};
   if (a->rope.kind == POM_ROPE_2D) return StreamPairs{2, a->P / 4};
+  if (a->causal == 3) return StreamPairs{1, a->P / 2};  // no rotation: first half | second half
   return StreamPairs{0, 0};
 }
-inline StreamPlan stream_plan_rope(int B, int N, const StreamPairs& sp) {
+inline StreamPlan stream_plan_rope(int B, int N, const StreamPairs& sp, int tile_tokens = kStTok) {
   StreamPlan s = stream_plan(B, N, 1);
+  s.tiles = static_cast<int>(ceil_div(N, tile_tokens));
   s.col_blocks = sp.sections * static_cast<int>(ceil_div(sp.q, kStHalf));
   const long long pairs = static_cast<long long>(s.col_blocks) * B;
   long long want = ceil_div(4LL * sm_count(), pairs);
@@ -934,14 +980,32 @@ inline StreamPlan stream_plan_rope(int B, int N, const StreamPairs& sp) {
 }
 
 bool stream_bwd_rope_eligible(const pom_agg_bwd_args* a) {
-  if (a->dtype != POM_BF16 || a->causal != 0 || a->K > 4) return false;
+  // non-causal degrees 3 and 4 would spill the paired register state: they take the chunked kernel (the fused
+  // token-causal form, causal == 3, has no other kernel and accepts the spills)
+  if (a->dtype != POM_BF16 || (a->causal != 0 && a->causal != 3) || a->K > (a->causal == 3 ? 4 : 2)) return false;
   const StreamPairs sp = stream_pairs(a);
   if (sp.sections == 0 || sp.q % 8 || sp.q * 2 * sp.sections != a->P) return false;
+  if (a->causal == 3 && (!a->dout || !a->partial || a->ld_dout % 8 || !aligned16(a->dout))) return false;
+  if (a->rope.kind == POM_ROPE_NONE)
+    return a->ldx % 8 == 0 && a->ld_dx % 8 == 0 && aligned16(a->x) && aligned16(a->dx);
+  if (a->rope.pos_stride != sp.sections || a->rope.len0 < 1 || (sp.sections == 2 && a->rope.len1 < 1)) return false;
+  if ((a->rope.step0 != 0 && a->rope.step0 != 1) || (sp.sections == 2 && a->rope.step1 != 0 && a->rope.step1 != 1))
+    return false;  // arbitrary positions: the chunked kernel reads a table row per token
   if (a->ldx % 8 || a->ld_dx % 8 || !aligned16(a->x) || !aligned16(a->dx)) return false;
   for (const void* t : {static_cast<const void*>(a->rope.cos0), static_cast<const void*>(a->rope.sin0),
                         static_cast<const void*>(a->rope.cos1), static_cast<const void*>(a->rope.sin1)})
     if (t && !aligned16(t)) return false;
   return true;
+}
+
+// (channels, tokens, samples) view of a bf16 activation for tiled bulk loads of box_cols x box_rows tiles
+// (row-major in shared memory, no swizzle).
+int stream_tile_map(CUtensorMap* m, const void* base, int64_t P, int64_t N, int64_t B, int64_t ld, int box_cols,
+                    int box_rows) {
+  uint64_t dims[3] = {static_cast<uint64_t>(P), static_cast<uint64_t>(N), static_cast<uint64_t>(B)};
+  uint64_t str[2] = {static_cast<uint64_t>(ld), static_cast<uint64_t>(ld) * static_cast<uint64_t>(N)};
+  uint32_t box[3] = {static_cast<uint32_t>(box_cols), static_cast<uint32_t>(box_rows), 1};
+  return make_map(m, base, 3, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
 bool stream_bwd_eligible(const pom_agg_bwd_args* a) {
@@ -1493,7 +1557,8 @@ int pom_poly_agg_mean_noalloc(const pom_agg_args* a, const float* denom, float s
 int32_t pom_poly_agg_bwd_slots(const pom_agg_bwd_args* a) {
   if (!a || a->B <= 0 || a->N <= 0 || a->P <= 0) return 0;
   if (stream_bwd_eligible(a)) return a->B * stream_plan(a->B, a->N, a->P).splits;
-  if (stream_bwd_rope_eligible(a)) return a->B * stream_plan_rope(a->B, a->N, stream_pairs(a)).splits;
+  if (stream_bwd_rope_eligible(a))
+    return a->B * stream_plan_rope(a->B, a->N, stream_pairs(a), a->causal == 3 ? 32 : kStTok).splits;
   return a->B * pom_agg_chunks(a->N);
 }
 
@@ -1515,8 +1580,8 @@ int pom_poly_agg_bwd(const pom_agg_bwd_args* a, void* stream) {
   if (a->B > 65535 || pom_agg_chunks(a->N) > 65535) return POM_ERR_TOO_LARGE;
   if (a->dtype != POM_BF16 && a->dtype != POM_F32) return POM_ERR_UNSUPPORTED;
   if (a->ldx < a->P || a->ld_dx < a->P) return POM_ERR_BAD_STRIDE;
-  if (a->causal < 0 || a->causal > 2) return POM_ERR_UNSUPPORTED;
-  if (a->causal ? (!a->dout || (!a->partial && a->causal == 1) || a->ld_dout < a->P) : !a->dH) return POM_ERR_NULL;
+  if (a->causal < 0 || a->causal > 3) return POM_ERR_UNSUPPORTED;
+  if (a->causal ? (!a->dout || (!a->partial && a->causal != 2) || a->ld_dout < a->P) : !a->dH) return POM_ERR_NULL;
   int rc = check_rope(a->rope, a->P);
   if (rc) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -1557,11 +1622,13 @@ int pom_poly_agg_bwd(const pom_agg_bwd_args* a, void* stream) {
                            kStSmemBytes);
     });
     constexpr int threads = kStCols / kStVec * 8;
+    CUtensorMap tmx;
+    if ((rc = stream_tile_map(&tmx, a->x, a->P, a->N, a->B, a->ldx, kStCols, kStTok))) return rc;
     if (a->K <= 2)
-      agg_bwd_stream_kernel<2, kStVec, true><<<sgrid, threads + 32, kStSmemBytes, st>>>(d, sp.tiles_per_cta, sp.splits,
-                                                                                        status);
+      agg_bwd_stream_kernel<2, kStVec, true><<<sgrid, threads + 32, kStSmemBytes, st>>>(tmx, d, sp.tiles_per_cta,
+                                                                                        sp.splits, status);
     else
-      agg_bwd_stream_kernel<4, kStVec, false><<<sgrid, threads, kStSmemBytes, st>>>(d, sp.tiles_per_cta, sp.splits,
+      agg_bwd_stream_kernel<4, kStVec, false><<<sgrid, threads, kStSmemBytes, st>>>(tmx, d, sp.tiles_per_cta, sp.splits,
                                                                                     status);
     count_launch();
     return check_launch();
@@ -1569,29 +1636,37 @@ int pom_poly_agg_bwd(const pom_agg_bwd_args* a, void* stream) {
   if (stream_bwd_rope_eligible(a)) {
     int* status = ops_status_ptr();
     if (!status) return POM_ERR_CUDA;
+    const bool fused_causal = a->causal == 3;
+    const int tt = fused_causal ? 32 : kStTok;
     const StreamPairs pr = stream_pairs(a);
-    const StreamPlan sp = stream_plan_rope(a->B, a->N, pr);
+    const StreamPlan sp = stream_plan_rope(a->B, a->N, pr, tt);
     if (sp.splits > 65535) return POM_ERR_TOO_LARGE;
     const dim3 sgrid(static_cast<unsigned>(sp.col_blocks), static_cast<unsigned>(sp.splits),
                      static_cast<unsigned>(a->B));
     static std::once_flag attr_once_rope;
     std::call_once(attr_once_rope, [] {
-      cudaFuncSetAttribute(agg_bwd_stream_rope_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           kStSmemBytes);
-      cudaFuncSetAttribute(agg_bwd_stream_rope_kernel<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           kStSmemBytes);
+      cudaFuncSetAttribute(agg_bwd_stream_pair_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStSmemBytes);
+      cudaFuncSetAttribute(agg_bwd_stream_pair_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStSmemBytes);
+      cudaFuncSetAttribute(agg_bwd_stream_pair_kernel<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStSmemBytes);
     });
     const int bps = sp.col_blocks / pr.sections;
-    // (a copy-only ninth warp would cap the kernel at 96 registers per thread, which the paired state spills)
-    if (a->K <= 2)
-      agg_bwd_stream_rope_kernel<2, false><<<sgrid, 256, kStSmemBytes, st>>>(d, sp.tiles_per_cta, sp.splits, pr.q, bps,
-                                                                           status);
+    CUtensorMap tmx, tms;
+    if ((rc = stream_tile_map(&tmx, a->x, a->P, a->N, a->B, a->ldx, kStHalf, tt))) return rc;
+    tms = tmx;
+    if (fused_causal && (rc = stream_tile_map(&tms, a->dout, a->P, a->N, a->B, a->ld_dout, kStHalf, tt))) return rc;
+    if (!fused_causal)
+      agg_bwd_stream_pair_kernel<2, false><<<sgrid, 256, kStSmemBytes, st>>>(tmx, tms, d, sp.tiles_per_cta, sp.splits,
+                                                                            pr.q, bps, status);
+    else if (a->K <= 2)
+      agg_bwd_stream_pair_kernel<2, true><<<sgrid, 256, kStSmemBytes, st>>>(tmx, tms, d, sp.tiles_per_cta, sp.splits,
+                                                                           pr.q, bps, status);
     else
-      agg_bwd_stream_rope_kernel<4, false><<<sgrid, 256, kStSmemBytes, st>>>(d, sp.tiles_per_cta, sp.splits, pr.q, bps,
-                                                                           status);
+      agg_bwd_stream_pair_kernel<4, true><<<sgrid, 256, kStSmemBytes, st>>>(tmx, tms, d, sp.tiles_per_cta, sp.splits,
+                                                                           pr.q, bps, status);
     count_launch();
     return check_launch();
   }
+  if (a->causal == 3) return POM_ERR_UNSUPPORTED;  // the fused token-causal form exists only as the paired stream
   const int vec = pick_vec(a->P, a->rope, a->dtype, a->K, {a->ldx, a->ld_dx, a->causal ? a->ld_dout : 0},
                            {a->x, a->dx, a->causal ? a->dout : nullptr});
   const WalkLaunch wl = walk_launch(a->P, a->rope.kind, vec, d.chunks, a->B);

@@ -9,7 +9,7 @@
 //                               slice r from all ranks (peer loads) and writes the result to all ranks.
 //
 // Synchronisation is by epoch flags in the buffer header, written with st.release.sys after a system fence and
-// polled with ld.acquire.sys under a 2 s limit; the epoch counters live in device memory so a replayed graph
+// polled with ld.acquire.sys under a time limit (pom_peer_comm::wait_ns, 2 s by default); the epoch counters live in device memory so a replayed graph
 // advances them.  A wait that expires records POM_ERR_TIMEOUT in the status word and the kernel carries on (its
 // result is then meaningless, which the host sees from the status word); later kernels skip their waits.
 // No TMA and no multicast instruction touches peer memory here.
@@ -26,7 +26,7 @@ constexpr int kMaxRanks = POM_PEER_MAX_RANKS;
 constexpr int kFlatCtas = POM_PEER_FLAT_CTAS;
 constexpr int kFlatThreads = 512;
 constexpr int kXchgThreads = 1024;
-constexpr unsigned long long kWaitNs = 2000000000ull;
+constexpr unsigned long long kDefaultWaitNs = 2000000000ull;  // pom_peer_comm::wait_ns == 0
 
 // Header at the start of every rank's exchange buffer (POM_PEER_HEADER_BYTES reserved).
 struct PeerHeader {
@@ -44,6 +44,7 @@ struct PeerDev {
   char* base[kMaxRanks];
   int rank, world;
   unsigned long long slot_floats, slots_off, flat_off;
+  unsigned long long wait_ns;  // limit of every wait on another rank
 };
 
 __device__ __forceinline__ PeerHeader* header(const PeerDev& c, int r) {
@@ -86,14 +87,14 @@ __device__ __forceinline__ unsigned long long now_ns() {
 }
 
 // Poll until *flag has reached `epoch` (wrap-safe) or the limit passes; false on expiry.
-__device__ __forceinline__ bool wait_flag(const unsigned* flag, unsigned epoch, bool skip) {
+__device__ __forceinline__ bool wait_flag(const unsigned* flag, unsigned epoch, bool skip, unsigned long long limit_ns) {
   if (static_cast<int>(ld_acquire_sys(flag) - epoch) >= 0) return true;
   if (skip) return false;
   const unsigned long long t0 = now_ns();
   for (;;) {
     for (int i = 0; i < 64; ++i)
       if (static_cast<int>(ld_acquire_sys(flag) - epoch) >= 0) return true;
-    if (now_ns() - t0 > kWaitNs) return false;
+    if (now_ns() - t0 > limit_ns) return false;
     __nanosleep(100);
   }
 }
@@ -139,7 +140,7 @@ __global__ void __launch_bounds__(kXchgThreads) peer_exchange_kernel(PeerDev c, 
   __threadfence_system();
   __syncthreads();
   if (tid < c.world) st_release_sys(&header(c, tid)->flag_small[parity][c.rank], epoch);
-  if (tid < c.world && !wait_flag(&mine->flag_small[parity][tid], epoch, poisoned)) s_fail = 1;
+  if (tid < c.world && !wait_flag(&mine->flag_small[parity][tid], epoch, poisoned, c.wait_ns)) s_fail = 1;
   __syncthreads();
   if (s_fail && tid == 0 && !poisoned) atomicCAS(status, 0, POM_ERR_TIMEOUT);
 
@@ -171,7 +172,7 @@ __global__ void __launch_bounds__(kFlatThreads) peer_allreduce_flat_kernel(PeerD
 
   // every rank's gradients are complete once its kernel has started (stream order)
   if (tid < c.world) st_release_sys(&header(c, tid)->flag_start[c.rank][cta], epoch);
-  if (tid < c.world && !wait_flag(&mine->flag_start[tid][cta], epoch, poisoned)) s_fail = 1;
+  if (tid < c.world && !wait_flag(&mine->flag_start[tid][cta], epoch, poisoned, c.wait_ns)) s_fail = 1;
   __syncthreads();
 
   const unsigned long long per = (n4 + c.world - 1) / c.world;
@@ -205,7 +206,7 @@ __global__ void __launch_bounds__(kFlatThreads) peer_allreduce_flat_kernel(PeerD
   __threadfence_system();
   __syncthreads();
   if (tid < c.world) st_release_sys(&header(c, tid)->flag_done[c.rank][cta], epoch);
-  if (tid < c.world && !wait_flag(&mine->flag_done[tid][cta], epoch, poisoned || s_fail)) s_fail = 1;
+  if (tid < c.world && !wait_flag(&mine->flag_done[tid][cta], epoch, poisoned || s_fail, c.wait_ns)) s_fail = 1;
   __syncthreads();
   if (s_fail && tid == 0 && !poisoned) atomicCAS(status, 0, POM_ERR_TIMEOUT);
 }
@@ -225,6 +226,7 @@ int to_dev(const pom_peer_comm* c, PeerDev* d) {
   d->slot_floats = c->slot_floats;
   d->slots_off = lay[0];
   d->flat_off = lay[1];
+  d->wait_ns = c->wait_ns ? c->wait_ns : kDefaultWaitNs;
   return POM_OK;
 }
 

@@ -19,6 +19,7 @@ by a local exclusive scan for the causal mask, and the mirrored exchanges in bac
 """
 from __future__ import annotations
 
+import weakref
 from dataclasses import dataclass
 from typing import Any, Optional, Tuple, Union
 
@@ -143,6 +144,30 @@ def _f32(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
     return ops.to_f32(t)
 
 
+_derived = {}
+
+
+def _derived_of(t: torch.Tensor, what: str, make):
+    """Value derived from tensor ``t`` (an fp32 copy of a small bf16 parameter, a transposed weight), remade only
+    when ``t`` changes: keyed on the tensor object and its version counter, so an optimizer step invalidates it."""
+    key = (id(t), what)
+    ent = _derived.get(key)
+    if ent is not None and ent[0]() is t and ent[1] == t._version:
+        return ent[2]
+    if len(_derived) > 256:
+        for k in [k for k, e in _derived.items() if e[0]() is None]:
+            del _derived[k]
+    val = make(t)
+    _derived[key] = (weakref.ref(t), t._version, val)
+    return val
+
+
+def _f32_cached(t: torch.Tensor) -> torch.Tensor:
+    if t.dtype == torch.float32:
+        return t.contiguous()
+    return _derived_of(t, "f32", lambda x: ops.to_f32(x.contiguous()))
+
+
 def _like_param(g: torch.Tensor, p: torch.Tensor) -> torch.Tensor:
     if p.dtype == torch.float32:
         return g
@@ -192,7 +217,7 @@ class _PoMLayer(torch.autograd.Function):
         w_qc = w_qc.contiguous()
         w_ag = w_ag.contiguous()
         w_po, w_se = w_qc[:P], w_qc[P:]
-        coeff32, bias32 = _f32(coeff.contiguous()), _f32(se_bias.contiguous())
+        coeff32, bias32 = _f32_cached(coeff), _f32_cached(se_bias)
         need_grad = any(ctx.needs_input_grad[:6]) or (h_past is not None and ctx.needs_input_grad[7])
         shard = spec.shard
         n_glob = shard.n_global if shard is not None else N
@@ -222,10 +247,16 @@ class _PoMLayer(torch.autograd.Function):
         rope_ok = K <= 4 and all(r is None or r.fusable(P) for r in (spec.rope_ctx, spec.rope_qry))
         fused = (bf16 and not heads and (not rotary or rope_ok) and not causal and not full
                  and P % 8 == 0 and D % 8 == 0)
+        # token-causal: the prefix means ride in the same epilogues (running sums per 32-token group + a scan over
+        # the groups), with or without rotation
+        two_d = any(r is not None and r.kind == _abi.ROPE_2D for r in (spec.rope_ctx, spec.rope_qry))
+        fused_causal = (causal and bf16 and not heads and (not rotary or rope_ok) and K <= 4 and D % 8 == 0
+                        and P % (32 if two_d else 16) == 0)
 
         hp = z = Hc = s32 = None
         collapsed = False
         ctx.collapsed = False
+        ctx.fused_causal = fused_causal
         ctx.composite = fused and shard is None and WHOLE_LAYER_CALLS and not rotary
         if ctx.composite:
             # the whole fused layer is one library call (no exchange to put between its phases)
@@ -248,7 +279,14 @@ class _PoMLayer(torch.autograd.Function):
             ctx.param_like = (w_qc, se_bias, coeff, w_ag)
             return (y, H.view(B, 1, P)) if spec.want_state else (y, None)
         # ---------------------------------------------------------------- context phase
-        if fused:
+        if fused_causal:
+            carry, hp, Hc = ops.ctx_gemm(xc, w_po, coeff32, save_hp=need_grad, rope=spec.rope_ctx, causal=True)
+            carry_in = None
+            if shard is not None:  # totals of the ranks before this one
+                carry_in = shard.exclusive_carry(ops.reduce_partials(carry))
+            ops.group_scan(carry, carry_in)          # group totals -> exclusive carries, in place
+            H = carry                                # saved in the slot of the aggregate; Hc holds `pre`
+        elif fused:
             partial, hp = ops.ctx_gemm(xc, w_po, coeff32, row_weight=maskf, save_hp=need_grad,
                                        tile_weight=None if maskf is None else ops.tile_weights(maskf),
                                        rope=spec.rope_ctx)
@@ -262,7 +300,9 @@ class _PoMLayer(torch.autograd.Function):
                 z = ops.gemm(xq.view(B * T, D), w_se).view(B, T, S)
             if not causal and not full:
                 S_part = ops.poly_agg_fwd(hp, coeff32, row_weight=maskf, rope=spec.rope_ctx)  # per-chunk sums
-        if causal:
+        if fused_causal:
+            pass
+        elif causal:
             carry = None
             if shard is not None:
                 S_loc = ops.reduce_partials(ops.poly_agg_fwd(hp, coeff32, rope=spec.rope_ctx))
@@ -291,7 +331,10 @@ class _PoMLayer(torch.autograd.Function):
                 H = ops.state_merge(_f32(h_past.reshape(B, P).contiguous()), H, spec.n_past)
 
         # ---------------------------------------------------------------- query phase
-        if fused:
+        if fused_causal:
+            sh, z = ops.gate_gemm(xq, w_se, bias32, None, save_z=need_grad, rope=spec.rope_qry,
+                                  causal=(Hc, H, offset))
+        elif fused:
             sh, z = ops.gate_gemm(xq, w_se, bias32, H, save_z=need_grad, rope=spec.rope_qry)
         elif heads:
             ones = _ones(B, heads, xq.device)
@@ -387,9 +430,27 @@ class _PoMLayer(torch.autograd.Function):
             g_z = torch.empty((B * T, S), dtype=dt, device=dev)
 
         # ---------------------------------------------------------------- query phase backward
-        if ctx.fused:
-            dh_p, db_p = ops.gate_bwd_gemm(dy, w_ag, bias32, H, z, g_z, rope=spec.rope_qry)
-            dH = ops.reduce_partials(dh_p)
+        dH_reduced = False  # True once dH already holds the sum over all ranks
+        suf = carry_b = None
+        if ctx.fused_causal:
+            w_t = _derived_of(p_ag, "transposed", lambda w: ops.transpose_bf16(w.contiguous()))
+            db_p, suf, carry_b = ops.gate_bwd_gemm(dy, w_ag, bias32, None, z, g_z, rope=spec.rope_qry, w_o_t=w_t,
+                                                   causal=(Hc, H, offset))
+            ops.reduce_partials(db_p.view(1, -1, P), out=d_bias.view(1, P))
+            carry_in = None
+            if shard is not None:  # totals of the ranks after this one
+                carry_in = shard.exclusive_carry(ops.reduce_partials(carry_b), reverse=True)
+            ops.group_scan(carry_b, carry_in, reverse=True)
+        elif ctx.fused:
+            w_t = None
+            if spec.rope_qry is not None:  # the rotary form reads the output weight transposed: (P, D)
+                w_t = _derived_of(p_ag, "transposed", lambda w: ops.transpose_bf16(w.contiguous()))
+            dh_p, db_p = ops.gate_bwd_gemm(dy, w_ag, bias32, H, z, g_z, rope=spec.rope_qry, w_o_t=w_t)
+            if shard is not None and dh_state is None and spec.frames == 1:
+                dH = shard.sum_partials(dh_p)  # chunk sums, cross-rank sum and hand-back in one exchange
+                dH_reduced = True
+            else:
+                dH = ops.reduce_partials(dh_p)
             ops.reduce_partials(db_p.view(1, -1, P), out=d_bias.view(1, P))
         elif ctx.collapsed:
             ds32, dMb = ops.heads_out_bwd(dy, s32, sh)          # sh holds Mb here
@@ -411,7 +472,10 @@ class _PoMLayer(torch.autograd.Function):
 
         # ---------------------------------------------------------------- context phase backward
         d_hpast = None
-        if causal:
+        if ctx.fused_causal:
+            ops.poly_agg_bwd(hp, coeff32, dx_out=g_hp.view(B, N, P), rope=spec.rope_ctx, fused_causal=(suf, carry_b),
+                             dcoeff_out=d_coeff)
+        elif causal:
             carry = None
             if shard is not None:
                 _, tot = ops.poly_agg_bwd(hp, coeff32, dx_out=g_hp.view(B, N, P), dout=dH, causal=True,
@@ -432,7 +496,7 @@ class _PoMLayer(torch.autograd.Function):
         else:
             if dh_state is not None:
                 dH = ops.reduce_partials(torch.stack([dH, _f32(dh_state.reshape(B, P).contiguous())], dim=1))
-            if shard is not None:
+            if shard is not None and not dH_reduced:
                 shard.all_reduce(dH)
             if spec.frames > 1:
                 dH = ops.frame_prefix_mean(dH.contiguous(), spec.frames, adjoint=True)

@@ -268,18 +268,35 @@ def tile_weights(mask: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def token_groups(n: int) -> int:
+    """Aligned groups of 32 tokens in a sequence of n tokens (the granularity of the fused token-causal path)."""
+    return (n + 31) // 32
+
+
 def ctx_gemm(x: torch.Tensor, w_po: torch.Tensor, coeff: torch.Tensor, *, row_weight: Optional[torch.Tensor] = None,
-             save_hp: bool = True, tile_weight: Optional[torch.Tensor] = None, rope: Optional[RopeSpec] = None):
+             save_hp: bool = True, tile_weight: Optional[torch.Tensor] = None, rope: Optional[RopeSpec] = None,
+             causal: bool = False):
     """Context phase: returns (partial (B, MT, P) fp32, hp (B, N, P) bf16 or None).  With ``tile_weight``
     (from :func:`tile_weights`) tiles that the mask empties are skipped and their rows of hp stay unwritten.
-    ``rope`` (fusable, degree <= 4): the polynomial features are rotated by the token positions before the sum."""
+    ``rope`` (fusable, degree <= 4): the polynomial features are rotated by the token positions before the sum.
+    ``causal``: returns (group totals (B, ceil(N/32), P) fp32, hp, pre (B, N, P) bf16) instead — per 32-token group
+    the running sums of the features and their totals; :func:`group_scan` turns the totals into carries."""
     dev = _require_cuda(x, w_po, coeff, row_weight)
     B, N, D = x.shape
     P, K = coeff.shape
-    partial = torch.empty((B, m_tiles(N), P), dtype=torch.float32, device=dev)
     hp = torch.empty((B, N, P), dtype=torch.bfloat16, device=dev) if save_hp else None
     a = CtxArgs()
     a.X, a.Wpo, a.coeff, a.row_weight = ptr(x), ptr(w_po), ptr(coeff), ptr(row_weight)
+    if causal:
+        sums = torch.empty((B, token_groups(N), P), dtype=torch.float32, device=dev)
+        pre = torch.empty((B, N, P), dtype=torch.bfloat16, device=dev)
+        a.hp_out, a.causal, a.pre_out, a.ld_pre, a.group_sums = ptr(hp), 1, ptr(pre), P, ptr(sums)
+        a.ldx, a.ldw, a.ld_hp = _row_stride(x), _row_stride(w_po), P
+        a.B, a.N, a.D, a.P, a.K = B, N, D, P, K
+        a.rope = _rope_c(rope)
+        _abi.check(_abi.lib().pom_ctx_gemm(C.byref(a), ptr(_abi.status_word(dev)), _abi.stream_ptr()), "pom_ctx_gemm")
+        return sums, hp, pre
+    partial = torch.empty((B, m_tiles(N), P), dtype=torch.float32, device=dev)
     a.hp_out, a.partial = ptr(hp), ptr(partial)
     a.tile_weight = ptr(tile_weight)
     a.ldx, a.ldw, a.ld_hp = _row_stride(x), _row_stride(w_po), P
@@ -289,10 +306,25 @@ def ctx_gemm(x: torch.Tensor, w_po: torch.Tensor, coeff: torch.Tensor, *, row_we
     return partial, hp
 
 
-def gate_gemm(x: torch.Tensor, w_se: torch.Tensor, bias: torch.Tensor, h: torch.Tensor, *, save_z: bool = True,
-              rope: Optional[RopeSpec] = None):
+def group_scan(sums: torch.Tensor, carry_in: Optional[torch.Tensor] = None, *, reverse: bool = False,
+               want_total: bool = False) -> Optional[torch.Tensor]:
+    """In-place exclusive scan over the 32-token groups of (B, groups, P) fp32 totals (forward: prefix, reverse:
+    suffix), seeded with ``carry_in`` (B, P).  Returns the (B, P) sum over the groups when ``want_total``."""
+    _require_cuda(sums, carry_in)
+    B, G, P = sums.shape
+    assert sums.dtype == torch.float32 and sums.is_contiguous()
+    scratch = torch.empty((B * ((G + 31) // 32) * P,), dtype=torch.float32, device=sums.device)
+    total = torch.empty((B, P), dtype=torch.float32, device=sums.device) if want_total else None
+    _abi.check(_abi.lib().pom_group_scan(ptr(sums), ptr(carry_in), ptr(total), ptr(scratch), B, G, P, int(reverse),
+                                         _abi.stream_ptr()), "pom_group_scan")
+    return total
+
+
+def gate_gemm(x: torch.Tensor, w_se: torch.Tensor, bias: torch.Tensor, h: Optional[torch.Tensor], *,
+              save_z: bool = True, rope: Optional[RopeSpec] = None, causal=None):
     """Query phase: returns (SH (B, T, P) bf16, z (B, T, P) bf16 or None). ``h`` is (B, P) fp32.  ``rope``: the
-    gate is rotated by the query positions after the hardsigmoid."""
+    gate is rotated by the query positions after the hardsigmoid.  ``causal`` = (pre, carry, token_offset): the
+    per-token prefix mean (pre + carry[group]) / (token_offset + t + 1) takes the place of ``h``."""
     dev = _require_cuda(x, w_se, bias, h)
     B, T, D = x.shape
     P = w_se.shape[0]
@@ -302,35 +334,55 @@ def gate_gemm(x: torch.Tensor, w_se: torch.Tensor, bias: torch.Tensor, h: torch.
     a.X, a.Wse, a.bias, a.H = ptr(x), ptr(w_se), ptr(bias), ptr(h)
     a.z_out, a.sh_out = ptr(z), ptr(sh)
     a.ldx, a.ldw, a.ld_z, a.ld_sh = _row_stride(x), _row_stride(w_se), P, P
-    a.h_batch_stride, a.h_row_stride = h.stride(0), 0
+    a.h_batch_stride, a.h_row_stride = (h.stride(0) if h is not None else 0), 0
     a.B, a.T, a.D, a.P = B, T, D, P
     a.rope = _rope_c(rope)
+    if causal is not None:
+        pre, carry, offset = causal
+        if tuple(pre.shape) != (B, T, P) or tuple(carry.shape) != (B, token_groups(T), P):
+            raise ValueError("pre must be (B, T, P) and carry (B, ceil(T/32), P)")
+        a.causal, a.pre, a.ld_pre, a.carry, a.token_offset = 1, ptr(pre), P, ptr(carry), int(offset)
     _abi.check(_abi.lib().pom_gate_gemm(C.byref(a), ptr(_abi.status_word(dev)), _abi.stream_ptr()), "pom_gate_gemm")
     return sh, z
 
 
-def gate_bwd_gemm(dy: torch.Tensor, w_o: torch.Tensor, bias: torch.Tensor, h: torch.Tensor, z: torch.Tensor,
-                  g_out: torch.Tensor, *, rope: Optional[RopeSpec] = None):
+def gate_bwd_gemm(dy: torch.Tensor, w_o: torch.Tensor, bias: torch.Tensor, h: Optional[torch.Tensor], z: torch.Tensor,
+                  g_out: torch.Tensor, *, rope: Optional[RopeSpec] = None, w_o_t: Optional[torch.Tensor] = None,
+                  causal=None):
     """Backward of the query phase. Writes dz into ``g_out`` (a (B*T, P) view with its own row
     stride) and returns (dh_partial, dbias_partial), both (B, MT, P) fp32.  ``rope``: backward of the rotated
-    gate; this form reads the output weight transposed (a (P, D) copy made here, 2 P D bytes each way)."""
+    gate; this form reads the output weight transposed: ``w_o_t`` (P, D), or a copy made here when it is None.
+    ``causal`` = (pre, carry, token_offset): returns (dbias_partial, suf (B, T, P) bf16, group totals
+    (B, ceil(T/32), P) fp32) instead — the running sums, up the rows of every 32-token group, of the gradient of the
+    prefix means, for :func:`group_scan` (reverse) and :func:`poly_agg_bwd` (``fused_causal``)."""
     dev = _require_cuda(dy, w_o, bias, h, z, g_out)
     B, T, D = dy.shape
     P = w_o.shape[1]
-    dh_p = torch.empty((B, m_tiles(T), P), dtype=torch.float32, device=dev)
+    dh_p = None if causal is not None else torch.empty((B, m_tiles(T), P), dtype=torch.float32, device=dev)
     db_p = torch.empty((B, m_tiles(T), P), dtype=torch.float32, device=dev)
     a = GateBwdArgs()
     a.dY, a.Wo, a.bias, a.H, a.z = ptr(dy), ptr(w_o), ptr(bias), ptr(h), ptr(z)
     a.g_out, a.dh_partial, a.db_partial = ptr(g_out), ptr(dh_p), ptr(db_p)
     a.ld_dy, a.ldw, a.ld_z, a.ld_g = _row_stride(dy), _row_stride(w_o), _row_stride(z), _row_stride(g_out)
-    a.h_batch_stride = h.stride(0)
+    a.h_batch_stride = h.stride(0) if h is not None else 0
     a.B, a.T, a.D, a.P = B, T, D, P
     a.rope = _rope_c(rope)
-    if rope is not None:
-        w_t = transpose_bf16(w_o)
+    suf = sums = None
+    if causal is not None:
+        pre, carry, offset = causal
+        suf = torch.empty((B, T, P), dtype=torch.bfloat16, device=dev)
+        sums = torch.empty((B, token_groups(T), P), dtype=torch.float32, device=dev)
+        a.causal, a.pre, a.ld_pre, a.carry, a.token_offset = 1, ptr(pre), P, ptr(carry), int(offset)
+        a.suf_out, a.ld_suf, a.group_sums = ptr(suf), P, ptr(sums)
+    if rope is not None or causal is not None:
+        w_t = w_o_t if w_o_t is not None else transpose_bf16(w_o)
+        if tuple(w_t.shape) != (P, D) or w_t.dtype != torch.bfloat16 or not w_t.is_contiguous():
+            raise ValueError(f"w_o_t must be a contiguous bfloat16 ({P}, {D}) tensor")
         a.WoT, a.ldwt = ptr(w_t), D
     _abi.check(_abi.lib().pom_gate_bwd_gemm(C.byref(a), ptr(_abi.status_word(dev)), _abi.stream_ptr()),
                "pom_gate_bwd_gemm")
+    if causal is not None:
+        return db_p, suf, sums
     return dh_p, db_p
 
 
@@ -428,9 +480,10 @@ def poly_agg_bwd(x: torch.Tensor, coeff: torch.Tensor, *, dx_out: torch.Tensor, 
                  denom: Optional[torch.Tensor] = None, scale: float = 1.0, causal: bool = False,
                  rope: Optional[RopeSpec] = None, carry: Optional[torch.Tensor] = None, token_offset: int = 0,
                  want_total: bool = False, totals_only: bool = False, dcoeff_out: Optional[torch.Tensor] = None,
-                 per_token: bool = False):
+                 per_token: bool = False, fused_causal=None):
     """Writes dx into ``dx_out`` (a (B, N, P) view, own row stride) and returns
-    (dcoeff (P, K) fp32, total (B, P) fp32 or None)."""
+    (dcoeff (P, K) fp32, total (B, P) fp32 or None).  ``fused_causal`` = (suf, carry): the gradient of token n's
+    features is suf[b, n] + carry[b, n // 32] (outputs of the causal :func:`gate_bwd_gemm` and :func:`group_scan`)."""
     dev = _require_cuda(x, coeff, dx_out, dH, dout, row_weight, denom, carry)
     B, N, P = x.shape
     K = coeff.shape[1]
@@ -439,6 +492,10 @@ def poly_agg_bwd(x: torch.Tensor, coeff: torch.Tensor, *, dx_out: torch.Tensor, 
     causal = causal or per_token
     partial = torch.empty((B, chunks, P), dtype=torch.float32, device=dev) if (causal and not per_token) else None
     total = torch.empty((B, P), dtype=torch.float32, device=dev) if (causal and want_total) else None
+    if fused_causal is not None:
+        dout, partial = fused_causal
+        if tuple(dout.shape) != (B, N, P) or tuple(partial.shape) != (B, token_groups(N), P):
+            raise ValueError("fused_causal needs suf (B, N, P) and carry (B, ceil(N/32), P)")
     a = AggBwdArgs()
     a.x, a.coeff, a.row_weight, a.denom = ptr(x), ptr(coeff), ptr(row_weight), ptr(denom)
     a.dH, a.dout, a.carry, a.partial, a.total = ptr(dH), ptr(dout), ptr(carry), ptr(partial), ptr(total)
@@ -448,6 +505,8 @@ def poly_agg_bwd(x: torch.Tensor, coeff: torch.Tensor, *, dx_out: torch.Tensor, 
     a.token_offset, a.scale = token_offset, scale
     a.B, a.N, a.P, a.K = B, N, P, K
     a.dtype, a.causal, a.phase = _abi.dtype_code(x.dtype), (2 if per_token else int(causal)), int(totals_only)
+    if fused_causal is not None:
+        a.causal = 3
     a.rope = _rope_c(rope)
     _abi.check(_abi.lib().pom_poly_agg_bwd(C.byref(a), _abi.stream_ptr()), "pom_poly_agg_bwd")
     if totals_only:

@@ -25,10 +25,12 @@ class PeerExchange:
 
     ``slot_floats``: largest message (B·P fp32 values) a single exchange may carry.
     ``flat_floats``: size of the parameter-gradient region that ``allreduce_flat`` sums in place.
+    ``wait_ms``: limit of every device-side wait on another rank (0 = the library default of 2 s).
     Collective: every rank of the group must construct it at the same point of the program.
     """
 
-    def __init__(self, group=None, slot_floats: int = 1 << 16, flat_floats: int = 0, device=None):
+    def __init__(self, group=None, slot_floats: int = 1 << 16, flat_floats: int = 0, device=None,
+                 wait_ms: float = 0.0):
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -62,6 +64,7 @@ class PeerExchange:
         self.comm = PeerComm()
         self.comm.rank, self.comm.world = self.rank, self.world
         self.comm.slot_floats, self.comm.flat_floats = slot_floats, flat_floats
+        self.comm.wait_ns = int(wait_ms * 1e6)  # 0: the library's default limit (2 s) for every wait on a peer
         mapped = True
         for r, (h, off) in enumerate(everyone):
             if r == self.rank:
@@ -114,6 +117,14 @@ class PeerExchange:
         n4 = (n + 3) // 4 * 4
         _abi.check(_abi.lib().pom_peer_allreduce_flat(C.byref(self.comm), n4, ptr(_abi.status_word(self.device)),
                                                       _abi.stream_ptr()), "pom_peer_allreduce_flat")
+
+    def check(self) -> None:
+        """Synchronising read of the device status word: raises when a wait on another rank ran out of time.
+        After that the exchange buffers are out of step (the rank that gave up has advanced its epochs): build a
+        new ``PeerExchange`` and clear the status word (``_abi.status_word(device).zero_()``) before going on."""
+        code = int(_abi.status_word(self.device).item())
+        if code:
+            raise _abi.PomError(code, "peer exchange")
 
     def close(self) -> None:
         """Unmap the peers' buffers (after a barrier: nobody may still be reading ours)."""

@@ -77,3 +77,43 @@ def test_flat_allreduce_with_one_rank_is_identity_and_graph_replay_advances_epoc
     torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-5)
     assert torch.equal(peer.flat, ref)
     assert _abi.read_status("cuda:0") == 0
+
+
+def test_a_wait_on_a_silent_rank_runs_out_and_reports_it():
+    """Two-rank layout on one GPU whose second rank never runs: rank 0 pushes its message, waits the configured
+    20 ms for a flag that nobody sets, records POM_ERR_TIMEOUT in the status word and returns; the next exchange
+    sees the word and does not wait again.  Nothing faults and nothing spins for ever."""
+    import ctypes as C
+
+    from pom_b200 import _abi
+
+    lib = _abi.lib()
+    lay = (C.c_ulonglong * 3)()
+    assert lib.pom_peer_layout(2, 256, 0, lay) == 0
+    bufs = [torch.zeros(int(lay[2]), dtype=torch.uint8, device="cuda") for _ in range(2)]
+    comm = _abi.PeerComm()
+    comm.rank, comm.world, comm.slot_floats, comm.flat_floats = 0, 2, 256, 0
+    comm.wait_ns = 20_000_000
+    for r in range(2):
+        comm.base[r] = bufs[r].data_ptr()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")  # a word of its own: the shared one stays clean
+    part = torch.ones(1, 1, 64, device="cuda")
+    out = torch.empty(1, 64, device="cuda")
+    a = _abi.PeerXchgArgs()
+    a.partial, a.out, a.scale, a.B, a.chunks, a.P, a.mode = part.data_ptr(), out.data_ptr(), 1.0, 1, 1, 64, 0
+
+    def launch():
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        assert lib.pom_peer_exchange(C.byref(comm), C.byref(a), _abi.ptr(status), _abi.stream_ptr()) == 0
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1)
+
+    ms = launch()
+    assert int(status.item()) == -7, "the expired wait must be recorded as POM_ERR_TIMEOUT"
+    assert 15.0 < ms < 500.0, f"expected about 20 ms of waiting, measured {ms:.1f} ms"
+    ms2 = launch()
+    assert int(status.item()) == -7
+    assert ms2 < 10.0, f"an exchange after a recorded timeout must not wait again ({ms2:.1f} ms)"
+    assert "time" in _abi.strerror(-7).lower()

@@ -80,9 +80,15 @@ def test_fused_rotary_layer_against_oracle(shape, gemm_mode, monkeypatch):
 @pytest.mark.parametrize("two_d", [False, True], ids=["1d", "2d"])
 def test_fused_rotary_at_the_long_sequence_width(two_d):
     """The channel width of the 64 k-token benchmark configuration (D = 1152, P = 2304: rotation partners
-    1152 or 576 channels apart) on a 64 x 64 grid of tokens."""
+    1152 or 576 channels apart) on a 64 x 64 grid of tokens.
+
+    The gate bias is kept small here: z is stored in bf16 for the backward pass, and with 9.4 M gate values a wide
+    bias puts a handful of them within one bf16 step of the hardsigmoid's kinks at +-3, where the rounded z and the
+    oracle's unrounded z take different derivatives (1/6 vs 0).  One such element moves a whole row of dX by a
+    full term, which the max-normalised bound then reports although nothing is wrong with the kernels (the
+    stand-alone operator path shows the same rows)."""
     side = 64
-    cfg, params, x, gy, kw = _case(1, side * side, 1152, 2, 2, seed=22, two_d=two_d, side=side)
+    cfg, params, x, gy, kw = _case(1, side * side, 1152, 2, 2, seed=22, two_d=two_d, side=side, bias_scale=0.1)
     _check_layer(cfg, params, x, gy, kw, f"D=1152 two_d={two_d}")
 
 
