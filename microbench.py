@@ -92,23 +92,31 @@ def main(argv=None) -> None:
         x = rnd(a.b, a.tokens, a.d)
         fl = 2.0 * a.b * a.tokens * a.d * P
         rope = _rope_spec(a.rope, a.tokens, P, dev)
+        # --causal: the token-causal forms of the three phases (running sums per 32-token group in the epilogue)
+        causal = None
+        if a.causal and a.what != "ctx":
+            pre = rnd(a.b, a.tokens, P)
+            carry = torch.randn(a.b, ops.token_groups(a.tokens), P, device=dev, generator=g)
+            causal = (pre, carry, 0)
         if a.what == "ctx":
             w = rnd(P, a.d) * 0.03
             coeff = torch.randn(P, a.degree, device=dev, generator=g) * 0.1
-            ms = _time(lambda: ops.ctx_gemm(x, w, coeff, rope=rope), a.iters)
+            ms = _time(lambda: ops.ctx_gemm(x, w, coeff, rope=rope, causal=a.causal), a.iters)
         elif a.what == "gate":
             w = rnd(P, a.d) * 0.03
             bias = torch.zeros(P, device=dev)
             h = torch.randn(a.b, P, device=dev, generator=g)
-            ms = _time(lambda: ops.gate_gemm(x, w, bias, h, rope=rope), a.iters)
+            ms = _time(lambda: ops.gate_gemm(x, w, bias, h, rope=rope, causal=causal), a.iters)
         else:
             wo = rnd(a.d, P) * 0.03
+            wot = wo.t().contiguous()
             bias = torch.zeros(P, device=dev)
             h = torch.randn(a.b, P, device=dev, generator=g)
             z = rnd(a.b, a.tokens, P)
             G = torch.empty(a.b * a.tokens, 2 * P, device=dev, dtype=torch.bfloat16)
-            ms = _time(lambda: ops.gate_bwd_gemm(x, wo, bias, h, z, G[:, P:], rope=rope), a.iters)
-        print(f"{a.what} b={a.b} tokens={a.tokens} d={a.d} p={P} degree={a.degree} rope={a.rope} mode={a.mode}: {ms:.4f} ms {fl / ms / 1e9:.0f} TFLOP/s")
+            ms = _time(lambda: ops.gate_bwd_gemm(x, wo, bias, h, z, G[:, P:], rope=rope, w_o_t=wot, causal=causal),
+                       a.iters)
+        print(f"{a.what} b={a.b} tokens={a.tokens} d={a.d} p={P} degree={a.degree} rope={a.rope} causal={a.causal} mode={a.mode}: {ms:.4f} ms {fl / ms / 1e9:.0f} TFLOP/s")
     else:
         P = a.p
         x = rnd(a.b, a.tokens, P) * 0.5

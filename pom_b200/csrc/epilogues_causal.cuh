@@ -334,9 +334,10 @@ struct EpiGateBwdCausal {
     RopeEpi rope;
     CausalEpi causal;  // carry: forward carries; group_sums: totals of u for the reverse scan
   };
-  // per warp: input set {z first, z partner, pre first, pre partner} (re-used as the transposition block once
-  // consumed), then dz first | dz partner | suf first | suf partner output blocks
-  static constexpr int kStageBytes = 8192;
+  // per warp: two alternating input sets {z first, z partner, pre first, pre partner} (the set in use becomes the
+  // transposition block once its rows are in registers, while the other one receives the next sub-unit's
+  // blocks), then dz first | dz partner | suf first | suf partner output blocks
+  static constexpr int kStageBytes = 12288;
   static constexpr int kSmemBytes = 0;
   template <int BN>
   static constexpr int smem_bytes() {
@@ -344,14 +345,15 @@ struct EpiGateBwdCausal {
   }
 
   static __device__ __forceinline__ void fetch_in(const EpiMaps& maps, const TileCtx& t, EpiIO& io, int quarter,
-                                                  int lane, int su) {
+                                                  int lane, int su, int set) {
     if (lane == 0) {
       const int u = t.u0 + 16 * su, y = t.row0 + quarter * 32;
+      uint8_t* blk = io.buf0 + set * 4096;
       mbar_expect_tx(io.bar, 4096);
-      tma_load_4d(io.buf0, &maps.in0, io.bar, u, 2 * t.sec, y, t.b);
-      tma_load_4d(io.buf0 + 1024, &maps.in0, io.bar, u, 2 * t.sec + 1, y, t.b);
-      tma_load_4d(io.buf0 + 2048, &maps.in1, io.bar, u, 2 * t.sec, y, t.b);
-      tma_load_4d(io.buf0 + 3072, &maps.in1, io.bar, u, 2 * t.sec + 1, y, t.b);
+      tma_load_4d(blk, &maps.in0, io.bar, u, 2 * t.sec, y, t.b);
+      tma_load_4d(blk + 1024, &maps.in0, io.bar, u, 2 * t.sec + 1, y, t.b);
+      tma_load_4d(blk + 2048, &maps.in1, io.bar, u, 2 * t.sec, y, t.b);
+      tma_load_4d(blk + 3072, &maps.in1, io.bar, u, 2 * t.sec + 1, y, t.b);
     }
   }
 
@@ -361,7 +363,7 @@ struct EpiGateBwdCausal {
                                                   EpiIO& io, int) {
     named_bar_sync(kEpiBarrier, kEpiThreads);
     const int half = warp_in_epi >> 2, quarter = (warp_in_epi + 2) & 3;
-    if (t.u0 + 16 * half < g.pair_q) fetch_in(maps, t, io, quarter, epi_tid & 31, half);
+    if (t.u0 + 16 * half < g.pair_q) fetch_in(maps, t, io, quarter, epi_tid & 31, half, 0);
     const RopeScratch<BN> rs(scratch + 9 * BN);
     rope_stage<BN>(p.rope, maps, g, t, epi_tid, rs, io);
     for (int c = epi_tid; c < BN; c += kEpiThreads) {
@@ -387,9 +389,9 @@ struct EpiGateBwdCausal {
     const int grp = (t.row0 >> 5) + quarter;
     const bool grp_ok = grp < p.causal.groups && t.rows_valid > 0;
     const float inv_n = 1.f / static_cast<float>(p.causal.token_offset + y + lane + 1);
-    uint8_t* in = io.buf0;
-    uint8_t* out = io.buf0 + 4096;
+    uint8_t* out = io.buf0 + 8192;
     bool alive = true;
+    int set = 0;
 #pragma unroll 1
     for (int su = half; su < BN / 32; su += kEpiColSplit) {
       float* b1p = buf_b + quarter * BN + 16 * su;
@@ -404,6 +406,12 @@ struct EpiGateBwdCausal {
       if (alive) alive = mbar_wait(io.bar, io.load_phase, io.abort_flag, io.status, kStatusEpilogueTimeout);
       alive = __all_sync(0xffffffffu, alive);
       io.load_phase ^= 1u;
+      // the other set was last touched (as the transposition block) one sub-unit ago by every lane: refill it
+      const int nsu = su + kEpiColSplit;
+      __syncwarp();
+      if (alive && nsu < BN / 32 && t.u0 + 16 * nsu < g.pair_q) fetch_in(maps, t, io, quarter, lane, nsu, set ^ 1);
+      uint8_t* in = io.buf0 + set * 4096;
+      set ^= 1;
       read_block16<0>(in, lane, z);
       read_block16<16>(in + 1024, lane, z);
       tmem_ld_wait();
@@ -452,9 +460,6 @@ struct EpiGateBwdCausal {
         tma_store_4d(&maps.out1, out + 3072, u, 2 * t.sec + 1, y, t.b);
         bulk_commit();
       }
-      // the transposition block is free again: start the next sub-unit's input loads behind the reduction below
-      const int nsu = su + kEpiColSplit;
-      if (alive && nsu < BN / 32 && t.u0 + 16 * nsu < g.pair_q) fetch_in(maps, t, io, quarter, lane, nsu);
       if (grp_ok && u + (lane & 15) < g.pair_q) {
         const int col = (lane < 16 ? t.col0 : t.col1) + 16 * su + (lane & 15);
         p.causal.group_sums[(static_cast<long long>(t.b) * p.causal.groups + grp) * p.causal.P + col] = total;

@@ -316,7 +316,7 @@ template <int STAGE_BYTES, class Epi, int BN>
 constexpr int stages_for() {
   constexpr int kMaxSmem = 232448;
   constexpr int n = (kMaxSmem - SmemPlan<1>::bytes(0, Epi::template smem_bytes<BN>(), Epi::kStageBytes)) / STAGE_BYTES;
-  return n > 8 ? 8 : n;
+  return n > 8 ? 8 : (n < 1 ? 1 : n);  // (a width that does not fit at all is never launched: see run_plan)
 }
 
 // Dispatch over kernel flavour and tile width for a fixed operand order and epilogue.
@@ -324,17 +324,20 @@ template <bool A_MN, bool B_MN, class Epi>
 int run_plan(const TilePlan& p, const Operands& o, int split, const EpiMaps& maps, const typename Epi::Params& ep,
              int* status, cudaStream_t st) {
   if (p.pair) {
-    if (p.bn == 256)
+    // an epilogue whose staging leaves fewer than three pipeline stages beside a 256-column tile takes the next width
+    constexpr bool k256_fits = stages_for<Gemm2Smem<256>::kStageBytes, Epi, 256>() >= 3;
+    if (p.bn == 256 && (k256_fits || B_MN))
       return launch_pair<256, stages_for<Gemm2Smem<256>::kStageBytes, Epi, 256>(), A_MN, B_MN, Epi>(o, split, maps, ep, status, st);
     if constexpr (!B_MN) {
-      if (p.bn == 192)
+      if (p.bn == 192 || p.bn == 256)
         return launch_pair<192, stages_for<Gemm2Smem<192>::kStageBytes, Epi, 192>(), A_MN, B_MN, Epi>(o, split, maps, ep, status, st);
     }
     return launch_pair<128, stages_for<Gemm2Smem<128>::kStageBytes, Epi, 128>(), A_MN, B_MN, Epi>(o, split, maps, ep, status, st);
   }
-  if (p.bn == 256)
+  constexpr bool k256_one_fits = stages_for<GemmSmem<256>::kStageBytes, Epi, 256>() >= 2;
+  if (p.bn == 256 && k256_one_fits)
     return launch<256, stages_for<GemmSmem<256>::kStageBytes, Epi, 256>(), A_MN, B_MN, Epi>(o, split, maps, ep, status, st);
-  if (p.bn == 192)
+  if (p.bn == 192 || p.bn == 256)
     return launch<192, stages_for<GemmSmem<192>::kStageBytes, Epi, 192>(), A_MN, B_MN, Epi>(o, split, maps, ep, status, st);
   return launch<128, stages_for<GemmSmem<128>::kStageBytes, Epi, 128>(), A_MN, B_MN, Epi>(o, split, maps, ep, status, st);
 }

@@ -967,11 +967,15 @@ inline StreamPairs stream_pairs(const pom_agg_bwd_args* a) {
   return StreamPairs{0, 0};
 }
 inline StreamPlan stream_plan_rope(int B, int N, const StreamPairs& sp, int tile_tokens = kStTok) {
-  StreamPlan s = stream_plan(B, N, 1);
+  StreamPlan s;
   s.tiles = static_cast<int>(ceil_div(N, tile_tokens));
   s.col_blocks = sp.sections * static_cast<int>(ceil_div(sp.q, kStHalf));
   const long long pairs = static_cast<long long>(s.col_blocks) * B;
   long long want = ceil_div(4LL * sm_count(), pairs);
+  // one coefficient-gradient partial per (sample, run of tiles): never more runs than the caller's capacity of
+  // pom_agg_chunks(N) slots per sample, whatever the tile length
+  const long long cap = ceil_div(N, kChunk);
+  if (want > cap) want = cap;
   if (want < 1) want = 1;
   if (want > s.tiles) want = s.tiles;
   s.tiles_per_cta = static_cast<int>(ceil_div(s.tiles, want));

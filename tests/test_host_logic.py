@@ -55,13 +55,18 @@ def test_layer_entry_points_validate_before_touching_the_gpu(lib):
 
 def test_backward_partial_slot_count_never_exceeds_the_chunk_capacity(lib):
     a = _abi.AggBwdArgs()
-    for B, N, P in ((32, 1024, 2304), (1, 65536, 2304), (64, 2048, 2048), (3, 70, 96)):
+    for B, N, P in ((32, 1024, 2304), (1, 65536, 2304), (64, 2048, 2048), (3, 70, 96), (2, 320, 256), (2, 24, 32)):
         a.B, a.N, a.P, a.K = B, N, P, 2
         a.dtype, a.causal = 0, 0
         a.ldx = a.ld_dx = P
         a.x = a.dx = C.c_void_p(512)
         slots = lib.pom_poly_agg_bwd_slots(C.byref(a))
         assert 0 < slots <= B * lib.pom_agg_chunks(N)
+        # the fused token-causal form walks 32-token tiles: its runs must fit the same capacity
+        a.causal, a.dout, a.partial, a.ld_dout = 3, C.c_void_p(512), C.c_void_p(512), P
+        slots = lib.pom_poly_agg_bwd_slots(C.byref(a))
+        assert 0 < slots <= B * lib.pom_agg_chunks(N), (B, N, P, slots)
+        a.causal, a.dout, a.partial = 0, None, None
 
 
 def _module_for(cfg):
