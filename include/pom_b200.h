@@ -529,7 +529,9 @@ int pom_layer_bwd(const pom_layer_args* a, int* status, void* stream);
  * (pom_peer_open, returns the allocation's base in this process; add the offset).  Layout:
  *   [0, POM_PEER_HEADER_BYTES)  epoch counters and flags
  *   [layout[0], layout[1])      message slots: 2 epochs x world writers x slot_floats fp32
- *   [layout[1], layout[2])      parameter-gradient region, flat_floats fp32, reduced in place
+ *   [layout[1], layout[2])      parameter-gradient region: flat_floats fp32 accumulators (reduced in place by
+ *                               pom_peer_allreduce_flat), then at layout[1] + 4 * flat_floats a bf16 staging image and
+ *                               at layout[1] + 6 * flat_floats the bf16 result image of pom_peer_allreduce_flat_bf16
  * The library allocates nothing; the caller owns the buffers and must keep them alive, and mapped by the
  * peers, until all ranks have finished their last exchange.  All ranks must issue the same sequence of
  * exchange calls.  Waits on other ranks are bounded (pom_peer_comm::wait_ns, 2 s when 0): on expiry
@@ -577,6 +579,15 @@ int pom_peer_exchange(const pom_peer_comm* c, const pom_peer_xchg_args* a, int* 
 /* In-place sum over ranks of the first n_floats (multiple of 4) of every rank's gradient region: rank r adds
  * slice r of all ranks in rank order and stores the result to all ranks. */
 int pom_peer_allreduce_flat(const pom_peer_comm* c, unsigned long long n_floats, int* status, void* stream);
+
+/* The same sum with bf16 on the wire, for gradients that end up in bf16 anyway: every rank rounds its fp32
+ * accumulators to bf16 (staging image, local), rank r adds slice r of all ranks in fp32 in rank order and stores the
+ * bf16 result into every rank's result image (byte offset layout[1] + 6 * flat_floats of its buffer).  n_floats and
+ * flat_floats multiples of 8.  The fp32 accumulators are left as they were. */
+int pom_peer_allreduce_flat_bf16(const pom_peer_comm* c, unsigned long long n_floats, int* status, void* stream);
+
+/* Asynchronous device-to-device copy of `bytes` bytes on the stream (cudaMemcpyAsync; no kernel). */
+int pom_copy_bytes(void* dst, const void* src, int64_t bytes, void* stream);
 
 #ifdef __cplusplus
 }

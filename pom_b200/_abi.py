@@ -247,6 +247,8 @@ _SIGNATURES = {
     "pom_peer_close": (C.c_int, [C.c_void_p]),
     "pom_peer_exchange": (C.c_int, [C.POINTER(PeerComm), C.POINTER(PeerXchgArgs), C.c_void_p, C.c_void_p]),
     "pom_peer_allreduce_flat": (C.c_int, [C.POINTER(PeerComm), C.c_ulonglong, C.c_void_p, C.c_void_p]),
+    "pom_peer_allreduce_flat_bf16": (C.c_int, [C.POINTER(PeerComm), C.c_ulonglong, C.c_void_p, C.c_void_p]),
+    "pom_copy_bytes": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
 }
 
 _lib = None

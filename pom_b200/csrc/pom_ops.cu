@@ -1867,6 +1867,18 @@ int pom_frame_prefix_mean(const float* in, float* out, int32_t B, int32_t F, int
   return check_launch();
 }
 
+int pom_copy_bytes(void* dst, const void* src, int64_t bytes, void* stream) {
+  if (!dst || !src) return POM_ERR_NULL;
+  if (bytes < 0) return POM_ERR_BAD_SHAPE;
+  if (bytes == 0) return POM_OK;
+  if (cudaMemcpyAsync(dst, src, static_cast<size_t>(bytes), cudaMemcpyDeviceToDevice,
+                      static_cast<cudaStream_t>(stream)) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return POM_ERR_CUDA;
+  }
+  return POM_OK;
+}
+
 int pom_fill_zero(void* dst, int64_t bytes, void* stream) {
   if (!dst) return POM_ERR_NULL;
   if (bytes <= 0) return POM_ERR_BAD_SHAPE;

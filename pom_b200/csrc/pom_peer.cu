@@ -16,6 +16,8 @@
 #include <cstring>
 #include <mutex>
 
+#include <cuda_bf16.h>
+
 #include "common.cuh"
 
 using namespace pomh;
@@ -44,6 +46,7 @@ struct PeerDev {
   char* base[kMaxRanks];
   int rank, world;
   unsigned long long slot_floats, slots_off, flat_off;
+  unsigned long long stage_off, result_off;  // bf16 images of the gradient region: local copy, reduced result
   unsigned long long wait_ns;  // limit of every wait on another rank
 };
 
@@ -211,6 +214,101 @@ __global__ void __launch_bounds__(kFlatThreads) peer_allreduce_flat_kernel(PeerD
   if (s_fail && tid == 0 && !poisoned) atomicCAS(status, 0, POM_ERR_TIMEOUT);
 }
 
+// The same all-reduce with bf16 on the wire: the layer's parameters (and so the gradients it hands back) are bf16,
+// so each rank first rounds its fp32 accumulators to bf16 into a staging image (local traffic only), rank r then
+// pulls slice r of every rank's image, adds in fp32 in rank order, and writes the bf16 sum into every rank's result
+// image.  Half the NVLink bytes of the fp32 form, and the separate fp32 -> bf16 cast of the result disappears.
+// One work unit = 8 values (32 bytes fp32, 16 bytes bf16).  CTA c converts, in every slice, exactly the units that
+// CTA c of the owning rank will pull, so the per-CTA start flags cover the dependency.
+__device__ __forceinline__ uint4 ld_sys_u4(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_sys_u4(uint4* p, uint4 v) {
+  asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ unsigned pack2_bf16(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&h);
+}
+
+__global__ void __launch_bounds__(kFlatThreads) peer_allreduce_flat_bf16_kernel(PeerDev c, unsigned long long n8,
+                                                                                int* status) {
+  __shared__ unsigned s_epoch;
+  __shared__ int s_fail;
+  const int tid = threadIdx.x, cta = blockIdx.x;
+  PeerHeader* mine = header(c, c.rank);
+  if (tid == 0) {
+    s_epoch = mine->ctr_flat[cta] + 1;
+    mine->ctr_flat[cta] = s_epoch;
+    s_fail = 0;
+  }
+  __syncthreads();
+  const unsigned epoch = s_epoch;
+  const bool poisoned = *reinterpret_cast<volatile int*>(status) != 0;
+  const unsigned long long per = (n8 + c.world - 1) / c.world;
+  const unsigned long long stride = static_cast<unsigned long long>(kFlatCtas) * kFlatThreads;
+  const unsigned long long first = static_cast<unsigned long long>(cta) * kFlatThreads + tid;
+
+  // local image: fp32 accumulators -> bf16, slice by slice with the pull pattern of the reducing rank
+  {
+    const float4* src = reinterpret_cast<const float4*>(c.base[c.rank] + c.flat_off);
+    uint4* dst = reinterpret_cast<uint4*>(c.base[c.rank] + c.stage_off);
+    for (int sl = 0; sl < c.world; ++sl) {
+      const unsigned long long lo = per * sl, hi = lo + per < n8 ? lo + per : n8;
+      for (unsigned long long i = lo + first; i < hi; i += stride) {
+        const float4 a = src[2 * i], b = src[2 * i + 1];
+        dst[i] = make_uint4(pack2_bf16(a.x, a.y), pack2_bf16(a.z, a.w), pack2_bf16(b.x, b.y), pack2_bf16(b.z, b.w));
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid < c.world) st_release_sys(&header(c, tid)->flag_start[c.rank][cta], epoch);
+  if (tid < c.world && !wait_flag(&mine->flag_start[tid][cta], epoch, poisoned, c.wait_ns)) s_fail = 1;
+  __syncthreads();
+
+  const unsigned long long lo = per * c.rank;
+  const unsigned long long hi = lo + per < n8 ? lo + per : n8;
+  if (!s_fail) {
+    for (unsigned long long i = lo + first; i < hi; i += stride) {
+      float acc[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+      uint4 v[kMaxRanks];
+#pragma unroll
+      for (int q = 0; q < kMaxRanks; ++q)
+        if (q < c.world) v[q] = ld_sys_u4(reinterpret_cast<const uint4*>(c.base[q] + c.stage_off) + i);
+#pragma unroll
+      for (int q = 0; q < kMaxRanks; ++q)
+        if (q < c.world) {
+          const unsigned w[4] = {v[q].x, v[q].y, v[q].z, v[q].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            acc[2 * e] += __uint_as_float(w[e] << 16);
+            acc[2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+          }
+        }
+      const uint4 out = make_uint4(pack2_bf16(acc[0], acc[1]), pack2_bf16(acc[2], acc[3]), pack2_bf16(acc[4], acc[5]),
+                                   pack2_bf16(acc[6], acc[7]));
+#pragma unroll
+      for (int q = 0; q < kMaxRanks; ++q)
+        if (q < c.world) st_sys_u4(reinterpret_cast<uint4*>(c.base[q] + c.result_off) + i, out);
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid < c.world) st_release_sys(&header(c, tid)->flag_done[c.rank][cta], epoch);
+  if (tid < c.world && !wait_flag(&mine->flag_done[tid][cta], epoch, poisoned || s_fail, c.wait_ns)) s_fail = 1;
+  __syncthreads();
+  if (s_fail && tid == 0 && !poisoned) atomicCAS(status, 0, POM_ERR_TIMEOUT);
+}
+
 int to_dev(const pom_peer_comm* c, PeerDev* d) {
   if (!c) return POM_ERR_NULL;
   if (c->world < 1 || c->world > kMaxRanks || c->rank < 0 || c->rank >= c->world) return POM_ERR_BAD_SHAPE;
@@ -226,6 +324,8 @@ int to_dev(const pom_peer_comm* c, PeerDev* d) {
   d->slot_floats = c->slot_floats;
   d->slots_off = lay[0];
   d->flat_off = lay[1];
+  d->stage_off = lay[1] + c->flat_floats * sizeof(float);
+  d->result_off = d->stage_off + c->flat_floats * 2;
   d->wait_ns = c->wait_ns ? c->wait_ns : kDefaultWaitNs;
   return POM_OK;
 }
@@ -256,7 +356,8 @@ int pom_peer_layout(int world, unsigned long long slot_floats, unsigned long lon
   if (slot_floats == 0 || (slot_floats & 3ull) || (flat_floats & 3ull)) return POM_ERR_BAD_ALIGN;
   out[0] = POM_PEER_HEADER_BYTES;
   out[1] = out[0] + 2ull * world * slot_floats * sizeof(float);
-  out[2] = out[1] + flat_floats * sizeof(float);
+  // gradient region: fp32 accumulators, then their bf16 staging image, then the bf16 result image
+  out[2] = out[1] + flat_floats * (sizeof(float) + 2 + 2);
   return POM_OK;
 }
 
@@ -335,6 +436,19 @@ int pom_peer_allreduce_flat(const pom_peer_comm* c, unsigned long long n_floats,
   if (n_floats > c->flat_floats) return POM_ERR_TOO_LARGE;
   peer_allreduce_flat_kernel<<<kFlatCtas, kFlatThreads, 0, static_cast<cudaStream_t>(stream)>>>(d, n_floats / 4,
                                                                                                  status);
+  count_launch();
+  return check_launch();
+}
+
+int pom_peer_allreduce_flat_bf16(const pom_peer_comm* c, unsigned long long n_floats, int* status, void* stream) {
+  if (!status) return POM_ERR_NULL;
+  PeerDev d;
+  int rc = to_dev(c, &d);
+  if (rc) return rc;
+  if (n_floats == 0 || (n_floats & 7ull) || (c->flat_floats & 7ull)) return POM_ERR_BAD_ALIGN;
+  if (n_floats > c->flat_floats) return POM_ERR_TOO_LARGE;
+  peer_allreduce_flat_bf16_kernel<<<kFlatCtas, kFlatThreads, 0, static_cast<cudaStream_t>(stream)>>>(d, n_floats / 8,
+                                                                                                      status);
   count_launch();
   return check_launch();
 }

@@ -408,7 +408,7 @@ class _PoMLayer(torch.autograd.Function):
         flat = None
         peer_flat = shard is not None and shard.reduce_weight_grads and shard.peer is not None
         if peer_flat:  # accumulate straight into the peer-mapped gradient region
-            flat = shard.peer.flat_buffer((n_flat + 3) // 4 * 4)
+            flat = shard.peer.flat_buffer((n_flat + 7) // 8 * 8)
         if flat is not None:
             ops.fill_zero(flat)
         else:
@@ -516,19 +516,23 @@ class _PoMLayer(torch.autograd.Function):
         dts = {p_qc.dtype, p_bias.dtype, p_coeff.dtype, p_ag.dtype}
         overlap = peer_flat and shard.overlap_grad_reduce and dts == {torch.bfloat16}
         f16 = None
-        # weight-gradient products first, so that (peer transport) their all-reduce over NVLink and the cast run on
-        # a side stream beside the data-gradient products: its 128 small CTAs fit next to the GEMM's one CTA per SM
+        # weight-gradient products first, so that (peer transport) their all-reduce over NVLink runs on a side stream
+        # beside the data-gradient products.  The GEMM's CTAs fill the shared memory of the SMs they occupy, so the
+        # all-reduce's CTAs run on the SMs the GEMM leaves idle (its last, partial wave) and otherwise right after
+        # it; no rank can block another for longer than that, and every wait is bounded
         if spec.self_mixing:
             ops.gemm(G, xq.view(B * T, D), a_mn=True, b_mn=True, out=d_wqc, accumulate=True)
         else:
             ops.gemm(g_hp, xc.view(B * N, D), a_mn=True, b_mn=True, out=d_wqc[:P], accumulate=True)
             ops.gemm(g_z, xq.view(B * T, D), a_mn=True, b_mn=True, out=d_wqc[P:], accumulate=True)
+        # all parameters bf16 and the peer transport: the gradients cross NVLink as bf16 (half the bytes; the result
+        # image is copied out because the next backward pass reuses it)
+        wire_bf16 = peer_flat and dts == {torch.bfloat16}
         if overlap:
             main, side = torch.cuda.current_stream(), shard.side_stream()
             side.wait_stream(main)
             with torch.cuda.stream(side):
-                shard.reduce_grads(flat)
-                f16 = ops.to_bf16(flat)
+                f16 = ops.clone(shard.peer.allreduce_flat_bf16(n_flat))
         if spec.self_mixing:
             dxq = ops.gemm(G, w_qc, b_mn=True).view(B, T, D)
             dxc = None
@@ -538,6 +542,8 @@ class _PoMLayer(torch.autograd.Function):
         if overlap:
             main.wait_stream(side)
             f16.record_stream(main)
+        elif wire_bf16 and shard.reduce_weight_grads:
+            f16 = ops.clone(shard.peer.allreduce_flat_bf16(n_flat))
         elif shard is not None and shard.reduce_weight_grads:
             shard.reduce_grads(flat)
         if dts == {torch.bfloat16}:

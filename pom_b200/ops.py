@@ -735,6 +735,17 @@ def fill_zero(t: torch.Tensor) -> torch.Tensor:
     return t
 
 
+def clone(src: torch.Tensor) -> torch.Tensor:
+    """Copy of a contiguous CUDA tensor (asynchronous device-to-device copy on the current stream)."""
+    _require_cuda(src)
+    if not src.is_contiguous():
+        raise ValueError("expected a contiguous tensor")
+    out = torch.empty_like(src)
+    _abi.check(_abi.lib().pom_copy_bytes(ptr(out), ptr(src), src.numel() * src.element_size(), _abi.stream_ptr()),
+               "pom_copy_bytes")
+    return out
+
+
 def to_bf16(src: torch.Tensor) -> torch.Tensor:
     _require_cuda(src)
     src = src.contiguous()

@@ -38,7 +38,7 @@ class PeerExchange:
             raise ValueError(f"at most {_abi.PEER_MAX_RANKS} ranks")
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         slot_floats = (int(slot_floats) + 3) // 4 * 4
-        flat_floats = (int(flat_floats) + 3) // 4 * 4
+        flat_floats = (int(flat_floats) + 7) // 8 * 8
         lay = (C.c_ulonglong * 3)()
         lib = _abi.lib()
         _abi.check(lib.pom_peer_layout(self.world, slot_floats, flat_floats, lay), "pom_peer_layout")
@@ -86,6 +86,8 @@ class PeerExchange:
             raise RuntimeError(f"mapping a peer's exchange buffer failed on rank(s) "
                                f"{[r for r, v in enumerate(verdicts) if not v]}")
         self.flat = self.mem[self._flat_off:self._flat_off + 4 * flat_floats].view(torch.float32)
+        res_off = self._flat_off + 6 * flat_floats   # after the fp32 accumulators and their bf16 staging image
+        self.flat_bf16 = self.mem[res_off:res_off + 2 * flat_floats].view(torch.bfloat16)
 
     # ------------------------------------------------------------------ exchanges
     def exchange(self, partial: torch.Tensor, *, mode: int = _abi.PEER_SUM_ALL, denom: Optional[torch.Tensor] = None,
@@ -117,6 +119,14 @@ class PeerExchange:
         n4 = (n + 3) // 4 * 4
         _abi.check(_abi.lib().pom_peer_allreduce_flat(C.byref(self.comm), n4, ptr(_abi.status_word(self.device)),
                                                       _abi.stream_ptr()), "pom_peer_allreduce_flat")
+
+    def allreduce_flat_bf16(self, n: int) -> torch.Tensor:
+        """Sum over ranks of the first ``n`` gradient accumulators with bf16 on the wire; returns the bf16 result
+        as a view of this rank's result image (valid until the next call: copy what must outlive it)."""
+        n8 = (n + 7) // 8 * 8
+        _abi.check(_abi.lib().pom_peer_allreduce_flat_bf16(C.byref(self.comm), n8, ptr(_abi.status_word(self.device)),
+                                                           _abi.stream_ptr()), "pom_peer_allreduce_flat_bf16")
+        return self.flat_bf16[:n]
 
     def check(self) -> None:
         """Synchronising read of the device status word: raises when a wait on another rank ran out of time.

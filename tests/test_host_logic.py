@@ -17,7 +17,7 @@ def test_peer_layout_offsets(lib):
     assert lib.pom_peer_layout(8, 4096, 1024, lay) == 0
     assert lay[0] == 65536                                   # header
     assert lay[1] == lay[0] + 2 * 8 * 4096 * 4               # two epochs x eight writers x slot
-    assert lay[2] == lay[1] + 1024 * 4
+    assert lay[2] == lay[1] + 1024 * (4 + 2 + 2)             # fp32 accumulators + bf16 staging and result images
     assert lib.pom_peer_layout(17, 4096, 0, lay) < 0         # more ranks than the header has flags for
     assert lib.pom_peer_layout(2, 4095, 0, lay) < 0          # slots are multiples of 4 floats (16-byte accesses)
 

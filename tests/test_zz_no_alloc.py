@@ -142,7 +142,7 @@ def test_the_limit_is_exact():
     from pom_b200 import _abi
     from pom_b200._abi import ptr
 
-    B, N, P = 8, 64 * 128, 512           # 8 samples x 128 chunks x 512 channels = 4 Mi floats exactly
+    B, N, P = 64, 64 * 128, 512          # 64 samples x 128 chunks x 512 channels = 4 Mi floats exactly
     assert B * _abi.lib().pom_agg_chunks(N) * P == 4 * 1024 * 1024
     g = torch.Generator(device="cuda").manual_seed(2)
     x = torch.randn(B, N, P, device="cuda", generator=g).bfloat16() * 0.5
