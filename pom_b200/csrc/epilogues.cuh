@@ -107,6 +107,7 @@ struct EpiStore {
   };
   static constexpr int kSmemBytes = 0;
   static constexpr int kStageBytes = kEpiStageBytes;
+  static constexpr bool kStager = false;
   template <int BN>
   static constexpr int smem_bytes() { return kSmemBytes; }
 
@@ -214,6 +215,7 @@ struct EpiCtx {
   static constexpr int kSumFloats = 2 * 4 * 256;
   static constexpr int kSmemBytes = (kSumFloats + kMaxDegree * 256) * 4;
   static constexpr int kStageBytes = kEpiStageBytes;
+  static constexpr bool kStager = false;
   template <int BN>
   static constexpr int smem_bytes() { return kSmemBytes; }
 
@@ -324,6 +326,7 @@ struct EpiGate {
   };
   static constexpr int kSmemBytes = 2 * 2 * 256 * 4;  // double-buffered {bias, H}
   static constexpr int kStageBytes = kEpiStageBytes;
+  static constexpr bool kStager = false;
   template <int BN>
   static constexpr int smem_bytes() { return kSmemBytes; }
 
@@ -387,6 +390,7 @@ struct EpiGateBwd {
   static constexpr int kSumFloats = 2 * 2 * 4 * 256;
   static constexpr int kSmemBytes = (kSumFloats + 2 * 2 * 256) * 4;
   static constexpr int kStageBytes = kEpiStageBytes;
+  static constexpr bool kStager = false;
   template <int BN>
   static constexpr int smem_bytes() { return kSmemBytes; }
 

@@ -71,19 +71,23 @@ struct CausalEpi {
   int P;
 };
 
-// carry[quarter][c] of the tile's four 32-token groups for the tile's (paired) columns.
+// Stager warp: carry[quarter][c] of the tile's four 32-token groups for the tile's (paired) columns, four columns
+// per load (P, pair_q and the tile's first pair are multiples of 4).
 template <int BN>
 __device__ __forceinline__ void stage_carry(float* dst, const CausalEpi& ce, const GemmGeom& g, const TileCtx& t,
-                                            int epi_tid) {
-  for (int idx = epi_tid; idx < 4 * BN; idx += kEpiThreads) {
-    const int quarter = idx / BN, c = idx - quarter * BN;
+                                            int lane) {
+  constexpr int kVec = BN / 4;  // float4 per row group
+#pragma unroll
+  for (int k = 0; k < 4 * kVec / 32; ++k) {
+    const int idx = lane + 32 * k;
+    const int quarter = idx / kVec, c = (idx - quarter * kVec) * 4;
     bool ok;
     const int col = paired_col<BN>(g, t, c, &ok);
     const int grp = (t.row0 >> 5) + quarter;
-    float v = 0.f;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (ok && grp < ce.groups && t.rows_valid > 0)
-      v = __ldg(ce.carry + (static_cast<long long>(t.b) * ce.groups + grp) * ce.P + col);
-    dst[idx] = v;
+      v = __ldg(reinterpret_cast<const float4*>(ce.carry + (static_cast<long long>(t.b) * ce.groups + grp) * ce.P + col));
+    *reinterpret_cast<float4*>(dst + 4 * idx) = v;
   }
 }
 
@@ -100,31 +104,43 @@ struct EpiCtxCausal {
   // per warp: {hp first, hp partner, pre first, pre partner} 1 KiB output blocks, then the 4 KiB transposition block
   static constexpr int kStageBytes = 8192;
   static constexpr int kSmemBytes = 0;
+  static constexpr bool kStager = true;
+  template <int BN>
+  using Scratch = PairScratch<BN, kMaxK, 0, 0>;  // columns: coefficients [degree][BN]
   template <int BN>
   static constexpr int smem_bytes() {
-    return kMaxK * BN * 4 + RopeScratch<BN>::kBytes;
+    return Scratch<BN>::kBytes;
   }
 
   template <int BN>
-  static __device__ __forceinline__ void prologue(const Params& p, const EpiMaps& maps, const GemmGeom& g,
-                                                  const TileCtx& t, int, int epi_tid, float* scratch, EpiIO& io, int) {
-    named_bar_sync(kEpiBarrier, kEpiThreads);
-    const RopeScratch<BN> rs(scratch + kMaxK * BN);
-    rope_stage<BN>(p.rope, maps, g, t, epi_tid, rs, io);
+  static __device__ __forceinline__ uint32_t stage_cols(const Params& p, const EpiMaps& maps, const GemmGeom& g,
+                                                        const TileCtx& t, int lane, float* scratch, uint64_t* bar) {
+    const Scratch<BN> sc(scratch);
+    const uint32_t tx = rope_stage_lane<BN>(p.rope, maps, g, t, lane, sc.lane(), bar);
+    float* cst = sc.cols();
     const int K = p.K;
-    for (int idx = epi_tid; idx < BN * K; idx += kEpiThreads) {
+    for (int idx = lane; idx < BN * K; idx += 32) {
       const int c = idx / K, i = idx - c * K;
       bool ok;
       const int col = paired_col<BN>(g, t, c, &ok);
-      scratch[i * BN + c] = ok ? __ldg(p.coeff + static_cast<long long>(col) * K + i) : 0.f;
+      cst[i * BN + c] = ok ? __ldg(p.coeff + static_cast<long long>(col) * K + i) : 0.f;
     }
-    named_bar_sync(kEpiBarrier, kEpiThreads);
+    return tx;
   }
+  template <int BN>
+  static __device__ __forceinline__ void stage_tile(const Params& p, const EpiMaps&, const GemmGeom& g,
+                                                    const TileCtx& t, int lane, float* scratch, int slot) {
+    const Scratch<BN> sc(scratch);
+    rope_stage_base<BN>(p.rope, g, t, lane, sc.base_cos(slot), sc.base_sin(slot));
+  }
+  template <int BN>
+  static __device__ __forceinline__ void prologue(const Params&, const EpiMaps&, const GemmGeom&, const TileCtx&, int,
+                                                  int, float*, EpiIO&, int) {}
 
   template <int KT, int BN>
   static __device__ __forceinline__ void body(const Params& p, const EpiMaps& maps, const GemmGeom& g,
                                               const TileCtx& t, uint32_t tmem_acc, int quarter, int lane, int half,
-                                              const float* cst, const RopeScratch<BN>& rs, EpiIO& io) {
+                                              const float* cst, const RopeView& rs, EpiIO& io) {
     const bool stepped = p.rope.step_of(t.sec) != 0;
     const int y = t.row0 + quarter * 32;
     const int grp = (t.row0 >> 5) + quarter;
@@ -186,14 +202,16 @@ struct EpiCtxCausal {
   template <int BN>
   static __device__ __forceinline__ void run(const Params& p, const EpiMaps& maps, const GemmGeom& g, const TileCtx& t,
                                              uint32_t tmem_acc, int quarter, int lane, int half, int, float* scratch,
-                                             EpiIO& io, int) {
-    const RopeScratch<BN> rs(scratch + kMaxK * BN);
-    rope_wait(p.rope, t, io);
+                                             EpiIO& io, int iter) {
+    const Scratch<BN> sc(scratch);
+    const int slot = iter & 1;
+    const float* cst = sc.cols();
+    const RopeView rs{sc.base_cos(slot), sc.base_sin(slot), sc.lane()};
     switch (p.K) {
-      case 1: body<1, BN>(p, maps, g, t, tmem_acc, quarter, lane, half, scratch, rs, io); break;
-      case 2: body<2, BN>(p, maps, g, t, tmem_acc, quarter, lane, half, scratch, rs, io); break;
-      case 3: body<3, BN>(p, maps, g, t, tmem_acc, quarter, lane, half, scratch, rs, io); break;
-      default: body<4, BN>(p, maps, g, t, tmem_acc, quarter, lane, half, scratch, rs, io); break;
+      case 1: body<1, BN>(p, maps, g, t, tmem_acc, quarter, lane, half, cst, rs, io); break;
+      case 2: body<2, BN>(p, maps, g, t, tmem_acc, quarter, lane, half, cst, rs, io); break;
+      case 3: body<3, BN>(p, maps, g, t, tmem_acc, quarter, lane, half, cst, rs, io); break;
+      default: body<4, BN>(p, maps, g, t, tmem_acc, quarter, lane, half, cst, rs, io); break;
     }
   }
 };
@@ -210,9 +228,12 @@ struct EpiGateCausal {
   // SH first | SH partner output blocks
   static constexpr int kStageBytes = 8192;
   static constexpr int kSmemBytes = 0;
+  static constexpr bool kStager = true;
+  template <int BN>
+  using Scratch = PairScratch<BN, 1, 4, 0>;  // columns: bias; tile: carries of the four row groups
   template <int BN>
   static constexpr int smem_bytes() {
-    return (BN + 4 * BN) * 4 + RopeScratch<BN>::kBytes;
+    return Scratch<BN>::kBytes;
   }
 
   static __device__ __forceinline__ void fetch_pre(const EpiMaps& maps, const TileCtx& t, EpiIO& io, int quarter,
@@ -226,31 +247,38 @@ struct EpiGateCausal {
   }
 
   template <int BN>
-  static __device__ __forceinline__ void prologue(const Params& p, const EpiMaps& maps, const GemmGeom& g,
-                                                  const TileCtx& t, int warp_in_epi, int epi_tid, float* scratch,
-                                                  EpiIO& io, int) {
-    named_bar_sync(kEpiBarrier, kEpiThreads);
+  static __device__ __forceinline__ uint32_t stage_cols(const Params& p, const EpiMaps& maps, const GemmGeom& g,
+                                                        const TileCtx& t, int lane, float* scratch, uint64_t* bar) {
+    const Scratch<BN> sc(scratch);
+    const uint32_t tx = rope_stage_lane<BN>(p.rope, maps, g, t, lane, sc.lane(), bar);
+    stage_paired_vector<BN>(sc.cols(), p.bias, g, t, lane);
+    return tx;
+  }
+  template <int BN>
+  static __device__ __forceinline__ void stage_tile(const Params& p, const EpiMaps&, const GemmGeom& g,
+                                                    const TileCtx& t, int lane, float* scratch, int slot) {
+    const Scratch<BN> sc(scratch);
+    rope_stage_base<BN>(p.rope, g, t, lane, sc.base_cos(slot), sc.base_sin(slot));
+    stage_carry<BN>(sc.tile(slot), p.causal, g, t, lane);
+  }
+  // Each warp starts the load of its first `pre` blocks while the tile's main loop is still running.
+  template <int BN>
+  static __device__ __forceinline__ void prologue(const Params&, const EpiMaps& maps, const GemmGeom& g,
+                                                  const TileCtx& t, int warp_in_epi, int epi_tid, float*, EpiIO& io,
+                                                  int) {
     const int half = warp_in_epi >> 2, quarter = (warp_in_epi + 2) & 3;
     if (t.u0 + 16 * half < g.pair_q) fetch_pre(maps, t, io, quarter, epi_tid & 31, half, 0);
-    const RopeScratch<BN> rs(scratch + 5 * BN);
-    rope_stage<BN>(p.rope, maps, g, t, epi_tid, rs, io);
-    for (int c = epi_tid; c < BN; c += kEpiThreads) {
-      bool ok;
-      const int col = paired_col<BN>(g, t, c, &ok);
-      scratch[c] = ok ? __ldg(p.bias + col) : 0.f;
-    }
-    stage_carry<BN>(scratch + BN, p.causal, g, t, epi_tid);
-    named_bar_sync(kEpiBarrier, kEpiThreads);
   }
 
   template <int BN>
   static __device__ __forceinline__ void run(const Params& p, const EpiMaps& maps, const GemmGeom& g, const TileCtx& t,
                                              uint32_t tmem_acc, int quarter, int lane, int half, int, float* scratch,
-                                             EpiIO& io, int) {
-    const float* bias = scratch;
-    const float* carry = scratch + BN + quarter * BN;
-    const RopeScratch<BN> rs(scratch + 5 * BN);
-    rope_wait(p.rope, t, io);
+                                             EpiIO& io, int iter) {
+    const Scratch<BN> sc(scratch);
+    const int slot = iter & 1;
+    const float* bias = sc.cols();
+    const float* carry = sc.tile(slot) + quarter * BN;
+    const RopeView rs{sc.base_cos(slot), sc.base_sin(slot), sc.lane()};
     const bool stepped = p.rope.step_of(t.sec) != 0;
     const int y = t.row0 + quarter * 32;
     const float inv_n = 1.f / static_cast<float>(p.causal.token_offset + y + lane + 1);
@@ -339,9 +367,12 @@ struct EpiGateBwdCausal {
   // blocks), then dz first | dz partner | suf first | suf partner output blocks
   static constexpr int kStageBytes = 12288;
   static constexpr int kSmemBytes = 0;
+  static constexpr bool kStager = true;
+  template <int BN>
+  using Scratch = PairScratch<BN, 1, 4, 1>;  // columns: bias; tile: forward carries; sums: dbias
   template <int BN>
   static constexpr int smem_bytes() {
-    return (4 * BN + BN + 4 * BN) * 4 + RopeScratch<BN>::kBytes;
+    return Scratch<BN>::kBytes;
   }
 
   static __device__ __forceinline__ void fetch_in(const EpiMaps& maps, const TileCtx& t, EpiIO& io, int quarter,
@@ -358,32 +389,39 @@ struct EpiGateBwdCausal {
   }
 
   template <int BN>
-  static __device__ __forceinline__ void prologue(const Params& p, const EpiMaps& maps, const GemmGeom& g,
-                                                  const TileCtx& t, int warp_in_epi, int epi_tid, float* scratch,
-                                                  EpiIO& io, int) {
-    named_bar_sync(kEpiBarrier, kEpiThreads);
+  static __device__ __forceinline__ uint32_t stage_cols(const Params& p, const EpiMaps& maps, const GemmGeom& g,
+                                                        const TileCtx& t, int lane, float* scratch, uint64_t* bar) {
+    const Scratch<BN> sc(scratch);
+    const uint32_t tx = rope_stage_lane<BN>(p.rope, maps, g, t, lane, sc.lane(), bar);
+    stage_paired_vector<BN>(sc.cols(), p.bias, g, t, lane);
+    return tx;
+  }
+  template <int BN>
+  static __device__ __forceinline__ void stage_tile(const Params& p, const EpiMaps&, const GemmGeom& g,
+                                                    const TileCtx& t, int lane, float* scratch, int slot) {
+    const Scratch<BN> sc(scratch);
+    rope_stage_base<BN>(p.rope, g, t, lane, sc.base_cos(slot), sc.base_sin(slot));
+    stage_carry<BN>(sc.tile(slot), p.causal, g, t, lane);
+  }
+  // Each warp starts the load of its first input blocks while the tile's main loop is still running.
+  template <int BN>
+  static __device__ __forceinline__ void prologue(const Params&, const EpiMaps& maps, const GemmGeom& g,
+                                                  const TileCtx& t, int warp_in_epi, int epi_tid, float*, EpiIO& io,
+                                                  int) {
     const int half = warp_in_epi >> 2, quarter = (warp_in_epi + 2) & 3;
     if (t.u0 + 16 * half < g.pair_q) fetch_in(maps, t, io, quarter, epi_tid & 31, half, 0);
-    const RopeScratch<BN> rs(scratch + 9 * BN);
-    rope_stage<BN>(p.rope, maps, g, t, epi_tid, rs, io);
-    for (int c = epi_tid; c < BN; c += kEpiThreads) {
-      bool ok;
-      const int col = paired_col<BN>(g, t, c, &ok);
-      scratch[4 * BN + c] = ok ? __ldg(p.bias + col) : 0.f;
-    }
-    stage_carry<BN>(scratch + 5 * BN, p.causal, g, t, epi_tid);
-    named_bar_sync(kEpiBarrier, kEpiThreads);
   }
 
   template <int BN>
   static __device__ __forceinline__ void run(const Params& p, const EpiMaps& maps, const GemmGeom& g, const TileCtx& t,
-                                             uint32_t tmem_acc, int quarter, int lane, int half, int epi_tid,
-                                             float* scratch, EpiIO& io, int) {
-    float* buf_b = scratch;
-    const float* bias = scratch + 4 * BN;
-    const float* carry = scratch + 5 * BN + quarter * BN;
-    const RopeScratch<BN> rs(scratch + 9 * BN);
-    rope_wait(p.rope, t, io);
+                                             uint32_t tmem_acc, int quarter, int lane, int half, int,
+                                             float* scratch, EpiIO& io, int iter) {
+    const Scratch<BN> sc(scratch);
+    const int slot = iter & 1;
+    float* buf_b = sc.sums(slot);
+    const float* bias = sc.cols();
+    const float* carry = sc.tile(slot) + quarter * BN;
+    const RopeView rs{sc.base_cos(slot), sc.base_sin(slot), sc.lane()};
     const bool stepped = p.rope.step_of(t.sec) != 0;
     const int y = t.row0 + quarter * 32;
     const int grp = (t.row0 >> 5) + quarter;
@@ -468,8 +506,8 @@ struct EpiGateBwdCausal {
       if (lane < 16) b1p[lane] = z[0];
       else b1p[BN / 2 + lane - 16] = z[0];
     }
-    named_bar_sync(kEpiBarrier, kEpiThreads);
-    for (int c = epi_tid; c < BN; c += kEpiThreads) {
+    if (!tail_last_warp(io, slot, lane)) return;
+    for (int c = lane; c < BN; c += 32) {
       bool ok;
       const int col = paired_col<BN>(g, t, c, &ok);
       if (ok && t.rows_valid > 0) {

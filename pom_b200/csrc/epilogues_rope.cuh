@@ -38,68 +38,112 @@ struct RopeEpi {
 // 16-byte piece j (0..1) of row `lane` inside a 32-row x 32-byte block stored with the 32-byte swizzle.
 __device__ __forceinline__ uint32_t swz32(int lane, int j) { return lane * 32 + ((j ^ ((lane >> 2) & 1)) << 4); }
 
-template <int BN>
-struct RopeScratch {
+// Scratch shared by the epilogue warps and the stager warp of a paired epilogue (floats unless noted):
+//   [column constants: COLF x BN]                       kept while consecutive tiles of the CTA share their columns
+//   [slot 0 | slot 1: tile constants TILEF x BN, cos | sin of the base position of the four row groups: 4 x BN]
+//   [column-sum exchange: 2 tile parities x SUMS x 4 quarters x BN]
+//   [lane tables, 1 KiB aligned: per 16-pair sub-unit a 32 x 16 cos block and a 32 x 16 sin block]
+// The stager fills slot (i & 1) for tile i while the epilogue warps read slot ((i - 1) & 1).
+template <int BN, int COLF, int TILEF, int SUMS>
+struct PairScratch {
   static constexpr int kHalf = BN / 2;
-  static constexpr int kSubs = BN / 32;                 // 16-pair sub-units per tile
-  static constexpr int kBaseFloats = 2 * 4 * kHalf;     // cos | sin of the base position of the four row groups
-  static constexpr int kLaneBytes = kSubs * 4096;       // per sub-unit: 32 x 16 cos block, 32 x 16 sin block
-  static constexpr int kBytes = kBaseFloats * 4 + kLaneBytes + 1024;  // + slack to align the lane blocks
-  float* base_cos;
-  float* base_sin;
-  uint8_t* lane;
-  __device__ __forceinline__ explicit RopeScratch(float* p) {
-    base_cos = p;
-    base_sin = p + 4 * kHalf;
-    lane = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p + kBaseFloats) + 1023) & ~uintptr_t(1023));
+  static constexpr int kSubs = BN / 32;
+  static constexpr int kSlotFloats = TILEF * BN + 4 * BN;
+  static constexpr int kSumFloats = SUMS * 4 * BN;
+  static constexpr int kFloats = COLF * BN + 2 * kSlotFloats + 2 * kSumFloats;
+  static constexpr int kLaneBytes = kSubs * 4096;
+  static constexpr int kBytes = kFloats * 4 + kLaneBytes + 1024;  // + slack to align the lane blocks
+  float* p;
+  __device__ __forceinline__ explicit PairScratch(float* scratch) : p(scratch) {}
+  __device__ __forceinline__ float* cols() const { return p; }
+  __device__ __forceinline__ float* tile(int slot) const { return p + COLF * BN + slot * kSlotFloats; }
+  __device__ __forceinline__ float* base_cos(int slot) const { return tile(slot) + TILEF * BN; }
+  __device__ __forceinline__ float* base_sin(int slot) const { return base_cos(slot) + 4 * kHalf; }
+  __device__ __forceinline__ float* sums(int parity) const { return p + COLF * BN + 2 * kSlotFloats + parity * kSumFloats; }
+  __device__ __forceinline__ uint8_t* lane() const {
+    return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p + kFloats) + 1023) & ~uintptr_t(1023));
   }
 };
 
-// Runs in every epilogue thread after the barrier that ends the previous tile: starts the bulk loads of the
-// lane tables (one thread) and stages the base rows of the four 32-row groups.
+// What an epilogue warp needs of the rotary constants of its tile.
+struct RopeView {
+  const float* base_cos;  // [4 quarters][BN/2]
+  const float* base_sin;
+  const uint8_t* lane;
+};
+
+// Stager warp: starts the bulk loads of the lane tables of the tile's columns on `bar`; returns their bytes.
 template <int BN>
-__device__ __forceinline__ void rope_stage(const RopeEpi& r, const EpiMaps& maps, const GemmGeom& g, const TileCtx& t,
-                                           int epi_tid, const RopeScratch<BN>& rs, EpiIO& io) {
-  constexpr int kHalf = BN / 2;
-  const int sec = t.sec;
-  if (epi_tid == 0 && r.step_of(sec) != 0 && t.rows_valid > 0 && t.live) {
-    const int nsub = min(BN / 32, (g.pair_q - t.u0 + 15) >> 4);
-    mbar_expect_tx(io.shared_bar, static_cast<uint32_t>(nsub) * 4096u);
+__device__ __forceinline__ uint32_t rope_stage_lane(const RopeEpi& r, const EpiMaps& maps, const GemmGeom& g,
+                                                    const TileCtx& t, int lane, uint8_t* lane_tab, uint64_t* bar) {
+  if (!r.rotate || r.step_of(t.sec) == 0) return 0;
+  const int nsub = min(BN / 32, (g.pair_q - t.u0 + 15) >> 4);
+  if (lane == 0) {
     for (int su = 0; su < nsub; ++su) {
-      tma_load_2d(rs.lane + su * 4096, &maps.lane[2 * sec], io.shared_bar, t.u0 + 16 * su, 0);
-      tma_load_2d(rs.lane + su * 4096 + 2048, &maps.lane[2 * sec + 1], io.shared_bar, t.u0 + 16 * su, 0);
+      tma_load_2d(lane_tab + su * 4096, &maps.lane[2 * t.sec], bar, t.u0 + 16 * su, 0);
+      tma_load_2d(lane_tab + su * 4096 + 2048, &maps.lane[2 * t.sec + 1], bar, t.u0 + 16 * su, 0);
     }
   }
+  return static_cast<uint32_t>(nsub) * 4096u;
+}
+
+// Stager warp: cos / sin of the base position of the tile's four 32-row groups for its BN/2 pairs, four pairs per
+// load (pair_q and the tile's first pair are multiples of 4, the tables 16-byte aligned: the lane-table tensor maps
+// have the same needs).
+template <int BN>
+__device__ __forceinline__ void rope_stage_base(const RopeEpi& r, const GemmGeom& g, const TileCtx& t, int lane,
+                                                float* base_cos, float* base_sin) {
+  constexpr int kHalf = BN / 2;
+  constexpr int kVec = kHalf / 4;  // float4 per row group
+  const int sec = t.sec;
   const int which = r.pos_stride == 2 ? sec : 0;
   const float* __restrict__ cosp = r.cos_of(sec);
   const float* __restrict__ sinp = r.sin_of(sec);
   const long long len = r.len_of(sec);
-  for (int idx = epi_tid; idx < 4 * kHalf; idx += kEpiThreads) {
-    const int quarter = idx / kHalf, j = idx - quarter * kHalf;
+  long long pos[4];
+#pragma unroll
+  for (int quarter = 0; quarter < 4; ++quarter) {
+    const int n = t.row0 + 32 * quarter;
+    long long p = 0;
+    if (r.rotate && n < g.rows_per_batch) p = __ldg(r.pos + static_cast<long long>(n) * r.pos_stride + which);
+    pos[quarter] = p < 0 ? 0 : (p >= len ? len - 1 : p);  // the host validates positions; never read outside the table
+  }
+  static_assert((4 * kVec) % 32 == 0, "tile width");
+#pragma unroll
+  for (int k = 0; k < 4 * kVec / 32; ++k) {
+    const int idx = lane + 32 * k;
+    const int quarter = idx / kVec, j = (idx - quarter * kVec) * 4;
     const int n = t.row0 + 32 * quarter, u = t.u0 + j;
-    float c = 1.f, s = 0.f;
+    float4 c = make_float4(1.f, 1.f, 1.f, 1.f), s = make_float4(0.f, 0.f, 0.f, 0.f);
     if (r.rotate && n < g.rows_per_batch && u < g.pair_q) {
-      long long p = __ldg(r.pos + static_cast<long long>(n) * r.pos_stride + which);
-      p = p < 0 ? 0 : (p >= len ? len - 1 : p);  // the host validates positions; never read outside the table
-      c = __ldg(cosp + p * g.pair_q + u);
-      s = __ldg(sinp + p * g.pair_q + u);
+      const long long p = quarter == 0 ? pos[0] : quarter == 1 ? pos[1] : quarter == 2 ? pos[2] : pos[3];
+      c = __ldg(reinterpret_cast<const float4*>(cosp + p * g.pair_q + u));
+      s = __ldg(reinterpret_cast<const float4*>(sinp + p * g.pair_q + u));
     }
-    rs.base_cos[idx] = c;
-    rs.base_sin[idx] = s;
+    *reinterpret_cast<float4*>(base_cos + 4 * idx) = c;
+    *reinterpret_cast<float4*>(base_sin + 4 * idx) = s;
   }
 }
 
-// All lanes of every epilogue warp: wait until this tile's lane tables have landed (when it uses any).
-__device__ __forceinline__ void rope_wait(const RopeEpi& r, const TileCtx& t, EpiIO& io) {
-  if (r.step_of(t.sec) != 0 && t.rows_valid > 0 && t.live) {
-    mbar_wait(io.shared_bar, io.shared_phase, io.abort_flag, io.status, kStatusEpilogueTimeout);
-    io.shared_phase ^= 1u;
+// Every epilogue warp, when its entries of the column-sum exchange buffers of this tile are written: returns true in
+// the warp that arrives last, which then adds the four quarters up and owns the buffers until it returns from run().
+__device__ __forceinline__ bool tail_last_warp(EpiIO& io, int parity, int lane) {
+  __syncwarp();
+  int old = 0;
+  if (lane == 0) {
+    __threadfence_block();
+    old = atomicAdd(&io.tail_count[parity], 1);
   }
+  old = __shfl_sync(0xffffffffu, old, 0);
+  if (old != kEpiWarps - 1) return false;
+  if (lane == 0) io.tail_count[parity] = 0;
+  __threadfence_block();
+  return true;
 }
 
 // cos/sin of this lane's token for pairs [16 su + i, 16 su + i + 4) of the tile.
 template <int BN>
-__device__ __forceinline__ void rope_cs4(const RopeScratch<BN>& rs, bool stepped, int quarter, int lane, int su, int i,
+__device__ __forceinline__ void rope_cs4(const RopeView& rs, bool stepped, int quarter, int lane, int su, int i,
                                          float (&c)[4], float (&s)[4]) {
   const float4 C0 = *reinterpret_cast<const float4*>(rs.base_cos + quarter * (BN / 2) + 16 * su + i);
   const float4 S0 = *reinterpret_cast<const float4*>(rs.base_sin + quarter * (BN / 2) + 16 * su + i);
@@ -175,32 +219,43 @@ struct EpiCtxRope {
   static constexpr int kMaxK = 4;
   static constexpr int kStageBytes = kEpiStageBytes;  // two alternating sets of {first, partner} 1 KiB blocks
   static constexpr int kSmemBytes = 0;
+  static constexpr bool kStager = true;
+  template <int BN>
+  using Scratch = PairScratch<BN, kMaxK, 0, 1>;  // columns: coefficients [degree][BN]; sums: the token sums
   template <int BN>
   static constexpr int smem_bytes() {
-    return (4 * BN + kMaxK * BN) * 4 + RopeScratch<BN>::kBytes;
+    return Scratch<BN>::kBytes;
   }
 
   template <int BN>
-  static __device__ __forceinline__ void prologue(const Params& p, const EpiMaps& maps, const GemmGeom& g,
-                                                  const TileCtx& t, int, int epi_tid, float* scratch, EpiIO& io, int) {
-    named_bar_sync(kEpiBarrier, kEpiThreads);  // everybody has left the previous tile: scratch may be rewritten
-    const RopeScratch<BN> rs(scratch + 4 * BN + kMaxK * BN);
-    rope_stage<BN>(p.rope, maps, g, t, epi_tid, rs, io);
-    float* cst = scratch + 4 * BN;
+  static __device__ __forceinline__ uint32_t stage_cols(const Params& p, const EpiMaps& maps, const GemmGeom& g,
+                                                        const TileCtx& t, int lane, float* scratch, uint64_t* bar) {
+    const Scratch<BN> sc(scratch);
+    const uint32_t tx = rope_stage_lane<BN>(p.rope, maps, g, t, lane, sc.lane(), bar);
+    float* cst = sc.cols();
     const int K = p.K;
-    for (int idx = epi_tid; idx < BN * K; idx += kEpiThreads) {
+    for (int idx = lane; idx < BN * K; idx += 32) {
       const int c = idx / K, i = idx - c * K;
       bool ok;
       const int col = paired_col<BN>(g, t, c, &ok);
       cst[i * BN + c] = ok ? __ldg(p.coeff + static_cast<long long>(col) * K + i) : 0.f;
     }
-    named_bar_sync(kEpiBarrier, kEpiThreads);
+    return tx;
   }
+  template <int BN>
+  static __device__ __forceinline__ void stage_tile(const Params& p, const EpiMaps&, const GemmGeom& g,
+                                                    const TileCtx& t, int lane, float* scratch, int slot) {
+    const Scratch<BN> sc(scratch);
+    rope_stage_base<BN>(p.rope, g, t, lane, sc.base_cos(slot), sc.base_sin(slot));
+  }
+  template <int BN>
+  static __device__ __forceinline__ void prologue(const Params&, const EpiMaps&, const GemmGeom&, const TileCtx&, int,
+                                                  int, float*, EpiIO&, int) {}
 
   template <int KT, int BN>
   static __device__ __forceinline__ void body(const Params& p, const EpiMaps& maps, const GemmGeom& g,
                                               const TileCtx& t, uint32_t tmem_acc, int quarter, int lane, int half,
-                                              float* buf, const float* cst, const RopeScratch<BN>& rs, EpiIO& io) {
+                                              float* buf, const float* cst, const RopeView& rs, EpiIO& io) {
     const int row = quarter * 32 + lane;
     const bool weighted = p.row_weight != nullptr;
     float w = 1.f;
@@ -265,20 +320,21 @@ struct EpiCtxRope {
 
   template <int BN>
   static __device__ __forceinline__ void run(const Params& p, const EpiMaps& maps, const GemmGeom& g, const TileCtx& t,
-                                             uint32_t tmem_acc, int quarter, int lane, int half, int epi_tid,
-                                             float* scratch, EpiIO& io, int) {
-    float* buf = scratch;
-    const float* cst = scratch + 4 * BN;
-    const RopeScratch<BN> rs(scratch + 4 * BN + kMaxK * BN);
-    rope_wait(p.rope, t, io);
+                                             uint32_t tmem_acc, int quarter, int lane, int half, int,
+                                             float* scratch, EpiIO& io, int iter) {
+    const Scratch<BN> sc(scratch);
+    const int slot = iter & 1;
+    float* buf = sc.sums(slot);
+    const float* cst = sc.cols();
+    const RopeView rs{sc.base_cos(slot), sc.base_sin(slot), sc.lane()};
     switch (p.K) {
       case 1: body<1, BN>(p, maps, g, t, tmem_acc, quarter, lane, half, buf, cst, rs, io); break;
       case 2: body<2, BN>(p, maps, g, t, tmem_acc, quarter, lane, half, buf, cst, rs, io); break;
       case 3: body<3, BN>(p, maps, g, t, tmem_acc, quarter, lane, half, buf, cst, rs, io); break;
       default: body<4, BN>(p, maps, g, t, tmem_acc, quarter, lane, half, buf, cst, rs, io); break;
     }
-    named_bar_sync(kEpiBarrier, kEpiThreads);
-    for (int c = epi_tid; c < BN; c += kEpiThreads) {
+    if (!tail_last_warp(io, slot, lane)) return;
+    for (int c = lane; c < BN; c += 32) {
       bool ok;
       const int col = paired_col<BN>(g, t, c, &ok);
       if (ok && t.rows_valid > 0) {
@@ -289,15 +345,14 @@ struct EpiCtxRope {
   }
 };
 
-// Stage bias and one H vector for the tile's (paired) columns: cst[0..BN) = bias, cst[BN..2BN) = H[b, :].
+// Stager warp: one per-column vector (bias) for the tile's paired columns.
 template <int BN>
-__device__ __forceinline__ void stage_bias_h_paired(float* cst, const float* bias, const float* hrow, const GemmGeom& g,
-                                                    const TileCtx& t, int epi_tid) {
-  for (int c = epi_tid; c < BN; c += kEpiThreads) {
+__device__ __forceinline__ void stage_paired_vector(float* dst, const float* src, const GemmGeom& g, const TileCtx& t,
+                                                    int lane) {
+  for (int c = lane; c < BN; c += 32) {
     bool ok;
     const int col = paired_col<BN>(g, t, c, &ok);
-    cst[c] = ok ? __ldg(bias + col) : 0.f;
-    cst[BN + c] = ok ? __ldg(hrow + col) : 0.f;
+    dst[c] = ok ? __ldg(src + col) : 0.f;
   }
 }
 
@@ -313,28 +368,42 @@ struct EpiGateRope {
   };
   static constexpr int kStageBytes = kEpiStageBytes;  // z first | z partner | SH first | SH partner, 1 KiB each
   static constexpr int kSmemBytes = 0;
+  static constexpr bool kStager = true;
+  template <int BN>
+  using Scratch = PairScratch<BN, 1, 1, 0>;  // columns: bias; tile: H of the tile's batch
   template <int BN>
   static constexpr int smem_bytes() {
-    return 2 * BN * 4 + RopeScratch<BN>::kBytes;
+    return Scratch<BN>::kBytes;
   }
 
   template <int BN>
-  static __device__ __forceinline__ void prologue(const Params& p, const EpiMaps& maps, const GemmGeom& g,
-                                                  const TileCtx& t, int, int epi_tid, float* scratch, EpiIO& io, int) {
-    named_bar_sync(kEpiBarrier, kEpiThreads);
-    const RopeScratch<BN> rs(scratch + 2 * BN);
-    rope_stage<BN>(p.rope, maps, g, t, epi_tid, rs, io);
-    stage_bias_h_paired<BN>(scratch, p.bias, p.H + static_cast<long long>(t.b) * p.h_batch_stride, g, t, epi_tid);
-    named_bar_sync(kEpiBarrier, kEpiThreads);
+  static __device__ __forceinline__ uint32_t stage_cols(const Params& p, const EpiMaps& maps, const GemmGeom& g,
+                                                        const TileCtx& t, int lane, float* scratch, uint64_t* bar) {
+    const Scratch<BN> sc(scratch);
+    const uint32_t tx = rope_stage_lane<BN>(p.rope, maps, g, t, lane, sc.lane(), bar);
+    stage_paired_vector<BN>(sc.cols(), p.bias, g, t, lane);
+    return tx;
   }
+  template <int BN>
+  static __device__ __forceinline__ void stage_tile(const Params& p, const EpiMaps&, const GemmGeom& g,
+                                                    const TileCtx& t, int lane, float* scratch, int slot) {
+    const Scratch<BN> sc(scratch);
+    rope_stage_base<BN>(p.rope, g, t, lane, sc.base_cos(slot), sc.base_sin(slot));
+    stage_paired_vector<BN>(sc.tile(slot), p.H + static_cast<long long>(t.b) * p.h_batch_stride, g, t, lane);
+  }
+  template <int BN>
+  static __device__ __forceinline__ void prologue(const Params&, const EpiMaps&, const GemmGeom&, const TileCtx&, int,
+                                                  int, float*, EpiIO&, int) {}
 
   template <int BN>
   static __device__ __forceinline__ void run(const Params& p, const EpiMaps& maps, const GemmGeom& g, const TileCtx& t,
                                              uint32_t tmem_acc, int quarter, int lane, int half, int, float* scratch,
-                                             EpiIO& io, int) {
-    const float* cst = scratch;
-    const RopeScratch<BN> rs(scratch + 2 * BN);
-    rope_wait(p.rope, t, io);
+                                             EpiIO& io, int iter) {
+    const Scratch<BN> sc(scratch);
+    const int slot = iter & 1;
+    const float* bias = sc.cols();
+    const float* hrow = sc.tile(slot);
+    const RopeView rs{sc.base_cos(slot), sc.base_sin(slot), sc.lane()};
     const bool stepped = p.rope.step_of(t.sec) != 0;
     const int y = t.row0 + quarter * 32;
 #pragma unroll 1
@@ -350,10 +419,10 @@ struct EpiGateRope {
       round_pack16<16>(v, pz2);
 #pragma unroll
       for (int i = 0; i < 16; i += 4) {
-        const float4 b1 = *reinterpret_cast<const float4*>(cst + 16 * su + i);
-        const float4 b2 = *reinterpret_cast<const float4*>(cst + BN / 2 + 16 * su + i);
-        const float4 h1 = *reinterpret_cast<const float4*>(cst + BN + 16 * su + i);
-        const float4 h2 = *reinterpret_cast<const float4*>(cst + BN + BN / 2 + 16 * su + i);
+        const float4 b1 = *reinterpret_cast<const float4*>(bias + 16 * su + i);
+        const float4 b2 = *reinterpret_cast<const float4*>(bias + BN / 2 + 16 * su + i);
+        const float4 h1 = *reinterpret_cast<const float4*>(hrow + 16 * su + i);
+        const float4 h2 = *reinterpret_cast<const float4*>(hrow + BN / 2 + 16 * su + i);
         const float bb1[4] = {b1.x, b1.y, b1.z, b1.w}, bb2[4] = {b2.x, b2.y, b2.z, b2.w};
         const float hh1[4] = {h1.x, h1.y, h1.z, h1.w}, hh2[4] = {h2.x, h2.y, h2.z, h2.w};
         float c[4], s[4];
@@ -412,9 +481,12 @@ struct EpiGateBwdRope {
   // per warp: two alternating sets of {z first, z partner} input blocks, then {dz first, dz partner} output blocks
   static constexpr int kStageBytes = 8192;
   static constexpr int kSmemBytes = 0;
+  static constexpr bool kStager = true;
+  template <int BN>
+  using Scratch = PairScratch<BN, 1, 1, 2>;  // columns: bias; tile: H of the batch; sums: dH then dbias
   template <int BN>
   static constexpr int smem_bytes() {
-    return (2 * 4 * BN + 2 * BN) * 4 + RopeScratch<BN>::kBytes;
+    return Scratch<BN>::kBytes;
   }
 
   static __device__ __forceinline__ void fetch_z(const EpiMaps& maps, const TileCtx& t, EpiIO& io, int quarter,
@@ -428,28 +500,40 @@ struct EpiGateBwdRope {
   }
 
   template <int BN>
-  static __device__ __forceinline__ void prologue(const Params& p, const EpiMaps& maps, const GemmGeom& g,
-                                                  const TileCtx& t, int warp_in_epi, int epi_tid, float* scratch,
-                                                  EpiIO& io, int) {
-    named_bar_sync(kEpiBarrier, kEpiThreads);
+  static __device__ __forceinline__ uint32_t stage_cols(const Params& p, const EpiMaps& maps, const GemmGeom& g,
+                                                        const TileCtx& t, int lane, float* scratch, uint64_t* bar) {
+    const Scratch<BN> sc(scratch);
+    const uint32_t tx = rope_stage_lane<BN>(p.rope, maps, g, t, lane, sc.lane(), bar);
+    stage_paired_vector<BN>(sc.cols(), p.bias, g, t, lane);
+    return tx;
+  }
+  template <int BN>
+  static __device__ __forceinline__ void stage_tile(const Params& p, const EpiMaps&, const GemmGeom& g,
+                                                    const TileCtx& t, int lane, float* scratch, int slot) {
+    const Scratch<BN> sc(scratch);
+    rope_stage_base<BN>(p.rope, g, t, lane, sc.base_cos(slot), sc.base_sin(slot));
+    stage_paired_vector<BN>(sc.tile(slot), p.H + static_cast<long long>(t.b) * p.h_batch_stride, g, t, lane);
+  }
+  // Each warp starts the load of its first z blocks while the tile's main loop is still running.
+  template <int BN>
+  static __device__ __forceinline__ void prologue(const Params&, const EpiMaps& maps, const GemmGeom& g,
+                                                  const TileCtx& t, int warp_in_epi, int epi_tid, float*, EpiIO& io,
+                                                  int) {
     const int half = warp_in_epi >> 2, quarter = (warp_in_epi + 2) & 3;
     if (t.u0 + 16 * half < g.pair_q) fetch_z(maps, t, io, quarter, epi_tid & 31, half, 0);
-    const RopeScratch<BN> rs(scratch + 2 * 4 * BN + 2 * BN);
-    rope_stage<BN>(p.rope, maps, g, t, epi_tid, rs, io);
-    stage_bias_h_paired<BN>(scratch + 2 * 4 * BN, p.bias, p.H + static_cast<long long>(t.b) * p.h_batch_stride, g, t,
-                            epi_tid);
-    named_bar_sync(kEpiBarrier, kEpiThreads);
   }
 
   template <int BN>
   static __device__ __forceinline__ void run(const Params& p, const EpiMaps& maps, const GemmGeom& g, const TileCtx& t,
-                                             uint32_t tmem_acc, int quarter, int lane, int half, int epi_tid,
-                                             float* scratch, EpiIO& io, int) {
-    float* buf_h = scratch;
-    float* buf_b = scratch + 4 * BN;
-    const float* cst = scratch + 2 * 4 * BN;
-    const RopeScratch<BN> rs(scratch + 2 * 4 * BN + 2 * BN);
-    rope_wait(p.rope, t, io);
+                                             uint32_t tmem_acc, int quarter, int lane, int half, int,
+                                             float* scratch, EpiIO& io, int iter) {
+    const Scratch<BN> sc(scratch);
+    const int slot = iter & 1;
+    float* buf_h = sc.sums(slot);
+    float* buf_b = buf_h + 4 * BN;
+    const float* bias = sc.cols();
+    const float* hrow = sc.tile(slot);
+    const RopeView rs{sc.base_cos(slot), sc.base_sin(slot), sc.lane()};
     const bool stepped = p.rope.step_of(t.sec) != 0;
     const int y = t.row0 + quarter * 32;
     uint8_t* out_blk = io.buf0 + 4096;
@@ -480,10 +564,10 @@ struct EpiGateBwdRope {
       tmem_ld_wait();
 #pragma unroll
       for (int i = 0; i < 16; i += 4) {
-        const float4 b1 = *reinterpret_cast<const float4*>(cst + 16 * su + i);
-        const float4 b2 = *reinterpret_cast<const float4*>(cst + BN / 2 + 16 * su + i);
-        const float4 h1 = *reinterpret_cast<const float4*>(cst + BN + 16 * su + i);
-        const float4 h2 = *reinterpret_cast<const float4*>(cst + BN + BN / 2 + 16 * su + i);
+        const float4 b1 = *reinterpret_cast<const float4*>(bias + 16 * su + i);
+        const float4 b2 = *reinterpret_cast<const float4*>(bias + BN / 2 + 16 * su + i);
+        const float4 h1 = *reinterpret_cast<const float4*>(hrow + 16 * su + i);
+        const float4 h2 = *reinterpret_cast<const float4*>(hrow + BN / 2 + 16 * su + i);
         const float bb1[4] = {b1.x, b1.y, b1.z, b1.w}, bb2[4] = {b2.x, b2.y, b2.z, b2.w};
         const float hh1[4] = {h1.x, h1.y, h1.z, h1.w}, hh2[4] = {h2.x, h2.y, h2.z, h2.w};
         float c[4], s[4];
@@ -521,8 +605,8 @@ struct EpiGateBwdRope {
       if (lane < 16) h1p[lane] = v[0], b1p[lane] = z[0];
       else h1p[BN / 2 + lane - 16] = v[0], b1p[BN / 2 + lane - 16] = z[0];
     }
-    named_bar_sync(kEpiBarrier, kEpiThreads);
-    for (int c = epi_tid; c < BN; c += kEpiThreads) {
+    if (!tail_last_warp(io, slot, lane)) return;
+    for (int c = lane; c < BN; c += 32) {
       bool ok;
       const int col = paired_col<BN>(g, t, c, &ok);
       if (ok && t.rows_valid > 0) {

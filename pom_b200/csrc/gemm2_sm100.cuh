@@ -166,6 +166,11 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     }
     for (int w = 0; w < kEpiWarps; ++w) mbar_init(&sm.wload_bar[w], 1);
     mbar_init(sm.eshared_bar, 1);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&sm.sfull_bar[a], 1);
+      mbar_init(&sm.sempty_bar[a], kEpiWarps);
+      sm.tail_count[a] = 0;
+    }
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -192,12 +197,15 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
+      // paired columns: the leader's half of the B tile holds the first channels, the peer's their partners
+      auto b_col = [&](const TileCtx& tt) {
+        return geom.pair_q ? (rank == 0 ? tt.col0 : tt.col1) : tt.col0 + static_cast<int>(rank) * kHalfN;
+      };
       for (int unit = cluster_id; unit < total_units && alive; unit += n_clusters) {
         const TileCtx t = decode_pair_tile(geom, unit, BN, rank);
         const int kb0 = t.split * geom.kb_per_split;
         const int kb1 = t.live ? min(geom.k_blocks, kb0 + geom.kb_per_split) : kb0;
-        // paired columns: the leader's half of the B tile holds the first channels, the peer's their partners
-        const int bcol0 = geom.pair_q ? (rank == 0 ? t.col0 : t.col1) : t.col0 + static_cast<int>(rank) * kHalfN;
+        const int bcol0 = b_col(t);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, status, kStatusProducerTimeout)) {
             alive = false;
@@ -286,7 +294,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         for (int i = 0; i < 64; ++i) __nanosleep(2000);
       }
     }
-  } else {
+  } else if (warp < kStagerWarp) {
     // ------------------------------------------------------------ epilogue (both CTAs, own rows)
     const int quarter = warp & 3;
     const int half = (warp - 2) >> 2;
@@ -300,6 +308,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     io.shared_phase = 0;
     io.abort_flag = abort_flag;
     io.status = status;
+    io.tail_count = sm.tail_count;
     const uint32_t tempty_leader[2] = {map_to_cta(smem_u32(&tempty_bar[0]), 0), map_to_cta(smem_u32(&tempty_bar[1]), 0)};
     int iter = 0;
     for (int unit = cluster_id; unit < total_units; unit += n_clusters, ++iter) {
@@ -307,16 +316,31 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       const int acc = iter & 1;
       const uint32_t acc_phase = (iter >> 1) & 1u;
       Epi::template prologue<BN>(ep, maps, geom, t, warp - 2, epi_tid, epi_scratch, io, iter);
-      const bool ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, status, kStatusEpilogueTimeout);
-      if (named_bar_any(kEpiBarrier, kEpiThreads, !ok)) break;
+      bool ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, status, kStatusEpilogueTimeout);
+      if constexpr (Epi::kStager) {
+        if (ok) ok = mbar_wait(&sm.sfull_bar[acc], acc_phase, abort_flag, status, kStatusEpilogueTimeout);
+        if (!__all_sync(0xffffffffu, ok)) break;
+      } else {
+        if (named_bar_any(kEpiBarrier, kEpiThreads, !ok)) break;
+      }
       tc_fence_after();
       const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(acc * BN) + (static_cast<uint32_t>(quarter * 32) << 16);
       Epi::template run<BN>(ep, maps, geom, t, tmem_acc, quarter, lane, half, epi_tid, epi_scratch, io, iter);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(tempty_leader[acc]);
+      if (lane == 0) {
+        mbar_arrive_cluster(tempty_leader[acc]);
+        if constexpr (Epi::kStager) mbar_arrive(&sm.sempty_bar[acc]);
+      }
     }
     if (lane == 0) bulk_wait_all();
+  } else {
+    // ------------------------------------------------------------ stager (both CTAs, own rows)
+    if constexpr (Epi::kStager) {
+      stager_loop<BN, Epi>(ep, maps, geom, cluster_id, n_clusters, total_units,
+                           [&](int unit) { return decode_pair_tile(geom, unit, BN, rank); }, lane, epi_scratch,
+                           sm.sfull_bar, sm.sempty_bar, abort_flag, status);
+    }
   }
 
   tc_fence_before();

@@ -151,6 +151,10 @@ inline int build_maps(const Operands& o, int b_rows, CUtensorMap* tmA, CUtensorM
   return rc;
 }
 
+// Diagnostic knob (pom_set_gemm_mode).  Units digit: 0 automatic choice, 1 always the one-CTA kernel, 2 always the
+// two-CTA (pair) kernel; tens digit: 1 / 2 / 3 forces 128 / 192 / 256 columns per tile.
+extern std::atomic<int> g_gemm_mode;
+
 inline GemmGeom make_geom(const Operands& o, int bn, int split_k) {
   GemmGeom g;
   g.batches = o.batches;
@@ -181,9 +185,6 @@ inline int check_operands(const Operands& o) {
   return POM_OK;
 }
 
-// 0: automatic choice, 1: always the one-CTA kernel, 2: always the two-CTA (pair) kernel.
-extern std::atomic<int> g_gemm_mode;
-
 template <class Kern>
 int set_smem_once(Kern kern, int smem, bool* done) {
   if (*done) return POM_OK;
@@ -193,6 +194,17 @@ int set_smem_once(Kern kern, int smem, bool* done) {
   }
   *done = true;
   return POM_OK;
+}
+
+// Epilogues whose constants depend on the tile's columns (Epi::kStager: lane tables, coefficients, bias) run
+// column-stationary when that costs little: a grid of rows x n_tiles CTAs (or clusters) walking bands of `rows`
+// m-tiles gives every CTA the same columns in all of its tiles, so those constants are loaded once per CTA.
+// Returns the rows per band, or 0 to keep the default schedule (more than 1/16 of the SMs would idle, or the
+// problem has no second wave).
+inline int stationary_rows(long long units, int n_tiles, int slots) {
+  if (n_tiles > slots || units <= slots) return 0;
+  const int rows = slots / n_tiles;
+  return (slots - rows * n_tiles) * 16 <= slots ? rows : 0;
 }
 
 // One CTA per 128 x BN tile.
@@ -209,7 +221,11 @@ int launch(const Operands& o, int split_k, const EpiMaps& maps, const typename E
   if ((rc = set_smem_once(kern, smem, &attr_set))) return rc;
   const long long units = 1ll * g.batches * g.m_tiles_per_batch * g.n_tiles * g.split_k;
   if (units > INT32_MAX) return POM_ERR_TOO_LARGE;
-  const int grid = static_cast<int>(units < sm_count() ? units : sm_count());
+  int grid = static_cast<int>(units < sm_count() ? units : sm_count());
+  if constexpr (Epi::kStager) {
+    const int rows = g.split_k == 1 ? stationary_rows(units, g.n_tiles, sm_count()) : 0;
+    if (rows) grid = rows * g.n_tiles, g.group_m = rows;
+  }
   kern<<<grid, kGemmThreads, smem, st>>>(tmA, tmB, maps, g, ep, status);
   count_launch();
   return check_launch();
@@ -229,7 +245,11 @@ int launch_pair(const Operands& o, int split_k, const EpiMaps& maps, const typen
   if ((rc = set_smem_once(kern, smem, &attr_set))) return rc;
   const long long units = 1ll * g.batches * ((g.m_tiles_per_batch + 1) / 2) * g.n_tiles * g.split_k;
   if (units > INT32_MAX) return POM_ERR_TOO_LARGE;
-  const int clusters = static_cast<int>(units < sm_count() / 2 ? units : sm_count() / 2);
+  int clusters = static_cast<int>(units < sm_count() / 2 ? units : sm_count() / 2);
+  if constexpr (Epi::kStager) {
+    const int rows = g.split_k == 1 ? stationary_rows(units, g.n_tiles, sm_count() / 2) : 0;
+    if (rows) clusters = rows * g.n_tiles, g.group_m = 2 * rows;  // group_m counts m-tiles: two per pair
+  }
   kern<<<2 * clusters, kGemmThreads, smem, st>>>(tmA, tmB, maps, g, ep, status);
   count_launch();
   return check_launch();

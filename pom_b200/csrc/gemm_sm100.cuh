@@ -29,8 +29,11 @@ namespace pomk {
 constexpr int kBM = 128;          // rows per tile (= TMEM lanes)
 constexpr int kBK = 64;           // K elements per pipeline stage (= one 128-byte swizzle row)
 constexpr int kEpiColSplit = 2;     // epilogue warps per 32-lane quarter; they interleave the 32-column chunks
-constexpr int kGemmThreads = 64 + 128 * kEpiColSplit;
 constexpr int kEpiThreads = 128 * kEpiColSplit;
+// warp 0: TMA producer, warp 1: MMA issuer, warps 2..9: epilogue, warp 10: stager (fills the constants of the
+// epilogue's next tile while the epilogue warps work on the current one; idle for epilogues that have none)
+constexpr int kStagerWarp = 2 + 4 * kEpiColSplit;
+constexpr int kGemmThreads = 32 * (kStagerWarp + 1);
 constexpr int kEpiBarrier = 1;
 
 enum GemmStatus : int {
@@ -143,6 +146,7 @@ struct EpiIO {
   uint32_t shared_phase;
   volatile int* abort_flag;
   int* status;
+  int* tail_count;  // [2] per tile parity: epilogue warps that have finished their share of a tile (stager epilogues)
 };
 
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
@@ -177,7 +181,8 @@ constexpr int kEpiWarps = 4 * kEpiColSplit;
 constexpr int kEpiStageBytes = 4096;  // default per epilogue warp: two 2 KiB blocks for bulk stores / loads
 
 // Carves the dynamic shared memory of both GEMM kernels:
-//   [pipeline tiles][epilogue staging 8 x 4 KiB][barriers, TMEM holder, abort flag: 256 B][epilogue scratch]
+//   [pipeline tiles][epilogue staging 8 x 4 KiB][barriers, TMEM holder, abort flag: 512 B][epilogue scratch]
+constexpr int kBarrierBytes = 512;
 template <int STAGES>
 struct SmemPlan {
   uint8_t* tiles;
@@ -188,8 +193,11 @@ struct SmemPlan {
   uint64_t* tempty_bar;  // [2]       epilogue -> MMA
   uint64_t* wload_bar;   // [8]       per epilogue warp: bulk loads into its staging block
   uint64_t* eshared_bar; // [1]       bulk loads that all epilogue warps consume
+  uint64_t* sfull_bar;   // [2]       stager -> epilogue: the constants of a tile are in their slot
+  uint64_t* sempty_bar;  // [2]       epilogue -> stager: every epilogue warp has finished with the slot
   uint32_t* tmem_holder;
   volatile int* abort_flag;
+  int* tail_count;
   float* epi_scratch;
   __device__ __forceinline__ SmemPlan(uint8_t* raw, int stage_bytes, int epi_stage_bytes = kEpiStageBytes) {
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
@@ -202,12 +210,16 @@ struct SmemPlan {
     tempty_bar = bars + 2 * STAGES + 2;
     wload_bar = bars + 2 * STAGES + 4;
     eshared_bar = bars + 2 * STAGES + 4 + kEpiWarps;
-    tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 5 + kEpiWarps);
+    sfull_bar = bars + 2 * STAGES + 5 + kEpiWarps;
+    sempty_bar = bars + 2 * STAGES + 7 + kEpiWarps;
+    tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 9 + kEpiWarps);
     abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
-    epi_scratch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);
+    tail_count = reinterpret_cast<int*>(tmem_holder + 2);
+    static_assert((2 * STAGES + 11 + kEpiWarps) * 8 <= kBarrierBytes, "barrier area too small");
+    epi_scratch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + kBarrierBytes);
   }
   static constexpr int bytes(int stage_bytes, int epi_smem, int epi_stage_bytes = kEpiStageBytes) {
-    return STAGES * stage_bytes + kEpiWarps * epi_stage_bytes + 256 + epi_smem + 1024;  // + alignment slack
+    return STAGES * stage_bytes + kEpiWarps * epi_stage_bytes + kBarrierBytes + epi_smem + 1024;  // + alignment slack
   }
 };
 
@@ -230,7 +242,49 @@ constexpr int gemm_smem_bytes() {
 //        runs before the accumulator is ready: stages per-column constants, starts bulk loads
 //   template<int BN> static __device__ void run(const Params&, const EpiMaps&, const GemmGeom&, const TileCtx&,
 //        uint32_t tmem_acc, int quarter, int lane, int half, int epi_tid, float* scratch, EpiIO&, int tile_iter);
+//   static constexpr bool kStager;      true: the constants of a tile are filled by the stager warp, one tile ahead,
+//        into slot (tile_iter & 1) of the scratch; the epilogue warps then never meet at a named barrier: prologue()
+//        only starts per-warp loads, run() finds its constants in place.  Such an epilogue also supplies
+//   template<int BN> static __device__ uint32_t stage_cols(const Params&, const EpiMaps&, const GemmGeom&,
+//        const TileCtx&, int lane, float* scratch, uint64_t* bar);
+//        constants that depend on the tile's columns only (kept while consecutive tiles of the CTA share their
+//        columns); returns the bytes of the bulk loads it started on `bar`
+//   template<int BN> static __device__ void stage_tile(const Params&, const EpiMaps&, const GemmGeom&,
+//        const TileCtx&, int lane, float* scratch, int slot);
+//        constants of this tile's rows and batch
 // ---------------------------------------------------------------------------
+
+// The stager warp's loop over the tiles of its CTA.  `decode(unit)` yields the TileCtx of a unit.
+template <int BN, class Epi, class Decode>
+__device__ __forceinline__ void stager_loop(const typename Epi::Params& ep, const EpiMaps& maps, const GemmGeom& geom,
+                                            int first_unit, int unit_stride, int total_units, Decode decode, int lane,
+                                            float* scratch, uint64_t* sfull, uint64_t* sempty,
+                                            volatile int* abort_flag, int* status) {
+  int cur_sec = -1, cur_u0 = -1, iter = 0;
+  for (int unit = first_unit; unit < total_units; unit += unit_stride, ++iter) {
+    const TileCtx t = decode(unit);
+    const int slot = iter & 1;
+    // the slot is free once every epilogue warp has released the tile before the previous one
+    bool ok = mbar_wait(&sempty[slot], ((iter >> 1) & 1u) ^ 1u, abort_flag, status, kStatusEpilogueTimeout);
+    const bool new_cols = t.sec != cur_sec || t.u0 != cur_u0;
+    // the column constants are shared by both slots: they change only after the previous tile has been released
+    if (ok && new_cols && iter >= 1)
+      ok = mbar_wait(&sempty[slot ^ 1], ((iter - 1) >> 1) & 1u, abort_flag, status, kStatusEpilogueTimeout);
+    if (!__all_sync(0xffffffffu, ok)) break;
+    uint32_t tx = 0;
+    if (new_cols) {
+      tx = Epi::template stage_cols<BN>(ep, maps, geom, t, lane, scratch, &sfull[slot]);
+      cur_sec = t.sec, cur_u0 = t.u0;
+    }
+    Epi::template stage_tile<BN>(ep, maps, geom, t, lane, scratch, slot);
+    __syncwarp();
+    if (lane == 0) {
+      if (tx) mbar_expect_tx(&sfull[slot], tx);  // arrives and adds the bytes of the bulk loads in flight
+      else mbar_arrive(&sfull[slot]);
+    }
+  }
+}
+
 template <int BN, int STAGES, bool A_MN, bool B_MN, class Epi>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -268,6 +322,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     for (int w = 0; w < kEpiWarps; ++w) mbar_init(&sm.wload_bar[w], 1);
     mbar_init(sm.eshared_bar, 1);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&sm.sfull_bar[a], 1);
+      mbar_init(&sm.sempty_bar[a], kEpiWarps);
+      sm.tail_count[a] = 0;
+    }
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -382,7 +441,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         for (int i = 0; i < 64; ++i) __nanosleep(2000);
       }
     }
-  } else {
+  } else if (warp < kStagerWarp) {
     // ------------------------------------------------------------ epilogue
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) are readable by this warp
     const int half = (warp - 2) >> 2;  // which of the interleaved column chunks this warp takes
@@ -396,26 +455,42 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     io.shared_phase = 0;
     io.abort_flag = abort_flag;
     io.status = status;
+    io.tail_count = sm.tail_count;
     int iter = 0;
     for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x, ++iter) {
       const TileCtx t = decode_tile(geom, unit, BN);
       const int acc = iter & 1;
       const uint32_t acc_phase = (iter >> 1) & 1u;
-      // Stage the per-column constants of this tile while its main loop is still running.
+      // Stage the per-column constants of this tile (or start this warp's loads) while its main loop is running.
       Epi::template prologue<BN>(ep, maps, geom, t, warp - 2, epi_tid, epi_scratch, io, iter);
       // All 32 lanes poll so the warp stays converged for the .aligned TMEM loads.
-      const bool ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, status, kStatusEpilogueTimeout);
-      // The epilogue warps decide together whether to go on, so none of them can be left
-      // waiting at a named barrier that another one will never reach.
-      if (named_bar_any(kEpiBarrier, kEpiThreads, !ok)) break;
+      bool ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, status, kStatusEpilogueTimeout);
+      if constexpr (Epi::kStager) {
+        if (ok) ok = mbar_wait(&sm.sfull_bar[acc], acc_phase, abort_flag, status, kStatusEpilogueTimeout);
+        if (!__all_sync(0xffffffffu, ok)) break;  // no named barriers in this epilogue: every warp leaves alone
+      } else {
+        // The epilogue warps decide together whether to go on, so none of them can be left
+        // waiting at a named barrier that another one will never reach.
+        if (named_bar_any(kEpiBarrier, kEpiThreads, !ok)) break;
+      }
       tc_fence_after();
       const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(acc * BN) + (static_cast<uint32_t>(quarter * 32) << 16);
       Epi::template run<BN>(ep, maps, geom, t, tmem_acc, quarter, lane, half, epi_tid, epi_scratch, io, iter);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      if (lane == 0) {
+        mbar_arrive(&tempty_bar[acc]);
+        if constexpr (Epi::kStager) mbar_arrive(&sm.sempty_bar[acc]);
+      }
     }
     if (lane == 0) bulk_wait_all();  // bulk stores still reading this warp's staging block
+  } else {
+    // ------------------------------------------------------------ stager
+    if constexpr (Epi::kStager) {
+      stager_loop<BN, Epi>(ep, maps, geom, blockIdx.x, gridDim.x, total_units,
+                           [&](int unit) { return decode_tile(geom, unit, BN); }, lane, epi_scratch, sm.sfull_bar,
+                           sm.sempty_bar, abort_flag, status);
+    }
   }
 
   tc_fence_before();

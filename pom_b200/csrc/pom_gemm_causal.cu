@@ -143,6 +143,7 @@ int ctx_gemm_causal(const pom_ctx_args* a, int* status, cudaStream_t st) {
 
 int gate_gemm_causal(const pom_gate_args* a, int* status, cudaStream_t st) {
   if (!a->pre || !a->carry) return POM_ERR_NULL;
+  if (reinterpret_cast<uintptr_t>(a->carry) % 16) return POM_ERR_BAD_STRIDE;  // staged four columns per load
   PairShape ps;
   int rc = pair_shape(a->rope, a->P, &ps);
   if (rc) return rc;
@@ -171,6 +172,7 @@ int gate_gemm_causal(const pom_gate_args* a, int* status, cudaStream_t st) {
 
 int gate_bwd_gemm_causal(const pom_gate_bwd_args* a, int* status, cudaStream_t st) {
   if (!a->WoT || !a->pre || !a->carry || !a->suf_out || !a->group_sums) return POM_ERR_NULL;
+  if (reinterpret_cast<uintptr_t>(a->carry) % 16) return POM_ERR_BAD_STRIDE;  // staged four columns per load
   PairShape ps;
   int rc = pair_shape(a->rope, a->P, &ps);
   if (rc) return rc;
