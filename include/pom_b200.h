@@ -146,7 +146,7 @@ int pom_gemm_f32(const pom_gemm_args* a, void* stream);
  * 128-token tile.  partial is (B * ceil(N/128), P) fp32; reduce it with pom_reduce_partials.
  * With rope.kind != POM_ROPE_NONE the polynomial features of every token are rotated by its position before
  * the reduction (reference pom/pom_rope.py:513-515, pom_triton_rope.py:93-217): needs K <= 4, P % 16 == 0
- * (1-D) or P % 32 == 0 (2-D) and rope.step0/1 in {0, 1}; otherwise POM_ERR_UNSUPPORTED (use pom_poly_agg_fwd).
+ * (1-D) or P % 64 == 0 (2-D) and rope.step0/1 in {0, 1}; otherwise POM_ERR_UNSUPPORTED (use pom_poly_agg_fwd).
  * Replaces: pom/pom.py:205-206 + pom/pom.py:83-91 / 35-38 (and pom_triton.py:68-153).
  * ------------------------------------------------------------------------------------------ */
 typedef struct pom_ctx_args {
@@ -166,7 +166,7 @@ typedef struct pom_ctx_args {
    * sums the epilogue writes, per aligned group of 32 tokens, the inclusive running sums of the (rotated)
    * polynomial features as bf16 `pre_out` (B*N, ld_pre) and the group totals `group_sums` (B, ceil(N/32), P) fp32;
    * `partial` and `row_weight` are not used.  pom_group_scan then turns the totals into carries for
-   * pom_gate_gemm.  Works with and without rotary embedding (K <= 4, P % 16 == 0; 2-D rotary P % 32 == 0). */
+   * pom_gate_gemm.  Works with and without rotary embedding (K <= 4, P % 16 == 0; 2-D rotary P % 64 == 0). */
   int32_t causal;
   void* pre_out;
   int64_t ld_pre;

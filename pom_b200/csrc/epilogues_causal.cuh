@@ -141,7 +141,6 @@ struct EpiCtxCausal {
   static __device__ __forceinline__ void body(const Params& p, const EpiMaps& maps, const GemmGeom& g,
                                               const TileCtx& t, uint32_t tmem_acc, int quarter, int lane, int half,
                                               const float* cst, const RopeView& rs, EpiIO& io) {
-    const bool stepped = p.rope.step_of(t.sec) != 0;
     const int y = t.row0 + quarter * 32;
     const int grp = (t.row0 >> 5) + quarter;
     const bool grp_ok = grp < p.causal.groups && t.rows_valid > 0;
@@ -149,7 +148,9 @@ struct EpiCtxCausal {
     uint8_t* scr = io.buf0 + 4096;   // transposition block
 #pragma unroll 1
     for (int su = half; su < BN / 32; su += kEpiColSplit) {
-      if (t.u0 + 16 * su >= g.pair_q) break;  // warp-uniform
+      const PairPos pp = pair_pos(g, t, 16 * su);
+      if (!pp.ok) break;  // warp-uniform
+      const bool stepped = p.rope.step_of(pp.sec) != 0;
       float v[32];
       tmem_ld16<0>(tmem_acc + 16 * su, v);
       tmem_ld16<16>(tmem_acc + BN / 2 + 16 * su, v);
@@ -182,18 +183,17 @@ struct EpiCtxCausal {
       const float total = scan_column<false>(scr, out + 2048, lane);
       fence_async_smem();
       __syncwarp();
-      const int u = t.u0 + 16 * su;
       if (lane == 0 && t.rows_valid > 0) {
         if (p.save_hp) {
-          tma_store_4d(&maps.out0, out, u, 2 * t.sec, y, t.b);
-          tma_store_4d(&maps.out0, out + 1024, u, 2 * t.sec + 1, y, t.b);
+          tma_store_4d(&maps.out0, out, pp.u, 2 * pp.sec, y, t.b);
+          tma_store_4d(&maps.out0, out + 1024, pp.u, 2 * pp.sec + 1, y, t.b);
         }
-        tma_store_4d(&maps.out1, out + 2048, u, 2 * t.sec, y, t.b);
-        tma_store_4d(&maps.out1, out + 3072, u, 2 * t.sec + 1, y, t.b);
+        tma_store_4d(&maps.out1, out + 2048, pp.u, 2 * pp.sec, y, t.b);
+        tma_store_4d(&maps.out1, out + 3072, pp.u, 2 * pp.sec + 1, y, t.b);
         bulk_commit();
       }
-      if (grp_ok && u + (lane & 15) < g.pair_q) {
-        const int col = (lane < 16 ? t.col0 : t.col1) + 16 * su + (lane & 15);
+      if (grp_ok && pp.u + (lane & 15) < g.pair_q) {
+        const int col = pp.col + (lane < 16 ? 0 : g.pair_q) + (lane & 15);
         p.causal.group_sums[(static_cast<long long>(t.b) * p.causal.groups + grp) * p.causal.P + col] = total;
       }
     }
@@ -236,13 +236,13 @@ struct EpiGateCausal {
     return Scratch<BN>::kBytes;
   }
 
-  static __device__ __forceinline__ void fetch_pre(const EpiMaps& maps, const TileCtx& t, EpiIO& io, int quarter,
-                                                   int lane, int su, int set) {
+  static __device__ __forceinline__ void fetch_pre(const EpiMaps& maps, const TileCtx& t, const PairPos& pp,
+                                                   EpiIO& io, int quarter, int lane, int set) {
     if (lane == 0) {
       uint8_t* blk = io.buf0 + set * 2048;
       mbar_expect_tx(io.bar, 2048);
-      tma_load_4d(blk, &maps.in0, io.bar, t.u0 + 16 * su, 2 * t.sec, t.row0 + quarter * 32, t.b);
-      tma_load_4d(blk + 1024, &maps.in0, io.bar, t.u0 + 16 * su, 2 * t.sec + 1, t.row0 + quarter * 32, t.b);
+      tma_load_4d(blk, &maps.in0, io.bar, pp.u, 2 * pp.sec, t.row0 + quarter * 32, t.b);
+      tma_load_4d(blk + 1024, &maps.in0, io.bar, pp.u, 2 * pp.sec + 1, t.row0 + quarter * 32, t.b);
     }
   }
 
@@ -267,7 +267,8 @@ struct EpiGateCausal {
                                                   const TileCtx& t, int warp_in_epi, int epi_tid, float*, EpiIO& io,
                                                   int) {
     const int half = warp_in_epi >> 2, quarter = (warp_in_epi + 2) & 3;
-    if (t.u0 + 16 * half < g.pair_q) fetch_pre(maps, t, io, quarter, epi_tid & 31, half, 0);
+    const PairPos pp = pair_pos(g, t, 16 * half);
+    if (pp.ok) fetch_pre(maps, t, pp, io, quarter, epi_tid & 31, 0);
   }
 
   template <int BN>
@@ -279,7 +280,6 @@ struct EpiGateCausal {
     const float* bias = sc.cols();
     const float* carry = sc.tile(slot) + quarter * BN;
     const RopeView rs{sc.base_cos(slot), sc.base_sin(slot), sc.lane()};
-    const bool stepped = p.rope.step_of(t.sec) != 0;
     const int y = t.row0 + quarter * 32;
     const float inv_n = 1.f / static_cast<float>(p.causal.token_offset + y + lane + 1);
     uint8_t* out = io.buf0 + 4096;
@@ -287,7 +287,9 @@ struct EpiGateCausal {
     int set = 0;
 #pragma unroll 1
     for (int su = half; su < BN / 32; su += kEpiColSplit) {
-      if (t.u0 + 16 * su >= g.pair_q) break;  // warp-uniform
+      const PairPos pp = pair_pos(g, t, 16 * su);
+      if (!pp.ok) break;  // warp-uniform
+      const bool stepped = p.rope.step_of(pp.sec) != 0;
       float v[32];
       tmem_ld16<0>(tmem_acc + 16 * su, v);
       tmem_ld16<16>(tmem_acc + BN / 2 + 16 * su, v);
@@ -296,7 +298,10 @@ struct EpiGateCausal {
       io.load_phase ^= 1u;
       const int nsu = su + kEpiColSplit;
       __syncwarp();  // every lane has finished reading the other set (previous sub-unit)
-      if (alive && nsu < BN / 32 && t.u0 + 16 * nsu < g.pair_q) fetch_pre(maps, t, io, quarter, lane, nsu, set ^ 1);
+      if (alive && nsu < BN / 32) {
+        const PairPos np = pair_pos(g, t, 16 * nsu);
+        if (np.ok) fetch_pre(maps, t, np, io, quarter, lane, set ^ 1);
+      }
       const uint8_t* in = io.buf0 + set * 2048;
       set ^= 1;
       tmem_ld_wait();
@@ -337,13 +342,12 @@ struct EpiGateCausal {
       fence_async_smem();
       __syncwarp();
       if (lane == 0) {
-        const int u = t.u0 + 16 * su;
         if (p.save_z) {
-          tma_store_4d(&maps.out0, out, u, 2 * t.sec, y, t.b);
-          tma_store_4d(&maps.out0, out + 1024, u, 2 * t.sec + 1, y, t.b);
+          tma_store_4d(&maps.out0, out, pp.u, 2 * pp.sec, y, t.b);
+          tma_store_4d(&maps.out0, out + 1024, pp.u, 2 * pp.sec + 1, y, t.b);
         }
-        tma_store_4d(&maps.out1, out + 2048, u, 2 * t.sec, y, t.b);
-        tma_store_4d(&maps.out1, out + 3072, u, 2 * t.sec + 1, y, t.b);
+        tma_store_4d(&maps.out1, out + 2048, pp.u, 2 * pp.sec, y, t.b);
+        tma_store_4d(&maps.out1, out + 3072, pp.u, 2 * pp.sec + 1, y, t.b);
         bulk_commit();
       }
     }
@@ -375,16 +379,16 @@ struct EpiGateBwdCausal {
     return Scratch<BN>::kBytes;
   }
 
-  static __device__ __forceinline__ void fetch_in(const EpiMaps& maps, const TileCtx& t, EpiIO& io, int quarter,
-                                                  int lane, int su, int set) {
+  static __device__ __forceinline__ void fetch_in(const EpiMaps& maps, const TileCtx& t, const PairPos& pp, EpiIO& io,
+                                                  int quarter, int lane, int set) {
     if (lane == 0) {
-      const int u = t.u0 + 16 * su, y = t.row0 + quarter * 32;
+      const int y = t.row0 + quarter * 32;
       uint8_t* blk = io.buf0 + set * 4096;
       mbar_expect_tx(io.bar, 4096);
-      tma_load_4d(blk, &maps.in0, io.bar, u, 2 * t.sec, y, t.b);
-      tma_load_4d(blk + 1024, &maps.in0, io.bar, u, 2 * t.sec + 1, y, t.b);
-      tma_load_4d(blk + 2048, &maps.in1, io.bar, u, 2 * t.sec, y, t.b);
-      tma_load_4d(blk + 3072, &maps.in1, io.bar, u, 2 * t.sec + 1, y, t.b);
+      tma_load_4d(blk, &maps.in0, io.bar, pp.u, 2 * pp.sec, y, t.b);
+      tma_load_4d(blk + 1024, &maps.in0, io.bar, pp.u, 2 * pp.sec + 1, y, t.b);
+      tma_load_4d(blk + 2048, &maps.in1, io.bar, pp.u, 2 * pp.sec, y, t.b);
+      tma_load_4d(blk + 3072, &maps.in1, io.bar, pp.u, 2 * pp.sec + 1, y, t.b);
     }
   }
 
@@ -409,7 +413,8 @@ struct EpiGateBwdCausal {
                                                   const TileCtx& t, int warp_in_epi, int epi_tid, float*, EpiIO& io,
                                                   int) {
     const int half = warp_in_epi >> 2, quarter = (warp_in_epi + 2) & 3;
-    if (t.u0 + 16 * half < g.pair_q) fetch_in(maps, t, io, quarter, epi_tid & 31, half, 0);
+    const PairPos pp = pair_pos(g, t, 16 * half);
+    if (pp.ok) fetch_in(maps, t, pp, io, quarter, epi_tid & 31, 0);
   }
 
   template <int BN>
@@ -422,7 +427,6 @@ struct EpiGateBwdCausal {
     const float* bias = sc.cols();
     const float* carry = sc.tile(slot) + quarter * BN;
     const RopeView rs{sc.base_cos(slot), sc.base_sin(slot), sc.lane()};
-    const bool stepped = p.rope.step_of(t.sec) != 0;
     const int y = t.row0 + quarter * 32;
     const int grp = (t.row0 >> 5) + quarter;
     const bool grp_ok = grp < p.causal.groups && t.rows_valid > 0;
@@ -433,7 +437,9 @@ struct EpiGateBwdCausal {
 #pragma unroll 1
     for (int su = half; su < BN / 32; su += kEpiColSplit) {
       float* b1p = buf_b + quarter * BN + 16 * su;
-      if (t.u0 + 16 * su >= g.pair_q) {  // warp-uniform
+      const PairPos pp = pair_pos(g, t, 16 * su);
+      const bool stepped = p.rope.step_of(pp.sec) != 0;
+      if (!pp.ok) {  // warp-uniform
         if (lane < 16) b1p[lane] = 0.f;
         else b1p[BN / 2 + lane - 16] = 0.f;
         continue;
@@ -447,7 +453,10 @@ struct EpiGateBwdCausal {
       // the other set was last touched (as the transposition block) one sub-unit ago by every lane: refill it
       const int nsu = su + kEpiColSplit;
       __syncwarp();
-      if (alive && nsu < BN / 32 && t.u0 + 16 * nsu < g.pair_q) fetch_in(maps, t, io, quarter, lane, nsu, set ^ 1);
+      if (alive && nsu < BN / 32) {
+        const PairPos np = pair_pos(g, t, 16 * nsu);
+        if (np.ok) fetch_in(maps, t, np, io, quarter, lane, set ^ 1);
+      }
       uint8_t* in = io.buf0 + set * 4096;
       set ^= 1;
       read_block16<0>(in, lane, z);
@@ -490,16 +499,15 @@ struct EpiGateBwdCausal {
       const float total = scan_column<true>(in, out + 2048, lane);
       fence_async_smem();
       __syncwarp();
-      const int u = t.u0 + 16 * su;
       if (lane == 0 && t.rows_valid > 0) {
-        tma_store_4d(&maps.out0, out, u, 2 * t.sec, y, t.b);
-        tma_store_4d(&maps.out0, out + 1024, u, 2 * t.sec + 1, y, t.b);
-        tma_store_4d(&maps.out1, out + 2048, u, 2 * t.sec, y, t.b);
-        tma_store_4d(&maps.out1, out + 3072, u, 2 * t.sec + 1, y, t.b);
+        tma_store_4d(&maps.out0, out, pp.u, 2 * pp.sec, y, t.b);
+        tma_store_4d(&maps.out0, out + 1024, pp.u, 2 * pp.sec + 1, y, t.b);
+        tma_store_4d(&maps.out1, out + 2048, pp.u, 2 * pp.sec, y, t.b);
+        tma_store_4d(&maps.out1, out + 3072, pp.u, 2 * pp.sec + 1, y, t.b);
         bulk_commit();
       }
-      if (grp_ok && u + (lane & 15) < g.pair_q) {
-        const int col = (lane < 16 ? t.col0 : t.col1) + 16 * su + (lane & 15);
+      if (grp_ok && pp.u + (lane & 15) < g.pair_q) {
+        const int col = pp.col + (lane < 16 ? 0 : g.pair_q) + (lane & 15);
         p.causal.group_sums[(static_cast<long long>(t.b) * p.causal.groups + grp) * p.causal.P + col] = total;
       }
       warp_colsum32(z, lane);

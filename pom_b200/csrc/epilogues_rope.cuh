@@ -76,15 +76,18 @@ struct RopeView {
 template <int BN>
 __device__ __forceinline__ uint32_t rope_stage_lane(const RopeEpi& r, const EpiMaps& maps, const GemmGeom& g,
                                                     const TileCtx& t, int lane, uint8_t* lane_tab, uint64_t* bar) {
-  if (!r.rotate || r.step_of(t.sec) == 0) return 0;
-  const int nsub = min(BN / 32, (g.pair_q - t.u0 + 15) >> 4);
-  if (lane == 0) {
-    for (int su = 0; su < nsub; ++su) {
-      tma_load_2d(lane_tab + su * 4096, &maps.lane[2 * t.sec], bar, t.u0 + 16 * su, 0);
-      tma_load_2d(lane_tab + su * 4096 + 2048, &maps.lane[2 * t.sec + 1], bar, t.u0 + 16 * su, 0);
+  if (!r.rotate) return 0;
+  uint32_t bytes = 0;
+  for (int su = 0; su < BN / 32; ++su) {
+    const PairPos pp = pair_pos(g, t, 16 * su);
+    if (!pp.ok || r.step_of(pp.sec) == 0) continue;  // no pairs, or one position per row group: no lane table
+    if (lane == 0) {
+      tma_load_2d(lane_tab + su * 4096, &maps.lane[2 * pp.sec], bar, pp.u, 0);
+      tma_load_2d(lane_tab + su * 4096 + 2048, &maps.lane[2 * pp.sec + 1], bar, pp.u, 0);
     }
+    bytes += 4096u;
   }
-  return static_cast<uint32_t>(nsub) * 4096u;
+  return bytes;
 }
 
 // Stager warp: cos / sin of the base position of the tile's four 32-row groups for its BN/2 pairs, four pairs per
@@ -95,30 +98,34 @@ __device__ __forceinline__ void rope_stage_base(const RopeEpi& r, const GemmGeom
                                                 float* base_cos, float* base_sin) {
   constexpr int kHalf = BN / 2;
   constexpr int kVec = kHalf / 4;  // float4 per row group
-  const int sec = t.sec;
-  const int which = r.pos_stride == 2 ? sec : 0;
-  const float* __restrict__ cosp = r.cos_of(sec);
-  const float* __restrict__ sinp = r.sin_of(sec);
-  const long long len = r.len_of(sec);
-  long long pos[4];
+  long long pos[4][2];  // [row group][section]; the host validates positions: the clamp only keeps reads inside the table
 #pragma unroll
   for (int quarter = 0; quarter < 4; ++quarter) {
     const int n = t.row0 + 32 * quarter;
-    long long p = 0;
-    if (r.rotate && n < g.rows_per_batch) p = __ldg(r.pos + static_cast<long long>(n) * r.pos_stride + which);
-    pos[quarter] = p < 0 ? 0 : (p >= len ? len - 1 : p);  // the host validates positions; never read outside the table
+#pragma unroll
+    for (int sec = 0; sec < 2; ++sec) {
+      long long p = 0;
+      if (r.rotate && n < g.rows_per_batch && (sec == 0 || r.pos_stride == 2))
+        p = __ldg(r.pos + static_cast<long long>(n) * r.pos_stride + sec);
+      const long long len = r.len_of(sec);
+      pos[quarter][sec] = p < 0 ? 0 : (p >= len ? len - 1 : p);
+    }
   }
   static_assert((4 * kVec) % 32 == 0, "tile width");
 #pragma unroll
   for (int k = 0; k < 4 * kVec / 32; ++k) {
     const int idx = lane + 32 * k;
     const int quarter = idx / kVec, j = (idx - quarter * kVec) * 4;
-    const int n = t.row0 + 32 * quarter, u = t.u0 + j;
+    const int n = t.row0 + 32 * quarter;
+    const PairPos pp = pair_pos(g, t, j);
     float4 c = make_float4(1.f, 1.f, 1.f, 1.f), s = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (r.rotate && n < g.rows_per_batch && u < g.pair_q) {
-      const long long p = quarter == 0 ? pos[0] : quarter == 1 ? pos[1] : quarter == 2 ? pos[2] : pos[3];
-      c = __ldg(reinterpret_cast<const float4*>(cosp + p * g.pair_q + u));
-      s = __ldg(reinterpret_cast<const float4*>(sinp + p * g.pair_q + u));
+    if (r.rotate && n < g.rows_per_batch && pp.ok) {
+      const int which = r.pos_stride == 2 ? pp.sec : 0;
+      const long long p0 = quarter == 0 ? pos[0][0] : quarter == 1 ? pos[1][0] : quarter == 2 ? pos[2][0] : pos[3][0];
+      const long long p1 = quarter == 0 ? pos[0][1] : quarter == 1 ? pos[1][1] : quarter == 2 ? pos[2][1] : pos[3][1];
+      const long long p = which ? p1 : p0;
+      c = __ldg(reinterpret_cast<const float4*>(r.cos_of(pp.sec) + p * g.pair_q + pp.u));
+      s = __ldg(reinterpret_cast<const float4*>(r.sin_of(pp.sec) + p * g.pair_q + pp.u));
     }
     *reinterpret_cast<float4*>(base_cos + 4 * idx) = c;
     *reinterpret_cast<float4*>(base_sin + 4 * idx) = s;
@@ -164,9 +171,9 @@ __device__ __forceinline__ void rope_cs4(const RopeView& rs, bool stepped, int q
 // Global column of tile column c (left half: first channels, right half: partners) and whether it exists.
 template <int BN>
 __device__ __forceinline__ int paired_col(const GemmGeom& g, const TileCtx& t, int c, bool* ok) {
-  const int j = c < BN / 2 ? c : c - BN / 2;
-  *ok = t.u0 + j < g.pair_q;
-  return (c < BN / 2 ? t.col0 : t.col1) + j;
+  const PairPos pp = pair_pos(g, t, c < BN / 2 ? c : c - BN / 2);
+  *ok = pp.ok;
+  return pp.col + (c < BN / 2 ? 0 : g.pair_q);
 }
 
 // Round 16 fp32 values v[OFF..OFF+16) to bf16 in place and keep the packed form.
@@ -261,14 +268,15 @@ struct EpiCtxRope {
     float w = 1.f;
     if (weighted)
       w = row < t.rows_valid ? __ldg(p.row_weight + static_cast<long long>(t.b) * g.rows_per_batch + t.row0 + row) : 0.f;
-    const bool stepped = p.rope.step_of(t.sec) != 0;
     const int y = t.row0 + quarter * 32;
     int flip = 0;
 #pragma unroll 1
     for (int su = half; su < BN / 32; su += kEpiColSplit) {
       float* b1 = buf + quarter * BN + 16 * su;
       float* b2 = b1 + BN / 2;
-      if (t.u0 + 16 * su >= g.pair_q || !t.live) {  // warp-uniform
+      const PairPos pp = pair_pos(g, t, 16 * su);
+      const bool stepped = p.rope.step_of(pp.sec) != 0;
+      if (!pp.ok || !t.live) {  // warp-uniform
         if (lane < 16) b1[lane] = 0.f;
         else b2[lane - 16] = 0.f;
         continue;
@@ -289,8 +297,8 @@ struct EpiCtxRope {
         fence_async_smem();
         __syncwarp();
         if (lane == 0) {
-          tma_store_4d(&maps.out0, blk, t.u0 + 16 * su, 2 * t.sec, y, t.b);
-          tma_store_4d(&maps.out0, blk + 1024, t.u0 + 16 * su, 2 * t.sec + 1, y, t.b);
+          tma_store_4d(&maps.out0, blk, pp.u, 2 * pp.sec, y, t.b);
+          tma_store_4d(&maps.out0, blk + 1024, pp.u, 2 * pp.sec + 1, y, t.b);
           bulk_commit();
         }
         flip ^= 1;
@@ -404,11 +412,12 @@ struct EpiGateRope {
     const float* bias = sc.cols();
     const float* hrow = sc.tile(slot);
     const RopeView rs{sc.base_cos(slot), sc.base_sin(slot), sc.lane()};
-    const bool stepped = p.rope.step_of(t.sec) != 0;
     const int y = t.row0 + quarter * 32;
 #pragma unroll 1
     for (int su = half; su < BN / 32; su += kEpiColSplit) {
-      if (t.u0 + 16 * su >= g.pair_q) break;  // warp-uniform
+      const PairPos pp = pair_pos(g, t, 16 * su);
+      if (!pp.ok) break;  // warp-uniform
+      const bool stepped = p.rope.step_of(pp.sec) != 0;
       float v[32];
       tmem_ld16<0>(tmem_acc + 16 * su, v);
       tmem_ld16<16>(tmem_acc + BN / 2 + 16 * su, v);
@@ -449,13 +458,12 @@ struct EpiGateRope {
       fence_async_smem();
       __syncwarp();
       if (lane == 0) {
-        const int u = t.u0 + 16 * su;
         if (p.save_z) {
-          tma_store_4d(&maps.out0, io.buf0, u, 2 * t.sec, y, t.b);
-          tma_store_4d(&maps.out0, io.buf0 + 1024, u, 2 * t.sec + 1, y, t.b);
+          tma_store_4d(&maps.out0, io.buf0, pp.u, 2 * pp.sec, y, t.b);
+          tma_store_4d(&maps.out0, io.buf0 + 1024, pp.u, 2 * pp.sec + 1, y, t.b);
         }
-        tma_store_4d(&maps.out1, io.buf0 + 2048, u, 2 * t.sec, y, t.b);
-        tma_store_4d(&maps.out1, io.buf0 + 3072, u, 2 * t.sec + 1, y, t.b);
+        tma_store_4d(&maps.out1, io.buf0 + 2048, pp.u, 2 * pp.sec, y, t.b);
+        tma_store_4d(&maps.out1, io.buf0 + 3072, pp.u, 2 * pp.sec + 1, y, t.b);
         bulk_commit();
       }
     }
@@ -489,13 +497,13 @@ struct EpiGateBwdRope {
     return Scratch<BN>::kBytes;
   }
 
-  static __device__ __forceinline__ void fetch_z(const EpiMaps& maps, const TileCtx& t, EpiIO& io, int quarter,
-                                                 int lane, int su, int set) {
+  static __device__ __forceinline__ void fetch_z(const EpiMaps& maps, const TileCtx& t, const PairPos& pp, EpiIO& io,
+                                                 int quarter, int lane, int set) {
     if (lane == 0) {
       uint8_t* blk = io.buf0 + set * 2048;
       mbar_expect_tx(io.bar, 2048);
-      tma_load_4d(blk, &maps.in0, io.bar, t.u0 + 16 * su, 2 * t.sec, t.row0 + quarter * 32, t.b);
-      tma_load_4d(blk + 1024, &maps.in0, io.bar, t.u0 + 16 * su, 2 * t.sec + 1, t.row0 + quarter * 32, t.b);
+      tma_load_4d(blk, &maps.in0, io.bar, pp.u, 2 * pp.sec, t.row0 + quarter * 32, t.b);
+      tma_load_4d(blk + 1024, &maps.in0, io.bar, pp.u, 2 * pp.sec + 1, t.row0 + quarter * 32, t.b);
     }
   }
 
@@ -520,7 +528,8 @@ struct EpiGateBwdRope {
                                                   const TileCtx& t, int warp_in_epi, int epi_tid, float*, EpiIO& io,
                                                   int) {
     const int half = warp_in_epi >> 2, quarter = (warp_in_epi + 2) & 3;
-    if (t.u0 + 16 * half < g.pair_q) fetch_z(maps, t, io, quarter, epi_tid & 31, half, 0);
+    const PairPos pp = pair_pos(g, t, 16 * half);
+    if (pp.ok) fetch_z(maps, t, pp, io, quarter, epi_tid & 31, 0);
   }
 
   template <int BN>
@@ -534,7 +543,6 @@ struct EpiGateBwdRope {
     const float* bias = sc.cols();
     const float* hrow = sc.tile(slot);
     const RopeView rs{sc.base_cos(slot), sc.base_sin(slot), sc.lane()};
-    const bool stepped = p.rope.step_of(t.sec) != 0;
     const int y = t.row0 + quarter * 32;
     uint8_t* out_blk = io.buf0 + 4096;
     bool alive = true;
@@ -543,7 +551,9 @@ struct EpiGateBwdRope {
     for (int su = half; su < BN / 32; su += kEpiColSplit) {
       float* h1p = buf_h + quarter * BN + 16 * su;
       float* b1p = buf_b + quarter * BN + 16 * su;
-      if (t.u0 + 16 * su >= g.pair_q) {  // warp-uniform
+      const PairPos pp = pair_pos(g, t, 16 * su);
+      const bool stepped = p.rope.step_of(pp.sec) != 0;
+      if (!pp.ok) {  // warp-uniform
         if (lane < 16) h1p[lane] = 0.f, b1p[lane] = 0.f;
         else h1p[BN / 2 + lane - 16] = 0.f, b1p[BN / 2 + lane - 16] = 0.f;
         continue;
@@ -557,7 +567,10 @@ struct EpiGateBwdRope {
       // the other set was consumed one sub-unit ago by every lane (the __all_sync above orders it): refill it
       const int nsu = su + kEpiColSplit;
       __syncwarp();
-      if (alive && nsu < BN / 32 && t.u0 + 16 * nsu < g.pair_q) fetch_z(maps, t, io, quarter, lane, nsu, set ^ 1);
+      if (alive && nsu < BN / 32) {
+        const PairPos np = pair_pos(g, t, 16 * nsu);
+        if (np.ok) fetch_z(maps, t, np, io, quarter, lane, set ^ 1);
+      }
       read_block16<0>(io.buf0 + set * 2048, lane, z);
       read_block16<16>(io.buf0 + set * 2048 + 1024, lane, z);
       set ^= 1;
@@ -595,8 +608,8 @@ struct EpiGateBwdRope {
         fence_async_smem();
         __syncwarp();
         if (lane == 0) {
-          tma_store_4d(&maps.out0, out_blk, t.u0 + 16 * su, 2 * t.sec, y, t.b);
-          tma_store_4d(&maps.out0, out_blk + 1024, t.u0 + 16 * su, 2 * t.sec + 1, y, t.b);
+          tma_store_4d(&maps.out0, out_blk, pp.u, 2 * pp.sec, y, t.b);
+          tma_store_4d(&maps.out0, out_blk + 1024, pp.u, 2 * pp.sec + 1, y, t.b);
           bulk_commit();
         }
       }

@@ -224,7 +224,12 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
               tma2_load_3d(sa + j * (kBK * 128), &tmA, full0, t.row0 + j * 64, kb * kBK, t.b);
           }
           if constexpr (!B_MN) {
-            tma2_load_3d(sb, &tmB, full0, kb * kBK, bcol0, bz);
+            if (geom.pair_q) {  // the leader's half of the B tile: first channels; the peer's: their partners
+              load_paired_b_half<BN>(geom, t, static_cast<int>(rank), sb,
+                                     [&](uint8_t* dst, int row) { tma2_load_3d(dst, &tmB, full0, kb * kBK, row, bz); });
+            } else {
+              tma2_load_3d(sb, &tmB, full0, kb * kBK, bcol0, bz);
+            }
           } else {
 #pragma unroll
             for (int j = 0; j < kHalfN / 64; ++j)

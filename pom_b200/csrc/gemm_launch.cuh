@@ -155,14 +155,28 @@ inline int build_maps(const Operands& o, int b_rows, CUtensorMap* tmA, CUtensorM
 // two-CTA (pair) kernel; tens digit: 1 / 2 / 3 forces 128 / 192 / 256 columns per tile.
 extern std::atomic<int> g_gemm_mode;
 
+// Rows per B-operand box of a paired tile: the whole half tile, or, with two sections, the largest piece that never
+// reaches over the border between them.
+inline int paired_box_rows(const Operands& o, int bn) {
+  if (!o.pair_q) return bn;
+  int a = o.pair_q, b = bn / 2;
+  if (o.pair_sections == 1) return b;
+  while (b) {
+    const int r = a % b;
+    a = b, b = r;
+  }
+  return a;
+}
+
 inline GemmGeom make_geom(const Operands& o, int bn, int split_k) {
   GemmGeom g;
   g.batches = o.batches;
   g.rows_per_batch = static_cast<int>(o.M);
   g.m_tiles_per_batch = static_cast<int>(ceil_div(o.M, kBM));
   g.pair_q = o.pair_q;
-  g.tiles_per_section = o.pair_q ? static_cast<int>(ceil_div(o.pair_q, bn / 2)) : 0;
-  g.n_tiles = o.pair_q ? o.pair_sections * g.tiles_per_section : static_cast<int>(ceil_div(o.N, bn));
+  g.pair_total = o.pair_q * o.pair_sections;
+  g.b_box_rows = paired_box_rows(o, bn);
+  g.n_tiles = static_cast<int>(o.pair_q ? ceil_div(g.pair_total, bn / 2) : ceil_div(o.N, bn));
   g.n_cols = static_cast<int>(o.N);
   g.k_blocks = static_cast<int>(ceil_div(o.K, kBK));
   if (split_k < 1) split_k = 1;
@@ -212,7 +226,7 @@ template <int BN, int STAGES, bool A_MN, bool B_MN, class Epi>
 int launch(const Operands& o, int split_k, const EpiMaps& maps, const typename Epi::Params& ep, int* status,
            cudaStream_t st) {
   CUtensorMap tmA, tmB;
-  int rc = build_maps(o, o.pair_q ? BN / 2 : BN, &tmA, &tmB);
+  int rc = build_maps(o, paired_box_rows(o, BN), &tmA, &tmB);
   if (rc) return rc;
   GemmGeom g = make_geom(o, BN, split_k);
   constexpr int smem = gemm_smem_bytes<BN, STAGES, Epi>();
@@ -236,7 +250,7 @@ template <int BN, int STAGES, bool A_MN, bool B_MN, class Epi>
 int launch_pair(const Operands& o, int split_k, const EpiMaps& maps, const typename Epi::Params& ep, int* status,
                 cudaStream_t st) {
   CUtensorMap tmA, tmB;
-  int rc = build_maps(o, BN / 2, &tmA, &tmB);
+  int rc = build_maps(o, o.pair_q ? paired_box_rows(o, BN) : BN / 2, &tmA, &tmB);
   if (rc) return rc;
   GemmGeom g = make_geom(o, BN, split_k);
   constexpr int smem = gemm2_smem_bytes<BN, STAGES, Epi>();
@@ -288,7 +302,7 @@ inline TilePlan pick_plan(const Operands& o, bool allow_192, bool splittable = f
       if (bn == 192 && !has_192) continue;
       if (o.N <= 128 && bn != 128) continue;
       if (force_bn && bn != force_bn && !(force_bn == 192 && !has_192)) continue;
-      const long long n_tiles = o.pair_q ? o.pair_sections * ceil_div(o.pair_q, bn / 2) : ceil_div(o.N, bn);
+      const long long n_tiles = o.pair_q ? ceil_div(1ll * o.pair_sections * o.pair_q, bn / 2) : ceil_div(o.N, bn);
       const long long units = (pair ? (m_tiles + 1) / 2 : m_tiles) * n_tiles;
       const int slots = pair ? sm_count() / 2 : sm_count();
       // split-K products fill the last wave with K slices (pick_split): their cost is the work itself (an odd row
@@ -326,7 +340,7 @@ inline int pick_split(long long units, long long kblocks, int slots) {
 
 inline long long plan_units(const Operands& o, const TilePlan& p) {
   const long long mt = ceil_div(o.M, kBM);
-  const long long nt = o.pair_q ? o.pair_sections * ceil_div(o.pair_q, p.bn / 2) : ceil_div(o.N, p.bn);
+  const long long nt = o.pair_q ? ceil_div(1ll * o.pair_sections * o.pair_q, p.bn / 2) : ceil_div(o.N, p.bn);
   return 1ll * o.batches * (p.pair ? (mt + 1) / 2 : mt) * nt;
 }
 

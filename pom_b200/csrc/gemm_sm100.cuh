@@ -57,11 +57,14 @@ struct GemmGeom {
   // epilogue sees t.live == false).  Used by the context phase to skip 128-token tiles that a mask empties.
   const float* tile_weight;
   int b_batched;          // 1: the B operand has one matrix per batch (third tensor-map coordinate = batch)
-  // Rotary column pairing (0 = off): the N columns are sections of 2 * pair_q channels, pair_q first channels
-  // followed by their pair_q rotation partners.  A tile then holds BN/2 first channels in its left half and
-  // their partners in its right half (two B boxes), and never straddles a section.
+  // Rotary column pairing (0 = off): the N columns are one or two sections of 2 * pair_q channels, pair_q first
+  // channels followed by their pair_q rotation partners.  The pairs of all sections, laid end to end, are cut into
+  // tiles of BN/2 pairs: a tile holds the first channels of its pairs in its left half and their partners in its
+  // right half.  A tile may reach over the border between the two sections; a 16-pair sub-unit and a B box of
+  // `b_box_rows` rows never do (two sections: pair_q is a multiple of 16 and of b_box_rows).
   int pair_q;
-  int tiles_per_section;  // ceil(pair_q / (BN / 2))
+  int pair_total;  // pair_q x sections
+  int b_box_rows;  // rows per B-operand box (paired, K-major B): BN/2, or gcd(pair_q, BN/2) with two sections
 };
 
 struct TileCtx {
@@ -72,22 +75,54 @@ struct TileCtx {
   int col0;        // first column of C (paired: global column of the tile's first first-channel)
   int col1;        // paired: global column of the partner of col0 (= col0 + pair_q)
   int u0;          // paired: index of col0 inside its section's run of first channels
-  int sec;         // paired: section
+  int sec;         // paired: section of the tile's first pair
+  int gp0;         // paired: index of the tile's first pair among the pairs of all sections laid end to end
   int split;       // K split index
   bool live;       // false: the main loop is skipped for this tile (see GemmGeom::tile_weight)
 };
 
+// Where pair j of a paired tile sits: its section, its index inside the section's run of first channels, the global
+// column of its first channel (the partner is pair_q columns further), and whether it exists at all.
+struct PairPos {
+  int sec, u, col;
+  bool ok;
+};
+__device__ __forceinline__ PairPos pair_pos(const GemmGeom& g, const TileCtx& t, int j) {
+  PairPos p;
+  const int gp = t.gp0 + j;
+  p.sec = gp >= g.pair_q && g.pair_total > g.pair_q ? 1 : 0;  // at most two sections
+  p.u = gp - (p.sec ? g.pair_q : 0);
+  p.col = p.sec * 2 * g.pair_q + p.u;
+  p.ok = gp < g.pair_total;
+  return p;
+}
+
 __device__ __forceinline__ void set_tile_cols(const GemmGeom& g, TileCtx& t, int n, int bn) {
   if (g.pair_q) {
-    t.sec = n / g.tiles_per_section;
-    t.u0 = (n - t.sec * g.tiles_per_section) * (bn >> 1);
-    t.col0 = t.sec * 2 * g.pair_q + t.u0;
+    t.gp0 = n * (bn >> 1);
+    const PairPos p = pair_pos(g, t, 0);
+    t.sec = p.sec;
+    t.u0 = p.u;
+    t.col0 = p.col;
     t.col1 = t.col0 + g.pair_q;
   } else {
     t.col0 = n * bn;
     t.col1 = t.col0;
     t.u0 = t.col0;
     t.sec = 0;
+    t.gp0 = 0;
+  }
+}
+
+// Paired tiles, K-major B: loads the BN/2 rows of one half of the B tile (partner == 0: the first channels of the
+// tile's pairs, 1: their partners) as boxes of g.b_box_rows rows; rows of pairs that do not exist are zero-filled
+// (a box starting past the last row of B).
+template <int BN, class Load>
+__device__ __forceinline__ void load_paired_b_half(const GemmGeom& g, const TileCtx& t, int partner, uint8_t* dst,
+                                                   Load load) {
+  for (int j = 0; j < BN / 2; j += g.b_box_rows) {
+    const PairPos p = pair_pos(g, t, j);
+    load(dst + j * (kBK * 2), p.ok ? p.col + partner * g.pair_q : g.n_cols);
   }
 }
 
@@ -370,9 +405,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               tma_load_3d(sa + j * (kBK * 128), &tmA, &full_bar[stage], t.row0 + j * 64, kb * kBK, t.b);
           }
           if constexpr (!B_MN) {
-            if (geom.pair_q) {  // first channels, then their rotation partners (two boxes of BN/2 rows)
-              tma_load_3d(sb, &tmB, &full_bar[stage], kb * kBK, t.col0, bz);
-              tma_load_3d(sb + (BN / 2) * kBK * 2, &tmB, &full_bar[stage], kb * kBK, t.col1, bz);
+            if (geom.pair_q) {  // first channels, then their rotation partners
+              auto load = [&](uint8_t* dst, int row) { tma_load_3d(dst, &tmB, &full_bar[stage], kb * kBK, row, bz); };
+              load_paired_b_half<BN>(geom, t, 0, sb, load);
+              load_paired_b_half<BN>(geom, t, 1, sb + (BN / 2) * kBK * 2, load);
             } else {
               tma_load_3d(sb, &tmB, &full_bar[stage], kb * kBK, t.col0, bz);
             }

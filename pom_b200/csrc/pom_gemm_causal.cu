@@ -16,7 +16,7 @@ struct PairShape {
 // Channel pairing of the tile: the rotary one when a rotation is asked for, else first half | second half.
 int pair_shape(const pom_rope& r, int P, PairShape* s) {
   if (r.kind == POM_ROPE_2D) {
-    if (P % 32) return POM_ERR_UNSUPPORTED;
+    if (P % 64) return POM_ERR_UNSUPPORTED;  // two sections: a 16-pair sub-unit never reaches over their border
     *s = PairShape{P / 4, 2};
   } else if (r.kind == POM_ROPE_1D || r.kind == POM_ROPE_NONE) {
     if (P % 16) return POM_ERR_UNSUPPORTED;

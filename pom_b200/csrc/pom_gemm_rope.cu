@@ -21,7 +21,7 @@ int pair_shape(const pom_rope& r, int P, PairShape* s) {
     if (P % 16) return POM_ERR_UNSUPPORTED;
     *s = PairShape{P / 2, 1};
   } else if (r.kind == POM_ROPE_2D) {
-    if (P % 32) return POM_ERR_UNSUPPORTED;
+    if (P % 64) return POM_ERR_UNSUPPORTED;  // two sections: a 16-pair sub-unit never reaches over their border
     *s = PairShape{P / 4, 2};
   } else {
     return POM_ERR_UNSUPPORTED;

@@ -75,7 +75,7 @@ class RopeSpec:
         """Whether the rotary GEMM epilogues can take this description for p channels."""
         if self.kind == _abi.ROPE_1D:
             return p % 16 == 0 and self.cos0.shape[1] == p // 2 and self.steps[0] in (0, 1)
-        return (p % 32 == 0 and self.cos0.shape[1] == p // 4 and self.cos1.shape[1] == p // 4
+        return (p % 64 == 0 and self.cos0.shape[1] == p // 4 and self.cos1.shape[1] == p // 4
                 and self.steps[0] in (0, 1) and self.steps[1] in (0, 1))
 
 

@@ -44,6 +44,7 @@ class PoM(nn.Module):
         self.n_sel_heads = n_sel_heads
         self.head_dim = dim * expand // max(n_sel_heads, 1)
         self._po_dim = expand * dim
+        self._grouped_cache = None  # (key, assembled grouped projection) for calls without autograd
         self._se_dim = n_sel_heads if n_sel_heads > 1 else expand * dim
         # creation order matters for seeded initialisation: (qc_proj, se_bias | po_proj, se_proj), po_coeff, ag_proj
         if n_groups > 1:
@@ -75,10 +76,20 @@ class PoM(nn.Module):
         through the copy to the blocks."""
         if self.n_groups == 1:
             return self.qc_proj.weight, self.se_bias
+        wp, ws = self.po_proj.weight, self.se_proj.weight
+        # Without autograd the assembled matrix is kept per parameter version (in-place updates and .data swaps
+        # change the key); with autograd it is rebuilt per call, which is once per version in a training loop.
+        track = torch.is_grad_enabled() and (wp.requires_grad or ws.requires_grad)
+        key = (wp._version, ws._version, wp.data_ptr(), ws.data_ptr(), wp.dtype, wp.device)
+        if not track and self._grouped_cache is not None and self._grouped_cache[0] == key:
+            return self._grouped_cache[1], self.se_proj.bias
         g = self.n_groups
-        w = self.po_proj.weight.squeeze(-1)
+        w = wp.squeeze(-1)
         dense = torch.block_diag(*w.view(g, self._po_dim // g, self.dim // g).unbind(0))
-        return torch.cat([dense, self.se_proj.weight], dim=0), self.se_proj.bias
+        w_qc = torch.cat([dense, ws], dim=0)
+        if not track:
+            self._grouped_cache = (key, w_qc)
+        return w_qc, self.se_proj.bias
 
     def _finish(self, y: torch.Tensor) -> torch.Tensor:
         return y if self.ag_proj.bias is None else y + self.ag_proj.bias

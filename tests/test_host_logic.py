@@ -116,3 +116,28 @@ def test_shape_errors_are_raised_before_any_device_work():
         mod(xq, torch.randn(3, 6, 16))
     with pytest.raises(ValueError, match="feature"):
         mod(xq, torch.randn(2, 6, 8))
+
+
+def test_grouped_projection_is_assembled_once_per_parameter_version():
+    """Without autograd the block-diagonal form of the grouped projection is reused until a parameter changes;
+    with autograd it stays part of the graph of every call (reference pom/pom.py:180-183, 203-205)."""
+    import torch
+    from pom_b200 import PoM
+
+    torch.manual_seed(0)
+    m = PoM(16, 2, 2, n_groups=4)
+    with torch.no_grad():
+        w1, _ = m._weights()
+        w2, _ = m._weights()
+        assert w1 is w2
+        blocks = m.po_proj.weight.squeeze(-1).view(4, 8, 4)
+        assert torch.equal(w1[:8, :4], blocks[0]) and torch.equal(w1[24:32, 12:16], blocks[3])
+        assert float(w1[:8, 4:].abs().max()) == 0.0
+        assert torch.equal(w1[32:], m.se_proj.weight)
+        m.po_proj.weight.mul_(2.0)  # in-place update: new version, new matrix
+        w3, _ = m._weights()
+        assert w3 is not w1 and torch.equal(w3[:8, :4], blocks[0])
+    w4, _ = m._weights()  # autograd on: rebuilt and differentiable
+    assert w4.requires_grad and w4 is not w3
+    w4.sum().backward()
+    assert m.po_proj.weight.grad is not None and float(m.po_proj.weight.grad.min()) == 1.0
