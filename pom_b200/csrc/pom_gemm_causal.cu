@@ -78,6 +78,8 @@ __global__ void __launch_bounds__(128) seg_sum_kernel(const float* __restrict__ 
   seg[(static_cast<long long>(b) * segs + s) * P + p] = a0 + a1;
 }
 
+// Loads of a batch are issued together and only then replaced by their running sums: one memory latency per batch
+// instead of one per element (the sums are formed in the same order either way).
 __global__ void __launch_bounds__(128) seg_scan_kernel(float* __restrict__ seg, const float* __restrict__ carry_in,
                                                        float* __restrict__ total_out, int segs, int P, int reverse) {
   const int p = blockIdx.x * 128 + threadIdx.x, b = blockIdx.y;
@@ -85,12 +87,23 @@ __global__ void __launch_bounds__(128) seg_scan_kernel(float* __restrict__ seg, 
   float* base = seg + static_cast<long long>(b) * segs * P + p;
   float run = carry_in ? carry_in[static_cast<long long>(b) * P + p] : 0.f;
   float own = 0.f;
-  for (int i = 0; i < segs; ++i) {
-    const int s = reverse ? segs - 1 - i : i;
-    const float v = base[static_cast<long long>(s) * P];
-    base[static_cast<long long>(s) * P] = run;
-    run += v;
-    own += v;
+  constexpr int kBatch = 16;
+  for (int i0 = 0; i0 < segs; i0 += kBatch) {
+    float v[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const int i = i0 + j;
+      v[j] = i < segs ? base[static_cast<long long>(reverse ? segs - 1 - i : i) * P] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const int i = i0 + j;
+      if (i < segs) {
+        base[static_cast<long long>(reverse ? segs - 1 - i : i) * P] = run;
+        run += v[j];
+        own += v[j];
+      }
+    }
   }
   if (total_out) total_out[static_cast<long long>(b) * P + p] = own;
 }
@@ -100,13 +113,18 @@ __global__ void __launch_bounds__(128) seg_apply_kernel(float* __restrict__ sums
   const int p = blockIdx.x * 128 + threadIdx.x, s = blockIdx.y, b = blockIdx.z;
   if (p >= P) return;
   const int g0 = s * kSeg, g1 = min(groups, g0 + kSeg);
+  const int n = g1 - g0;
   float run = seg[(static_cast<long long>(b) * segs + s) * P + p];
   float* base = sums + static_cast<long long>(b) * groups * P + p;
-  for (int i = 0; i < g1 - g0; ++i) {
-    const int g = reverse ? g1 - 1 - i : g0 + i;
-    const float v = base[static_cast<long long>(g) * P];
-    base[static_cast<long long>(g) * P] = run;
-    run += v;
+  float v[kSeg];
+#pragma unroll
+  for (int i = 0; i < kSeg; ++i) v[i] = i < n ? base[static_cast<long long>(reverse ? g1 - 1 - i : g0 + i) * P] : 0.f;
+#pragma unroll
+  for (int i = 0; i < kSeg; ++i) {
+    if (i < n) {
+      base[static_cast<long long>(reverse ? g1 - 1 - i : g0 + i) * P] = run;
+      run += v[i];
+    }
   }
 }
 
