@@ -133,7 +133,8 @@ int pom_gemm_bf16(const pom_gemm_args* a, int* status, void* stream);
  * variant; production code leaves it at 0 = choose per problem).  Units digit: 1 = always the kernel that gives one
  * CTA a 128 x BN tile, 2 = always the kernel in which a cluster of two CTAs shares a 256 x BN tile (tcgen05
  * cta_group::2; each CTA loads half of the B tile).  Tens digit: 1 / 2 / 3 = 128 / 192 / 256 columns per tile where
- * the operands allow that width.  Process-wide, not thread-safe against concurrent launches. */
+ * the operands allow that width.  Hundreds digit 1 = the paired epilogues never get the column-stationary grid (every
+ * CTA then changes its column block from tile to tile).  Process-wide, not thread-safe against concurrent launches. */
 int pom_set_gemm_mode(int mode);
 
 /* fp32 SIMT GEMM with the same meaning (fp32 A, Bm, C; out_mode F32 or F32_ACCUM); used by the

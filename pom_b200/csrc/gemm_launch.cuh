@@ -152,7 +152,8 @@ inline int build_maps(const Operands& o, int b_rows, CUtensorMap* tmA, CUtensorM
 }
 
 // Diagnostic knob (pom_set_gemm_mode).  Units digit: 0 automatic choice, 1 always the one-CTA kernel, 2 always the
-// two-CTA (pair) kernel; tens digit: 1 / 2 / 3 forces 128 / 192 / 256 columns per tile.
+// two-CTA (pair) kernel; tens digit: 1 / 2 / 3 forces 128 / 192 / 256 columns per tile; hundreds digit 1: the
+// paired epilogues never get the column-stationary grid.
 extern std::atomic<int> g_gemm_mode;
 
 // Rows per B-operand box of a paired tile: the whole half tile, or, with two sections, the largest piece that never
@@ -216,6 +217,7 @@ int set_smem_once(Kern kern, int smem, bool* done) {
 // Returns the rows per band, or 0 to keep the default schedule (more than 1/16 of the SMs would idle, or the
 // problem has no second wave).
 inline int stationary_rows(long long units, int n_tiles, int slots) {
+  if (g_gemm_mode.load(std::memory_order_relaxed) / 100 == 1) return 0;  // diagnostic: default schedule
   if (n_tiles > slots || units <= slots) return 0;
   const int rows = slots / n_tiles;
   return (slots - rows * n_tiles) * 16 <= slots ? rows : 0;
@@ -287,7 +289,7 @@ inline double plan_factor(bool pair, int bn) {
 inline TilePlan pick_plan(const Operands& o, bool allow_192, bool splittable = false) {
   // diagnostic override (pom_set_gemm_mode): units digit 1 / 2 forces the one-CTA / pair kernel, tens digit
   // 1 / 2 / 3 forces 128 / 192 / 256 columns per tile where that width exists for the operands
-  const int knob = g_gemm_mode.load(std::memory_order_relaxed);
+  const int knob = g_gemm_mode.load(std::memory_order_relaxed) % 100;
   const int mode = knob % 10;
   const int force_bn = knob / 10 == 1 ? 128 : knob / 10 == 2 ? 192 : knob / 10 == 3 ? 256 : 0;
   const long long m_tiles = 1ll * o.batches * ceil_div(o.M, kBM);

@@ -131,7 +131,7 @@ int pom_gemm_bf16(const pom_gemm_args* a, int* status, void* stream) {
 }
 
 int pom_set_gemm_mode(int mode) {
-  if (mode < 0 || mode % 10 > 2 || mode / 10 > 3) return POM_ERR_UNSUPPORTED;
+  if (mode < 0 || mode % 10 > 2 || (mode / 10) % 10 > 3 || mode / 100 > 1) return POM_ERR_UNSUPPORTED;
   g_gemm_mode.store(mode);
   return POM_OK;
 }

@@ -77,6 +77,26 @@ def test_fused_rotary_layer_against_oracle(shape, gemm_mode, monkeypatch):
     assert spy.calls == 0, "the layer left the fused rotary path"
 
 
+@pytest.mark.parametrize("causal", [False, True], ids=["mean", "causal"])
+@pytest.mark.parametrize("gemm_mode", [11, 12, 111, 112], ids=["one_cta", "cta_pair", "one_cta_moving", "cta_pair_moving"])
+def test_several_tiles_per_cta(gemm_mode, causal):
+    """16 384 tokens on a 128 x 128 grid at 128 columns per tile: every CTA works through several tiles, so the
+    stager warp fills the constants of a tile while the epilogue warps are still busy with the one before.  With the
+    column-stationary grid a CTA keeps its column block (and its lane tables) for the whole launch; with the default
+    schedule (hundreds digit of the mode) it changes column block, and section, from tile to tile."""
+    from pom_b200 import _abi
+
+    side = 128
+    cfg, params, x, gy, kw = _case(1, side * side, 128, 2, 2, seed=25, two_d=True, side=side, bias_scale=0.1)
+    if causal:
+        kw["mask"] = "causal"
+    assert _abi.lib().pom_set_gemm_mode(gemm_mode) == 0
+    try:
+        _check_layer(cfg, params, x, gy, kw, f"mode {gemm_mode} causal={causal}")
+    finally:
+        _abi.lib().pom_set_gemm_mode(0)
+
+
 @pytest.mark.parametrize("two_d", [False, True], ids=["1d", "2d"])
 def test_fused_rotary_at_the_long_sequence_width(two_d):
     """The channel width of the 64 k-token benchmark configuration (D = 1152, P = 2304: rotation partners
