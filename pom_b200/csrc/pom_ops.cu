@@ -170,6 +170,11 @@ __device__ __forceinline__ float poly_reg(float a, const float (&c)[KR]) {
   for (int i = KR - 2; i >= 0; --i) r = fmaf(r, a, c[i]);
   return r * a;
 }
+// Two bf16 values packed in a word -> two fp32 values.
+__device__ __forceinline__ float2 bf16x2_to_float2(uint32_t w) {
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+
 template <int KR>
 __device__ __forceinline__ float poly_grad_reg(float a, const float (&c)[KR]) {
   float r = static_cast<float>(KR) * c[KR - 1];
@@ -601,14 +606,21 @@ agg_bwd_stream_kernel(const __grid_constant__ CUtensorMap tmx, const AggBwdDev a
 
   const int c = tx * VEC;
   const bool live = consumer && c < width;
-  float cf[VEC][KR], g[VEC], dc[VEC][KR];
+  // Two channels per register pair: the arithmetic of the loop is issued as packed fp32 pairs (fma.rn.f32x2 ...),
+  // each the IEEE operation of its two halves, which halves its instruction count in an issue-bound kernel.
+  constexpr int H = VEC / 2;
+  float2 pf[H][KR], g[H], dc[H][KR];  // pf: (k + 1) * coeff[k], the factors of the polynomial's derivative
 #pragma unroll
-  for (int e = 0; e < VEC; ++e) {
-    g[e] = live ? a.dH[static_cast<long long>(b) * a.P + p0 + c + e] : 0.f;
+  for (int h = 0; h < H; ++h) {
+    const long long ch = p0 + c + 2 * h;
+    g[h] = live ? make_float2(a.dH[static_cast<long long>(b) * a.P + ch], a.dH[static_cast<long long>(b) * a.P + ch + 1])
+                : make_float2(0.f, 0.f);
 #pragma unroll
     for (int k = 0; k < KR; ++k) {
-      cf[e][k] = (live && k < a.K) ? __ldg(a.coeff + static_cast<long long>(p0 + c + e) * a.K + k) : 0.f;
-      dc[e][k] = 0.f;
+      const bool on = live && k < a.K;
+      const float f = static_cast<float>(k + 1);
+      pf[h][k] = make_float2(on ? f * __ldg(a.coeff + ch * a.K + k) : 0.f, on ? f * __ldg(a.coeff + (ch + 1) * a.K + k) : 0.f);
+      dc[h][k] = make_float2(0.f, 0.f);
     }
   }
   float wb = a.scale;
@@ -637,7 +649,7 @@ agg_bwd_stream_kernel(const __grid_constant__ CUtensorMap tmx, const AggBwdDev a
 #pragma unroll 2
       for (int r = ty; r < rows; r += kGroups) {
         const int n = n0 + r;
-        float x[VEC], o[VEC];
+        float2 x[H], o[H];
         {
           const __nv_bfloat16* src = ring + (stage * kStTok + r) * kStCols + c;
           uint32_t w4[VEC / 2];
@@ -649,32 +661,33 @@ agg_bwd_stream_kernel(const __grid_constant__ CUtensorMap tmx, const AggBwdDev a
             w4[0] = q.x, w4[1] = q.y;
           }
 #pragma unroll
-          for (int e = 0; e < VEC / 2; ++e) {
-            x[2 * e] = __uint_as_float(w4[e] << 16);
-            x[2 * e + 1] = __uint_as_float(w4[e] & 0xffff0000u);
-          }
+          for (int h = 0; h < H; ++h) x[h] = bf16x2_to_float2(w4[h]);
         }
         const float w = a.row_weight ? wb * __ldg(a.row_weight + static_cast<long long>(b) * a.N + n) : wb;
         if (w == 0.f) {  // a token of weight zero: its saved projection may never have been written
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) x[e] = 0.f;
+          for (int h = 0; h < H; ++h) x[h] = make_float2(0.f, 0.f);
         }
+        const float2 w2 = make_float2(w, w);
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) {
-          const float d = w * g[e];
-          const float av = pom_act(x[e]);
-          o[e] = d * poly_grad_reg<KR>(av, cf[e]) * pom_act_grad(x[e]);
-          float pw = av;
+        for (int h = 0; h < H; ++h) {
+          const float2 d = __fmul2_rn(w2, g[h]);
+          const float2 av = make_float2(pom_act(x[h].x), pom_act(x[h].y));
+          float2 rr = pf[h][KR - 1];
+#pragma unroll
+          for (int k = KR - 2; k >= 0; --k) rr = __ffma2_rn(rr, av, pf[h][k]);
+          o[h] = __fmul2_rn(__fmul2_rn(d, rr), make_float2(pom_act_grad(x[h].x), pom_act_grad(x[h].y)));
+          float2 pw = av;
 #pragma unroll
           for (int k = 0; k < KR; ++k) {
-            dc[e][k] = fmaf(d, pw, dc[e][k]);
-            pw *= av;
+            dc[h][k] = __ffma2_rn(d, pw, dc[h][k]);
+            if (k + 1 < KR) pw = __fmul2_rn(pw, av);
           }
         }
         {
           uint32_t pk[VEC / 2];
 #pragma unroll
-          for (int e = 0; e < VEC / 2; ++e) pk[e] = pack_bf16x2(o[2 * e], o[2 * e + 1]);
+          for (int h = 0; h < H; ++h) pk[h] = pack_bf16x2(o[h].x, o[h].y);
           __nv_bfloat16* dst = dxb + static_cast<long long>(n) * a.ld_dx + c;
           if constexpr (VEC == 8) *reinterpret_cast<uint4*>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
           else *reinterpret_cast<uint2*>(dst) = make_uint2(pk[0], pk[1]);
@@ -692,7 +705,8 @@ agg_bwd_stream_kernel(const __grid_constant__ CUtensorMap tmx, const AggBwdDev a
 #pragma unroll
     for (int e = 0; e < VEC; ++e)
 #pragma unroll
-      for (int k = 0; k < KR; ++k) red[((ty - 1) * VEC * KR + e * KR + k) * kLanes + tx] = dc[e][k];
+      for (int k = 0; k < KR; ++k)
+        red[((ty - 1) * VEC * KR + e * KR + k) * kLanes + tx] = (e & 1) ? dc[e >> 1][k].y : dc[e >> 1][k].x;
   }
   __syncthreads();
   if (ty == 0 && live) {
@@ -701,7 +715,7 @@ agg_bwd_stream_kernel(const __grid_constant__ CUtensorMap tmx, const AggBwdDev a
     for (int e = 0; e < VEC; ++e)
 #pragma unroll
       for (int k = 0; k < KR; ++k) {
-        float s = dc[e][k];
+        float s = (e & 1) ? dc[e >> 1][k].y : dc[e >> 1][k].x;
         for (int q = 0; q < kGroups - 1; ++q) s += red[(q * VEC * KR + e * KR + k) * kLanes + tx];
         if (k < a.K) dcp[static_cast<long long>(p0 + c + e) * a.K + k] = s;
       }
@@ -782,17 +796,27 @@ agg_bwd_stream_pair_kernel(const __grid_constant__ CUtensorMap tmx, const __grid
 
   const int c = tx * VEC;
   const bool live = c < width;
-  float cf1[VEC][KR], cf2[VEC][KR], g1[VEC], g2[VEC], dc1[VEC][KR], dc2[VEC][KR];
+  // Two channels per register pair: the arithmetic below is issued as packed fp32 pairs (fma.rn.f32x2 ...), which
+  // halves its instruction count in a kernel that is bound by instruction issue.  Every packed operation is the
+  // IEEE operation of its two halves.
+  constexpr int H = VEC / 2;
+  float2 pf1[H][KR], pf2[H][KR];  // (k + 1) * coeff[k]: the factors of the polynomial's derivative
+  float2 g1[H], g2[H], dc1[H][KR], dc2[H][KR];
 #pragma unroll
-  for (int e = 0; e < VEC; ++e) {
-    g1[e] = (live && !CAUSAL) ? a.dH[static_cast<long long>(b) * a.P + p1_0 + c + e] : 0.f;
-    g2[e] = (live && !CAUSAL) ? a.dH[static_cast<long long>(b) * a.P + p2_0 + c + e] : 0.f;
+  for (int h = 0; h < H; ++h) {
+    const long long ch1 = p1_0 + c + 2 * h, ch2 = p2_0 + c + 2 * h;
+    g1[h] = g2[h] = make_float2(0.f, 0.f);
+    if (live && !CAUSAL) {
+      g1[h] = make_float2(a.dH[static_cast<long long>(b) * a.P + ch1], a.dH[static_cast<long long>(b) * a.P + ch1 + 1]);
+      g2[h] = make_float2(a.dH[static_cast<long long>(b) * a.P + ch2], a.dH[static_cast<long long>(b) * a.P + ch2 + 1]);
+    }
 #pragma unroll
     for (int k = 0; k < KR; ++k) {
-      cf1[e][k] = (live && k < a.K) ? __ldg(a.coeff + static_cast<long long>(p1_0 + c + e) * a.K + k) : 0.f;
-      cf2[e][k] = (live && k < a.K) ? __ldg(a.coeff + static_cast<long long>(p2_0 + c + e) * a.K + k) : 0.f;
-      dc1[e][k] = 0.f;
-      dc2[e][k] = 0.f;
+      const bool on = live && k < a.K;
+      const float f = static_cast<float>(k + 1);
+      pf1[h][k] = make_float2(on ? f * __ldg(a.coeff + ch1 * a.K + k) : 0.f, on ? f * __ldg(a.coeff + (ch1 + 1) * a.K + k) : 0.f);
+      pf2[h][k] = make_float2(on ? f * __ldg(a.coeff + ch2 * a.K + k) : 0.f, on ? f * __ldg(a.coeff + (ch2 + 1) * a.K + k) : 0.f);
+      dc1[h][k] = dc2[h][k] = make_float2(0.f, 0.f);
     }
   }
   float wb = a.scale;
@@ -866,25 +890,23 @@ agg_bwd_stream_pair_kernel(const __grid_constant__ CUtensorMap tmx, const __grid
         if (r >= rows) break;
         const int n = n0 + r;
         const int g = k >> 2, j = k & 3;
-        float x1[VEC], x2[VEC], o1[VEC], o2[VEC], gg1[VEC], gg2[VEC];
+        float2 x1[H], x2[H], o1[H], o2[H], gg1[H], gg2[H];
         {
           const __nv_bfloat16* src = tile + r * kStHalf + c;
           const uint2 qa = *reinterpret_cast<const uint2*>(src);
           const uint2 qb = *reinterpret_cast<const uint2*>(src + kBox);
-          x1[0] = __uint_as_float(qa.x << 16), x1[1] = __uint_as_float(qa.x & 0xffff0000u);
-          x1[2] = __uint_as_float(qa.y << 16), x1[3] = __uint_as_float(qa.y & 0xffff0000u);
-          x2[0] = __uint_as_float(qb.x << 16), x2[1] = __uint_as_float(qb.x & 0xffff0000u);
-          x2[2] = __uint_as_float(qb.y << 16), x2[3] = __uint_as_float(qb.y & 0xffff0000u);
+          x1[0] = bf16x2_to_float2(qa.x), x1[1] = bf16x2_to_float2(qa.y);
+          x2[0] = bf16x2_to_float2(qb.x), x2[1] = bf16x2_to_float2(qb.y);
           if (CAUSAL) {
             const uint2 sa = *reinterpret_cast<const uint2*>(src + 2 * kBox);
             const uint2 sb = *reinterpret_cast<const uint2*>(src + 3 * kBox);
-            gg1[0] = __uint_as_float(sa.x << 16) + kb1.x, gg1[1] = __uint_as_float(sa.x & 0xffff0000u) + kb1.y;
-            gg1[2] = __uint_as_float(sa.y << 16) + kb1.z, gg1[3] = __uint_as_float(sa.y & 0xffff0000u) + kb1.w;
-            gg2[0] = __uint_as_float(sb.x << 16) + kb2.x, gg2[1] = __uint_as_float(sb.x & 0xffff0000u) + kb2.y;
-            gg2[2] = __uint_as_float(sb.y << 16) + kb2.z, gg2[3] = __uint_as_float(sb.y & 0xffff0000u) + kb2.w;
+            gg1[0] = __fadd2_rn(bf16x2_to_float2(sa.x), make_float2(kb1.x, kb1.y));
+            gg1[1] = __fadd2_rn(bf16x2_to_float2(sa.y), make_float2(kb1.z, kb1.w));
+            gg2[0] = __fadd2_rn(bf16x2_to_float2(sb.x), make_float2(kb2.x, kb2.y));
+            gg2[1] = __fadd2_rn(bf16x2_to_float2(sb.y), make_float2(kb2.z, kb2.w));
           } else {
 #pragma unroll
-            for (int e = 0; e < VEC; ++e) gg1[e] = g1[e], gg2[e] = g2[e];
+            for (int h = 0; h < H; ++h) gg1[h] = g1[h], gg2[h] = g2[h];
           }
         }
         float w = 1.f;
@@ -892,32 +914,46 @@ agg_bwd_stream_pair_kernel(const __grid_constant__ CUtensorMap tmx, const __grid
           w = a.row_weight ? wb * __ldg(a.row_weight + static_cast<long long>(b) * a.N + n) : wb;
           if (w == 0.f) {  // a token of weight zero: its saved projection may never have been written
 #pragma unroll
-            for (int e = 0; e < VEC; ++e) x1[e] = 0.f, x2[e] = 0.f;
+            for (int h = 0; h < H; ++h) x1[h] = x2[h] = make_float2(0.f, 0.f);
           }
         }
-        const float C0[4] = {c0[g].x, c0[g].y, c0[g].z, c0[g].w}, S0[4] = {s0[g].x, s0[g].y, s0[g].z, s0[g].w};
-        const float CL[4] = {cl[j].x, cl[j].y, cl[j].z, cl[j].w}, SL[4] = {sl[j].x, sl[j].y, sl[j].z, sl[j].w};
+        const float2 w2 = make_float2(w, w), nw2 = make_float2(-w, -w);
+        const float2 C0[H] = {make_float2(c0[g].x, c0[g].y), make_float2(c0[g].z, c0[g].w)};
+        const float2 S0[H] = {make_float2(s0[g].x, s0[g].y), make_float2(s0[g].z, s0[g].w)};
+        const float2 nS0[H] = {make_float2(-s0[g].x, -s0[g].y), make_float2(-s0[g].z, -s0[g].w)};
+        const float2 CL[H] = {make_float2(cl[j].x, cl[j].y), make_float2(cl[j].z, cl[j].w)};
+        const float2 SL[H] = {make_float2(sl[j].x, sl[j].y), make_float2(sl[j].z, sl[j].w)};
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) {
-          const float cc = C0[e] * CL[e] - S0[e] * SL[e];
-          const float ss = S0[e] * CL[e] + C0[e] * SL[e];
-          const float d1 = w * (gg1[e] * cc + gg2[e] * ss);
-          const float d2 = w * (gg2[e] * cc - gg1[e] * ss);
-          const float av = pom_act(x1[e]), bv = pom_act(x2[e]);
-          o1[e] = d1 * poly_grad_reg<KR>(av, cf1[e]) * pom_act_grad(x1[e]);
-          o2[e] = d2 * poly_grad_reg<KR>(bv, cf2[e]) * pom_act_grad(x2[e]);
-          float pa = av, pb = bv;
+        for (int h = 0; h < H; ++h) {
+          const float2 cc = __ffma2_rn(nS0[h], SL[h], __fmul2_rn(C0[h], CL[h]));  // cos(base + lane offset)
+          const float2 ss = __ffma2_rn(C0[h], SL[h], __fmul2_rn(S0[h], CL[h]));   // sin(base + lane offset)
+          // transposed rotation of the incoming gradient: d1 = w (g1 cc + g2 ss), d2 = w (g2 cc - g1 ss)
+          const float2 d1 = __fmul2_rn(w2, __ffma2_rn(gg2[h], ss, __fmul2_rn(gg1[h], cc)));
+          const float2 d2 = __fmul2_rn(nw2, __ffma2_rn(gg1[h], ss, __fmul2_rn(make_float2(-gg2[h].x, -gg2[h].y), cc)));
+          const float2 av = make_float2(pom_act(x1[h].x), pom_act(x1[h].y));
+          const float2 bv = make_float2(pom_act(x2[h].x), pom_act(x2[h].y));
+          float2 ra = pf1[h][KR - 1], rb = pf2[h][KR - 1];
+#pragma unroll
+          for (int kk = KR - 2; kk >= 0; --kk) {
+            ra = __ffma2_rn(ra, av, pf1[h][kk]);
+            rb = __ffma2_rn(rb, bv, pf2[h][kk]);
+          }
+          o1[h] = __fmul2_rn(__fmul2_rn(d1, ra), make_float2(pom_act_grad(x1[h].x), pom_act_grad(x1[h].y)));
+          o2[h] = __fmul2_rn(__fmul2_rn(d2, rb), make_float2(pom_act_grad(x2[h].x), pom_act_grad(x2[h].y)));
+          float2 pa = av, pb = bv;
 #pragma unroll
           for (int kk = 0; kk < KR; ++kk) {
-            dc1[e][kk] = fmaf(d1, pa, dc1[e][kk]);
-            dc2[e][kk] = fmaf(d2, pb, dc2[e][kk]);
-            pa *= av;
-            pb *= bv;
+            dc1[h][kk] = __ffma2_rn(d1, pa, dc1[h][kk]);
+            dc2[h][kk] = __ffma2_rn(d2, pb, dc2[h][kk]);
+            if (kk + 1 < KR) {
+              pa = __fmul2_rn(pa, av);
+              pb = __fmul2_rn(pb, bv);
+            }
           }
         }
         __nv_bfloat16* dst = dxb + static_cast<long long>(n) * a.ld_dx;
-        *reinterpret_cast<uint2*>(dst + p1_0 + c) = make_uint2(pack_bf16x2(o1[0], o1[1]), pack_bf16x2(o1[2], o1[3]));
-        *reinterpret_cast<uint2*>(dst + p2_0 + c) = make_uint2(pack_bf16x2(o2[0], o2[1]), pack_bf16x2(o2[2], o2[3]));
+        *reinterpret_cast<uint2*>(dst + p1_0 + c) = make_uint2(pack_bf16x2(o1[0].x, o1[0].y), pack_bf16x2(o1[1].x, o1[1].y));
+        *reinterpret_cast<uint2*>(dst + p2_0 + c) = make_uint2(pack_bf16x2(o2[0].x, o2[0].y), pack_bf16x2(o2[1].x, o2[1].y));
       }
     }
     __syncwarp();
@@ -932,8 +968,8 @@ agg_bwd_stream_pair_kernel(const __grid_constant__ CUtensorMap tmx, const __grid
     for (int e = 0; e < VEC; ++e)
 #pragma unroll
       for (int k = 0; k < KR; ++k) {
-        red[((ty - 1) * 2 * VEC * KR + e * KR + k) * kLanes + tx] = dc1[e][k];
-        red[((ty - 1) * 2 * VEC * KR + VEC * KR + e * KR + k) * kLanes + tx] = dc2[e][k];
+        red[((ty - 1) * 2 * VEC * KR + e * KR + k) * kLanes + tx] = (e & 1) ? dc1[e >> 1][k].y : dc1[e >> 1][k].x;
+        red[((ty - 1) * 2 * VEC * KR + VEC * KR + e * KR + k) * kLanes + tx] = (e & 1) ? dc2[e >> 1][k].y : dc2[e >> 1][k].x;
       }
   }
   __syncthreads();
@@ -943,7 +979,8 @@ agg_bwd_stream_pair_kernel(const __grid_constant__ CUtensorMap tmx, const __grid
     for (int e = 0; e < VEC; ++e)
 #pragma unroll
       for (int k = 0; k < KR; ++k) {
-        float s1 = dc1[e][k], s2 = dc2[e][k];
+        float s1 = (e & 1) ? dc1[e >> 1][k].y : dc1[e >> 1][k].x;
+        float s2 = (e & 1) ? dc2[e >> 1][k].y : dc2[e >> 1][k].x;
         for (int qg = 0; qg < kGroups - 1; ++qg) {
           s1 += red[(qg * 2 * VEC * KR + e * KR + k) * kLanes + tx];
           s2 += red[(qg * 2 * VEC * KR + VEC * KR + e * KR + k) * kLanes + tx];
