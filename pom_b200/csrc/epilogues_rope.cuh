@@ -486,8 +486,9 @@ struct EpiGateBwdRope {
     int P;
     RopeEpi rope;
   };
-  // per warp: two alternating sets of {z first, z partner} input blocks, then {dz first, dz partner} output blocks
-  static constexpr int kStageBytes = 8192;
+  // per warp: the {z first, z partner} input blocks (refilled for the next sub-unit as soon as their rows are in
+  // registers), then the {dz first, dz partner} output blocks.  4 KiB per warp leave room for a fourth pipeline stage.
+  static constexpr int kStageBytes = 4096;
   static constexpr int kSmemBytes = 0;
   static constexpr bool kStager = true;
   template <int BN>
@@ -498,9 +499,9 @@ struct EpiGateBwdRope {
   }
 
   static __device__ __forceinline__ void fetch_z(const EpiMaps& maps, const TileCtx& t, const PairPos& pp, EpiIO& io,
-                                                 int quarter, int lane, int set) {
+                                                 int quarter, int lane) {
     if (lane == 0) {
-      uint8_t* blk = io.buf0 + set * 2048;
+      uint8_t* blk = io.buf0;
       mbar_expect_tx(io.bar, 2048);
       tma_load_4d(blk, &maps.in0, io.bar, pp.u, 2 * pp.sec, t.row0 + quarter * 32, t.b);
       tma_load_4d(blk + 1024, &maps.in0, io.bar, pp.u, 2 * pp.sec + 1, t.row0 + quarter * 32, t.b);
@@ -529,7 +530,7 @@ struct EpiGateBwdRope {
                                                   int) {
     const int half = warp_in_epi >> 2, quarter = (warp_in_epi + 2) & 3;
     const PairPos pp = pair_pos(g, t, 16 * half);
-    if (pp.ok) fetch_z(maps, t, pp, io, quarter, epi_tid & 31, 0);
+    if (pp.ok) fetch_z(maps, t, pp, io, quarter, epi_tid & 31);
   }
 
   template <int BN>
@@ -544,9 +545,8 @@ struct EpiGateBwdRope {
     const float* hrow = sc.tile(slot);
     const RopeView rs{sc.base_cos(slot), sc.base_sin(slot), sc.lane()};
     const int y = t.row0 + quarter * 32;
-    uint8_t* out_blk = io.buf0 + 4096;
+    uint8_t* out_blk = io.buf0 + 2048;
     bool alive = true;
-    int set = 0;
 #pragma unroll 1
     for (int su = half; su < BN / 32; su += kEpiColSplit) {
       float* h1p = buf_h + quarter * BN + 16 * su;
@@ -564,16 +564,15 @@ struct EpiGateBwdRope {
       if (alive) alive = mbar_wait(io.bar, io.load_phase, io.abort_flag, io.status, kStatusEpilogueTimeout);
       alive = __all_sync(0xffffffffu, alive);
       io.load_phase ^= 1u;
-      // the other set was consumed one sub-unit ago by every lane (the __all_sync above orders it): refill it
+      read_block16<0>(io.buf0, lane, z);
+      read_block16<16>(io.buf0 + 1024, lane, z);
+      // every lane holds its z rows: the blocks are refilled for this warp's next sub-unit
       const int nsu = su + kEpiColSplit;
       __syncwarp();
       if (alive && nsu < BN / 32) {
         const PairPos np = pair_pos(g, t, 16 * nsu);
-        if (np.ok) fetch_z(maps, t, np, io, quarter, lane, set ^ 1);
+        if (np.ok) fetch_z(maps, t, np, io, quarter, lane);
       }
-      read_block16<0>(io.buf0 + set * 2048, lane, z);
-      read_block16<16>(io.buf0 + set * 2048 + 1024, lane, z);
-      set ^= 1;
       tmem_ld_wait();
 #pragma unroll
       for (int i = 0; i < 16; i += 4) {
