@@ -78,6 +78,26 @@ def test_fused_rotary_layer_against_oracle(shape, gemm_mode, monkeypatch):
 
 
 @pytest.mark.parametrize("causal", [False, True], ids=["mean", "causal"])
+@pytest.mark.parametrize("gemm_mode", [11, 12, 21, 22, 31, 32], ids=["one128", "pair128", "one192", "pair192", "one256", "pair256"])
+@pytest.mark.parametrize("D", [96, 160], ids=["P192", "P320"])
+def test_tiles_that_reach_over_the_section_border(D, gemm_mode, causal):
+    """2-D layouts whose sections (48 or 80 pairs) are not a multiple of any tile's half width: every tile width
+    cuts the pairs of both sections laid end to end, so tiles reach over the border between the row half and the
+    column half, and the B operand arrives in boxes of gcd(pairs per section, half width) = 16 rows."""
+    from pom_b200 import _abi
+
+    side = 32
+    cfg, params, x, gy, kw = _case(2, side * side, D, 2, 2, seed=26, two_d=True, side=side, bias_scale=0.1)
+    if causal:
+        kw["mask"] = "causal"
+    assert _abi.lib().pom_set_gemm_mode(gemm_mode) == 0
+    try:
+        _check_layer(cfg, params, x, gy, kw, f"D={D} mode {gemm_mode} causal={causal}")
+    finally:
+        _abi.lib().pom_set_gemm_mode(0)
+
+
+@pytest.mark.parametrize("causal", [False, True], ids=["mean", "causal"])
 @pytest.mark.parametrize("gemm_mode", [11, 12, 111, 112], ids=["one_cta", "cta_pair", "one_cta_moving", "cta_pair_moving"])
 def test_several_tiles_per_cta(gemm_mode, causal):
     """16 384 tokens on a 128 x 128 grid at 128 columns per tile: every CTA works through several tiles, so the
