@@ -141,18 +141,37 @@ def bind_to_gpu_numa_node(local_rank):
     try:
         p = torch.cuda.get_device_properties(local_rank)
         bus = f"{p.pci_domain_id:04x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0"
+    except Exception:
+        return None
+    cpus, how = set(), None
+    try:
         node = int(open(f"/sys/bus/pci/devices/{bus}/numa_node").read().strip())
-        if node < 0:
-            return None
+        if node >= 0:
+            for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+            how = f"numa node {node} (sysfs)"
+    except Exception:
         cpus = set()
-        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
-            lo, _, hi = part.partition("-")
-            cpus.update(range(int(lo), int(hi or lo) + 1))
+    if not cpus:
+        # containers often hide the PCI device's numa_node: the driver's own CPU affinity mask of the GPU (a read)
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+            words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+            for i, w in enumerate(words):
+                cpus.update(64 * i + b for b in range(64) if (int(w) >> b) & 1)
+            how = "cpu affinity of the GPU (NVML)"
+        except Exception:
+            cpus = set()
+    try:
         allowed = cpus & os.sched_getaffinity(0)
-        if not allowed:
+        if not allowed or allowed == os.sched_getaffinity(0):
             return None
         os.sched_setaffinity(0, allowed)
-        return f"numa node {node}, {len(allowed)} cpus"
+        return f"{how}, {len(allowed)} cpus"
     except Exception:
         return None
 
