@@ -9,11 +9,12 @@
 // (G·W) and the weight-gradient products (Gᵀ·X) of the PoM layer without any
 // transposed copy.
 //
-// CTA layout (320 threads, one CTA per SM):
+// CTA layout (352 threads, one CTA per SM):
 //   warp 0      : TMA producer   (one lane issues the tile loads)
 //   warp 1      : MMA issuer     (one lane issues tcgen05.mma / commit); owns TMEM alloc
 //   warps 2..9  : epilogue       (two warps per 32-lane quarter of the accumulator, interleaving
 //                                 the 32-column chunks of the tile)
+//   warp 10     : stager         (epilogues with Epi::kStager: fills the constants of the next tile)
 // The accumulator is double-buffered in tensor memory (2 x BN fp32 columns), so
 // the epilogue of tile i overlaps the main loop of tile i+1.
 //
