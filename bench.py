@@ -90,6 +90,12 @@ class ClockSampler:
               "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
+        # nvidia-smi numbers GPUs by PCI bus id, CUDA by its own order: name the GPU by its bus id where possible
+        try:
+            p = torch.cuda.get_device_properties(index)
+            index = f"{p.pci_domain_id:08x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0"
+        except Exception:
+            pass
         self.index, self.rows, self.proc = index, [], None
 
     def start(self):
