@@ -32,7 +32,7 @@
 extern "C" {
 #endif
 
-#define POM_ABI_VERSION 2
+#define POM_ABI_VERSION 3
 
 enum {
   POM_OK = 0,
@@ -513,6 +513,19 @@ typedef struct pom_layer_args {
   float* d_hpast;             /* (B, P) fp32 or NULL */
   void* workspace;            /* pom_layer_workspace_bytes() bytes, 256-byte aligned, shared by both calls */
   uint64_t workspace_bytes;
+  /* Rotary embedding (pom/pom_rope.py:487-522) and the token-causal mask (pom/pom.py:92-95) inside the same two
+   * calls, under the conditions of pom_ctx_gemm / pom_gate_gemm (degree <= 4, P % 16 == 0, 2-D: P % 64 == 0,
+   * positions constant or consecutive inside aligned 32-token groups); otherwise POM_ERR_UNSUPPORTED. */
+  pom_rope rope_c;            /* positions of the N context tokens (kind POM_ROPE_NONE: no rotation) */
+  pom_rope rope_q;            /* positions of the T query tokens */
+  const void* w_ag_t;         /* backward with rope_q or causal: (P, D) bf16, the output weight transposed
+                                 (pom_transpose_bf16) */
+  int32_t causal;             /* 1: token-causal prefix mean; needs T == N, no mask, frames == 1, no state */
+  int32_t reserved0;
+  int64_t token_offset;       /* causal: global index of token 0 */
+  void* pre;                  /* causal: (B, N, P) bf16 running sums per 32-token group (forward out, backward in) */
+  float* carry;               /* causal: (B, ceil(N/32), P) fp32 group carries (forward out, backward in); H is
+                                 not used */
 } pom_layer_args;
 uint64_t pom_layer_workspace_bytes(const pom_layer_args* a);
 int pom_layer_fwd(const pom_layer_args* a, int* status, void* stream);

@@ -13,7 +13,7 @@ import torch
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libpom_b200.so")
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 POM_BF16, POM_F32 = 0, 1
 ROPE_NONE, ROPE_1D, ROPE_2D = 0, 1, 2
 OUT_BF16, OUT_F32, OUT_F32_ACCUM = 0, 1, 2
@@ -175,6 +175,9 @@ class LayerArgs(C.Structure):
         ("dy", C.c_void_p), ("dh_state", C.c_void_p), ("G", C.c_void_p), ("dxq", C.c_void_p), ("dxc", C.c_void_p),
         ("grads", C.c_void_p), ("d_hpast", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_uint64),
+        ("rope_c", Rope), ("rope_q", Rope), ("w_ag_t", C.c_void_p),
+        ("causal", C.c_int32), ("reserved0", C.c_int32), ("token_offset", C.c_int64),
+        ("pre", C.c_void_p), ("carry", C.c_void_p),
     ]
 
 

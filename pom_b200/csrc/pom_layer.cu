@@ -2,7 +2,8 @@
 // autograd as two calls, pom_layer_fwd and pom_layer_bwd, that enqueue the tensor-core phases, the small
 // reductions between them and the streamed aggregation backward on one stream.  Host-side sequencing only: every
 // kernel belongs to the phase entry points of this library, which stay available for hosts that need to put an
-// exchange between the phases (token sharding) or that use the operator path (rotary embedding, causal, fp32).
+// exchange between the phases (token sharding) or that use the operator path (fp32, unusual positions).  Rotary
+// embedding and the token-causal mask ride in the same phases (pom_layer_args::rope_c / rope_q / causal).
 #include "common.cuh"
 #include <cuda_bf16.h>
 
@@ -24,8 +25,14 @@ struct Workspace {
   uint64_t dc_partial;    // (B * chunks_N, P * K)
   uint64_t dh;            // (B, P)
   uint64_t dh2;           // (B, P)
+  // token-causal
+  uint64_t scan;          // (B, ceil(groups/32), P) fp32: scratch of pom_group_scan (both calls)
+  uint64_t suf;           // (B, N, P) bf16: running sums of the gradient of the prefix means (backward)
+  uint64_t gsum;          // (B, groups, P) fp32: their group totals, then carries (backward)
   uint64_t total;
 };
+
+inline int groups_of(int rows) { return (rows + 31) / 32; }
 
 Workspace carve(const pom_layer_args* a) {
   Workspace w;
@@ -37,8 +44,10 @@ Workspace carve(const pom_layer_args* a) {
   off = align_up(off + bp);
   w.tile_w = off;
   off = align_up(off + static_cast<uint64_t>(a->B) * m_tiles(a->N) * sizeof(float));
+  w.scan = off;
+  if (a->causal) off = align_up(off + static_cast<uint64_t>((groups_of(a->N) + 31) / 32) * bp);
   const uint64_t fwd_end = off;
-  // the backward regions reuse the buffer from its start
+  // the backward regions reuse the buffer from its start (the scan scratch keeps its place: it is free again then)
   off = 0;
   w.dh_partial = off;
   off = align_up(off + static_cast<uint64_t>(m_tiles(a->T)) * bp);
@@ -50,12 +59,21 @@ Workspace carve(const pom_layer_args* a) {
   off = align_up(off + bp);
   w.dh2 = off;
   off = align_up(off + bp);
+  w.suf = w.gsum = off;
+  if (a->causal) {
+    if (off < fwd_end) off = fwd_end;  // past the scan scratch
+    w.suf = off;
+    off = align_up(off + static_cast<uint64_t>(a->B) * a->N * a->P * 2);
+    w.gsum = off;
+    off = align_up(off + static_cast<uint64_t>(groups_of(a->N)) * bp);
+  }
   w.total = off > fwd_end ? off : fwd_end;
   return w;
 }
 
 int check_common(const pom_layer_args* a) {
-  if (!a || !a->xq || !a->w_qc || !a->w_ag || !a->se_bias || !a->coeff || !a->H || !a->workspace) return POM_ERR_NULL;
+  if (!a || !a->xq || !a->w_qc || !a->w_ag || !a->se_bias || !a->coeff || !a->workspace) return POM_ERR_NULL;
+  if (!a->causal && !a->H) return POM_ERR_NULL;
   if (a->B <= 0 || a->T <= 0 || a->N <= 0 || a->D <= 0 || a->P <= 0 || a->K < 1) return POM_ERR_BAD_SHAPE;
   if (a->K > 16) return POM_ERR_K_TOO_LARGE;
   if (a->D % 8 || a->P % 8) return POM_ERR_BAD_ALIGN;
@@ -64,6 +82,10 @@ int check_common(const pom_layer_args* a) {
   if (a->frames < 1 || a->B % a->frames) return POM_ERR_BAD_SHAPE;
   if (a->frames > 1 && (a->mask || a->h_past)) return POM_ERR_UNSUPPORTED;
   if (a->mask && !a->denom) return POM_ERR_NULL;
+  if (a->causal) {
+    if (a->causal != 1 || a->T != a->N || a->mask || a->frames != 1 || a->h_past) return POM_ERR_UNSUPPORTED;
+    if (!a->pre || !a->carry) return POM_ERR_NULL;
+  }
   if (a->workspace_bytes < carve(a).total) return POM_ERR_TOO_LARGE;
   return POM_OK;
 }
@@ -102,6 +124,25 @@ int gemm(const void* A, const void* Bm, void* C, int64_t M, int64_t N, int64_t K
   g.residual = residual;
   g.ldr = ldr;
   return pom_gemm_bf16(&g, status, stream);
+}
+
+// dX (and dXc) = G·Wqc, dWqc += Gᵀ·X: the last launches of the backward call, whatever produced G = [dhp | dz].
+int input_and_weight_grads(const pom_layer_args* a, __nv_bfloat16* G, __nv_bfloat16* g_hp, __nv_bfloat16* g_z,
+                           float* d_wqc, int* status, void* stream) {
+  const int D = a->D, P = a->P;
+  const int64_t rows_q = static_cast<int64_t>(a->B) * a->T, rows_c = static_cast<int64_t>(a->B) * a->N;
+  if (a->self_mixing) {
+    POM_TRY(gemm(G, a->w_qc, a->dxq, rows_q, D, 2LL * P, 2LL * P, D, D, false, true, POM_OUT_BF16, nullptr, 0, status,
+                 stream));
+    return gemm(G, a->xq, d_wqc, 2LL * P, D, rows_q, 2LL * P, D, D, true, true, POM_OUT_F32_ACCUM, nullptr, 0, status,
+                stream);
+  }
+  const __nv_bfloat16* w_se = bf(a->w_qc) + static_cast<int64_t>(P) * D;
+  POM_TRY(gemm(g_hp, a->w_qc, a->dxc, rows_c, D, P, P, D, D, false, true, POM_OUT_BF16, nullptr, 0, status, stream));
+  POM_TRY(gemm(g_z, w_se, a->dxq, rows_q, D, P, P, D, D, false, true, POM_OUT_BF16, nullptr, 0, status, stream));
+  POM_TRY(gemm(g_hp, a->xc, d_wqc, P, D, rows_c, P, D, D, true, true, POM_OUT_F32_ACCUM, nullptr, 0, status, stream));
+  return gemm(g_z, a->xq, d_wqc + static_cast<int64_t>(P) * D, P, D, rows_q, P, D, D, true, true, POM_OUT_F32_ACCUM,
+              nullptr, 0, status, stream);
 }
 
 }  // namespace
@@ -144,6 +185,40 @@ int pom_layer_fwd(const pom_layer_args* a, int* status, void* stream) {
   c.D = a->D;
   c.P = a->P;
   c.K = a->K;
+  c.rope = a->rope_c;
+  const int64_t rows = static_cast<int64_t>(a->B) * a->T;
+  if (a->causal) {
+    // running sums per 32-token group in the context epilogue, carries across groups, prefix means in the gate epilogue
+    c.causal = 1;
+    c.pre_out = a->pre;
+    c.ld_pre = a->P;
+    c.group_sums = a->carry;
+    POM_TRY(pom_ctx_gemm(&c, status, stream));
+    POM_TRY(pom_group_scan(a->carry, nullptr, nullptr, at<float>(a, w.scan), a->B, groups_of(a->N), a->P, 0, stream));
+    pom_gate_args g{};
+    g.X = a->xq;
+    g.Wse = w_se;
+    g.bias = a->se_bias;
+    g.z_out = a->save ? a->z : nullptr;
+    g.sh_out = a->sh;
+    g.ldx = a->D;
+    g.ldw = a->D;
+    g.ld_z = a->P;
+    g.ld_sh = a->P;
+    g.B = a->B;
+    g.T = a->T;
+    g.D = a->D;
+    g.P = a->P;
+    g.rope = a->rope_q;
+    g.causal = 1;
+    g.pre = a->pre;
+    g.ld_pre = a->P;
+    g.carry = a->carry;
+    g.token_offset = a->token_offset;
+    POM_TRY(pom_gate_gemm(&g, status, stream));
+    return gemm(a->sh, a->w_ag, a->y, rows, a->D, a->P, a->P, a->P, a->D, false, false, POM_OUT_BF16, a->residual,
+                a->D, status, stream);
+  }
   POM_TRY(pom_ctx_gemm(&c, status, stream));
 
   const bool post = a->frames > 1 || a->h_past;
@@ -170,9 +245,9 @@ int pom_layer_fwd(const pom_layer_args* a, int* status, void* stream) {
   g.T = a->T;
   g.D = a->D;
   g.P = a->P;
+  g.rope = a->rope_q;
   POM_TRY(pom_gate_gemm(&g, status, stream));
 
-  const int64_t rows = static_cast<int64_t>(a->B) * a->T;
   return gemm(a->sh, a->w_ag, a->y, rows, a->D, a->P, a->P, a->P, a->D, false, false, POM_OUT_BF16, a->residual, a->D,
               status, stream);
 }
@@ -181,6 +256,8 @@ int pom_layer_bwd(const pom_layer_args* a, int* status, void* stream) {
   POM_TRY(check_common(a));
   if (!a->dy || !a->hp || !a->z || !a->sh || !a->G || !a->dxq || !a->grads) return POM_ERR_NULL;
   if (!a->self_mixing && !a->dxc) return POM_ERR_NULL;
+  const bool rot_q = a->rope_q.kind != POM_ROPE_NONE;
+  if ((rot_q || a->causal) && !a->w_ag_t) return POM_ERR_NULL;
   const Workspace w = carve(a);
   const int B = a->B, T = a->T, N = a->N, D = a->D, P = a->P, K = a->K;
   const int64_t rows_q = static_cast<int64_t>(B) * T, rows_c = static_cast<int64_t>(B) * N;
@@ -218,6 +295,44 @@ int pom_layer_bwd(const pom_layer_args* a, int* status, void* stream) {
   gb.T = T;
   gb.D = D;
   gb.P = P;
+  gb.rope = a->rope_q;
+  gb.WoT = a->w_ag_t;
+  gb.ldwt = D;
+  pom_agg_bwd_args ab{};
+  ab.x = a->hp;
+  ab.coeff = a->coeff;
+  ab.dx = g_hp;
+  ab.dcoeff_partial = at<float>(a, w.dc_partial);
+  ab.ldx = P;
+  ab.ld_dx = ld_g;
+  ab.B = B;
+  ab.N = N;
+  ab.P = P;
+  ab.K = K;
+  ab.dtype = POM_BF16;
+  ab.rope = a->rope_c;
+  if (a->causal) {
+    gb.causal = 1;
+    gb.pre = a->pre;
+    gb.ld_pre = P;
+    gb.carry = a->carry;
+    gb.suf_out = at<void>(a, w.suf);
+    gb.ld_suf = P;
+    gb.group_sums = at<float>(a, w.gsum);
+    gb.token_offset = a->token_offset;
+    POM_TRY(pom_gate_bwd_gemm(&gb, status, stream));
+    POM_TRY(pom_reduce_partials(gb.db_partial, d_bias, nullptr, 1.f, 1, B * m_tiles(T), P, stream));
+    POM_TRY(pom_group_scan(gb.group_sums, nullptr, nullptr, at<float>(a, w.scan), B, groups_of(N), P, 1, stream));
+    // gradient of token n's features: suf[n] + carry of the groups after its own
+    ab.dout = gb.suf_out;
+    ab.ld_dout = P;
+    ab.partial = gb.group_sums;
+    ab.scale = 1.f;
+    ab.causal = 3;
+    POM_TRY(pom_poly_agg_bwd(&ab, stream));
+    POM_TRY(pom_reduce_partials(ab.dcoeff_partial, d_coeff, nullptr, 1.f, 1, pom_poly_agg_bwd_slots(&ab), P * K, stream));
+    return input_and_weight_grads(a, G, g_hp, g_z, d_wqc, status, stream);
+  }
   POM_TRY(pom_gate_bwd_gemm(&gb, status, stream));
   float* dH = at<float>(a, w.dh);
   float* dH2 = at<float>(a, w.dh2);
@@ -244,38 +359,14 @@ int pom_layer_bwd(const pom_layer_args* a, int* status, void* stream) {
     scale /= (a->n_past + 1.f);
   }
 
-  pom_agg_bwd_args ab{};
-  ab.x = a->hp;
-  ab.coeff = a->coeff;
   ab.row_weight = a->mask;
   ab.denom = a->mask ? a->denom : nullptr;
   ab.dH = dH;
-  ab.dx = g_hp;
-  ab.dcoeff_partial = at<float>(a, w.dc_partial);
-  ab.ldx = P;
-  ab.ld_dx = ld_g;
   ab.scale = scale;
-  ab.B = B;
-  ab.N = N;
-  ab.P = P;
-  ab.K = K;
-  ab.dtype = POM_BF16;
   ab.causal = 0;
   POM_TRY(pom_poly_agg_bwd(&ab, stream));
   POM_TRY(pom_reduce_partials(ab.dcoeff_partial, d_coeff, nullptr, 1.f, 1, pom_poly_agg_bwd_slots(&ab), P * K, stream));
-
-  if (a->self_mixing) {
-    POM_TRY(gemm(G, a->w_qc, a->dxq, rows_q, D, 2LL * P, 2LL * P, D, D, false, true, POM_OUT_BF16, nullptr, 0, status,
-                 stream));
-    return gemm(G, a->xq, d_wqc, 2LL * P, D, rows_q, 2LL * P, D, D, true, true, POM_OUT_F32_ACCUM, nullptr, 0, status,
-                stream);
-  }
-  const __nv_bfloat16* w_se = bf(a->w_qc) + static_cast<int64_t>(P) * D;
-  POM_TRY(gemm(g_hp, a->w_qc, a->dxc, rows_c, D, P, P, D, D, false, true, POM_OUT_BF16, nullptr, 0, status, stream));
-  POM_TRY(gemm(g_z, w_se, a->dxq, rows_q, D, P, P, D, D, false, true, POM_OUT_BF16, nullptr, 0, status, stream));
-  POM_TRY(gemm(g_hp, a->xc, d_wqc, P, D, rows_c, P, D, D, true, true, POM_OUT_F32_ACCUM, nullptr, 0, status, stream));
-  return gemm(g_z, a->xq, d_wqc + static_cast<int64_t>(P) * D, P, D, rows_q, P, D, D, true, true, POM_OUT_F32_ACCUM,
-              nullptr, 0, status, stream);
+  return input_and_weight_grads(a, G, g_hp, g_z, d_wqc, status, stream);
 }
 
 }  // extern "C"

@@ -251,13 +251,13 @@ class _PoMLayer(torch.autograd.Function):
         # the groups), with or without rotation
         two_d = any(r is not None and r.kind == _abi.ROPE_2D for r in (spec.rope_ctx, spec.rope_qry))
         fused_causal = (causal and bf16 and not heads and (not rotary or rope_ok) and K <= 4 and D % 8 == 0
-                        and P % (32 if two_d else 16) == 0)
+                        and P % (64 if two_d else 16) == 0)
 
         hp = z = Hc = s32 = None
         collapsed = False
         ctx.collapsed = False
         ctx.fused_causal = fused_causal
-        ctx.composite = fused and shard is None and WHOLE_LAYER_CALLS and not rotary
+        ctx.composite = (fused or fused_causal) and shard is None and WHOLE_LAYER_CALLS
         if ctx.composite:
             # the whole fused layer is one library call (no exchange to put between its phases)
             if spec.frames > 1 and (spec.n_past is not None or maskf is not None):
@@ -265,10 +265,13 @@ class _PoMLayer(torch.autograd.Function):
             h_past32 = None
             if spec.n_past is not None and h_past is not None:
                 h_past32 = _f32(h_past.reshape(B, P).contiguous())
-            y, hp, z, sh, H, denom = ops.layer_fwd(
+            out = ops.layer_fwd(
                 xq, None if spec.self_mixing else xc, w_qc, w_ag, bias32, coeff32, mask=maskf, h_past=h_past32,
                 n_past=spec.n_past, residual=None if residual is None else residual.contiguous(), frames=spec.frames,
-                save=need_grad)
+                save=need_grad, rope_c=spec.rope_ctx, rope_q=spec.rope_qry, causal=fused_causal, token_offset=offset)
+            y, hp, z, sh, H, denom = out[:6]
+            if fused_causal:
+                h_past32 = out[6]  # the running sums `pre` travel in the slot that holds h_past otherwise
             ctx.has_residual = residual is not None
             ctx.spec = spec
             ctx.fused = True
@@ -384,10 +387,15 @@ class _PoMLayer(torch.autograd.Function):
         if ctx.composite:
             h_past32 = Hc  # slot reused by the composite forward
             dh32 = None if dh_state is None else _f32(dh_state.reshape(B, P).contiguous())
+            w_t = None
+            if ctx.fused_causal or spec.rope_qry is not None:  # these forms read the output weight transposed
+                w_t = _derived_of(p_ag, "transposed", lambda w: ops.transpose_bf16(w.contiguous()))
             dxq, dxc, flat, d_hpast = ops.layer_bwd(
                 dy, xq, None if spec.self_mixing else xc, w_qc, w_ag, bias32, coeff32, hp, z, sh, H, mask=maskf,
-                denom=denom, h_past=h_past32, n_past=spec.n_past, dh_state=dh32, frames=spec.frames,
-                want_d_hpast=bool(ctx.needs_input_grad[7]))
+                denom=denom, h_past=None if ctx.fused_causal else h_past32, n_past=spec.n_past, dh_state=dh32,
+                frames=spec.frames, want_d_hpast=bool(ctx.needs_input_grad[7]), rope_c=spec.rope_ctx,
+                rope_q=spec.rope_qry, w_ag_t=w_t, causal=h_past32 if ctx.fused_causal else None,
+                token_offset=ctx.dims[9])
             if d_hpast is not None:
                 d_hpast = d_hpast.view(B, 1, P)
                 if ctx.h_past_dtype != torch.float32:

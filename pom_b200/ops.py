@@ -387,7 +387,8 @@ def gate_bwd_gemm(dy: torch.Tensor, w_o: torch.Tensor, bias: torch.Tensor, h: Op
 
 
 # ---------------------------------------------------------------------------- whole layer (bf16, fused path)
-def _layer_args(xq, xc, w_qc, w_ag, bias, coeff, mask, h_past, n_past, frames):
+def _layer_args(xq, xc, w_qc, w_ag, bias, coeff, mask, h_past, n_past, frames, rope_c=None, rope_q=None,
+                causal=False, token_offset=0):
     B, T, D = xq.shape
     N = T if xc is None else xc.shape[1]
     P, K = coeff.shape
@@ -396,6 +397,8 @@ def _layer_args(xq, xc, w_qc, w_ag, bias, coeff, mask, h_past, n_past, frames):
     a.self_mixing, a.frames, a.n_past = int(xc is None), int(frames), float(n_past or 0.0)
     a.xq, a.xc, a.w_qc, a.w_ag = ptr(xq), ptr(xc), ptr(w_qc), ptr(w_ag)
     a.se_bias, a.coeff, a.mask, a.h_past = ptr(bias), ptr(coeff), ptr(mask), ptr(h_past)
+    a.rope_c, a.rope_q = _rope_c(rope_c), _rope_c(rope_q)
+    a.causal, a.token_offset = int(bool(causal)), int(token_offset)
     nbytes = int(_abi.lib().pom_layer_workspace_bytes(C.byref(a)))
     ws = torch.empty((nbytes,), dtype=torch.uint8, device=xq.device)
     a.workspace, a.workspace_bytes = ptr(ws), nbytes
@@ -403,30 +406,48 @@ def _layer_args(xq, xc, w_qc, w_ag, bias, coeff, mask, h_past, n_past, frames):
 
 
 def layer_fwd(xq, xc, w_qc, w_ag, bias, coeff, *, mask=None, h_past=None, n_past=0.0, residual=None, frames=1,
-              save=True):
-    """Whole fused forward (``xc`` None = self-mixing).  Returns (y, hp, z, sh, H, denom); hp and z are None unless
-    ``save``; denom is None without a mask."""
+              save=True, rope_c: Optional[RopeSpec] = None, rope_q: Optional[RopeSpec] = None, causal=False,
+              token_offset=0):
+    """Whole fused forward (``xc`` None = self-mixing), optionally with rotary embedding of the context features
+    (``rope_c``) and of the gate (``rope_q``).  Returns (y, hp, z, sh, H, denom); hp and z are None unless ``save``;
+    denom is None without a mask.  ``causal``: the token-causal prefix mean; H is then the (B, ceil(N/32), P) group
+    carries and the seventh return value the (B, N, P) bf16 running sums ``pre`` (both needed by :func:`layer_bwd`)."""
     dev = _require_cuda(xq, xc, w_qc, w_ag, bias, coeff, mask, h_past, residual)
-    a, ws = _layer_args(xq, xc, w_qc, w_ag, bias, coeff, mask, h_past, n_past, frames)
+    a, ws = _layer_args(xq, xc, w_qc, w_ag, bias, coeff, mask, h_past, n_past, frames, rope_c, rope_q, causal,
+                        token_offset)
     B, T, N, D, P = a.B, a.T, a.N, a.D, a.P
     bf = dict(dtype=torch.bfloat16, device=dev)
     y, sh = torch.empty((B, T, D), **bf), torch.empty((B, T, P), **bf)
     hp = torch.empty((B, N, P), **bf) if save else None
     z = torch.empty((B, T, P), **bf) if save else None
-    H = torch.empty((B, P), dtype=torch.float32, device=dev)
     denom = torch.empty((B,), dtype=torch.float32, device=dev) if mask is not None else None
     a.save, a.residual = int(save), ptr(residual)
-    a.y, a.hp, a.z, a.sh, a.H, a.denom = ptr(y), ptr(hp), ptr(z), ptr(sh), ptr(H), ptr(denom)
+    a.y, a.hp, a.z, a.sh, a.denom = ptr(y), ptr(hp), ptr(z), ptr(sh), ptr(denom)
+    pre = None
+    if causal:
+        pre = torch.empty((B, N, P), **bf)
+        H = torch.empty((B, token_groups(N), P), dtype=torch.float32, device=dev)
+        a.pre, a.carry = ptr(pre), ptr(H)
+    else:
+        H = torch.empty((B, P), dtype=torch.float32, device=dev)
+        a.H = ptr(H)
     _abi.check(_abi.lib().pom_layer_fwd(C.byref(a), ptr(_abi.status_word(dev)), _abi.stream_ptr()), "pom_layer_fwd")
+    if causal:
+        return y, hp, z, sh, H, denom, pre
     return y, hp, z, sh, H, denom
 
 
 def layer_bwd(dy, xq, xc, w_qc, w_ag, bias, coeff, hp, z, sh, H, *, mask=None, denom=None, h_past=None, n_past=0.0,
-              dh_state=None, frames=1, want_d_hpast=False):
+              dh_state=None, frames=1, want_d_hpast=False, rope_c: Optional[RopeSpec] = None,
+              rope_q: Optional[RopeSpec] = None, w_ag_t: Optional[torch.Tensor] = None, causal=None, token_offset=0):
     """Whole fused backward.  Returns (dxq, dxc or None, flat fp32 parameter gradients
-    [dWqc | dWo | dbias | dcoeff], d_hpast (B, P) fp32 or None)."""
-    dev = _require_cuda(dy, xq, xc, w_qc, w_ag, bias, coeff, hp, z, sh, H, mask, denom, h_past, dh_state)
-    a, ws = _layer_args(xq, xc, w_qc, w_ag, bias, coeff, mask, h_past, n_past, frames)
+    [dWqc | dWo | dbias | dcoeff], d_hpast (B, P) fp32 or None).  With ``rope_q`` or ``causal`` the transposed output
+    weight ``w_ag_t`` (P, D) is required; ``causal`` = the running sums ``pre`` of the forward call, whose carries
+    come in ``H``."""
+    dev = _require_cuda(dy, xq, xc, w_qc, w_ag, bias, coeff, hp, z, sh, H, mask, denom, h_past, dh_state, w_ag_t, causal)
+    a, ws = _layer_args(xq, xc, w_qc, w_ag, bias, coeff, mask, h_past, n_past, frames, rope_c, rope_q,
+                        causal is not None, token_offset)
+    a.w_ag_t = ptr(w_ag_t)
     B, T, N, D, P, K = a.B, a.T, a.N, a.D, a.P, a.K
     bf = dict(dtype=torch.bfloat16, device=dev)
     G = torch.empty((B * T * 2 * P if xc is None else (B * N + B * T) * P,), **bf)
@@ -434,7 +455,11 @@ def layer_bwd(dy, xq, xc, w_qc, w_ag, bias, coeff, hp, z, sh, H, *, mask=None, d
     dxc = None if xc is None else torch.empty((B, N, D), **bf)
     flat = torch.empty((2 * P * D + D * P + P + P * K,), dtype=torch.float32, device=dev)
     d_hpast = torch.empty((B, P), dtype=torch.float32, device=dev) if (want_d_hpast and h_past is not None) else None
-    a.hp, a.z, a.sh, a.H, a.denom = ptr(hp), ptr(z), ptr(sh), ptr(H), ptr(denom)
+    a.hp, a.z, a.sh, a.denom = ptr(hp), ptr(z), ptr(sh), ptr(denom)
+    if causal is not None:
+        a.pre, a.carry = ptr(causal), ptr(H)
+    else:
+        a.H = ptr(H)
     a.dy, a.dh_state, a.G, a.dxq, a.dxc = ptr(dy), ptr(dh_state), ptr(G), ptr(dxq), ptr(dxc)
     a.grads, a.d_hpast = ptr(flat), ptr(d_hpast)
     _abi.check(_abi.lib().pom_layer_bwd(C.byref(a), ptr(_abi.status_word(dev)), _abi.stream_ptr()), "pom_layer_bwd")

@@ -96,6 +96,34 @@ def test_fused_causal_cross_mixing():
         assert_close(grads[k], w, BF16_TOL, f"d_{k}")
 
 
+@pytest.mark.parametrize("case", [
+    # B, N, D, K, E, rope, side, mask
+    (2, 320, 128, 3, 2, None, None, "causal"),
+    (1, 1024, 64, 2, 2, "2d", 32, "causal"),
+    (3, 200, 96, 2, 2, "1d", None, "causal"),
+    (1, 1024, 64, 2, 2, "2d", 32, None),
+    (3, 200, 96, 2, 2, "1d", None, None),
+], ids=["causal_plain", "causal_rope2d", "causal_rope1d", "rope2d", "rope1d"])
+def test_whole_layer_calls_equal_the_phase_calls(case, monkeypatch):
+    """A layer without token sharding runs as two library calls (pom_layer_fwd / pom_layer_bwd); with sharding the
+    host calls the phases one by one and puts the exchanges between them.  Both sequence the same kernels on the same
+    buffers, so outputs and every gradient agree bit for bit — with rotary embedding, the token-causal mask, or both."""
+    from pom_b200 import functional
+
+    B, N, D, K, E, rope, side, mask = case
+    cfg, params, x, gy, kw = _case(B, N, D, K, E, seed=64, rope=rope, side=side)
+    kw["mask"] = mask
+    mod = make_cuda_module(cfg, params, torch.bfloat16)
+    assert functional.WHOLE_LAYER_CALLS
+    y1, g1 = cuda_run(mod, x, None, kw, gy, torch.bfloat16)
+    monkeypatch.setattr(functional, "WHOLE_LAYER_CALLS", False)
+    y2, g2 = cuda_run(mod, x, None, kw, gy, torch.bfloat16)
+    assert_status_clean()
+    assert torch.equal(y1, y2)
+    for k in g1:
+        assert torch.equal(g1[k], g2[k]), k
+
+
 @pytest.mark.parametrize("reverse", [False, True])
 @pytest.mark.parametrize("shape", [(1, 1, 32), (2, 33, 100), (1, 2048, 2304), (3, 70, 8)])
 def test_group_scan_matches_cumsum(shape, reverse):
