@@ -12,8 +12,10 @@
 // (RopeEpi::step, checked on the host), so
 //     angle(lane, j) = angle(group base, j) + lane * step * freq_j
 // and the epilogue combines, per pair,
-//     the table row of the group's base position (staged per tile: 4 groups x BN/2 channels), and
-//     rows 0..31 of the same table (cos/sin of lane * freq_j; one 32 x 16 block per sub-unit, bulk-loaded)
+//     the table row of the group's base position (staged one tile ahead by the stager warp: 4 groups x BN/2
+//     channels), and
+//     rows 0..31 of the same table (cos/sin of lane * freq_j; one 32 x 16 block per sub-unit, bulk-loaded once per
+//     column block)
 // with the angle-addition formulas: 4 multiply-adds instead of two table reads per element.
 #pragma once
 #include "epilogues.cuh"

@@ -165,7 +165,6 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       mbar_init(&tempty_bar[a], 2 * kEpiWarps);
     }
     for (int w = 0; w < kEpiWarps; ++w) mbar_init(&sm.wload_bar[w], 1);
-    mbar_init(sm.eshared_bar, 1);
     for (int a = 0; a < 2; ++a) {
       mbar_init(&sm.sfull_bar[a], 1);
       mbar_init(&sm.sempty_bar[a], kEpiWarps);
@@ -309,8 +308,6 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     io.buf1 = io.buf0 + Epi::kStageBytes / 2;
     io.bar = &sm.wload_bar[warp - 2];
     io.load_phase = 0;
-    io.shared_bar = sm.eshared_bar;
-    io.shared_phase = 0;
     io.abort_flag = abort_flag;
     io.status = status;
     io.tail_count = sm.tail_count;

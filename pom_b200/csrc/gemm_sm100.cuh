@@ -178,8 +178,6 @@ struct EpiIO {
   uint8_t* buf1;
   uint64_t* bar;
   uint32_t load_phase;  // parity of the next bulk load to complete on `bar`
-  uint64_t* shared_bar;  // one barrier for loads that all epilogue warps consume (rotary lane tables)
-  uint32_t shared_phase;
   volatile int* abort_flag;
   int* status;
   int* tail_count;  // [2] per tile parity: epilogue warps that have finished their share of a tile (stager epilogues)
@@ -228,7 +226,6 @@ struct SmemPlan {
   uint64_t* tfull_bar;   // [2]       MMA -> epilogue
   uint64_t* tempty_bar;  // [2]       epilogue -> MMA
   uint64_t* wload_bar;   // [8]       per epilogue warp: bulk loads into its staging block
-  uint64_t* eshared_bar; // [1]       bulk loads that all epilogue warps consume
   uint64_t* sfull_bar;   // [2]       stager -> epilogue: the constants of a tile are in their slot
   uint64_t* sempty_bar;  // [2]       epilogue -> stager: every epilogue warp has finished with the slot
   uint32_t* tmem_holder;
@@ -245,13 +242,12 @@ struct SmemPlan {
     tfull_bar = bars + 2 * STAGES;
     tempty_bar = bars + 2 * STAGES + 2;
     wload_bar = bars + 2 * STAGES + 4;
-    eshared_bar = bars + 2 * STAGES + 4 + kEpiWarps;
-    sfull_bar = bars + 2 * STAGES + 5 + kEpiWarps;
-    sempty_bar = bars + 2 * STAGES + 7 + kEpiWarps;
-    tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 9 + kEpiWarps);
+    sfull_bar = bars + 2 * STAGES + 4 + kEpiWarps;
+    sempty_bar = bars + 2 * STAGES + 6 + kEpiWarps;
+    tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 8 + kEpiWarps);
     abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
     tail_count = reinterpret_cast<int*>(tmem_holder + 2);
-    static_assert((2 * STAGES + 11 + kEpiWarps) * 8 <= kBarrierBytes, "barrier area too small");
+    static_assert((2 * STAGES + 10 + kEpiWarps) * 8 <= kBarrierBytes, "barrier area too small");
     epi_scratch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + kBarrierBytes);
   }
   static constexpr int bytes(int stage_bytes, int epi_smem, int epi_stage_bytes = kEpiStageBytes) {
@@ -357,7 +353,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       mbar_init(&tempty_bar[a], kEpiWarps);
     }
     for (int w = 0; w < kEpiWarps; ++w) mbar_init(&sm.wload_bar[w], 1);
-    mbar_init(sm.eshared_bar, 1);
     for (int a = 0; a < 2; ++a) {
       mbar_init(&sm.sfull_bar[a], 1);
       mbar_init(&sm.sempty_bar[a], kEpiWarps);
@@ -488,8 +483,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     io.buf1 = io.buf0 + Epi::kStageBytes / 2;
     io.bar = &sm.wload_bar[warp - 2];
     io.load_phase = 0;
-    io.shared_bar = sm.eshared_bar;
-    io.shared_phase = 0;
     io.abort_flag = abort_flag;
     io.status = status;
     io.tail_count = sm.tail_count;
