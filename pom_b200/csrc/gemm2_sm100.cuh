@@ -184,6 +184,9 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   cluster_sync_all();  // both CTAs' barriers exist before any remote arrive or remote load completion
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  // everything above overlapped the tail of the previous kernel of the stream; its results are read from here on
+  griddep_wait();
+  griddep_launch();
 
   const int pairs_per_batch = (geom.m_tiles_per_batch + 1) >> 1;
   const int total_units = geom.batches * pairs_per_batch * geom.n_tiles * geom.split_k;

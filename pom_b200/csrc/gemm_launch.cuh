@@ -223,6 +223,28 @@ inline int stationary_rows(long long units, int n_tiles, int slots) {
   return (slots - rows * n_tiles) * 16 <= slots ? rows : 0;
 }
 
+// Launch with programmatic stream serialization: the kernel may become resident while its predecessor drains; it
+// calls griddepcontrol.wait before it reads anything the predecessor wrote.
+template <class Kern, class... Args>
+int launch_overlapped(Kern kern, int grid, int smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = static_cast<size_t>(smem);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kern, args...) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return POM_ERR_CUDA;
+  }
+  count_launch();
+  return check_launch();
+}
+
 // One CTA per 128 x BN tile.
 template <int BN, int STAGES, bool A_MN, bool B_MN, class Epi>
 int launch(const Operands& o, int split_k, const EpiMaps& maps, const typename Epi::Params& ep, int* status,
@@ -242,9 +264,7 @@ int launch(const Operands& o, int split_k, const EpiMaps& maps, const typename E
     const int rows = g.split_k == 1 ? stationary_rows(units, g.n_tiles, sm_count()) : 0;
     if (rows) grid = rows * g.n_tiles, g.group_m = rows;
   }
-  kern<<<grid, kGemmThreads, smem, st>>>(tmA, tmB, maps, g, ep, status);
-  count_launch();
-  return check_launch();
+  return launch_overlapped(kern, grid, smem, st, tmA, tmB, maps, g, ep, status);
 }
 
 // Two CTAs (one cluster) per 256 x BN tile; each CTA loads BN/2 rows of the B tile.
@@ -266,9 +286,7 @@ int launch_pair(const Operands& o, int split_k, const EpiMaps& maps, const typen
     const int rows = g.split_k == 1 ? stationary_rows(units, g.n_tiles, sm_count() / 2) : 0;
     if (rows) clusters = rows * g.n_tiles, g.group_m = 2 * rows;  // group_m counts m-tiles: two per pair
   }
-  kern<<<2 * clusters, kGemmThreads, smem, st>>>(tmA, tmB, maps, g, ep, status);
-  count_launch();
-  return check_launch();
+  return launch_overlapped(kern, 2 * clusters, smem, st, tmA, tmB, maps, g, ep, status);
 }
 
 struct TilePlan {

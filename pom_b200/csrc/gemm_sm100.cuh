@@ -371,6 +371,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  // everything above overlapped the tail of the previous kernel of the stream; its results are read from here on
+  griddep_wait();
+  griddep_launch();
 
   const int total_units = geom.batches * geom.m_tiles_per_batch * geom.n_tiles * geom.split_k;
 

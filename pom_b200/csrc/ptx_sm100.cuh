@@ -93,6 +93,13 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may become
+// resident while its predecessor in the stream is still draining; griddep_wait() returns once that predecessor has
+// completed and its writes are visible, so everything before it (barrier set-up, tensor-memory allocation,
+// descriptor prefetch) overlaps the predecessor's tail.  griddep_launch() lets this kernel's own successor in.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
