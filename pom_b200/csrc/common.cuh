@@ -33,6 +33,24 @@ inline int sm_count() {
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
+// Launch with programmatic stream serialization: the kernel may become resident while its predecessor in the stream
+// drains.  Only for kernels that execute griddepcontrol.wait (pomk::griddep_wait) before they touch memory the
+// predecessor may have written.
+template <class Kern, class... Args>
+inline cudaError_t launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
 // Rotary forms of the fused tensor-core phases (pom_gemm_rope.cu), reached through pom_ctx_gemm,
 // pom_gate_gemm and pom_gate_bwd_gemm when their `rope` member names a rotary kind.
 int ctx_gemm_rope(const pom_ctx_args* a, int* status, cudaStream_t st);

@@ -227,17 +227,8 @@ inline int stationary_rows(long long units, int n_tiles, int slots) {
 // calls griddepcontrol.wait before it reads anything the predecessor wrote.
 template <class Kern, class... Args>
 int launch_overlapped(Kern kern, int grid, int smem, cudaStream_t st, Args... args) {
-  cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(static_cast<unsigned>(grid));
-  cfg.blockDim = dim3(kGemmThreads);
-  cfg.dynamicSmemBytes = static_cast<size_t>(smem);
-  cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, kern, args...) != cudaSuccess) {
+  if (launch_pdl(kern, dim3(static_cast<unsigned>(grid)), dim3(kGemmThreads), static_cast<size_t>(smem), st, args...) !=
+      cudaSuccess) {
     (void)cudaGetLastError();
     return POM_ERR_CUDA;
   }

@@ -67,6 +67,8 @@ constexpr int kSeg = 32;
 
 __global__ void __launch_bounds__(128) seg_sum_kernel(const float* __restrict__ sums, float* __restrict__ seg,
                                                       int groups, int segs, int P) {
+  griddep_wait();  // launched with programmatic stream serialization
+  griddep_launch();
   const int p = blockIdx.x * 128 + threadIdx.x, s = blockIdx.y, b = blockIdx.z;
   if (p >= P) return;
   const int g0 = s * kSeg, g1 = min(groups, g0 + kSeg);
@@ -82,6 +84,8 @@ __global__ void __launch_bounds__(128) seg_sum_kernel(const float* __restrict__ 
 // instead of one per element (the sums are formed in the same order either way).
 __global__ void __launch_bounds__(128) seg_scan_kernel(float* __restrict__ seg, const float* __restrict__ carry_in,
                                                        float* __restrict__ total_out, int segs, int P, int reverse) {
+  griddep_wait();  // launched with programmatic stream serialization
+  griddep_launch();
   const int p = blockIdx.x * 128 + threadIdx.x, b = blockIdx.y;
   if (p >= P) return;
   float* base = seg + static_cast<long long>(b) * segs * P + p;
@@ -110,6 +114,8 @@ __global__ void __launch_bounds__(128) seg_scan_kernel(float* __restrict__ seg, 
 
 __global__ void __launch_bounds__(128) seg_apply_kernel(float* __restrict__ sums, const float* __restrict__ seg,
                                                         int groups, int segs, int P, int reverse) {
+  griddep_wait();  // launched with programmatic stream serialization
+  griddep_launch();
   const int p = blockIdx.x * 128 + threadIdx.x, s = blockIdx.y, b = blockIdx.z;
   if (p >= P) return;
   const int g0 = s * kSeg, g1 = min(groups, g0 + kSeg);
@@ -232,9 +238,11 @@ int pom_group_scan(float* sums, const float* carry_in, float* total_out, float* 
   if (B > 65535 || segs > 65535) return POM_ERR_TOO_LARGE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const unsigned px = static_cast<unsigned>(ceil_div(P, 128));
-  seg_sum_kernel<<<dim3(px, segs, B), 128, 0, st>>>(sums, scratch, groups, segs, P);
-  seg_scan_kernel<<<dim3(px, B), 128, 0, st>>>(scratch, carry_in, total_out, segs, P, reverse);
-  seg_apply_kernel<<<dim3(px, segs, B), 128, 0, st>>>(sums, scratch, groups, segs, P, reverse);
+  (void)launch_pdl(seg_sum_kernel, dim3(px, segs, B), dim3(128), 0, st, static_cast<const float*>(sums), scratch, groups,
+                   segs, P);
+  (void)launch_pdl(seg_scan_kernel, dim3(px, B), dim3(128), 0, st, scratch, carry_in, total_out, segs, P, reverse);
+  (void)launch_pdl(seg_apply_kernel, dim3(px, segs, B), dim3(128), 0, st, sums, static_cast<const float*>(scratch), groups,
+                   segs, P, reverse);
   count_launch(3);
   return check_launch();
 }

@@ -306,6 +306,8 @@ __global__ void chunk_scan_kernel(float* partial, const float* carry, float* tot
 __global__ void __launch_bounds__(256) reduce_partials_kernel(const float* __restrict__ partial, float* __restrict__ out,
                                                                const float* __restrict__ denom, float scale, int chunks,
                                                                int P) {
+  pomk::griddep_wait();  // launched with programmatic stream serialization
+  pomk::griddep_launch();
   __shared__ float sm[8][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int p = blockIdx.x * 32 + tx;
@@ -578,6 +580,8 @@ agg_bwd_stream_kernel(const __grid_constant__ CUtensorMap tmx, const AggBwdDev a
     mbar_fence_init();
   }
   __syncthreads();
+  griddep_wait();  // launched with programmatic stream serialization: the set-up above overlapped the previous kernel
+  griddep_launch();
 
   __nv_bfloat16* dxb = static_cast<__nv_bfloat16*>(a.dx) + static_cast<long long>(b) * a.N * a.ld_dx + p0;
   // One tiled bulk load brings the whole 64-token x 256-channel tile (rows and channels past the end are
@@ -773,6 +777,8 @@ agg_bwd_stream_pair_kernel(const __grid_constant__ CUtensorMap tmx, const __grid
     mbar_fence_init();
   }
   __syncthreads();
+  griddep_wait();  // launched with programmatic stream serialization: the set-up above overlapped the previous kernel
+  griddep_launch();
 
   __nv_bfloat16* dxb = static_cast<__nv_bfloat16*>(a.dx) + static_cast<long long>(b) * a.N * a.ld_dx;
   // tiled bulk loads per tile: [TT tokens x 128 first channels], [TT x 128 partners] (and the same two boxes of suf)
@@ -1337,6 +1343,8 @@ __global__ void frame_prefix_kernel(const float* __restrict__ in, float* __restr
   }
 }
 __global__ void cast_f32_bf16_kernel(const float* __restrict__ s, __nv_bfloat16* __restrict__ d, long long count) {
+  pomk::griddep_wait();  // launched with programmatic stream serialization
+  pomk::griddep_launch();
   const long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
   if (i + 4 <= count && ((reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(d)) & 15) == 0) {
     const float4 f = __ldg(reinterpret_cast<const float4*>(s + i));
@@ -1456,7 +1464,7 @@ int pom_reduce_partials(const float* partial, float* out, const float* denom, fl
   if (B <= 0 || chunks <= 0 || P <= 0) return POM_ERR_BAD_SHAPE;
   if (B > 65535) return POM_ERR_TOO_LARGE;
   dim3 grid(static_cast<unsigned>(ceil_div(P, 32)), static_cast<unsigned>(B));
-  reduce_partials_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(partial, out, denom, scale, chunks,
+  (void)launch_pdl(reduce_partials_kernel, grid, dim3(256), 0, static_cast<cudaStream_t>(stream), partial, out, denom, scale, chunks,
                                                                              P);
   count_launch();
   return check_launch();
@@ -1590,7 +1598,7 @@ int pom_poly_agg_mean_noalloc(const pom_agg_args* a, const float* denom, float s
   count_launch();
   if ((rc = check_launch())) return rc;
   dim3 grid(static_cast<unsigned>(ceil_div(a->P, 32)), static_cast<unsigned>(a->B));
-  reduce_partials_kernel<<<grid, 256, 0, st>>>(ws, out, denom, scale, chunks, a->P);
+  (void)launch_pdl(reduce_partials_kernel, grid, dim3(256), 0, st, ws, out, denom, scale, chunks, a->P);
   count_launch();
   return check_launch();
 }
@@ -1666,11 +1674,11 @@ int pom_poly_agg_bwd(const pom_agg_bwd_args* a, void* stream) {
     CUtensorMap tmx;
     if ((rc = stream_tile_map(&tmx, a->x, a->P, a->N, a->B, a->ldx, kStCols, kStTok))) return rc;
     if (a->K <= 2)
-      agg_bwd_stream_kernel<2, kStVec, true><<<sgrid, threads + 32, kStSmemBytes, st>>>(tmx, d, sp.tiles_per_cta,
-                                                                                        sp.splits, status);
+      (void)launch_pdl(agg_bwd_stream_kernel<2, kStVec, true>, sgrid, dim3(threads + 32), kStSmemBytes, st, tmx, d,
+                       sp.tiles_per_cta, sp.splits, status);
     else
-      agg_bwd_stream_kernel<4, kStVec, false><<<sgrid, threads, kStSmemBytes, st>>>(tmx, d, sp.tiles_per_cta, sp.splits,
-                                                                                    status);
+      (void)launch_pdl(agg_bwd_stream_kernel<4, kStVec, false>, sgrid, dim3(threads), kStSmemBytes, st, tmx, d,
+                       sp.tiles_per_cta, sp.splits, status);
     count_launch();
     return check_launch();
   }
@@ -1696,14 +1704,14 @@ int pom_poly_agg_bwd(const pom_agg_bwd_args* a, void* stream) {
     tms = tmx;
     if (fused_causal && (rc = stream_tile_map(&tms, a->dout, a->P, a->N, a->B, a->ld_dout, kStHalf, tt))) return rc;
     if (!fused_causal)
-      agg_bwd_stream_pair_kernel<2, false><<<sgrid, 256, kStSmemBytes, st>>>(tmx, tms, d, sp.tiles_per_cta, sp.splits,
-                                                                            pr.q, bps, status);
+      (void)launch_pdl(agg_bwd_stream_pair_kernel<2, false>, sgrid, dim3(256), kStSmemBytes, st, tmx, tms, d,
+                       sp.tiles_per_cta, sp.splits, pr.q, bps, status);
     else if (a->K <= 2)
-      agg_bwd_stream_pair_kernel<2, true><<<sgrid, 256, kStSmemBytes, st>>>(tmx, tms, d, sp.tiles_per_cta, sp.splits,
-                                                                           pr.q, bps, status);
+      (void)launch_pdl(agg_bwd_stream_pair_kernel<2, true>, sgrid, dim3(256), kStSmemBytes, st, tmx, tms, d,
+                       sp.tiles_per_cta, sp.splits, pr.q, bps, status);
     else
-      agg_bwd_stream_pair_kernel<4, true><<<sgrid, 256, kStSmemBytes, st>>>(tmx, tms, d, sp.tiles_per_cta, sp.splits,
-                                                                           pr.q, bps, status);
+      (void)launch_pdl(agg_bwd_stream_pair_kernel<4, true>, sgrid, dim3(256), kStSmemBytes, st, tmx, tms, d,
+                       sp.tiles_per_cta, sp.splits, pr.q, bps, status);
     count_launch();
     return check_launch();
   }
@@ -1929,8 +1937,8 @@ int pom_fill_zero(void* dst, int64_t bytes, void* stream) {
 int pom_cast_f32_to_bf16(const float* src, void* dst, int64_t count, void* stream) {
   if (!src || !dst) return POM_ERR_NULL;
   if (count <= 0) return POM_ERR_BAD_SHAPE;
-  cast_f32_bf16_kernel<<<static_cast<unsigned>(ceil_div(ceil_div(count, 4), 256)), 256, 0,
-                         static_cast<cudaStream_t>(stream)>>>(src, static_cast<__nv_bfloat16*>(dst), count);
+  (void)launch_pdl(cast_f32_bf16_kernel, dim3(static_cast<unsigned>(ceil_div(ceil_div(count, 4), 256))), dim3(256), 0,
+                   static_cast<cudaStream_t>(stream), src, static_cast<__nv_bfloat16*>(dst), count);
   count_launch();
   return check_launch();
 }
