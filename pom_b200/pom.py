@@ -30,7 +30,7 @@ class PoM(nn.Module):
                      assembled per call (a copy; no arithmetic).
         n_sel_heads: 0 or 1: one gate value per channel; > 1: one gate value per head, shared by the
                      dim*expand / n_sel_heads channels of that head (bf16 needs a multiple of 8 heads).
-        bias:        add a bias to the output projection.
+        bias:        add a bias to the output projection (and, with n_groups > 1, to the grouped projection).
     """
 
     def __init__(self, dim: int, degree: int, expand: int, n_groups: int = 1, n_sel_heads: int = 1, bias: bool = False):
@@ -48,9 +48,7 @@ class PoM(nn.Module):
         self._se_dim = n_sel_heads if n_sel_heads > 1 else expand * dim
         # creation order matters for seeded initialisation: (qc_proj, se_bias | po_proj, se_proj), po_coeff, ag_proj
         if n_groups > 1:
-            if bias:
-                raise NotImplementedError("a bias on the grouped polynomial projection is not implemented by the CUDA path")
-            self.po_proj = nn.Conv1d(dim, expand * dim, kernel_size=1, bias=False, groups=n_groups)
+            self.po_proj = nn.Conv1d(dim, expand * dim, kernel_size=1, bias=bias, groups=n_groups)
             self.se_proj = nn.Linear(dim, self._se_dim, bias=True)
         else:
             self.qc_proj = nn.Linear(dim, self._po_dim + self._se_dim, bias=False)
@@ -70,28 +68,65 @@ class PoM(nn.Module):
                          n_sel_heads=self.n_sel_heads, frames=frames)
         return spec, (mask if kind in ("keypad", "full") else None)
 
+    # A bias of the grouped projection (reference pom/pom.py:182, nn.Conv1d(..., bias=bias)) travels as one more
+    # input column: the tokens get _BIAS_COLS extra channels (1, 0, ..., 0) and the projection weight as many extra
+    # columns, the first of which holds the bias for the polynomial rows and 0 for the gate rows.  Eight columns
+    # keep the rows of both operands 16-byte aligned in bf16.
+    _BIAS_COLS = 8
+
+    def _tokens(self, x: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        """The tokens as the projection reads them: unchanged, or with the bias channels appended."""
+        if x is None or not self._has_bias_cols():
+            return x
+        one = x.new_zeros(self._BIAS_COLS)
+        one[0] = 1
+        return torch.cat([x, one.expand(*x.shape[:-1], self._BIAS_COLS)], dim=-1)
+
     def _weights(self) -> Tuple[torch.Tensor, torch.Tensor]:
         """(P + S, D) projection weight and (S,) gate bias.  Grouped: the (P, D/g, 1) convolution weight is laid
         out as its block-diagonal (P, D) matrix (reference pom/pom.py:180-183, 203-205); gradients flow back
-        through the copy to the blocks."""
+        through the copy to the blocks.  With a bias on the grouped projection the matrix is (P + S, D + 8)
+        (see ``_tokens``)."""
         if self.n_groups == 1:
             return self.qc_proj.weight, self.se_bias
-        wp, ws = self.po_proj.weight, self.se_proj.weight
+        wp, ws, bp = self.po_proj.weight, self.se_proj.weight, self.po_proj.bias
         # Without autograd the assembled matrix is kept per parameter version (in-place updates and .data swaps
         # change the key); with autograd it is rebuilt per call, which is once per version in a training loop.
-        track = torch.is_grad_enabled() and (wp.requires_grad or ws.requires_grad)
-        key = (wp._version, ws._version, wp.data_ptr(), ws.data_ptr(), wp.dtype, wp.device)
+        track = torch.is_grad_enabled() and (wp.requires_grad or ws.requires_grad
+                                              or (bp is not None and bp.requires_grad))
+        key = (wp._version, ws._version, wp.data_ptr(), ws.data_ptr(), wp.dtype, wp.device,
+               None if bp is None else (bp._version, bp.data_ptr()))
         if not track and self._grouped_cache is not None and self._grouped_cache[0] == key:
             return self._grouped_cache[1], self.se_proj.bias
         g = self.n_groups
         w = wp.squeeze(-1)
         dense = torch.block_diag(*w.view(g, self._po_dim // g, self.dim // g).unbind(0))
         w_qc = torch.cat([dense, ws], dim=0)
+        if bp is not None:
+            extra = w_qc.new_zeros(w_qc.shape[0], self._BIAS_COLS - 1)
+            first = torch.cat([bp.to(w_qc.dtype), w_qc.new_zeros(ws.shape[0])])
+            w_qc = torch.cat([w_qc, first[:, None], extra], dim=1)
         if not track:
             self._grouped_cache = (key, w_qc)
         return w_qc, self.se_proj.bias
 
+    def _has_bias_cols(self) -> bool:
+        return self.n_groups > 1 and self.po_proj.bias is not None
+
+    def _out_weight(self) -> torch.Tensor:
+        """(D, P) output projection; with the bias channels, as many zero rows below it, so that the layer keeps
+        one width on both sides (the extra outputs are 0 and ``_finish`` drops them)."""
+        w = self.ag_proj.weight
+        return torch.cat([w, w.new_zeros(self._BIAS_COLS, w.shape[1])], dim=0) if self._has_bias_cols() else w
+
+    def _residual(self, r: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        if r is None or not self._has_bias_cols():
+            return r
+        return torch.cat([r, r.new_zeros(*r.shape[:-1], self._BIAS_COLS)], dim=-1)
+
     def _finish(self, y: torch.Tensor) -> torch.Tensor:
+        if self._has_bias_cols():
+            y = y[..., :self.dim]
         return y if self.ag_proj.bias is None else y + self.ag_proj.bias
 
     # ------------------------------------------------------------------ API
@@ -104,7 +139,9 @@ class PoM(nn.Module):
         """
         spec, m = self._spec(xq, xc, mask, shard)
         w_qc, se_bias = self._weights()
-        y, _ = pom_layer(xq, xc, w_qc, se_bias, self.po_coeff, self.ag_proj.weight, m, None, spec, residual)
+        xq, xc = self._tokens(xq), (None if spec.self_mixing else self._tokens(xc))
+        y, _ = pom_layer(xq, xc, w_qc, se_bias, self.po_coeff, self._out_weight(), m, None, spec,
+                         self._residual(residual))
         return self._finish(y)
 
     def state_forward(self, xq: torch.Tensor, xc: Optional[torch.Tensor] = None,
@@ -131,7 +168,9 @@ class PoM(nn.Module):
         else:
             h_past = None
         w_qc, se_bias = self._weights()
-        y, h = pom_layer(xq, xc, w_qc, se_bias, self.po_coeff, self.ag_proj.weight, None, h_past, spec, residual)
+        xq, xc = self._tokens(xq), (None if spec.self_mixing else self._tokens(xc))
+        y, h = pom_layer(xq, xc, w_qc, se_bias, self.po_coeff, self._out_weight(), None, h_past, spec,
+                         self._residual(residual))
         return self._finish(y), {"h": h, "n": n_past + 1}
 
     @torch.no_grad()
@@ -142,6 +181,7 @@ class PoM(nn.Module):
         chunks use :meth:`state_forward`."""
         if not xq.is_cuda:
             raise RuntimeError("pom_b200 has no CPU path: move the module and its inputs to a CUDA device")
+        xq = self._tokens(xq)
         B, T, D = xq.shape
         P, S = self._po_dim, self._se_dim
         w_qc, se_bias = self._weights()
@@ -153,7 +193,7 @@ class PoM(nn.Module):
             sh = ops.select_heads_fwd(s32, hp, xq.dtype)
         else:
             sh = ops.select_fwd(z, bias32, hp)
-        y = ops.gemm(sh.view(B * T, P), self.ag_proj.weight).view(B, T, D)
+        y = ops.gemm(sh.view(B * T, P), self.ag_proj.weight).view(B, T, self.dim)
         return self._finish(y), {"max_len": state["max_len"], "h": hp, "n": state["n"] + T}
 
     def reset(self, state: Dict[str, Any]) -> Dict[str, Any]:

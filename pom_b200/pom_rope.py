@@ -143,6 +143,7 @@ class PoMRoPE(PoM):
         spec = LayerSpec(degree=self.order, mask_kind=kind, self_mixing=self_mixing, rope_ctx=rope_c, rope_qry=rope_q,
                          shard=shard, n_sel_heads=self.n_sel_heads)
         w_qc, se_bias = self._weights()
-        y, _ = pom_layer(xq, xc, w_qc, se_bias, self.po_coeff, self.ag_proj.weight,
+        xq, xc = self._tokens(xq), (None if self_mixing else self._tokens(xc))
+        y, _ = pom_layer(xq, xc, w_qc, se_bias, self.po_coeff, self._out_weight(),
                          mask if kind in ("keypad", "full") else None, None, spec)
         return self._finish(y)

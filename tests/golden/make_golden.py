@@ -109,6 +109,16 @@ def main(ref_root: str) -> None:
     record("pom_groups2_cross_mask2d", mg, lambda: dict(mask=m2c), xq_cross, xc=x, cfg=cfg_g)
     mgh = make_grouped(PoM, heads=4)
     record("pom_groups2_heads4_none", mgh, lambda: dict(mask=None), x, cfg=dict(cfg_g, heads=4))
+    # bias=True: the grouped convolution and the output projection both carry a bias (pom/pom.py:182, 191)
+    mgb = make_grouped(PoM, seed=5, bias=True)
+    with torch.no_grad():
+        torch.manual_seed(205)
+        mgb.po_proj.bias.copy_(torch.randn_like(mgb.po_proj.bias) * 0.3)
+        mgb.ag_proj.bias.copy_(torch.randn_like(mgb.ag_proj.bias) * 0.3)
+    cfg_gb = dict(cfg_g, bias=True)
+    record("pom_groups2_bias_none", mgb, lambda: dict(mask=None), x, cfg=cfg_gb)
+    record("pom_groups2_bias_causal", mgb, lambda: dict(mask="causal"), x, cfg=cfg_gb)
+    record("pom_groups2_bias_cross", mgb, lambda: dict(mask=None), xq_cross, xc=x, cfg=cfg_gb)
 
     # ar_forward as the reference defines it (no aggregation: the gate multiplies the raw projection)
     with torch.no_grad():

@@ -13,7 +13,8 @@ GROUPED_PARAM_ORDER = ["po_proj.weight", "se_proj.weight", "se_proj.bias", "po_c
 
 def param_order(params):
     """Trainable-parameter names of a case: the fused layout, or the grouped one when po_proj is present."""
-    return GROUPED_PARAM_ORDER if "po_proj.weight" in params else PARAM_ORDER
+    order = GROUPED_PARAM_ORDER if "po_proj.weight" in params else PARAM_ORDER
+    return order + [k for k in ("po_proj.bias", "ag_proj.bias") if k in params]
 
 
 def rope_cfg(cfg):
@@ -31,10 +32,11 @@ def make_cuda_module(cfg, params, dtype, device="cuda"):
     r = cfg.get("rope")
     groups = cfg.get("groups", 1)
     if r is None:
-        mod = PoM(cfg["dim"], cfg["degree"], cfg["expand"], groups, cfg["heads"])
+        mod = PoM(cfg["dim"], cfg["degree"], cfg["expand"], groups, cfg["heads"], bias=cfg.get("bias", False))
     else:
         mod = PoMRoPE(cfg["dim"], cfg["degree"], cfg["expand"], groups, cfg["heads"], rope_2d=r["two_d"],
-                      max_seq_len=r.get("max_seq_len", 4096), max_h=r.get("max_h", 64), max_w=r.get("max_w", 64))
+                      max_seq_len=r.get("max_seq_len", 4096), max_h=r.get("max_h", 64), max_w=r.get("max_w", 64),
+                      bias=cfg.get("bias", False))
     with torch.no_grad():
         named = dict(mod.named_parameters())
         for k in param_order(params):

@@ -15,7 +15,8 @@ LAYER_CASES = ["pom_none", "pom_causal", "pom_mask2d", "pom_mask3d", "pom_cross"
 
 
 HEAD_CASES = ["pom_heads4_none", "pom_heads4_causal", "rope2d_heads4_none", "rope1d_heads4_causal"]
-GROUP_CASES = ["pom_groups2_none", "pom_groups2_causal", "pom_groups2_cross_mask2d", "pom_groups2_heads4_none"]
+GROUP_CASES = ["pom_groups2_none", "pom_groups2_causal", "pom_groups2_cross_mask2d", "pom_groups2_heads4_none",
+               "pom_groups2_bias_none", "pom_groups2_bias_causal", "pom_groups2_bias_cross"]
 
 
 @pytest.mark.parametrize("name", LAYER_CASES + HEAD_CASES + GROUP_CASES)
@@ -54,7 +55,8 @@ def test_ar_forward_matches_reference_vectors(golden, name, dtype):
     assert_close(st["h"], want_h, tol, f"{name} state h")
 
 
-@pytest.mark.parametrize("name", LAYER_CASES + ["pom_groups2_none", "pom_groups2_causal"])
+@pytest.mark.parametrize("name", LAYER_CASES + ["pom_groups2_none", "pom_groups2_causal", "pom_groups2_bias_none",
+                                                "pom_groups2_bias_causal", "pom_groups2_bias_cross"])
 def test_bf16_layer_matches_oracle_on_rounded_inputs(golden, name):
     case = golden[name]
     cfg = case["cfg"]

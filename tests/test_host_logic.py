@@ -75,12 +75,13 @@ def _module_for(cfg):
     r = cfg.get("rope")
     args = (cfg["dim"], cfg["degree"], cfg["expand"], cfg.get("groups", 1), cfg["heads"])
     if r is None:
-        return PoM(*args)
-    return PoMRoPE(*args, rope_2d=r["two_d"], max_seq_len=r.get("max_seq_len", 4096), max_h=r.get("max_h", 64),
+        return PoM(*args, bias=cfg.get("bias", False))
+    return PoMRoPE(*args, bias=cfg.get("bias", False), rope_2d=r["two_d"], max_seq_len=r.get("max_seq_len", 4096), max_h=r.get("max_h", 64),
                    max_w=r.get("max_w", 64))
 
 
 @pytest.mark.parametrize("name", ["pom_none", "pom_heads4_none", "pom_groups2_none", "pom_groups2_heads4_none",
+                                  "pom_groups2_bias_none",
                                   "rope1d_none", "rope2d_none", "rope2d_heads4_none"])
 def test_reference_state_dicts_load_strictly_and_round_trip(golden, name):
     """Checkpoints interchange with the reference: same parameter and buffer names and shapes, and the rotary

@@ -13,7 +13,7 @@ def _oracle_from_case(case, requires_grad=True):
     params = {}
     for k, v in case["params"].items():
         if k in ("qc_proj.weight", "se_bias", "po_coeff", "ag_proj.weight", "po_proj.weight", "se_proj.weight",
-                 "se_proj.bias"):
+                 "se_proj.bias", "po_proj.bias", "ag_proj.bias"):
             params[k] = v.clone().requires_grad_(requires_grad)
     rope = None
     if "rope" in cfg:
@@ -29,6 +29,7 @@ MODULE_CASES = [
     "rope1d_none", "rope1d_causal", "rope1d_mask2d", "rope1d_positions", "rope1d_cross",
     "rope2d_none", "rope2d_causal", "rope2d_heads4_none", "rope1d_heads4_causal",
     "pom_groups2_none", "pom_groups2_causal", "pom_groups2_cross_mask2d", "pom_groups2_heads4_none",
+    "pom_groups2_bias_none", "pom_groups2_bias_causal", "pom_groups2_bias_cross",
 ]
 
 
@@ -45,6 +46,7 @@ def test_layer_matches_reference_vectors(golden, name):
     order = ["se_bias", "po_coeff", "qc_proj.weight", "ag_proj.weight"]
     if "po_proj.weight" in params:
         order = ["po_proj.weight", "se_proj.weight", "se_proj.bias", "po_coeff", "ag_proj.weight"]
+    order += [k for k in ("po_proj.bias", "ag_proj.bias") if k in params]
     grads = torch.autograd.grad(y, ins + [params[k] for k in order], case["gy"])
     want = [case["grads"][f"d_in{i}"] for i in range(len(ins))] + [case["grads"]["d_" + k] for k in order]
     for g, w, label in zip(grads, want, [f"in{i}" for i in range(len(ins))] + order):
