@@ -8,6 +8,7 @@ checkpoints interchange.
 """
 from __future__ import annotations
 
+import math
 from typing import Any, Dict, Optional, Tuple
 
 import torch
@@ -29,7 +30,7 @@ class PoM(nn.Module):
                      runs the grouped projection as one dense tensor-core GEMM on the block-diagonal weight
                      assembled per call (a copy; no arithmetic).
         n_sel_heads: 0 or 1: one gate value per channel; > 1: one gate value per head, shared by the
-                     dim*expand / n_sel_heads channels of that head (bf16 needs a multiple of 8 heads).
+                     dim*expand / n_sel_heads channels of that head.
         bias:        add a bias to the output projection (and, with n_groups > 1, to the grouped projection).
     """
 
@@ -65,7 +66,7 @@ class PoM(nn.Module):
                 raise ValueError(f"sequence length {xq.shape[1]} is not a multiple of frame_len {mask.frame_len}")
             kind, frames = "none", xq.shape[1] // mask.frame_len
         spec = LayerSpec(degree=self.order, mask_kind=kind, self_mixing=(xc is None or xc is xq), shard=shard,
-                         n_sel_heads=self.n_sel_heads, frames=frames)
+                         n_sel_heads=self._heads(), frames=frames)
         return spec, (mask if kind in ("keypad", "full") else None)
 
     # A bias of the grouped projection (reference pom/pom.py:182, nn.Conv1d(..., bias=bias)) travels as one more
@@ -82,33 +83,62 @@ class PoM(nn.Module):
         one[0] = 1
         return torch.cat([x, one.expand(*x.shape[:-1], self._BIAS_COLS)], dim=-1)
 
+    def _head_copies(self) -> int:
+        """How many adjacent copies of every gate head the CUDA path works with.  A bf16 gate projection needs
+        rows of 16 bytes, that is a multiple of 8 heads; other head counts are brought there by repeating each row
+        of the gate weight (and bias, and rotary column) r times: r * heads heads of head_dim / r channels gate
+        exactly as heads heads of head_dim channels, and autograd sums the copies' gradients."""
+        h = self.n_sel_heads
+        ws = self.qc_proj.weight if self.n_groups == 1 else self.se_proj.weight
+        if h <= 1 or ws.dtype != torch.bfloat16 or h % 8 == 0:
+            return 1
+        r = 8 // math.gcd(h, 8)
+        if self._po_dim % (h * r):
+            raise NotImplementedError("bf16 multi-head gating needs dim * expand to be a multiple of 8")
+        return r
+
+    def _heads(self) -> int:
+        """Gate heads as the CUDA path sees them (see ``_head_copies``)."""
+        return self.n_sel_heads * self._head_copies() if self.n_sel_heads > 1 else self.n_sel_heads
+
     def _weights(self) -> Tuple[torch.Tensor, torch.Tensor]:
         """(P + S, D) projection weight and (S,) gate bias.  Grouped: the (P, D/g, 1) convolution weight is laid
         out as its block-diagonal (P, D) matrix (reference pom/pom.py:180-183, 203-205); gradients flow back
         through the copy to the blocks.  With a bias on the grouped projection the matrix is (P + S, D + 8)
-        (see ``_tokens``)."""
-        if self.n_groups == 1:
+        (see ``_tokens``); with repeated gate heads S = r * heads (see ``_head_copies``)."""
+        r = self._head_copies()
+        if self.n_groups == 1 and r == 1:
             return self.qc_proj.weight, self.se_bias
-        wp, ws, bp = self.po_proj.weight, self.se_proj.weight, self.po_proj.bias
-        # Without autograd the assembled matrix is kept per parameter version (in-place updates and .data swaps
-        # change the key); with autograd it is rebuilt per call, which is once per version in a training loop.
-        track = torch.is_grad_enabled() and (wp.requires_grad or ws.requires_grad
-                                              or (bp is not None and bp.requires_grad))
-        key = (wp._version, ws._version, wp.data_ptr(), ws.data_ptr(), wp.dtype, wp.device,
-               None if bp is None else (bp._version, bp.data_ptr()))
+        P = self._po_dim
+        if self.n_groups == 1:
+            src = (self.qc_proj.weight, self.se_bias)
+        else:
+            src = tuple(t for t in (self.po_proj.weight, self.se_proj.weight, self.se_proj.bias, self.po_proj.bias)
+                        if t is not None)
+        # Without autograd the assembled tensors are kept per parameter version (in-place updates and .data swaps
+        # change the key); with autograd they are rebuilt per call, which is once per version in a training loop.
+        track = torch.is_grad_enabled() and any(t.requires_grad for t in src)
+        key = tuple((t._version, t.data_ptr(), t.dtype, t.device) for t in src) + (r,)
         if not track and self._grouped_cache is not None and self._grouped_cache[0] == key:
-            return self._grouped_cache[1], self.se_proj.bias
-        g = self.n_groups
-        w = wp.squeeze(-1)
-        dense = torch.block_diag(*w.view(g, self._po_dim // g, self.dim // g).unbind(0))
-        w_qc = torch.cat([dense, ws], dim=0)
+            return self._grouped_cache[1]
+        if self.n_groups == 1:
+            w_po, ws, bias = self.qc_proj.weight[:P], self.qc_proj.weight[P:], self.se_bias
+        else:
+            g = self.n_groups
+            w = self.po_proj.weight.squeeze(-1)
+            w_po = torch.block_diag(*w.view(g, P // g, self.dim // g).unbind(0))
+            ws, bias = self.se_proj.weight, self.se_proj.bias
+        if r > 1:
+            ws, bias = ws.repeat_interleave(r, dim=0), bias.repeat_interleave(r)
+        w_qc = torch.cat([w_po, ws], dim=0)
+        bp = None if self.n_groups == 1 else self.po_proj.bias
         if bp is not None:
             extra = w_qc.new_zeros(w_qc.shape[0], self._BIAS_COLS - 1)
             first = torch.cat([bp.to(w_qc.dtype), w_qc.new_zeros(ws.shape[0])])
             w_qc = torch.cat([w_qc, first[:, None], extra], dim=1)
         if not track:
-            self._grouped_cache = (key, w_qc)
-        return w_qc, self.se_proj.bias
+            self._grouped_cache = (key, (w_qc, bias))
+        return w_qc, bias
 
     def _has_bias_cols(self) -> bool:
         return self.n_groups > 1 and self.po_proj.bias is not None
@@ -154,7 +184,7 @@ class PoM(nn.Module):
         to the output inside the output projection's epilogue.
         """
         spec = LayerSpec(degree=self.order, self_mixing=(xc is None or xc is xq), want_state=True,
-                         n_sel_heads=self.n_sel_heads)
+                         n_sel_heads=self._heads())
         h_past = None
         n_past = 0
         if state is not None:
@@ -183,8 +213,8 @@ class PoM(nn.Module):
             raise RuntimeError("pom_b200 has no CPU path: move the module and its inputs to a CUDA device")
         xq = self._tokens(xq)
         B, T, D = xq.shape
-        P, S = self._po_dim, self._se_dim
         w_qc, se_bias = self._weights()
+        P, S = self._po_dim, se_bias.shape[0]
         hs = ops.gemm(xq.contiguous().view(B * T, D), w_qc.contiguous()).view(B, T, P + S)
         hp, z = hs[..., :P], hs[..., P:]
         bias32 = _f32(se_bias.contiguous())

@@ -83,6 +83,9 @@ class PoMRoPE(PoM):
             else:
                 stride, keep = self.head_dim // 2, self.n_sel_heads // 2
             tabs = [t[:, ::stride][:, :keep] for t in tabs]
+            r = self._head_copies()
+            if r > 1:  # repeated gate heads: pair k of the r * heads wide gate is copy k % r of pair k // r
+                tabs = [t.repeat_interleave(r, dim=1) for t in tabs]
         return [t.contiguous() for t in tabs]
 
     def _default_positions(self, n_tokens: int, device) -> torch.Tensor:
@@ -141,7 +144,7 @@ class PoMRoPE(PoM):
         same = self_mixing and ctx_positions is None and ctx_positions_hw is None and self.n_sel_heads <= 1
         rope_c = rope_q if same else self._rope_spec(N, cpos, cpos_hw, xq.device)
         spec = LayerSpec(degree=self.order, mask_kind=kind, self_mixing=self_mixing, rope_ctx=rope_c, rope_qry=rope_q,
-                         shard=shard, n_sel_heads=self.n_sel_heads)
+                         shard=shard, n_sel_heads=self._heads())
         w_qc, se_bias = self._weights()
         xq, xc = self._tokens(xq), (None if self_mixing else self._tokens(xc))
         y, _ = pom_layer(xq, xc, w_qc, se_bias, self.po_coeff, self._out_weight(),

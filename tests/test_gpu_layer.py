@@ -36,8 +36,6 @@ def test_fp32_layer_matches_reference_vectors(golden, name):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_ar_forward_matches_reference_vectors(golden, name, dtype):
     """ar_forward as the reference defines it (gate x raw projection per token, state = that projection)."""
-    if dtype == torch.bfloat16 and name == "pom_ar_heads4":
-        pytest.skip("bf16 multi-head gating needs a multiple of 8 heads (16-byte rows of the gate projection)")
     case = golden[name]
     params, x = case["params"], case["xq"]
     want_y, want_h = case["y"], case["h"]
@@ -117,9 +115,11 @@ def test_bf16_fused_path_against_oracle(shape, coeff_scale):
 
 @pytest.mark.parametrize("mask", [None, "causal"])
 @pytest.mark.parametrize("rope", [None, "1d", "2d"])
-def test_bf16_multi_head_gating_against_oracle(mask, rope):
-    """n_sel_heads = 16, the setting of the reference's own benchmark scripts (bench_attn_vs_pom.py:94-97)."""
-    B, side, D, K, E, heads = 2, 16, 64, 2, 2, 16
+@pytest.mark.parametrize("heads", [16, 4, 12])
+def test_bf16_multi_head_gating_against_oracle(mask, rope, heads):
+    """n_sel_heads = 16 is the setting of the reference's own benchmark scripts (bench_attn_vs_pom.py:94-97);
+    4 and 12 heads are not a multiple of 8 and run with repeated gate heads (``PoM._head_copies``)."""
+    B, side, D, K, E = 2, 16, (96 if heads == 12 else 64), 2, 2
     N = side * side
     params = O.init_params(D, K, E, n_sel_heads=heads, seed=9, coeff_scale=0.1)
     g = torch.Generator().manual_seed(10)
@@ -258,7 +258,7 @@ def test_all_masked_sample_aggregates_to_zero():
     mod = make_cuda_module(cfg, params, torch.float32)
     y = mod(x.cuda(), mask=mask.cuda())
     assert torch.isfinite(y).all()
-    assert float(y[1].abs().max()) == 0.0
+    assert float(y[1].detach().abs().max()) == 0.0
 
 
 def test_state_forward_matches_reference_vectors(golden):
