@@ -168,6 +168,11 @@ def _f32_cached(t: torch.Tensor) -> torch.Tensor:
     return _derived_of(t, "f32", lambda x: ops.to_f32(x.contiguous()))
 
 
+def _inv_rows(row_sums: torch.Tensor) -> torch.Tensor:
+    """1 / row sum of a (B, T, N) mask, 0 where a row is empty (fp32)."""
+    return torch.where(row_sums > 0, 1.0 / row_sums, torch.zeros_like(row_sums))
+
+
 def _like_param(g: torch.Tensor, p: torch.Tensor) -> torch.Tensor:
     if p.dtype == torch.float32:
         return g
@@ -228,8 +233,8 @@ class _PoMLayer(torch.autograd.Function):
         denom = None
         maskd = rowden = None
         if full:
-            if shard is not None or heads or spec.n_past is not None:
-                raise NotImplementedError("(B, M, N) masks are not combined with token sharding, multi-head gating or state")
+            if shard is not None or spec.n_past is not None:
+                raise NotImplementedError("(B, M, N) masks are not combined with token sharding or state")
             if mask.dim() != 3 or mask.shape[0] != B or mask.shape[2] != N or mask.shape[1] != T:
                 raise ValueError(f"expected a (B, T, N) = ({B}, {T}, {N}) mask, got {tuple(mask.shape)}")
             maskd = mask.to(device=xq.device, dtype=xq.dtype).contiguous()
@@ -342,13 +347,15 @@ class _PoMLayer(torch.autograd.Function):
         elif heads:
             ones = _ones(B, heads, xq.device)
             s32 = _f32(ops.select_fwd(z, bias32, ones, rope=spec.rope_qry))   # gate in head space (B, T, heads)
+            if full:  # the division by the mask's row sums rides on the (small) gate: s / rowsum, 0 for empty rows
+                s32 = s32 * _inv_rows(rowden).view(B, T, 1)
             # one aggregate per sample: the P-wide gated state and its output GEMM collapse to a (heads x D)
             # matrix per sample (pom_heads_*); per-token aggregates (causal) keep the explicit form
-            collapsed = not causal and ops.heads_supported(heads, D, P)
+            collapsed = not causal and not full and ops.heads_supported(heads, D, P)
             if collapsed:
                 sh = ops.heads_mix(H, w_ag, heads)  # Mb (B, heads, D), kept in the slot of the gated state
             else:
-                sh = ops.select_heads_fwd(s32, Hc if causal else H, xq.dtype)
+                sh = ops.select_heads_fwd(s32, Hc if (causal or full) else H, xq.dtype)
         else:
             sh = ops.select_fwd(z, bias32, Hc if (causal or full) else H, rope=spec.rope_qry, row_denom=rowden)
         if residual is not None and not bf16:
@@ -470,7 +477,9 @@ class _PoMLayer(torch.autograd.Function):
             dsh = ops.gemm(dy2, w_ag, b_mn=True).view(B, T, P)
             if heads:
                 ds32 = ops.zeros_f32(B * T * heads, dev).view(B, T, heads)
-                dH = ops.select_heads_bwd(dsh, s32, Hc if causal else H, ds32)
+                dH = ops.select_heads_bwd(dsh, s32, Hc if (causal or full) else H, ds32)
+                if full:
+                    ds32 = ds32 * _inv_rows(rowden).view(B, T, 1)
                 ds = ds32 if dt == torch.float32 else ops.to_bf16(ds32)
                 ops.select_bwd(ds, z, bias32, _ones(B, heads, dev), g_z.view(B, T, heads), rope=spec.rope_qry,
                                dbias_out=d_bias)

@@ -16,6 +16,7 @@ import torch
 from . import _abi, ops
 from .functional import LayerSpec, SeqShard, _mask_kind, pom_layer
 from .ops import RopeSpec
+from .operators import apply_rope_1d, apply_rope_2d  # noqa: F401  (the reference defines them in this module)
 from .pom import PoM
 
 

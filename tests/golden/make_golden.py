@@ -91,6 +91,7 @@ def main(ref_root: str) -> None:
     mh = make_module(PoM, D, K, E, heads=4)
     record("pom_heads4_none", mh, lambda: dict(mask=None), x, cfg=cfg_h)
     record("pom_heads4_causal", mh, lambda: dict(mask="causal"), x, cfg=cfg_h)
+    record("pom_heads4_mask3d", mh, lambda: dict(mask=m3), x, cfg=cfg_h)
 
     # grouped polynomial projection (n_groups = 2): po_proj is a grouped 1x1 convolution, se_proj a biased Linear
     def make_grouped(cls, heads=1, seed=3, **kw):

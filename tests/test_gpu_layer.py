@@ -14,7 +14,7 @@ LAYER_CASES = ["pom_none", "pom_causal", "pom_mask2d", "pom_mask3d", "pom_cross"
                "rope2d_none", "rope2d_causal"]
 
 
-HEAD_CASES = ["pom_heads4_none", "pom_heads4_causal", "rope2d_heads4_none", "rope1d_heads4_causal"]
+HEAD_CASES = ["pom_heads4_none", "pom_heads4_causal", "pom_heads4_mask3d", "rope2d_heads4_none", "rope1d_heads4_causal"]
 GROUP_CASES = ["pom_groups2_none", "pom_groups2_causal", "pom_groups2_cross_mask2d", "pom_groups2_heads4_none",
                "pom_groups2_bias_none", "pom_groups2_bias_causal", "pom_groups2_bias_cross"]
 
@@ -54,7 +54,8 @@ def test_ar_forward_matches_reference_vectors(golden, name, dtype):
 
 
 @pytest.mark.parametrize("name", LAYER_CASES + ["pom_groups2_none", "pom_groups2_causal", "pom_groups2_bias_none",
-                                                "pom_groups2_bias_causal", "pom_groups2_bias_cross"])
+                                                "pom_groups2_bias_causal", "pom_groups2_bias_cross",
+                                                "pom_heads4_mask3d", "pom_heads4_causal"])
 def test_bf16_layer_matches_oracle_on_rounded_inputs(golden, name):
     case = golden[name]
     cfg = case["cfg"]

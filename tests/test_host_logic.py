@@ -142,3 +142,22 @@ def test_grouped_projection_is_assembled_once_per_parameter_version():
     assert w4.requires_grad and w4 is not w3
     w4.sum().backward()
     assert m.po_proj.weight.grad is not None and float(m.po_proj.weight.grad.min()) == 1.0
+
+
+def test_operator_module_carries_the_reference_names():
+    """Every operator function the reference's tests and benchmarks import has a namesake in pom_b200.operators
+    (pom/pom_triton.py:383, pom_triton_causal.py:400, pom_triton_masked.py:402, pom_triton_rope.py:985, 1020,
+    pom/pom.py:27, pom/pom_rope.py:152, 183), and the CPU is refused rather than served by a fallback."""
+    import torch
+
+    from pom_b200 import operators, pom_rope
+
+    for name in ("poly_agg_mean_triton", "poly_agg_causal_triton", "poly_agg_masked_triton",
+                 "poly_agg_rope_mean_triton", "poly_agg_rope_causal_triton", "pom_activation", "apply_rope_1d",
+                 "apply_rope_2d", "poly_features"):
+        assert callable(getattr(operators, name)), name
+    assert pom_rope.apply_rope_1d is operators.apply_rope_1d and pom_rope.apply_rope_2d is operators.apply_rope_2d
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        operators.pom_activation(torch.randn(2, 3, 8))
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        operators.apply_rope_1d(torch.randn(1, 4, 8), torch.arange(4), torch.ones(4, 4), torch.zeros(4, 4))

@@ -25,7 +25,7 @@ def _oracle_from_case(case, requires_grad=True):
 
 MODULE_CASES = [
     "pom_none", "pom_causal", "pom_mask2d", "pom_mask3d", "pom_cross", "pom_cross_mask2d",
-    "pom_heads4_none", "pom_heads4_causal",
+    "pom_heads4_none", "pom_heads4_causal", "pom_heads4_mask3d",
     "rope1d_none", "rope1d_causal", "rope1d_mask2d", "rope1d_positions", "rope1d_cross",
     "rope2d_none", "rope2d_causal", "rope2d_heads4_none", "rope1d_heads4_causal",
     "pom_groups2_none", "pom_groups2_causal", "pom_groups2_cross_mask2d", "pom_groups2_heads4_none",
