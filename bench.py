@@ -844,7 +844,7 @@ def gemm_roofline(step, dev_sets, peaks, reps=5):
     tot_fl = sum(v[0] for v in agg.values()) / reps
     tot_ms = sum(v[1] for v in agg.values()) / reps
     top = rows[0]
-    return {"bound": "tensor", "kernel": "gemm_tcgen05_kernel: " + top["kernel"], "achieved": top["tflops"],
+    return {"bound": "tensor", "kernel": "gemm_tcgen05_2cta_kernel: " + top["kernel"], "achieved": top["tflops"],
             "peak": peaks["burst"], "unit": "TFLOP/s", "frac": top["tflops"] / peaks["burst"],
             "peak_sustained": peaks["sustained"], "frac_of_sustained": top["tflops"] / peaks["sustained"],
             "peak_source": peaks["source"], "traffic": top["ncu_dram_bytes"],
