@@ -602,6 +602,11 @@ def _ones(b: int, n: int, device) -> torch.Tensor:
 def pom_layer(xq, xc, w_qc, se_bias, coeff, w_ag, mask=None, h_past=None, spec: Optional[LayerSpec] = None,
               residual=None):
     """Whole layer; ``residual`` (B, T, D), bf16 only, is added to the output inside the output projection."""
+    if xq.numel() == 0 and xq.dim() == 3 and xq.is_cuda:
+        # no query token: an empty result that still belongs to the graph (the parameters receive zero gradients)
+        zero = sum(t.sum() * 0 for t in (xq, w_qc, se_bias, coeff, w_ag))
+        y = xq.new_zeros((xq.shape[0], xq.shape[1], w_ag.shape[0])) + zero.to(xq.dtype)
+        return (y if residual is None else y + residual), None
     if spec is not None and spec.frames > 1:
         F = spec.frames
         B, T, D = xq.shape

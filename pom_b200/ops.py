@@ -31,15 +31,24 @@ def _require_cuda(*tensors) -> torch.device:
     return dev
 
 
+def _ld(t: torch.Tensor, dim: int) -> int:
+    """Stride of ``dim``, or the tight row length when that dimension has size 1 (its stride is arbitrary)."""
+    return t.stride(dim) if t.shape[dim] > 1 else t.shape[-1]
+
+
 def _row_stride(t: torch.Tensor) -> int:
     """Leading dimension of a 2-D or 3-D tensor whose last dim is contiguous and whose
-    leading dims collapse to one row index."""
+    leading dims collapse to one row index.  PyTorch leaves the stride of a dimension of size 1 arbitrary (a slice
+    of a (B, 1, W) tensor may report any value there), so such a dimension never decides the answer."""
     if t.stride(-1) != 1:
         raise ValueError("last dimension must be contiguous")
     if t.dim() == 2:
-        return t.stride(0)
+        return t.stride(0) if t.shape[0] > 1 else t.shape[1]
     if t.dim() == 3:
-        if t.shape[0] > 1 and t.stride(0) != t.stride(1) * t.shape[1]:
+        B, N = t.shape[0], t.shape[1]
+        if N == 1:
+            return t.stride(0) if B > 1 else t.shape[2]
+        if B > 1 and t.stride(0) != t.stride(1) * N:
             raise ValueError("batch and token dimensions must collapse to one row stride")
         return t.stride(1)
     raise ValueError("expected a 2-D or 3-D tensor")
@@ -215,7 +224,7 @@ def gemm_batched(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: 
     g = GemmArgs()
     g.A, g.Bm, g.C = ptr(a), ptr(b), ptr(out)
     g.M, g.N, g.K = M, N, K
-    g.lda, g.ldb, g.ldc = a.stride(1), b.stride(-2), out.stride(1)
+    g.lda, g.ldb, g.ldc = _ld(a, 1), _ld(b, -2), _ld(out, 1)
     g.batches = nb
     g.a_batch_stride, g.c_batch_stride = a.stride(0), out.stride(0)
     g.b_batched, g.b_batch_stride = int(bb), (b.stride(0) if bb else 0)
@@ -226,7 +235,7 @@ def gemm_batched(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: 
         if residual.shape != out.shape or residual.dtype != torch.bfloat16 or not residual.is_contiguous() \
                 or not out.is_contiguous():
             raise ValueError("residual must be a contiguous bfloat16 tensor of the (contiguous) output's shape")
-        g.residual, g.ldr = ptr(residual), residual.stride(1)
+        g.residual, g.ldr = ptr(residual), _ld(residual, 1)
         g.c_batch_stride = 0
     _abi.check(_abi.lib().pom_gemm_bf16(C.byref(g), ptr(_abi.status_word(dev)), _abi.stream_ptr()), "pom_gemm_bf16")
     return out

@@ -114,6 +114,60 @@ def test_bf16_fused_path_against_oracle(shape, coeff_scale):
         assert_close(grads[k], w, BF16_TOL, f"d_{k}")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("mask", [None, "causal"])
+@pytest.mark.parametrize("B,N,D,K,E", [(1, 1, 8, 1, 1), (3, 1, 64, 2, 2), (1, 2, 8, 3, 4), (5, 33, 16, 2, 1)])
+def test_smallest_shapes(B, N, D, K, E, mask, dtype):
+    """One token, one sample, eight channels: every tile is partial in every dimension."""
+    cfg, params, x, gy = _seeded_case(B, N, D, K, E, seed=21, coeff_scale=0.1, bias_scale=0.5)
+    tol = FP32_TOL
+    if dtype == torch.bfloat16:
+        params = {k: O.bf16_round(v) for k, v in params.items()}
+        x, gy, tol = O.bf16_round(x), O.bf16_round(gy), BF16_TOL
+    want_y, want_g = oracle_run(cfg, params, x, None, {"mask": mask}, gy)
+    mod = make_cuda_module(cfg, params, dtype)
+    y, grads = cuda_run(mod, x, None, {"mask": mask}, gy, dtype)
+    assert_status_clean()
+    assert_close(y, want_y, tol, "y")
+    for k, w in want_g.items():
+        assert_close(grads[k], w, tol, f"d_{k}")
+
+
+def test_empty_batch_gives_an_empty_result():
+    """No sample, or no query token: the reference's PyTorch path returns an empty tensor; so does this one, and
+    the backward pass gives the parameters zero gradients."""
+    from pom_b200 import PoM
+
+    mod = PoM(64, 2, 2).cuda().to(torch.bfloat16)
+    x = torch.zeros(0, 16, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y = mod(x)
+    assert y.shape == (0, 16, 64)
+    y.sum().backward()
+    assert x.grad.shape == x.shape and float(mod.qc_proj.weight.grad.abs().max()) == 0.0
+    y = mod(torch.zeros(2, 0, 64, device="cuda", dtype=torch.bfloat16), torch.randn(2, 8, 64, device="cuda").bfloat16())
+    assert y.shape == (2, 0, 64)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_one_query_token_against_a_long_context(dtype):
+    """Cross-mixing with T = 1 (a decode step reading a prefilled context) and with N = 1 (many queries, one
+    context token)."""
+    for T, N in ((1, 300), (300, 1)):
+        cfg, params, xq, gy = _seeded_case(2, T, 64, 2, 2, seed=22, coeff_scale=0.1, bias_scale=0.5)
+        xc = torch.randn(2, N, 64, generator=torch.Generator().manual_seed(23))
+        tol = FP32_TOL
+        if dtype == torch.bfloat16:
+            params = {k: O.bf16_round(v) for k, v in params.items()}
+            xq, xc, gy, tol = O.bf16_round(xq), O.bf16_round(xc), O.bf16_round(gy), BF16_TOL
+        want_y, want_g = oracle_run(cfg, params, xq, xc, {}, gy)
+        mod = make_cuda_module(cfg, params, dtype)
+        y, grads = cuda_run(mod, xq, xc, {}, gy, dtype)
+        assert_status_clean()
+        assert_close(y, want_y, tol, f"T={T} N={N} y")
+        for k, w in want_g.items():
+            assert_close(grads[k], w, tol, f"T={T} N={N} d_{k}")
+
+
 @pytest.mark.parametrize("mask", [None, "causal"])
 @pytest.mark.parametrize("rope", [None, "1d", "2d"])
 @pytest.mark.parametrize("heads", [16, 4, 12])
