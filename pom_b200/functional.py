@@ -168,6 +168,19 @@ def _f32_cached(t: torch.Tensor) -> torch.Tensor:
     return _derived_of(t, "f32", lambda x: ops.to_f32(x.contiguous()))
 
 
+def _mask_operand(mask: torch.Tensor, device, dtype) -> torch.Tensor:
+    """(B, T, N) mask as a GEMM operand: rows start on 16-byte boundaries (the row stride is N rounded up to 8
+    elements; the columns past N are never read, the tensor map ends at N)."""
+    B, T, N = mask.shape
+    ld = (N + 7) // 8 * 8
+    if ld == N:
+        return mask.to(device=device, dtype=dtype).contiguous()
+    buf = torch.zeros((B, T, ld), device=device, dtype=dtype)
+    out = buf[..., :N]
+    out.copy_(mask)
+    return out
+
+
 def _inv_rows(row_sums: torch.Tensor) -> torch.Tensor:
     """1 / row sum of a (B, T, N) mask, 0 where a row is empty (fp32)."""
     return torch.where(row_sums > 0, 1.0 / row_sums, torch.zeros_like(row_sums))
@@ -215,8 +228,11 @@ class _PoMLayer(torch.autograd.Function):
         heads = spec.n_sel_heads if spec.n_sel_heads > 1 else 0
         S = heads if heads else P  # width of the gate projection
         bf16 = xq.dtype == torch.bfloat16
-        if heads and bf16 and (heads % 8 or P % 8 or D % 8):
-            raise NotImplementedError("bf16 multi-head gating needs n_sel_heads, dim and dim*expand to be multiples of 8")
+        if bf16 and (P % 8 or D % 8 or (heads and heads % 8)):
+            # rows of every bf16 operand must start on 16-byte boundaries (bulk tensor copies)
+            raise NotImplementedError(
+                f"bfloat16 needs dim ({D}), dim * expand ({P}) and the number of gate heads to be multiples of 8; "
+                "use float32 or pad the channels")
         xq = xq.contiguous()
         xc = xq if spec.self_mixing else xc.contiguous()
         w_qc = w_qc.contiguous()
@@ -237,7 +253,7 @@ class _PoMLayer(torch.autograd.Function):
                 raise NotImplementedError("(B, M, N) masks are not combined with token sharding or state")
             if mask.dim() != 3 or mask.shape[0] != B or mask.shape[2] != N or mask.shape[1] != T:
                 raise ValueError(f"expected a (B, T, N) = ({B}, {T}, {N}) mask, got {tuple(mask.shape)}")
-            maskd = mask.to(device=xq.device, dtype=xq.dtype).contiguous()
+            maskd = _mask_operand(mask, xq.device, xq.dtype)
             rowden = _row_sums(mask.to(device=xq.device, dtype=torch.float32).contiguous().view(B * T, N))
         if spec.mask_kind == "keypad":
             if tuple(mask.shape) != (B, N):
@@ -686,7 +702,7 @@ class _PolyAggFull(torch.autograd.Function):
         if x.stride(-1) != 1 or (B > 1 and x.stride(0) != x.stride(1) * N):
             x = x.contiguous()
         coeff32 = _f32(coeff.contiguous())
-        maskd = mask.to(device=x.device, dtype=x.dtype).contiguous()
+        maskd = _mask_operand(mask, x.device, x.dtype)
         rowden = _row_sums(mask.to(device=x.device, dtype=torch.float32).contiguous().view(B * M, N))
         feat = ops.poly_agg_fwd(x, coeff32, rope=rope, per_token=True)
         Hc = torch.empty((B, M, P), dtype=x.dtype, device=x.device)
@@ -742,7 +758,7 @@ def polynomial_aggregation_(x: torch.Tensor, coeff: torch.Tensor, k: int, mask=N
     """Polynomial aggregation over the sequence dimension (reference pom/pom.py:52-100).
 
     x (B, N, P), coeff (P, K).  Returns (B, 1, P) for mask None or a (B, N) mask, (B, N, P) for "causal" and
-    (B, M, P) for a (B, M, N) mask (bf16: N a multiple of 8; a mask row of zeros gives 0 where the reference
+    (B, M, P) for a (B, M, N) mask (a mask row of zeros gives 0 where the reference
     divides by zero).
     """
     if coeff.shape[1] != k:

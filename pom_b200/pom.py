@@ -16,6 +16,8 @@ import torch.nn as nn
 
 from . import ops
 from .functional import LayerSpec, SeqShard, _f32, _mask_kind, _ones, pom_layer
+from .functional import polynomial_aggregation_, polynomial_selection_, pom  # noqa: F401  (defined here in the reference)
+from .operators import pom_activation  # noqa: F401
 
 
 class PoM(nn.Module):

@@ -133,6 +133,38 @@ def test_smallest_shapes(B, N, D, K, E, mask, dtype):
         assert_close(grads[k], w, tol, f"d_{k}")
 
 
+@pytest.mark.parametrize("heads", [1, 4])
+@pytest.mark.parametrize("N,T", [(37, 5), (3, 3), (9, 130), (130, 9)])
+def test_bf16_ragged_full_masks(N, T, heads):
+    """(B, T, N) masks whose row length is not a multiple of 8 elements (the mask operand's rows are padded to
+    16-byte boundaries), with and without a multi-head gate."""
+    B, D, K, E = 2, 64, 2, 2
+    params = O.init_params(D, K, E, n_sel_heads=heads, seed=31, coeff_scale=0.1)
+    params = {k: O.bf16_round(v) for k, v in params.items()}
+    g = torch.Generator().manual_seed(32)
+    xq, xc = O.bf16_round(torch.randn(B, T, D, generator=g)), O.bf16_round(torch.randn(B, N, D, generator=g))
+    gy = O.bf16_round(torch.randn(B, T, D, generator=g))
+    mask = ((torch.rand(B, T, N, generator=g) < 0.5).float() + torch.eye(T, N)).clamp(max=1.0)
+    cfg = dict(dim=D, degree=K, expand=E, heads=heads)
+    want_y, want_g = oracle_run(cfg, params, xq, xc, {"mask": mask}, gy)
+    mod = make_cuda_module(cfg, params, torch.bfloat16)
+    y, grads = cuda_run(mod, xq, xc, {"mask": mask}, gy, torch.bfloat16)
+    assert_status_clean()
+    assert_close(y, want_y, BF16_TOL, "y")
+    for k, w in want_g.items():
+        assert_close(grads[k], w, BF16_TOL, f"d_{k}")
+
+
+def test_bf16_widths_that_are_not_multiples_of_8_are_refused_with_a_reason():
+    from pom_b200 import PoM
+
+    mod = PoM(100, 2, 1).cuda().to(torch.bfloat16)
+    with pytest.raises(NotImplementedError, match="multiples of 8"):
+        mod(torch.randn(2, 16, 100, device="cuda", dtype=torch.bfloat16))
+    y = PoM(100, 2, 1).cuda()(torch.randn(2, 16, 100, device="cuda"))  # float32 takes any width
+    assert y.shape == (2, 16, 100)
+
+
 def test_empty_batch_gives_an_empty_result():
     """No sample, or no query token: the reference's PyTorch path returns an empty tensor; so does this one, and
     the backward pass gives the parameters zero gradients."""

@@ -153,3 +153,19 @@ def test_degree_above_16_is_refused_like_the_reference():
     x = torch.randn(1, 8, 16, device="cuda")
     with pytest.raises(NotImplementedError):
         poly_agg_mean_triton(x, torch.randn(16, 17, device="cuda"), 17)
+
+
+@pytest.mark.parametrize("mask", [None, "causal"])
+@pytest.mark.parametrize("heads", [1, 4])
+def test_pom_function(mask, heads):
+    """``pom(xq, xc, coeff, k, n_sel_heads, mask)`` imported from the package as in the reference
+    (pom/__init__.py, pom/pom.py:125-135): aggregation of the context gated by the (already activated) queries."""
+    from pom_b200 import pom
+
+    torch.manual_seed(3)
+    B, N, D, K = 2, 40, 32, 3
+    s = torch.rand(B, N, heads if heads > 1 else D)
+    xc, c = torch.randn(B, N, D) * 0.5, torch.randn(D, K) * 0.1
+    _compare(lambda s, x, coeff: pom(s, x, coeff, K, heads, mask),
+             lambda s, x, coeff: O.selection(s, O.aggregate(O.poly_features(x, coeff), mask), heads),
+             {"s": s, "x": xc, "coeff": c}, torch.float32)

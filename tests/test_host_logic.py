@@ -157,6 +157,13 @@ def test_operator_module_carries_the_reference_names():
                  "apply_rope_2d", "poly_features"):
         assert callable(getattr(operators, name)), name
     assert pom_rope.apply_rope_1d is operators.apply_rope_1d and pom_rope.apply_rope_2d is operators.apply_rope_2d
+    # the import lines of the reference's scripts, with the package name changed
+    from pom_b200 import PoM, PoMRoPE, pom  # noqa: F401  (pom/__init__.py)
+    from pom_b200.pom import polynomial_aggregation_, polynomial_selection_, pom_activation  # noqa: F401
+    from pom_b200.pom import pom as pom_fn
+    from pom_b200.pom_rope import precompute_freqs_1d, precompute_freqs_2d  # noqa: F401
+
+    assert callable(pom) and pom is pom_fn and not isinstance(pom, type(operators))
     with pytest.raises(RuntimeError, match="no CPU path"):
         operators.pom_activation(torch.randn(2, 3, 8))
     with pytest.raises(RuntimeError, match="no CPU path"):
