@@ -53,6 +53,21 @@ def test_layer_entry_points_validate_before_touching_the_gpu(lib):
     assert lib.pom_layer_fwd(C.byref(a), None, None) == -9      # workspace too small
 
 
+def test_gemm_entry_point_validates_before_touching_the_gpu(lib):
+    g = _abi.GemmArgs()
+    assert lib.pom_gemm_bf16(C.byref(g), None, None) == -8       # null operands
+    g.A = g.Bm = g.C = 0x1000
+    assert lib.pom_gemm_bf16(C.byref(g), None, None) == -1       # empty problem
+    g.M, g.N, g.K, g.batches = 128, 128, 64, 1
+    g.lda, g.ldb, g.ldc = 60, 64, 128
+    assert lib.pom_gemm_bf16(C.byref(g), None, None) == -2       # row stride not a multiple of 8 elements
+    g.lda, g.ldc = 32, 128
+    assert lib.pom_gemm_bf16(C.byref(g), None, None) == -2       # row stride shorter than a row
+    lib.pom_strerror.restype = C.c_char_p
+    texts = {code: lib.pom_strerror(code) for code in range(0, -10, -1)}
+    assert all(t for t in texts.values()) and len(set(texts.values())) == 10  # one message per code
+
+
 def test_backward_partial_slot_count_never_exceeds_the_chunk_capacity(lib):
     a = _abi.AggBwdArgs()
     for B, N, P in ((32, 1024, 2304), (1, 65536, 2304), (64, 2048, 2048), (3, 70, 96), (2, 320, 256), (2, 24, 32)):
