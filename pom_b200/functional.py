@@ -150,6 +150,8 @@ _derived = {}
 def _derived_of(t: torch.Tensor, what: str, make):
     """Value derived from tensor ``t`` (an fp32 copy of a small bf16 parameter, a transposed weight), remade only
     when ``t`` changes: keyed on the tensor object and its version counter, so an optimizer step invalidates it."""
+    if t.is_inference():  # no version counter to tell an in-place update from no update: remake every time
+        return make(t)
     key = (id(t), what)
     ent = _derived.get(key)
     if ent is not None and ent[0]() is t and ent[1] == t._version:
@@ -157,7 +159,8 @@ def _derived_of(t: torch.Tensor, what: str, make):
     if len(_derived) > 256:
         for k in [k for k, e in _derived.items() if e[0]() is None]:
             del _derived[k]
-    val = make(t)
+    with torch.inference_mode(False):  # a value cached under inference mode must stay usable by a later backward
+        val = make(t)
     _derived[key] = (weakref.ref(t), t._version, val)
     return val
 
@@ -611,7 +614,8 @@ def _ones(b: int, n: int, device) -> torch.Tensor:
     """(b, n) fp32 ones on ``device`` (identity 'state' used to run the gate kernels in head space)."""
     key = (b, n, str(device))
     if key not in _ones_cache:
-        _ones_cache[key] = torch.ones((b, n), dtype=torch.float32, device=device)
+        with torch.inference_mode(False):  # cached: must stay usable by a later backward pass
+            _ones_cache[key] = torch.ones((b, n), dtype=torch.float32, device=device)
     return _ones_cache[key]
 
 

@@ -100,7 +100,9 @@ def rope_pos_info(pos: torch.Tensor):
     if pos.dtype != torch.int64 or not pos.is_contiguous():
         raise TypeError("positions must be a contiguous int64 tensor")
     key = id(pos)
-    ent = _pos_info_cache.get(key)
+    # a tensor made under torch.inference_mode() has no version counter: it is scanned on every call
+    cacheable = not pos.is_inference()
+    ent = _pos_info_cache.get(key) if cacheable else None
     if ent is not None and ent[0]() is pos and ent[1] == pos._version:
         return ent[2]
     for k in [k for k, e in _pos_info_cache.items() if e[0]() is None]:
@@ -112,7 +114,8 @@ def rope_pos_info(pos: torch.Tensor):
     vals = info.cpu().tolist()
     out = tuple((vals[4 * c], vals[4 * c + 1], 0 if vals[4 * c + 2] else (1 if vals[4 * c + 3] else -1))
                 for c in range(stride))
-    _pos_info_cache[key] = (weakref.ref(pos), pos._version, out)
+    if cacheable:
+        _pos_info_cache[key] = (weakref.ref(pos), pos._version, out)
     return out
 
 

@@ -120,9 +120,14 @@ class PoM(nn.Module):
         # Without autograd the assembled tensors are kept per parameter version (in-place updates and .data swaps
         # change the key); with autograd they are rebuilt per call, which is once per version in a training loop.
         track = torch.is_grad_enabled() and any(t.requires_grad for t in src)
-        key = tuple((t._version, t.data_ptr(), t.dtype, t.device) for t in src) + (r,)
-        if not track and self._grouped_cache is not None and self._grouped_cache[0] == key:
+        # parameters made under torch.inference_mode() have no version counter: assembled on every call
+        keep = not track and not any(t.is_inference() for t in src)
+        key = tuple((t._version, t.data_ptr(), t.dtype, t.device) for t in src) + (r,) if keep else None
+        if keep and self._grouped_cache is not None and self._grouped_cache[0] == key:
             return self._grouped_cache[1]
+        if keep and torch.is_inference_mode_enabled():
+            with torch.inference_mode(False), torch.no_grad():  # what is cached must stay usable by a later backward
+                return self._weights()
         if self.n_groups == 1:
             w_po, ws, bias = self.qc_proj.weight[:P], self.qc_proj.weight[P:], self.se_bias
         else:
@@ -138,7 +143,7 @@ class PoM(nn.Module):
             extra = w_qc.new_zeros(w_qc.shape[0], self._BIAS_COLS - 1)
             first = torch.cat([bp.to(w_qc.dtype), w_qc.new_zeros(ws.shape[0])])
             w_qc = torch.cat([w_qc, first[:, None], extra], dim=1)
-        if not track:
+        if keep:
             self._grouped_cache = (key, (w_qc, bias))
         return w_qc, bias
 

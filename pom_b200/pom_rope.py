@@ -94,7 +94,8 @@ class PoMRoPE(PoM):
         cache = self.__dict__.setdefault("_arange_cache", {})
         key = (n_tokens, str(device))
         if key not in cache:
-            cache[key] = torch.arange(n_tokens, device=device, dtype=torch.int64)
+            with torch.inference_mode(False):  # an ordinary tensor, so that its position scan can be cached
+                cache[key] = torch.arange(n_tokens, device=device, dtype=torch.int64)
         return cache[key]
 
     @staticmethod

@@ -165,6 +165,41 @@ def test_bf16_widths_that_are_not_multiples_of_8_are_refused_with_a_reason():
     assert y.shape == (2, 16, 100)
 
 
+def test_inference_mode_tensors_are_accepted():
+    """Tensors made under torch.inference_mode() carry no version counter, which the per-parameter and
+    per-position caches are keyed on: modules built, and positions made, inside such a block still work and give
+    the results of ordinary tensors."""
+    from pom_b200 import PoM, PoMRoPE
+
+    torch.manual_seed(0)
+    x = torch.randn(2, 64, 64, device="cuda").bfloat16()
+    hw = torch.stack([torch.arange(64) // 8, torch.arange(64) % 8], 1).cuda()
+    plain = PoM(64, 2, 2, n_groups=2).cuda().bfloat16()
+    rope = PoMRoPE(64, 2, 2, rope_2d=True, max_h=8, max_w=8).cuda().bfloat16()
+    want_plain, want_rope = plain(x), rope(x, positions_hw=hw)
+    r1 = PoMRoPE(64, 2, 2, max_seq_len=64).cuda().bfloat16()
+    with torch.inference_mode():
+        inside = PoM(64, 2, 2, n_groups=2).cuda().bfloat16()
+        inside.load_state_dict(plain.state_dict())
+        assert torch.equal(inside(x), want_plain)
+        inside.se_proj.bias.add_(1.0)  # an in-place update that no version counter records
+        assert not torch.equal(inside(x), want_plain)
+        assert torch.equal(rope(x, positions_hw=hw.clone()), want_rope)
+        assert torch.equal(rope(x, positions_hw=hw), want_rope)
+        y_in = r1(x)  # default positions first requested inside the block
+    assert torch.equal(r1(x), y_in)
+    # what the first call cached inside the block (fp32 copies of the coefficients, the assembled grouped
+    # projection of a frozen module) must not poison a later training step
+    xg = x.clone().requires_grad_(True)
+    r1(xg).sum().backward()
+    for p_ in plain.parameters():
+        p_.requires_grad_(False)
+    with torch.inference_mode():
+        plain(x)
+    plain(xg).sum().backward()
+    assert bool(torch.isfinite(xg.grad).all())
+
+
 def test_empty_batch_gives_an_empty_result():
     """No sample, or no query token: the reference's PyTorch path returns an empty tensor; so does this one, and
     the backward pass gives the parameters zero gradients."""
