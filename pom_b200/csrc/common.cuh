@@ -3,6 +3,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <atomic>
+#include <mutex>
 #include <stdint.h>
 #include "../../include/pom_b200.h"
 
@@ -32,6 +33,24 @@ inline int sm_count() {
 }
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// Runs `f` (returning POM_OK or an error) once per device of this process: attributes of a kernel function
+// (the opt-in to more than 48 KB of dynamic shared memory) belong to the device that is current when they are set.
+// `done` holds one bit per device ordinal; beyond 64 devices, or when the current device cannot be read, `f` runs
+// on every call.
+template <class F>
+inline int once_per_device(std::atomic<uint64_t>& done, F&& f) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return f();
+  const uint64_t bit = 1ull << dev;
+  if (done.load(std::memory_order_acquire) & bit) return POM_OK;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  if (done.load(std::memory_order_relaxed) & bit) return POM_OK;
+  const int rc = f();
+  if (rc == POM_OK) done.fetch_or(bit, std::memory_order_release);
+  return rc;
+}
 
 // Launch with programmatic stream serialization: the kernel may become resident while its predecessor in the stream
 // drains.  Only for kernels that execute griddepcontrol.wait (pomk::griddep_wait) before they touch memory the

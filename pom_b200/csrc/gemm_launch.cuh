@@ -201,14 +201,14 @@ inline int check_operands(const Operands& o) {
 }
 
 template <class Kern>
-int set_smem_once(Kern kern, int smem, bool* done) {
-  if (*done) return POM_OK;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
-    (void)cudaGetLastError();
-    return POM_ERR_CUDA;
-  }
-  *done = true;
-  return POM_OK;
+int set_smem_once(Kern kern, int smem, std::atomic<uint64_t>* done) {
+  return once_per_device(*done, [&] {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return static_cast<int>(POM_ERR_CUDA);
+    }
+    return static_cast<int>(POM_OK);
+  });
 }
 
 // Epilogues whose constants depend on the tile's columns (Epi::kStager: lane tables, coefficients, bias) run
@@ -246,7 +246,7 @@ int launch(const Operands& o, int split_k, const EpiMaps& maps, const typename E
   GemmGeom g = make_geom(o, BN, split_k);
   constexpr int smem = gemm_smem_bytes<BN, STAGES, Epi>();
   auto kern = gemm_tcgen05_kernel<BN, STAGES, A_MN, B_MN, Epi>;
-  static bool attr_set = false;
+  static std::atomic<uint64_t> attr_set{0};
   if ((rc = set_smem_once(kern, smem, &attr_set))) return rc;
   const long long units = 1ll * g.batches * g.m_tiles_per_batch * g.n_tiles * g.split_k;
   if (units > INT32_MAX) return POM_ERR_TOO_LARGE;
@@ -268,7 +268,7 @@ int launch_pair(const Operands& o, int split_k, const EpiMaps& maps, const typen
   GemmGeom g = make_geom(o, BN, split_k);
   constexpr int smem = gemm2_smem_bytes<BN, STAGES, Epi>();
   auto kern = gemm_tcgen05_2cta_kernel<BN, STAGES, A_MN, B_MN, Epi>;
-  static bool attr_set = false;
+  static std::atomic<uint64_t> attr_set{0};
   if ((rc = set_smem_once(kern, smem, &attr_set))) return rc;
   const long long units = 1ll * g.batches * ((g.m_tiles_per_batch + 1) / 2) * g.n_tiles * g.split_k;
   if (units > INT32_MAX) return POM_ERR_TOO_LARGE;

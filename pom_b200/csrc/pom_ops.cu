@@ -1663,12 +1663,13 @@ int pom_poly_agg_bwd(const pom_agg_bwd_args* a, void* stream) {
     const dim3 sgrid(static_cast<unsigned>(sp.col_blocks), static_cast<unsigned>(sp.splits),
                      static_cast<unsigned>(a->B));
     if (sp.splits > 65535) return POM_ERR_TOO_LARGE;
-    static std::once_flag attr_once;
-    std::call_once(attr_once, [] {
+    static std::atomic<uint64_t> attr_done{0};
+    (void)once_per_device(attr_done, [] {
       cudaFuncSetAttribute(agg_bwd_stream_kernel<2, kStVec, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            kStSmemBytes);
       cudaFuncSetAttribute(agg_bwd_stream_kernel<4, kStVec, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            kStSmemBytes);
+      return static_cast<int>(POM_OK);
     });
     constexpr int threads = kStCols / kStVec * 8;
     CUtensorMap tmx;
@@ -1692,11 +1693,12 @@ int pom_poly_agg_bwd(const pom_agg_bwd_args* a, void* stream) {
     if (sp.splits > 65535) return POM_ERR_TOO_LARGE;
     const dim3 sgrid(static_cast<unsigned>(sp.col_blocks), static_cast<unsigned>(sp.splits),
                      static_cast<unsigned>(a->B));
-    static std::once_flag attr_once_rope;
-    std::call_once(attr_once_rope, [] {
+    static std::atomic<uint64_t> attr_done_rope{0};
+    (void)once_per_device(attr_done_rope, [] {
       cudaFuncSetAttribute(agg_bwd_stream_pair_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStSmemBytes);
       cudaFuncSetAttribute(agg_bwd_stream_pair_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStSmemBytes);
       cudaFuncSetAttribute(agg_bwd_stream_pair_kernel<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStSmemBytes);
+      return static_cast<int>(POM_OK);
     });
     const int bps = sp.col_blocks / pr.sections;
     CUtensorMap tmx, tms;

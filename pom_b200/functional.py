@@ -19,6 +19,7 @@ by a local exclusive scan for the causal mask, and the mirrored exchanges in bac
 """
 from __future__ import annotations
 
+import functools
 import weakref
 from dataclasses import dataclass
 from typing import Any, Optional, Tuple, Union
@@ -28,6 +29,22 @@ import torch.distributed as dist
 
 from . import _abi, ops
 from .ops import RopeSpec
+
+
+def on_tensor_device(fn):
+    """Runs ``fn`` with the device of its first CUDA tensor argument current: the library launches on the current
+    device's current stream, so a tensor on another GPU than the current one (``x.to("cuda:1")`` without
+    ``torch.cuda.set_device(1)``) must switch devices first, as PyTorch's own operators do."""
+
+    @functools.wraps(fn)
+    def wrapper(*args, **kwargs):
+        dev = next((a.device for a in args if torch.is_tensor(a) and a.is_cuda), None)
+        if dev is None or dev.index == torch.cuda.current_device():
+            return fn(*args, **kwargs)
+        with torch.cuda.device(dev):
+            return fn(*args, **kwargs)
+
+    return wrapper
 
 
 # True: a fused-path layer without token sharding is two library calls (pom_layer_fwd / pom_layer_bwd).  False:
@@ -149,19 +166,21 @@ _derived = {}
 
 def _derived_of(t: torch.Tensor, what: str, make):
     """Value derived from tensor ``t`` (an fp32 copy of a small bf16 parameter, a transposed weight), remade only
-    when ``t`` changes: keyed on the tensor object and its version counter, so an optimizer step invalidates it."""
+    when ``t`` changes: keyed on the tensor object, its version counter and its storage, so an optimizer step or a move
+    to another device invalidates it."""
     if t.is_inference():  # no version counter to tell an in-place update from no update: remake every time
         return make(t)
     key = (id(t), what)
     ent = _derived.get(key)
-    if ent is not None and ent[0]() is t and ent[1] == t._version:
+    stamp = (t._version, t.data_ptr(), t.device, t.dtype)  # .data swaps (Module.to, casts) keep the version
+    if ent is not None and ent[0]() is t and ent[1] == stamp:
         return ent[2]
     if len(_derived) > 256:
         for k in [k for k, e in _derived.items() if e[0]() is None]:
             del _derived[k]
     with torch.inference_mode(False):  # a value cached under inference mode must stay usable by a later backward
         val = make(t)
-    _derived[key] = (weakref.ref(t), t._version, val)
+    _derived[key] = (weakref.ref(t), stamp, val)
     return val
 
 
@@ -223,6 +242,7 @@ class _PoMLayer(torch.autograd.Function):
     value per head (Wse is (heads, D)) and multiplies all channels of its head (pom/pom.py:119-122)."""
 
     @staticmethod
+    @on_tensor_device
     def forward(ctx, xq, xc, w_qc, se_bias, coeff, w_ag, mask, h_past, spec: LayerSpec, residual=None):
         _check_inputs(xq, xc, w_qc, w_ag, coeff, spec)
         B, T, D = xq.shape
@@ -398,6 +418,7 @@ class _PoMLayer(torch.autograd.Function):
         return y, None
 
     @staticmethod
+    @on_tensor_device
     def backward(ctx, dy, dh_state):
         spec: LayerSpec = ctx.spec
         xq, xc, w_qc, w_ag, coeff32, bias32, hp, z, H, Hc, sh, maskf, denom, s32, maskd, rowden = ctx.saved_tensors
@@ -648,6 +669,7 @@ class _PolyAgg(torch.autograd.Function):
     """polynomial_aggregation_ for mask None / "causal" / (B, N), optional rotary embedding."""
 
     @staticmethod
+    @on_tensor_device
     def forward(ctx, x, coeff, mask_kind, mask, rope):
         if not x.is_cuda:
             raise RuntimeError("pom_b200 has no CPU path: pass CUDA tensors")
@@ -672,6 +694,7 @@ class _PolyAgg(torch.autograd.Function):
         return out
 
     @staticmethod
+    @on_tensor_device
     def backward(ctx, g):
         x, coeff32, maskf, denom = ctx.saved_tensors
         mask_kind, rope, cdt = ctx.meta
@@ -696,6 +719,7 @@ class _PolyAggFull(torch.autograd.Function):
     division by the row sums inside the selection kernel (whose gate is the constant 1 here)."""
 
     @staticmethod
+    @on_tensor_device
     def forward(ctx, x, coeff, mask, rope):
         if not x.is_cuda:
             raise RuntimeError("pom_b200 has no CPU path: pass CUDA tensors")
@@ -721,6 +745,7 @@ class _PolyAggFull(torch.autograd.Function):
         return ops.select_fwd(one, None, Hc, activated=True, row_denom=rowden)
 
     @staticmethod
+    @on_tensor_device
     def backward(ctx, g):
         x, coeff32, maskd, rowden, Hc, one = ctx.saved_tensors
         rope, cdt = ctx.meta
@@ -781,6 +806,7 @@ class _GateMul(torch.autograd.Function):
     """s ⊙ h with h broadcast over tokens (g == 1) or matched per token (g == t)."""
 
     @staticmethod
+    @on_tensor_device
     def forward(ctx, s, h):
         if not s.is_cuda:
             raise RuntimeError("pom_b200 has no CPU path: pass CUDA tensors")
@@ -793,6 +819,7 @@ class _GateMul(torch.autograd.Function):
         return ops.select_fwd(s, None, hk, activated=True)
 
     @staticmethod
+    @on_tensor_device
     def backward(ctx, g):
         s, hk = ctx.saved_tensors
         per_tok, hdt, hshape = ctx.meta
@@ -809,6 +836,7 @@ class _GateMulHeads(torch.autograd.Function):
     """s (B, T, heads) broadcast over the channels of each head, times h (per sample or per token)."""
 
     @staticmethod
+    @on_tensor_device
     def forward(ctx, s, h):
         if not s.is_cuda:
             raise RuntimeError("pom_b200 has no CPU path: pass CUDA tensors")
@@ -821,6 +849,7 @@ class _GateMulHeads(torch.autograd.Function):
         return ops.select_heads_fwd(s32, hk, h.dtype)
 
     @staticmethod
+    @on_tensor_device
     def backward(ctx, g):
         s32, hk = ctx.saved_tensors
         per_tok, sdt, hdt, hshape = ctx.meta

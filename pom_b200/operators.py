@@ -17,7 +17,7 @@ from typing import Optional
 import torch
 
 from . import _abi, ops
-from .functional import _f32, _ones, polynomial_aggregation_
+from .functional import _f32, _ones, on_tensor_device, polynomial_aggregation_
 from .ops import RopeSpec
 
 __all__ = [
@@ -98,6 +98,7 @@ class _Rotate(torch.autograd.Function):
     hardsigmoid, no bias) and the constant 1 as the aggregate."""
 
     @staticmethod
+    @on_tensor_device
     def forward(ctx, x, spec: RopeSpec):
         x = _rows(x)
         ctx.spec = spec
@@ -105,6 +106,7 @@ class _Rotate(torch.autograd.Function):
         return ops.select_fwd(x, None, _ones(x.shape[0], x.shape[2], x.device), rope=spec, activated=True)
 
     @staticmethod
+    @on_tensor_device
     def backward(ctx, g):
         B, N, P = ctx.shape
         g = _rows(g)
@@ -114,6 +116,7 @@ class _Rotate(torch.autograd.Function):
         return dx, None
 
 
+@on_tensor_device
 def apply_rope_1d(x: torch.Tensor, positions: torch.Tensor, freqs_cos: torch.Tensor,
                   freqs_sin: torch.Tensor) -> torch.Tensor:
     """Rotate-half 1-D rotary embedding: channel k pairs with k + D/2 (reference pom/pom_rope.py:152-180).
@@ -122,6 +125,7 @@ def apply_rope_1d(x: torch.Tensor, positions: torch.Tensor, freqs_cos: torch.Ten
     return _Rotate.apply(x, _spec_1d(x, positions, freqs_cos, freqs_sin))
 
 
+@on_tensor_device
 def apply_rope_2d(x: torch.Tensor, positions_hw: torch.Tensor, row_cos: torch.Tensor, row_sin: torch.Tensor,
                   col_cos: torch.Tensor, col_sin: torch.Tensor) -> torch.Tensor:
     """2-D rotary embedding: the first half of the channels rotates with the row position, the second half with
@@ -136,6 +140,7 @@ class _Features(torch.autograd.Function):
     """f[b, n, p] = sum_k coeff[p, k] act(x[b, n, p])^(k+1) (reference pom/pom_rope.py:242-265, pom/pom.py:83-89)."""
 
     @staticmethod
+    @on_tensor_device
     def forward(ctx, x, coeff):
         x = _rows(x)
         coeff32 = _f32(coeff.contiguous())
@@ -144,6 +149,7 @@ class _Features(torch.autograd.Function):
         return ops.poly_agg_fwd(x, coeff32, per_token=True)
 
     @staticmethod
+    @on_tensor_device
     def backward(ctx, g):
         x, coeff32 = ctx.saved_tensors
         dx = torch.empty_like(x)
@@ -192,6 +198,7 @@ def poly_agg_masked(x: torch.Tensor, mask: torch.Tensor, coeff: torch.Tensor, k:
     return polynomial_aggregation_(x, coeff, k, mask)
 
 
+@on_tensor_device
 def poly_agg_rope_mean(x: torch.Tensor, coeff: torch.Tensor, k: int, freqs_cos: torch.Tensor,
                        freqs_sin: torch.Tensor, positions: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Features, 1-D rotation by position, mean over the tokens: -> (B, 1, D); positions default to 0..N-1
@@ -201,6 +208,7 @@ def poly_agg_rope_mean(x: torch.Tensor, coeff: torch.Tensor, k: int, freqs_cos: 
     return polynomial_aggregation_(x, coeff, k, None, rope=_spec_1d(x, positions, freqs_cos, freqs_sin))
 
 
+@on_tensor_device
 def poly_agg_rope_causal(x: torch.Tensor, coeff: torch.Tensor, k: int, freqs_cos: torch.Tensor,
                          freqs_sin: torch.Tensor, positions: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Features, 1-D rotation by position, causal prefix mean: -> (B, N, D)

@@ -16,7 +16,7 @@ import torch
 import torch.nn as nn
 
 from . import ops
-from .functional import BlockCausal
+from .functional import BlockCausal, on_tensor_device
 from .pom import PoM
 
 
@@ -30,6 +30,7 @@ class PoMStack(nn.Module):
         self.ffn_in = nn.ModuleList([nn.Linear(dim, ffn_mult * dim, bias=False) for _ in range(n_layers)])
         self.ffn_out = nn.ModuleList([nn.Linear(ffn_mult * dim, dim, bias=False) for _ in range(n_layers)])
 
+    @on_tensor_device
     @torch.no_grad()
     def frame_forward(self, x: torch.Tensor, states: Optional[List[Optional[dict]]] = None):
         """One frame (B, L, D) bf16 through all layers; ``states`` is the per-layer list returned by the
@@ -46,6 +47,7 @@ class PoMStack(nn.Module):
             h = ops.gemm(u, self.ffn_out[i].weight, residual=h2).view(B, L, D)
         return h, states
 
+    @on_tensor_device
     @torch.no_grad()
     def forward_single_pass(self, x: torch.Tensor, frame_len: int) -> torch.Tensor:
         """Same result as :meth:`forward`, all frames at once: each mixer runs with ``BlockCausal(frame_len)``, so
@@ -62,6 +64,7 @@ class PoMStack(nn.Module):
             h = ops.gemm(u, self.ffn_out[i].weight, residual=h2).view(B, N, D)
         return h
 
+    @on_tensor_device
     @torch.no_grad()
     def forward(self, x: torch.Tensor, frame_len: int) -> torch.Tensor:
         """Full sequence (B, F·frame_len, D), processed frame by frame with state carried across frames."""

@@ -200,6 +200,28 @@ def test_inference_mode_tensors_are_accepted():
     assert bool(torch.isfinite(xg.grad).all())
 
 
+def test_module_cast_after_first_use():
+    """nn.Module.to / .float() swap the parameters' storage without touching their version counters: values the
+    layer derived from them (fp32 copies of coefficients and bias) must follow."""
+    from pom_b200 import PoM
+
+    torch.manual_seed(0)
+    mod = PoM(64, 2, 2).cuda().bfloat16()
+    with torch.no_grad():
+        mod.po_coeff.copy_(torch.randn_like(mod.po_coeff) * 0.1)
+    x = torch.randn(2, 40, 64, device="cuda")
+    y16 = mod(x.bfloat16())
+    mod.float()
+    y32 = mod(x)
+    assert y32.dtype == torch.float32
+    assert_close(y32, y16.float().cpu(), BF16_TOL, "fp32 after bf16")
+    with torch.no_grad():
+        mod.po_coeff.mul_(2.0)  # in-place update: version counter
+    assert not torch.allclose(mod(x), y32)
+    mod.po_coeff.data = mod.po_coeff.data / 2.0  # storage swap: no version change
+    assert torch.allclose(mod(x), y32, rtol=1e-5, atol=1e-6)
+
+
 def test_empty_batch_gives_an_empty_result():
     """No sample, or no query token: the reference's PyTorch path returns an empty tensor; so does this one, and
     the backward pass gives the parameters zero gradients."""
