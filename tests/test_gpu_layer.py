@@ -551,6 +551,51 @@ def test_full_size_dit_layer_properties():
     assert_status_clean()
 
 
+@pytest.mark.parametrize("kind", ["plain", "rope2d_causal"])
+def test_tensors_beyond_two_billion_elements(kind):
+    """16 sequences of 65 536 tokens at D = 1152: the projected tensors hold 2.4e9 elements, past 32-bit element
+    indices.  Size-independent properties: samples are independent (each half of the batch reproduces its part
+    of the output and of the input gradient bit for bit) and parameter gradients add up over the halves."""
+    from pom_b200 import PoM, PoMRoPE
+
+    B, N, D = 16, 65536, 1152
+    if torch.cuda.mem_get_info()[0] < 60 << 30:
+        pytest.skip("needs 60 GB of free device memory")
+    torch.manual_seed(0)
+    kw = {}
+    if kind == "plain":
+        mod = PoM(D, 2, 2).cuda()
+    else:
+        mod = PoMRoPE(D, 2, 2, rope_2d=True, max_h=256, max_w=256).cuda()
+        kw = dict(mask="causal", positions_hw=torch.stack([torch.arange(N) // 256, torch.arange(N) % 256], 1).cuda())
+    for p_ in mod.parameters():
+        p_.data = p_.data.bfloat16()
+    with torch.no_grad():
+        mod.po_coeff.copy_(torch.randn_like(mod.po_coeff) * 0.1)
+    x = torch.randn(B, N, D, device="cuda", dtype=torch.bfloat16)
+    gy = torch.randn(B, N, D, device="cuda", dtype=torch.bfloat16)
+
+    def step(xs, gs):
+        xs = xs.clone().requires_grad_(True)
+        y = mod(xs, **kw)
+        y.backward(gs)
+        grads = [p_.grad.float().clone() for p_ in mod.parameters()]
+        for p_ in mod.parameters():
+            p_.grad = None
+        return y.detach(), xs.grad, grads
+
+    y, dx, g = step(x, gy)
+    assert_status_clean()
+    assert bool(torch.isfinite(y).all()) and bool(torch.isfinite(dx).all())
+    h = B // 2
+    y0, dx0, g0 = step(x[:h], gy[:h])
+    y1, dx1, g1 = step(x[h:], gy[h:])
+    assert torch.equal(y[:h], y0) and torch.equal(y[h:], y1)
+    assert torch.equal(dx[:h], dx0) and torch.equal(dx[h:], dx1)
+    for a, b, c in zip(g, g0, g1):  # each gradient was rounded to bf16 once
+        assert float((a - (b + c)).norm() / a.norm()) < 1e-2
+
+
 def test_cpu_tensors_are_rejected_loudly():
     from pom_b200 import PoM
 
