@@ -31,6 +31,13 @@ from . import _abi, ops
 from .ops import RopeSpec
 
 
+def eager_only(fn):
+    """Keeps ``torch.compile`` out of ``fn``: the library is called through ctypes with raw pointers, which a tracing
+    compiler can neither follow nor fake, so a compiled model runs these calls as they are (a graph break)."""
+    disable = getattr(getattr(torch, "compiler", None), "disable", None)
+    return disable(fn) if disable is not None else fn
+
+
 def on_tensor_device(fn):
     """Runs ``fn`` with the device of its first CUDA tensor argument current: the library launches on the current
     device's current stream, so a tensor on another GPU than the current one (``x.to("cuda:1")`` without
@@ -188,6 +195,20 @@ def _f32_cached(t: torch.Tensor) -> torch.Tensor:
     if t.dtype == torch.float32:
         return t.contiguous()
     return _derived_of(t, "f32", lambda x: ops.to_f32(x.contiguous()))
+
+
+MAX_BATCH = 65535  # samples per library call: the operator kernels put the sample index in a grid dimension
+
+
+def _batch_slices(n_samples: int, per_call: int = MAX_BATCH):
+    """Slices that cut ``n_samples`` into runs of at most ``per_call`` (samples are independent of one another)."""
+    per_call = max(1, per_call)
+    return [slice(i, min(i + per_call, n_samples)) for i in range(0, n_samples, per_call)]
+
+
+def _cut(t, sl):
+    """``t[sl]`` for a per-sample tensor, ``t`` itself for anything shared by the samples (None, "causal", ...)."""
+    return t[sl] if torch.is_tensor(t) else t
 
 
 def _mask_operand(mask: torch.Tensor, device, dtype) -> torch.Tensor:
@@ -390,7 +411,9 @@ class _PoMLayer(torch.autograd.Function):
                 s32 = s32 * _inv_rows(rowden).view(B, T, 1)
             # one aggregate per sample: the P-wide gated state and its output GEMM collapse to a (heads x D)
             # matrix per sample (pom_heads_*); per-token aggregates (causal) keep the explicit form
-            collapsed = not causal and not full and ops.heads_supported(heads, D, P)
+            # (bf16: the batched tensor-core products of the collapsed form read rows of head_dim elements)
+            collapsed = (not causal and not full and ops.heads_supported(heads, D, P)
+                         and (not bf16 or (P // heads) % 8 == 0))
             if collapsed:
                 sh = ops.heads_mix(H, w_ag, heads)  # Mb (B, heads, D), kept in the slot of the gated state
             else:
@@ -640,6 +663,7 @@ def _ones(b: int, n: int, device) -> torch.Tensor:
     return _ones_cache[key]
 
 
+@eager_only
 def pom_layer(xq, xc, w_qc, se_bias, coeff, w_ag, mask=None, h_past=None, spec: Optional[LayerSpec] = None,
               residual=None):
     """Whole layer; ``residual`` (B, T, D), bf16 only, is added to the output inside the output projection."""
@@ -648,6 +672,16 @@ def pom_layer(xq, xc, w_qc, se_bias, coeff, w_ag, mask=None, h_past=None, spec: 
         zero = sum(t.sum() * 0 for t in (xq, w_qc, se_bias, coeff, w_ag))
         y = xq.new_zeros((xq.shape[0], xq.shape[1], w_ag.shape[0])) + zero.to(xq.dtype)
         return (y if residual is None else y + residual), None
+    frames = spec.frames if spec is not None else 1
+    if xq.dim() == 3 and xq.shape[0] * frames > MAX_BATCH and (spec is None or spec.shard is None):
+        # more samples than one library call takes: the samples are independent, so run them in slices
+        ys, hs = [], []
+        for sl in _batch_slices(xq.shape[0], MAX_BATCH // frames):
+            y, h = pom_layer(xq[sl], _cut(xc, sl), w_qc, se_bias, coeff, w_ag, _cut(mask, sl), _cut(h_past, sl), spec,
+                             _cut(residual, sl))
+            ys.append(y)
+            hs.append(h)
+        return torch.cat(ys, dim=0), (None if hs[0] is None else torch.cat(hs, dim=0))
     if spec is not None and spec.frames > 1:
         F = spec.frames
         B, T, D = xq.shape
@@ -782,6 +816,7 @@ def _mask_kind(mask) -> str:
     raise ValueError('Unsupported mask: expected None, "causal", or a 2/3-D tensor.')
 
 
+@eager_only
 def polynomial_aggregation_(x: torch.Tensor, coeff: torch.Tensor, k: int, mask=None,
                             rope: Optional[RopeSpec] = None) -> torch.Tensor:
     """Polynomial aggregation over the sequence dimension (reference pom/pom.py:52-100).
@@ -797,6 +832,9 @@ def polynomial_aggregation_(x: torch.Tensor, coeff: torch.Tensor, k: int, mask=N
     kind = _mask_kind(mask)
     if kind == "block":
         raise ValueError("BlockCausal is a layer-level mask (PoM.forward); pass a (B, M, N) tensor to the operator")
+    if x.dim() == 3 and x.shape[0] > MAX_BATCH:
+        return torch.cat([polynomial_aggregation_(x[sl], coeff, k, _cut(mask, sl), rope)
+                          for sl in _batch_slices(x.shape[0])], dim=0)
     if kind == "full":
         return _PolyAggFull.apply(x, coeff, mask, rope)
     return _PolyAgg.apply(x, coeff, kind, mask if kind == "keypad" else None, rope)
@@ -862,12 +900,15 @@ class _GateMulHeads(torch.autograd.Function):
         return (ds32 if sdt == torch.float32 else ops.to_bf16(ds32)), dh
 
 
+@eager_only
 def polynomial_selection_(s: torch.Tensor, h: torch.Tensor, n_sel_heads: int) -> torch.Tensor:
     """Gated selection s ⊙ h (reference pom/pom.py:103-122): s already activated, (B, T, P) — or
     (B, T, n_sel_heads) with one gate value per head —, h (B, G, P) with G == 1 or G == T."""
     b, g, dh = h.shape
     t = s.shape[1]
     assert g == 1 or t == 1 or g == t, f"incompatible shapes: g={g} t={t}"
+    if b > MAX_BATCH:
+        return torch.cat([polynomial_selection_(s[sl], h[sl], n_sel_heads) for sl in _batch_slices(b)], dim=0)
     if n_sel_heads > 1:
         if s.shape[2] != n_sel_heads or dh % n_sel_heads:
             raise ValueError(f"expected a (B, T, {n_sel_heads}) gate and dim divisible by n_sel_heads")

@@ -17,7 +17,7 @@ from typing import Optional
 import torch
 
 from . import _abi, ops
-from .functional import _f32, _ones, on_tensor_device, polynomial_aggregation_
+from .functional import MAX_BATCH, _batch_slices, _f32, _ones, eager_only, on_tensor_device, polynomial_aggregation_
 from .ops import RopeSpec
 
 __all__ = [
@@ -92,6 +92,14 @@ def _spec_2d(x: torch.Tensor, positions_hw, row_cos, row_sin, col_cos, col_sin) 
     return RopeSpec(_abi.ROPE_2D, tabs[0], tabs[1], pos, tabs[2], tabs[3])
 
 
+def _in_batch_slices(fn, x: torch.Tensor, *shared):
+    """``fn(x, *shared)``, in runs of at most MAX_BATCH samples when x has more (the kernels put the sample index in
+    a grid dimension; the samples are independent)."""
+    if x.dim() != 3 or x.shape[0] <= MAX_BATCH:
+        return fn(x, *shared)
+    return torch.cat([fn(x[sl], *shared) for sl in _batch_slices(x.shape[0])], dim=0)
+
+
 # --------------------------------------------------------------------------- rotation alone
 class _Rotate(torch.autograd.Function):
     """y = R(positions) · x and dx = Rᵀ · dy: the selection operator with the gate taken as given (no
@@ -116,15 +124,17 @@ class _Rotate(torch.autograd.Function):
         return dx, None
 
 
+@eager_only
 @on_tensor_device
 def apply_rope_1d(x: torch.Tensor, positions: torch.Tensor, freqs_cos: torch.Tensor,
                   freqs_sin: torch.Tensor) -> torch.Tensor:
     """Rotate-half 1-D rotary embedding: channel k pairs with k + D/2 (reference pom/pom_rope.py:152-180).
     x (B, N, D); positions (N,) int64; freqs_cos / freqs_sin (max_len, D // 2).  Returns (B, N, D)."""
     x = _rows(x)
-    return _Rotate.apply(x, _spec_1d(x, positions, freqs_cos, freqs_sin))
+    return _in_batch_slices(_Rotate.apply, x, _spec_1d(x, positions, freqs_cos, freqs_sin))
 
 
+@eager_only
 @on_tensor_device
 def apply_rope_2d(x: torch.Tensor, positions_hw: torch.Tensor, row_cos: torch.Tensor, row_sin: torch.Tensor,
                   col_cos: torch.Tensor, col_sin: torch.Tensor) -> torch.Tensor:
@@ -132,7 +142,7 @@ def apply_rope_2d(x: torch.Tensor, positions_hw: torch.Tensor, row_cos: torch.Te
     the column position, each half pairing k with k + D/4 (reference pom/pom_rope.py:183-235).
     x (B, N, D); positions_hw (N, 2) int64; row_* (max_h, D // 4); col_* (max_w, D // 4)."""
     x = _rows(x)
-    return _Rotate.apply(x, _spec_2d(x, positions_hw, row_cos, row_sin, col_cos, col_sin))
+    return _in_batch_slices(_Rotate.apply, x, _spec_2d(x, positions_hw, row_cos, row_sin, col_cos, col_sin))
 
 
 # --------------------------------------------------------------------------- per-token polynomial features
@@ -158,12 +168,14 @@ class _Features(torch.autograd.Function):
         return dx, (dc if ctx.cdt == torch.float32 else ops.to_bf16(dc))
 
 
+@eager_only
 def poly_features(x: torch.Tensor, coeff: torch.Tensor, k: int) -> torch.Tensor:
     """Per-token polynomial features (B, N, D) before any aggregation (the reference's ``_poly_features``)."""
     _check_degree(coeff, k)
-    return _Features.apply(x, coeff)
+    return _in_batch_slices(_Features.apply, x, coeff)
 
 
+@eager_only
 def pom_activation(x: torch.Tensor) -> torch.Tensor:
     """clamp(leaky_relu(x, 0.01), -0.1, 6) (reference pom/pom.py:27-28) for a (B, N, D) tensor: the degree-1
     feature with coefficient 1."""
@@ -171,7 +183,7 @@ def pom_activation(x: torch.Tensor) -> torch.Tensor:
     shape = x.shape
     if x.dim() != 3:  # any shape with the channels last
         x = x.reshape(1, -1, shape[-1]) if x.dim() < 3 else x.reshape(-1, shape[-2], shape[-1])
-    return _Features.apply(x, one).view(shape)
+    return _in_batch_slices(_Features.apply, x, one).view(shape)
 
 
 # --------------------------------------------------------------------------- fused aggregations
@@ -198,6 +210,7 @@ def poly_agg_masked(x: torch.Tensor, mask: torch.Tensor, coeff: torch.Tensor, k:
     return polynomial_aggregation_(x, coeff, k, mask)
 
 
+@eager_only
 @on_tensor_device
 def poly_agg_rope_mean(x: torch.Tensor, coeff: torch.Tensor, k: int, freqs_cos: torch.Tensor,
                        freqs_sin: torch.Tensor, positions: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -208,6 +221,7 @@ def poly_agg_rope_mean(x: torch.Tensor, coeff: torch.Tensor, k: int, freqs_cos: 
     return polynomial_aggregation_(x, coeff, k, None, rope=_spec_1d(x, positions, freqs_cos, freqs_sin))
 
 
+@eager_only
 @on_tensor_device
 def poly_agg_rope_causal(x: torch.Tensor, coeff: torch.Tensor, k: int, freqs_cos: torch.Tensor,
                          freqs_sin: torch.Tensor, positions: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -15,7 +15,7 @@ import torch
 import torch.nn as nn
 
 from . import ops
-from .functional import LayerSpec, SeqShard, _f32, _mask_kind, _ones, on_tensor_device, pom_layer
+from .functional import LayerSpec, SeqShard, _f32, _mask_kind, _ones, eager_only, on_tensor_device, pom_layer
 from .functional import polynomial_aggregation_, polynomial_selection_, pom  # noqa: F401  (defined here in the reference)
 from .operators import pom_activation  # noqa: F401
 
@@ -167,6 +167,7 @@ class PoM(nn.Module):
         return y if self.ag_proj.bias is None else y + self.ag_proj.bias
 
     # ------------------------------------------------------------------ API
+    @eager_only
     @on_tensor_device
     def forward(self, xq: torch.Tensor, xc: Optional[torch.Tensor] = None, mask=None,
                 shard: Optional[SeqShard] = None, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -182,6 +183,7 @@ class PoM(nn.Module):
                          self._residual(residual))
         return self._finish(y)
 
+    @eager_only
     @on_tensor_device
     def state_forward(self, xq: torch.Tensor, xc: Optional[torch.Tensor] = None,
                       state: Optional[Dict[str, Any]] = None,
@@ -212,6 +214,7 @@ class PoM(nn.Module):
                          self._residual(residual))
         return self._finish(y), {"h": h, "n": n_past + 1}
 
+    @eager_only
     @on_tensor_device
     @torch.no_grad()
     def ar_forward(self, xq: torch.Tensor, state: Dict[str, Any]) -> Tuple[torch.Tensor, Dict[str, Any]]:

@@ -14,7 +14,7 @@ from typing import Optional, Tuple
 import torch
 
 from . import _abi, ops
-from .functional import LayerSpec, SeqShard, _mask_kind, on_tensor_device, pom_layer
+from .functional import LayerSpec, SeqShard, _mask_kind, eager_only, on_tensor_device, pom_layer
 from .ops import RopeSpec
 from .operators import apply_rope_1d, apply_rope_2d  # noqa: F401  (the reference defines them in this module)
 from .pom import PoM
@@ -127,6 +127,7 @@ class PoMRoPE(PoM):
         steps = self._checked_steps(pos, (tabs[0].shape[0],))
         return RopeSpec(_abi.ROPE_1D, tabs[0], tabs[1], pos, steps=(steps[0], -1))
 
+    @eager_only
     @on_tensor_device
     def forward(self, xq: torch.Tensor, xc: Optional[torch.Tensor] = None, mask=None,
                 positions: Optional[torch.Tensor] = None, ctx_positions: Optional[torch.Tensor] = None,

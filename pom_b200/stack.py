@@ -16,7 +16,7 @@ import torch
 import torch.nn as nn
 
 from . import ops
-from .functional import BlockCausal, on_tensor_device
+from .functional import BlockCausal, eager_only, on_tensor_device
 from .pom import PoM
 
 
@@ -30,6 +30,7 @@ class PoMStack(nn.Module):
         self.ffn_in = nn.ModuleList([nn.Linear(dim, ffn_mult * dim, bias=False) for _ in range(n_layers)])
         self.ffn_out = nn.ModuleList([nn.Linear(ffn_mult * dim, dim, bias=False) for _ in range(n_layers)])
 
+    @eager_only
     @on_tensor_device
     @torch.no_grad()
     def frame_forward(self, x: torch.Tensor, states: Optional[List[Optional[dict]]] = None):
@@ -47,6 +48,7 @@ class PoMStack(nn.Module):
             h = ops.gemm(u, self.ffn_out[i].weight, residual=h2).view(B, L, D)
         return h, states
 
+    @eager_only
     @on_tensor_device
     @torch.no_grad()
     def forward_single_pass(self, x: torch.Tensor, frame_len: int) -> torch.Tensor:
@@ -64,6 +66,7 @@ class PoMStack(nn.Module):
             h = ops.gemm(u, self.ffn_out[i].weight, residual=h2).view(B, N, D)
         return h
 
+    @eager_only
     @on_tensor_device
     @torch.no_grad()
     def forward(self, x: torch.Tensor, frame_len: int) -> torch.Tensor:

@@ -222,6 +222,58 @@ def test_module_cast_after_first_use():
     assert torch.allclose(mod(x), y32, rtol=1e-5, atol=1e-6)
 
 
+@pytest.mark.parametrize("mask", [None, "causal"])
+@pytest.mark.parametrize("D,E,heads", [(16, 2, 8), (8, 1, 8), (24, 1, 3), (64, 2, 128)])
+def test_bf16_gate_heads_of_a_few_channels(D, E, heads, mask):
+    """Heads of 4, 1, 8 and 1 channels: too narrow for the batched tensor-core products of the collapsed form
+    (rows of head_dim elements), so the explicit per-head selection runs."""
+    params = O.init_params(D, 2, E, n_sel_heads=heads, seed=3, coeff_scale=0.1)
+    params = {k: O.bf16_round(v) for k, v in params.items()}
+    g = torch.Generator().manual_seed(4)
+    x, gy = O.bf16_round(torch.randn(3, 20, D, generator=g)), O.bf16_round(torch.randn(3, 20, D, generator=g))
+    cfg = dict(dim=D, degree=2, expand=E, heads=heads)
+    want_y, want_g = oracle_run(cfg, params, x, None, {"mask": mask}, gy)
+    mod = make_cuda_module(cfg, params, torch.bfloat16)
+    y, grads = cuda_run(mod, x, None, {"mask": mask}, gy, torch.bfloat16)
+    assert_close(y, want_y, BF16_TOL, "y")
+    for k, w in want_g.items():
+        assert_close(grads[k], w, BF16_TOL, f"d_{k}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("mask", [None, "causal", "block"])
+def test_more_samples_than_one_library_call_takes(mask, dtype):
+    """70 000 short sequences (windowed use): the sample index lives in a grid dimension of the operator kernels
+    (65 535 at most), so the layer runs the samples in slices; every sample equals its own small-batch result."""
+    from pom_b200 import BlockCausal, PoM
+
+    torch.manual_seed(0)
+    mod = PoM(8, 2, 2).cuda().to(dtype)
+    B = 70000 if mask != "block" else 35000  # 2 frames per sample: 70 000 (sample, frame) rows
+    x = torch.randn(B, 4, 8, device="cuda", dtype=dtype, requires_grad=True)
+    m = BlockCausal(2) if mask == "block" else mask
+    y = mod(x, mask=m)
+    y.float().sum().backward()
+    assert y.shape == (B, 4, 8) and bool(torch.isfinite(x.grad).all())
+    for sl in (slice(0, 3), slice(B - 3, B)):
+        assert torch.equal(y[sl], mod(x[sl], mask=m))
+
+
+def test_torch_compile_runs_the_layer_as_it_is():
+    """The library is called through ctypes, which a tracing compiler cannot follow: a compiled model takes a
+    graph break around the layer and gets the eager result."""
+    from pom_b200 import PoM
+
+    torch.manual_seed(0)
+    mod = PoM(64, 2, 2).cuda().bfloat16()
+    x = torch.randn(2, 64, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    want = mod(x)
+    got = torch.compile(mod)(x)
+    assert torch.equal(got, want)
+    got.float().sum().backward()
+    assert bool(torch.isfinite(x.grad).all())
+
+
 def test_empty_batch_gives_an_empty_result():
     """No sample, or no query token: the reference's PyTorch path returns an empty tensor; so does this one, and
     the backward pass gives the parameters zero gradients."""

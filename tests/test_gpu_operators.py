@@ -169,3 +169,22 @@ def test_pom_function(mask, heads):
     _compare(lambda s, x, coeff: pom(s, x, coeff, K, heads, mask),
              lambda s, x, coeff: O.selection(s, O.aggregate(O.poly_features(x, coeff), mask), heads),
              {"s": s, "x": xc, "coeff": c}, torch.float32)
+
+
+def test_operators_on_more_samples_than_one_library_call_takes():
+    from pom_b200 import polynomial_aggregation_, polynomial_selection_
+    from pom_b200.operators import apply_rope_1d, pom_activation
+
+    torch.manual_seed(5)
+    B = 70000
+    x = torch.randn(B, 3, 16, device="cuda")
+    c = torch.randn(16, 2, device="cuda") * 0.1
+    cos, sin = (t.cuda() for t in O.rope_tables_1d(16, 8))
+    pos = torch.arange(3, device="cuda")
+    full = [pom_activation(x), apply_rope_1d(x, pos, cos, sin), polynomial_aggregation_(x, c, 2, None),
+            polynomial_aggregation_(x, c, 2, "causal"), polynomial_selection_(torch.sigmoid(x), x[:, :1], 1)]
+    sl = slice(B - 4, B)
+    part = [pom_activation(x[sl]), apply_rope_1d(x[sl], pos, cos, sin), polynomial_aggregation_(x[sl], c, 2, None),
+            polynomial_aggregation_(x[sl], c, 2, "causal"), polynomial_selection_(torch.sigmoid(x[sl]), x[sl, :1], 1)]
+    for a, b in zip(full, part):
+        assert a.shape[0] == B and torch.equal(a[sl], b)
