@@ -14,7 +14,7 @@ from typing import Optional, Tuple
 import torch
 
 from . import _abi, ops
-from .functional import LayerSpec, SeqShard, _mask_kind, eager_only, on_tensor_device, pom_layer
+from .functional import LayerSpec, SeqShard, _derived_of, _mask_kind, eager_only, on_tensor_device, pom_layer
 from .ops import RopeSpec
 from .operators import apply_rope_1d, apply_rope_2d  # noqa: F401  (the reference defines them in this module)
 from .pom import PoM
@@ -75,19 +75,26 @@ class PoMRoPE(PoM):
 
     def _tables(self, for_gate: bool):
         """fp32 tables; for the per-head gate the columns are sub-sampled so that gate pair k rotates at the
-        leading frequency of head k (reference pom/pom_rope.py:417-437)."""
+        leading frequency of head k (reference pom/pom_rope.py:417-437).  Derived tables (an fp32 copy of buffers
+        that were cast with the module, the sub-sampled gate tables) are kept until their buffer changes."""
         names = ("row_cos", "row_sin", "col_cos", "col_sin") if self.rope_2d else ("freqs_cos", "freqs_sin")
-        tabs = [getattr(self, n).float() for n in names]
-        if for_gate and self.n_sel_heads > 1:
-            if self.rope_2d:
-                stride, keep = self.head_dim, self.n_sel_heads // 4
-            else:
-                stride, keep = self.head_dim // 2, self.n_sel_heads // 2
-            tabs = [t[:, ::stride][:, :keep] for t in tabs]
-            r = self._head_copies()
-            if r > 1:  # repeated gate heads: pair k of the r * heads wide gate is copy k % r of pair k // r
-                tabs = [t.repeat_interleave(r, dim=1) for t in tabs]
-        return [t.contiguous() for t in tabs]
+        sub = for_gate and self.n_sel_heads > 1
+        r = self._head_copies() if sub else 1
+        if self.rope_2d:
+            stride, keep = self.head_dim, self.n_sel_heads // 4
+        else:
+            stride, keep = self.head_dim // 2, self.n_sel_heads // 2
+
+        def make(t: torch.Tensor) -> torch.Tensor:
+            t = t.float()
+            if sub:
+                t = t[:, ::stride][:, :keep]
+                if r > 1:  # repeated gate heads: pair k of the r * heads wide gate is copy k % r of pair k // r
+                    t = t.repeat_interleave(r, dim=1)
+            return t.contiguous()
+
+        what = f"rope_table/{int(sub)}/{r}"
+        return [_derived_of(getattr(self, n), what, make) for n in names]
 
     def _default_positions(self, n_tokens: int, device) -> torch.Tensor:
         """0..n-1 on ``device``, one tensor per (length, device) so that its position scan is cached."""
