@@ -285,7 +285,13 @@ def check(code: int, where: str) -> None:
         raise PomError(code, where)
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def stream_ptr() -> C.c_void_p:
+    """The current device's current stream as the library's ``void* stream`` argument."""
+    if _raw_stream is not None:  # one C call instead of building a torch.cuda.Stream object
+        return C.c_void_p(_raw_stream(torch.cuda.current_device()))
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
