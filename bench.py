@@ -461,6 +461,37 @@ class Case:
             out.append(reduce_max(e0.elapsed_time(e1)) / steps)
         return out
 
+    def timed_with_grad_allreduce(self, steps, reps, sync_all, reduce_max, overlap=True):
+        """Data-parallel form of the batch-sharded step: as `timed`, plus an NCCL sum of every parameter gradient over
+        the ranks inside the timed region, on a side stream so that it runs beside the next step's kernels (what
+        DistributedDataParallel does with its buckets).  Returns (ms per step per repetition, bytes reduced per step)."""
+        import torch.distributed as dist
+
+        main, side = torch.cuda.current_stream(), torch.cuda.Stream()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        out, nbytes = [], 0
+        for _ in range(reps):
+            sync_all()
+            e0.record()
+            for i in range(steps):
+                _, grads = self.step(*self.dev_sets[i % len(self.dev_sets)])
+                # the layer returns its parameter gradients as views of one flat buffer: one collective for all
+                base = grads[1]._base
+                bufs = [base] if base is not None and all(g._base is base for g in grads[1:]) else list(grads[1:])
+                if overlap:
+                    side.wait_stream(main)
+                with torch.cuda.stream(side if overlap else main):
+                    for g in bufs:
+                        dist.all_reduce(g)
+                        if overlap:
+                            g.record_stream(side)
+                nbytes = sum(g.numel() * g.element_size() for g in bufs)
+            main.wait_stream(side)
+            e1.record()
+            sync_all()
+            out.append(reduce_max(e0.elapsed_time(e1)) / steps)
+        return out, nbytes
+
     def release(self):
         self.graphs = []
         self.dev_sets = []
@@ -575,6 +606,19 @@ def main():
     # key-padding workload: `value` counts padded tokens; the fraction of valid context tokens is reported beside it
     valid_frac = float(case.kw["mask"].float().mean().item()) if torch.is_tensor(case.kw.get("mask")) else None
 
+    # ---- the same batch-sharded step as data-parallel training: parameter gradients summed over the ranks
+    data_parallel = None
+    if world > 1 and not token and not video:
+        dp_rep, dp_bytes = case.timed_with_grad_allreduce(args.steps, min(args.reps, 5), sync_all, reduce_max)
+        dp_ms = statistics.median(dp_rep)
+        data_parallel = {
+            "ms_per_step": dp_ms, "ms_per_step_min": min(dp_rep), "ms_per_step_max": max(dp_rep),
+            "tokens_per_s": tokens_all / (dp_ms * 1e-3), "reps": len(dp_rep),
+            "grad_allreduce": "one NCCL sum of the flat bf16 parameter-gradient buffer over the ranks inside the timed "
+                              "region, on a side stream beside the next step's kernels",
+            "grad_bytes_per_rank_and_step": dp_bytes,
+        }
+
     # ---- end to end through the module API with host buffers (pinned), copies inside the timed region
     e2e = measure_e2e(case, args, device, world, sync_all, reduce_max)
 
@@ -624,6 +668,7 @@ def main():
                               "frac_of_burst_peak": fl / (ms_step * 1e-3) / 1e12 / peaks["burst"],
                               "peak_source": peaks["source"]},
             "headline_n4096": headline,
+            "data_parallel": data_parallel,
             "token_shard": shard_rec,
             "cpu_baseline": cpu,
             "e2e": e2e,
