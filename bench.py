@@ -492,6 +492,18 @@ class Case:
             out.append(reduce_max(e0.elapsed_time(e1)) / steps)
         return out, nbytes
 
+    def timed_with_peer_grad_sum(self, peer, steps, reps, sync_all, reduce_max):
+        """The data-parallel step with the library's own exchange: the backward pass of the layer accumulates the
+        parameter gradients in the peer-mapped region and sums them over the ranks itself (bf16 on the wire, the
+        all-reduce kernel also does the rounding that a cast kernel does otherwise).  Nothing else is added."""
+        self.kw["grad_peer"] = peer
+        try:
+            for i in range(3):
+                self.step(*self.dev_sets[i % len(self.dev_sets)])
+            return self.timed(steps, reps, sync_all, reduce_max)
+        finally:
+            del self.kw["grad_peer"]
+
     def release(self):
         self.graphs = []
         self.dev_sets = []
@@ -618,6 +630,19 @@ def main():
                               "region, on a side stream beside the next step's kernels",
             "grad_bytes_per_rank_and_step": dp_bytes,
         }
+        dp_peer = make_peer(w, world, device, rank) if args.exchange == "peer" else None
+        if dp_peer is not None:
+            pr = case.timed_with_peer_grad_sum(dp_peer, args.steps, min(args.reps, 5), sync_all, reduce_max)
+            pm = statistics.median(pr)
+            data_parallel["peer_kernels"] = {
+                "ms_per_step": pm, "ms_per_step_min": min(pr), "ms_per_step_max": max(pr),
+                "tokens_per_s": tokens_all / (pm * 1e-3), "reps": len(pr),
+                "grad_allreduce": "inside the layer's backward pass: fp32 accumulators in the peer-mapped region, summed "
+                                  "over the ranks by the library's all-reduce kernel with bf16 on the wire",
+                "peer_status_max_over_ranks": int(reduce_max(float(abs(_abi.read_status(device))))),
+            }
+            sync_all()
+            dp_peer.close()
 
     # ---- end to end through the module API with host buffers (pinned), copies inside the timed region
     e2e = measure_e2e(case, args, device, world, sync_all, reduce_max)

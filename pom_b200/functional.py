@@ -160,6 +160,9 @@ class LayerSpec:
     want_state: bool = False
     n_sel_heads: int = 1
     frames: int = 1                  # > 1: the batch rows are (sample, frame) pairs of a block-causal sequence
+    # data-parallel replicas: a peer.PeerExchange over which the parameter gradients are summed inside the backward
+    # pass (bf16 on the wire, straight from the fp32 accumulators; fused bf16 path only)
+    grad_peer: Any = None
 
 
 def _f32(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
@@ -323,6 +326,12 @@ class _PoMLayer(torch.autograd.Function):
         ctx.collapsed = False
         ctx.fused_causal = fused_causal
         ctx.composite = (fused or fused_causal) and shard is None and WHOLE_LAYER_CALLS
+        if spec.grad_peer is not None and need_grad:
+            if not ctx.composite or {w_qc.dtype, w_ag.dtype, se_bias.dtype, coeff.dtype} != {torch.bfloat16}:
+                raise NotImplementedError("grad_peer needs the fused bf16 path with bf16 parameters and no token shard")
+            if spec.grad_peer.flat_buffer((3 * P * D + P + P * K + 7) // 8 * 8) is None:
+                raise ValueError("the gradient region of grad_peer is smaller than this layer's parameters "
+                                 f"({3 * P * D + P + P * K} floats)")
         if ctx.composite:
             # the whole fused layer is one library call (no exchange to put between its phases)
             if spec.frames > 1 and (spec.n_past is not None or maskf is not None):
@@ -465,13 +474,20 @@ class _PoMLayer(torch.autograd.Function):
                 denom=denom, h_past=None if ctx.fused_causal else h_past32, n_past=spec.n_past, dh_state=dh32,
                 frames=spec.frames, want_d_hpast=bool(ctx.needs_input_grad[7]), rope_c=spec.rope_ctx,
                 rope_q=spec.rope_qry, w_ag_t=w_t, causal=h_past32 if ctx.fused_causal else None,
-                token_offset=ctx.dims[9])
+                token_offset=ctx.dims[9],
+                flat_out=None if spec.grad_peer is None else spec.grad_peer.flat_buffer(
+                    (3 * P * D + P + P * K + 7) // 8 * 8))
             if d_hpast is not None:
                 d_hpast = d_hpast.view(B, 1, P)
                 if ctx.h_past_dtype != torch.float32:
                     d_hpast = ops.to_bf16(d_hpast)
             n_qc, n_ag = 2 * P * D, D * P
-            f16 = ops.to_bf16(flat)
+            if spec.grad_peer is not None:
+                # summed over the replicas by the exchange's own kernel, which also does the rounding to bf16; the
+                # result image is copied out because the next layer's backward pass reuses it
+                f16 = ops.clone(spec.grad_peer.allreduce_flat_bf16(n_qc + n_ag + P + P * K))
+            else:
+                f16 = ops.to_bf16(flat)
             g_qc, g_ag = f16[:n_qc].view(2 * P, D), f16[n_qc:n_qc + n_ag].view(D, P)
             g_bias, g_coeff = f16[n_qc + n_ag:n_qc + n_ag + P], f16[n_qc + n_ag + P:].view(P, K)
             if p_bias.dtype == torch.float32:

@@ -451,11 +451,12 @@ def layer_fwd(xq, xc, w_qc, w_ag, bias, coeff, *, mask=None, h_past=None, n_past
 
 def layer_bwd(dy, xq, xc, w_qc, w_ag, bias, coeff, hp, z, sh, H, *, mask=None, denom=None, h_past=None, n_past=0.0,
               dh_state=None, frames=1, want_d_hpast=False, rope_c: Optional[RopeSpec] = None,
-              rope_q: Optional[RopeSpec] = None, w_ag_t: Optional[torch.Tensor] = None, causal=None, token_offset=0):
+              rope_q: Optional[RopeSpec] = None, w_ag_t: Optional[torch.Tensor] = None, causal=None, token_offset=0,
+              flat_out: Optional[torch.Tensor] = None):
     """Whole fused backward.  Returns (dxq, dxc or None, flat fp32 parameter gradients
     [dWqc | dWo | dbias | dcoeff], d_hpast (B, P) fp32 or None).  With ``rope_q`` or ``causal`` the transposed output
     weight ``w_ag_t`` (P, D) is required; ``causal`` = the running sums ``pre`` of the forward call, whose carries
-    come in ``H``."""
+    come in ``H``.  The flat buffer is zero-filled by the call."""
     dev = _require_cuda(dy, xq, xc, w_qc, w_ag, bias, coeff, hp, z, sh, H, mask, denom, h_past, dh_state, w_ag_t, causal)
     a, ws = _layer_args(xq, xc, w_qc, w_ag, bias, coeff, mask, h_past, n_past, frames, rope_c, rope_q,
                         causal is not None, token_offset)
@@ -465,7 +466,12 @@ def layer_bwd(dy, xq, xc, w_qc, w_ag, bias, coeff, hp, z, sh, H, *, mask=None, d
     G = torch.empty((B * T * 2 * P if xc is None else (B * N + B * T) * P,), **bf)
     dxq = torch.empty((B, T, D), **bf)
     dxc = None if xc is None else torch.empty((B, N, D), **bf)
-    flat = torch.empty((2 * P * D + D * P + P + P * K,), dtype=torch.float32, device=dev)
+    n_flat = 2 * P * D + D * P + P + P * K
+    flat = flat_out  # ``flat_out``: caller-owned fp32 accumulators (e.g. the gradient region of a peer exchange)
+    if flat is None:
+        flat = torch.empty((n_flat,), dtype=torch.float32, device=dev)
+    elif flat.dtype != torch.float32 or flat.numel() < n_flat or not flat.is_contiguous() or flat.device != dev:
+        raise ValueError(f"flat_out must be a contiguous float32 tensor of at least {n_flat} elements on {dev}")
     d_hpast = torch.empty((B, P), dtype=torch.float32, device=dev) if (want_d_hpast and h_past is not None) else None
     a.hp, a.z, a.sh, a.denom = ptr(hp), ptr(z), ptr(sh), ptr(denom)
     if causal is not None:

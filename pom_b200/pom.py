@@ -170,13 +170,17 @@ class PoM(nn.Module):
     @eager_only
     @on_tensor_device
     def forward(self, xq: torch.Tensor, xc: Optional[torch.Tensor] = None, mask=None,
-                shard: Optional[SeqShard] = None, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+                shard: Optional[SeqShard] = None, residual: Optional[torch.Tensor] = None,
+                grad_peer=None) -> torch.Tensor:
         """xq (B, T, D) queries; xc (B, N, D) context (None: self-mixing); mask None, "causal", (B, N), (B, T, N) or ``BlockCausal(frame_len)`` (extension).
 
         ``shard`` (extension) declares that xq/xc are this rank's token slice of a longer sequence;
-        ``residual`` (extension, bf16) is added to the output inside the output projection's epilogue.
+        ``residual`` (extension, bf16) is added to the output inside the output projection's epilogue;
+        ``grad_peer`` (extension): a ``peer.PeerExchange`` over data-parallel replicas — the backward pass sums the
+        parameter gradients over its ranks itself (bf16 on the wire), so no all-reduce is needed afterwards.
         """
         spec, m = self._spec(xq, xc, mask, shard)
+        spec.grad_peer = grad_peer
         w_qc, se_bias = self._weights()
         xq, xc = self._tokens(xq), (None if spec.self_mixing else self._tokens(xc))
         y, _ = pom_layer(xq, xc, w_qc, se_bias, self.po_coeff, self._out_weight(), m, None, spec,

@@ -139,10 +139,11 @@ class PoMRoPE(PoM):
     def forward(self, xq: torch.Tensor, xc: Optional[torch.Tensor] = None, mask=None,
                 positions: Optional[torch.Tensor] = None, ctx_positions: Optional[torch.Tensor] = None,
                 positions_hw: Optional[torch.Tensor] = None, ctx_positions_hw: Optional[torch.Tensor] = None,
-                shard: Optional[SeqShard] = None) -> torch.Tensor:
+                shard: Optional[SeqShard] = None, grad_peer=None) -> torch.Tensor:
         """As ``PoM.forward`` plus token positions: ``positions`` (T,) / ``ctx_positions`` (N,) int64 for
         1-D tables (default 0..T-1; the context defaults to the query positions under self-mixing, else
-        0..N-1), ``positions_hw`` (T, 2) / ``ctx_positions_hw`` (N, 2) for 2-D tables."""
+        0..N-1), ``positions_hw`` (T, 2) / ``ctx_positions_hw`` (N, 2) for 2-D tables.  ``shard`` and ``grad_peer``
+        (extensions) as in ``PoM.forward``."""
         self_mixing = xc is None or xc is xq
         kind = _mask_kind(mask)
         if kind == "block":
@@ -155,7 +156,7 @@ class PoMRoPE(PoM):
         same = self_mixing and ctx_positions is None and ctx_positions_hw is None and self.n_sel_heads <= 1
         rope_c = rope_q if same else self._rope_spec(N, cpos, cpos_hw, xq.device)
         spec = LayerSpec(degree=self.order, mask_kind=kind, self_mixing=self_mixing, rope_ctx=rope_c, rope_qry=rope_q,
-                         shard=shard, n_sel_heads=self._heads())
+                         shard=shard, n_sel_heads=self._heads(), grad_peer=grad_peer)
         w_qc, se_bias = self._weights()
         xq, xc = self._tokens(xq), (None if self_mixing else self._tokens(xc))
         y, _ = pom_layer(xq, xc, w_qc, se_bias, self.po_coeff, self._out_weight(),

@@ -1,6 +1,7 @@
 """The layer under torch.nn.parallel.DistributedDataParallel on two GPUs (batch sharding: the data-parallel use of
 the benchmark's default workload).  The loss is a mean over the rank's samples, so the parameter gradients that DDP
-averages over the ranks must equal the gradients of the whole batch's mean on one GPU.  Needs two devices."""
+averages over the ranks must equal the gradients of the whole batch's mean on one GPU; so must the sums that the
+layer's own gradient exchange (``grad_peer``) produces, divided by the number of ranks.  Needs two devices."""
 import os
 import socket
 
@@ -48,7 +49,22 @@ def _worker(rank, world, port, ret):
                 p.grad = None
             ddp(xs).float().square().mean().backward()
         got = [p.grad.float() for p in mod.parameters()]
-        ret[rank] = max(float((a - b).norm() / (b.norm() + 1e-20)) for a, b in zip(got, want))
+        worst = max(float((a - b).norm() / (b.norm() + 1e-20)) for a, b in zip(got, want))
+        # the same with the library's own exchange: the backward pass sums the gradients over the ranks itself
+        from pom_b200 import _abi
+        from pom_b200.peer import PeerExchange
+
+        n_params = sum(p.numel() for p in mod.parameters())
+        peer = PeerExchange(slot_floats=4096, flat_floats=n_params + 8)
+        for _ in range(2):
+            for p in mod.parameters():
+                p.grad = None
+            mod(xs, grad_peer=peer).float().square().mean().backward()
+        assert _abi.read_status(torch.device("cuda", rank)) == 0, "an exchange wait expired"
+        got = [p.grad.float() / world for p in mod.parameters()]  # sums over the ranks, where DDP averages
+        worst = max([worst] + [float((a - b).norm() / (b.norm() + 1e-20)) for a, b in zip(got, want)])
+        peer.close()
+        ret[rank] = worst
     finally:
         dist.destroy_process_group()
 
