@@ -183,3 +183,78 @@ def test_operator_module_carries_the_reference_names():
         operators.pom_activation(torch.randn(2, 3, 8))
     with pytest.raises(RuntimeError, match="no CPU path"):
         operators.apply_rope_1d(torch.randn(1, 4, 8), torch.arange(4), torch.ones(4, 4), torch.zeros(4, 4))
+
+
+def test_row_strides_ignore_dimensions_of_size_one():
+    """PyTorch reports arbitrary strides for dimensions of size 1; the leading dimension handed to the library must
+    not depend on them."""
+    import torch
+
+    from pom_b200.ops import _ld, _row_stride
+
+    wide = torch.zeros(3, 1, 12)
+    assert _row_stride(wide[..., :8]) == 12                    # (3, 1, 8) slice of rows that are 12 long
+    assert _row_stride(torch.zeros(1, 5, 12)[..., :8]) == 12   # one sample: the token stride decides
+    assert _row_stride(torch.zeros(1, 1, 12)[..., :8]) == 8    # a single row: any stride would do, the tight one
+    assert _row_stride(torch.zeros(1, 12)[:, :8]) == 8
+    assert _row_stride(torch.zeros(4, 12)[:, :8]) == 12
+    odd = torch.zeros(3, 1, 8).as_strided((3, 1, 8), (8, 999, 1))
+    assert _row_stride(odd) == 8 and _ld(odd, 1) == 8
+    with pytest.raises(ValueError):
+        _row_stride(torch.zeros(2, 6, 8)[:, :5])               # batch and token dimensions do not collapse
+
+
+def test_batch_slices_and_mask_operand():
+    import torch
+
+    from pom_b200 import functional as Fn
+
+    sl = Fn._batch_slices(70000)
+    assert [(s.start, s.stop) for s in sl] == [(0, 65535), (65535, 70000)]
+    assert [(s.start, s.stop) for s in Fn._batch_slices(10, 4)] == [(0, 4), (4, 8), (8, 10)]
+    assert Fn._batch_slices(5, 0)[0] == slice(0, 1)            # never an empty or endless cut
+    assert Fn._cut("causal", sl[0]) == "causal" and Fn._cut(None, sl[0]) is None
+    m = (torch.rand(2, 3, 37) < 0.5)
+    op = Fn._mask_operand(m, "cpu", torch.bfloat16)
+    assert op.shape == (2, 3, 37) and op.stride() == (3 * 40, 40, 1) and torch.equal(op.float(), m.float())
+    dense = Fn._mask_operand(torch.ones(2, 3, 40), "cpu", torch.float32)
+    assert dense.is_contiguous()
+    assert torch.equal(Fn._inv_rows(torch.tensor([0.0, 2.0, 4.0])), torch.tensor([0.0, 0.5, 0.25]))
+
+
+def test_gate_heads_are_repeated_up_to_a_multiple_of_eight_in_bf16():
+    """4 heads -> 8 (two copies each), 12 -> 24, 16 stays, fp32 stays; the repeated gate weight and bias keep every
+    copy next to its original, and the cache of the assembled projection follows in-place updates."""
+    import torch
+
+    from pom_b200 import PoM
+
+    for heads, want in ((4, 2), (12, 2), (16, 1), (6, 4), (3, 8)):
+        m = PoM(48, 2, 2, n_sel_heads=heads)
+        assert m._head_copies() == 1 and m._heads() == heads
+        m.bfloat16()
+        assert m._head_copies() == want and m._heads() == heads * want
+        with torch.no_grad():
+            w, b = m._weights()
+            assert w.shape == (96 + heads * want, 48) and b.shape == (heads * want,)
+            assert torch.equal(w[96:], m.qc_proj.weight[96:].repeat_interleave(want, 0))
+            if want > 1:
+                assert m._weights()[0] is w                    # kept while the parameters are unchanged
+                m.se_bias.add_(1.0)
+                assert torch.equal(m._weights()[1], m.se_bias.repeat_interleave(want))
+
+
+def test_grouped_bias_travels_as_an_input_channel():
+    import torch
+
+    from pom_b200 import PoM
+
+    m = PoM(16, 2, 2, n_groups=2, bias=True)
+    with torch.no_grad():
+        m.po_proj.bias.copy_(torch.arange(32.0))
+        w, _ = m._weights()
+    assert w.shape == (64, 24) and torch.equal(w[:32, 16], torch.arange(32.0)) and float(w[32:, 16:].abs().sum()) == 0
+    x = m._tokens(torch.zeros(2, 3, 16))
+    assert x.shape == (2, 3, 24) and float(x[..., 16].min()) == 1.0 and float(x[..., 17:].abs().sum()) == 0
+    assert m._out_weight().shape == (24, 32) and float(m._out_weight()[16:].detach().abs().sum()) == 0
+    assert PoM(16, 2, 2, n_groups=2)._tokens(torch.zeros(1, 1, 16)).shape == (1, 1, 16)
