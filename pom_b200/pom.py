@@ -15,7 +15,7 @@ import torch
 import torch.nn as nn
 
 from . import ops
-from .functional import LayerSpec, SeqShard, _f32, _mask_kind, _ones, eager_only, on_tensor_device, pom_layer
+from .functional import LayerSpec, SeqShard, _derived_of, _f32, _mask_kind, _ones, eager_only, on_tensor_device, pom_layer
 from .functional import polynomial_aggregation_, polynomial_selection_, pom  # noqa: F401  (defined here in the reference)
 from .operators import pom_activation  # noqa: F401
 
@@ -85,6 +85,27 @@ class PoM(nn.Module):
         one[0] = 1
         return torch.cat([x, one.expand(*x.shape[:-1], self._BIAS_COLS)], dim=-1)
 
+    @staticmethod
+    def _autocast_dtype() -> Optional[torch.dtype]:
+        """bfloat16 while CUDA autocast to bfloat16 is active, else None.  Under autocast the reference's Linear
+        layers compute in bf16 from fp32 master weights; so does this layer (tokens and projection weights are cast
+        on the way in, gradients come back in the parameters' own dtype)."""
+        try:
+            on, dt = torch.is_autocast_enabled("cuda"), torch.get_autocast_dtype("cuda")
+        except TypeError:  # older signature
+            on, dt = torch.is_autocast_enabled(), torch.get_autocast_gpu_dtype()
+        return dt if on and dt == torch.bfloat16 else None
+
+    def _cast(self, t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        """A token tensor or projection weight in the autocast dtype (unchanged outside autocast).  The cast of a
+        weight that needs no gradient is kept until the weight changes."""
+        dt = self._autocast_dtype()
+        if t is None or dt is None or t.dtype == dt or not t.is_floating_point():
+            return t
+        if isinstance(t, nn.Parameter) and not (torch.is_grad_enabled() and t.requires_grad):
+            return _derived_of(t, "autocast", lambda w: w.detach().to(dt))
+        return t.to(dt)
+
     def _head_copies(self) -> int:
         """How many adjacent copies of every gate head the CUDA path works with.  A bf16 gate projection needs
         rows of 16 bytes, that is a multiple of 8 heads; other head counts are brought there by repeating each row
@@ -92,7 +113,7 @@ class PoM(nn.Module):
         exactly as heads heads of head_dim channels, and autograd sums the copies' gradients."""
         h = self.n_sel_heads
         ws = self.qc_proj.weight if self.n_groups == 1 else self.se_proj.weight
-        if h <= 1 or ws.dtype != torch.bfloat16 or h % 8 == 0:
+        if h <= 1 or (self._autocast_dtype() or ws.dtype) != torch.bfloat16 or h % 8 == 0:
             return 1
         r = 8 // math.gcd(h, 8)
         if self._po_dim % (h * r):
@@ -153,7 +174,7 @@ class PoM(nn.Module):
     def _out_weight(self) -> torch.Tensor:
         """(D, P) output projection; with the bias channels, as many zero rows below it, so that the layer keeps
         one width on both sides (the extra outputs are 0 and ``_finish`` drops them)."""
-        w = self.ag_proj.weight
+        w = self._cast(self.ag_proj.weight)
         return torch.cat([w, w.new_zeros(self._BIAS_COLS, w.shape[1])], dim=0) if self._has_bias_cols() else w
 
     def _residual(self, r: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
@@ -164,7 +185,7 @@ class PoM(nn.Module):
     def _finish(self, y: torch.Tensor) -> torch.Tensor:
         if self._has_bias_cols():
             y = y[..., :self.dim]
-        return y if self.ag_proj.bias is None else y + self.ag_proj.bias
+        return y if self.ag_proj.bias is None else y + self.ag_proj.bias.to(y.dtype)
 
     # ------------------------------------------------------------------ API
     @eager_only
@@ -182,9 +203,9 @@ class PoM(nn.Module):
         spec, m = self._spec(xq, xc, mask, shard)
         spec.grad_peer = grad_peer
         w_qc, se_bias = self._weights()
-        xq, xc = self._tokens(xq), (None if spec.self_mixing else self._tokens(xc))
-        y, _ = pom_layer(xq, xc, w_qc, se_bias, self.po_coeff, self._out_weight(), m, None, spec,
-                         self._residual(residual))
+        xq, xc = self._tokens(self._cast(xq)), (None if spec.self_mixing else self._tokens(self._cast(xc)))
+        y, _ = pom_layer(xq, xc, self._cast(w_qc), se_bias, self.po_coeff, self._out_weight(), m, None, spec,
+                         self._residual(self._cast(residual)))
         return self._finish(y)
 
     @eager_only
@@ -213,9 +234,9 @@ class PoM(nn.Module):
         else:
             h_past = None
         w_qc, se_bias = self._weights()
-        xq, xc = self._tokens(xq), (None if spec.self_mixing else self._tokens(xc))
-        y, h = pom_layer(xq, xc, w_qc, se_bias, self.po_coeff, self._out_weight(), None, h_past, spec,
-                         self._residual(residual))
+        xq, xc = self._tokens(self._cast(xq)), (None if spec.self_mixing else self._tokens(self._cast(xc)))
+        y, h = pom_layer(xq, xc, self._cast(w_qc), se_bias, self.po_coeff, self._out_weight(), None, h_past, spec,
+                         self._residual(self._cast(residual)))
         return self._finish(y), {"h": h, "n": n_past + 1}
 
     @eager_only
@@ -228,11 +249,11 @@ class PoM(nn.Module):
         chunks use :meth:`state_forward`."""
         if not xq.is_cuda:
             raise RuntimeError("pom_b200 has no CPU path: move the module and its inputs to a CUDA device")
-        xq = self._tokens(xq)
+        xq = self._tokens(self._cast(xq))
         B, T, D = xq.shape
         w_qc, se_bias = self._weights()
         P, S = self._po_dim, se_bias.shape[0]
-        hs = ops.gemm(xq.contiguous().view(B * T, D), w_qc.contiguous()).view(B, T, P + S)
+        hs = ops.gemm(xq.contiguous().view(B * T, D), self._cast(w_qc).contiguous()).view(B, T, P + S)
         hp, z = hs[..., :P], hs[..., P:]
         bias32 = _f32(se_bias.contiguous())
         if self.n_sel_heads > 1:
@@ -240,7 +261,7 @@ class PoM(nn.Module):
             sh = ops.select_heads_fwd(s32, hp, xq.dtype)
         else:
             sh = ops.select_fwd(z, bias32, hp)
-        y = ops.gemm(sh.view(B * T, P), self.ag_proj.weight).view(B, T, self.dim)
+        y = ops.gemm(sh.view(B * T, P), self._cast(self.ag_proj.weight)).view(B, T, self.dim)
         return self._finish(y), {"max_len": state["max_len"], "h": hp, "n": state["n"] + T}
 
     def reset(self, state: Dict[str, Any]) -> Dict[str, Any]:

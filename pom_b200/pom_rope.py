@@ -158,7 +158,7 @@ class PoMRoPE(PoM):
         spec = LayerSpec(degree=self.order, mask_kind=kind, self_mixing=self_mixing, rope_ctx=rope_c, rope_qry=rope_q,
                          shard=shard, n_sel_heads=self._heads(), grad_peer=grad_peer)
         w_qc, se_bias = self._weights()
-        xq, xc = self._tokens(xq), (None if self_mixing else self._tokens(xc))
-        y, _ = pom_layer(xq, xc, w_qc, se_bias, self.po_coeff, self._out_weight(),
+        xq, xc = self._tokens(self._cast(xq)), (None if self_mixing else self._tokens(self._cast(xc)))
+        y, _ = pom_layer(xq, xc, self._cast(w_qc), se_bias, self.po_coeff, self._out_weight(),
                          mask if kind in ("keypad", "full") else None, None, spec)
         return self._finish(y)

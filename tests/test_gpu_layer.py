@@ -274,6 +274,52 @@ def test_torch_compile_runs_the_layer_as_it_is():
     assert bool(torch.isfinite(x.grad).all())
 
 
+@pytest.mark.parametrize("kind", ["plain", "causal", "heads4", "rope1d", "grouped_bias"])
+def test_bf16_autocast_with_fp32_master_weights(kind):
+    """Under torch.autocast(bfloat16) the reference's Linear layers compute in bf16 from fp32 parameters.  The layer
+    does the same: an fp32 module inside autocast equals a bf16 module holding the rounded weights, its output is
+    bf16 and its parameter gradients arrive in fp32."""
+    from pom_b200 import PoM, PoMRoPE
+
+    torch.manual_seed(0)
+    kw, mk = {}, {}
+    if kind == "causal":
+        kw["mask"] = "causal"
+    if kind == "rope1d":
+        make = lambda: PoMRoPE(64, 2, 2, max_seq_len=64)
+    elif kind == "grouped_bias":
+        make = lambda: PoM(64, 2, 2, n_groups=2, bias=True)
+    else:
+        make = lambda: PoM(64, 2, 2, n_sel_heads=4 if kind == "heads4" else 1)
+    master = make().cuda()
+    with torch.no_grad():
+        master.po_coeff.copy_(torch.randn_like(master.po_coeff) * 0.1)
+        for p_ in master.parameters():  # bf16-representable values, so that both modules hold the same numbers
+            p_.copy_(p_.bfloat16().float())
+    low = make().cuda()
+    low.load_state_dict(master.state_dict())
+    for p_ in low.parameters():
+        p_.data = p_.data.bfloat16()
+    x = torch.randn(2, 48, 64, device="cuda")
+    xm = x.clone().requires_grad_(True)
+    xl = x.bfloat16().requires_grad_(True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        ym = master(xm, **kw)
+    yl = low(xl, **kw)
+    assert ym.dtype == torch.bfloat16 and torch.equal(ym, yl)
+    g = torch.randn_like(yl)
+    ym.backward(g)
+    yl.backward(g)
+    assert xm.grad.dtype == torch.float32 and torch.equal(xm.grad, xl.grad.float())
+    for (n, pm), pl in zip(master.named_parameters(), low.parameters()):
+        assert pm.grad.dtype == torch.float32, n
+        assert_close(pm.grad, pl.grad.float().cpu(), 1e-2, f"d_{n}")  # fp32 accumulators rounded once to bf16 in `low`
+    with torch.autocast("cuda", dtype=torch.bfloat16), torch.no_grad():
+        assert torch.equal(master(x, **kw), yl)  # cached casts of the weights
+        master.ag_proj.weight.mul_(2.0)
+        assert not torch.equal(master(x, **kw), yl)
+
+
 def test_empty_batch_gives_an_empty_result():
     """No sample, or no query token: the reference's PyTorch path returns an empty tensor; so does this one, and
     the backward pass gives the parameters zero gradients."""
