@@ -185,12 +185,10 @@ def _derived_of(t: torch.Tensor, what: str, make):
     stamp = (t._version, t.data_ptr(), t.device, t.dtype)  # .data swaps (Module.to, casts) keep the version
     if ent is not None and ent[0]() is t and ent[1] == stamp:
         return ent[2]
-    if len(_derived) > 256:
-        for k in [k for k, e in _derived.items() if e[0]() is None]:
-            del _derived[k]
     with torch.inference_mode(False):  # a value cached under inference mode must stay usable by a later backward
         val = make(t)
-    _derived[key] = (weakref.ref(t), stamp, val)
+    # the entry (and the memory of its value) goes when the tensor does
+    _derived[key] = (weakref.ref(t, lambda _ref, k=key: _derived.pop(k, None)), stamp, val)
     return val
 
 

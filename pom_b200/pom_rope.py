@@ -101,6 +101,8 @@ class PoMRoPE(PoM):
         cache = self.__dict__.setdefault("_arange_cache", {})
         key = (n_tokens, str(device))
         if key not in cache:
+            if len(cache) >= 16:  # many distinct lengths (variable-length batches): do not let them pile up
+                cache.clear()
             with torch.inference_mode(False):  # an ordinary tensor, so that its position scan can be cached
                 cache[key] = torch.arange(n_tokens, device=device, dtype=torch.int64)
         return cache[key]
