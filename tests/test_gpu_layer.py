@@ -320,6 +320,45 @@ def test_bf16_autocast_with_fp32_master_weights(kind):
         assert not torch.equal(master(x, **kw), yl)
 
 
+def test_a_small_model_trains_and_memory_stays_flat():
+    """Two mixer blocks with fp32 master weights under bf16 autocast, AdamW, sequences of varying length: the loss of
+    a simple regression (reproduce the running mean of the tokens) falls, and device memory does not creep."""
+    import torch.nn as nn
+
+    from pom_b200 import PoM
+
+    torch.manual_seed(0)
+
+    class Block(nn.Module):
+        def __init__(self, d):
+            super().__init__()
+            self.norm, self.mix = nn.LayerNorm(d), PoM(d, 2, 2)
+
+        def forward(self, x):
+            return x + self.mix(self.norm(x), mask="causal").float()
+
+    model = nn.Sequential(Block(64), Block(64)).cuda()
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-3)
+    losses, mem = [], []
+    for it in range(120):
+        n = 64 + 8 * (it % 5)
+        x = torch.randn(8, n, 64, device="cuda")
+        target = x.cumsum(1) / torch.arange(1, n + 1, device="cuda").view(1, n, 1)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            y = model(x)
+        loss = (y - x - target).square().mean()
+        opt.zero_grad(set_to_none=True)
+        loss.backward()
+        opt.step()
+        losses.append(float(loss.detach()))
+        if it % 5 == 4:
+            mem.append(torch.cuda.memory_allocated())
+    assert_status_clean()
+    first, last = sum(losses[:10]) / 10, sum(losses[-10:]) / 10
+    assert last < 0.5 * first, (first, last)
+    assert max(mem[4:]) <= mem[3], mem  # after the first rounds over the five lengths nothing grows
+
+
 def test_empty_batch_gives_an_empty_result():
     """No sample, or no query token: the reference's PyTorch path returns an empty tensor; so does this one, and
     the backward pass gives the parameters zero gradients."""
