@@ -32,8 +32,13 @@ def _require_cuda(*tensors) -> torch.device:
 
 
 def _ld(t: torch.Tensor, dim: int) -> int:
-    """Stride of ``dim``, or the tight row length when that dimension has size 1 (its stride is arbitrary)."""
-    return t.stride(dim) if t.shape[dim] > 1 else t.shape[-1]
+    """Stride of ``dim``.  A dimension of size 1 may report any stride: it is kept when it is a usable leading
+    dimension (at least a row long, a multiple of 8 elements), else replaced by the row length rounded up to 8."""
+    s = t.stride(dim)
+    if t.shape[dim] > 1:
+        return s
+    w = t.shape[-1]
+    return s if (s >= w and s % 8 == 0) else (w + 7) // 8 * 8
 
 
 def _row_stride(t: torch.Tensor) -> int:

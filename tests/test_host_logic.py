@@ -200,6 +200,8 @@ def test_row_strides_ignore_dimensions_of_size_one():
     assert _row_stride(torch.zeros(4, 12)[:, :8]) == 12
     odd = torch.zeros(3, 1, 8).as_strided((3, 1, 8), (8, 999, 1))
     assert _row_stride(odd) == 8 and _ld(odd, 1) == 8
+    padded = torch.zeros(2, 1, 8)[..., :1]                      # one mask row of one element, rows padded to 8
+    assert _ld(padded, 1) == 8 and _ld(torch.zeros(2, 1, 3), 1) == 8 and _ld(torch.zeros(2, 5, 16), 1) == 16
     with pytest.raises(ValueError):
         _row_stride(torch.zeros(2, 6, 8)[:, :5])               # batch and token dimensions do not collapse
 
