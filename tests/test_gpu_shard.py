@@ -1,6 +1,8 @@
 """Token-sharded layer on two GPUs (NCCL or the peer-memory exchange kernels, eager and replayed from a CUDA
 graph): forward output, input gradient and the all-reduced parameter
-gradients of each rank's slice must match the single-GPU layer on the full sequence.  Needs two devices."""
+gradients of each rank's slice must match the single-GPU layer on the full sequence — the library against itself,
+which other tests pin to the oracle on one GPU — and, directly, the CPU oracle run on the whole sequence (2e-2).
+Needs two devices."""
 import os
 import socket
 
@@ -74,6 +76,20 @@ def _one_combo(rank, world, mask, rope2d, transport, peer):
         torch.cuda.synchronize()
     errs = [O.rel_errors(y_loc, y_full[:, lo:lo + n_loc])[0], O.rel_errors(g_loc[0], g_full[0][:, lo:lo + n_loc])[0]]
     errs += [O.rel_errors(a, b)[0] for a, b in zip(g_loc[1:], g_full[1:])]
+    # and against the CPU oracle on the whole sequence (fp32 on the same bf16-rounded values): this rank's slice of
+    # the output and of the input gradient, and the parameter gradients summed over the ranks
+    names = [n for n, _ in mod.named_parameters()]
+    ps = {n: p.detach().float().cpu().requires_grad_(True) for n, p in mod.named_parameters()}
+    rope = O.RopeConfig(two_d=True, max_seq_len=4096, max_h=side, max_w=side) if rope2d else None
+    xo = x.float().cpu().requires_grad_(True)
+    kw_o = {"mask": mask.cpu() if keypad else mask}
+    if rope2d:
+        kw_o["positions_hw"] = hw.cpu()
+    want = O.OraclePoM(ps, K, E, 1, rope).forward(xo, **kw_o)
+    want_g = torch.autograd.grad(want, [xo] + [ps[n] for n in names], gy.float().cpu())
+    errs_o = [O.rel_errors(y_loc, want[:, lo:lo + n_loc])[0], O.rel_errors(g_loc[0], want_g[0][:, lo:lo + n_loc])[0]]
+    errs_o += [O.rel_errors(a, b)[0] for a, b in zip(g_loc[1:], want_g[1:])]
+    assert max(errs_o) < 2e-2, (mask if not keypad else "keypad", rope2d, transport, errs_o)
     return max(errs)
 
 
