@@ -850,6 +850,10 @@ def polynomial_aggregation_(x: torch.Tensor, coeff: torch.Tensor, k: int, mask=N
         return torch.cat([polynomial_aggregation_(x[sl], coeff, k, _cut(mask, sl), rope)
                           for sl in _batch_slices(x.shape[0])], dim=0)
     if kind == "full":
+        if x.dtype == torch.bfloat16 and x.shape[-1] % 8:
+            # the tensor-core product mask · features reads rows of P bf16 values, which must start on 16-byte
+            # boundaries: other widths take the float32 form of the same operator
+            return _PolyAggFull.apply(x.float(), coeff.float(), mask, rope).to(x.dtype)
         return _PolyAggFull.apply(x, coeff, mask, rope)
     return _PolyAgg.apply(x, coeff, kind, mask if kind == "keypad" else None, rope)
 

@@ -93,3 +93,107 @@ def test_random_configurations_against_the_oracle(seed):
         if not all(bool(torch.isfinite(v.float()).all()) for v in grads.values()):
             failures.append(f"{desc}: a gradient is not finite")
     assert not failures, "\n".join(failures)
+
+
+def _operator_case(rng, case):
+    """One random call of an operator-level function: returns (description, oracle closure, CUDA closure, inputs)."""
+    from pom_b200 import operators as P
+    from pom_b200 import polynomial_aggregation_, polynomial_selection_
+
+    dtype = rng.choice([torch.bfloat16, torch.float32])
+    bf = dtype == torch.bfloat16
+    B, N, K = rng.randint(1, 4), rng.randint(1, 300), rng.randint(1, 16)
+    D = rng.choice([1, 2, 3, 4, 7, 8, 12, 16, 33, 48, 64, 96, 100, 128, 130, 256])
+    kind = rng.choice(["none", "causal", "keypad", "full", "rope_mean", "rope_causal", "features", "act", "rot1",
+                       "rot2", "select"])
+    g = torch.Generator().manual_seed(9000 + case)
+    rnd = lambda *shape: torch.randn(*shape, generator=g)
+    x, c = rnd(B, N, D) * 0.5, rnd(D, K) * (0.1 if K <= 4 else 0.02)
+    dev = lambda t: t.cuda()
+    second = "coeff"
+    if kind in ("none", "causal"):
+        m = None if kind == "none" else "causal"
+        ref = lambda x, c: O.aggregate(O.poly_features(x, c), m)
+        run = lambda x, c: polynomial_aggregation_(x, c, K, m)
+    elif kind == "keypad":
+        m = (torch.rand(B, N, generator=g) < 0.5).float()
+        m[:, 0] = 1
+        ref = lambda x, c: O.aggregate(O.poly_features(x, c), m)
+        run = lambda x, c: polynomial_aggregation_(x, c, K, dev(m))
+    elif kind == "full":
+        m = (torch.rand(B, rng.randint(1, 40), N, generator=g) < 0.5).float()
+        m[:, :, 0] = 1
+        ref = lambda x, c: O.aggregate(O.poly_features(x, c), m)
+        run = lambda x, c: polynomial_aggregation_(x, c, K, dev(m))
+    elif kind in ("rope_mean", "rope_causal", "rot1"):
+        if D % 2:
+            return None
+        cos, sin = O.rope_tables_1d(D, N + 9)
+        pos = torch.randint(0, N + 9, (N,), generator=g)
+        if kind == "rot1":
+            second = None
+            ref = lambda x, c: O.rope_apply_1d(x, pos, cos, sin)
+            run = lambda x, c: P.apply_rope_1d(x, dev(pos), dev(cos), dev(sin))
+        else:
+            m = None if kind == "rope_mean" else "causal"
+            fn = P.poly_agg_rope_mean_triton if m is None else P.poly_agg_rope_causal_triton
+            ref = lambda x, c: O.aggregate(O.rope_apply_1d(O.poly_features(x, c), pos, cos, sin), m)
+            run = lambda x, c: fn(x, c, K, dev(cos), dev(sin), dev(pos))
+    elif kind == "rot2":
+        if D % 4:
+            return None
+        hh, ww = rng.randint(1, 9), rng.randint(1, 9)
+        tabs = O.rope_tables_2d(D, hh, ww)
+        hw = torch.stack([torch.randint(0, hh, (N,), generator=g), torch.randint(0, ww, (N,), generator=g)], 1)
+        second = None
+        ref = lambda x, c: O.rope_apply_2d(x, hw, *tabs)
+        run = lambda x, c: P.apply_rope_2d(x, dev(hw), *[dev(t) for t in tabs])
+    elif kind == "features":
+        ref = lambda x, c: O.poly_features(x, c)
+        run = lambda x, c: P.poly_features(x, c, K)
+    elif kind == "act":
+        second = None
+        ref = lambda x, c: O.activation(x * 8)
+        run = lambda x, c: P.pom_activation(x * 8)
+    else:  # selection: x plays the gate, c the aggregate
+        heads = rng.choice([1, 1, 2, 4])
+        heads = heads if D % heads == 0 else 1
+        x = torch.rand(B, N, heads if heads > 1 else D, generator=g)
+        c = rnd(B, rng.choice([1, N]), D)
+        second = "aggregate"
+        ref = lambda x, c: O.selection(x, c, heads)
+        run = lambda x, c: polynomial_selection_(x, c, heads)
+    if bf:
+        x, c = O.bf16_round(x), O.bf16_round(c)
+    desc = f"#{case} {kind} {str(dtype)[6:]} B={B} N={N} D={D} K={K}"
+    return desc, dtype, ref, run, x, c, second, g
+
+
+def test_random_operator_calls_against_the_oracle():
+    """The operator-level functions (aggregation with every mask kind, the rotary forms, per-token features,
+    activation, rotation alone, selection) on random shapes — channel counts from 1 to 256 that are and are not
+    multiples of the vector widths, degrees 1 to 16 — in bf16 and fp32: forward and every gradient."""
+    rng = random.Random(0)
+    failures = []
+    for case in range(250):
+        drawn = _operator_case(rng, case)
+        if drawn is None:
+            continue
+        desc, dtype, ref, run, x, c, second, g = drawn
+        bf = dtype == torch.bfloat16
+        xr, cr = x.clone().requires_grad_(True), c.clone().requires_grad_(True)
+        xg, cg = x.cuda().to(dtype).requires_grad_(True), c.cuda().to(dtype).requires_grad_(True)
+        want, got = ref(xr, cr), run(xg, cg)
+        if got.shape != want.shape or got.dtype != dtype:
+            failures.append(f"{desc}: shape/dtype {tuple(got.shape)} {got.dtype} vs {tuple(want.shape)}")
+            continue
+        gy = torch.randn(want.shape, generator=g)
+        gy = O.bf16_round(gy) if bf else gy
+        ins_r, ins_g = ([xr, cr], [xg, cg]) if second else ([xr], [xg])
+        want_g = torch.autograd.grad(want, ins_r, gy)
+        got_g = torch.autograd.grad(got, ins_g, gy.cuda().to(dtype))
+        errs = [_rel(got.detach(), want.detach())]
+        errs += [_rel(a, b) for a, b in zip(got_g, want_g) if float(b.norm()) > 1e-6]
+        if not max(errs) <= (BF16_TOL if bf else 2 * FP32_TOL):
+            failures.append(f"{desc}: off by {[f'{e:.1e}' for e in errs]}")
+    assert not failures, "\n".join(failures)
