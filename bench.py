@@ -631,8 +631,13 @@ def main():
             "grad_bytes_per_rank_and_step": dp_bytes,
         }
         dp_peer = make_peer(w, world, device, rank) if args.exchange == "peer" else None
+        pr = None
         if dp_peer is not None:
-            pr = case.timed_with_peer_grad_sum(dp_peer, args.steps, min(args.reps, 5), sync_all, reduce_max)
+            try:
+                pr = case.timed_with_peer_grad_sum(dp_peer, args.steps, min(args.reps, 5), sync_all, reduce_max)
+            except NotImplementedError as e:  # raised on every rank alike, before anything is launched
+                data_parallel["peer_kernels"] = {"unavailable": str(e)}
+        if pr is not None:
             pm = statistics.median(pr)
             data_parallel["peer_kernels"] = {
                 "ms_per_step": pm, "ms_per_step_min": min(pr), "ms_per_step_max": max(pr),
@@ -641,6 +646,7 @@ def main():
                                   "over the ranks by the library's all-reduce kernel with bf16 on the wire",
                 "peer_status_max_over_ranks": int(reduce_max(float(abs(_abi.read_status(device))))),
             }
+        if dp_peer is not None:
             sync_all()
             dp_peer.close()
 
