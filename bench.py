@@ -470,10 +470,10 @@ class Case:
         main, side = torch.cuda.current_stream(), torch.cuda.Stream()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         out, nbytes = [], 0
-        for _ in range(reps):
+        for rep in range(-1, reps):  # repetition -1: three untimed steps (first use of the collective on this stream)
             sync_all()
             e0.record()
-            for i in range(steps):
+            for i in range(steps if rep >= 0 else 3):
                 _, grads = self.step(*self.dev_sets[i % len(self.dev_sets)])
                 # the layer returns its parameter gradients as views of one flat buffer: one collective for all
                 base = grads[1]._base
@@ -489,7 +489,8 @@ class Case:
             main.wait_stream(side)
             e1.record()
             sync_all()
-            out.append(reduce_max(e0.elapsed_time(e1)) / steps)
+            if rep >= 0:
+                out.append(reduce_max(e0.elapsed_time(e1)) / steps)
         return out, nbytes
 
     def timed_with_peer_grad_sum(self, peer, steps, reps, sync_all, reduce_max):
